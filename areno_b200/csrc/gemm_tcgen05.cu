@@ -1,0 +1,399 @@
+// bf16 GEMM family for sm_100a: TMA -> 128B-swizzled shared memory -> tcgen05.mma with the
+// fp32 accumulator in TMEM -> tcgen05.ld epilogue.  Persistent, warp-specialised:
+//   warp 0      TMA producer          (one lane issues)
+//   warp 1      MMA issuer + TMEM owner (one lane issues)
+//   warps 2..5  epilogue (each warp reads its own 32-lane quarter of TMEM)
+// The accumulator is double-buffered in TMEM so the epilogue of tile i overlaps the main
+// loop of tile i+1.
+//
+// Logical problem: D[M,N] = sum_k A(m,k) * B(n,k), with each operand either K-major
+// (memory [rows, K]) or MN-major (memory [K, rows]).  That covers the three linear-layer
+// products without any transpose pass:
+//   forward  Y  = X  W^T   : A = X  (K-major),  B = W (K-major)
+//   dgrad    dX = dY W     : A = dY (K-major),  B = W (MN-major)
+//   wgrad    dW = dY^T X   : A = dY (MN-major), B = X (MN-major), fp32 accumulate epilogue
+// Replaces the cublasGemmEx wrapper of the reference (areno/accel/csrc/linear.cu:73-249).
+#include "common.cuh"
+#include "launch.h"
+
+#include <mutex>
+#include <unordered_map>
+
+namespace areno {
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;
+constexpr int kGemmThreads = 192;
+
+struct GemmParams {
+  int M, N, K;
+  void* C;
+  long long ldc;
+  const void* bias;  // bf16 [N] or nullptr
+  int* status;
+  int tiles_m, tiles_n;
+  int epi;
+};
+
+template <int BN, int STAGES>
+struct GemmSmem {
+  static constexpr uint32_t kABytes = kBM * kBK * 2;
+  static constexpr uint32_t kBBytes = BN * kBK * 2;
+  static constexpr uint32_t kBarOffset = STAGES * (kABytes + kBBytes);
+  static constexpr uint32_t kTotal = kBarOffset + (2 * STAGES + 4) * 8 + 16 + 1024;  // + align slack
+};
+
+__device__ __forceinline__ void store_row_bf16(__nv_bfloat16* dst, const uint32_t (&r)[32], int ncols,
+                                               const __nv_bfloat16* bias) {
+  // dst points at 32 consecutive output columns of one row; ncols (<=32) of them are valid.
+  if (ncols == 32) {
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float a = __uint_as_float(r[v * 8 + 2 * j]);
+        float b = __uint_as_float(r[v * 8 + 2 * j + 1]);
+        if (bias != nullptr) {
+          a += __bfloat162float(bias[v * 8 + 2 * j]);
+          b += __bfloat162float(bias[v * 8 + 2 * j + 1]);
+        }
+        o[j] = pack_bf16x2(a, b);
+      }
+      *reinterpret_cast<uint4*>(dst + v * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      if (j < ncols) {
+        float a = __uint_as_float(r[j]);
+        if (bias != nullptr) a += __bfloat162float(bias[j]);
+        dst[j] = __float2bfloat16_rn(a);
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void store_row_f32(float* dst, const uint32_t (&r)[32], int ncols,
+                                              bool accumulate) {
+  if (ncols == 32) {
+#pragma unroll
+    for (int v = 0; v < 8; ++v) {
+      float4 o = make_float4(__uint_as_float(r[v * 4]), __uint_as_float(r[v * 4 + 1]),
+                             __uint_as_float(r[v * 4 + 2]), __uint_as_float(r[v * 4 + 3]));
+      float4* p = reinterpret_cast<float4*>(dst + v * 4);
+      if (accumulate) {
+        float4 c = *p;
+        o.x += c.x; o.y += c.y; o.z += c.z; o.w += c.w;
+      }
+      *p = o;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      if (j < ncols) {
+        float a = __uint_as_float(r[j]);
+        dst[j] = accumulate ? dst[j] + a : a;
+      }
+    }
+  }
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                 const GemmParams p) {
+  using S = GemmSmem<BN, STAGES>;
+  constexpr uint32_t NCOLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128
+                             : (2 * BN <= 256) ? 256 : 512;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * S::kABytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::kBarOffset);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, NCOLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_kb = (p.K + kBK - 1) / kBK;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const int m0 = (tile % p.tiles_m) * kBM;
+      const int n0 = (tile / p.tiles_m) * BN;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
+        if (lane == 0) {
+          mbar_expect_tx(&full_bar[stage], S::kABytes + S::kBBytes);
+          uint8_t* a_dst = sA + stage * S::kABytes;
+          uint8_t* b_dst = sB + stage * S::kBBytes;
+          const int k0 = kb * kBK;
+          if constexpr (A_MN) {
+#pragma unroll
+            for (int j = 0; j < kBM / 64; ++j)
+              tma_load_2d(a_dst + j * 8192, &tma_a, &full_bar[stage], m0 + j * 64, k0);
+          } else {
+            tma_load_2d(a_dst, &tma_a, &full_bar[stage], k0, m0);
+          }
+          if constexpr (B_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(b_dst + j * 8192, &tma_b, &full_bar[stage], n0 + j * 64, k0);
+          } else {
+            tma_load_2d(b_dst, &tma_b, &full_bar[stage], k0, n0);
+          }
+        }
+        __syncwarp();
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+      }
+    }
+    if (!ok) {
+      // Give copies already in flight time to land before the CTA's shared memory goes away.
+      for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    constexpr uint32_t idesc = make_idesc_bf16(kBM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+    int stage = 0;
+    uint32_t phase = 0;
+    uint32_t acc_phase[2] = {0, 0};
+    int acc = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      if (!mbar_wait(&tempty_bar[acc], acc_phase[acc] ^ 1u, abort_flag, p.status, 2)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 3)) { ok = false; break; }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t a_base = smem_u32(sA + stage * S::kABytes);
+          const uint32_t b_base = smem_u32(sB + stage * S::kBBytes);
+#pragma unroll
+          for (int kk = 0; kk < kBK / 16; ++kk) {
+            const uint64_t da = A_MN ? make_smem_desc_sw128(a_base + kk * 2048, 8192, 1024)
+                                     : make_smem_desc_sw128(a_base + kk * 32, 0, 1024);
+            const uint64_t db = B_MN ? make_smem_desc_sw128(b_base + kk * 2048, 8192, 1024)
+                                     : make_smem_desc_sw128(b_base + kk * 32, 0, 1024);
+            umma_f16(d_tmem, da, db, idesc, (kb | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
+        }
+        __syncwarp();
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+      }
+      if (!ok) break;
+      if (lane == 0) umma_commit(&tfull_bar[acc]);
+      __syncwarp();
+      acc_phase[acc] ^= 1u;
+      acc ^= 1;
+    }
+  } else {
+    // ------------------------------- epilogue ----------------------------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    uint32_t acc_phase[2] = {0, 0};
+    int acc = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const int m0 = (tile % p.tiles_m) * kBM;
+      const int n0 = (tile / p.tiles_m) * BN;
+      if (!mbar_wait(&tfull_bar[acc], acc_phase[acc], abort_flag, p.status, 4)) { ok = false; break; }
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                             static_cast<uint32_t>(acc * BN);
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c, r);
+        tmem_ld_wait();
+        const int col = n0 + c;
+        const int ncols = min(32, p.N - col);
+        if (row < p.M && ncols > 0) {
+          if (p.epi == 0 || p.epi == 1) {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col;
+            const __nv_bfloat16* bias =
+                p.epi == 1 ? reinterpret_cast<const __nv_bfloat16*>(p.bias) + col : nullptr;
+            store_row_bf16(dst, r, ncols, bias);
+          } else {
+            float* dst = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col;
+            store_row_f32(dst, r, ncols, p.epi == 3);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      acc_phase[acc] ^= 1u;
+      acc ^= 1;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, NCOLS);
+}
+
+// ------------------------------- host side ---------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  });
+  return fn;
+}
+
+int make_tensor_map_2d_bf16(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer,
+                            uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return -1;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {row_stride_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
+static int num_sms() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream) {
+  using S = GemmSmem<BN, STAGES>;
+  auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  int grid = p.tiles_m * p.tiles_n;
+  if (grid > num_sms()) grid = num_sms();
+  kern<<<grid, kGemmThreads, S::kTotal, stream>>>(ta, tb, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+template <bool A_MN, bool B_MN>
+static int dispatch_bn(int bn, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
+                       cudaStream_t stream) {
+  switch (bn) {
+    case 256: return launch_gemm<256, 4, A_MN, B_MN>(ta, tb, p, stream);
+    case 128: return launch_gemm<128, 6, A_MN, B_MN>(ta, tb, p, stream);
+    case 64: return launch_gemm<64, 8, A_MN, B_MN>(ta, tb, p, stream);
+    case 32:
+      if constexpr (!B_MN) return launch_gemm<32, 10, A_MN, B_MN>(ta, tb, p, stream);
+      return -2;
+    default: return -2;
+  }
+}
+
+static int pick_bn(int M, int N, bool b_mn) {
+  const int sms = num_sms();
+  const int tiles_m = (M + kBM - 1) / kBM;
+  const int cands[4] = {256, 128, 64, 32};
+  // Per-tile efficiency of the main loop relative to BN=256 (B-operand reuse shrinks with BN).
+  const float tile_eff[4] = {1.0f, 0.92f, 0.75f, 0.5f};
+  int best = 64;
+  float best_score = -1.f;
+  for (int i = 0; i < 4; ++i) {
+    const int bn = cands[i];
+    if (b_mn && bn < 64) continue;
+    const long tiles = (long)tiles_m * ((N + bn - 1) / bn);
+    const long waves = (tiles + sms - 1) / sms;
+    const float wave_eff = (float)tiles / (float)(waves * sms);
+    const float score = wave_eff * tile_eff[i];
+    if (score > best_score) { best_score = score; best = bn; }
+  }
+  return best;
+}
+
+}  // namespace areno
+
+using namespace areno;
+
+extern "C" int areno_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
+                               long long lda, long long ldb, long long ldc, int a_mn, int b_mn, int epi, int bn,
+                               int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda % 8) != 0 || (ldb % 8) != 0) return -3;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
+      (reinterpret_cast<uintptr_t>(C) & 15))
+    return -3;
+  if (epi <= 1 ? (ldc % 8) != 0 : (ldc % 4) != 0) return -3;
+  if (bn <= 0) bn = pick_bn(M, N, b_mn != 0);
+  if (b_mn && bn < 64) bn = 64;
+  CUtensorMap ta, tb;
+  int rc;
+  if (a_mn) rc = make_tensor_map_2d_bf16(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, 64, 64);
+  else rc = make_tensor_map_2d_bf16(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, 64, kBM);
+  if (rc != 0) return rc;
+  if (b_mn) rc = make_tensor_map_2d_bf16(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, 64);
+  else rc = make_tensor_map_2d_bf16(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, 64, (uint32_t)bn);
+  if (rc != 0) return rc;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.C = C; p.ldc = ldc; p.bias = bias; p.status = status;
+  p.tiles_m = (M + kBM - 1) / kBM;
+  p.tiles_n = (N + bn - 1) / bn;
+  p.epi = epi;
+  if (a_mn) {
+    if (b_mn) return dispatch_bn<true, true>(bn, ta, tb, p, stream);
+    return dispatch_bn<true, false>(bn, ta, tb, p, stream);
+  }
+  if (b_mn) return dispatch_bn<false, true>(bn, ta, tb, p, stream);
+  return dispatch_bn<false, false>(bn, ta, tb, p, stream);
+}

@@ -1,0 +1,133 @@
+"""ctypes loader for ``libareno_kernels.so`` (the sm_100a kernel library).
+
+The library exposes a flat C ABI (see ``csrc/launch.h``).  Python passes raw device pointers
+(``tensor.data_ptr()``) and the current CUDA stream handle; nothing here allocates.
+
+On a machine with a GPU a missing library is a hard error: ops never fall back to eager
+PyTorch for CUDA tensors.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import threading
+from typing import Any
+
+import torch
+
+_SIG_CODES = {
+    "p": ctypes.c_void_p,
+    "i": ctypes.c_int,
+    "l": ctypes.c_longlong,
+    "f": ctypes.c_float,
+}
+
+# name -> argument type codes (p = pointer, i = int, l = long long, f = float); all return int.
+_SIGNATURES: dict[str, str] = {
+    "areno_gemm_bf16": "ppppiiillliiiipp",
+    "areno_rmsnorm_fwd": "pppifppplifp",
+    "areno_rmsnorm_bwd_blocks": "l",
+    "areno_rmsnorm_bwd": "pppifpppppilip",
+    "areno_gated_act_fwd": "ppliip",
+    "areno_gated_act_bwd": "pppliip",
+    "areno_unary_act": "pppliip",
+    "areno_rope": "pppliiilffip",
+    "areno_embedding_fwd": "ppplillfp",
+    "areno_embedding_bwd": "ppplillfp",
+    "areno_accumulate_bf16": "pplp",
+    "areno_attn_fwd": "pppppppp" + "iiiii" + "llll" + "fiip",
+    "areno_attn_bwd": "pppppppppp" + "pppp" + "iii" + "l" + "iii" + "llllllll" + "fiip",
+}
+
+_lock = threading.Lock()
+_cdll: ctypes.CDLL | None = None
+_load_error: str | None = None
+
+
+def register_signature(name: str, codes: str) -> None:
+    """Declare the argument types of another exported symbol (used by sibling op modules)."""
+    _SIGNATURES[name] = codes
+
+
+def _load() -> ctypes.CDLL:
+    global _cdll, _load_error
+    if _cdll is not None:
+        return _cdll
+    with _lock:
+        if _cdll is not None:
+            return _cdll
+        from areno_b200 import build
+
+        path = build.kernels_lib_path()
+        try:
+            build.build_kernels()
+        except Exception as exc:  # pragma: no cover - depends on toolchain
+            if not path.exists():
+                _load_error = f"kernel library is not built and could not be built: {exc}"
+                raise RuntimeError(_load_error) from exc
+        _cdll = ctypes.CDLL(str(path))
+        return _cdll
+
+
+def available() -> bool:
+    """True when the kernel library can be loaded (does not require a GPU)."""
+    try:
+        _load()
+        return True
+    except Exception:
+        return False
+
+
+_fn_cache: dict[str, Any] = {}
+
+
+def fn(name: str):
+    f = _fn_cache.get(name)
+    if f is None:
+        lib = _load()
+        f = getattr(lib, name)
+        codes = _SIGNATURES[name]
+        f.argtypes = [_SIG_CODES[c] for c in codes]
+        f.restype = ctypes.c_int
+        _fn_cache[name] = f
+    return f
+
+
+def call(name: str, *args) -> int:
+    """Invoke an entry point and raise on a non-zero return code."""
+    rc = fn(name)(*args)
+    if rc != 0:
+        raise RuntimeError(f"{name} failed with code {rc}")
+    return rc
+
+
+def ptr(t: torch.Tensor | None):
+    return None if t is None else t.data_ptr()
+
+
+def stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+_status: dict[int, torch.Tensor] = {}
+
+
+def status_buffer(device: torch.device) -> torch.Tensor:
+    """Per-device int32[4] status words written by kernels whose bounded waits ran out."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    buf = _status.get(idx)
+    if buf is None:
+        buf = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", idx))
+        _status[idx] = buf
+    return buf
+
+
+def check_status(device: torch.device | None = None) -> None:
+    """Synchronising check of the status words; raises if any kernel reported an error."""
+    for idx, buf in list(_status.items()):
+        if device is not None and device.index not in (None, idx):
+            continue
+        vals = buf.tolist()
+        if vals[0] != 0:
+            buf.zero_()
+            raise RuntimeError(f"device kernel reported status code={vals[0]} block={vals[1]} stage={vals[2]}")

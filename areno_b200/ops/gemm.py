@@ -1,0 +1,135 @@
+"""bf16 GEMM on the tcgen05 tensor cores and the ``linear`` autograd op built on it.
+
+``gemm`` computes ``D[M,N] = sum_k A(m,k) B(n,k)``.  Each operand may be stored K-major
+(``[rows, K]``) or MN-major (``[K, rows]``), which gives forward, dgrad and wgrad of a linear
+layer without transposes.  The wgrad can accumulate straight into an fp32 ``main_grad``
+buffer in the kernel epilogue.
+
+Counterpart of ``areno/accel/linear.py`` and ``areno/accel/csrc/linear.cu:147-249`` in the
+reference (a cuBLAS wrapper there; a hand-written TMA + tcgen05 + TMEM kernel here).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+EPI_BF16 = 0
+EPI_BF16_BIAS = 1
+EPI_F32 = 2
+EPI_F32_ACC = 3
+
+
+def _gemm_reference(a, b, a_mn, b_mn, bias, out, accumulate, out_dtype):
+    am = a.t() if a_mn else a
+    bm = b.t() if b_mn else b
+    d = am.float() @ bm.float().t()
+    if bias is not None:
+        d = d + bias.float()
+    if out is not None:
+        if accumulate:
+            out.add_(d.to(out.dtype))
+        else:
+            out.copy_(d.to(out.dtype))
+        return out
+    return d.to(out_dtype)
+
+
+def gemm(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    *,
+    a_mn: bool = False,
+    b_mn: bool = False,
+    bias: torch.Tensor | None = None,
+    out: torch.Tensor | None = None,
+    accumulate: bool = False,
+    out_dtype: torch.dtype = torch.bfloat16,
+    bn: int = 0,
+) -> torch.Tensor:
+    """``D = A · Bᵀ`` in the logical (row, K) view of both operands.
+
+    a: ``[M, K]`` (or ``[K, M]`` when ``a_mn``), b: ``[N, K]`` (or ``[K, N]`` when ``b_mn``).
+    ``out`` may be bf16 or fp32; ``accumulate`` (fp32 only) adds into it.
+    """
+    if not a.is_cuda:
+        return _gemm_reference(a, b, a_mn, b_mn, bias, out, accumulate, out_dtype)
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, "gemm operands must be bf16"
+    assert a.dim() == 2 and b.dim() == 2
+    if a.stride(1) != 1:
+        a = a.contiguous()
+    if b.stride(1) != 1:
+        b = b.contiguous()
+    if a_mn:
+        k, m = a.shape
+    else:
+        m, k = a.shape
+    if b_mn:
+        kb, n = b.shape
+    else:
+        n, kb = b.shape
+    assert k == kb, f"contraction mismatch {k} vs {kb}"
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype, device=a.device)
+    else:
+        assert out.shape == (m, n) and out.stride(1) == 1
+    if out.dtype == torch.bfloat16:
+        assert not accumulate, "accumulate requires an fp32 output"
+        epi = EPI_BF16_BIAS if bias is not None else EPI_BF16
+    else:
+        assert out.dtype == torch.float32 and bias is None
+        epi = EPI_F32_ACC if accumulate else EPI_F32
+    if m == 0 or n == 0:
+        return out
+    if bias is not None:
+        assert bias.dtype == torch.bfloat16 and bias.is_contiguous() and bias.numel() == n
+    status = _lib.status_buffer(a.device)
+    _lib.call(
+        "areno_gemm_bf16",
+        a.data_ptr(), b.data_ptr(), out.data_ptr(), _lib.ptr(bias),
+        m, n, k, a.stride(0), b.stride(0), out.stride(0),
+        int(a_mn), int(b_mn), epi, bn, status.data_ptr(), _lib.stream(),
+    )
+    return out
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        y = gemm(x2, weight, bias=bias)
+        ctx.save_for_backward(x2, weight)
+        ctx.has_bias = bias is not None
+        ctx.in_shape = shape
+        return y.view(*shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if dy2.stride(1) != 1 or (dy2.stride(0) % 8) != 0:
+            dy2 = dy2.contiguous()
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, weight, b_mn=True).view(ctx.in_shape)
+        if ctx.needs_input_grad[1]:
+            main_grad = getattr(weight, "main_grad", None)
+            if main_grad is not None:
+                # fused fp32 accumulation: main_grad += dyᵀ x, no bf16 grad tensor is materialised
+                gemm(dy2, x2, a_mn=True, b_mn=True, out=main_grad, accumulate=True)
+                weight.grad_added_to_main_grad = True
+                dw = None
+            else:
+                dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=torch.float32).to(weight.dtype)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.float().sum(0).to(dy2.dtype)
+        return dx, dw, db
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """``y = x Wᵀ (+ b)`` with tcgen05 forward, dgrad and wgrad."""
+    if not x.is_cuda:
+        return torch.nn.functional.linear(x, weight, bias)
+    return _Linear.apply(x, weight, bias)
