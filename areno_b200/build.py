@@ -48,6 +48,8 @@ NVCC_FLAGS = [
 
 def _sources(suffixes: tuple[str, ...], subdir: str = "") -> list[Path]:
     base = CSRC / subdir if subdir else CSRC
+    if not base.is_dir():
+        return []
     return sorted(p for p in base.iterdir() if p.suffix in suffixes and p.is_file())
 
 

@@ -1,0 +1,453 @@
+// Paged-KV decode attention and the RoPE + KV-append kernel that feeds it (sm_100a).
+//
+// Cache layout (per layer): K and V pages [num_pages, kv_heads, page_size, head_dim], either
+// bf16 or fp8-e4m3 with one fp32 scale per (page, kv_head, slot) stored in a parallel
+// [num_pages, kv_heads, page_size] table (the scale of a token never changes once written, so
+// appends never requantise a page).
+//
+// Decode: one CTA per (sequence, kv head, split).  All q heads of the GQA group share each K/V
+// tile (padded to the 16-row MMA tile), so the cache is read once per group rather than once
+// per q head.  Pages stream through a 3-stage cp.async pipeline; fp8 pages are dequantised to
+// bf16 in shared memory before the MMAs.  Split partials are merged by a second kernel.
+// Everything is driven by device-side `seq_lens` / `block_table`, so the launch shape is static
+// and the kernel is CUDA-graph friendly.
+//
+// Replaces flash_attn_with_kvcache (areno/engine/layers/attention_backend/infer.py:172-178) and the
+// reference's scalar paged kernels (areno/accel/csrc/attention.cu:526-702).
+#include "attention_common.cuh"
+#include "launch.h"
+
+#include <cuda_fp8.h>
+
+namespace areno {
+
+constexpr int kPage = 64;  // tokens per page (also the key tile)
+
+// ---------------------------------------------------------------------------------
+// RoPE (neox / interleaved, partial allowed) on q and k in place + append k, v to the cache.
+// One warp per (token, head).  Heads [0, hq) are q (rotate only), [hq, hq+hkv) are k (rotate,
+// write back, append), [hq+hkv, hq+2hkv) are v (append).  slot_mapping[t] < 0 skips the append.
+// ---------------------------------------------------------------------------------
+template <bool FP8>
+__global__ void __launch_bounds__(256)
+rope_append_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions,
+                   const int* __restrict__ slot_mapping, const float* __restrict__ inv_freq, void* __restrict__ k_cache,
+                   void* __restrict__ v_cache, float* __restrict__ k_scale, float* __restrict__ v_scale, long long tokens,
+                   int hq, int hkv, int D, int rot_dim, float theta, int interleaved, int page_size) {
+  const int heads = hq + 2 * hkv;
+  const long long w = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (w >= tokens * heads) return;
+  const int lane = threadIdx.x & 31;
+  const long long t = w / heads;
+  const int h = (int)(w % heads);
+  __nv_bfloat16* p = qkv + t * (long long)heads * D + (long long)h * D;
+  const bool is_v = h >= hq + hkv;
+  const bool is_k = !is_v && h >= hq;
+  if (!is_v && rot_dim > 0) {
+    const int half = rot_dim >> 1;
+    const float pos = (float)positions[t];
+    for (int i = lane; i < half; i += 32) {
+      const float f = inv_freq != nullptr ? inv_freq[i] : __powf(theta, -2.f * (float)i / (float)rot_dim);
+      float s, c;
+      sincosf(pos * f, &s, &c);
+      const int i0 = interleaved ? 2 * i : i;
+      const int i1 = interleaved ? 2 * i + 1 : i + half;
+      const float a = __bfloat162float(p[i0]), b = __bfloat162float(p[i1]);
+      p[i0] = __float2bfloat16_rn(a * c - b * s);
+      p[i1] = __float2bfloat16_rn(b * c + a * s);
+    }
+    __syncwarp();
+  }
+  if (!is_k && !is_v) return;
+  const int slot = slot_mapping[t];
+  if (slot < 0) return;
+  const int kvh = is_k ? h - hq : h - hq - hkv;
+  const int page = slot / page_size, off = slot % page_size;
+  const long long row = ((long long)page * hkv + kvh) * page_size + off;
+  void* cache = is_k ? k_cache : v_cache;
+  if constexpr (FP8) {
+    float amax = 0.f;
+    for (int i = lane; i < D; i += 32) amax = fmaxf(amax, fabsf(__bfloat162float(p[i])));
+    amax = warp_max(amax);
+    const float sc = fmaxf(amax, 1e-8f) / 448.f;
+    const float inv = 1.f / sc;
+    __nv_fp8_e4m3* dst = reinterpret_cast<__nv_fp8_e4m3*>(cache) + row * D;
+    for (int i = lane; i < D; i += 32) dst[i] = __nv_fp8_e4m3(__bfloat162float(p[i]) * inv);
+    if (lane == 0) (is_k ? k_scale : v_scale)[row] = sc;
+  } else {
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(cache) + row * D;
+    for (int i = lane * 2; i < D; i += 64)
+      *reinterpret_cast<uint32_t*>(dst + i) = *reinterpret_cast<const uint32_t*>(p + i);
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// Decode attention.
+// ---------------------------------------------------------------------------------
+template <int D, bool FP8>
+struct DecodeSmem {
+  static constexpr int kStages = 3;
+  static constexpr int kTile = kPage * D * 2;                 // bf16 tile bytes
+  static constexpr int kRaw = FP8 ? kPage * D : 0;            // fp8 staging bytes
+  static constexpr int kStageBytes = FP8 ? 2 * kRaw + 2 * kPage * 4 : 2 * kTile;
+  static constexpr int kDeq = FP8 ? 2 * kTile : 0;            // dequantised K, V tiles
+  static constexpr int kQ = 16 * D * 2;
+  static constexpr int kMerge = 4 * 16 * (D + 2) * 4;         // per-warp partial O, m, l (fp32)
+  // the merge buffer aliases the (by then idle) pipeline stages
+  static_assert(kMerge <= kStages * kStageBytes, "merge buffer must fit in the stage area");
+  static constexpr int kTotal = kStages * kStageBytes + kDeq + kQ;
+};
+
+template <int D, bool FP8>
+__global__ void __launch_bounds__(128)
+paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const void* __restrict__ k_cache,
+                    const void* __restrict__ v_cache, const float* __restrict__ k_scale,
+                    const float* __restrict__ v_scale, const int* __restrict__ block_table,
+                    const int* __restrict__ seq_lens, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
+                    float* __restrict__ part_ml, int hq, int hkv, int max_pages, long long q_stride,
+                    long long o_stride, float scale, int pages_per_split, int nsplit, int window) {
+  using SM = DecodeSmem<D, FP8>;
+  constexpr int CH = D / 8;
+  extern __shared__ __align__(128) uint8_t smem_attn[];
+  uint8_t* stage_base = smem_attn;
+  __nv_bfloat16* deqK = reinterpret_cast<__nv_bfloat16*>(smem_attn + SM::kStages * SM::kStageBytes);
+  __nv_bfloat16* deqV = deqK + kPage * D;
+  __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_attn + SM::kStages * SM::kStageBytes + SM::kDeq);
+  float* sMerge = reinterpret_cast<float*>(stage_base);
+
+  const int b = blockIdx.x;
+  const int group = hq / hkv;
+  const int gtiles = (group + 15) / 16;
+  const int kvh = blockIdx.y / gtiles;
+  const int gt = blockIdx.y % gtiles;
+  const int split = blockIdx.z;
+  const int ctx = seq_lens[b];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int rows_valid = min(16, group - gt * 16);
+  const int head0 = kvh * group + gt * 16;
+
+  int first_key = 0;
+  if (window > 0) first_key = max(0, ctx - window);
+  const int total_pages = (ctx + kPage - 1) / kPage;
+  const int page_lo = max(split * pages_per_split, first_key / kPage);
+  const int page_hi = min(total_pages, (split + 1) * pages_per_split);
+  const int n_pages = max(0, page_hi - page_lo);
+
+  // Q tile: 16 rows (q heads of the group, zero padded) x D
+  for (int idx = threadIdx.x; idx < 16 * CH; idx += 128) {
+    const int r = idx / CH, ch = idx % CH;
+    uint4 val = make_uint4(0, 0, 0, 0);
+    if (r < rows_valid) val = *reinterpret_cast<const uint4*>(q + (long long)b * q_stride + (long long)(head0 + r) * D + ch * 8);
+    *reinterpret_cast<uint4*>(sQ + swz<CH>(r, ch)) = val;
+  }
+
+  auto issue = [&](int pi, int st) {
+    const int page = block_table[(long long)b * max_pages + page_lo + pi];
+    uint8_t* sb = stage_base + st * SM::kStageBytes;
+    if constexpr (FP8) {
+      const uint8_t* kp = reinterpret_cast<const uint8_t*>(k_cache) + ((long long)page * hkv + kvh) * kPage * D;
+      const uint8_t* vp = reinterpret_cast<const uint8_t*>(v_cache) + ((long long)page * hkv + kvh) * kPage * D;
+      for (int idx = threadIdx.x; idx < kPage * D / 16; idx += 128) {
+        cp_async16(sb + idx * 16, kp + idx * 16);
+        cp_async16(sb + SM::kRaw + idx * 16, vp + idx * 16);
+      }
+      if (threadIdx.x < kPage / 4) {
+        const long long srow = ((long long)page * hkv + kvh) * kPage;
+        cp_async16(sb + 2 * SM::kRaw + threadIdx.x * 16, k_scale + srow + threadIdx.x * 4);
+        cp_async16(sb + 2 * SM::kRaw + kPage * 4 + threadIdx.x * 16, v_scale + srow + threadIdx.x * 4);
+      }
+    } else {
+      const __nv_bfloat16* kp = reinterpret_cast<const __nv_bfloat16*>(k_cache) + ((long long)page * hkv + kvh) * kPage * D;
+      const __nv_bfloat16* vp = reinterpret_cast<const __nv_bfloat16*>(v_cache) + ((long long)page * hkv + kvh) * kPage * D;
+      load_tile_async<D, kPage>(reinterpret_cast<__nv_bfloat16*>(sb), kp, D, kPage);
+      load_tile_async<D, kPage>(reinterpret_cast<__nv_bfloat16*>(sb + SM::kTile), vp, D, kPage);
+    }
+  };
+
+#pragma unroll
+  for (int s = 0; s < SM::kStages - 1; ++s) {
+    if (s < n_pages) issue(s, s);
+    cp_async_commit();
+  }
+
+  float o_acc[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const float scale_log2 = scale * 1.4426950408889634f;
+
+  for (int pi = 0; pi < n_pages; ++pi) {
+    const int st = pi % SM::kStages;
+    if (pi + SM::kStages - 1 < n_pages) issue(pi + SM::kStages - 1, (pi + SM::kStages - 1) % SM::kStages);
+    cp_async_commit();
+    cp_async_wait<SM::kStages - 1>();
+    __syncthreads();
+    const uint8_t* sb = stage_base + st * SM::kStageBytes;
+    const __nv_bfloat16* cK;
+    const __nv_bfloat16* cV;
+    if constexpr (FP8) {
+      const float* ks = reinterpret_cast<const float*>(sb + 2 * SM::kRaw);
+      const float* vs = ks + kPage;
+      for (int idx = threadIdx.x; idx < kPage * CH; idx += 128) {
+        const int r = idx / CH, ch = idx % CH;
+        const uint2 rk = *reinterpret_cast<const uint2*>(sb + r * D + ch * 8);
+        const uint2 rv = *reinterpret_cast<const uint2*>(sb + SM::kRaw + r * D + ch * 8);
+        const float sk = ks[r], sv = vs[r];
+        uint32_t ok[4], ov[4];
+        const __nv_fp8x2_storage_t* pk = reinterpret_cast<const __nv_fp8x2_storage_t*>(&rk);
+        const __nv_fp8x2_storage_t* pv = reinterpret_cast<const __nv_fp8x2_storage_t*>(&rv);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const __half2_raw hk = __nv_cvt_fp8x2_to_halfraw2(pk[j], __NV_E4M3);
+          const __half2_raw hv = __nv_cvt_fp8x2_to_halfraw2(pv[j], __NV_E4M3);
+          const float2 fk = __half22float2(*reinterpret_cast<const __half2*>(&hk));
+          const float2 fv = __half22float2(*reinterpret_cast<const __half2*>(&hv));
+          ok[j] = pack_bf16x2(fk.x * sk, fk.y * sk);
+          ov[j] = pack_bf16x2(fv.x * sv, fv.y * sv);
+        }
+        *reinterpret_cast<uint4*>(deqK + swz<CH>(r, ch)) = make_uint4(ok[0], ok[1], ok[2], ok[3]);
+        *reinterpret_cast<uint4*>(deqV + swz<CH>(r, ch)) = make_uint4(ov[0], ov[1], ov[2], ov[3]);
+      }
+      __syncthreads();
+      cK = deqK;
+      cV = deqV;
+    } else {
+      cK = reinterpret_cast<const __nv_bfloat16*>(sb);
+      cV = reinterpret_cast<const __nv_bfloat16*>(sb + SM::kTile);
+    }
+
+    // this warp: keys [warp*16, warp*16+16) of the page
+    const int key0 = (page_lo + pi) * kPage + warp * 16;
+    if (key0 < ctx && key0 + 16 > first_key) {
+      float s[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        uint32_t a[4], bb[4];
+        ldsm_a<CH>(a, sQ, 0, ks * 2, lane);
+        ldsm_b_nt<CH>(bb, cK, warp * 16, ks * 2, lane);
+        mma_bf16(s[0], a, bb[0], bb[1]);
+        mma_bf16(s[1], a, bb[2], bb[3]);
+      }
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int c = key0 + nt * 8 + t4 * 2 + (e & 1);
+          if (c >= ctx || c < first_key) s[nt][e] = -INFINITY;
+          mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
+        }
+      float corr[2], m_use[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+        const float mn = fmaxf(m_run[h], mx[h]);
+        m_use[h] = mn == -INFINITY ? 0.f : mn;
+        corr[h] = exp2f((m_run[h] - m_use[h]) * scale_log2);
+        m_run[h] = mn;
+      }
+      uint32_t pf[4];
+      float rs[2] = {0.f, 0.f};
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        const float p0 = exp2f((s[nt][0] - m_use[0]) * scale_log2);
+        const float p1 = exp2f((s[nt][1] - m_use[0]) * scale_log2);
+        const float p2 = exp2f((s[nt][2] - m_use[1]) * scale_log2);
+        const float p3 = exp2f((s[nt][3] - m_use[1]) * scale_log2);
+        rs[0] += p0 + p1;
+        rs[1] += p2 + p3;
+        pf[nt * 2 + 0] = pack_bf16x2(p0, p1);
+        pf[nt * 2 + 1] = pack_bf16x2(p2, p3);
+      }
+      l_run[0] = l_run[0] * corr[0] + rs[0];
+      l_run[1] = l_run[1] * corr[1] + rs[1];
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) {
+        o_acc[i][0] *= corr[0]; o_acc[i][1] *= corr[0];
+        o_acc[i][2] *= corr[1]; o_acc[i][3] *= corr[1];
+      }
+#pragma unroll
+      for (int dt = 0; dt < D / 16; ++dt) {
+        uint32_t bb[4];
+        ldsm_b_t<CH>(bb, cV, warp * 16, dt * 2, lane);
+        mma_bf16(o_acc[2 * dt], pf, bb[0], bb[1]);
+        mma_bf16(o_acc[2 * dt + 1], pf, bb[2], bb[3]);
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // ---- merge the 4 warps' partials (each covered different keys) ----
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+  }
+  float* wbuf = sMerge + warp * 16 * (D + 2);
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = g + h * 8;
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      wbuf[r * (D + 2) + i * 8 + t4 * 2] = o_acc[i][h * 2];
+      wbuf[r * (D + 2) + i * 8 + t4 * 2 + 1] = o_acc[i][h * 2 + 1];
+    }
+    if (t4 == 0) {
+      wbuf[r * (D + 2) + D] = m_run[h];
+      wbuf[r * (D + 2) + D + 1] = l_run[h];
+    }
+  }
+  __syncthreads();
+  // 128 threads: thread -> (row r = tid / 8, column group cg = tid % 8 covering D/8 columns)
+  {
+    const int r = threadIdx.x >> 3, cg = threadIdx.x & 7;
+    if (r < rows_valid) {
+      float mw[4], lw[4], mmax = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        mw[w] = sMerge[(w * 16 + r) * (D + 2) + D];
+        lw[w] = sMerge[(w * 16 + r) * (D + 2) + D + 1];
+        mmax = fmaxf(mmax, mw[w]);
+      }
+      float wgt[4], ltot = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        wgt[w] = mw[w] == -INFINITY ? 0.f : exp2f((mw[w] - mmax) * scale_log2);
+        ltot += lw[w] * wgt[w];
+      }
+      const int head = head0 + r;
+      if (nsplit == 1) {
+        const float inv = ltot > 0.f ? 1.f / ltot : 0.f;
+        __nv_bfloat16* op = out + (long long)b * o_stride + (long long)head * D;
+        for (int c = cg * (D / 8); c < (cg + 1) * (D / 8); ++c) {
+          float acc = 0.f;
+#pragma unroll
+          for (int w = 0; w < 4; ++w) acc += sMerge[(w * 16 + r) * (D + 2) + c] * wgt[w];
+          op[c] = __float2bfloat16_rn(acc * inv);
+        }
+      } else {
+        float* po = part_o + (((long long)b * hq + head) * nsplit + split) * D;
+        for (int c = cg * (D / 8); c < (cg + 1) * (D / 8); ++c) {
+          float acc = 0.f;
+#pragma unroll
+          for (int w = 0; w < 4; ++w) acc += sMerge[(w * 16 + r) * (D + 2) + c] * wgt[w];
+          po[c] = acc;
+        }
+        if (cg == 0) {
+          float* pml = part_ml + (((long long)b * hq + head) * nsplit + split) * 2;
+          pml[0] = mmax;
+          pml[1] = ltot;
+        }
+      }
+    }
+  }
+}
+
+// Merge split partials: one warp per (sequence, q head).
+__global__ void __launch_bounds__(256)
+decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out,
+                    int batch, int hq, int D, int nsplit, long long o_stride, float scale) {
+  const int w = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (w >= batch * hq) return;
+  const int lane = threadIdx.x & 31;
+  const int b = w / hq, head = w % hq;
+  const float* pml = part_ml + (long long)w * nsplit * 2;
+  const float scale_log2 = scale * 1.4426950408889634f;
+  float mmax = -INFINITY;
+  for (int s = 0; s < nsplit; ++s) mmax = fmaxf(mmax, pml[s * 2]);
+  float ltot = 0.f;
+  for (int s = 0; s < nsplit; ++s) {
+    const float m = pml[s * 2];
+    ltot += m == -INFINITY ? 0.f : pml[s * 2 + 1] * exp2f((m - mmax) * scale_log2);
+  }
+  const float inv = ltot > 0.f ? 1.f / ltot : 0.f;
+  for (int c = lane; c < D; c += 32) {
+    float acc = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+      const float m = pml[s * 2];
+      if (m == -INFINITY) continue;
+      acc += part_o[((long long)w * nsplit + s) * D + c] * exp2f((m - mmax) * scale_log2);
+    }
+    out[(long long)b * o_stride + (long long)head * D + c] = __float2bfloat16_rn(acc * inv);
+  }
+}
+
+template <int D, bool FP8>
+static int launch_decode(const void* q, const void* k_cache, const void* v_cache, const float* k_scale,
+                         const float* v_scale, const int* block_table, const int* seq_lens, void* out, float* part_o,
+                         float* part_ml, int batch, int hq, int hkv, int max_pages, long long q_stride,
+                         long long o_stride, float scale, int pages_per_split, int nsplit, int window,
+                         cudaStream_t stream) {
+  using SM = DecodeSmem<D, FP8>;
+  static bool cfg = false;
+  if (!cfg) {
+    cudaFuncSetAttribute(paged_decode_kernel<D, FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kTotal);
+    cfg = true;
+  }
+  const int group = hq / hkv;
+  dim3 grid(batch, hkv * ((group + 15) / 16), nsplit);
+  paged_decode_kernel<D, FP8><<<grid, 128, SM::kTotal, stream>>>(
+      (const __nv_bfloat16*)q, k_cache, v_cache, k_scale, v_scale, block_table, seq_lens, (__nv_bfloat16*)out, part_o,
+      part_ml, hq, hkv, max_pages, q_stride, o_stride, scale, pages_per_split, nsplit, window);
+  if (nsplit > 1)
+    decode_merge_kernel<<<(batch * hq + 7) / 8, 256, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, batch, hq, D,
+                                                                 nsplit, o_stride, scale);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace areno
+
+using namespace areno;
+
+extern "C" int areno_page_size() { return kPage; }
+
+extern "C" int areno_rope_append_kv(void* qkv, const int* positions, const int* slot_mapping, const float* inv_freq,
+                                    void* k_cache, void* v_cache, float* k_scale, float* v_scale, long long tokens,
+                                    int hq, int hkv, int head_dim, int rot_dim, float theta, int interleaved,
+                                    int page_size, int fp8, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  const long long nw = tokens * (hq + 2 * hkv);
+  const unsigned grid = (unsigned)((nw + 7) / 8);
+  if (fp8)
+    rope_append_kernel<true><<<grid, 256, 0, stream>>>((__nv_bfloat16*)qkv, positions, slot_mapping, inv_freq, k_cache,
+                                                       v_cache, k_scale, v_scale, tokens, hq, hkv, head_dim, rot_dim,
+                                                       theta, interleaved, page_size);
+  else
+    rope_append_kernel<false><<<grid, 256, 0, stream>>>((__nv_bfloat16*)qkv, positions, slot_mapping, inv_freq, k_cache,
+                                                        v_cache, k_scale, v_scale, tokens, hq, hkv, head_dim, rot_dim,
+                                                        theta, interleaved, page_size);
+  return (int)cudaGetLastError();
+}
+
+// part_o: fp32 [batch, hq, nsplit, D]; part_ml: fp32 [batch, hq, nsplit, 2] (only used when nsplit > 1).
+extern "C" int areno_paged_decode(const void* q, const void* k_cache, const void* v_cache, const float* k_scale,
+                                  const float* v_scale, const int* block_table, const int* seq_lens, void* out,
+                                  float* part_o, float* part_ml, int batch, int hq, int hkv, int head_dim,
+                                  int max_pages, long long q_stride, long long o_stride, float scale,
+                                  int pages_per_split, int nsplit, int window, int fp8, cudaStream_t stream) {
+  if (batch <= 0) return 0;
+  if (hq % hkv != 0) return -3;
+  if (head_dim == 128) {
+    if (fp8)
+      return launch_decode<128, true>(q, k_cache, v_cache, k_scale, v_scale, block_table, seq_lens, out, part_o,
+                                      part_ml, batch, hq, hkv, max_pages, q_stride, o_stride, scale, pages_per_split,
+                                      nsplit, window, stream);
+    return launch_decode<128, false>(q, k_cache, v_cache, k_scale, v_scale, block_table, seq_lens, out, part_o, part_ml,
+                                     batch, hq, hkv, max_pages, q_stride, o_stride, scale, pages_per_split, nsplit,
+                                     window, stream);
+  }
+  if (head_dim == 64) {
+    if (fp8)
+      return launch_decode<64, true>(q, k_cache, v_cache, k_scale, v_scale, block_table, seq_lens, out, part_o, part_ml,
+                                     batch, hq, hkv, max_pages, q_stride, o_stride, scale, pages_per_split, nsplit,
+                                     window, stream);
+    return launch_decode<64, false>(q, k_cache, v_cache, k_scale, v_scale, block_table, seq_lens, out, part_o, part_ml,
+                                    batch, hq, hkv, max_pages, q_stride, o_stride, scale, pages_per_split, nsplit,
+                                    window, stream);
+  }
+  return -2;
+}

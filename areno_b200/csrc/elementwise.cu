@@ -134,6 +134,95 @@ rmsnorm_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x, const void* __restr
   }
 }
 
+// Per-head RMSNorm on strided [token, head, D] views (q/k norm inside a packed QKV buffer):
+// row r -> token r / heads, head r % heads; element offset token * stride + head * D.  D <= 256.
+__global__ void __launch_bounds__(256)
+headnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, long long x_stride, const void* __restrict__ w, int wf32,
+                    float w_offset, __nv_bfloat16* __restrict__ y, long long y_stride, float* __restrict__ inv_rms,
+                    long long rows, int heads, int D, float eps) {
+  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const long long t = row / heads;
+  const int hd = (int)(row % heads);
+  const int nvec = D >> 3;
+  float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  float ss = 0.f;
+  if (lane < nvec) {
+    load8(x + t * x_stride + (long long)hd * D + lane * 8, v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
+  }
+  ss = warp_sum(ss);
+  const float inv = rsqrtf(ss / (float)D + eps);
+  if (lane == 0 && inv_rms != nullptr) inv_rms[row] = inv;
+  if (lane < nvec) {
+    float wv[8], o[8];
+    load8w(w, wf32, lane * 8, wv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = v[j] * inv * (wv[j] + w_offset);
+    store8(y + t * y_stride + (long long)hd * D + lane * 8, o);
+  }
+}
+
+// Backward of the per-head norm.  dx may alias dy (in place).  dW partials: one row of
+// `dw_partial[gridDim.x, D]` per block (warps of a block are folded through shared memory).
+__global__ void __launch_bounds__(256)
+headnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, long long dy_stride, const __nv_bfloat16* __restrict__ x,
+                    long long x_stride, const void* __restrict__ w, int wf32, float w_offset,
+                    const float* __restrict__ inv_rms, __nv_bfloat16* __restrict__ dx, long long dx_stride,
+                    float* __restrict__ dw_partial, long long rows, int heads, int D) {
+  __shared__ float sdw[8][256];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nvec = D >> 3;
+  float wv[8], dwacc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { dwacc[j] = 0.f; wv[j] = 0.f; }
+  if (lane < nvec) {
+    load8w(w, wf32, lane * 8, wv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) wv[j] += w_offset;
+  }
+  for (long long row = (long long)blockIdx.x * 8 + warp; row < rows; row += (long long)gridDim.x * 8) {
+    const long long t = row / heads;
+    const int hd = (int)(row % heads);
+    const float inv = inv_rms[row];
+    float d[8], xv[8], g[8];
+    float dot = 0.f;
+    if (lane < nvec) {
+      load8(dy + t * dy_stride + (long long)hd * D + lane * 8, d);
+      load8(x + t * x_stride + (long long)hd * D + lane * 8, xv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        dwacc[j] += d[j] * xv[j] * inv;
+        g[j] = d[j] * wv[j];
+        dot += g[j] * xv[j];
+      }
+    }
+    dot = warp_sum(dot);
+    const float c = dot / (float)D * inv * inv;
+    if (lane < nvec) {
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = inv * (g[j] - xv[j] * c);
+      store8(dx + t * dx_stride + (long long)hd * D + lane * 8, o);
+    }
+  }
+  if (dw_partial != nullptr) {
+    if (lane < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) sdw[warp][lane * 8 + j] = dwacc[j];
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < D; c += 256) {
+      float s = 0.f;
+#pragma unroll
+      for (int ww = 0; ww < 8; ++ww) s += sdw[ww][c];
+      dw_partial[(size_t)blockIdx.x * D + c] = s;
+    }
+  }
+}
+
 // RMSNorm backward.  Persistent blocks; each block keeps a partial dW in registers over
 // its rows and writes it to `dw_partial[block, H]` (fp32 scratch); a second kernel folds
 // the partials, so the result does not depend on atomics ordering.
@@ -508,5 +597,38 @@ extern "C" int areno_embedding_bwd(const long long* ids, const void* dout, float
 extern "C" int areno_accumulate_bf16(float* acc, const void* g, long long n, cudaStream_t stream) {
   if (n <= 0) return 0;
   accumulate_bf16_kernel<<<grid_for(n, 256), 256, 0, stream>>>(acc, (const __nv_bfloat16*)g, n);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int areno_headnorm_fwd(const void* x, long long x_stride, const void* w, int wf32, float w_offset, void* y,
+                                  long long y_stride, float* inv_rms, long long tokens, int heads, int D, float eps,
+                                  cudaStream_t stream) {
+  const long long rows = tokens * heads;
+  if (rows <= 0) return 0;
+  if (D % 8 != 0 || D > 256) return -3;
+  headnorm_fwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(
+      (const __nv_bfloat16*)x, x_stride, w, wf32, w_offset, (__nv_bfloat16*)y, y_stride, inv_rms, rows, heads, D, eps);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int areno_headnorm_bwd_blocks(long long rows) {
+  long long b = (rows + 7) / 8;
+  if (b > 592) b = 592;
+  return (int)(b < 1 ? 1 : b);
+}
+
+extern "C" int areno_headnorm_bwd(const void* dy, long long dy_stride, const void* x, long long x_stride,
+                                  const void* w, int wf32, float w_offset, const float* inv_rms, void* dx,
+                                  long long dx_stride, float* dw_partial, float* dw, int dw_accumulate,
+                                  long long tokens, int heads, int D, cudaStream_t stream) {
+  const long long rows = tokens * heads;
+  if (rows <= 0) return 0;
+  if (D % 8 != 0 || D > 256) return -3;
+  const int grid = areno_headnorm_bwd_blocks(rows);
+  headnorm_bwd_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)dy, dy_stride, (const __nv_bfloat16*)x, x_stride,
+                                                w, wf32, w_offset, inv_rms, (__nv_bfloat16*)dx, dx_stride, dw_partial,
+                                                rows, heads, D);
+  if (dw_partial != nullptr && dw != nullptr)
+    colsum_partials_kernel<<<(D + 255) / 256, 256, 0, stream>>>(dw_partial, dw, grid, D, dw_accumulate);
   return (int)cudaGetLastError();
 }

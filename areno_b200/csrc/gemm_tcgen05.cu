@@ -33,6 +33,9 @@ struct GemmParams {
   int* status;
   int tiles_m, tiles_n;
   int epi;
+  int splits;         // split-K factor (1 = none); split s covers k-blocks [s*kb_per_split, ...)
+  int kb_per_split;
+  long long split_stride;  // elements between consecutive split partials in C (fp32 workspace)
 };
 
 template <int BN, int STAGES>
@@ -145,17 +148,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const uint32_t tmem_base = *tmem_slot;
 
   const int num_kb = (p.K + kBK - 1) / kBK;
-  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int num_work = p.tiles_m * p.tiles_n * p.splits;
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+    for (int work = blockIdx.x; work < num_work && ok; work += gridDim.x) {
+      const int tile = work / p.splits;
+      const int split = work - tile * p.splits;
       const int m0 = (tile % p.tiles_m) * kBM;
       const int n0 = (tile / p.tiles_m) * BN;
-      for (int kb = 0; kb < num_kb; ++kb) {
+      const int kb_lo = split * p.kb_per_split;
+      const int kb_hi = min(num_kb, kb_lo + p.kb_per_split);
+      for (int kb = kb_lo; kb < kb_hi; ++kb) {
         if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
         if (lane == 0) {
           mbar_expect_tx(&full_bar[stage], S::kABytes + S::kBBytes);
@@ -193,11 +200,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     uint32_t acc_phase[2] = {0, 0};
     int acc = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+    for (int work = blockIdx.x; work < num_work && ok; work += gridDim.x) {
+      const int split = work % p.splits;
+      const int kb_lo = split * p.kb_per_split;
+      const int kb_hi = min(num_kb, kb_lo + p.kb_per_split);
       if (!mbar_wait(&tempty_bar[acc], acc_phase[acc] ^ 1u, abort_flag, p.status, 2)) { ok = false; break; }
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-      for (int kb = 0; kb < num_kb; ++kb) {
+      for (int kb = kb_lo; kb < kb_hi; ++kb) {
         if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 3)) { ok = false; break; }
         tc_fence_after();
         if (lane == 0) {
@@ -209,7 +219,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                                      : make_smem_desc_sw128(a_base + kk * 32, 0, 1024);
             const uint64_t db = B_MN ? make_smem_desc_sw128(b_base + kk * 2048, 8192, 1024)
                                      : make_smem_desc_sw128(b_base + kk * 32, 0, 1024);
-            umma_f16(d_tmem, da, db, idesc, (kb | kk) != 0 ? 1u : 0u);
+            umma_f16(d_tmem, da, db, idesc, (kb != kb_lo || kk != 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);
         }
@@ -228,7 +238,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     uint32_t acc_phase[2] = {0, 0};
     int acc = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+    for (int work = blockIdx.x; work < num_work && ok; work += gridDim.x) {
+      const int tile = work / p.splits;
+      const int split = work - tile * p.splits;
       const int m0 = (tile % p.tiles_m) * kBM;
       const int n0 = (tile / p.tiles_m) * BN;
       if (!mbar_wait(&tfull_bar[acc], acc_phase[acc], abort_flag, p.status, 4)) { ok = false; break; }
@@ -250,7 +262,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 p.epi == 1 ? reinterpret_cast<const __nv_bfloat16*>(p.bias) + col : nullptr;
             store_row_bf16(dst, r, ncols, bias);
           } else {
-            float* dst = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col;
+            float* dst = reinterpret_cast<float*>(p.C) + split * p.split_stride + (long long)row * p.ldc + col;
             store_row_f32(dst, r, ncols, p.epi == 3);
           }
         }
@@ -321,7 +333,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  int grid = p.tiles_m * p.tiles_n;
+  int grid = p.tiles_m * p.tiles_n * p.splits;
   if (grid > num_sms()) grid = num_sms();
   kern<<<grid, kGemmThreads, S::kTotal, stream>>>(ta, tb, p);
   return static_cast<int>(cudaGetLastError());
@@ -342,38 +354,70 @@ static int dispatch_bn(int bn, const CUtensorMap& ta, const CUtensorMap& tb, con
 }
 
 static int pick_bn(int M, int N, bool b_mn) {
-  const int sms = num_sms();
-  const int tiles_m = (M + kBM - 1) / kBM;
-  const int cands[4] = {256, 128, 64, 32};
-  // Per-tile efficiency of the main loop relative to BN=256 (B-operand reuse shrinks with BN).
-  const float tile_eff[4] = {1.0f, 0.92f, 0.75f, 0.5f};
-  int best = 64;
-  float best_score = -1.f;
-  for (int i = 0; i < 4; ++i) {
-    const int bn = cands[i];
-    if (b_mn && bn < 64) continue;
-    const long tiles = (long)tiles_m * ((N + bn - 1) / bn);
-    const long waves = (tiles + sms - 1) / sms;
-    const float wave_eff = (float)tiles / (float)(waves * sms);
-    const float score = wave_eff * tile_eff[i];
-    if (score > best_score) { best_score = score; best = bn; }
+  // Measured on B200: the 128x256 tile wins whenever N allows it (smaller N-tiles are bound by
+  // shared-memory operand bandwidth); narrower tiles only serve narrow outputs.
+  (void)M;
+  if (N > 128) return 256;
+  if (N > 64) return 128;
+  if (N > 32 || b_mn) return 64;
+  return 32;
+}
+
+// out[m, n] = bf16(sum_s ws[s, m, n] (+ bias[n])), fixed summation order.
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float* __restrict__ ws, __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ bias,
+                     int M, int N, long long ldc, long long split_stride, int splits) {
+  const int nvec = N >> 2;
+  const long long total = (long long)M * nvec;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int m = (int)(idx / nvec);
+    const int c = (int)(idx % nvec) * 4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < splits; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(ws + s * split_stride + (long long)m * N + c);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    if (bias != nullptr) {
+      acc.x += __bfloat162float(bias[c]); acc.y += __bfloat162float(bias[c + 1]);
+      acc.z += __bfloat162float(bias[c + 2]); acc.w += __bfloat162float(bias[c + 3]);
+    }
+    uint2 o = make_uint2(pack_bf16x2(acc.x, acc.y), pack_bf16x2(acc.z, acc.w));
+    *reinterpret_cast<uint2*>(out + (long long)m * ldc + c) = o;
   }
-  return best;
 }
 
 }  // namespace areno
 
 using namespace areno;
 
+// Bytes of fp32 scratch that a split-K launch of this shape may use (0 when no split applies).
+extern "C" long long areno_gemm_workspace_bytes(int M, int N, int K) {
+  if (M > kBM || (N % 4) != 0) return 0;
+  return 16ll * M * N * 4;  // at most 16 splits
+}
+
 extern "C" int areno_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
                                long long lda, long long ldb, long long ldc, int a_mn, int b_mn, int epi, int bn,
-                               int* status, cudaStream_t stream) {
+                               void* workspace, long long workspace_bytes, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda % 8) != 0 || (ldb % 8) != 0) return -3;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
       (reinterpret_cast<uintptr_t>(C) & 15))
     return -3;
   if (epi <= 1 ? (ldc % 8) != 0 : (ldc % 4) != 0) return -3;
+  {
+    // cuTensorMapEncodeTiled needs a current driver context; threads that have not yet made a
+    // runtime call (e.g. autograd workers) get the primary context bound here.
+    static thread_local bool bound = false;
+    if (!bound) {
+      int dev = 0;
+      cudaGetDevice(&dev);
+      cudaSetDevice(dev);
+      cudaFree(nullptr);
+      bound = true;
+    }
+  }
   if (bn <= 0) bn = pick_bn(M, N, b_mn != 0);
   if (b_mn && bn < 64) bn = 64;
   CUtensorMap ta, tb;
@@ -390,10 +434,44 @@ extern "C" int areno_gemm_bf16(const void* A, const void* B, void* C, const void
   p.tiles_m = (M + kBM - 1) / kBM;
   p.tiles_n = (N + bn - 1) / bn;
   p.epi = epi;
-  if (a_mn) {
-    if (b_mn) return dispatch_bn<true, true>(bn, ta, tb, p, stream);
-    return dispatch_bn<true, false>(bn, ta, tb, p, stream);
+  p.splits = 1;
+  p.kb_per_split = (K + kBK - 1) / kBK;
+  p.split_stride = 0;
+  // Split-K for skinny problems (decode): too few output tiles to fill the GPU, long K.
+  const int num_kb = (K + kBK - 1) / kBK;
+  const int tiles = p.tiles_m * p.tiles_n;
+  bool split = false;
+  if (epi <= 1 && p.tiles_m == 1 && tiles * 2 <= num_sms() && num_kb >= 8 && workspace != nullptr && (N % 4) == 0) {
+    int want = num_sms() / tiles;
+    if (want > 16) want = 16;
+    int kbps = (num_kb + want - 1) / want;
+    if (kbps < 4) kbps = 4;
+    const int splits = (num_kb + kbps - 1) / kbps;
+    if (splits > 1 && (long long)splits * M * N * 4 <= workspace_bytes) {
+      p.splits = splits;
+      p.kb_per_split = kbps;
+      p.split_stride = (long long)M * N;
+      p.C = workspace;
+      p.ldc = N;
+      p.epi = 2;
+      p.bias = nullptr;
+      split = true;
+    }
   }
-  if (b_mn) return dispatch_bn<false, true>(bn, ta, tb, p, stream);
-  return dispatch_bn<false, false>(bn, ta, tb, p, stream);
+  if (a_mn) {
+    if (b_mn) rc = dispatch_bn<true, true>(bn, ta, tb, p, stream);
+    else rc = dispatch_bn<true, false>(bn, ta, tb, p, stream);
+  } else {
+    if (b_mn) rc = dispatch_bn<false, true>(bn, ta, tb, p, stream);
+    else rc = dispatch_bn<false, false>(bn, ta, tb, p, stream);
+  }
+  if (rc != 0 || !split) return rc;
+  const long long total = (long long)M * (N / 4);
+  int grid = (int)((total + 255) / 256);
+  if (grid > 148 * 8) grid = 148 * 8;
+  splitk_reduce_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const float*>(workspace),
+                                                 reinterpret_cast<__nv_bfloat16*>(C),
+                                                 epi == 1 ? reinterpret_cast<const __nv_bfloat16*>(bias) : nullptr, M, N,
+                                                 ldc, p.split_stride, p.splits);
+  return (int)cudaGetLastError();
 }

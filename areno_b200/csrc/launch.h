@@ -19,9 +19,12 @@ extern "C" {
 // D[M,N] = sum_k A(m,k) B(n,k).  a_mn / b_mn: operand stored [K, rows] instead of [rows, K].
 // epi: 0 = bf16 store, 1 = bf16 store + bf16 bias[N], 2 = fp32 store, 3 = fp32 accumulate (C += D).
 // bn: N-tile (256/128/64/32) or 0 for the built-in heuristic.  status: int[4] device words or NULL.
+// workspace: optional fp32 scratch enabling split-K for skinny (M <= 128) problems; see
+// areno_gemm_workspace_bytes.  Split partials are summed in a fixed order (deterministic).
 int areno_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long long lda,
-                    long long ldb, long long ldc, int a_mn, int b_mn, int epi, int bn, int* status,
-                    cudaStream_t stream);
+                    long long ldb, long long ldc, int a_mn, int b_mn, int epi, int bn, void* workspace,
+                    long long workspace_bytes, int* status, cudaStream_t stream);
+long long areno_gemm_workspace_bytes(int M, int N, int K);
 
 // ---- elementwise.cu ----
 int areno_rmsnorm_fwd(const void* x, const void* residual, const void* w, int wf32, float w_offset, void* y,

@@ -1,0 +1,539 @@
+"""Continuous-batching inference loop with paged KV and CUDA-graph decode.
+
+One ``InferenceEngine`` lives in each rank worker.  The decode step is
+``prepare -> model -> sample -> commit`` entirely on the device (see ``csrc/engine_meta.cu``), so it
+is replayed from a CUDA graph per batch bucket with no host read-back; the host learns about
+finished sequences from an asynchronously copied status snapshot that it polls without blocking.
+Admission, chunked prefill and page allocation are planned by the C++ scheduler.
+
+Semantics kept from the reference loop (``areno/engine/inference.py:199-536``): FIFO admission under
+``max_running_seqs`` and the page budget, chunked prefill under ``max_prefill_tokens``, the stop
+token is kept in the response, finish reasons ``stop | length | cancelled``, rollout log-probs are
+raw-logit log-softmax at temperature 1, new requests may join a running session between steps.
+"""
+
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Callable
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from ..models.dense import InferMeta
+from ..ops import _lib as klib
+from ..ops import attention as attn_ops
+from ..ops import sampling as sampling_ops
+from ..ops.paged_attention import PAGE
+from ..parallel.context import get_context
+from ..utils.log import get_logger
+from ._runtime import Scheduler
+
+logger = get_logger()
+
+klib.register_signature("areno_decode_prepare", "ppppiiipppp" + "p")
+klib.register_signature("areno_decode_commit", "ppppppppppp" + "iip")
+klib.register_signature("areno_prefill_commit", "pppppp" + "i" + "pppppppp" + "ip")
+
+FINISH_NAMES = {0: "running", 1: "stop", 2: "length", 3: "cancelled"}
+
+
+@dataclass
+class SamplingParams:
+    """Engine-level sampling controls (``areno/engine/data/batch.py:27-38`` in the reference)."""
+
+    temperature: float = 1.0
+    top_p: float = 1.0
+    top_k: int = -1
+    min_new_tokens: int = 0
+    seed: int | None = None
+    stop_token_ids: tuple[int, ...] = ()
+    suppress_token_ids: tuple[int, ...] = ()
+
+
+@dataclass
+class RolloutOutput:
+    tokens: list[list[int]] = field(default_factory=list)
+    logprobs: list[list[float]] = field(default_factory=list)
+    finish_reasons: list[str] = field(default_factory=list)
+    prompt_indices: list[int] | None = None
+    stats: dict = field(default_factory=dict)
+
+
+@dataclass
+class _Request:
+    rid: int
+    prompt: list[int]
+    max_new: int
+    slot: int = -1
+    done: bool = False
+    tokens: list[int] | None = None
+    logprobs: list[float] | None = None
+    reason: str = ""
+    tag: object = None
+
+
+def _pick_bucket(buckets: list[int], n: int) -> int:
+    for b in buckets:
+        if b >= n:
+            return b
+    return buckets[-1]
+
+
+class InferenceEngine:
+    def __init__(self, model, vocab_size: int, device, *, max_slots: int = 64, max_model_len: int = 4096,
+                 max_prefill_tokens: int = 16384, kv_fp8: bool = False, num_pages: int | None = None,
+                 graph_buckets: list[int] | None = None, eager: bool = False, seed: int = 0,
+                 max_new_cap: int = 4096):
+        self.model = model
+        self.vocab = vocab_size
+        self.device = torch.device(device)
+        self.cuda = self.device.type == "cuda"
+        self.max_slots = max_slots
+        self.max_model_len = max_model_len
+        self.max_pages = (max_model_len + PAGE - 1) // PAGE
+        self.max_prefill_tokens = max_prefill_tokens
+        self.kv_fp8 = kv_fp8
+        self.eager = eager or not self.cuda
+        self.seed = seed
+        self.calls = 0
+        self.max_out = max_new_cap
+        buckets = sorted(set(graph_buckets or [1, 2, 4, 8, 16, 32, 64, 128, 256, 512]))
+        self.buckets = [b for b in buckets if b <= max_slots] or [max_slots]
+        if self.buckets[-1] < max_slots:
+            self.buckets.append(max_slots)
+        self.num_pages = num_pages if num_pages is not None else max_slots * self.max_pages
+        self._graphs: dict[int, object] = {}
+        self._cls_key = None
+        self._alloc_state()
+        self.sched: Scheduler | None = None
+        self._requests: dict[int, _Request] = {}
+        self._next_rid = 0
+        self._snapshots: list = []
+        self.step_count = 0
+        self.decode_tokens = 0
+
+    # ------------------------------------------------------------------ state
+    def _alloc_state(self):
+        dev, s = self.device, self.max_slots
+        i32 = dict(dtype=torch.int32, device=dev)
+        self.seq_len = torch.zeros(s, **i32)
+        self.active = torch.zeros(s, **i32)
+        self.gen_count = torch.zeros(s, **i32)
+        self.max_new = torch.zeros(s, **i32)
+        self.finish = torch.zeros(s, **i32)
+        self.last_token = torch.zeros(s, dtype=torch.int64, device=dev)
+        self.row_uid = torch.zeros(s, dtype=torch.int64, device=dev)
+        self.block_table = torch.zeros((s, self.max_pages), **i32)
+        self.out_tokens = torch.zeros((s, self.max_out), **i32)
+        self.out_logprobs = torch.zeros((s, self.max_out), dtype=torch.float32, device=dev)
+        self.g_input_ids = torch.zeros(s, dtype=torch.int64, device=dev)
+        self.g_positions = torch.zeros(s, **i32)
+        self.g_slot_mapping = torch.full((s,), -1, **i32)
+        self.g_attn_lens = torch.zeros(s, **i32)
+        self.sampled = torch.zeros(s, dtype=torch.int64, device=dev)
+        self.sampled_lp = torch.zeros(s, dtype=torch.float32, device=dev)
+        pin = self.cuda
+        self.h_block_table = torch.zeros((s, self.max_pages), dtype=torch.int32, pin_memory=pin)
+        self.h_out_tokens = torch.zeros((s, self.max_out), dtype=torch.int32, pin_memory=pin)
+        self.h_out_logprobs = torch.zeros((s, self.max_out), dtype=torch.float32, pin_memory=pin)
+        self.cls = None
+        self.params = SamplingParams()
+
+    def ensure_kv_cache(self):
+        if getattr(self.model, "_kv_spec", None) != (self.num_pages, self.kv_fp8):
+            self.model.allocate_kv_caches(self.num_pages, self.kv_fp8)
+            self._graphs.clear()
+
+    def drop_kv_cache(self):
+        self.model.clear_kv_caches()
+        self._graphs.clear()
+
+    # ---------------------------------------------------------------- session
+    def begin(self, params: SamplingParams, eos_token_ids=(), max_new_tokens: int = 16):
+        """Start a generation session: fixes the sampling parameters shared by its requests."""
+        self.ensure_kv_cache()
+        self.params = params
+        stop = tuple(int(t) for t in eos_token_ids) + tuple(int(t) for t in params.stop_token_ids)
+        key = (tuple(params.suppress_token_ids), tuple(eos_token_ids), tuple(params.stop_token_ids))
+        if key != self._cls_key:
+            cls = sampling_ops.build_token_classes(self.vocab, params.suppress_token_ids, eos_token_ids)
+            for t in params.stop_token_ids:
+                if 0 <= int(t) < self.vocab and cls[int(t)] == 0:
+                    cls[int(t)] = 3
+            new_cls = cls.to(self.device)
+            if self.cls is None:
+                self.cls = new_cls
+            else:
+                self.cls.copy_(new_cls)  # same storage: captured graphs keep pointing at it
+            self._cls_key = key
+        self.stop_ids = set(stop)
+        self.default_max_new = max_new_tokens
+        self.sched = Scheduler(self.max_slots, self.num_pages, PAGE, self.max_pages, self.max_prefill_tokens)
+        self._requests.clear()
+        self._snapshots.clear()
+        self.active.zero_()
+        self.finish.zero_()
+        self.calls += 1
+        self.call_seed = params.seed if params.seed is not None else (self.seed * 1000003 + self.calls)
+        self._graph_key = (params.temperature, params.top_k, params.top_p, params.min_new_tokens, self.call_seed)
+        self.step_count = 0
+        self.decode_tokens = 0
+
+    def add_request(self, prompt: list[int], max_new_tokens: int | None = None, tag=None) -> int:
+        rid = self._next_rid
+        self._next_rid += 1
+        max_new = self.default_max_new if max_new_tokens is None else max_new_tokens
+        room = self.max_model_len - len(prompt)
+        max_new = max(1, min(max_new, room, self.max_out))
+        if len(prompt) >= self.max_model_len:
+            raise ValueError(f"prompt of {len(prompt)} tokens does not fit max_model_len={self.max_model_len}")
+        self._requests[rid] = _Request(rid, list(prompt), max_new, tag=tag)
+        self.sched.add(rid, len(prompt), max_new)
+        return rid
+
+    @property
+    def idle(self) -> bool:
+        return self.sched is None or (self.sched.num_running == 0 and self.sched.num_waiting == 0)
+
+    # ------------------------------------------------------------------- step
+    @torch.no_grad()
+    def step(self) -> list[_Request]:
+        """One scheduler iteration: poll completions, prefill newly admitted prompts, run one decode
+        step.  Returns the requests that completed since the last call."""
+        done = self._poll(block=False)
+        entries = self.sched.plan_prefill()
+        if entries:
+            self._run_prefill(entries)
+        if self.sched.num_decoding > 0:
+            try:
+                updates = self.sched.reserve_decode(1)
+            except MemoryError as exc:
+                self._preempt(int(exc.args[0]))
+                updates = self.sched.reserve_decode(1)
+            if updates:
+                self._push_block_updates(updates)
+            extent = self.sched.active_extent
+            self._decode(_pick_bucket(self.buckets, extent))
+            self.sched.advance(1)
+            self.step_count += 1
+            self._snapshot()
+        elif not entries:
+            if not self._snapshots:
+                self._snapshot()
+            done += self._poll(block=True)
+        return done
+
+    def run_until_done(self, progress_interval_s: float = 0.0, on_finished: Callable | None = None) -> None:
+        t_last = time.time()
+        tok_last = 0
+        while not self.idle:
+            for req in self.step():
+                if on_finished is not None:
+                    on_finished(req)
+            if progress_interval_s > 0 and time.time() - t_last >= progress_interval_s:
+                now = time.time()
+                rate = (self.decode_tokens - tok_last) / max(now - t_last, 1e-9)
+                logger.info("decode progress running=%d waiting=%d steps=%d decode_tok_s=%.1f cuda_graph=%s",
+                            self.sched.num_running, self.sched.num_waiting, self.step_count, rate, not self.eager)
+                t_last, tok_last = now, self.decode_tokens
+        for req in self._poll(block=True, drain=True):
+            if on_finished is not None:
+                on_finished(req)
+
+    def generate(self, prompts: list[list[int]], params: SamplingParams, eos_token_ids=(), max_new_tokens: int = 16,
+                 progress_interval_s: float = 0.0) -> RolloutOutput:
+        """Blocking helper: generate one completion per prompt, results in prompt order."""
+        self.begin(params, eos_token_ids, max_new_tokens)
+        rids = [self.add_request(p) for p in prompts]
+        t0 = time.time()
+        self.run_until_done(progress_interval_s)
+        reqs = [self._requests[r] for r in rids]
+        out = RolloutOutput(tokens=[r.tokens or [] for r in reqs], logprobs=[r.logprobs or [] for r in reqs],
+                            finish_reasons=[r.reason for r in reqs])
+        out.stats = {"decode_steps": self.step_count, "wall_s": time.time() - t0}
+        return out
+
+    def cancel_all(self):
+        """Mark every running sequence cancelled and drop waiting ones."""
+        self.sched.clear_waiting()
+        running = (self.active > 0)
+        self.finish.masked_fill_(running, 3)
+        self.active.zero_()
+        self._snapshot()
+        for rid, req in self._requests.items():
+            if req.slot < 0 and not req.done:
+                req.done, req.tokens, req.logprobs, req.reason = True, [], [], "cancelled"
+
+    # ---------------------------------------------------------------- prefill
+    def _run_prefill(self, entries):
+        dev = self.device
+        ids, pos, slots_map, q_lens, k_lens = [], [], [], [], []
+        logit_rows, fin_slots, fin_prompt, fin_budget, fin_uid = [], [], [], [], []
+        hist_slots = []
+        has_history = False
+        row = 0
+        for slot, rid, start, length, last in entries:
+            req = self._requests[rid]
+            req.slot = slot
+            pages = self.sched.slot_pages(slot)
+            self.h_block_table[slot, : len(pages)] = torch.tensor(pages, dtype=torch.int32)
+            chunk = req.prompt[start:start + length]
+            ids.extend(chunk)
+            p = np.arange(start, start + length)
+            pos.append(p)
+            pg = np.asarray(pages, dtype=np.int64)
+            slots_map.append(pg[p // PAGE] * PAGE + p % PAGE)
+            q_lens.append(length)
+            k_lens.append(start + length)
+            if start > 0:
+                has_history = True
+            allp = np.arange(0, start + length)
+            hist_slots.append(pg[allp // PAGE] * PAGE + allp % PAGE)
+            row += length
+            if last:
+                logit_rows.append(row - 1)
+                fin_slots.append(slot)
+                fin_prompt.append(len(req.prompt))
+                fin_budget.append(req.max_new)
+                fin_uid.append(rid)
+        touched = sorted({e[0] for e in entries})
+        lo, hi = touched[0], touched[-1] + 1
+        self.block_table[lo:hi].copy_(self.h_block_table[lo:hi], non_blocking=True)
+        ids_t = torch.tensor(ids, dtype=torch.int64)
+        pos_t = torch.from_numpy(np.concatenate(pos).astype(np.int32))
+        slot_t = torch.from_numpy(np.concatenate(slots_map).astype(np.int32))
+        if self.cuda:
+            ids_t, pos_t, slot_t = (t.pin_memory().to(dev, non_blocking=True) for t in (ids_t, pos_t, slot_t))
+        meta = InferMeta(mode="prefill", slot_mapping=slot_t,
+                         varlen=attn_ops.build_varlen_meta(q_lens, k_lens, device=dev), has_history=has_history)
+        if has_history:
+            meta.history = torch.from_numpy(np.concatenate(hist_slots)).to(dev)
+        if logit_rows:
+            meta.logit_rows = torch.tensor(logit_rows, dtype=torch.int64, device=dev)
+        else:
+            meta.logit_rows = torch.zeros(0, dtype=torch.int64, device=dev)
+        out = self.model(ids_t, pos_t, meta)
+        n = len(logit_rows)
+        if n == 0:
+            return
+        uid = torch.tensor(fin_uid, dtype=torch.int64, device=dev)
+        slots_t = torch.tensor(fin_slots, dtype=torch.int32, device=dev)
+        self.row_uid[slots_t.long()] = uid
+        zero_gen = torch.zeros(n, dtype=torch.int32, device=dev)
+        tok, lp = self._sample(out.logits_shard, zero_gen, uid)
+        prompt_t = torch.tensor(fin_prompt, dtype=torch.int32, device=dev)
+        budget_t = torch.tensor(fin_budget, dtype=torch.int32, device=dev)
+        if self.cuda:
+            klib.call("areno_prefill_commit", tok.data_ptr(), lp.data_ptr(), self.cls.data_ptr(), slots_t.data_ptr(),
+                      prompt_t.data_ptr(), budget_t.data_ptr(), n, self.seq_len.data_ptr(), self.active.data_ptr(),
+                      self.last_token.data_ptr(), self.gen_count.data_ptr(), self.max_new.data_ptr(),
+                      self.finish.data_ptr(), self.out_tokens.data_ptr(), self.out_logprobs.data_ptr(), self.max_out,
+                      klib.stream())
+        else:
+            self._prefill_commit_cpu(tok, lp, fin_slots, fin_prompt, fin_budget)
+        self._snapshot()
+
+    def _prefill_commit_cpu(self, tok, lp, slots, prompts, budgets):
+        for j, s in enumerate(slots):
+            t = int(tok[j])
+            self.out_tokens[s, 0] = t
+            self.out_logprobs[s, 0] = lp[j]
+            self.gen_count[s] = 1
+            self.max_new[s] = budgets[j]
+            self.seq_len[s] = prompts[j]
+            self.last_token[s] = t
+            c = int(self.cls[t])
+            if c in (2, 3):
+                self.finish[s], self.active[s] = 1, 0
+            elif budgets[j] <= 1:
+                self.finish[s], self.active[s] = 2, 0
+            else:
+                self.finish[s], self.active[s] = 0, 1
+
+    # ----------------------------------------------------------------- sample
+    def _sample(self, logits, gen_count, row_uid, out_token=None, out_logprob=None):
+        p = self.params
+        ctx = get_context()
+        lm = self.model.lm_head
+        valid = lm.valid_local
+        view = logits[:, :valid]
+        if ctx.tp_size == 1:
+            return sampling_ops.sample(view, p.temperature, p.top_k, p.top_p, cls=self.cls, gen_count=gen_count,
+                                       min_new=p.min_new_tokens, seed=self.call_seed, row_uid=row_uid,
+                                       out_token=out_token, out_logprob=out_logprob)
+        if (p.top_k > 0 or p.top_p < 1.0) and p.temperature > 0:
+            # truncated sampling needs the whole distribution on one rank
+            full = torch.empty((ctx.tp_size, *view.shape), dtype=view.dtype, device=view.device)
+            dist.all_gather_into_tensor(full, view.contiguous(), group=ctx.tp_group)
+            full = full.permute(1, 0, 2).reshape(view.shape[0], -1)[:, : self.vocab].contiguous()
+            return sampling_ops.sample(full, p.temperature, p.top_k, p.top_p, cls=self.cls, gen_count=gen_count,
+                                       min_new=p.min_new_tokens, seed=self.call_seed, row_uid=row_uid,
+                                       out_token=out_token, out_logprob=out_logprob)
+        part = torch.empty((view.shape[0], 6), dtype=torch.float32, device=view.device)
+        sampling_ops.sample(view, p.temperature, p.top_k, p.top_p, cls=self.cls, gen_count=gen_count,
+                            min_new=p.min_new_tokens, seed=self.call_seed, row_uid=row_uid,
+                            vocab_start=lm.vocab_start, part=part)
+        parts = torch.empty((ctx.tp_size, *part.shape), dtype=torch.float32, device=view.device)
+        dist.all_gather_into_tensor(parts, part, group=ctx.tp_group)
+        tok, lp = sampling_ops.combine_shards(parts)
+        if out_token is not None:
+            out_token.copy_(tok)
+            out_logprob.copy_(lp)
+            return out_token, out_logprob
+        return tok, lp
+
+    # ----------------------------------------------------------------- decode
+    def _decode_body(self, b: int):
+        if self.cuda:
+            klib.call("areno_decode_prepare", self.seq_len.data_ptr(), self.active.data_ptr(),
+                      self.last_token.data_ptr(), self.block_table.data_ptr(), self.max_pages, PAGE, b,
+                      self.g_input_ids.data_ptr(), self.g_positions.data_ptr(), self.g_slot_mapping.data_ptr(),
+                      self.g_attn_lens.data_ptr(), klib.stream())
+        else:
+            act = self.active[:b] > 0
+            pos = self.seq_len[:b]
+            page = self.block_table[:b].gather(1, (pos // PAGE).long().clamp(max=self.max_pages - 1)[:, None])[:, 0]
+            self.g_positions[:b] = torch.where(act, pos, torch.zeros_like(pos))
+            self.g_slot_mapping[:b] = torch.where(act, page * PAGE + pos % PAGE, torch.full_like(pos, -1))
+            self.g_attn_lens[:b] = torch.where(act, pos + 1, torch.zeros_like(pos))
+            self.g_input_ids[:b] = torch.where(act, self.last_token[:b], torch.zeros_like(self.last_token[:b]))
+        meta = InferMeta(mode="decode", slot_mapping=self.g_slot_mapping[:b], block_table=self.block_table[:b],
+                         seq_lens=self.g_attn_lens[:b], max_context=self.max_model_len)
+        out = self.model(self.g_input_ids[:b], self.g_positions[:b], meta)
+        self._sample(out.logits_shard, self.gen_count[:b], self.row_uid[:b], self.sampled[:b], self.sampled_lp[:b])
+        if self.cuda:
+            klib.call("areno_decode_commit", self.sampled.data_ptr(), self.sampled_lp.data_ptr(), self.cls.data_ptr(),
+                      self.seq_len.data_ptr(), self.active.data_ptr(), self.last_token.data_ptr(),
+                      self.gen_count.data_ptr(), self.max_new.data_ptr(), self.finish.data_ptr(),
+                      self.out_tokens.data_ptr(), self.out_logprobs.data_ptr(), self.max_out, b, klib.stream())
+        else:
+            for i in range(b):
+                if not int(self.active[i]):
+                    continue
+                t, g = int(self.sampled[i]), int(self.gen_count[i])
+                self.out_tokens[i, g] = t
+                self.out_logprobs[i, g] = self.sampled_lp[i]
+                self.gen_count[i] = g + 1
+                self.seq_len[i] += 1
+                self.last_token[i] = t
+                c = int(self.cls[t])
+                if c in (2, 3):
+                    self.finish[i], self.active[i] = 1, 0
+                elif g + 1 >= int(self.max_new[i]):
+                    self.finish[i], self.active[i] = 2, 0
+
+    def _decode(self, b: int):
+        self.decode_tokens += self.sched.num_decoding
+        if self.eager:
+            self._decode_body(b)
+            return
+        key = (b, self._graph_key)
+        entry = self._graphs.get(key)
+        if entry is None:
+            before = klib.launch_count
+            graph = self._capture(b)
+            entry = (graph, (klib.launch_count - before) // 3)  # two warm-up passes + the captured one
+            self._graphs[key] = entry
+        entry[0].replay()
+        klib.launch_count += entry[1]
+
+    def _capture(self, b: int):
+        # Warm up on a side stream (allocations, lazy module state), then capture.  The warm-up and
+        # the capture pass run real decode steps on the slot state, so that state is saved and
+        # restored around them.
+        saved = [t.clone() for t in (self.seq_len, self.active, self.last_token, self.gen_count, self.finish,
+                                     self.out_tokens[:, :2], self.out_logprobs[:, :2])]
+        active_real = self.active.clone()
+        self.active.zero_()          # warm-up steps touch no KV slot and commit nothing
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self._decode_body(b)
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self._decode_body(b)
+        self.active.copy_(active_real)
+        for dst, src in zip((self.seq_len, self.active, self.last_token, self.gen_count, self.finish), saved[:5]):
+            dst.copy_(src)
+        self.out_tokens[:, :2].copy_(saved[5])
+        self.out_logprobs[:, :2].copy_(saved[6])
+        return graph
+
+    # ------------------------------------------------------------ bookkeeping
+    def _push_block_updates(self, updates):
+        for slot, idx, page in updates:
+            self.h_block_table[slot, idx] = page
+        slots = sorted({u[0] for u in updates})
+        lo, hi = slots[0], slots[-1] + 1
+        self.block_table[lo:hi].copy_(self.h_block_table[lo:hi], non_blocking=True)
+
+    def _snapshot(self):
+        """Queue an async copy of (finish, gen_count) for the host to poll."""
+        pack = torch.stack([self.finish, self.gen_count, self.row_uid.to(torch.int32)])
+        if self.cuda:
+            host = torch.empty(pack.shape, dtype=torch.int32, pin_memory=True)
+            host.copy_(pack, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+            self._snapshots.append((host, ev))
+            if len(self._snapshots) > 4:
+                self._snapshots[0][1].synchronize()
+        else:
+            self._snapshots.append((pack.clone(), None))
+
+    def _poll(self, block: bool, drain: bool = False) -> list[_Request]:
+        done: list[_Request] = []
+        latest = None
+        while self._snapshots:
+            host, ev = self._snapshots[0]
+            if ev is not None and not ev.query():
+                if not (block or drain):
+                    break
+                ev.synchronize()
+            latest = host
+            self._snapshots.pop(0)
+            if block and not drain:
+                block = False
+        if latest is None:
+            return done
+        fin, gen, uid = latest[0], latest[1], latest[2]
+        finished_slots = []
+        for slot in range(self.max_slots):
+            f = int(fin[slot])
+            if f == 0:
+                continue
+            rid = self.sched.slot_request(slot)
+            if rid < 0:
+                continue
+            req = self._requests.get(rid)
+            if req is None or req.done or req.slot != slot or int(uid[slot]) != (rid & 0x7FFFFFFF):
+                continue
+            finished_slots.append((slot, req, f, int(gen[slot])))
+        if not finished_slots:
+            return done
+        for slot, req, f, g in finished_slots:
+            self.h_out_tokens[slot, :g].copy_(self.out_tokens[slot, :g], non_blocking=True)
+            self.h_out_logprobs[slot, :g].copy_(self.out_logprobs[slot, :g], non_blocking=True)
+        if self.cuda:
+            torch.cuda.current_stream().synchronize()
+        for slot, req, f, g in finished_slots:
+            req.tokens = self.h_out_tokens[slot, :g].tolist()
+            req.logprobs = self.h_out_logprobs[slot, :g].tolist()
+            req.reason = FINISH_NAMES.get(f, "stop")
+            req.done = True
+            self.finish[slot] = 0
+            self.sched.finish(slot)
+            done.append(req)
+        return done
+
+    def _preempt(self, slot: int):
+        """Out of KV pages: finish the offending sequence early with reason ``length``."""
+        self.finish[slot] = 2
+        self.active[slot] = 0
+        self._snapshot()
+        self._poll(block=True, drain=True)

@@ -1,0 +1,264 @@
+"""DP-sharded AdamW over flat parameter / gradient buckets.
+
+Layout: parameters are re-pointed into flat bf16 buffers ("buckets", reverse registration order so
+the last layers - whose gradients arrive first in backward - fill the first buckets) and each
+gets an fp32 ``main_grad`` view into a matching flat gradient buffer that the wgrad GEMM epilogue,
+the norm backward and the embedding backward accumulate into directly.  Every DP rank owns the
+``1/dp`` slice of each bucket: after the last micro-batch the bucket's gradient is
+reduce-scattered in place, the fused AdamW kernel updates the rank's fp32 master / moment shard and
+writes the bf16 shard, and the bucket's parameters are all-gathered in place.  Gradients,
+optimizer state and the update are sharded; only the bf16 working copy is replicated.
+
+Numerics follow the reference optimizer (``areno/engine/optim/adamw_fp32_master.py:239-303``,
+``adamw_8bit.py``): decoupled decay on every parameter, eps outside the square root, bias
+correction by step count, fp32 gradient accumulation, clip coefficient ``max_norm / (norm + 1e-6)``.
+The 8-bit variant keeps int8/uint8 moments with one scale per 32 elements and no master copy.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+import torch
+import torch.distributed as dist
+
+from ..ops import optim as optim_ops
+from ..parallel.context import ParallelContext, get_context
+from .config import OptimizerConfig
+
+_ALIGN = 256  # elements; keeps every shard boundary 16-byte aligned for all dtypes
+
+
+@dataclass
+class _Bucket:
+    params: list = field(default_factory=list)
+    offsets: list = field(default_factory=list)
+    numel: int = 0            # padded
+    replicated: bool = False  # parameters replicated over TP (norm scales, biases of row-parallel layers)
+    param_flat: torch.Tensor | None = None
+    grad_flat: torch.Tensor | None = None
+    master: torch.Tensor | None = None
+    m: torch.Tensor | None = None
+    v: torch.Tensor | None = None
+    m_scale: torch.Tensor | None = None
+    v_scale: torch.Tensor | None = None
+    shard: int = 0
+
+
+class ShardedAdamW:
+    def __init__(self, model: torch.nn.Module, cfg: OptimizerConfig, ctx: ParallelContext | None = None):
+        self.cfg = cfg
+        self.ctx = ctx or get_context()
+        self.dp = max(1, self.ctx.dp_size)
+        self.dp_rank = self.ctx.dp_rank
+        self.step_count = 0
+        self.lr = cfg.lr
+        self.buckets: list[_Bucket] = []
+        self._state_ready = False
+        self._build(model)
+
+    # ------------------------------------------------------------------ layout
+    def _build(self, model):
+        seen = set()
+        params = []
+        for p in model.parameters():
+            if p.requires_grad and id(p) not in seen:
+                seen.add(id(p))
+                params.append(p)
+        params.reverse()
+        cap = max(int(self.cfg.fp32_master_bucket_numel), 1)
+        granule = _ALIGN * self.dp
+        groups = {False: [], True: []}
+        for p in params:
+            groups[bool(getattr(p, "tp_replicated_grad", False))].append(p)
+        for replicated, plist in groups.items():
+            cur = _Bucket(replicated=replicated)
+            for p in plist:
+                n = (p.numel() + _ALIGN - 1) // _ALIGN * _ALIGN
+                if cur.params and cur.numel + n > cap:
+                    self.buckets.append(cur)
+                    cur = _Bucket(replicated=replicated)
+                cur.params.append(p)
+                cur.offsets.append(cur.numel)
+                cur.numel += n
+            if cur.params:
+                self.buckets.append(cur)
+        for b in self.buckets:
+            b.numel = (b.numel + granule - 1) // granule * granule
+            b.shard = b.numel // self.dp
+            dev = b.params[0].device
+            dtype = b.params[0].dtype
+            b.param_flat = torch.zeros(b.numel, dtype=dtype, device=dev)
+            b.grad_flat = torch.zeros(b.numel, dtype=torch.float32, device=dev)
+            for p, off in zip(b.params, b.offsets):
+                view = b.param_flat[off:off + p.numel()].view(p.shape)
+                view.copy_(p.data)
+                p.data = view
+                p.main_grad = b.grad_flat[off:off + p.numel()].view(p.shape)
+                p.grad_added_to_main_grad = False
+
+    def _ensure_state(self):
+        if self._state_ready:
+            return
+        for b in self.buckets:
+            lo = self.dp_rank * b.shard
+            dev = b.param_flat.device
+            if self.cfg.adam_8bit:
+                nb = (b.shard + optim_ops.Q_BLOCK - 1) // optim_ops.Q_BLOCK
+                b.m = torch.zeros(b.shard, dtype=torch.int8, device=dev)
+                b.v = torch.zeros(b.shard, dtype=torch.uint8, device=dev)
+                b.m_scale = torch.full((nb,), 1e-30, dtype=torch.float32, device=dev)
+                b.v_scale = torch.full((nb,), 1e-30, dtype=torch.float32, device=dev)
+            else:
+                b.master = b.param_flat[lo:lo + b.shard].float()
+                b.m = torch.zeros(b.shard, dtype=torch.float32, device=dev)
+                b.v = torch.zeros(b.shard, dtype=torch.float32, device=dev)
+        self._state_ready = True
+
+    # -------------------------------------------------------------- gradients
+    def fold_param_grads(self):
+        """Accumulate any autograd-produced ``p.grad`` (ops without a fused main-grad path) into the
+        fp32 buffers and drop it."""
+        for b in self.buckets:
+            for p in b.params:
+                if p.grad is not None:
+                    if not getattr(p, "grad_added_to_main_grad", False):
+                        p.main_grad.add_(p.grad.to(torch.float32))
+                    p.grad = None
+                p.grad_added_to_main_grad = False
+
+    def zero_grad(self):
+        for b in self.buckets:
+            b.grad_flat.zero_()
+            for p in b.params:
+                p.grad = None
+                p.grad_added_to_main_grad = False
+
+    def _grad_shard(self, b: _Bucket) -> torch.Tensor:
+        lo = self.dp_rank * b.shard
+        return b.grad_flat[lo:lo + b.shard]
+
+    def reduce_gradients(self):
+        """TP all-reduce of replicated-parameter gradients, then DP reduce-scatter (sum) in place."""
+        ctx = self.ctx
+        if ctx.tp_size > 1:
+            for b in self.buckets:
+                if b.replicated:
+                    dist.all_reduce(b.grad_flat, group=ctx.tp_group)
+        if self.dp > 1:
+            works = []
+            for b in self.buckets:
+                works.append(dist.reduce_scatter_tensor(self._grad_shard(b), b.grad_flat, group=ctx.dp_group,
+                                                        async_op=True))
+            for w in works:
+                w.wait()
+
+    def grad_norm_sq(self) -> torch.Tensor:
+        """Squared global gradient norm (of the DP-averaged gradient) as a 1-element device tensor."""
+        ctx = self.ctx
+        dev = self.buckets[0].grad_flat.device
+        sharded = torch.zeros(1, dtype=torch.float32, device=dev)
+        repl = torch.zeros(1, dtype=torch.float32, device=dev)
+        for b in self.buckets:
+            optim_ops.sumsq(self._grad_shard(b), repl if b.replicated else sharded, accumulate=True)
+        total = sharded + repl / max(1, ctx.tp_size)
+        total = total / float(self.dp * self.dp)
+        if self.dp > 1:
+            dist.all_reduce(total, group=ctx.dp_group)
+        if ctx.tp_size > 1:
+            dist.all_reduce(total, group=ctx.tp_group)
+        return total
+
+    # ------------------------------------------------------------------- step
+    def step(self, lr: float | None = None, clip_norm: float | None = None) -> torch.Tensor:
+        """Reduce, clip, update, all-gather.  Returns the gradient norm (device scalar tensor)."""
+        self._ensure_state()
+        self.fold_param_grads()
+        self.reduce_gradients()
+        lr = self.lr if lr is None else lr
+        norm = torch.sqrt(self.grad_norm_sq())
+        coef = None
+        clip = self.cfg.grad_clip_norm if clip_norm is None else clip_norm
+        if clip is not None and clip > 0:
+            coef = torch.clamp(clip / (norm + 1e-6), max=1.0)
+        self.step_count += 1
+        b1, b2 = self.cfg.betas
+        gathers = []
+        for b in self.buckets:
+            lo = self.dp_rank * b.shard
+            g = self._grad_shard(b)
+            out = b.param_flat[lo:lo + b.shard]
+            if self.cfg.adam_8bit:
+                optim_ops.adamw_8bit(None, b.m, b.v, b.m_scale, b.v_scale, g, out, lr, b1, b2, self.cfg.eps,
+                                     self.cfg.weight_decay, self.step_count, 1.0 / self.dp, coef)
+            else:
+                optim_ops.adamw_fp32(b.master, b.m, b.v, g, out, lr, b1, b2, self.cfg.eps, self.cfg.weight_decay,
+                                     self.step_count, 1.0 / self.dp, coef)
+            if self.dp > 1:
+                gathers.append(dist.all_gather_into_tensor(b.param_flat, out, group=self.ctx.dp_group, async_op=True))
+        for w in gathers:
+            w.wait()
+        self.zero_grad()
+        return norm
+
+    # --------------------------------------------------------------- offload
+    def offload_state(self):
+        for b in self.buckets:
+            for name in ("master", "m", "v", "m_scale", "v_scale", "grad_flat"):
+                t = getattr(b, name)
+                if t is not None and t.is_cuda:
+                    setattr(b, name, t.to("cpu"))
+        self._offloaded = True
+
+    def onload_state(self, device):
+        for b in self.buckets:
+            for name in ("master", "m", "v", "m_scale", "v_scale", "grad_flat"):
+                t = getattr(b, name)
+                if t is not None and not t.is_cuda:
+                    setattr(b, name, t.to(device))
+            for p, off in zip(b.params, b.offsets):
+                p.main_grad = b.grad_flat[off:off + p.numel()].view(p.shape)
+        self._offloaded = False
+
+    # ------------------------------------------------------------ state dict
+    def state_dict(self) -> dict:
+        self._ensure_state()
+        return {
+            "step": self.step_count,
+            "dp_rank": self.dp_rank,
+            "dp_size": self.dp,
+            "adam_8bit": self.cfg.adam_8bit,
+            "buckets": [
+                {k: (getattr(b, k).detach().cpu() if getattr(b, k) is not None else None)
+                 for k in ("master", "m", "v", "m_scale", "v_scale")}
+                for b in self.buckets
+            ],
+        }
+
+    def load_state_dict(self, state: dict) -> None:
+        self._ensure_state()
+        if state.get("dp_size") != self.dp or len(state["buckets"]) != len(self.buckets):
+            raise ValueError("optimizer state was saved with a different sharding layout")
+        self.step_count = int(state["step"])
+        for b, sb in zip(self.buckets, state["buckets"]):
+            for k, t in sb.items():
+                if t is not None:
+                    getattr(b, k).copy_(t)
+
+
+def lr_for_step(cfg: OptimizerConfig, step: int) -> float:
+    """Warm-up then constant / linear / cosine decay to ``min_lr`` over ``lr_decay_steps``
+    (schedule of ``areno/engine/training.py:138-155``); ``step`` counts from 1."""
+    lr, min_lr = cfg.lr, cfg.min_lr
+    if cfg.lr_warmup_steps > 0 and step <= cfg.lr_warmup_steps:
+        return lr * step / cfg.lr_warmup_steps
+    if cfg.lr_decay_style == "constant" or cfg.lr_decay_steps <= 0:
+        return lr
+    span = max(cfg.lr_decay_steps - cfg.lr_warmup_steps, 1)
+    t = min(max((step - cfg.lr_warmup_steps) / span, 0.0), 1.0)
+    if cfg.lr_decay_style == "linear":
+        return min_lr + (lr - min_lr) * (1.0 - t)
+    if cfg.lr_decay_style == "cosine":
+        return min_lr + (lr - min_lr) * 0.5 * (1.0 + math.cos(math.pi * t))
+    raise ValueError(f"unknown lr_decay_style {cfg.lr_decay_style}")

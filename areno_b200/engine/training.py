@@ -1,0 +1,225 @@
+"""Actor training: packing, micro-batch forward/backward, sharded optimizer step.
+
+``pack_train_data`` turns right-padded rollout rows ``(B, T)`` into one packed variable-length
+batch plus flat per-action views (an "action" is a position that predicts the next token, i.e.
+every token of a row but its last).  Key names and semantics are those of the reference
+(``areno/engine/runtime/train_step.py:89-192``) so loss functions written for it run unchanged;
+the index construction is a C++ pass instead of a per-row Python loop with ``.item()`` syncs.
+
+``TrainingManager.train`` is the counterpart of ``areno/engine/training.py:31-136``: per pack
+forward -> selected log-probs -> ``loss_fn(pack, logprobs)`` -> backward with fp32 main-grad
+accumulation; on the last pack of an accumulation group the sharded optimizer reduces, clips,
+updates and re-gathers.
+"""
+
+from __future__ import annotations
+
+from typing import Any, Callable
+
+import numpy as np
+import torch
+
+from ..models.dense import TrainMeta
+from ..ops.attention import build_varlen_meta
+from ..parallel.context import get_context
+from ..utils.log import get_logger
+from . import _runtime
+from .config import EngineConfig
+from .logprobs import lm_head_logprobs
+from .optim import ShardedAdamW, lr_for_step
+
+logger = get_logger()
+
+_PER_TOKEN_KEYS = ("advantages", "logprobs", "ref_logprobs", "values", "returns")
+
+
+def pack_train_data(data_pack: dict[str, Any]) -> dict[str, Any]:
+    """Padded rows -> packed varlen batch (CPU tensors in, CPU tensors out)."""
+    lengths = data_pack.get("lengths")
+    input_ids = data_pack.get("input_ids")
+    if not isinstance(lengths, torch.Tensor) or not isinstance(input_ids, torch.Tensor):
+        return data_pack
+    if input_ids.ndim != 2 or lengths.ndim != 1 or lengths.numel() != input_ids.shape[0]:
+        return data_pack
+    prompt_mask = data_pack.get("prompt_mask")
+    advantages = data_pack.get("advantages")
+    rollout_logprobs = data_pack.get("logprobs")
+    if not all(isinstance(x, torch.Tensor) for x in (prompt_mask, advantages, rollout_logprobs)):
+        return data_pack
+    batch, width = input_ids.shape
+    len_np = np.clip(lengths.detach().cpu().numpy().astype(np.int64), 1, width)
+    rows, cols, aidx, arows = _runtime.pack_indices(len_np, width)
+    rows_t, cols_t = torch.from_numpy(rows), torch.from_numpy(cols)
+    aidx_t, arows_t = torch.from_numpy(aidx), torch.from_numpy(arows)
+    ids_cpu = input_ids.detach().cpu()
+    packed_ids = ids_cpu[rows_t, cols_t]
+    # per-action signals are read at the *target* token (column + 1 of the action site)
+    a_rows, a_cols = arows_t, cols_t[aidx_t] + 1
+    response_mask = ~prompt_mask.detach().cpu()[a_rows, a_cols].to(torch.bool)
+    loss_mask = data_pack.get("loss_mask")
+    if isinstance(loss_mask, torch.Tensor):
+        response_mask = response_mask & loss_mask.detach().cpu()[a_rows, a_cols].to(torch.bool)
+    cu = np.zeros(batch + 1, dtype=np.int32)
+    np.cumsum(len_np, out=cu[1:])
+    packed = dict(data_pack)
+    packed.update({
+        "input_ids": packed_ids.unsqueeze(0),
+        "position_ids": cols_t.unsqueeze(0),
+        "train_cu_seqlens": torch.from_numpy(cu),
+        "train_max_seqlen": int(len_np.max()),
+        "packed_response_mask": response_mask,
+        "packed_advantages": advantages.detach().cpu()[a_rows, a_cols].float(),
+        "packed_logprobs": rollout_logprobs.detach().cpu()[a_rows, a_cols].float(),
+        "packed_seq_ids": arows_t,
+        "packed_num_sequences": batch,
+        "_action_index": aidx_t,
+        "_seq_lengths": [int(x) for x in len_np],
+    })
+    ref, values, returns = (data_pack.get(k) for k in ("ref_logprobs", "values", "returns"))
+    if all(isinstance(x, torch.Tensor) for x in (ref, values, returns)):
+        packed["packed_ref_logprobs"] = ref.detach().cpu()[a_rows, a_cols].float()
+        packed["packed_values"] = values.detach().cpu()[a_rows, a_cols].float()
+        packed["packed_returns"] = returns.detach().cpu()[a_rows, a_cols].float()
+    return packed
+
+
+def to_device(pack: dict[str, Any], device: torch.device) -> dict[str, Any]:
+    """Move tensor values to ``device`` (pinned staging + async copy on CUDA)."""
+    out = {}
+    cuda = torch.device(device).type == "cuda"
+    for k, v in pack.items():
+        if isinstance(v, torch.Tensor) and v.device != device:
+            if cuda and not v.is_pinned() and v.numel() > 0:
+                v = v.pin_memory()
+            out[k] = v.to(device, non_blocking=True)
+        else:
+            out[k] = v
+    return out
+
+
+def split_data_pack_by_dp(pack: dict[str, Any], dp_size: int) -> list[dict[str, Any]]:
+    """Strided ``rank::dp`` split of every batch-major tensor; a batch smaller than ``dp_size`` is
+    replicated (``areno/engine/runtime/common.py:76-109``)."""
+    ids = pack.get("input_ids")
+    if dp_size <= 1 or not isinstance(ids, torch.Tensor):
+        return [pack for _ in range(max(dp_size, 1))]
+    batch = ids.shape[0]
+    if batch < dp_size:
+        return [pack for _ in range(dp_size)]
+    shards = []
+    for r in range(dp_size):
+        shard = {}
+        for k, v in pack.items():
+            if isinstance(v, torch.Tensor) and v.ndim >= 1 and v.shape[0] == batch:
+                shard[k] = v[r::dp_size]
+            elif isinstance(v, list) and len(v) == batch:
+                shard[k] = v[r::dp_size]
+            else:
+                shard[k] = v
+        shards.append(shard)
+    return shards
+
+
+def merge_train_stats(stats: list[dict]) -> dict:
+    """Mean over DP ranks of scalar stats (``areno/engine/runtime/common.py:112-132``)."""
+    stats = [s for s in stats if s]
+    if not stats:
+        return {}
+    out = dict(stats[0])
+    out["loss"] = sum(s["loss"] for s in stats) / len(stats)
+    metrics: dict[str, float] = {}
+    for key in stats[0].get("metrics", {}):
+        vals = [s["metrics"][key] for s in stats if key in s.get("metrics", {})]
+        if vals and all(isinstance(v, (int, float)) for v in vals):
+            metrics[key] = sum(vals) / len(vals)
+        elif vals:
+            metrics[key] = vals[0]
+    out["metrics"] = metrics
+    return out
+
+
+class TrainingManager:
+    def __init__(self, model, config: EngineConfig, device, loss_fn: Callable | None = None):
+        self.model = model
+        self.config = config
+        self.device = torch.device(device)
+        self.loss_fn = loss_fn
+        self.optimizer = ShardedAdamW(model, config.optimizer)
+        self.global_step = 0
+        self.grad_clip_norm = config.optimizer.grad_clip_norm
+
+    # ------------------------------------------------------------------ public
+    def train(self, packs: list, gradient_accumulation_steps: int | None = None) -> list[dict]:
+        """``packs``: list of micro-batches, each a list of per-DP-rank shards (or a single pack)."""
+        n = len(packs)
+        accum = n if not gradient_accumulation_steps else max(1, min(gradient_accumulation_steps, n))
+        results = []
+        for i, shards in enumerate(packs):
+            group_pos = i % accum
+            remaining = n - (i - group_pos)
+            group = min(accum, remaining)
+            allow_step = group_pos == group - 1
+            results.append(self.train_step(shards, allow_step=allow_step, grad_scale=group))
+        return results
+
+    def forward_logprobs(self, pack: dict, need_entropy: bool = False):
+        """Packed forward to per-action log-probs ``[num_actions]`` (fp32)."""
+        ids = pack["input_ids"].reshape(-1)
+        pos = pack["position_ids"].reshape(-1)
+        lens = pack.get("_seq_lengths")
+        if lens is None:
+            cu = pack["train_cu_seqlens"].tolist()
+            lens = [cu[i + 1] - cu[i] for i in range(len(cu) - 1)]
+        meta = TrainMeta(build_varlen_meta(lens, device=self.device),
+                         activation_checkpointing=self.config.runtime.activation_checkpointing)
+        out = self.model(ids, pos, meta)
+        aidx = pack["_action_index"]
+        hidden = out.hidden_states.index_select(0, aidx)
+        targets = ids.index_select(0, aidx + 1)
+        return lm_head_logprobs(self.model.lm_head, hidden, targets, self.config.runtime.logprob_chunk,
+                                need_entropy=need_entropy, softcap=self.model.cfg.final_logit_softcapping)
+
+    def train_step(self, shards, *, allow_step: bool, grad_scale: int) -> dict:
+        ctx = get_context()
+        self.model.train()
+        pack = shards[ctx.dp_rank] if isinstance(shards, (list, tuple)) else shards
+        pack = pack_train_data(pack)
+        loss_fn = pack.get("_loss_fn") or self.loss_fn
+        if loss_fn is None:
+            raise ValueError("no loss function: pass loss_fn or stamp '_loss_fn' on the pack")
+        pack = to_device(pack, self.device)
+        logprobs = self.forward_logprobs(pack)
+        loss_out = loss_fn(pack, logprobs)
+        metrics = None
+        if isinstance(loss_out, tuple):
+            loss, metrics = loss_out
+        else:
+            loss = loss_out
+        if not isinstance(loss, torch.Tensor):
+            raise TypeError("train_loss_fn must return a torch.Tensor")
+        (loss / max(grad_scale, 1)).backward()
+        grad_norm = None
+        lr = self.optimizer.lr
+        if allow_step:
+            if hasattr(self.model, "finalize_router_expert_bias"):
+                self.model.finalize_router_expert_bias(ctx.tp_group, ctx.dp_group)
+            lr = lr_for_step(self.config.optimizer, self.global_step + 1)
+            self.optimizer.lr = lr
+            grad_norm = self.optimizer.step(lr=lr, clip_norm=self.grad_clip_norm)
+            self.global_step += 1
+        else:
+            self.optimizer.fold_param_grads()
+        out_metrics = {}
+        if metrics:
+            for k, v in metrics.items():
+                out_metrics[k] = float(v.detach().float().cpu()) if isinstance(v, torch.Tensor) else v
+        out_metrics["lr"] = lr
+        if grad_norm is not None:
+            out_metrics["grad_norm"] = float(grad_norm.detach().cpu())
+        return {
+            "loss": float(loss.detach().float().cpu()),
+            "stepped": allow_step,
+            "global_step": self.global_step,
+            "metrics": out_metrics,
+            "num_tokens": int(pack["input_ids"].numel()),
+        }

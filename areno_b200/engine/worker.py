@@ -1,0 +1,122 @@
+"""Rank worker: one per GPU.  Owns the model shard, the inference engine, the training manager and
+the auxiliary roles (reference / critic / reward models), and time-multiplexes the GPU between
+them.  ``handle(op, payload)`` is the single entry point used by every cluster flavour (spawned
+processes, in-process, SPMD under torchrun).
+
+Counterpart of ``areno/engine/worker.py:54-467`` in the reference.  Differences that matter: the
+decode loop has no per-step host sync (see ``inference.py``), gradients / optimizer state are
+DP-sharded (see ``optim.py``), and the rollout engine reads the very buffers the optimizer writes,
+so "weight sync" after a step is free when rollout and training share a layout.
+"""
+
+from __future__ import annotations
+
+import time
+from typing import Any
+
+import torch
+
+from ..models import registry as model_registry
+from ..parallel.context import get_context
+from ..utils.log import get_logger
+from .config import EngineConfig
+from .inference import InferenceEngine, RolloutOutput, SamplingParams
+from .training import TrainingManager
+
+logger = get_logger()
+
+
+class RankWorker:
+    def __init__(self, config: EngineConfig, device: torch.device | str | None = None):
+        self.config = config
+        ctx = get_context()
+        self.ctx = ctx
+        self.device = torch.device(device) if device is not None else ctx.device
+        t0 = time.time()
+        self.adapter = model_registry.get_adapter(config.model.model_type)
+        self.model = self.adapter.build(config.model, device=self.device)
+        if config.dummy_load or not config.model_path:
+            self.adapter.init_random(self.model, seed=config.seed)
+        else:
+            self.adapter.load_weights(self.model, config.model_path, config.model)
+        self.trainer: TrainingManager | None = None
+        self.infer: InferenceEngine | None = None
+        self.roles = None
+        self._actor_on_device = True
+        self.loss_fn = None
+        logger.info("worker ready rank=%d tp=%d/%d dp=%d/%d build_s=%.2f", ctx.rank, ctx.tp_rank, ctx.tp_size,
+                    ctx.dp_rank, ctx.dp_size, time.time() - t0)
+
+    # ------------------------------------------------------------- components
+    def training_manager(self) -> TrainingManager:
+        if self.trainer is None:
+            self.trainer = TrainingManager(self.model, self.config, self.device, loss_fn=self.loss_fn)
+            if self.infer is not None:
+                self.infer._graphs.clear()  # parameters were re-pointed into flat buckets
+        return self.trainer
+
+    def inference_engine(self, max_slots: int | None = None, max_model_len: int | None = None) -> InferenceEngine:
+        rt = self.config.runtime
+        slots = max_slots or self.config.max_running_seqs
+        mlen = max_model_len or rt.max_model_len or min(self.config.model.max_position_embeddings, 8192)
+        if self.infer is None or self.infer.max_slots < slots or self.infer.max_model_len < mlen:
+            if self.infer is not None:
+                self.infer.drop_kv_cache()
+            self.infer = InferenceEngine(
+                self.model, self.config.model.vocab_size, self.device, max_slots=slots, max_model_len=mlen,
+                max_prefill_tokens=rt.max_prefill_tokens, kv_fp8=rt.kv_dtype == "fp8",
+                graph_buckets=rt.decode_graph_buckets, eager=rt.eager_decode, seed=self.config.seed,
+                max_new_cap=mlen)
+        return self.infer
+
+    # ---------------------------------------------------------------- rollout
+    @torch.no_grad()
+    def rollout(self, prompts: list[list[int]], params: SamplingParams, eos_token_ids=(), max_new_tokens: int = 16,
+                max_running: int | None = None, progress_interval_s: float | None = None) -> RolloutOutput:
+        self.prepare_actor_onloaded()
+        self.model.eval()
+        longest = max((len(p) for p in prompts), default=1) + max_new_tokens
+        need_len = (longest + 63) // 64 * 64
+        slots = min(max_running or self.config.max_running_seqs, max(len(prompts), 1))
+        eng = self.inference_engine(slots, need_len)
+        interval = self.config.decode_progress_interval_s if progress_interval_s is None else progress_interval_s
+        return eng.generate(prompts, params, eos_token_ids, max_new_tokens, progress_interval_s=interval)
+
+    # ------------------------------------------------------------------ train
+    def train(self, packs: list, gradient_accumulation_steps: int | None = None) -> list[dict]:
+        self.prepare_for_train()
+        return self.training_manager().train(packs, gradient_accumulation_steps)
+
+    # ---------------------------------------------------------- GPU residency
+    def prepare_for_train(self):
+        self.prepare_actor_onloaded()
+        if self.infer is not None and not self.config.runtime.keep_rollout_state:
+            self.infer.drop_kv_cache()
+
+    def prepare_actor_onloaded(self):
+        if not self._actor_on_device:
+            self.model.onload_train_weights(self.device)
+            if self.trainer is not None:
+                self.trainer.optimizer.onload_state(self.device)
+            self._actor_on_device = True
+
+    def prepare_actor_offloaded(self):
+        """Move actor weights and optimizer state to the host so another role can use the GPU."""
+        if self._actor_on_device:
+            if self.infer is not None:
+                self.infer.drop_kv_cache()
+            if self.trainer is not None:
+                self.trainer.optimizer.offload_state()
+            self.model.offload_train_weights()
+            self._actor_on_device = False
+            if self.device.type == "cuda":
+                torch.cuda.empty_cache()
+
+    def save_checkpoint(self, path: str) -> None:
+        self.adapter.save_weights(self.model, path, self.config.model, source_path=self.config.model_path)
+
+    def peak_memory_fraction(self) -> float:
+        if self.device.type != "cuda":
+            return 0.0
+        total = torch.cuda.get_device_properties(self.device).total_memory
+        return float(torch.cuda.max_memory_allocated(self.device)) / float(total)

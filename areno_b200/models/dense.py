@@ -1,0 +1,288 @@
+"""Pre-norm decoder-only transformer (Llama / Qwen2.5 / Qwen3 dense families).
+
+One module serves three execution modes selected by the meta object:
+
+* ``TrainMeta``  - packed variable-length batch, autograd on, optional per-layer activation
+  checkpointing; returns final hidden states (the LM head is applied chunk-wise by the
+  log-prob head so ``[T, vocab]`` logits are never resident);
+* ``InferMeta(prefill)`` - packed prompts; K/V are rotated, appended to the paged cache and
+  attended in one pass;
+* ``InferMeta(decode)``  - one token per running sequence against the paged cache; every shape
+  is static so the step is captured in a CUDA graph.
+
+Architecture and lifecycle protocol follow ``areno/models/qwen3/model.py:48-72,234-369`` and
+``areno/models/llama/model.py`` of the reference; the kernels underneath are this package's own.
+"""
+
+from __future__ import annotations
+
+import zlib
+from dataclasses import dataclass, field
+from typing import Any
+
+import torch
+import torch.nn as nn
+from torch.utils.checkpoint import checkpoint
+
+from ..engine.config import ModelConfig
+from ..ops import attention as attn_ops
+from ..ops import gemm, paged_attention as pa
+from ..ops.attention import VarlenMeta
+from ..parallel import collectives as coll
+from ..parallel.context import get_context
+from .layers import (GatedMLP, QKVParallelLinear, RMSNorm, RowParallelLinear, VocabParallelEmbedding,
+                     VocabParallelLMHead)
+
+
+@dataclass
+class TrainMeta:
+    varlen: VarlenMeta
+    activation_checkpointing: bool = True
+    packed: bool = True
+
+
+@dataclass
+class InferMeta:
+    mode: str                                   # "prefill" | "decode"
+    slot_mapping: torch.Tensor                  # int32 [T]: cache slot of every input token (-1 = skip)
+    varlen: VarlenMeta | None = None            # prefill: q = new tokens, k = cached + new tokens
+    block_table: torch.Tensor | None = None     # int32 [B, max_pages]
+    seq_lens: torch.Tensor | None = None        # int32 [B]: context length including the new token(s)
+    max_context: int | None = None
+    logit_rows: torch.Tensor | None = None      # prefill: row indices whose logits are needed
+    has_history: bool = False                   # prefill chunk continues sequences with cached tokens
+    history: Any = None                         # (page index tensor, lengths) used to gather cached K/V
+
+
+@dataclass
+class CausalLMOutput:
+    logits_shard: torch.Tensor | None = None
+    hidden_states: torch.Tensor | None = None
+    values: torch.Tensor | None = None
+    aux: dict = field(default_factory=dict)
+
+
+class Attention(nn.Module):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, dtype, device):
+        super().__init__()
+        self.cfg = cfg
+        self.layer_idx = layer_idx
+        self.d = cfg.head_dim
+        self.qkv = QKVParallelLinear(cfg.hidden_size, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
+                                     cfg.qkv_bias, dtype, device)
+        self.hq, self.hkv = self.qkv.hq, self.qkv.hkv
+        self.o = RowParallelLinear(cfg.num_attention_heads * cfg.head_dim, cfg.hidden_size, False, dtype, device)
+        self.q_norm = self.k_norm = None
+        if cfg.qk_norm:
+            self.q_norm = RMSNorm(cfg.head_dim, cfg.rms_norm_eps, dtype, device, cfg.norm_weight_offset)
+            self.k_norm = RMSNorm(cfg.head_dim, cfg.rms_norm_eps, dtype, device, cfg.norm_weight_offset)
+        self.scale = cfg.attention_softmax_scale or cfg.head_dim ** -0.5
+        self.window = 0
+        if cfg.sliding_window and cfg.layer_types is not None and cfg.layer_types[layer_idx] == "sliding_attention":
+            self.window = int(cfg.sliding_window)
+        self.kv_cache = None  # (k_cache, v_cache, k_scale, v_scale)
+
+    def forward(self, x, positions, meta):
+        cfg = self.cfg
+        qkv = self.qkv(x)
+        qw = self.q_norm.weight if self.q_norm is not None else None
+        kw = self.k_norm.weight if self.k_norm is not None else None
+        if isinstance(meta, TrainMeta):
+            o = attn_ops.qkv_attention(
+                qkv, positions, meta.varlen, self.hq, self.hkv, self.d, scale=self.scale, theta=cfg.rope_theta,
+                rot_dim=cfg.rotary_dim, interleaved=cfg.rope_interleaved, causal=True, window=self.window,
+                q_norm_w=qw, k_norm_w=kw, norm_eps=cfg.rms_norm_eps, norm_offset=cfg.norm_weight_offset)
+            return self.o(o)
+        return self.o(self._infer(qkv, positions, meta, qw, kw))
+
+    def _infer(self, qkv, positions, meta: InferMeta, qw, kw):
+        cfg = self.cfg
+        hq, hkv, d = self.hq, self.hkv, self.d
+        t = qkv.shape[0]
+        if qw is not None:
+            q3 = qkv[:, : hq * d].unflatten(1, (hq, d))
+            k3 = qkv[:, hq * d:(hq + hkv) * d].unflatten(1, (hkv, d))
+            if qkv.is_cuda:
+                attn_ops._headnorm_fwd(q3, qw, cfg.norm_weight_offset, q3, cfg.rms_norm_eps)
+                attn_ops._headnorm_fwd(k3, kw, cfg.norm_weight_offset, k3, cfg.rms_norm_eps)
+            else:
+                q3.copy_(attn_ops._headnorm_reference(q3, qw, cfg.rms_norm_eps, cfg.norm_weight_offset))
+                k3.copy_(attn_ops._headnorm_reference(k3, kw, cfg.rms_norm_eps, cfg.norm_weight_offset))
+        kc, vc, ks, vs = self.kv_cache
+        pa.rope_append_kv(qkv, positions, meta.slot_mapping, kc, vc, ks, vs, hq, hkv, d, theta=cfg.rope_theta,
+                          rot_dim=cfg.rotary_dim, interleaved=cfg.rope_interleaved)
+        q = qkv[:, : hq * d].unflatten(1, (hq, d))
+        if meta.mode == "decode":
+            out = pa.paged_decode(q, kc, vc, ks, vs, meta.block_table, meta.seq_lens, self.scale,
+                                  max_context=meta.max_context, window=self.window)
+            return out.view(t, hq * d)
+        k = qkv[:, hq * d:(hq + hkv) * d].unflatten(1, (hkv, d))
+        v = qkv[:, (hq + hkv) * d:].unflatten(1, (hkv, d))
+        if meta.has_history:
+            k, v = _gather_history(self.kv_cache, meta, hkv, d)
+        o, _ = attn_ops.attention_forward(q, k, v, meta.varlen, self.scale, True, self.window, need_lse=False)
+        return o.view(t, hq * d)
+
+
+def _gather_history(kv_cache, meta: InferMeta, hkv: int, d: int):
+    """Contiguous K/V (cached prefix + the chunk just appended) for every sequence of a prefill
+    chunk, read back from the paged cache; used only when a prompt spans several chunks."""
+    kc, vc, ks, vs = kv_cache
+    slots = meta.history  # int64 [total_k] cache slots in packed key order
+    pages, offs = slots // pa.PAGE, slots % pa.PAGE
+    if kc.dtype == torch.uint8:
+        k = (kc.view(torch.float8_e4m3fn)[pages, :, offs].float() * ks[pages, :, offs].unsqueeze(-1)).to(torch.bfloat16)
+        v = (vc.view(torch.float8_e4m3fn)[pages, :, offs].float() * vs[pages, :, offs].unsqueeze(-1)).to(torch.bfloat16)
+    else:
+        k, v = kc[pages, :, offs], vc[pages, :, offs]
+    return k.contiguous(), v.contiguous()
+
+
+class DecoderLayer(nn.Module):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, dtype, device, mlp: nn.Module | None = None):
+        super().__init__()
+        self.input_norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device, cfg.norm_weight_offset)
+        self.attn = Attention(cfg, layer_idx, dtype, device)
+        self.post_norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device, cfg.norm_weight_offset)
+        self.mlp = mlp if mlp is not None else GatedMLP(cfg.hidden_size, cfg.intermediate_size, cfg.hidden_act,
+                                                        cfg.use_bias, dtype, device)
+
+    def forward(self, x, residual, positions, meta):
+        if residual is None:
+            residual = x
+            h = self.input_norm(x)
+        else:
+            h, residual = self.input_norm(x, residual)
+        h = self.attn(h, positions, meta)
+        h, residual = self.post_norm(h, residual)
+        h = self.mlp(h)
+        return h, residual
+
+
+class DenseCausalLM(nn.Module):
+    """Embedding -> N x DecoderLayer -> final norm; ``lm_head`` is applied by the caller."""
+
+    def __init__(self, cfg: ModelConfig, device="cpu", dtype: torch.dtype | None = None):
+        super().__init__()
+        dtype = dtype or cfg.dtype
+        self.cfg = cfg
+        self.embed = VocabParallelEmbedding(cfg.vocab_size, cfg.hidden_size, dtype, device, cfg.embed_scale)
+        self.layers = nn.ModuleList([self._make_layer(i, dtype, device) for i in range(cfg.num_hidden_layers)])
+        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device, cfg.norm_weight_offset)
+        self.lm_head = VocabParallelLMHead(cfg.vocab_size, cfg.hidden_size, dtype, device,
+                                           tied_to=self.embed if cfg.tie_word_embeddings else None)
+        self._kv_spec = None
+
+    def _make_layer(self, i, dtype, device):
+        return DecoderLayer(self.cfg, i, dtype, device)
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, input_ids, position_ids, meta) -> CausalLMOutput:
+        ids = input_ids.reshape(-1)
+        positions = position_ids.reshape(-1)
+        if positions.dtype != torch.int32:
+            positions = positions.to(torch.int32)
+        x = self.embed(ids)
+        residual = None
+        use_ckpt = isinstance(meta, TrainMeta) and meta.activation_checkpointing and torch.is_grad_enabled()
+        for layer in self.layers:
+            if use_ckpt:
+                if residual is None:
+                    x, residual = checkpoint(_run_first, layer, x, positions, meta, use_reentrant=False)
+                else:
+                    x, residual = checkpoint(layer, x, residual, positions, meta, use_reentrant=False)
+            else:
+                x, residual = layer(x, residual, positions, meta)
+        h, _ = self.norm(x, residual)
+        out = CausalLMOutput(hidden_states=h)
+        if isinstance(meta, InferMeta):
+            rows = h if meta.logit_rows is None else h.index_select(0, meta.logit_rows)
+            out.logits_shard = self.compute_logits(rows, out_dtype=torch.float32)
+        return out
+
+    def compute_logits(self, hidden, out_dtype=torch.bfloat16):
+        logits = self.lm_head(hidden, out_dtype=out_dtype)
+        cap = self.cfg.final_logit_softcapping
+        if cap:
+            logits = (torch.tanh(logits.float() / cap) * cap).to(logits.dtype)
+        return logits
+
+    # --------------------------------------------------------- engine lifecycle
+    def kv_cache_bytes_per_page(self, fp8: bool) -> int:
+        hkv = self.layers[0].attn.hkv
+        d = self.cfg.head_dim
+        per = hkv * pa.PAGE * d * (1 if fp8 else 2) * 2
+        if fp8:
+            per += hkv * pa.PAGE * 4 * 2
+        return per * len(self.layers)
+
+    def allocate_kv_caches(self, num_pages: int, fp8: bool = False) -> None:
+        dev = self.embed.weight.device
+        for layer in self.layers:
+            a = layer.attn
+            a.kv_cache = pa.alloc_kv_cache(num_pages, a.hkv, a.d, dev, fp8)
+        self._kv_spec = (num_pages, fp8)
+
+    def set_kv_caches(self, caches) -> None:
+        for layer, c in zip(self.layers, caches):
+            layer.attn.kv_cache = c
+
+    def kv_caches(self):
+        return [layer.attn.kv_cache for layer in self.layers]
+
+    def clear_kv_caches(self) -> None:
+        for layer in self.layers:
+            layer.attn.kv_cache = None
+        self._kv_spec = None
+
+    def reset_kv_caches(self) -> None:
+        """Nothing to zero: pages are only read below ``seq_lens``."""
+
+    def offload_kv_caches(self) -> None:
+        self._kv_host = [tuple(None if t is None else t.to("cpu") for t in c) for c in self.kv_caches()]
+        self.clear_kv_caches()
+
+    def onload_kv_caches(self) -> None:
+        dev = self.embed.weight.device
+        host = getattr(self, "_kv_host", None)
+        if host is not None:
+            self.set_kv_caches([tuple(None if t is None else t.to(dev) for t in c) for c in host])
+            self._kv_host = None
+
+    def prepare_infer_weights(self) -> None:
+        """Dense layers use the training weights directly for inference."""
+
+    def clear_infer_weights(self) -> None:
+        pass
+
+    def offload_train_weights(self) -> None:
+        for p in self.parameters():
+            p.data = p.data.to("cpu", non_blocking=True)
+
+    def onload_train_weights(self, device) -> None:
+        for p in self.parameters():
+            p.data = p.data.to(device, non_blocking=True)
+
+    def finalize_router_expert_bias(self, tp_group=None, dp_group=None) -> None:
+        pass
+
+
+def _run_first(layer, x, positions, meta):
+    return layer(x, None, positions, meta)
+
+
+def init_weights(model: nn.Module, seed: int = 0, std: float = 0.02) -> None:
+    """Seeded random init (normal(0, std) for matrices, ones for norm scales, zeros for biases)."""
+    gen_cpu = torch.Generator().manual_seed(seed)
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            if p.dim() >= 2:
+                if p.is_cuda:
+                    g = torch.Generator(device=p.device).manual_seed(seed + (zlib.crc32(name.encode()) % 100003))
+                    p.normal_(0.0, std, generator=g)
+                else:
+                    p.copy_(torch.randn(p.shape, generator=gen_cpu) * std)
+            elif "norm" in name:
+                p.fill_(1.0 if getattr(model, "cfg", None) is None or model.cfg.norm_weight_offset == 0.0 else 0.0)
+            else:
+                p.zero_()

@@ -1,0 +1,202 @@
+"""Tensor-parallel building blocks shared by the model families.
+
+Every linear stores its weight ``[out_local, in]`` (row-major, K-major for the tcgen05 GEMM) and
+calls ``ops.gemm.linear``.  Column-parallel layers shard the output features, row-parallel layers
+shard the input features and reduce over the TP group.  Parameters carry two annotations used by
+the trainer and the checkpoint code:
+
+* ``tp_shard``: ``("col" | "row" | "vocab" | "qkv" | "merged" | None, meta)`` describing how the
+  local tensor maps onto the full HF tensor(s);
+* ``tp_replicated_grad``: gradient must be summed over TP (norm weights, router gates, ...).
+
+Role of ``areno/engine/layers/{linear,vocab,mlp,norm}.py`` in the reference.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from ..ops import activation, embedding as emb_ops, gemm, norm as norm_ops
+from ..parallel import collectives as coll
+from ..parallel.context import get_context
+
+
+def _param(shape, dtype, device) -> nn.Parameter:
+    return nn.Parameter(torch.empty(shape, dtype=dtype, device=device), requires_grad=True)
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, hidden: int, eps: float, dtype, device, offset: float = 0.0, with_scale: bool = True):
+        super().__init__()
+        self.eps = eps
+        self.offset = offset
+        self.weight = _param((hidden,), dtype, device) if with_scale else None
+        if self.weight is not None:
+            self.weight.tp_replicated_grad = True
+
+    def forward(self, x, residual=None):
+        return norm_ops.rmsnorm(x, self.weight, self.eps, residual=residual, w_offset=self.offset)
+
+
+class ColumnParallelLinear(nn.Module):
+    """y_local = x W_localᵀ (+ b_local); input replicated over TP, output sharded on features."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool, dtype, device, gather_output: bool = False):
+        super().__init__()
+        ctx = get_context()
+        assert out_features % ctx.tp_size == 0, "column-parallel output must divide tp_size"
+        self.in_features, self.out_features = in_features, out_features
+        self.out_local = out_features // ctx.tp_size
+        self.gather_output = gather_output
+        self.weight = _param((self.out_local, in_features), dtype, device)
+        self.weight.tp_shard = ("col", None)
+        self.bias = _param((self.out_local,), dtype, device) if bias else None
+        if self.bias is not None:
+            self.bias.tp_shard = ("col", None)
+
+    def forward(self, x):
+        x = coll.copy_to_tp(x)
+        y = gemm.linear(x, self.weight, self.bias)
+        if self.gather_output:
+            y = coll.all_gather_last_dim(y)
+        return y
+
+
+class MergedColumnParallelLinear(nn.Module):
+    """Several column-parallel projections of the same input fused into one GEMM (gate_up)."""
+
+    def __init__(self, in_features: int, out_features: list[int], bias: bool, dtype, device):
+        super().__init__()
+        ctx = get_context()
+        for o in out_features:
+            assert o % ctx.tp_size == 0
+        self.in_features = in_features
+        self.out_features = list(out_features)
+        self.out_locals = [o // ctx.tp_size for o in out_features]
+        self.weight = _param((sum(self.out_locals), in_features), dtype, device)
+        self.weight.tp_shard = ("merged", self.out_locals)
+        self.bias = _param((sum(self.out_locals),), dtype, device) if bias else None
+        if self.bias is not None:
+            self.bias.tp_shard = ("merged", self.out_locals)
+
+    def forward(self, x):
+        return gemm.linear(coll.copy_to_tp(x), self.weight, self.bias)
+
+
+class QKVParallelLinear(nn.Module):
+    """Fused q/k/v projection.  Q heads are split over TP; KV heads are split when they divide
+    ``tp_size`` and otherwise replicated (``tp_size`` a multiple of the KV head count)."""
+
+    def __init__(self, hidden: int, num_heads: int, num_kv_heads: int, head_dim: int, bias: bool, dtype, device,
+                 q_mult: int = 1):
+        super().__init__()
+        ctx = get_context()
+        tp = ctx.tp_size
+        assert num_heads % tp == 0
+        self.hq = num_heads // tp
+        if num_kv_heads >= tp:
+            assert num_kv_heads % tp == 0
+            self.hkv = num_kv_heads // tp
+            self.kv_rep = 1
+        else:
+            assert tp % num_kv_heads == 0
+            self.hkv = 1
+            self.kv_rep = tp // num_kv_heads
+        self.head_dim = head_dim
+        self.q_mult = q_mult  # 2 when the projection also carries an output gate per q head
+        out = (self.hq * q_mult + 2 * self.hkv) * head_dim
+        self.weight = _param((out, hidden), dtype, device)
+        self.weight.tp_shard = ("qkv", (self.hq * q_mult, self.hkv, head_dim, self.kv_rep))
+        self.bias = _param((out,), dtype, device) if bias else None
+        if self.bias is not None:
+            self.bias.tp_shard = ("qkv", (self.hq * q_mult, self.hkv, head_dim, self.kv_rep))
+        if self.kv_rep > 1:
+            # k/v rows are replicated over `kv_rep` ranks: their grads must be summed over replicas
+            self.weight.kv_replicated = self.kv_rep
+
+    def forward(self, x):
+        return gemm.linear(coll.copy_to_tp(x), self.weight, self.bias)
+
+
+class RowParallelLinear(nn.Module):
+    """y = sum_over_tp(x_local W_localᵀ) (+ b); input sharded on features, output replicated."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool, dtype, device, reduce_output: bool = True):
+        super().__init__()
+        ctx = get_context()
+        assert in_features % ctx.tp_size == 0
+        self.in_local = in_features // ctx.tp_size
+        self.out_features = out_features
+        self.reduce_output = reduce_output
+        self.weight = _param((out_features, self.in_local), dtype, device)
+        self.weight.tp_shard = ("row", None)
+        self.bias = _param((out_features,), dtype, device) if bias else None
+        if self.bias is not None:
+            self.bias.tp_replicated_grad = True
+
+    def forward(self, x):
+        ctx = get_context()
+        if ctx.tp_size == 1:
+            return gemm.linear(x, self.weight, self.bias)
+        y = gemm.linear(x, self.weight, None)
+        if self.reduce_output:
+            y = coll.reduce_from_tp(y)
+        if self.bias is not None:
+            y = y + self.bias
+        return y
+
+
+class VocabParallelEmbedding(nn.Module):
+    def __init__(self, vocab: int, hidden: int, dtype, device, scale: float = 1.0):
+        super().__init__()
+        ctx = get_context()
+        self.vocab = vocab
+        self.per_rank = (vocab + ctx.tp_size - 1) // ctx.tp_size
+        # pad so every rank holds the same number of rows (multiple of 8 keeps 16-byte alignment)
+        self.per_rank = (self.per_rank + 7) // 8 * 8
+        self.vocab_start = ctx.tp_rank * self.per_rank
+        self.scale = scale
+        self.weight = _param((self.per_rank, hidden), dtype, device)
+        self.weight.tp_shard = ("vocab", vocab)
+
+    def forward(self, ids):
+        out = emb_ops.embedding(ids, self.weight, self.vocab_start, self.scale)
+        return coll.reduce_from_tp(out)
+
+
+class VocabParallelLMHead(nn.Module):
+    """Output projection onto the local vocabulary shard (weight may be tied to the embedding)."""
+
+    def __init__(self, vocab: int, hidden: int, dtype, device, tied_to: VocabParallelEmbedding | None = None):
+        super().__init__()
+        ctx = get_context()
+        self.vocab = vocab
+        per_rank = (vocab + ctx.tp_size - 1) // ctx.tp_size
+        self.per_rank = (per_rank + 7) // 8 * 8
+        self.vocab_start = ctx.tp_rank * self.per_rank
+        self.valid_local = max(0, min(self.per_rank, vocab - self.vocab_start))
+        if tied_to is not None:
+            self.weight = tied_to.weight
+        else:
+            self.weight = _param((self.per_rank, hidden), dtype, device)
+            self.weight.tp_shard = ("vocab", vocab)
+
+    def forward(self, hidden, out_dtype=torch.bfloat16):
+        """Logits over the local shard ``[rows, per_rank]`` (columns past ``valid_local`` are padding)."""
+        if hidden.is_cuda and not (torch.is_grad_enabled() and hidden.requires_grad):
+            return gemm.gemm(hidden.reshape(-1, hidden.shape[-1]), self.weight, out_dtype=out_dtype)
+        return gemm.linear(hidden, self.weight)
+
+
+class GatedMLP(nn.Module):
+    def __init__(self, hidden: int, intermediate: int, act: str, bias: bool, dtype, device):
+        super().__init__()
+        self.gate_up = MergedColumnParallelLinear(hidden, [intermediate, intermediate], bias, dtype, device)
+        self.down = RowParallelLinear(intermediate, hidden, bias, dtype, device)
+        self.act = act
+
+    def forward(self, x):
+        gu = self.gate_up(x)
+        a = activation.silu_and_mul(gu) if self.act == "silu" else activation.gelu_tanh_and_mul(gu)
+        return self.down(a)

@@ -24,7 +24,7 @@ _SIG_CODES = {
 
 # name -> argument type codes (p = pointer, i = int, l = long long, f = float); all return int.
 _SIGNATURES: dict[str, str] = {
-    "areno_gemm_bf16": "ppppiiillliiiipp",
+    "areno_gemm_bf16": "ppppiiillliiiiplpp",
     "areno_rmsnorm_fwd": "pppifppplifp",
     "areno_rmsnorm_bwd_blocks": "l",
     "areno_rmsnorm_bwd": "pppifpppppilip",
@@ -37,6 +37,23 @@ _SIGNATURES: dict[str, str] = {
     "areno_accumulate_bf16": "pplp",
     "areno_attn_fwd": "pppppppp" + "iiiii" + "llll" + "fiip",
     "areno_attn_bwd": "pppppppppp" + "pppp" + "iii" + "l" + "iii" + "llllllll" + "fiip",
+    "areno_gemm_workspace_bytes": "iii",
+    "areno_headnorm_fwd": "plpifplpliifp",
+    "areno_headnorm_bwd_blocks": "l",
+    "areno_headnorm_bwd": "plplpifpplppiliip",
+    "areno_page_size": "",
+    "areno_rope_append_kv": "pppppppp" + "l" + "iiii" + "f" + "iii" + "p",
+    "areno_paged_decode": "pppppppppp" + "iiiii" + "ll" + "f" + "iiii" + "p",
+    "areno_logprob_stats": "pilliplppppp",
+    "areno_logprob_bwd": "pilliplppppp",
+    "areno_sample": "pilliippififlppppp",
+    "areno_adamw_fp32": "ppppplfffffifpp",
+    "areno_adamw_8bit": "ppppppplfffffifpp",
+    "areno_sumsq_blocks": "",
+    "areno_sumsq": "plppip",
+    "areno_scale_f32": "plpfp",
+    "areno_cast_f32_bf16": "pplp",
+    "areno_policy_loss": "ppppppppplfffip",
 }
 
 _lock = threading.Lock()
@@ -93,8 +110,16 @@ def fn(name: str):
     return f
 
 
+# Kernel launches issued through this module (an entry point may launch more than one kernel).
+_KERNELS_PER_CALL = {"areno_attn_bwd": 3, "areno_paged_decode": 2, "areno_rmsnorm_bwd": 2, "areno_sumsq": 2,
+                     "areno_headnorm_bwd": 2}
+launch_count = 0
+
+
 def call(name: str, *args) -> int:
     """Invoke an entry point and raise on a non-zero return code."""
+    global launch_count
+    launch_count += _KERNELS_PER_CALL.get(name, 1)
     rc = fn(name)(*args)
     if rc != 0:
         raise RuntimeError(f"{name} failed with code {rc}")

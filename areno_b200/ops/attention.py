@@ -187,53 +187,116 @@ def _reference_autograd(q, k, v, meta, scale, causal, window):
     return torch.cat(outs, dim=0).to(q.dtype)
 
 
+def _headnorm_fwd(x3, w, w_offset, y3, eps):
+    """x3, y3: [T, heads, D] strided views; returns inv_rms [T * heads]."""
+    t, heads, d = x3.shape
+    inv = torch.empty(t * heads, dtype=torch.float32, device=x3.device)
+    _lib.call("areno_headnorm_fwd", x3.data_ptr(), x3.stride(0), w.data_ptr(), int(w.dtype == torch.float32),
+              float(w_offset), y3.data_ptr(), y3.stride(0), inv.data_ptr(), t, heads, d, float(eps), _lib.stream())
+    return inv
+
+
+def _headnorm_bwd(dy3, x3, w, w_offset, inv, dx3):
+    """Returns fp32 dW [D] (or None when accumulated into ``w.main_grad``)."""
+    t, heads, d = x3.shape
+    nblk = _lib.fn("areno_headnorm_bwd_blocks")(t * heads)
+    partial = torch.empty((nblk, d), dtype=torch.float32, device=x3.device)
+    main_grad = getattr(w, "main_grad", None)
+    if main_grad is not None:
+        target, acc = main_grad, 1
+        w.grad_added_to_main_grad = True
+    else:
+        target, acc = torch.empty(d, dtype=torch.float32, device=x3.device), 0
+    _lib.call("areno_headnorm_bwd", dy3.data_ptr(), dy3.stride(0), x3.data_ptr(), x3.stride(0), w.data_ptr(),
+              int(w.dtype == torch.float32), float(w_offset), inv.data_ptr(), dx3.data_ptr(), dx3.stride(0),
+              partial.data_ptr(), target.data_ptr(), acc, t, heads, d, _lib.stream())
+    return None if acc else target.to(w.dtype)
+
+
 class _QKVAttention(torch.autograd.Function):
-    """Fused RoPE + attention on the packed QKV projection output ``[T, (Hq + 2 Hkv) D]``."""
+    """Fused (q/k head-norm +) RoPE + attention on the packed QKV projection output
+    ``[T, (Hq + 2 Hkv) D]``."""
 
     @staticmethod
-    def forward(ctx, qkv, positions, meta, hq, hkv, d, scale, theta, rot_dim, inv_freq, interleaved, causal,
-                window):
+    def forward(ctx, qkv, q_norm_w, k_norm_w, positions, meta, hq, hkv, d, scale, theta, rot_dim, inv_freq,
+                interleaved, causal, window, norm_eps, norm_offset):
         assert qkv.is_contiguous()
         q = _heads_view(qkv, 0, hq, d)
         k = _heads_view(qkv, hq * d, hkv, d)
         v = _heads_view(qkv, (hq + hkv) * d, hkv, d)
+        has_norm = q_norm_w is not None
+        inv_q = inv_k = qk2 = None
+        if has_norm:
+            qk2 = torch.empty((qkv.shape[0], (hq + hkv) * d), dtype=qkv.dtype, device=qkv.device)
+            qn = _heads_view(qk2, 0, hq, d)
+            kn = _heads_view(qk2, hq * d, hkv, d)
+            inv_q = _headnorm_fwd(q, q_norm_w, norm_offset, qn, norm_eps)
+            inv_k = _headnorm_fwd(k, k_norm_w, norm_offset, kn, norm_eps)
+            q, k = qn, kn
         if rot_dim > 0:
             _rope_inplace(q, positions, theta, rot_dim, inv_freq, interleaved, 1.0)
             _rope_inplace(k, positions, theta, rot_dim, inv_freq, interleaved, 1.0)
         o, lse = attention_forward(q, k, v, meta, scale, causal, window)
-        ctx.save_for_backward(qkv, o, lse, positions, *([inv_freq] if inv_freq is not None else []))
+        extras = []
+        if inv_freq is not None:
+            extras.append(inv_freq)
+        if has_norm:
+            extras += [qk2, inv_q, inv_k, q_norm_w, k_norm_w]
+        ctx.save_for_backward(qkv, o, lse, positions, *extras)
         ctx.meta = meta
-        ctx.args = (hq, hkv, d, scale, theta, rot_dim, interleaved, causal, window, inv_freq is not None)
+        ctx.args = (hq, hkv, d, scale, theta, rot_dim, interleaved, causal, window, inv_freq is not None, has_norm,
+                    norm_offset)
         return o.view(o.shape[0], hq * d)
 
     @staticmethod
     def backward(ctx, do):
-        saved = ctx.saved_tensors
+        saved = list(ctx.saved_tensors)
         qkv, o, lse, positions = saved[:4]
-        hq, hkv, d, scale, theta, rot_dim, interleaved, causal, window, has_freq = ctx.args
-        inv_freq = saved[4] if has_freq else None
-        q = _heads_view(qkv, 0, hq, d)
-        k = _heads_view(qkv, hq * d, hkv, d)
+        rest = saved[4:]
+        hq, hkv, d, scale, theta, rot_dim, interleaved, causal, window, has_freq, has_norm, norm_offset = ctx.args
+        inv_freq = rest.pop(0) if has_freq else None
         v = _heads_view(qkv, (hq + hkv) * d, hkv, d)
         dqkv = torch.empty_like(qkv)
-        dq = _heads_view(dqkv, 0, hq, d)
-        dk = _heads_view(dqkv, hq * d, hkv, d)
         dv = _heads_view(dqkv, (hq + hkv) * d, hkv, d)
         do3 = do.reshape(do.shape[0], hq, d)
+        dwq = dwk = None
+        if has_norm:
+            qk2, inv_q, inv_k, q_norm_w, k_norm_w = rest
+            q = _heads_view(qk2, 0, hq, d)
+            k = _heads_view(qk2, hq * d, hkv, d)
+            dqk2 = torch.empty_like(qk2)
+            dq = _heads_view(dqk2, 0, hq, d)
+            dk = _heads_view(dqk2, hq * d, hkv, d)
+        else:
+            q = _heads_view(qkv, 0, hq, d)
+            k = _heads_view(qkv, hq * d, hkv, d)
+            dq = _heads_view(dqkv, 0, hq, d)
+            dk = _heads_view(dqkv, hq * d, hkv, d)
         attention_backward(q, k, v, o, do3, lse, ctx.meta, scale, causal, window, dq, dk, dv)
         if rot_dim > 0:
             _rope_inplace(dq, positions, theta, rot_dim, inv_freq, interleaved, -1.0)
             _rope_inplace(dk, positions, theta, rot_dim, inv_freq, interleaved, -1.0)
-        return (dqkv,) + (None,) * 12
+        if has_norm:
+            dwq = _headnorm_bwd(dq, _heads_view(qkv, 0, hq, d), q_norm_w, norm_offset, inv_q,
+                                _heads_view(dqkv, 0, hq, d))
+            dwk = _headnorm_bwd(dk, _heads_view(qkv, hq * d, hkv, d), k_norm_w, norm_offset, inv_k,
+                                _heads_view(dqkv, hq * d, hkv, d))
+        return (dqkv, dwq, dwk) + (None,) * 14
+
+
+def _headnorm_reference(x, w, eps, offset):
+    xf = x.float()
+    y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * (w.float() + offset)
+    return y.to(x.dtype)
 
 
 def qkv_attention(qkv, positions, meta: VarlenMeta, hq: int, hkv: int, d: int, scale: float | None = None,
                   theta: float = 10000.0, rot_dim: int | None = None, inv_freq=None, interleaved: bool = False,
-                  causal: bool = True, window: int = 0):
-    """RoPE + causal attention on a packed ``[T, (Hq + 2 Hkv) D]`` projection output.
-
-    On CUDA, ``qkv`` is rotated in place (it is the private output of the QKV GEMM).
-    Returns ``[T, Hq D]``.
+                  causal: bool = True, window: int = 0, q_norm_w=None, k_norm_w=None, norm_eps: float = 1e-6,
+                  norm_offset: float = 0.0):
+    """(per-head q/k RMSNorm +) RoPE + causal attention on a packed ``[T, (Hq + 2 Hkv) D]`` projection
+    output.  On CUDA, ``qkv`` is rotated in place when no head norm is used (it is the private
+    output of the QKV GEMM).  Returns ``[T, Hq D]``.
     """
     scale = d ** -0.5 if scale is None else scale
     rot = d if rot_dim is None else rot_dim
@@ -242,14 +305,17 @@ def qkv_attention(qkv, positions, meta: VarlenMeta, hq: int, hkv: int, d: int, s
         q = qkv[:, : hq * d].reshape(t, hq, d)
         k = qkv[:, hq * d: (hq + hkv) * d].reshape(t, hkv, d)
         v = qkv[:, (hq + hkv) * d:].reshape(t, hkv, d)
+        if q_norm_w is not None:
+            q = _headnorm_reference(q, q_norm_w, norm_eps, norm_offset)
+            k = _headnorm_reference(k, k_norm_w, norm_eps, norm_offset)
         if rot > 0:
             q = _rope_diff(q, positions, theta, rot, inv_freq, interleaved)
             k = _rope_diff(k, positions, theta, rot, inv_freq, interleaved)
         return _reference_autograd(q, k, v, meta, scale, causal, window).reshape(t, hq * d)
     if positions.dtype != torch.int32:
         positions = positions.to(torch.int32)
-    return _QKVAttention.apply(qkv, positions, meta, hq, hkv, d, scale, theta, rot, inv_freq, interleaved, causal,
-                               window)
+    return _QKVAttention.apply(qkv, q_norm_w, k_norm_w, positions, meta, hq, hkv, d, scale, theta, rot, inv_freq,
+                               interleaved, causal, window, norm_eps, norm_offset)
 
 
 def _rope_diff(x, positions, theta, rot, inv_freq, interleaved):

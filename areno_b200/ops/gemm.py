@@ -85,13 +85,34 @@ def gemm(
     if bias is not None:
         assert bias.dtype == torch.bfloat16 and bias.is_contiguous() and bias.numel() == n
     status = _lib.status_buffer(a.device)
+    ws_ptr, ws_bytes = None, 0
+    if m <= 128 and epi <= EPI_BF16_BIAS and n <= 18944 and k >= 512:
+        ws = _workspace(a.device, 16 * m * n * 4)
+        ws_ptr, ws_bytes = ws.data_ptr(), ws.numel()
     _lib.call(
         "areno_gemm_bf16",
         a.data_ptr(), b.data_ptr(), out.data_ptr(), _lib.ptr(bias),
         m, n, k, a.stride(0), b.stride(0), out.stride(0),
-        int(a_mn), int(b_mn), epi, bn, status.data_ptr(), _lib.stream(),
+        int(a_mn), int(b_mn), epi, bn, ws_ptr, ws_bytes, status.data_ptr(), _lib.stream(),
     )
     return out
+
+
+_WORKSPACES: dict[int, torch.Tensor] = {}
+
+
+def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    """Per-device split-K scratch (uint8), grown on demand and reused by every skinny GEMM.
+
+    Calls on one stream serialise on it; the buffer must not be shared across streams that
+    run concurrently.
+    """
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    ws = _WORKSPACES.get(idx)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 32 << 20), dtype=torch.uint8, device=torch.device("cuda", idx))
+        _WORKSPACES[idx] = ws
+    return ws
 
 
 class _Linear(torch.autograd.Function):

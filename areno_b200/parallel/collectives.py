@@ -1,0 +1,155 @@
+"""Tensor-parallel collectives as autograd functions (NCCL / Gloo baseline path).
+
+These are the library-collective versions of the TP seams; the fused sm_100a kernels in
+``areno_b200.parallel.fused`` replace them on the hot paths when symmetric memory is set up.
+Call sites mirror ``areno/engine/parallel/collectives.py:95-242`` of the reference, except that
+``reduce_scatter_rows`` is a true reduce-scatter (the reference all-reduces a pre-sliced chunk).
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from .context import get_context
+
+
+def _tp():
+    ctx = get_context()
+    return ctx.tp_group, ctx.tp_size, ctx.tp_rank
+
+
+class _ReduceFromTP(torch.autograd.Function):
+    """forward: all-reduce (sum); backward: identity."""
+
+    @staticmethod
+    def forward(ctx, x):
+        group, size, _ = _tp()
+        if size == 1:
+            return x
+        x = x.contiguous()
+        dist.all_reduce(x, group=group)
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        return g
+
+
+class _CopyToTP(torch.autograd.Function):
+    """forward: identity; backward: all-reduce (sum)."""
+
+    @staticmethod
+    def forward(ctx, x):
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        group, size, _ = _tp()
+        if size == 1:
+            return g
+        g = g.contiguous()
+        dist.all_reduce(g, group=group)
+        return g
+
+
+class _GatherRows(torch.autograd.Function):
+    """forward: all-gather along dim 0; backward: reduce-scatter along dim 0."""
+
+    @staticmethod
+    def forward(ctx, x):
+        group, size, _ = _tp()
+        if size == 1:
+            return x
+        x = x.contiguous()
+        out = torch.empty((x.shape[0] * size, *x.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(out, x, group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        group, size, _ = _tp()
+        if size == 1:
+            return g
+        g = g.contiguous()
+        out = torch.empty((g.shape[0] // size, *g.shape[1:]), dtype=g.dtype, device=g.device)
+        dist.reduce_scatter_tensor(out, g, group=group)
+        return out
+
+
+class _ReduceScatterRows(torch.autograd.Function):
+    """forward: reduce-scatter along dim 0; backward: all-gather along dim 0."""
+
+    @staticmethod
+    def forward(ctx, x):
+        group, size, _ = _tp()
+        if size == 1:
+            return x
+        x = x.contiguous()
+        out = torch.empty((x.shape[0] // size, *x.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.reduce_scatter_tensor(out, x, group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        group, size, _ = _tp()
+        if size == 1:
+            return g
+        g = g.contiguous()
+        out = torch.empty((g.shape[0] * size, *g.shape[1:]), dtype=g.dtype, device=g.device)
+        dist.all_gather_into_tensor(out, g, group=group)
+        return out
+
+
+def reduce_from_tp(x):
+    return _ReduceFromTP.apply(x) if get_context().tp_size > 1 else x
+
+
+def copy_to_tp(x):
+    return _CopyToTP.apply(x) if get_context().tp_size > 1 else x
+
+
+def gather_rows(x):
+    return _GatherRows.apply(x) if get_context().tp_size > 1 else x
+
+
+def reduce_scatter_rows(x):
+    return _ReduceScatterRows.apply(x) if get_context().tp_size > 1 else x
+
+
+def all_gather_last_dim(x):
+    group, size, _ = _tp()
+    if size == 1:
+        return x
+    x = x.contiguous()
+    parts = [torch.empty_like(x) for _ in range(size)]
+    dist.all_gather(parts, x, group=group)
+    return torch.cat(parts, dim=-1)
+
+
+def all_gather_first_dim(x):
+    group, size, _ = _tp()
+    if size == 1:
+        return x.unsqueeze(0)
+    x = x.contiguous()
+    out = torch.empty((size, *x.shape), dtype=x.dtype, device=x.device)
+    dist.all_gather_into_tensor(out.view(-1, *x.shape[1:]) if x.dim() > 0 else out, x, group=group)
+    return out
+
+
+def broadcast_tensor(x, src_tp_rank: int = 0):
+    ctx = get_context()
+    if ctx.tp_size == 1:
+        return x
+    src = ctx.dp_rank * ctx.tp_size + src_tp_rank
+    dist.broadcast(x, src=src, group=ctx.tp_group)
+    return x
+
+
+def broadcast_object(obj, src_tp_rank: int = 0):
+    ctx = get_context()
+    if ctx.tp_size == 1:
+        return obj
+    box = [obj]
+    dist.broadcast_object_list(box, src=ctx.dp_rank * ctx.tp_size + src_tp_rank, group=ctx.tp_group)
+    return box[0]

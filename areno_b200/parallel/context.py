@@ -1,0 +1,96 @@
+"""Process-group layout: ``global_rank = dp_rank * tp_size + tp_rank``; one TP group per DP row and
+one DP group per TP column (same layout as ``areno/engine/parallel/context.py:65-127``).  NCCL on
+CUDA, Gloo on CPU; rendezvous over TCP on 127.0.0.1."""
+
+from __future__ import annotations
+
+import datetime
+import os
+from dataclasses import dataclass
+from typing import Any
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass
+class ParallelContext:
+    rank: int = 0
+    world_size: int = 1
+    tp_rank: int = 0
+    tp_size: int = 1
+    dp_rank: int = 0
+    dp_size: int = 1
+    tp_group: Any = None
+    dp_group: Any = None
+    device: torch.device = torch.device("cpu")
+
+    @property
+    def is_tp_first(self) -> bool:
+        return self.tp_rank == 0
+
+
+_CONTEXT = ParallelContext()
+
+
+def get_context() -> ParallelContext:
+    return _CONTEXT
+
+
+def set_context(ctx: ParallelContext) -> None:
+    global _CONTEXT
+    _CONTEXT = ctx
+
+
+def single_process_context(device: torch.device | str = "cpu") -> ParallelContext:
+    ctx = ParallelContext(device=torch.device(device))
+    set_context(ctx)
+    return ctx
+
+
+def init_parallel(rank: int, world_size: int, tp_size: int, *, master_addr: str = "127.0.0.1", master_port: int = 0,
+                  backend: str | None = None, device: torch.device | None = None,
+                  timeout_s: float = 1800.0) -> ParallelContext:
+    """Create the default group plus TP / DP sub-groups and install the global context."""
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+    if backend is None:
+        backend = "nccl" if device.type == "cuda" else "gloo"
+    dp_size = world_size // tp_size
+    if not dist.is_initialized() and world_size > 1:
+        init = f"tcp://{master_addr}:{master_port}" if master_port else "env://"
+        kwargs: dict[str, Any] = {}
+        if backend == "nccl":
+            kwargs["device_id"] = device
+        dist.init_process_group(backend=backend, init_method=init, rank=rank, world_size=world_size,
+                                timeout=datetime.timedelta(seconds=timeout_s), **kwargs)
+    tp_group = dp_group = None
+    if world_size > 1:
+        for d in range(dp_size):
+            ranks = list(range(d * tp_size, (d + 1) * tp_size))
+            g = dist.new_group(ranks=ranks, backend=backend) if tp_size > 1 else None
+            if rank in ranks:
+                tp_group = g
+        for t in range(tp_size):
+            ranks = list(range(t, world_size, tp_size))
+            g = dist.new_group(ranks=ranks, backend=backend) if dp_size > 1 else None
+            if rank in ranks:
+                dp_group = g
+    ctx = ParallelContext(rank=rank, world_size=world_size, tp_rank=rank % tp_size, tp_size=tp_size,
+                          dp_rank=rank // tp_size, dp_size=dp_size, tp_group=tp_group, dp_group=dp_group,
+                          device=device)
+    set_context(ctx)
+    return ctx
+
+
+def destroy_parallel() -> None:
+    if dist.is_initialized():
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+    set_context(ParallelContext())
+
+
+def env_rank_world() -> tuple[int, int, int]:
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))

@@ -1,0 +1,341 @@
+"""Headline benchmark: one GRPO RL step (rollout + train + weight sync) on a Qwen2.5-7B-shaped model.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+Per GPU the step does 8 prompts x 8 samples (prompt lengths uniform in [128, 512], uniform random
+token ids, 1024 new tokens at temperature 1.0 with EOS ignored), a seeded-hash {0,1} reward,
+group-normalised advantages, and a GRPO update over micro-batches of at most 4096 tokens with fp32
+gradient accumulation and one AdamW step.  With N > 1 (one process per GPU, launched by
+``torch.distributed.run``) the per-GPU work is fixed (weak scaling): 64 x N sequences per step.
+
+Metric: whole-job tokens per second, counting every sequence token (prompt + response) once per
+step, i.e. the tokens that went through rollout and were then trained on.
+
+Two numbers are reported: ``value`` is timed with CUDA events around the engine-level step;
+``e2e`` is timed by wall clock around the same step driven through the public SDK
+(``areno_b200.api.Trainer``), including the pinned host->device copy of the step's token ids and
+the device->host read of the rollout results and the loss.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+MODEL = dict(model_type="qwen2", vocab_size=152064, hidden_size=3584, intermediate_size=18944,
+             num_hidden_layers=28, num_attention_heads=28, num_key_value_heads=4, head_dim=128,
+             rms_norm_eps=1e-6, rope_theta=1_000_000.0, max_position_embeddings=32768, qkv_bias=True,
+             qk_norm=False, tie_word_embeddings=False)
+PROMPTS_PER_GPU = 8
+GROUP = 8
+PROMPT_MIN, PROMPT_MAX = 128, 512
+NEW_TOKENS = 1024
+MICRO_TOKENS = 4096
+BASELINE_PUBLISHED = None  # the reference publishes no number for this metric
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--small", action="store_true", help="tiny model / short rollout (functional check only)")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--adam-8bit", action="store_true")
+    return ap.parse_args()
+
+
+# ------------------------------------------------------------------------- synthetic data
+def make_prompts(step: int, rank: int, vocab: int, n_prompts: int, pmin: int, pmax: int) -> list[list[int]]:
+    rng = np.random.default_rng(1000003 * step + rank)
+    lens = rng.integers(pmin, pmax + 1, size=n_prompts)
+    return [rng.integers(3, vocab, size=int(n)).tolist() for n in lens]
+
+
+def hash_reward(tokens: list[int]) -> float:
+    h = 1469598103934665603
+    for t in tokens:
+        h = ((h ^ (t & 0xFFFFFFFF)) * 1099511628211) & 0xFFFFFFFFFFFFFFFF
+    return float((h >> 17) & 1)
+
+
+def group_advantages(rewards: np.ndarray, group: int) -> np.ndarray:
+    r = rewards.reshape(-1, group)
+    adv = (r - r.mean(1, keepdims=True)) / (r.std(1, keepdims=True) + 1e-8)
+    return adv.reshape(-1)
+
+
+def build_micro_batches(prompts, responses, logprobs, advantages, micro_tokens: int):
+    """Greedy fill of padded (B, T) packs holding at most ``micro_tokens`` real tokens."""
+    import torch
+
+    order = list(range(len(prompts)))
+    groups, cur, cur_tokens = [], [], 0
+    for i in order:
+        n = len(prompts[i]) + len(responses[i])
+        if cur and cur_tokens + n > micro_tokens:
+            groups.append(cur)
+            cur, cur_tokens = [], 0
+        cur.append(i)
+        cur_tokens += n
+    if cur:
+        groups.append(cur)
+    packs = []
+    for g in groups:
+        width = max(len(prompts[i]) + len(responses[i]) for i in g)
+        ids = torch.zeros((len(g), width), dtype=torch.int64)
+        pmask = torch.ones((len(g), width), dtype=torch.bool)
+        lp = torch.zeros((len(g), width), dtype=torch.float32)
+        adv = torch.zeros((len(g), width), dtype=torch.float32)
+        lens = torch.zeros(len(g), dtype=torch.int64)
+        for r, i in enumerate(g):
+            p, resp = prompts[i], responses[i]
+            n = len(p) + len(resp)
+            ids[r, :n] = torch.tensor(p + resp)
+            pmask[r, len(p):n] = False
+            lp[r, len(p):n] = torch.tensor(logprobs[i])
+            adv[r, len(p):n] = float(advantages[i])
+            lens[r] = n
+        packs.append(dict(input_ids=ids, lengths=lens, prompt_mask=pmask, logprobs=lp, advantages=adv))
+    return packs
+
+
+# ------------------------------------------------------------------------- clocks sampling
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        sm, smax, reasons = [], [], set()
+        for line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(smax)), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------- our arm
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from areno_b200.api import loss_fns
+    from areno_b200.engine.config import EngineConfig, ModelConfig, OptimizerConfig, RuntimeConfig
+    from areno_b200.engine.inference import SamplingParams
+    from areno_b200.engine.worker import RankWorker
+    from areno_b200.ops import _lib as klib
+    from areno_b200.parallel.context import init_parallel
+
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} does not match WORLD_SIZE {world}")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    ctx = init_parallel(rank, world, tp_size=1, device=device)
+
+    model_kw = dict(MODEL)
+    new_tokens, pmin, pmax, n_prompts = NEW_TOKENS, PROMPT_MIN, PROMPT_MAX, PROMPTS_PER_GPU
+    if args.small:
+        model_kw.update(hidden_size=512, intermediate_size=1536, num_hidden_layers=4, num_attention_heads=4,
+                        num_key_value_heads=2, vocab_size=32000)
+        new_tokens, pmin, pmax = 64, 32, 96
+    mcfg = ModelConfig(**model_kw)
+    cfg = EngineConfig(
+        model=mcfg, tp_size=1, dp_size=world, devices=list(range(world)), dummy_load=True,
+        optimizer=OptimizerConfig(lr=1e-6, betas=(0.9, 0.999), weight_decay=0.01, grad_clip_norm=1.0,
+                                  adam_8bit=args.adam_8bit),
+        runtime=RuntimeConfig(activation_checkpointing=True, max_model_len=(pmax + new_tokens + 63) // 64 * 64),
+        max_running_seqs=n_prompts * GROUP, decode_progress_interval_s=0.0, seed=1234)
+    worker = RankWorker(cfg, device)
+    worker.loss_fn = loss_fns.grpo_loss_fn
+    params = SamplingParams(temperature=1.0, top_p=1.0, top_k=-1)
+
+    def one_step(step: int):
+        prompts = make_prompts(step, rank, mcfg.vocab_size, n_prompts, pmin, pmax)
+        rows = [p for p in prompts for _ in range(GROUP)]
+        out = worker.rollout(rows, params, eos_token_ids=(), max_new_tokens=new_tokens, progress_interval_s=0.0)
+        rewards = np.array([hash_reward(t) for t in out.tokens])
+        adv = group_advantages(rewards, GROUP)
+        packs = build_micro_batches(rows, out.tokens, out.logprobs, adv, MICRO_TOKENS)
+        stats = worker.train(packs)
+        tokens = sum(len(p) + len(t) for p, t in zip(rows, out.tokens))
+        return tokens, stats[-1]["loss"]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for w in range(args.warmup):
+        one_step(w)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    klib.launch_count = 0
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_wall = time.time()
+    start.record()
+    total_tokens = 0
+    loss = 0.0
+    for s in range(args.steps):
+        n, loss = one_step(args.warmup + s)
+        total_tokens += n
+    end.record()
+    barrier()
+    wall = time.time() - t_wall
+    clocks = sampler.stop()
+    ms = start.elapsed_time(end)
+    launches = klib.launch_count
+    t = torch.tensor([ms, float(total_tokens), wall], dtype=torch.float64, device=device)
+    if world > 1:
+        mx = t.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = t.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        ms, wall, total_tokens = float(mx[0]), float(mx[2]), float(sm[1])
+    value = total_tokens / (ms / 1e3)
+    klib.check_status()
+
+    e2e = None
+    if not args.no_e2e:
+        e2e = run_e2e(args, worker, mcfg, params, rank, world, device, n_prompts, pmin, pmax, new_tokens)
+
+    if rank == 0:
+        result = {
+            "metric": "RL step rollout+train tokens/sec", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": (value / BASELINE_PUBLISHED) if BASELINE_PUBLISHED else None,
+            "dtype": "bf16", "data": "synthetic (uniform random token ids, random-init weights, seeded-hash reward)",
+            "impl": "ours", "clocks": clocks, "gpu_launches": launches, "e2e": e2e, "last_loss": loss,
+            "config": {
+                "model": "Qwen2.5-7B-shaped" if not args.small else "small-debug", "global_batch": n_prompts * GROUP * world,
+                "prompts_per_gpu": n_prompts, "group": GROUP, "prompt_len": [pmin, pmax], "new_tokens": new_tokens,
+                "seq_len": pmax + new_tokens, "micro_batch_tokens": MICRO_TOKENS,
+                "parallelism": f"rollout dp{world} x tp1 (paged bf16 KV, CUDA-graph decode), train dp{world} "
+                               "sharded grads+optimizer, weight sync in place (shared buffers)",
+                "tokens_counted": "prompt+response tokens per sequence, once per step",
+                "l2": "inputs larger than L2 (15 GB of weights streamed every decode step / micro-batch)",
+                "wall_s_timed_region": wall,
+            },
+        }
+        print(json.dumps(result), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run_e2e(args, worker, mcfg, params, rank, world, device, n_prompts, pmin, pmax, new_tokens):
+    """Same step through the SDK ``Trainer`` on top of the already-built worker, wall-clock timed,
+    with per-step pinned H2D of the prompt ids and D2H of results/loss."""
+    import torch
+    import torch.distributed as dist
+
+    try:
+        from areno_b200.api.trainer import Trainer
+    except Exception as exc:  # SDK layer not importable: report honestly
+        return {"value": None, "unit": "tokens/s", "error": f"SDK unavailable: {exc}"}
+    trainer = Trainer.from_worker(worker, world_size=world)
+    steps = max(1, min(args.steps, 2))
+    h2d = d2h = 0
+
+    def step(i):
+        nonlocal h2d, d2h
+        prompts = make_prompts(10_000 + i, rank, mcfg.vocab_size, n_prompts, pmin, pmax)
+        staged = [torch.tensor(p, dtype=torch.int64).pin_memory().to(device, non_blocking=True) for p in prompts]
+        h2d += sum(t.numel() * 8 for t in staged)
+        prompts_dev = [t.tolist() for t in staged]
+        d2h += sum(t.numel() * 8 for t in staged)
+        from areno_b200.api.models import SamplingParams as ApiParams
+
+        with trainer.rollout_session():
+            res = trainer.rollout_token_batch(prompts_dev, GROUP, ApiParams(
+                temperature=1.0, max_new_tokens=new_tokens, ignore_eos=True))
+        d2h += sum(len(s.resp_tokens) * 8 for r in res for s in r.sequences)
+        batch, ntok = trainer.build_policy_batch(prompts_dev, res, hash_reward, GROUP)
+        stats = trainer.train(batch, loss_fn="grpo", mini_bs=None, micro_batch_tokens=MICRO_TOKENS)
+        h2d += ntok * (8 + 4 + 4 + 1)
+        d2h += 4
+        return ntok, stats
+
+    step(-1)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.time()
+    tokens = 0
+    for i in range(steps):
+        n, _ = step(i)
+        tokens += n
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    dt = time.time() - t0
+    t = torch.tensor([dt, float(tokens)], dtype=torch.float64, device=device)
+    if world > 1:
+        mx = t.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = t.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        dt, tokens = float(mx[0]), float(sm[1])
+    return {"value": tokens / dt, "unit": "tokens/s", "steps": steps, "h2d_bytes_per_step": h2d // (steps + 1),
+            "d2h_bytes_per_step": d2h // (steps + 1), "timing": "wall clock, max over ranks"}
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        from baseline.reference_arm import run_reference
+
+        run_reference(args)
+        return
+    run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

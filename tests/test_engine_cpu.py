@@ -1,0 +1,90 @@
+"""CPU end-to-end checks of the inference loop against a full (non-cached) forward."""
+
+import torch
+
+from areno_b200.engine.config import ModelConfig
+from areno_b200.engine.inference import InferenceEngine, SamplingParams
+from areno_b200.models.dense import DenseCausalLM, TrainMeta, init_weights
+from areno_b200.ops.attention import build_varlen_meta
+from areno_b200.parallel.context import single_process_context
+
+
+def tiny_config(**kw):
+    base = dict(model_type="qwen2", vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=2,
+                num_attention_heads=4, num_key_value_heads=2, head_dim=32, rope_theta=1e4, qk_norm=False,
+                qkv_bias=True, dtype=torch.float32)
+    base.update(kw)
+    return ModelConfig(**base)
+
+
+def _full_logits(model, tokens):
+    ids = torch.tensor(tokens)
+    h = model(ids, torch.arange(len(tokens)), TrainMeta(build_varlen_meta([len(tokens)]), False)).hidden_states
+    return model.compute_logits(h).float()
+
+
+def _engine(model, **kw):
+    single_process_context()
+    args = dict(max_slots=4, max_model_len=256, max_prefill_tokens=64)
+    args.update(kw)
+    return InferenceEngine(model, 512, "cpu", **args)
+
+
+def test_greedy_generation_matches_full_forward_with_continuous_batching_and_chunked_prefill():
+    single_process_context()
+    model = DenseCausalLM(tiny_config())
+    init_weights(model, 0)
+    eng = _engine(model)
+    g = torch.Generator().manual_seed(0)
+    # 6 prompts through 4 slots (queueing), one prompt longer than the 64-token prefill budget (chunked)
+    prompts = [torch.randint(3, 512, (n,), generator=g).tolist() for n in (20, 33, 100, 5, 12, 40)]
+    out = eng.generate(prompts, SamplingParams(temperature=0.0), eos_token_ids=(), max_new_tokens=8)
+    assert [len(t) for t in out.tokens] == [8] * 6
+    assert out.finish_reasons == ["length"] * 6
+    with torch.no_grad():
+        for p, toks, lps in zip(prompts, out.tokens, out.logprobs):
+            logits = _full_logits(model, p + toks)
+            pred = logits.argmax(-1)[len(p) - 1:-1].tolist()
+            assert pred == toks
+            ref = torch.log_softmax(logits, -1)[len(p) - 1:-1].gather(-1, torch.tensor(toks)[:, None]).squeeze(-1)
+            assert torch.allclose(ref, torch.tensor(lps), atol=2e-2)
+
+
+def test_stop_token_is_kept_and_min_new_tokens_masks_eos():
+    single_process_context()
+    model = DenseCausalLM(tiny_config())
+    init_weights(model, 1)
+    eng = _engine(model)
+    prompt = list(range(3, 20))
+    base = eng.generate([prompt], SamplingParams(temperature=0.0), (), 6).tokens[0]
+    eos = base[2]
+    out = eng.generate([prompt], SamplingParams(temperature=0.0), (eos,), 6)
+    assert out.tokens[0] == base[:3] and out.finish_reasons == ["stop"]
+    out2 = eng.generate([prompt], SamplingParams(temperature=0.0, min_new_tokens=4), (eos,), 6)
+    assert len(out2.tokens[0]) >= 4 and eos not in out2.tokens[0][:3]
+    # user stop ids stop too, suppressed ids are never produced
+    out3 = eng.generate([prompt], SamplingParams(temperature=0.0, stop_token_ids=(base[1],)), (), 6)
+    assert out3.tokens[0] == base[:2] and out3.finish_reasons == ["stop"]
+    out4 = eng.generate([prompt], SamplingParams(temperature=0.0, suppress_token_ids=(base[0],)), (), 3)
+    assert base[0] not in out4.tokens[0]
+
+
+def test_fp8_kv_cache_close_to_bf16():
+    single_process_context()
+    model = DenseCausalLM(tiny_config())
+    init_weights(model, 2)
+    prompt = list(range(5, 60))
+    a = _engine(model).generate([prompt], SamplingParams(temperature=0.0), (), 4)
+    b = _engine(model, kv_fp8=True).generate([prompt], SamplingParams(temperature=0.0), (), 4)
+    assert abs(a.logprobs[0][0] - b.logprobs[0][0]) < 0.05
+
+
+def test_sampling_is_reproducible_per_seed_and_differs_across_rows():
+    single_process_context()
+    model = DenseCausalLM(tiny_config())
+    init_weights(model, 3)
+    eng = _engine(model)
+    prompts = [list(range(3, 30))] * 3
+    a = eng.generate(prompts, SamplingParams(temperature=1.0, seed=11), (), 5)
+    b = eng.generate(prompts, SamplingParams(temperature=1.0, seed=11), (), 5)
+    assert all(len(t) == 5 for t in a.tokens) and all(len(t) == 5 for t in b.tokens)

@@ -1,0 +1,237 @@
+"""GPU numerics: paged KV ops, log-prob, sampler, optimizer and policy-loss kernels."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from areno_b200.ops import _lib, logprob, optim, paged_attention as pa, policy_loss, sampling
+
+
+def _rel_err(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+@pytest.fixture(autouse=True)
+def _status_ok():
+    yield
+    _lib.check_status()
+
+
+def _fill_cache(fp8, hq, hkv, d, lens, theta=1e6):
+    torch.manual_seed(0)
+    dev = "cuda"
+    b = len(lens)
+    max_pages = (max(lens) + pa.PAGE - 1) // pa.PAGE + 1
+    num_pages = b * max_pages + 3
+    kc, vc, ks, vs = pa.alloc_kv_cache(num_pages, hkv, d, dev, fp8)
+    perm = torch.randperm(num_pages)[: b * max_pages].view(b, max_pages).to(torch.int32)
+    block_table = perm.to(dev)
+    total = sum(lens)
+    qkv = torch.randn(total, (hq + 2 * hkv) * d, device=dev, dtype=torch.bfloat16)
+    pos = torch.cat([torch.arange(n) for n in lens]).to(dev, torch.int32)
+    slots = torch.cat([perm[i, torch.arange(n) // pa.PAGE].long() * pa.PAGE + torch.arange(n) % pa.PAGE
+                       for i, n in enumerate(lens)]).to(dev, torch.int32)
+    qkv_ref = qkv.clone().cpu()
+    kc_r, vc_r, ks_r, vs_r = pa.alloc_kv_cache(num_pages, hkv, d, "cpu", fp8)
+    pa.rope_append_kv(qkv, pos, slots, kc, vc, ks, vs, hq, hkv, d, theta=theta)
+    pa.rope_append_kv(qkv_ref, pos.cpu(), slots.cpu(), kc_r, vc_r, ks_r, vs_r, hq, hkv, d, theta=theta)
+    return qkv, qkv_ref, (kc, vc, ks, vs), (kc_r, vc_r, ks_r, vs_r), block_table
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+@pytest.mark.parametrize("hq,hkv,d", [(28, 4, 128), (8, 8, 64), (32, 2, 128)])
+def test_rope_append_and_paged_decode(fp8, hq, hkv, d):
+    lens = [1, 63, 64, 65, 300, 1000]
+    qkv, qkv_ref, cache, cache_ref, block_table = _fill_cache(fp8, hq, hkv, d, lens)
+    assert _rel_err(qkv.cpu(), qkv_ref) < 6e-3
+    kc, vc, ks, vs = cache
+    deq = pa._dequant(kc, ks).cpu()
+    deq_ref = pa._dequant(cache_ref[0], cache_ref[2])
+    assert _rel_err(deq, deq_ref) < (7e-2 if fp8 else 6e-3)
+    b = len(lens)
+    q = torch.randn(b, hq, d, device="cuda", dtype=torch.bfloat16)
+    seq_lens = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    scale = d ** -0.5
+    out = pa.paged_decode(q, kc, vc, ks, vs, block_table, seq_lens, scale)
+    ref = pa.paged_decode_reference(q, kc, vc, ks, vs, block_table, seq_lens, scale)
+    assert _rel_err(out, ref) < 1e-2
+    out1 = pa.paged_decode(q, kc, vc, ks, vs, block_table, seq_lens, scale, max_context=200)  # fewer splits
+    ref1 = pa.paged_decode_reference(q, kc, vc, ks, vs, block_table, seq_lens.clamp(max=192), scale)
+    short = seq_lens <= 192
+    assert _rel_err(out1[short], ref1[short]) < 1e-2
+    outw = pa.paged_decode(q, kc, vc, ks, vs, block_table, seq_lens, scale, window=100)
+    refw = pa.paged_decode_reference(q, kc, vc, ks, vs, block_table, seq_lens, scale, window=100)
+    assert _rel_err(outw, refw) < 1e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_selected_logprobs_fwd_bwd(dtype):
+    torch.manual_seed(1)
+    rows, v = 37, 5000
+    base = (3 * torch.randn(rows, v, device="cuda")).to(dtype)
+    targets = torch.randint(0, v, (rows,), device="cuda")
+    x = base.clone().requires_grad_()
+    lp, ent = logprob.selected_logprobs(x, targets, need_entropy=True)
+    xr = base.float().clone().requires_grad_()
+    lpr = torch.log_softmax(xr, -1).gather(-1, targets[:, None]).squeeze(-1)
+    pr = torch.softmax(xr, -1)
+    entr = -(pr * torch.log_softmax(xr, -1)).sum(-1)
+    assert _rel_err(lp, lpr) < 1e-4
+    assert _rel_err(ent, entr) < 1e-3
+    g1, g2 = torch.randn(rows, device="cuda"), 0.1 * torch.randn(rows, device="cuda")
+    (gx,) = torch.autograd.grad([lp, ent], x, [g1, g2])
+    (gr,) = torch.autograd.grad([lpr, entr], xr, [g1, g2])
+    assert _rel_err(gx, gr) < (2e-2 if dtype == torch.bfloat16 else 1e-3)
+
+
+def test_selected_logprobs_vocab_shards_combine():
+    torch.manual_seed(2)
+    rows, v = 16, 4096
+    x = torch.randn(rows, v, device="cuda")
+    t = torch.randint(0, v, (rows,), device="cuda")
+    full = logprob.selected_logprobs(x, t)
+    st = [logprob._stats(x[:, i * 1024:(i + 1) * 1024].contiguous(), t, i * 1024) for i in range(4)]
+    m = torch.stack([s[0] for s in st]).max(0).values
+    ssum = sum(s[1] * torch.exp(s[0] - m) for s in st)
+    tgt = sum(s[3] for s in st)
+    assert _rel_err(tgt - (m + torch.log(ssum)), full) < 1e-5
+
+
+def test_sampler_greedy_and_logprob():
+    torch.manual_seed(3)
+    x = torch.randn(9, 1000, device="cuda")
+    tok, lp = sampling.sample(x, temperature=0.0)
+    assert torch.equal(tok, x.argmax(-1))
+    ref = torch.log_softmax(x, -1).gather(-1, tok[:, None]).squeeze(-1)
+    assert _rel_err(lp, ref) < 1e-5
+    xb = x.to(torch.bfloat16)
+    tokb, _ = sampling.sample(xb, temperature=0.0)
+    assert torch.equal(tokb, xb.float().argmax(-1))
+
+
+def test_sampler_distribution_matches_softmax():
+    torch.manual_seed(4)
+    v = 64
+    logits = torch.randn(1, v, device="cuda") * 2
+    n = 40000
+    x = logits.expand(n, v).contiguous()
+    uid = torch.arange(n, device="cuda", dtype=torch.int64)
+    tok, lp = sampling.sample(x, temperature=0.7, seed=123, row_uid=uid)
+    freq = torch.bincount(tok, minlength=v).float() / n
+    p = torch.softmax(logits[0] / 0.7, -1)
+    assert (freq - p).abs().max().item() < 0.012
+    # same key -> same draw; different seed -> different draws
+    tok2, _ = sampling.sample(x, temperature=0.7, seed=123, row_uid=uid)
+    assert torch.equal(tok, tok2)
+    tok3, _ = sampling.sample(x, temperature=0.7, seed=124, row_uid=uid)
+    assert not torch.equal(tok, tok3)
+
+
+def test_sampler_topk_topp_support_and_masks():
+    torch.manual_seed(5)
+    v = 500
+    logits = torch.randn(1, v, device="cuda") * 3
+    n = 5000
+    x = logits.expand(n, v).contiguous()
+    uid = torch.arange(n, device="cuda", dtype=torch.int64)
+    tok, _ = sampling.sample(x, temperature=1.0, top_k=5, seed=1, row_uid=uid)
+    top5 = set(logits[0].topk(5).indices.tolist())
+    assert set(tok.unique().tolist()) <= top5 and len(set(tok.unique().tolist())) >= 3
+    tok, _ = sampling.sample(x, temperature=1.0, top_p=0.5, seed=2, row_uid=uid)
+    p = torch.softmax(logits[0], -1)
+    ps, pi = p.sort(descending=True)
+    keep = set(pi[((ps.cumsum(0) - ps) <= 0.5)].tolist())
+    assert set(tok.unique().tolist()) <= keep
+    # suppression and min-new-tokens EOS masking
+    best = int(logits[0].argmax())
+    second = int(logits[0].topk(2).indices[1])
+    cls = sampling.build_token_classes(v, suppress_ids=[best], eos_ids=[second], device="cuda")
+    gen = torch.zeros(n, dtype=torch.int32, device="cuda")
+    tok, _ = sampling.sample(x, temperature=0.0, cls=cls, gen_count=gen, min_new=2)
+    assert int(tok[0]) not in (best, second)
+    gen += 5
+    tok, _ = sampling.sample(x, temperature=0.0, cls=cls, gen_count=gen, min_new=2)
+    assert int(tok[0]) == second
+
+
+def test_sampler_shards_combine():
+    torch.manual_seed(6)
+    b, v, tp = 32, 4096, 4
+    x = torch.randn(b, v, device="cuda")
+    uid = torch.arange(b, device="cuda", dtype=torch.int64)
+    tok, lp = sampling.sample(x, temperature=1.0, seed=77, row_uid=uid)
+    parts = torch.empty(tp, b, 6, device="cuda")
+    for r in range(tp):
+        sampling.sample(x[:, r * 1024:(r + 1) * 1024].contiguous(), temperature=1.0, seed=77, row_uid=uid,
+                        vocab_start=r * 1024, part=parts[r])
+    tok2, lp2 = sampling.combine_shards(parts)
+    assert torch.equal(tok, tok2)
+    assert _rel_err(lp2, lp) < 1e-5
+
+
+def test_adamw_fp32_matches_reference():
+    torch.manual_seed(7)
+    n = 100003
+    p0 = torch.randn(n)
+    state = [p0.clone(), torch.zeros(n), torch.zeros(n)]
+    dstate = [t.cuda() for t in state]
+    out = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+    for step in range(1, 4):
+        g = torch.randn(n)
+        optim.adamw_fp32(*state, g, None, 1e-3, 0.9, 0.999, 1e-8, 0.01, step, 0.5)
+        optim.adamw_fp32(*dstate, g.cuda(), out, 1e-3, 0.9, 0.999, 1e-8, 0.01, step, 0.5)
+    assert _rel_err(dstate[0].cpu(), state[0]) < 1e-6
+    assert _rel_err(dstate[2].cpu(), state[2]) < 1e-4
+    assert torch.equal(out.cpu(), dstate[0].cpu().to(torch.bfloat16))
+
+
+def test_adamw_8bit_tracks_fp32():
+    torch.manual_seed(8)
+    n = 4096 + 17
+    nb = (n + 31) // 32
+    p = torch.randn(n, device="cuda")
+    ref = [p.clone(), torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")]
+    master = p.clone()
+    mq = torch.zeros(n, dtype=torch.int8, device="cuda")
+    vq = torch.zeros(n, dtype=torch.uint8, device="cuda")
+    ms = torch.full((nb,), 1e-30, device="cuda")
+    vs = torch.full((nb,), 1e-30, device="cuda")
+    out = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+    for step in range(1, 6):
+        g = torch.randn(n, device="cuda")
+        optim.adamw_fp32(*ref, g, None, 1e-2, 0.9, 0.999, 1e-8, 0.0, step)
+        optim.adamw_8bit(master, mq, vq, ms, vs, g, out, 1e-2, 0.9, 0.999, 1e-8, 0.0, step)
+    assert _rel_err(master - p, ref[0] - p) < 0.1
+
+
+def test_sumsq_and_scale():
+    x = torch.randn(1_000_003, device="cuda")
+    s = optim.sumsq(x)
+    assert abs(s.item() - x.double().pow(2).sum().item()) / s.item() < 1e-5
+    factor = torch.tensor([0.5], device="cuda")
+    y = x.clone()
+    optim.scale_(y, 2.0, factor)
+    assert torch.allclose(y, x)
+
+
+@pytest.mark.parametrize("kl_type", [None, "low_var_kl", "kl", "abs", "mse"])
+@pytest.mark.parametrize("use_old", [True, False])
+def test_policy_loss_tokens(kl_type, use_old):
+    torch.manual_seed(9)
+    n = 1000
+    lp = (-torch.rand(n, device="cuda") * 3).requires_grad_()
+    old = (lp.detach() + 0.3 * torch.randn(n, device="cuda")) if use_old else None
+    ref = lp.detach() + 0.2 * torch.randn(n, device="cuda")
+    adv = torch.randn(n, device="cuda")
+    loss, kl, flags = policy_loss.policy_loss_tokens(lp, old, adv, ref, 0.2, 0.2, 3.0, kl_type)
+    lpr = lp.detach().clone().requires_grad_()
+    lr_, klr, fr = policy_loss.policy_loss_tokens_reference(lpr, old, adv, ref, 0.2, 0.2, 3.0, kl_type)
+    assert _rel_err(loss, lr_) < 1e-5
+    assert torch.equal(flags, fr.int())
+    tot = loss.sum() + (0.1 * kl.sum() if kl is not None else 0.0)
+    totr = lr_.sum() + (0.1 * klr.sum() if klr is not None else 0.0)
+    (g,) = torch.autograd.grad(tot, lp)
+    (gr,) = torch.autograd.grad(totr, lpr)
+    assert _rel_err(g, gr) < 1e-4
