@@ -1,0 +1,45 @@
+"""Typed backend configuration (``areno/api/config.py`` in the reference)."""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any
+
+from .models import BackendType
+
+
+@dataclass
+class ArenoConfig:
+    """Layout and tuning of the native backend.  ``optimizer`` / ``runtime`` are passed verbatim to the
+    engine's ``OptimizerConfig`` / ``RuntimeConfig``."""
+
+    model_path: str | None = None
+    tp_size: int = 1
+    dp_size: int | None = None
+    devices: list[int] | None = None
+    dummy_load: bool = False
+    optimizer: dict[str, Any] = field(default_factory=dict)
+    runtime: dict[str, Any] = field(default_factory=dict)
+    max_running_prompts: int = 64
+    decode_progress_interval_s: float = 10.0
+    # how workers are launched: "spawn" (one process per GPU), "inprocess" (single GPU, no process hop),
+    # "spmd" (this process is one of WORLD_SIZE ranks started by torch.distributed.run)
+    launcher: str | None = None
+    model_config: Any = None  # explicit ModelConfig (synthetic models without a checkpoint directory)
+    seed: int = 0
+
+
+BackendConfig = ArenoConfig
+
+
+def resolve_backend_type(backend_type: BackendType | None, custom_config: Any) -> BackendType:
+    del custom_config
+    return backend_type if backend_type is not None else BackendType.Areno
+
+
+def coerce_backend_config(backend_type: BackendType, custom_config: Any) -> BackendConfig | None:
+    if custom_config is None:
+        return None
+    if backend_type == BackendType.Areno and isinstance(custom_config, ArenoConfig):
+        return custom_config
+    raise TypeError(f"{backend_type.value} requires its typed backend config dataclass, got {type(custom_config)!r}")

@@ -1,0 +1,58 @@
+"""Wire-format models of the SDK: what rollouts return and what training consumes.
+
+Field-for-field compatible with ``areno/api/models.py`` of the reference (pydantic models), so
+algorithm scripts written against it run unchanged.
+"""
+
+from __future__ import annotations
+
+from enum import Enum
+
+from pydantic import BaseModel, Field
+
+
+class BackendType(Enum):
+    Areno = "Areno"
+
+
+class SamplingParams(BaseModel):
+    """Generation controls.  ``greedy`` forces temperature 0; ``top_k=-1`` disables top-k;
+    ``max_context_len`` caps whole agentic trajectories (prompt plus every generated turn)."""
+
+    greedy: bool = Field(default=False)
+    top_p: float = Field(default=1.0)
+    top_k: int = Field(default=-1)
+    max_new_tokens: int = Field(default=16)
+    max_context_len: int | None = Field(default=None)
+    temperature: float = Field(default=1.0)
+    stop: list[str] | None = Field(default=None)
+    stop_token_ids: list[int] | None = Field(default=None)
+    ignore_eos: bool = Field(default=False)
+    skip_special_tokens: bool = Field(default=True)
+    max_prompt_len: int | None = Field(default=None)
+
+
+class RolloutSequence(BaseModel):
+    """One sampled completion; ``resp_logprobs[i]`` is the rollout-policy log-prob of ``resp_tokens[i]``."""
+
+    resp_tokens: list[int] = Field(default_factory=list)
+    resp_logprobs: list[float] = Field(default_factory=list)
+
+
+class RolloutResult(BaseModel):
+    sequences: list[RolloutSequence] = Field(default_factory=list)
+
+
+class TrainSequence(BaseModel):
+    """A rollout converted into a training sample: prompt + response tokens with per-token signals."""
+
+    prompt_mask: list[bool] = Field(default_factory=list)
+    loss_mask: list[bool] = Field(default_factory=list)
+    tokens: list[int] = Field(default_factory=list)
+    logprobs: list[float] = Field(default_factory=list)
+    advantages: list[float] = Field(default_factory=list)
+    returns: list[float] = Field(default_factory=list)
+    values: list[float] = Field(default_factory=list)
+    ref_logprobs: list[float] = Field(default_factory=list)
+    reward: float = Field(default=0.0)
+    eos_token_id: int = Field(default=0)

@@ -196,14 +196,25 @@ def run_ours(args):
     worker.loss_fn = loss_fns.grpo_loss_fn
     params = SamplingParams(temperature=1.0, top_p=1.0, top_k=-1)
 
+    phase = {"rollout_s": 0.0, "train_s": 0.0, "host_s": 0.0}
+
     def one_step(step: int):
+        t0 = time.time()
         prompts = make_prompts(step, rank, mcfg.vocab_size, n_prompts, pmin, pmax)
         rows = [p for p in prompts for _ in range(GROUP)]
+        t1 = time.time()
         out = worker.rollout(rows, params, eos_token_ids=(), max_new_tokens=new_tokens, progress_interval_s=0.0)
+        t2 = time.time()
         rewards = np.array([hash_reward(t) for t in out.tokens])
         adv = group_advantages(rewards, GROUP)
         packs = build_micro_batches(rows, out.tokens, out.logprobs, adv, MICRO_TOKENS)
+        t3 = time.time()
         stats = worker.train(packs)
+        torch.cuda.synchronize()
+        t4 = time.time()
+        phase["rollout_s"] += t2 - t1
+        phase["train_s"] += t4 - t3
+        phase["host_s"] += (t1 - t0) + (t3 - t2)
         tokens = sum(len(p) + len(t) for p, t in zip(rows, out.tokens))
         return tokens, stats[-1]["loss"]
 
@@ -218,6 +229,8 @@ def run_ours(args):
     sampler = ClockSampler(local_rank)
     sampler.start()
     klib.launch_count = 0
+    for k in phase:
+        phase[k] = 0.0
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_wall = time.time()
     start.record()
@@ -253,6 +266,7 @@ def run_ours(args):
             "scaling": "weak", "vs_baseline": (value / BASELINE_PUBLISHED) if BASELINE_PUBLISHED else None,
             "dtype": "bf16", "data": "synthetic (uniform random token ids, random-init weights, seeded-hash reward)",
             "impl": "ours", "clocks": clocks, "gpu_launches": launches, "e2e": e2e, "last_loss": loss,
+            "phase_s_per_step": {k: v / args.steps for k, v in phase.items()},
             "config": {
                 "model": "Qwen2.5-7B-shaped" if not args.small else "small-debug", "global_batch": n_prompts * GROUP * world,
                 "prompts_per_gpu": n_prompts, "group": GROUP, "prompt_len": [pmin, pmax], "new_tokens": new_tokens,
