@@ -121,9 +121,10 @@ class InferenceEngine:
         i32 = dict(dtype=torch.int32, device=dev)
         self.seq_len = torch.zeros(s, **i32)
         self.active = torch.zeros(s, **i32)
-        self.gen_count = torch.zeros(s, **i32)
+        # finish / gen_count / request uid live in one tensor so a status snapshot is a single D2H copy
+        self.state = torch.zeros((3, s), **i32)
+        self.finish, self.gen_count, self.uid32 = self.state[0], self.state[1], self.state[2]
         self.max_new = torch.zeros(s, **i32)
-        self.finish = torch.zeros(s, **i32)
         self.last_token = torch.zeros(s, dtype=torch.int64, device=dev)
         self.row_uid = torch.zeros(s, dtype=torch.int64, device=dev)
         self.block_table = torch.zeros((s, self.max_pages), **i32)
@@ -322,6 +323,7 @@ class InferenceEngine:
         uid = torch.tensor(fin_uid, dtype=torch.int64, device=dev)
         slots_t = torch.tensor(fin_slots, dtype=torch.int32, device=dev)
         self.row_uid[slots_t.long()] = uid
+        self.uid32[slots_t.long()] = (uid & 0x7FFFFFFF).to(torch.int32)
         zero_gen = torch.zeros(n, dtype=torch.int32, device=dev)
         tok, lp = self._sample(out.logits_shard, zero_gen, uid)
         prompt_t = torch.tensor(fin_prompt, dtype=torch.int32, device=dev)
@@ -473,18 +475,29 @@ class InferenceEngine:
         self.block_table[lo:hi].copy_(self.h_block_table[lo:hi], non_blocking=True)
 
     def _snapshot(self):
-        """Queue an async copy of (finish, gen_count) for the host to poll."""
-        pack = torch.stack([self.finish, self.gen_count, self.row_uid.to(torch.int32)])
-        if self.cuda:
-            host = torch.empty(pack.shape, dtype=torch.int32, pin_memory=True)
-            host.copy_(pack, non_blocking=True)
-            ev = torch.cuda.Event()
-            ev.record()
-            self._snapshots.append((host, ev))
-            if len(self._snapshots) > 4:
-                self._snapshots[0][1].synchronize()
-        else:
-            self._snapshots.append((pack.clone(), None))
+        """Queue an async copy of the (finish, gen_count, uid) status rows for the host to poll."""
+        if not self.cuda:
+            self._snapshots.append((self.state.clone(), None))
+            return
+        # ring of pinned buffers (pinned allocation is far too slow to do per step)
+        if not hasattr(self, "_snap_ring"):
+            self._snap_ring = [torch.empty((3, self.max_slots), dtype=torch.int32, pin_memory=True) for _ in range(8)]
+            self._snap_events = [torch.cuda.Event() for _ in range(8)]
+            self._snap_next = 0
+        while len(self._snapshots) >= 6:
+            # bound how far the device may run ahead of the host; a newer snapshot supersedes older ones
+            self._snapshots[0][1].synchronize()
+            if len(self._snapshots) >= 7:
+                self._snapshots.pop(0)
+            else:
+                break
+        i = self._snap_next
+        self._snap_next = (i + 1) % len(self._snap_ring)
+        host = self._snap_ring[i]
+        host.copy_(self.state, non_blocking=True)
+        ev = self._snap_events[i]
+        ev.record()
+        self._snapshots.append((host, ev))
 
     def _poll(self, block: bool, drain: bool = False) -> list[_Request]:
         done: list[_Request] = []

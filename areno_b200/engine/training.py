@@ -159,8 +159,8 @@ class TrainingManager:
             remaining = n - (i - group_pos)
             group = min(accum, remaining)
             allow_step = group_pos == group - 1
-            results.append(self.train_step(shards, allow_step=allow_step, grad_scale=group))
-        return results
+            results.append(self.train_step(shards, allow_step=allow_step, grad_scale=group, defer_sync=True))
+        return [_materialize(r) for r in results]
 
     def forward_logprobs(self, pack: dict, need_entropy: bool = False):
         """Packed forward to per-action log-probs ``[num_actions]`` (fp32)."""
@@ -171,7 +171,8 @@ class TrainingManager:
             cu = pack["train_cu_seqlens"].tolist()
             lens = [cu[i + 1] - cu[i] for i in range(len(cu) - 1)]
         meta = TrainMeta(build_varlen_meta(lens, device=self.device),
-                         activation_checkpointing=self.config.runtime.activation_checkpointing)
+                         activation_checkpointing=self.config.runtime.activation_checkpointing,
+                         checkpoint_layers=self._checkpoint_layers(int(ids.numel())))
         out = self.model(ids, pos, meta)
         aidx = pack["_action_index"]
         hidden = out.hidden_states.index_select(0, aidx)
@@ -179,7 +180,35 @@ class TrainingManager:
         return lm_head_logprobs(self.model.lm_head, hidden, targets, self.config.runtime.logprob_chunk,
                                 need_entropy=need_entropy, softcap=self.model.cfg.final_logit_softcapping)
 
-    def train_step(self, shards, *, allow_step: bool, grad_scale: int) -> dict:
+    def _checkpoint_layers(self, tokens: int) -> int | None:
+        """How many layers to recompute in backward.  Checkpointing exists to save memory; when the
+        device has room, layers keep their activations and skip the recompute.  Decided from the
+        free memory seen once the optimizer state exists, with a fixed reserve for transients."""
+        if not self.config.runtime.activation_checkpointing or self.device.type != "cuda":
+            return None
+        mc = self.model.cfg
+        n_layers = mc.num_hidden_layers
+        cached = getattr(self, "_ckpt_cache", None)
+        if cached is not None and cached[0] >= tokens:
+            return cached[1]
+        self.optimizer._ensure_state()
+        ctx = get_context()
+        tp = max(1, ctx.tp_size)
+        qkv_w = (mc.num_attention_heads + 2 * mc.num_key_value_heads) * mc.head_dim // tp
+        inter = (mc.moe_intermediate_size * max(1, mc.num_experts_per_tok) if mc.num_experts else mc.intermediate_size)
+        per_token = 2 * (5 * mc.hidden_size + qkv_w + mc.num_attention_heads * mc.head_dim // tp + 3 * inter // tp)
+        per_layer = per_token * max(tokens, 1)
+        free, _total = torch.cuda.mem_get_info(self.device)
+        free += torch.cuda.memory_reserved(self.device) - torch.cuda.memory_allocated(self.device)
+        reserve = 26 << 30
+        keep = max(0, int((free - reserve) // max(per_layer, 1)))
+        n_ckpt = max(0, n_layers - keep)
+        self._ckpt_cache = (tokens, n_ckpt)
+        logger.info("activation checkpointing: recompute %d of %d layers (free=%.1f GB, per-layer=%.2f GB)", n_ckpt,
+                    n_layers, free / 2**30, per_layer / 2**30)
+        return n_ckpt
+
+    def train_step(self, shards, *, allow_step: bool, grad_scale: int, defer_sync: bool = False) -> dict:
         ctx = get_context()
         self.model.train()
         pack = shards[ctx.dp_rank] if isinstance(shards, (list, tuple)) else shards
@@ -209,17 +238,29 @@ class TrainingManager:
             self.global_step += 1
         else:
             self.optimizer.fold_param_grads()
-        out_metrics = {}
-        if metrics:
-            for k, v in metrics.items():
-                out_metrics[k] = float(v.detach().float().cpu()) if isinstance(v, torch.Tensor) else v
+        out_metrics = dict(metrics) if metrics else {}
         out_metrics["lr"] = lr
         if grad_norm is not None:
-            out_metrics["grad_norm"] = float(grad_norm.detach().cpu())
-        return {
-            "loss": float(loss.detach().float().cpu()),
+            out_metrics["grad_norm"] = grad_norm
+        result = {
+            "loss": loss.detach(),
             "stepped": allow_step,
             "global_step": self.global_step,
             "metrics": out_metrics,
             "num_tokens": int(pack["input_ids"].numel()),
         }
+        # device scalars are read back once per call to train(), not once per micro-batch
+        return result if defer_sync else _materialize(result)
+
+
+def _scalar(v):
+    if isinstance(v, torch.Tensor):
+        return float(v.detach().float().reshape(-1)[0].cpu()) if v.numel() else 0.0
+    return v
+
+
+def _materialize(result: dict) -> dict:
+    out = dict(result)
+    out["loss"] = _scalar(result["loss"])
+    out["metrics"] = {k: _scalar(v) for k, v in result.get("metrics", {}).items()}
+    return out

@@ -39,6 +39,7 @@ class TrainMeta:
     varlen: VarlenMeta
     activation_checkpointing: bool = True
     packed: bool = True
+    checkpoint_layers: int | None = None   # recompute only the first N layers (None = every layer)
 
 
 @dataclass
@@ -185,8 +186,11 @@ class DenseCausalLM(nn.Module):
         x = self.embed(ids)
         residual = None
         use_ckpt = isinstance(meta, TrainMeta) and meta.activation_checkpointing and torch.is_grad_enabled()
-        for layer in self.layers:
-            if use_ckpt:
+        n_ckpt = len(self.layers)
+        if use_ckpt and meta.checkpoint_layers is not None:
+            n_ckpt = max(0, min(n_ckpt, int(meta.checkpoint_layers)))
+        for li, layer in enumerate(self.layers):
+            if use_ckpt and li < n_ckpt:
                 if residual is None:
                     x, residual = checkpoint(_run_first, layer, x, positions, meta, use_reentrant=False)
                 else:

@@ -234,8 +234,9 @@ class _QKVAttention(torch.autograd.Function):
             inv_k = _headnorm_fwd(k, k_norm_w, norm_offset, kn, norm_eps)
             q, k = qn, kn
         if rot_dim > 0:
-            _rope_inplace(q, positions, theta, rot_dim, inv_freq, interleaved, 1.0)
-            _rope_inplace(k, positions, theta, rot_dim, inv_freq, interleaved, 1.0)
+            # q heads are followed directly by k heads in both buffers: one launch rotates both
+            qk = _heads_view(qk2 if has_norm else qkv, 0, hq + hkv, d)
+            _rope_inplace(qk, positions, theta, rot_dim, inv_freq, interleaved, 1.0)
         o, lse = attention_forward(q, k, v, meta, scale, causal, window)
         extras = []
         if inv_freq is not None:
@@ -274,8 +275,8 @@ class _QKVAttention(torch.autograd.Function):
             dk = _heads_view(dqkv, hq * d, hkv, d)
         attention_backward(q, k, v, o, do3, lse, ctx.meta, scale, causal, window, dq, dk, dv)
         if rot_dim > 0:
-            _rope_inplace(dq, positions, theta, rot_dim, inv_freq, interleaved, -1.0)
-            _rope_inplace(dk, positions, theta, rot_dim, inv_freq, interleaved, -1.0)
+            dqk = _heads_view(dqk2 if has_norm else dqkv, 0, hq + hkv, d)
+            _rope_inplace(dqk, positions, theta, rot_dim, inv_freq, interleaved, -1.0)
         if has_norm:
             dwq = _headnorm_bwd(dq, _heads_view(qkv, 0, hq, d), q_norm_w, norm_offset, inv_q,
                                 _heads_view(dqkv, 0, hq, d))
