@@ -1,0 +1,440 @@
+"""Worker clusters: how rank workers are hosted and how commands reach them.
+
+* ``InProcessCluster`` - world size 1: the worker lives in a thread of the driver process (no
+  pickling, no process hop); used for single-GPU runs, CPU tests and ``areno serve`` on one GPU.
+* ``SpawnCluster`` - one spawned process per rank (``multiprocessing`` spawn context), a command
+  queue per rank and one shared result queue demultiplexed by request id on a pump thread; dead
+  workers are detected while calls are pending; ``close`` escalates SHUTDOWN -> join -> terminate.
+* ``SPMDCluster`` - the current process is already one of ``WORLD_SIZE`` ranks started by
+  ``torch.distributed.run``; every rank runs the same driver code, executes its own share and
+  exchanges results with ``all_gather_object``.
+
+All three expose ``call`` (blocking, one result per rank) and ``call_async`` (awaitable, optional
+``result_ranks`` subset).  Role of ``TPCluster`` in the reference
+(``areno/engine/protocol.py:200-557``).
+"""
+
+from __future__ import annotations
+
+import asyncio
+import itertools
+import os
+import queue
+import socket
+import threading
+import time
+import traceback
+from typing import Any
+
+import torch
+
+from ..utils.log import get_logger
+from .config import EngineConfig
+from .protocol import Command, Op, WorkerResult
+
+logger = get_logger()
+
+
+def _free_port() -> int:
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+class WorkerError(RuntimeError):
+    pass
+
+
+def _device_for(config: EngineConfig, rank: int) -> torch.device:
+    if torch.cuda.is_available() and config.backend != "gloo":
+        return torch.device("cuda", config.devices[rank])
+    return torch.device("cpu")
+
+
+# --------------------------------------------------------------------------- base
+class _ClusterBase:
+    def __init__(self, config: EngineConfig):
+        self.config = config
+        self.world_size = config.world_size
+        self._ids = itertools.count(1)
+        self._closed = False
+
+    def call(self, op: Op, payload: Any = None, timeout: float | None = None) -> list:
+        raise NotImplementedError
+
+    async def call_async(self, op: Op, payload: Any = None, result_ranks=None) -> list:
+        loop = asyncio.get_running_loop()
+        return await loop.run_in_executor(None, lambda: self.call(op, payload))
+
+    def close(self) -> None:
+        self._closed = True
+
+
+# --------------------------------------------------------------------- in process
+class InProcessCluster(_ClusterBase):
+    def __init__(self, config: EngineConfig, worker=None):
+        super().__init__(config)
+        if config.world_size != 1:
+            raise ValueError("InProcessCluster supports world_size == 1 only")
+        from ..parallel.context import single_process_context
+        from .worker import RankWorker
+        from .worker_loop import WorkerLoop, make_queue_getter
+
+        self._cmd_q: queue.Queue = queue.Queue()
+        self._pending: dict[int, Any] = {}
+        self._lock = threading.Lock()
+        self._ready = threading.Event()
+        self._startup_error: str | None = None
+        self._worker = worker
+
+        def main():
+            try:
+                device = _device_for(config, 0) if worker is None else worker.device
+                if device.type == "cuda":
+                    torch.cuda.set_device(device)
+                if worker is None:
+                    single_process_context(device)
+                    self._worker = RankWorker(config, device)
+                loop = WorkerLoop(self._worker, 0, make_queue_getter(self._cmd_q), self._deliver)
+            except BaseException:  # noqa: BLE001
+                self._startup_error = traceback.format_exc()
+                self._ready.set()
+                return
+            self._ready.set()
+            loop.run()
+
+        self._thread = threading.Thread(target=main, name="areno-worker", daemon=True)
+        self._thread.start()
+        self._ready.wait()
+        if self._startup_error:
+            raise WorkerError(f"worker failed to start:\n{self._startup_error}")
+
+    @property
+    def worker(self):
+        return self._worker
+
+    def _deliver(self, res: WorkerResult) -> None:
+        with self._lock:
+            slot = self._pending.pop(res.request_id, None)
+        if slot is None:
+            return
+        kind, target = slot
+        if kind == "sync":
+            target.put(res)
+        else:
+            loop, fut = target
+            loop.call_soon_threadsafe(_set_future, fut, res)
+
+    def call(self, op, payload=None, timeout=None):
+        if self._closed:
+            raise WorkerError("cluster is closed")
+        rid = next(self._ids)
+        box: queue.Queue = queue.Queue()
+        with self._lock:
+            self._pending[rid] = ("sync", box)
+        self._cmd_q.put(Command(op, rid, payload))
+        deadline = None if timeout is None else time.time() + timeout
+        while True:
+            try:
+                res = box.get(timeout=0.2)
+                break
+            except queue.Empty:
+                if not self._thread.is_alive():
+                    raise WorkerError(f"worker exited without reporting result for {op}")
+                if deadline is not None and time.time() > deadline:
+                    raise TimeoutError(f"{op} timed out after {timeout}s")
+        if not res.ok:
+            raise WorkerError(f"worker failed in {op}:\n{res.error}")
+        return [res.payload]
+
+    async def call_async(self, op, payload=None, result_ranks=None):
+        if self._closed:
+            raise WorkerError("cluster is closed")
+        rid = next(self._ids)
+        loop = asyncio.get_running_loop()
+        fut = loop.create_future()
+        with self._lock:
+            self._pending[rid] = ("async", (loop, fut))
+        self._cmd_q.put(Command(op, rid, payload))
+        res = await fut
+        if not res.ok:
+            raise WorkerError(f"worker failed in {op}:\n{res.error}")
+        return [res.payload]
+
+    def close(self):
+        if self._closed:
+            return
+        self._closed = True
+        self._cmd_q.put(Command(Op.SHUTDOWN, 0, None))
+        self._thread.join(timeout=5)
+
+
+def _set_future(fut, res):
+    if not fut.done():
+        fut.set_result(res)
+
+
+# -------------------------------------------------------------------------- spawn
+def _spawn_entry(rank: int, config: EngineConfig, port: int, cmd_q, result_q) -> None:
+    """Process entry point of one rank."""
+    from ..parallel.context import destroy_parallel, init_parallel
+    from .worker import RankWorker
+    from .worker_loop import WorkerLoop, make_queue_getter
+
+    try:
+        device = _device_for(config, rank)
+        if device.type == "cuda":
+            torch.cuda.set_device(device)
+        torch.set_float32_matmul_precision("high")
+        init_parallel(rank, config.world_size, config.tp_size, master_addr="127.0.0.1", master_port=port,
+                      backend=config.backend, device=device)
+        worker = RankWorker(config, device)
+        result_q.put(WorkerResult(rank, -1, True, "READY"))
+    except BaseException:  # noqa: BLE001
+        result_q.put(WorkerResult(rank, -1, False, None, traceback.format_exc()))
+        return
+    try:
+        WorkerLoop(worker, rank, make_queue_getter(cmd_q), result_q.put).run()
+    finally:
+        try:
+            destroy_parallel()
+        except Exception:
+            pass
+
+
+class SpawnCluster(_ClusterBase):
+    def __init__(self, config: EngineConfig, start: bool = True):
+        super().__init__(config)
+        import torch.multiprocessing as mp
+
+        self._mp = mp.get_context("spawn")
+        self._procs: list = []
+        self._cmd_qs: list = []
+        self._result_q = None
+        self._pending: dict[int, dict] = {}
+        self._lock = threading.Lock()
+        self._pump: threading.Thread | None = None
+        self._stop_pump = threading.Event()
+        if start:
+            self.start()
+
+    def start(self, ready_timeout: float = 1800.0) -> None:
+        port = _free_port()
+        self._result_q = self._mp.Queue()
+        for rank in range(self.world_size):
+            q = self._mp.Queue()
+            p = self._mp.Process(target=_spawn_entry, args=(rank, self.config, port, q, self._result_q), daemon=True)
+            p.start()
+            self._cmd_qs.append(q)
+            self._procs.append(p)
+        ready = 0
+        deadline = time.time() + ready_timeout
+        while ready < self.world_size:
+            try:
+                res = self._result_q.get(timeout=0.5)
+            except queue.Empty:
+                dead = [i for i, p in enumerate(self._procs) if p.exitcode not in (None, 0)]
+                if dead:
+                    self.close()
+                    raise WorkerError(f"worker rank(s) {dead} exited during start-up")
+                if time.time() > deadline:
+                    self.close()
+                    raise TimeoutError("workers did not become ready in time")
+                continue
+            if not res.ok:
+                self.close()
+                raise WorkerError(f"worker rank {res.rank} failed to start:\n{res.error}")
+            ready += 1
+        self._pump = threading.Thread(target=self._pump_results, name="areno-result-pump", daemon=True)
+        self._pump.start()
+
+    # results are demultiplexed by request id; a request completes when every awaited rank answered
+    def _pump_results(self) -> None:
+        while not self._stop_pump.is_set():
+            try:
+                res: WorkerResult = self._result_q.get(timeout=0.2)
+            except queue.Empty:
+                self._check_dead_workers()
+                continue
+            except (EOFError, OSError):
+                return
+            with self._lock:
+                entry = self._pending.get(res.request_id)
+                if entry is None:
+                    continue
+                entry["results"][res.rank] = res
+                done = all(r in entry["results"] for r in entry["ranks"]) or not res.ok
+                if done:
+                    self._pending.pop(res.request_id, None)
+            if done:
+                self._complete(entry)
+
+    def _check_dead_workers(self) -> None:
+        dead = [i for i, p in enumerate(self._procs) if p.exitcode is not None]
+        if not dead:
+            return
+        with self._lock:
+            entries = list(self._pending.values())
+            self._pending.clear()
+        for entry in entries:
+            entry["dead"] = dead
+            self._complete(entry)
+
+    @staticmethod
+    def _complete(entry: dict) -> None:
+        if entry["kind"] == "sync":
+            entry["box"].put(entry)
+        else:
+            loop, fut = entry["future"]
+            loop.call_soon_threadsafe(_set_future, fut, entry)
+
+    def _submit(self, op, payload, result_ranks, kind, extra) -> int:
+        if self._closed:
+            raise WorkerError("cluster is closed")
+        rid = next(self._ids)
+        ranks = tuple(range(self.world_size)) if result_ranks is None else tuple(sorted(result_ranks))
+        entry = {"kind": kind, "ranks": ranks, "results": {}, "op": op, **extra}
+        with self._lock:
+            self._pending[rid] = entry
+        cmd = Command(op, rid, payload, ranks)
+        for q in self._cmd_qs:
+            q.put(cmd)
+        return rid
+
+    @staticmethod
+    def _unpack(entry: dict, op) -> list:
+        if entry.get("dead"):
+            raise WorkerError(f"worker exited without reporting result for {op} (dead ranks: {entry['dead']})")
+        for res in entry["results"].values():
+            if not res.ok:
+                raise WorkerError(f"worker rank {res.rank} failed in {op}:\n{res.error}")
+        return [entry["results"][r].payload if r in entry["results"] else None
+                for r in range(max(entry["ranks"]) + 1)]
+
+    def call(self, op, payload=None, timeout=None, result_ranks=None):
+        box: queue.Queue = queue.Queue()
+        self._submit(op, payload, result_ranks, "sync", {"box": box})
+        try:
+            entry = box.get(timeout=timeout)
+        except queue.Empty:
+            raise TimeoutError(f"{op} timed out after {timeout}s") from None
+        return self._unpack(entry, op)
+
+    async def call_async(self, op, payload=None, result_ranks=None):
+        loop = asyncio.get_running_loop()
+        fut = loop.create_future()
+        self._submit(op, payload, result_ranks, "async", {"future": (loop, fut)})
+        entry = await fut
+        return self._unpack(entry, op)
+
+    def close(self) -> None:
+        if self._closed:
+            return
+        self._closed = True
+        for q in self._cmd_qs:
+            try:
+                q.put(Command(Op.SHUTDOWN, 0, None))
+            except Exception:
+                pass
+        for p in self._procs:
+            p.join(timeout=5)
+        for p in self._procs:
+            if p.is_alive():
+                p.terminate()
+        for p in self._procs:
+            if p.is_alive():
+                p.join(timeout=2)
+                if p.is_alive():
+                    p.kill()
+        self._stop_pump.set()
+        for q in self._cmd_qs + ([self._result_q] if self._result_q is not None else []):
+            try:
+                q.close()
+                q.cancel_join_thread()
+            except Exception:
+                pass
+        self._procs.clear()
+        self._cmd_qs.clear()
+
+
+# --------------------------------------------------------------------------- SPMD
+class SPMDCluster(_ClusterBase):
+    """Every torchrun rank constructs the same engine and issues the same calls; each executes its
+    share locally and the per-rank results are exchanged so that all ranks see the full list."""
+
+    def __init__(self, config: EngineConfig, worker=None):
+        super().__init__(config)
+        import torch.distributed as dist
+
+        from ..parallel.context import get_context, init_parallel
+        from .worker import RankWorker
+
+        rank = int(os.environ.get("RANK", 0))
+        world = int(os.environ.get("WORLD_SIZE", 1))
+        if world != config.world_size:
+            raise ValueError(f"WORLD_SIZE={world} does not match the configured world size {config.world_size}")
+        if worker is None:
+            local = int(os.environ.get("LOCAL_RANK", rank))
+            device = torch.device("cuda", local) if torch.cuda.is_available() and config.backend != "gloo" \
+                else torch.device("cpu")
+            if device.type == "cuda":
+                torch.cuda.set_device(device)
+            if get_context().world_size != world:
+                init_parallel(rank, world, config.tp_size, backend=config.backend, device=device)
+            worker = RankWorker(config, device)
+        self._worker = worker
+        self.rank = rank
+        self._dist = dist
+
+    @property
+    def worker(self):
+        return self._worker
+
+    def call(self, op, payload=None, timeout=None, result_ranks=None):
+        from .worker_loop import execute
+
+        try:
+            mine = WorkerResult(self.rank, 0, True, execute(self._worker, Command(op, 0, payload)))
+        except BaseException:  # noqa: BLE001
+            mine = WorkerResult(self.rank, 0, False, None, traceback.format_exc())
+        if self.world_size == 1:
+            results = [mine]
+        else:
+            results = [None] * self.world_size
+            self._dist.all_gather_object(results, _to_cpu(mine))
+        for res in results:
+            if not res.ok:
+                raise WorkerError(f"worker rank {res.rank} failed in {op}:\n{res.error}")
+        return [r.payload for r in results]
+
+
+def _to_cpu(obj):
+    if isinstance(obj, torch.Tensor):
+        return obj.detach().cpu()
+    if isinstance(obj, WorkerResult):
+        obj.payload = _to_cpu(obj.payload)
+        return obj
+    if isinstance(obj, dict):
+        return {k: _to_cpu(v) for k, v in obj.items()}
+    if isinstance(obj, (list, tuple)):
+        return type(obj)(_to_cpu(v) for v in obj)
+    return obj
+
+
+def make_cluster(config: EngineConfig, launcher: str | None = None, worker=None):
+    """Pick the cluster flavour: explicit ``launcher`` or, by default, SPMD under torchrun,
+    in-process for one rank, spawned processes otherwise."""
+    if launcher is None:
+        if int(os.environ.get("WORLD_SIZE", "1")) > 1 and int(os.environ.get("WORLD_SIZE", "1")) == config.world_size:
+            launcher = "spmd"
+        elif config.world_size == 1:
+            launcher = "inprocess"
+        else:
+            launcher = "spawn"
+    if launcher == "spmd":
+        return SPMDCluster(config, worker)
+    if launcher == "inprocess":
+        return InProcessCluster(config, worker)
+    if launcher == "spawn":
+        return SpawnCluster(config)
+    raise ValueError(f"unknown launcher {launcher!r}")

@@ -112,6 +112,30 @@ class RankWorker:
             if self.device.type == "cuda":
                 torch.cuda.empty_cache()
 
+    def role_manager(self):
+        if self.roles is None:
+            from .roles import RoleManager
+
+            self.roles = RoleManager(self)
+        return self.roles
+
+    def probe_rollout_cache(self, max_running_seqs: int, max_cache_len: int) -> float:
+        """Allocate the KV cache (and capture the largest decode graph) for the given rollout shape and
+        report the resulting peak memory fraction; used by the auto-tuner."""
+        self.prepare_actor_onloaded()
+        if self.device.type == "cuda":
+            torch.cuda.reset_peak_memory_stats(self.device)
+        eng = self.inference_engine(max_running_seqs, (max_cache_len + 63) // 64 * 64)
+        eng.ensure_kv_cache()
+        return self.peak_memory_fraction()
+
+    def model_info(self) -> dict:
+        mc = self.config.model
+        return {"model_type": mc.model_type, "vocab_size": mc.vocab_size, "hidden_size": mc.hidden_size,
+                "num_hidden_layers": mc.num_hidden_layers, "max_position_embeddings": mc.max_position_embeddings,
+                "parameters": sum(p.numel() for p in self.model.parameters()), "tp_size": self.ctx.tp_size,
+                "dp_size": self.ctx.dp_size}
+
     def save_checkpoint(self, path: str) -> None:
         self.adapter.save_weights(self.model, path, self.config.model, source_path=self.config.model_path)
 

@@ -285,60 +285,73 @@ def run_ours(args):
 
 
 def run_e2e(args, worker, mcfg, params, rank, world, device, n_prompts, pmin, pmax, new_tokens):
-    """Same step through the SDK ``Trainer`` on top of the already-built worker, wall-clock timed,
-    with per-step pinned H2D of the prompt ids and D2H of results/loss."""
+    """The same step through the public SDK (``Trainer.rollout_session`` / ``rollout_token_batch`` /
+    ``train``) on top of the already-built worker, timed by wall clock.  Every step the SDK path
+    copies that step's token ids (prompts for prefill, packed sequences and per-token signals for
+    training) from pinned host memory to the device and reads the sampled tokens, their
+    log-probs and the loss / metrics back to the host; those bytes are counted from the tensors."""
     import torch
     import torch.distributed as dist
+    from functools import partial
 
     try:
-        from areno_b200.api.trainer import Trainer
+        from areno_b200.api import SamplingParams as ApiParams, Trainer, TrainSequence, grpo_loss_fn
+        from areno_b200.api.rewards import compute_group_advantages
     except Exception as exc:  # SDK layer not importable: report honestly
         return {"value": None, "unit": "tokens/s", "error": f"SDK unavailable: {exc}"}
     trainer = Trainer.from_worker(worker, world_size=world)
+    api_params = ApiParams(temperature=1.0, top_p=1.0, top_k=-1, max_new_tokens=new_tokens, ignore_eos=True)
+    loss_fn = partial(grpo_loss_fn, clip_eps=0.2)
     steps = max(1, min(args.steps, 2))
-    h2d = d2h = 0
+    counters = {"h2d": 0, "d2h": 0}
 
     def step(i):
-        nonlocal h2d, d2h
-        prompts = make_prompts(10_000 + i, rank, mcfg.vocab_size, n_prompts, pmin, pmax)
-        staged = [torch.tensor(p, dtype=torch.int64).pin_memory().to(device, non_blocking=True) for p in prompts]
-        h2d += sum(t.numel() * 8 for t in staged)
-        prompts_dev = [t.tolist() for t in staged]
-        d2h += sum(t.numel() * 8 for t in staged)
-        from areno_b200.api.models import SamplingParams as ApiParams
-
-        with trainer.rollout_session():
-            res = trainer.rollout_token_batch(prompts_dev, GROUP, ApiParams(
-                temperature=1.0, max_new_tokens=new_tokens, ignore_eos=True))
-        d2h += sum(len(s.resp_tokens) * 8 for r in res for s in r.sequences)
-        batch, ntok = trainer.build_policy_batch(prompts_dev, res, hash_reward, GROUP)
-        stats = trainer.train(batch, loss_fn="grpo", mini_bs=None, micro_batch_tokens=MICRO_TOKENS)
-        h2d += ntok * (8 + 4 + 4 + 1)
-        d2h += 4
+        prompts = []
+        for r in range(world):
+            prompts.extend(make_prompts(10_000 + i, r, mcfg.vocab_size, n_prompts, pmin, pmax))
+        with trainer.rollout_session(sampling_params=api_params):
+            results = trainer.rollout_token_batch(prompts, GROUP, api_params)
+        batch = []
+        ntok = 0
+        for p, res in zip(prompts, results):
+            rewards = [hash_reward(s.resp_tokens) for s in res.sequences]
+            for s, adv, rew in zip(res.sequences, compute_group_advantages(rewards), rewards):
+                n_r = len(s.resp_tokens)
+                batch.append(TrainSequence(prompt_mask=[True] * len(p) + [False] * n_r, tokens=p + s.resp_tokens,
+                                           logprobs=[0.0] * len(p) + s.resp_logprobs,
+                                           advantages=[0.0] * len(p) + [adv] * n_r, reward=rew, eos_token_id=0))
+                ntok += len(p) + n_r
+        stats = trainer.train(batch, loss_fn, mini_bs=3 * world)
+        my_share = 1.0 / world
+        # per rank: prompt ids (int64) for prefill; ids, positions (int64), 2 float32 signals, mask, seq ids for training
+        counters["h2d"] += int(my_share * (sum(len(p) for p in prompts) * GROUP * 8 + ntok * (8 + 8 + 4 + 4 + 1 + 8)))
+        counters["d2h"] += int(my_share * sum(len(s.resp_tokens) for r in results for s in r.sequences) * (4 + 4)) + 4 * 16
         return ntok, stats
 
     step(-1)
+    counters["h2d"] = counters["d2h"] = 0
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
     t0 = time.time()
     tokens = 0
+    stats = {}
     for i in range(steps):
-        n, _ = step(i)
+        n, stats = step(i)
         tokens += n
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     dt = time.time() - t0
-    t = torch.tensor([dt, float(tokens)], dtype=torch.float64, device=device)
     if world > 1:
-        mx = t.clone()
-        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
-        sm = t.clone()
-        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
-        dt, tokens = float(mx[0]), float(sm[1])
-    return {"value": tokens / dt, "unit": "tokens/s", "steps": steps, "h2d_bytes_per_step": h2d // (steps + 1),
-            "d2h_bytes_per_step": d2h // (steps + 1), "timing": "wall clock, max over ranks"}
+        t = torch.tensor([dt], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dt = float(t[0])
+    return {"value": tokens / dt, "unit": "tokens/s", "steps": steps, "ms_per_step": dt / steps * 1e3,
+            "h2d_bytes_per_step": counters["h2d"] // steps, "d2h_bytes_per_step": counters["d2h"] // steps,
+            "timing": "wall clock around Trainer.rollout_token_batch + Trainer.train, max over ranks",
+            "step_rollout_time_s": stats.get("step_rollout_time_s"), "step_train_time_s": stats.get("step_train_time_s"),
+            "loss": stats.get("loss")}
 
 
 def main():
