@@ -14,6 +14,7 @@ updates and re-gathers.
 
 from __future__ import annotations
 
+import os
 from typing import Any, Callable
 
 import numpy as np
@@ -200,7 +201,7 @@ class TrainingManager:
         per_layer = per_token * max(tokens, 1)
         free, _total = torch.cuda.mem_get_info(self.device)
         free += torch.cuda.memory_reserved(self.device) - torch.cuda.memory_allocated(self.device)
-        reserve = 26 << 30
+        reserve = int(float(os.environ.get("ARENO_CKPT_RESERVE_GB", "26")) * (1 << 30))
         keep = max(0, int((free - reserve) // max(per_layer, 1)))
         n_ckpt = max(0, n_layers - keep)
         self._ckpt_cache = (tokens, n_ckpt)
