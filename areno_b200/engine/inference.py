@@ -61,6 +61,19 @@ class RolloutOutput:
     prompt_indices: list[int] | None = None
     stats: dict = field(default_factory=dict)
 
+    # Field names of the reference's rollout result (``areno/engine/data/batch.py``), as read-only views.
+    @property
+    def response_ids(self) -> list[list[int]]:
+        return self.tokens
+
+    @property
+    def response_logprobs(self) -> list[list[float]]:
+        return self.logprobs
+
+    @property
+    def finish_reason(self) -> list[str]:
+        return self.finish_reasons
+
 
 @dataclass
 class _Request:
@@ -73,6 +86,7 @@ class _Request:
     logprobs: list[float] | None = None
     reason: str = ""
     tag: object = None
+    stream: int = -1  # random-stream id keyed into the sampler; defaults to rid
 
 
 def _pick_bucket(buckets: list[int], n: int) -> int:
@@ -183,7 +197,11 @@ class InferenceEngine:
         self.step_count = 0
         self.decode_tokens = 0
 
-    def add_request(self, prompt: list[int], max_new_tokens: int | None = None, tag=None) -> int:
+    def add_request(self, prompt: list[int], max_new_tokens: int | None = None, tag=None,
+                    stream: int | None = None) -> int:
+        """``stream`` selects the sampler's random stream for this row.  Callers that want a seeded
+        request to reproduce pass the row's index within the request; by default every request gets a
+        fresh stream."""
         rid = self._next_rid
         self._next_rid += 1
         max_new = self.default_max_new if max_new_tokens is None else max_new_tokens
@@ -191,7 +209,7 @@ class InferenceEngine:
         max_new = max(1, min(max_new, room, self.max_out))
         if len(prompt) >= self.max_model_len:
             raise ValueError(f"prompt of {len(prompt)} tokens does not fit max_model_len={self.max_model_len}")
-        self._requests[rid] = _Request(rid, list(prompt), max_new, tag=tag)
+        self._requests[rid] = _Request(rid, list(prompt), max_new, tag=tag, stream=rid if stream is None else int(stream))
         self.sched.add(rid, len(prompt), max_new)
         return rid
 
@@ -248,7 +266,8 @@ class InferenceEngine:
                  progress_interval_s: float = 0.0) -> RolloutOutput:
         """Blocking helper: generate one completion per prompt, results in prompt order."""
         self.begin(params, eos_token_ids, max_new_tokens)
-        rids = [self.add_request(p) for p in prompts]
+        seeded = params.seed is not None
+        rids = [self.add_request(p, stream=i if seeded else None) for i, p in enumerate(prompts)]
         t0 = time.time()
         self.run_until_done(progress_interval_s)
         reqs = [self._requests[r] for r in rids]
@@ -272,7 +291,7 @@ class InferenceEngine:
     def _run_prefill(self, entries):
         dev = self.device
         ids, pos, slots_map, q_lens, k_lens = [], [], [], [], []
-        logit_rows, fin_slots, fin_prompt, fin_budget, fin_uid = [], [], [], [], []
+        logit_rows, fin_slots, fin_prompt, fin_budget, fin_uid, fin_stream = [], [], [], [], [], []
         hist_slots = []
         has_history = False
         row = 0
@@ -300,6 +319,7 @@ class InferenceEngine:
                 fin_prompt.append(len(req.prompt))
                 fin_budget.append(req.max_new)
                 fin_uid.append(rid)
+                fin_stream.append(req.stream)
         touched = sorted({e[0] for e in entries})
         lo, hi = touched[0], touched[-1] + 1
         self.block_table[lo:hi].copy_(self.h_block_table[lo:hi], non_blocking=True)
@@ -322,10 +342,11 @@ class InferenceEngine:
             return
         uid = torch.tensor(fin_uid, dtype=torch.int64, device=dev)
         slots_t = torch.tensor(fin_slots, dtype=torch.int32, device=dev)
-        self.row_uid[slots_t.long()] = uid
+        stream = torch.tensor(fin_stream, dtype=torch.int64, device=dev)
+        self.row_uid[slots_t.long()] = stream
         self.uid32[slots_t.long()] = (uid & 0x7FFFFFFF).to(torch.int32)
         zero_gen = torch.zeros(n, dtype=torch.int32, device=dev)
-        tok, lp = self._sample(out.logits_shard, zero_gen, uid)
+        tok, lp = self._sample(out.logits_shard, zero_gen, stream)
         prompt_t = torch.tensor(fin_prompt, dtype=torch.int32, device=dev)
         budget_t = torch.tensor(fin_budget, dtype=torch.int32, device=dev)
         if self.cuda:

@@ -128,8 +128,11 @@ class WorkerLoop:
             if not rows:
                 self._finish(state)
                 return
-            for r in rows:
-                rid = eng.add_request(r, cmd.payload.max_new_tokens, tag=cmd.request_id)
+            seeded = cmd.payload.sampling_params.seed is not None
+            for r, idx in zip(rows, indices):
+                # a seeded request reproduces: its rows draw from streams numbered by their position
+                rid = eng.add_request(r, cmd.payload.max_new_tokens, tag=cmd.request_id,
+                                      stream=int(idx) if seeded else None)
                 state["reqs"].append(rid)
 
         admit(first)

@@ -65,7 +65,19 @@ def sample(logits, temperature: float = 1.0, top_k: int = -1, top_p: float = 1.0
     """Returns ``(token_ids int64 [B], logprobs fp32 [B])``; with ``part`` (fp32 [B, 6]) writes the
     shard-local candidate record instead (see ``combine_shards``)."""
     if not logits.is_cuda:
-        tok, lp = sample_reference(logits, temperature, top_k, top_p, cls, gen_count, min_new, generator)
+        if generator is None and row_uid is not None and temperature > 0.0:
+            # counter-based like the kernel: the draw depends only on (seed, row stream, step)
+            toks, lps = [], []
+            for i in range(logits.shape[0]):
+                step = int(gen_count[i]) if gen_count is not None else 0
+                g = torch.Generator().manual_seed((int(seed) * 0x9E3779B1 + int(row_uid[i]) * 0x85EBCA77 + step) % (1 << 63))
+                t, l = sample_reference(logits[i:i + 1], temperature, top_k, top_p, cls,
+                                        None if gen_count is None else gen_count[i:i + 1], min_new, g)
+                toks.append(t)
+                lps.append(l)
+            tok, lp = torch.cat(toks), torch.cat(lps)
+        else:
+            tok, lp = sample_reference(logits, temperature, top_k, top_p, cls, gen_count, min_new, generator)
         if out_token is not None:
             out_token.copy_(tok)
             tok = out_token
