@@ -632,3 +632,74 @@ extern "C" int areno_headnorm_bwd(const void* dy, long long dy_stride, const voi
     colsum_partials_kernel<<<(D + 255) / 256, 256, 0, stream>>>(dw_partial, dw, grid, D, dw_accumulate);
   return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------------------------
+// RMSNorm backward with library-owned scratch (declared in no_alloc.h).
+// The partial-dW rows go to a fixed device array instead of a caller buffer, so the call
+// needs no allocator.  `g_rmsnorm_bwd_scratch` below is the host-side handle of that array,
+// not a device address: the address differs per device and is looked up once per device with
+// cudaGetSymbolAddress while that device is current, then cached in g_scratch_addr[].
+// ---------------------------------------------------------------------------------
+#include <mutex>
+
+#include "no_alloc.h"
+
+static __device__ __align__(256) float
+    g_rmsnorm_bwd_scratch[(size_t)ARENO_RMSNORM_BWD_STATIC_BLOCKS * ARENO_RMSNORM_BWD_STATIC_MAX_H];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_scratch_addr[kMaxDevices] = {};  // filled lazily, one slot per device ordinal
+std::mutex g_scratch_mutex;
+
+// Returns 0 and the device address of the scratch on the current device, or an error code.
+int static_scratch_for_current_device(float** out) {
+  int dev = -1;
+  cudaError_t rc = cudaGetDevice(&dev);
+  if (rc != cudaSuccess) return (int)rc;
+  if (dev < 0 || dev >= kMaxDevices) return ARENO_NOALLOC_ERR_DEVICE;
+  std::lock_guard<std::mutex> guard(g_scratch_mutex);
+  if (g_scratch_addr[dev] == nullptr) {
+    float* p = nullptr;
+    rc = cudaGetSymbolAddress((void**)&p, g_rmsnorm_bwd_scratch);
+    if (rc != cudaSuccess) return (int)rc;
+    if (p == nullptr) return ARENO_NOALLOC_ERR_SYMBOL;
+    g_scratch_addr[dev] = p;
+  }
+  *out = g_scratch_addr[dev];
+  return 0;
+}
+}  // namespace
+
+extern "C" const char* areno_no_alloc_strerror(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case -2: return "hidden size not supported by the RMSNorm kernels";
+    case -3: return "hidden size must be a multiple of 8";
+    case ARENO_NOALLOC_ERR_H_TOO_LARGE:
+      return "hidden size exceeds ARENO_RMSNORM_BWD_STATIC_MAX_H (8192): the fixed scratch cannot hold it; "
+             "use areno_rmsnorm_bwd with caller-provided scratch";
+    case ARENO_NOALLOC_ERR_SYMBOL: return "could not resolve the device address of the fixed scratch array";
+    case ARENO_NOALLOC_ERR_DEVICE: return "device ordinal is outside the per-device table (64 entries)";
+    default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown error code";
+  }
+}
+
+extern "C" int areno_rmsnorm_bwd_static(const void* dy, const void* h, const void* w, int wf32, float w_offset,
+                                        const float* inv_rms, const void* dres_in, void* dx, float* dw,
+                                        int dw_accumulate, long long rows, int H, cudaStream_t stream) {
+  if (H % 8 != 0) return -3;
+  if (H > ARENO_RMSNORM_BWD_STATIC_MAX_H) return ARENO_NOALLOC_ERR_H_TOO_LARGE;
+  float* scratch = nullptr;
+  const int rc = static_scratch_for_current_device(&scratch);  // set-up on the first call per device
+  if (rc != 0) return rc;
+  if (rows <= 0) return 0;
+  const int grid = (int)(rows < ARENO_RMSNORM_BWD_STATIC_BLOCKS ? rows : ARENO_RMSNORM_BWD_STATIC_BLOCKS);
+  // Each of the `grid` blocks writes its whole H-wide row of the scratch (zeros included), and the
+  // fold reads exactly those rows, so leftovers of earlier calls are never read.
+  RMS_DISPATCH(rmsnorm_bwd_kernel, H, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)h, w, wf32, w_offset,
+               inv_rms, (const __nv_bfloat16*)dres_in, (__nv_bfloat16*)dx, scratch, (int)rows, H);
+  if (dw != nullptr)
+    colsum_partials_kernel<<<(H + 255) / 256, 256, 0, stream>>>(scratch, dw, grid, H, dw_accumulate);
+  return (int)cudaGetLastError();
+}
