@@ -29,6 +29,9 @@ logger = get_logger()
 class RankWorker:
     def __init__(self, config: EngineConfig, device: torch.device | str | None = None):
         self.config = config
+        from .. import configure_allocator
+
+        configure_allocator()
         ctx = get_context()
         self.ctx = ctx
         self.device = torch.device(device) if device is not None else ctx.device
