@@ -389,9 +389,9 @@ class InferenceEngine:
                                        out_token=out_token, out_logprob=out_logprob)
         if (p.top_k > 0 or p.top_p < 1.0) and p.temperature > 0:
             # truncated sampling needs the whole distribution on one rank
-            full = torch.empty((ctx.tp_size, *view.shape), dtype=view.dtype, device=view.device)
+            full = torch.empty((ctx.tp_size * view.shape[0], view.shape[1]), dtype=view.dtype, device=view.device)
             dist.all_gather_into_tensor(full, view.contiguous(), group=ctx.tp_group)
-            full = full.permute(1, 0, 2).reshape(view.shape[0], -1)[:, : self.vocab].contiguous()
+            full = full.view(ctx.tp_size, *view.shape).permute(1, 0, 2).reshape(view.shape[0], -1)[:, : self.vocab].contiguous()
             return sampling_ops.sample(full, p.temperature, p.top_k, p.top_p, cls=self.cls, gen_count=gen_count,
                                        min_new=p.min_new_tokens, seed=self.call_seed, row_uid=row_uid,
                                        out_token=out_token, out_logprob=out_logprob)
@@ -399,9 +399,9 @@ class InferenceEngine:
         sampling_ops.sample(view, p.temperature, p.top_k, p.top_p, cls=self.cls, gen_count=gen_count,
                             min_new=p.min_new_tokens, seed=self.call_seed, row_uid=row_uid,
                             vocab_start=lm.vocab_start, part=part)
-        parts = torch.empty((ctx.tp_size, *part.shape), dtype=torch.float32, device=view.device)
+        parts = torch.empty((ctx.tp_size * part.shape[0], 6), dtype=torch.float32, device=view.device)
         dist.all_gather_into_tensor(parts, part, group=ctx.tp_group)
-        tok, lp = sampling_ops.combine_shards(parts)
+        tok, lp = sampling_ops.combine_shards(parts.view(ctx.tp_size, *part.shape))
         if out_token is not None:
             out_token.copy_(tok)
             out_logprob.copy_(lp)

@@ -17,7 +17,7 @@ from typing import Any
 import torch
 
 from ..models import registry as model_registry
-from ..parallel.context import get_context
+from ..parallel.context import get_context, use_context
 from ..utils.log import get_logger
 from .config import EngineConfig
 from .inference import InferenceEngine, RolloutOutput, SamplingParams
@@ -42,6 +42,19 @@ class RankWorker:
             self.adapter.init_random(self.model, seed=config.seed)
         else:
             self.adapter.load_weights(self.model, config.model_path, config.model)
+        # Rollout may use its own layout (e.g. tensor parallel while training is data parallel); it then
+        # gets its own model instance whose shards are cut from the training replica after every step.
+        self.rollout_ctx = ctx.rollout_layout
+        if self.rollout_ctx is not ctx:
+            if ctx.tp_size != 1:
+                raise ValueError("a separate rollout layout requires the training layout to have tp_size == 1")
+            with use_context(self.rollout_ctx):
+                self.rollout_model = self.adapter.build(config.model, device=self.device)
+            for p in self.rollout_model.parameters():
+                p.requires_grad_(False)
+        else:
+            self.rollout_model = self.model
+        self._rollout_stale = True
         self.trainer: TrainingManager | None = None
         self.infer: InferenceEngine | None = None
         self.roles = None
@@ -66,28 +79,66 @@ class RankWorker:
             if self.infer is not None:
                 self.infer.drop_kv_cache()
             self.infer = InferenceEngine(
-                self.model, self.config.model.vocab_size, self.device, max_slots=slots, max_model_len=mlen,
+                self.rollout_model, self.config.model.vocab_size, self.device, max_slots=slots, max_model_len=mlen,
                 max_prefill_tokens=rt.max_prefill_tokens, kv_fp8=rt.kv_dtype == "fp8",
                 graph_buckets=rt.decode_graph_buckets, eager=rt.eager_decode, seed=self.config.seed,
                 max_new_cap=mlen)
         return self.infer
 
     # ---------------------------------------------------------------- rollout
+    def sync_rollout_weights(self) -> int:
+        """Bring the rollout model up to date with the trained parameters.  With a shared layout the
+        engine reads the optimizer's own buffers and there is nothing to do; with a separate rollout
+        layout every rank cuts its shard out of its local replica (no communication)."""
+        if self.rollout_model is self.model or not self._rollout_stale:
+            self._rollout_stale = False
+            return 0
+        from ..parallel.reshard import reshard_into
+
+        n = reshard_into(self.rollout_model, self.model, self.rollout_ctx.tp_rank, self.rollout_ctx.tp_size)
+        self._rollout_stale = False
+        return n
+
+    def prepare_for_rollout(self):
+        self.prepare_actor_onloaded()
+        self.sync_rollout_weights()
+        self.rollout_model.eval()
+
     @torch.no_grad()
     def rollout(self, prompts: list[list[int]], params: SamplingParams, eos_token_ids=(), max_new_tokens: int = 16,
-                max_running: int | None = None, progress_interval_s: float | None = None) -> RolloutOutput:
-        self.prepare_actor_onloaded()
-        self.model.eval()
+                max_running: int | None = None, progress_interval_s: float | None = None,
+                gather_tp: bool = False) -> RolloutOutput:
+        """Generate one completion per prompt.  Every rank of a rollout TP group must pass the same
+        prompts; with ``gather_tp`` each rank passes only its own prompts, the group's prompts are
+        concatenated in rank order, and each rank gets back the results of its own rows."""
+        self.prepare_for_rollout()
+        rctx = self.rollout_ctx
+        lo, hi = 0, len(prompts)
+        if gather_tp and rctx.tp_size > 1:
+            import torch.distributed as dist
+
+            parts: list = [None] * rctx.tp_size
+            dist.all_gather_object(parts, prompts, group=rctx.tp_group)
+            lo = sum(len(x) for x in parts[:rctx.tp_rank])
+            hi = lo + len(prompts)
+            prompts = [row for part in parts for row in part]
+            max_running = (max_running or self.config.max_running_seqs) * rctx.tp_size
         longest = max((len(p) for p in prompts), default=1) + max_new_tokens
         need_len = (longest + 63) // 64 * 64
         slots = min(max_running or self.config.max_running_seqs, max(len(prompts), 1))
-        eng = self.inference_engine(slots, need_len)
         interval = self.config.decode_progress_interval_s if progress_interval_s is None else progress_interval_s
-        return eng.generate(prompts, params, eos_token_ids, max_new_tokens, progress_interval_s=interval)
+        with use_context(rctx):
+            eng = self.inference_engine(slots, need_len)
+            out = eng.generate(prompts, params, eos_token_ids, max_new_tokens, progress_interval_s=interval)
+        if (lo, hi) != (0, len(prompts)):
+            out = RolloutOutput(tokens=out.tokens[lo:hi], logprobs=out.logprobs[lo:hi],
+                                finish_reasons=out.finish_reasons[lo:hi], stats=out.stats)
+        return out
 
     # ------------------------------------------------------------------ train
     def train(self, packs: list, gradient_accumulation_steps: int | None = None) -> list[dict]:
         self.prepare_for_train()
+        self._rollout_stale = True
         return self.training_manager().train(packs, gradient_accumulation_steps)
 
     # ---------------------------------------------------------- GPU residency
@@ -125,11 +176,12 @@ class RankWorker:
     def probe_rollout_cache(self, max_running_seqs: int, max_cache_len: int) -> float:
         """Allocate the KV cache (and capture the largest decode graph) for the given rollout shape and
         report the resulting peak memory fraction; used by the auto-tuner."""
-        self.prepare_actor_onloaded()
+        self.prepare_for_rollout()
         if self.device.type == "cuda":
             torch.cuda.reset_peak_memory_stats(self.device)
-        eng = self.inference_engine(max_running_seqs, (max_cache_len + 63) // 64 * 64)
-        eng.ensure_kv_cache()
+        with use_context(self.rollout_ctx):
+            eng = self.inference_engine(max_running_seqs, (max_cache_len + 63) // 64 * 64)
+            eng.ensure_kv_cache()
         return self.peak_memory_fraction()
 
     def model_info(self) -> dict:

@@ -16,7 +16,7 @@ import queue
 import traceback
 from typing import Any, Callable
 
-from ..parallel.context import get_context
+from ..parallel.context import get_context, use_context
 from .inference import RolloutOutput
 from .protocol import (CachePayload, Command, Op, RolesPayload, RolloutPayload, SavePayload, ScorePayload, TrainPayload,
                        TrainValuesPayload, WorkerResult)
@@ -65,13 +65,14 @@ def execute(worker, cmd: Command) -> Any:
     raise ValueError(f"unsupported op {op}")
 
 
-def _local_rows(p: RolloutPayload):
-    ctx = get_context()
+def _local_rows(p: RolloutPayload, worker=None):
+    """Rollout prompts are split over the data-parallel rows of the ROLLOUT layout."""
+    ctx = worker.rollout_ctx if worker is not None else get_context().rollout_layout
     return p.prompts_by_dp[ctx.dp_rank], p.prompt_indices_by_dp[ctx.dp_rank]
 
 
 def _rollout_blocking(worker, p: RolloutPayload) -> RolloutOutput:
-    prompts, indices = _local_rows(p)
+    prompts, indices = _local_rows(p, worker)
     if not prompts:
         return RolloutOutput(prompt_indices=[])
     out = worker.rollout(prompts, p.sampling_params, p.eos_token_ids, p.max_new_tokens, max_running=p.max_running_seqs,
@@ -100,7 +101,7 @@ class WorkerLoop:
                 self.put_result(WorkerResult(self.rank, cmd.request_id, True, None))
                 return
             try:
-                if cmd.op == Op.INFER_ROLLOUT and get_context().tp_size == 1:
+                if cmd.op == Op.INFER_ROLLOUT and self.worker.rollout_ctx.tp_size == 1:
                     self._continuous_rollout(cmd)
                 else:
                     self.put_result(WorkerResult(self.rank, cmd.request_id, True, execute(self.worker, cmd)))
@@ -112,9 +113,8 @@ class WorkerLoop:
         worker = self.worker
         p0: RolloutPayload = first.payload
         key = p0.compatibility_key()
-        worker.prepare_actor_onloaded()
-        worker.model.eval()
-        rows0, _ = _local_rows(p0)
+        worker.prepare_for_rollout()
+        rows0, _ = _local_rows(p0, worker)
         longest = max((len(r) for r in rows0), default=1) + p0.max_new_tokens
         eng = worker.inference_engine(max(p0.max_running_seqs, 1), max((longest + 63) // 64 * 64,
                                                                         p0.max_cache_len or 0))
@@ -122,7 +122,7 @@ class WorkerLoop:
         pending: dict[int, dict] = {}
 
         def admit(cmd: Command) -> None:
-            rows, indices = _local_rows(cmd.payload)
+            rows, indices = _local_rows(cmd.payload, self.worker)
             state = {"cmd": cmd, "indices": list(indices), "left": len(rows), "reqs": []}
             pending[cmd.request_id] = state
             if not rows:
@@ -172,7 +172,7 @@ class WorkerLoop:
 
     @staticmethod
     def _fits(eng, payload: RolloutPayload) -> bool:
-        rows = payload.prompts_by_dp[get_context().dp_rank]
+        rows = payload.prompts_by_dp[get_context().rollout_layout.dp_rank]
         longest = max((len(r) for r in rows), default=1) + payload.max_new_tokens
         return longest <= eng.max_model_len
 

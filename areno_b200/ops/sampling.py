@@ -59,25 +59,88 @@ def sample_reference(logits, temperature, top_k, top_p, cls=None, gen_count=None
     return tok, lp
 
 
+def _s64(x: int) -> int:
+    x &= (1 << 64) - 1
+    return x - (1 << 64) if x >= (1 << 63) else x
+
+
+def _lsr(x: torch.Tensor, n: int) -> torch.Tensor:
+    return (x >> n) & ((1 << (64 - n)) - 1)
+
+
+def _keyed_uniform(seed: int, uid: torch.Tensor, step: torch.Tensor, gidx: torch.Tensor) -> torch.Tensor:
+    """Counter-based uniforms in (0, 1): a pure function of (seed, row stream, step, global token id),
+    so vocabulary shards on different ranks draw consistent noise (splitmix64 finaliser)."""
+    x = (uid.to(torch.int64)[:, None] * _s64(0x9E3779B97F4A7C15) + step.to(torch.int64)[:, None] * _s64(0xD1B54A32D192ED03)
+         + gidx.to(torch.int64)[None, :] * _s64(0x8CB92BA72F3D8DD7) + _s64(int(seed) * 0xA0761D6478BD642F))
+    x = (x ^ _lsr(x, 30)) * _s64(0xBF58476D1CE4E5B9)
+    x = (x ^ _lsr(x, 27)) * _s64(0x94D049BB133111EB)
+    x = x ^ _lsr(x, 31)
+    u = (_lsr(x, 11).to(torch.float64) + 0.5) / float(1 << 53)
+    return u
+
+
+def sample_keyed_reference(logits, temperature, top_k, top_p, cls=None, gen_count=None, min_new=0, seed=0,
+                           row_uid=None, vocab_start=0):
+    """CPU counterpart of the sampling kernel: Gumbel-max with counter-based noise.  Returns the
+    candidate record ``[B, 6]`` = (best perturbed score, global token id bits, raw logit of the
+    winner, raw max, raw sum-exp relative to the max, 0); ``combine_shards`` finishes it."""
+    raw = logits.float()
+    b, v = raw.shape
+    scores = torch.where(torch.isnan(raw), torch.full_like(raw, float("-inf")), raw)
+    if cls is not None:
+        c = cls.to(raw.device)[vocab_start:vocab_start + v]
+        scores = scores.masked_fill((c == CLS_SUPPRESS)[None, :], float("-inf"))
+        if gen_count is not None and min_new > 0:
+            early = (gen_count.to(raw.device) < min_new)[:, None] & (c == CLS_EOS)[None, :]
+            scores = scores.masked_fill(early, float("-inf"))
+    greedy = temperature <= 0.0
+    if not greedy and (top_k > 0 or top_p < 1.0):
+        probs = torch.softmax(scores / temperature, -1)
+        ps, pi = probs.sort(-1, descending=True)
+        keep_sorted = torch.ones_like(ps, dtype=torch.bool)
+        if top_k > 0:
+            keep_sorted[:, min(top_k, v):] = False
+        if top_p < 1.0:
+            keep_sorted &= (ps.cumsum(-1) - ps) <= top_p
+        keep = torch.zeros_like(keep_sorted).scatter(1, pi, keep_sorted)
+        scores = scores.masked_fill(~keep, float("-inf"))
+    if greedy:
+        pert = scores
+    else:
+        uid = row_uid if row_uid is not None else torch.arange(b)
+        step = gen_count if gen_count is not None else torch.zeros(b, dtype=torch.int64)
+        u = _keyed_uniform(seed, uid.cpu(), step.cpu(), vocab_start + torch.arange(v))
+        pert = scores / temperature + (-torch.log(-torch.log(u))).to(torch.float32)
+    bv, bi = pert.max(-1)
+    finite = torch.where(torch.isnan(raw), torch.full_like(raw, float("-inf")), raw).clamp(max=3.0e38)
+    m = finite.max(-1).values
+    ssum = torch.exp(finite - m[:, None]).sum(-1)
+    rec = torch.zeros((b, 6), dtype=torch.float32)
+    rec[:, 0] = bv
+    rec[:, 1] = (vocab_start + bi).to(torch.int32).view(torch.float32)
+    rec[:, 2] = raw.gather(-1, bi[:, None]).squeeze(-1)
+    rec[:, 3] = m
+    rec[:, 4] = ssum
+    return rec
+
+
+
 def sample(logits, temperature: float = 1.0, top_k: int = -1, top_p: float = 1.0, *, cls=None, gen_count=None,
            min_new: int = 0, seed: int = 0, row_uid=None, vocab_start: int = 0, out_token=None, out_logprob=None,
            part=None, generator=None):
     """Returns ``(token_ids int64 [B], logprobs fp32 [B])``; with ``part`` (fp32 [B, 6]) writes the
     shard-local candidate record instead (see ``combine_shards``)."""
     if not logits.is_cuda:
-        if generator is None and row_uid is not None and temperature > 0.0:
-            # counter-based like the kernel: the draw depends only on (seed, row stream, step)
-            toks, lps = [], []
-            for i in range(logits.shape[0]):
-                step = int(gen_count[i]) if gen_count is not None else 0
-                g = torch.Generator().manual_seed((int(seed) * 0x9E3779B1 + int(row_uid[i]) * 0x85EBCA77 + step) % (1 << 63))
-                t, l = sample_reference(logits[i:i + 1], temperature, top_k, top_p, cls,
-                                        None if gen_count is None else gen_count[i:i + 1], min_new, g)
-                toks.append(t)
-                lps.append(l)
-            tok, lp = torch.cat(toks), torch.cat(lps)
-        else:
+        if generator is not None:
             tok, lp = sample_reference(logits, temperature, top_k, top_p, cls, gen_count, min_new, generator)
+        else:
+            rec = sample_keyed_reference(logits, temperature, top_k, top_p, cls, gen_count, min_new, seed, row_uid,
+                                         vocab_start)
+            if part is not None:
+                part.copy_(rec)
+                return None, None
+            tok, lp = combine_shards(rec[None])
         if out_token is not None:
             out_token.copy_(tok)
             tok = out_token

@@ -1,9 +1,16 @@
 """Process-group layout: ``global_rank = dp_rank * tp_size + tp_rank``; one TP group per DP row and
 one DP group per TP column (same layout as ``areno/engine/parallel/context.py:65-127``).  NCCL on
-CUDA, Gloo on CPU; rendezvous over TCP on 127.0.0.1."""
+CUDA, Gloo on CPU; rendezvous over TCP on 127.0.0.1.
+
+A job may use two layouts over the same ranks: the training layout (the installed context) and a
+rollout layout with a different TP width (``ctx.rollout``), e.g. training as pure data parallel with
+sharded optimizer state while decoding tensor-parallel so that every weight byte is read once per
+TP group instead of once per GPU.  Code that must run in the rollout layout wraps itself in
+``use_context(ctx.rollout)``."""
 
 from __future__ import annotations
 
+import contextlib
 import datetime
 import os
 from dataclasses import dataclass
@@ -24,10 +31,15 @@ class ParallelContext:
     tp_group: Any = None
     dp_group: Any = None
     device: torch.device = torch.device("cpu")
+    rollout: "ParallelContext | None" = None  # second layout for the inference engine (None: same as training)
 
     @property
     def is_tp_first(self) -> bool:
         return self.tp_rank == 0
+
+    @property
+    def rollout_layout(self) -> "ParallelContext":
+        return self.rollout if self.rollout is not None else self
 
 
 _CONTEXT = ParallelContext()
@@ -42,28 +54,29 @@ def set_context(ctx: ParallelContext) -> None:
     _CONTEXT = ctx
 
 
+@contextlib.contextmanager
+def use_context(ctx: ParallelContext):
+    """Temporarily install ``ctx`` as the global context (layer construction and forward read it)."""
+    global _CONTEXT
+    prev = _CONTEXT
+    _CONTEXT = ctx
+    try:
+        yield ctx
+    finally:
+        _CONTEXT = prev
+
+
 def single_process_context(device: torch.device | str = "cpu") -> ParallelContext:
     ctx = ParallelContext(device=torch.device(device))
     set_context(ctx)
     return ctx
 
 
-def init_parallel(rank: int, world_size: int, tp_size: int, *, master_addr: str = "127.0.0.1", master_port: int = 0,
-                  backend: str | None = None, device: torch.device | None = None,
-                  timeout_s: float = 1800.0) -> ParallelContext:
-    """Create the default group plus TP / DP sub-groups and install the global context."""
-    if device is None:
-        device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
-    if backend is None:
-        backend = "nccl" if device.type == "cuda" else "gloo"
+def _layout(rank: int, world_size: int, tp_size: int, backend: str, device) -> ParallelContext:
+    """Create the TP / DP sub-groups of one layout (collective: every rank must call it)."""
+    if world_size % tp_size != 0:
+        raise ValueError(f"world_size {world_size} is not divisible by tp_size {tp_size}")
     dp_size = world_size // tp_size
-    if not dist.is_initialized() and world_size > 1:
-        init = f"tcp://{master_addr}:{master_port}" if master_port else "env://"
-        kwargs: dict[str, Any] = {}
-        if backend == "nccl":
-            kwargs["device_id"] = device
-        dist.init_process_group(backend=backend, init_method=init, rank=rank, world_size=world_size,
-                                timeout=datetime.timedelta(seconds=timeout_s), **kwargs)
     tp_group = dp_group = None
     if world_size > 1:
         for d in range(dp_size):
@@ -76,9 +89,30 @@ def init_parallel(rank: int, world_size: int, tp_size: int, *, master_addr: str 
             g = dist.new_group(ranks=ranks, backend=backend) if dp_size > 1 else None
             if rank in ranks:
                 dp_group = g
-    ctx = ParallelContext(rank=rank, world_size=world_size, tp_rank=rank % tp_size, tp_size=tp_size,
-                          dp_rank=rank // tp_size, dp_size=dp_size, tp_group=tp_group, dp_group=dp_group,
-                          device=device)
+    return ParallelContext(rank=rank, world_size=world_size, tp_rank=rank % tp_size, tp_size=tp_size,
+                           dp_rank=rank // tp_size, dp_size=dp_size, tp_group=tp_group, dp_group=dp_group,
+                           device=device)
+
+
+def init_parallel(rank: int, world_size: int, tp_size: int, *, master_addr: str = "127.0.0.1", master_port: int = 0,
+                  backend: str | None = None, device: torch.device | None = None,
+                  timeout_s: float = 1800.0, rollout_tp_size: int | None = None) -> ParallelContext:
+    """Create the default group plus TP / DP sub-groups and install the global context.  With
+    ``rollout_tp_size`` different from ``tp_size`` a second layout is created as ``ctx.rollout``."""
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+    if backend is None:
+        backend = "nccl" if device.type == "cuda" else "gloo"
+    if not dist.is_initialized() and world_size > 1:
+        init = f"tcp://{master_addr}:{master_port}" if master_port else "env://"
+        kwargs: dict[str, Any] = {}
+        if backend == "nccl":
+            kwargs["device_id"] = device
+        dist.init_process_group(backend=backend, init_method=init, rank=rank, world_size=world_size,
+                                timeout=datetime.timedelta(seconds=timeout_s), **kwargs)
+    ctx = _layout(rank, world_size, tp_size, backend, device)
+    if rollout_tp_size and rollout_tp_size != tp_size:
+        ctx.rollout = _layout(rank, world_size, rollout_tp_size, backend, device)
     set_context(ctx)
     return ctx
 
