@@ -16,6 +16,8 @@ class ArenoConfig:
     model_path: str | None = None
     tp_size: int = 1
     dp_size: int | None = None
+    # decode tensor-parallel over this many GPUs while training stays data parallel (needs tp_size == 1)
+    rollout_tp_size: int | None = None
     devices: list[int] | None = None
     dummy_load: bool = False
     optimizer: dict[str, Any] = field(default_factory=dict)

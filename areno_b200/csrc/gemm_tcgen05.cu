@@ -36,6 +36,11 @@ struct GemmParams {
   int splits;         // split-K factor (1 = none); split s covers k-blocks [s*kb_per_split, ...)
   int kb_per_split;
   long long split_stride;  // elements between consecutive split partials in C (fp32 workspace)
+  // Extra destinations of a bf16 result (epi 0/1): the same tile is also stored at the same
+  // (row, col) of each of these buffers, which may live in a peer GPU's memory (plain st.global
+  // over NVLink).  Used by row-parallel TP linears to deliver their partial to every rank.
+  int n_extra;
+  void* extra[7];
 };
 
 template <int BN, int STAGES>
@@ -261,6 +266,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             const __nv_bfloat16* bias =
                 p.epi == 1 ? reinterpret_cast<const __nv_bfloat16*>(p.bias) + col : nullptr;
             store_row_bf16(dst, r, ncols, bias);
+            for (int e = 0; e < p.n_extra; ++e)
+              store_row_bf16(reinterpret_cast<__nv_bfloat16*>(p.extra[e]) + (long long)row * p.ldc + col, r, ncols,
+                             bias);
           } else {
             float* dst = reinterpret_cast<float*>(p.C) + split * p.split_stride + (long long)row * p.ldc + col;
             store_row_f32(dst, r, ncols, p.epi == 3);
@@ -363,10 +371,16 @@ static int pick_bn(int M, int N, bool b_mn) {
   return 32;
 }
 
-// out[m, n] = bf16(sum_s ws[s, m, n] (+ bias[n])), fixed summation order.
+struct ExtraDst {
+  int n;
+  void* p[7];
+};
+
+// out[m, n] = bf16(sum_s ws[s, m, n] (+ bias[n])), fixed summation order; the result is also
+// written to every extra destination (peer inboxes of a TP group).
 __global__ void __launch_bounds__(256)
 splitk_reduce_kernel(const float* __restrict__ ws, __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ bias,
-                     int M, int N, long long ldc, long long split_stride, int splits) {
+                     int M, int N, long long ldc, long long split_stride, int splits, ExtraDst extra) {
   const int nvec = N >> 2;
   const long long total = (long long)M * nvec;
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
@@ -384,6 +398,8 @@ splitk_reduce_kernel(const float* __restrict__ ws, __nv_bfloat16* __restrict__ o
     }
     uint2 o = make_uint2(pack_bf16x2(acc.x, acc.y), pack_bf16x2(acc.z, acc.w));
     *reinterpret_cast<uint2*>(out + (long long)m * ldc + c) = o;
+    for (int e = 0; e < extra.n; ++e)
+      *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(extra.p[e]) + (long long)m * ldc + c) = o;
   }
 }
 
@@ -397,10 +413,14 @@ extern "C" long long areno_gemm_workspace_bytes(int M, int N, int K) {
   return 16ll * M * N * 4;  // at most 16 splits
 }
 
-extern "C" int areno_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
-                               long long lda, long long ldb, long long ldc, int a_mn, int b_mn, int epi, int bn,
-                               void* workspace, long long workspace_bytes, int* status, cudaStream_t stream) {
+static int gemm_bf16_impl(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
+                          long long lda, long long ldb, long long ldc, int a_mn, int b_mn, int epi, int bn,
+                          void* workspace, long long workspace_bytes, int* status, cudaStream_t stream,
+                          void* const* extra, int n_extra) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (n_extra < 0 || n_extra > 7 || (n_extra > 0 && epi > 1)) return -3;
+  for (int e = 0; e < n_extra; ++e)
+    if (reinterpret_cast<uintptr_t>(extra[e]) & 15) return -3;
   if ((lda % 8) != 0 || (ldb % 8) != 0) return -3;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
       (reinterpret_cast<uintptr_t>(C) & 15))
@@ -437,6 +457,8 @@ extern "C" int areno_gemm_bf16(const void* A, const void* B, void* C, const void
   p.splits = 1;
   p.kb_per_split = (K + kBK - 1) / kBK;
   p.split_stride = 0;
+  p.n_extra = n_extra;
+  for (int e = 0; e < 7; ++e) p.extra[e] = e < n_extra ? extra[e] : nullptr;
   // Split-K for skinny problems (decode): too few output tiles to fill the GPU, long K.
   const int num_kb = (K + kBK - 1) / kBK;
   const int tiles = p.tiles_m * p.tiles_n;
@@ -455,6 +477,7 @@ extern "C" int areno_gemm_bf16(const void* A, const void* B, void* C, const void
       p.ldc = N;
       p.epi = 2;
       p.bias = nullptr;
+      p.n_extra = 0;  // partials go to the workspace; the fold kernel delivers the result
       split = true;
     }
   }
@@ -466,12 +489,33 @@ extern "C" int areno_gemm_bf16(const void* A, const void* B, void* C, const void
     else rc = dispatch_bn<false, false>(bn, ta, tb, p, stream);
   }
   if (rc != 0 || !split) return rc;
+  ExtraDst xd;
+  xd.n = n_extra;
+  for (int e = 0; e < 7; ++e) xd.p[e] = e < n_extra ? extra[e] : nullptr;
   const long long total = (long long)M * (N / 4);
   int grid = (int)((total + 255) / 256);
   if (grid > 148 * 8) grid = 148 * 8;
   splitk_reduce_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const float*>(workspace),
                                                  reinterpret_cast<__nv_bfloat16*>(C),
                                                  epi == 1 ? reinterpret_cast<const __nv_bfloat16*>(bias) : nullptr, M, N,
-                                                 ldc, p.split_stride, p.splits);
+                                                 ldc, p.split_stride, p.splits, xd);
   return (int)cudaGetLastError();
+}
+
+extern "C" int areno_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
+                               long long lda, long long ldb, long long ldc, int a_mn, int b_mn, int epi, int bn,
+                               void* workspace, long long workspace_bytes, int* status, cudaStream_t stream) {
+  return gemm_bf16_impl(A, B, C, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, epi, bn, workspace, workspace_bytes, status,
+                        stream, nullptr, 0);
+}
+
+// Same GEMM (K-major operands, bf16 result with optional bias), with the result ALSO stored at the
+// same offsets of `n_extra` (<= 7) further buffers given as a host array of device pointers; these
+// are typically the inbox lanes of the other ranks of a TP group, written over NVLink from the
+// epilogue while later tiles are still being multiplied.
+extern "C" int areno_gemm_bf16_push(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
+                                    long long lda, long long ldb, long long ldc, void* const* extra, int n_extra,
+                                    void* workspace, long long workspace_bytes, int* status, cudaStream_t stream) {
+  return gemm_bf16_impl(A, B, C, bias, M, N, K, lda, ldb, ldc, 0, 0, bias != nullptr ? 1 : 0, 0, workspace,
+                        workspace_bytes, status, stream, extra, n_extra);
 }

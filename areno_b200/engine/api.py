@@ -59,7 +59,7 @@ class ArenoEngine:
                         optimizer_config: OptimizerConfig | None = None, runtime_config: RuntimeConfig | None = None,
                         loss_fn: Callable | None = None, model_config: ModelConfig | None = None,
                         launcher: str | None = None, max_running_seqs: int = 64, seed: int = 0,
-                        backend: str | None = None) -> "ArenoEngine":
+                        backend: str | None = None, rollout_tp_size: int | None = None) -> "ArenoEngine":
         if model_config is None:
             if model is None:
                 raise ValueError("from_pretrained() requires a local model path or an explicit model_config")
@@ -70,7 +70,7 @@ class ArenoEngine:
         cfg = EngineConfig(model=model_config, model_path=model or "", tp_size=tp_size, dp_size=dp_size, devices=devices,
                            dummy_load=dummy_load or not model, optimizer=optimizer_config or OptimizerConfig(),
                            runtime=runtime_config or RuntimeConfig(), max_running_seqs=max_running_seqs, seed=seed,
-                           backend=backend)
+                           backend=backend, rollout_tp_size=rollout_tp_size)
         return cls(cfg, loss_fn=loss_fn, launcher=launcher)
 
     # ---------------------------------------------------------------- sessions
@@ -92,7 +92,7 @@ class ArenoEngine:
     # ----------------------------------------------------------------- rollout
     def _rollout_payload(self, prompts, indices_by_dp, prompts_by_dp, *, max_new_tokens, max_running_prompts,
                          eos_token_id, sampling_params, decode_progress_interval_s, cancel_flags) -> RolloutPayload:
-        dp = int(self.config.dp_size)
+        dp = int(self.config.rollout_dp)
         if eos_token_id is None:
             eos = ()
         elif isinstance(eos_token_id, int):
@@ -116,14 +116,14 @@ class ArenoEngine:
             raise ValueError("prompts must be non-empty")
         if max_running_prompts < 1:
             raise ValueError("max_running_prompts must be >= 1")
-        dp = int(self.config.dp_size)
+        dp = int(self.config.rollout_dp)
         payload = self._rollout_payload(
             prompts, split_list_by_dp(list(range(len(prompts))), dp), split_list_by_dp(prompts, dp),
             max_new_tokens=max_new_tokens, max_running_prompts=max_running_prompts, eos_token_id=eos_token_id,
             sampling_params=sampling_params, decode_progress_interval_s=decode_progress_interval_s,
             cancel_flags=cancel_flags)
         results = self.cluster.call(Op.INFER_ROLLOUT, payload)
-        return merge_rollouts_in_input_order(dp_rank0_results(results, self.config.tp_size, dp), len(prompts))
+        return merge_rollouts_in_input_order(dp_rank0_results(results, self.config.rollout_tp, dp), len(prompts))
 
     async def generate_rollout_async(self, prompts: list[list[int]], *, max_new_tokens: int, max_running_prompts: int,
                                      max_prompt_len: int | None = None, eos_token_id=None,
@@ -134,7 +134,7 @@ class ArenoEngine:
         joins that worker's running batch; only that row's TP-rank-0 result is awaited."""
         if not prompts:
             raise ValueError("prompts must be non-empty")
-        dp, tp = int(self.config.dp_size), int(self.config.tp_size)
+        dp, tp = int(self.config.rollout_dp), int(self.config.rollout_tp)
         owner = next(self._dp_cursor) % dp
         prompts_by_dp = [[] for _ in range(dp)]
         indices_by_dp = [[] for _ in range(dp)]
@@ -151,7 +151,7 @@ class ArenoEngine:
     def probe_rollout_cache(self, *, max_new_tokens: int, max_running_prompts: int, max_prompt_len: int) -> float:
         if min(max_running_prompts, max_prompt_len, max_new_tokens) < 1:
             raise ValueError("max_running_prompts, max_prompt_len and max_new_tokens must be >= 1")
-        dp = int(self.config.dp_size)
+        dp = int(self.config.rollout_dp)
         res = self.cluster.call(Op.PROBE_ROLLOUT_CACHE, CachePayload(max((max_running_prompts + dp - 1) // dp, 1),
                                                                      max_prompt_len + max_new_tokens))
         return max(float(r or 0.0) for r in res) if res else 0.0

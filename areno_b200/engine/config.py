@@ -164,6 +164,10 @@ class EngineConfig:
     model_path: str = ""
     tp_size: int = 1
     dp_size: int | None = None
+    # TP width of the rollout engine when it differs from training (None: same layout).  Requires the
+    # training layout to be pure data parallel (tp_size == 1): every rank then owns a full replica and
+    # cuts its rollout shard locally.
+    rollout_tp_size: int | None = None
     devices: list[int] | None = None
     dummy_load: bool = False
     max_running_seqs: int = 64
@@ -187,9 +191,23 @@ class EngineConfig:
         if self.dp_size * self.tp_size != world:
             raise ValueError(f"tp_size*dp_size = {self.tp_size * self.dp_size} does not match {world} devices")
         self.model.validate_tp(self.tp_size)
+        if self.rollout_tp_size is not None and self.rollout_tp_size != self.tp_size:
+            if self.tp_size != 1:
+                raise ValueError("rollout_tp_size requires tp_size == 1 for training")
+            if self.rollout_tp_size < 1 or world % self.rollout_tp_size != 0:
+                raise ValueError(f"world size {world} must be a multiple of rollout_tp_size={self.rollout_tp_size}")
+            self.model.validate_tp(self.rollout_tp_size)
         if self.runtime.kv_block_size % 16 != 0:
             raise ValueError("runtime.kv_block_size must be a multiple of 16")
 
     @property
     def world_size(self) -> int:
         return len(self.devices or [])
+
+    @property
+    def rollout_tp(self) -> int:
+        return int(self.rollout_tp_size or self.tp_size)
+
+    @property
+    def rollout_dp(self) -> int:
+        return self.world_size // self.rollout_tp

@@ -11,6 +11,7 @@ so "weight sync" after a step is free when rollout and training share a layout.
 
 from __future__ import annotations
 
+import os
 import time
 from typing import Any
 
@@ -55,6 +56,13 @@ class RankWorker:
         else:
             self.rollout_model = self.model
         self._rollout_stale = True
+        self.tp_comm = None
+        rctx = self.rollout_ctx
+        if rctx.tp_size > 1 and self.device.type == "cuda" and os.environ.get("ARENO_TP_COMM", "fused") != "nccl":
+            # peer-memory communicator for the fused GEMM -> all-reduce -> residual -> RMSNorm path
+            from ..parallel.symm import setup_tp_comm
+
+            self.tp_comm = setup_tp_comm(rctx, config.model.hidden_size, 512)
         self.trainer: TrainingManager | None = None
         self.infer: InferenceEngine | None = None
         self.roles = None

@@ -147,6 +147,10 @@ class DecoderLayer(nn.Module):
         self.post_norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device, cfg.norm_weight_offset)
         self.mlp = mlp if mlp is not None else GatedMLP(cfg.hidden_size, cfg.intermediate_size, cfg.hidden_act,
                                                         cfg.use_bias, dtype, device)
+        # both row-parallel outputs of this block feed an RMSNorm with residual
+        self.attn.o.defer_reduce = True
+        if isinstance(self.mlp, GatedMLP):
+            self.mlp.down.defer_reduce = True
 
     def forward(self, x, residual, positions, meta):
         if residual is None:

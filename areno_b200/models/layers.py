@@ -20,6 +20,10 @@ import torch.nn as nn
 from ..ops import activation, embedding as emb_ops, gemm, norm as norm_ops
 from ..parallel import collectives as coll
 from ..parallel.context import get_context
+from ..parallel.symm import TpPartial, get_tp_comm
+
+
+FUSED_TP_MAX_ROWS = 512
 
 
 def _param(shape, dtype, device) -> nn.Parameter:
@@ -36,6 +40,11 @@ class RMSNorm(nn.Module):
             self.weight.tp_replicated_grad = True
 
     def forward(self, x, residual=None):
+        if isinstance(x, TpPartial):
+            # x is a row-parallel partial still spread over the TP group's inboxes: reduce it, add the
+            # residual stream and normalise in one kernel
+            y, h = x.comm.reduce_rmsnorm(x, residual, self.weight, self.eps, self.offset)
+            return (y, h) if residual is not None else y
         return norm_ops.rmsnorm(x, self.weight, self.eps, residual=residual, w_offset=self.offset)
 
 
@@ -129,6 +138,9 @@ class RowParallelLinear(nn.Module):
         self.in_local = in_features // ctx.tp_size
         self.out_features = out_features
         self.reduce_output = reduce_output
+        # set by owners whose next op is an RMSNorm with residual: lets inference hand the un-reduced
+        # partial to the fused reduce + residual + norm kernel instead of calling an all-reduce
+        self.defer_reduce = False
         self.weight = _param((out_features, self.in_local), dtype, device)
         self.weight.tp_shard = ("row", None)
         self.bias = _param((out_features,), dtype, device) if bias else None
@@ -139,6 +151,13 @@ class RowParallelLinear(nn.Module):
         ctx = get_context()
         if ctx.tp_size == 1:
             return gemm.linear(x, self.weight, self.bias)
+        if self.defer_reduce and self.bias is None and x.is_cuda and not torch.is_grad_enabled():
+            comm = get_tp_comm(ctx)
+            x2 = x.reshape(-1, x.shape[-1])
+            # decode-sized batches only: per-thread 64-byte peer stores from the epilogue stop paying
+            # off once the output is large (prefill), where the library all-reduce is used instead
+            if comm is not None and comm.hidden == self.out_features and x2.shape[0] <= min(comm.max_rows, FUSED_TP_MAX_ROWS):
+                return comm.push_linear(x2, self.weight)
         y = gemm.linear(x, self.weight, None)
         if self.reduce_output:
             y = coll.reduce_from_tp(y)

@@ -53,7 +53,14 @@ def parse_args():
     ap.add_argument("--small", action="store_true", help="tiny model / short rollout (functional check only)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--adam-8bit", action="store_true")
+    ap.add_argument("--rollout-tp", type=int, default=0,
+                    help="TP width of the rollout engine (0: pick automatically; 1: one replica per GPU)")
     return ap.parse_args()
+
+
+def pick_rollout_tp(world: int) -> int:
+    """Rollout layout for the benchmark model (28 query heads, 4 KV heads: TP must divide 4)."""
+    return 1
 
 
 # ------------------------------------------------------------------------- synthetic data
@@ -177,7 +184,8 @@ def run_ours(args):
         raise SystemExit(f"--gpus {args.gpus} does not match WORLD_SIZE {world}")
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
-    ctx = init_parallel(rank, world, tp_size=1, device=device)
+    rollout_tp = args.rollout_tp or pick_rollout_tp(world)
+    ctx = init_parallel(rank, world, tp_size=1, device=device, rollout_tp_size=rollout_tp)
 
     model_kw = dict(MODEL)
     new_tokens, pmin, pmax, n_prompts = NEW_TOKENS, PROMPT_MIN, PROMPT_MAX, PROMPTS_PER_GPU
@@ -187,7 +195,7 @@ def run_ours(args):
         new_tokens, pmin, pmax = 64, 32, 96
     mcfg = ModelConfig(**model_kw)
     cfg = EngineConfig(
-        model=mcfg, tp_size=1, dp_size=world, devices=list(range(world)), dummy_load=True,
+        model=mcfg, tp_size=1, dp_size=world, rollout_tp_size=rollout_tp, devices=list(range(world)), dummy_load=True,
         optimizer=OptimizerConfig(lr=1e-6, betas=(0.9, 0.999), weight_decay=0.01, grad_clip_norm=1.0,
                                   adam_8bit=args.adam_8bit),
         runtime=RuntimeConfig(activation_checkpointing=True, max_model_len=(pmax + new_tokens + 63) // 64 * 64),
@@ -203,7 +211,8 @@ def run_ours(args):
         prompts = make_prompts(step, rank, mcfg.vocab_size, n_prompts, pmin, pmax)
         rows = [p for p in prompts for _ in range(GROUP)]
         t1 = time.time()
-        out = worker.rollout(rows, params, eos_token_ids=(), max_new_tokens=new_tokens, progress_interval_s=0.0)
+        out = worker.rollout(rows, params, eos_token_ids=(), max_new_tokens=new_tokens, progress_interval_s=0.0,
+                             gather_tp=True)
         t2 = time.time()
         rewards = np.array([hash_reward(t) for t in out.tokens])
         adv = group_advantages(rewards, GROUP)
@@ -271,8 +280,9 @@ def run_ours(args):
                 "model": "Qwen2.5-7B-shaped" if not args.small else "small-debug", "global_batch": n_prompts * GROUP * world,
                 "prompts_per_gpu": n_prompts, "group": GROUP, "prompt_len": [pmin, pmax], "new_tokens": new_tokens,
                 "seq_len": pmax + new_tokens, "micro_batch_tokens": MICRO_TOKENS,
-                "parallelism": f"rollout dp{world} x tp1 (paged bf16 KV, CUDA-graph decode), train dp{world} "
-                               "sharded grads+optimizer, weight sync in place (shared buffers)",
+                "parallelism": f"rollout dp{world // rollout_tp} x tp{rollout_tp} (paged bf16 KV, CUDA-graph decode), "
+                               f"train dp{world} sharded grads+optimizer, weight sync: "
+                               + ("in place (shared buffers)" if rollout_tp == 1 else "local reshard of the DP replica"),
                 "tokens_counted": "prompt+response tokens per sequence, once per step",
                 "l2": "inputs larger than L2 (15 GB of weights streamed every decode step / micro-batch)",
                 "wall_s_timed_region": wall,
@@ -280,8 +290,14 @@ def run_ours(args):
         }
         print(json.dumps(result), flush=True)
     if world > 1:
+        # Leave without tearing the communicators down: captured decode graphs still reference them, and
+        # destroying a communicator in that state can block forever.  The barrier keeps ranks together
+        # until rank 0 has printed.
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def run_e2e(args, worker, mcfg, params, rank, world, device, n_prompts, pmin, pmax, new_tokens):
