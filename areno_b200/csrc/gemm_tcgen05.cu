@@ -41,7 +41,65 @@ struct GemmParams {
   // over NVLink).  Used by row-parallel TP linears to deliver their partial to every rank.
   int n_extra;
   void* extra[7];
+  // Grouped (mixture-of-experts) modes, driven by the device-side plan of moe.cu:
+  //   1: every 128-row M tile belongs to one expert (tile_expert[m_tile], -1 = unused tile); the B
+  //      operand of expert e starts b_group_rows further along B's outer TMA coordinate.
+  //   2: work item = (expert, output tile); the K range of expert e is rows
+  //      [expert_rows[2e], expert_rows[2e] + expert_rows[2e+1]) of A and B (multiples of 128) and
+  //      its output starts c_group_stride elements further into C (per-expert weight gradients).
+  int group_mode;
+  const int* tile_expert;
+  const int* expert_rows;
+  long long b_group_rows;
+  long long c_group_stride;
+  int num_groups;
 };
+
+struct WorkItem {
+  int m0, n0, kb_lo, kb_hi, split;
+  int b_off;        // added to B's outer TMA coordinate
+  long long c_off;  // elements added to the C pointer
+  bool skip;        // nothing to do for any role
+  bool zero;        // no K range: the epilogue stores zeros, the other roles skip
+};
+
+template <int BN>
+__device__ __forceinline__ WorkItem decode_work(const GemmParams& p, int work, int num_kb) {
+  WorkItem w;
+  w.b_off = 0;
+  w.c_off = 0;
+  w.skip = false;
+  w.zero = false;
+  if (p.group_mode == 2) {
+    const int tiles = p.tiles_m * p.tiles_n;
+    const int e = work / tiles;
+    const int tile = work - e * tiles;
+    w.m0 = (tile % p.tiles_m) * kBM;
+    w.n0 = (tile / p.tiles_m) * BN;
+    w.split = 0;
+    w.kb_lo = p.expert_rows[2 * e] / kBK;
+    w.kb_hi = w.kb_lo + p.expert_rows[2 * e + 1] / kBK;
+    w.c_off = (long long)e * p.c_group_stride;
+    if (w.kb_hi == w.kb_lo) {
+      if (p.epi == 3) w.skip = true;  // accumulate: adding nothing
+      else w.zero = true;
+    }
+    return w;
+  }
+  const int tile = work / p.splits;
+  w.split = work - tile * p.splits;
+  const int m_tile = tile % p.tiles_m;
+  w.m0 = m_tile * kBM;
+  w.n0 = (tile / p.tiles_m) * BN;
+  w.kb_lo = w.split * p.kb_per_split;
+  w.kb_hi = min(num_kb, w.kb_lo + p.kb_per_split);
+  if (p.group_mode == 1) {
+    const int e = p.tile_expert[m_tile];
+    if (e < 0) w.skip = true;
+    else w.b_off = (int)(e * p.b_group_rows);
+  }
+  return w;
+}
 
 template <int BN, int STAGES>
 struct GemmSmem {
@@ -153,7 +211,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const uint32_t tmem_base = *tmem_slot;
 
   const int num_kb = (p.K + kBK - 1) / kBK;
-  const int num_work = p.tiles_m * p.tiles_n * p.splits;
+  const int num_work = p.tiles_m * p.tiles_n * p.splits * (p.group_mode == 2 ? p.num_groups : 1);
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -161,12 +219,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     uint32_t phase = 0;
     bool ok = true;
     for (int work = blockIdx.x; work < num_work && ok; work += gridDim.x) {
-      const int tile = work / p.splits;
-      const int split = work - tile * p.splits;
-      const int m0 = (tile % p.tiles_m) * kBM;
-      const int n0 = (tile / p.tiles_m) * BN;
-      const int kb_lo = split * p.kb_per_split;
-      const int kb_hi = min(num_kb, kb_lo + p.kb_per_split);
+      const WorkItem wi = decode_work<BN>(p, work, num_kb);
+      if (wi.skip || wi.zero) continue;
+      const int m0 = wi.m0, n0 = wi.n0, kb_lo = wi.kb_lo, kb_hi = wi.kb_hi;
       for (int kb = kb_lo; kb < kb_hi; ++kb) {
         if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
         if (lane == 0) {
@@ -184,9 +239,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           if constexpr (B_MN) {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
-              tma_load_2d(b_dst + j * 8192, &tma_b, &full_bar[stage], n0 + j * 64, k0);
+              tma_load_2d(b_dst + j * 8192, &tma_b, &full_bar[stage], n0 + j * 64, k0 + wi.b_off);
           } else {
-            tma_load_2d(b_dst, &tma_b, &full_bar[stage], k0, n0);
+            tma_load_2d(b_dst, &tma_b, &full_bar[stage], k0, n0 + wi.b_off);
           }
         }
         __syncwarp();
@@ -206,9 +261,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     int acc = 0;
     bool ok = true;
     for (int work = blockIdx.x; work < num_work && ok; work += gridDim.x) {
-      const int split = work % p.splits;
-      const int kb_lo = split * p.kb_per_split;
-      const int kb_hi = min(num_kb, kb_lo + p.kb_per_split);
+      const WorkItem wi = decode_work<BN>(p, work, num_kb);
+      if (wi.skip || wi.zero) continue;
+      const int kb_lo = wi.kb_lo, kb_hi = wi.kb_hi;
       if (!mbar_wait(&tempty_bar[acc], acc_phase[acc] ^ 1u, abort_flag, p.status, 2)) { ok = false; break; }
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
@@ -244,10 +299,26 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     int acc = 0;
     bool ok = true;
     for (int work = blockIdx.x; work < num_work && ok; work += gridDim.x) {
-      const int tile = work / p.splits;
-      const int split = work - tile * p.splits;
-      const int m0 = (tile % p.tiles_m) * kBM;
-      const int n0 = (tile / p.tiles_m) * BN;
+      const WorkItem wi = decode_work<BN>(p, work, num_kb);
+      if (wi.skip) continue;
+      const int split = wi.split, m0 = wi.m0, n0 = wi.n0;
+      if (wi.zero) {
+        // an expert without rows: its gradient tile is zero (no accumulator was produced)
+        const int zrow = m0 + q * 32 + lane;
+        uint32_t z[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) z[j] = 0u;
+        for (int c = 0; c < BN && zrow < p.M; c += 32) {
+          const int col = n0 + c;
+          const int ncols = min(32, p.N - col);
+          if (ncols <= 0) break;
+          if (p.epi <= 1)
+            store_row_bf16(reinterpret_cast<__nv_bfloat16*>(p.C) + wi.c_off + (long long)zrow * p.ldc + col, z, ncols, nullptr);
+          else
+            store_row_f32(reinterpret_cast<float*>(p.C) + wi.c_off + (long long)zrow * p.ldc + col, z, ncols, false);
+        }
+        continue;
+      }
       if (!mbar_wait(&tfull_bar[acc], acc_phase[acc], abort_flag, p.status, 4)) { ok = false; break; }
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
@@ -262,7 +333,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         const int ncols = min(32, p.N - col);
         if (row < p.M && ncols > 0) {
           if (p.epi == 0 || p.epi == 1) {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col;
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + wi.c_off + (long long)row * p.ldc + col;
             const __nv_bfloat16* bias =
                 p.epi == 1 ? reinterpret_cast<const __nv_bfloat16*>(p.bias) + col : nullptr;
             store_row_bf16(dst, r, ncols, bias);
@@ -270,7 +341,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
               store_row_bf16(reinterpret_cast<__nv_bfloat16*>(p.extra[e]) + (long long)row * p.ldc + col, r, ncols,
                              bias);
           } else {
-            float* dst = reinterpret_cast<float*>(p.C) + split * p.split_stride + (long long)row * p.ldc + col;
+            float* dst = reinterpret_cast<float*>(p.C) + wi.c_off + split * p.split_stride + (long long)row * p.ldc + col;
             store_row_f32(dst, r, ncols, p.epi == 3);
           }
         }
@@ -413,10 +484,19 @@ extern "C" long long areno_gemm_workspace_bytes(int M, int N, int K) {
   return 16ll * M * N * 4;  // at most 16 splits
 }
 
+struct GroupArgs {
+  int mode;
+  const int* tile_expert;
+  const int* expert_rows;
+  long long b_group_rows;
+  long long c_group_stride;
+  int num_groups;
+};
+
 static int gemm_bf16_impl(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
                           long long lda, long long ldb, long long ldc, int a_mn, int b_mn, int epi, int bn,
                           void* workspace, long long workspace_bytes, int* status, cudaStream_t stream,
-                          void* const* extra, int n_extra) {
+                          void* const* extra, int n_extra, const GroupArgs* group = nullptr, int b_groups = 1) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (n_extra < 0 || n_extra > 7 || (n_extra > 0 && epi > 1)) return -3;
   for (int e = 0; e < n_extra; ++e)
@@ -445,8 +525,10 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, const void* bia
   if (a_mn) rc = make_tensor_map_2d_bf16(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, 64, 64);
   else rc = make_tensor_map_2d_bf16(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, 64, kBM);
   if (rc != 0) return rc;
-  if (b_mn) rc = make_tensor_map_2d_bf16(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, 64);
-  else rc = make_tensor_map_2d_bf16(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, 64, (uint32_t)bn);
+  // grouped mode 1: B holds `b_groups` experts stacked along its outer dimension
+  const uint64_t b_mult = (group != nullptr && group->mode == 1) ? (uint64_t)b_groups : 1u;
+  if (b_mn) rc = make_tensor_map_2d_bf16(&tb, B, (uint64_t)N, (uint64_t)K * b_mult, (uint64_t)ldb * 2, 64, 64);
+  else rc = make_tensor_map_2d_bf16(&tb, B, (uint64_t)K, (uint64_t)N * b_mult, (uint64_t)ldb * 2, 64, (uint32_t)bn);
   if (rc != 0) return rc;
   GemmParams p;
   p.M = M; p.N = N; p.K = K;
@@ -459,6 +541,21 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, const void* bia
   p.split_stride = 0;
   p.n_extra = n_extra;
   for (int e = 0; e < 7; ++e) p.extra[e] = e < n_extra ? extra[e] : nullptr;
+  p.group_mode = 0;
+  p.tile_expert = nullptr;
+  p.expert_rows = nullptr;
+  p.b_group_rows = 0;
+  p.c_group_stride = 0;
+  p.num_groups = 1;
+  if (group != nullptr && group->mode != 0) {
+    p.group_mode = group->mode;
+    p.tile_expert = group->tile_expert;
+    p.expert_rows = group->expert_rows;
+    p.b_group_rows = group->b_group_rows;
+    p.c_group_stride = group->c_group_stride;
+    p.num_groups = group->num_groups;
+    workspace = nullptr;  // no split-K in grouped modes
+  }
   // Split-K for skinny problems (decode): too few output tiles to fill the GPU, long K.
   const int num_kb = (K + kBK - 1) / kBK;
   const int tiles = p.tiles_m * p.tiles_n;
@@ -518,4 +615,30 @@ extern "C" int areno_gemm_bf16_push(const void* A, const void* B, void* C, const
                                     void* workspace, long long workspace_bytes, int* status, cudaStream_t stream) {
   return gemm_bf16_impl(A, B, C, bias, M, N, K, lda, ldb, ldc, 0, 0, bias != nullptr ? 1 : 0, 0, workspace,
                         workspace_bytes, status, stream, extra, n_extra);
+}
+
+// ---- grouped (mixture-of-experts) entry points; plans come from areno_moe_align -------------------
+// Forward / input-gradient: C[P, N] = A[P, K] * B_e, rows grouped by expert in 128-row tiles.
+//   b_mn = 0: B is [E, N, K] (K contiguous)  -> C = A * B_e^T          (forward)
+//   b_mn = 1: B is [E, K, N] (N contiguous)  -> C = A * B_e            (input gradient of the above)
+extern "C" int areno_grouped_gemm_bf16(const void* A, const void* B, void* C, int P, int N, int K, int E, int b_mn,
+                                       const int* tile_expert, int* status, cudaStream_t stream) {
+  if (P <= 0) return 0;
+  if (P % kBM != 0 || E < 1) return -3;
+  GroupArgs g{1, tile_expert, nullptr, b_mn ? (long long)K : (long long)N, 0, E};
+  // B flattened over experts: [E*N, K] (K-major) or [E*K, N] (MN-major)
+  return gemm_bf16_impl(A, B, C, nullptr, P, N, K, K, b_mn ? N : K, N, 0, b_mn, 0, 0, nullptr, 0, status, stream, nullptr,
+                        0, &g, E);
+}
+
+// Weight gradient: dW[e][N, K] (+)= dY_e^T[N, rows_e] * X_e[rows_e, K]; dY is [P, N], X is [P, K].
+// out_f32_accumulate = 1: fp32 accumulate into dW (main-grad buffers); 0: bf16 store.
+extern "C" int areno_grouped_wgrad_bf16(const void* dY, const void* X, void* dW, int P, int N, int K, int E,
+                                        const int* expert_rows, int out_f32_accumulate, int* status,
+                                        cudaStream_t stream) {
+  if (P <= 0 || E < 1) return 0;
+  if (P % kBM != 0) return -3;
+  GroupArgs g{2, nullptr, expert_rows, 0, (long long)N * K, E};
+  return gemm_bf16_impl(dY, X, dW, nullptr, N, K, P, N, K, K, 1, 1, out_f32_accumulate ? 3 : 0, 0, nullptr, 0, status,
+                        stream, nullptr, 0, &g, E);
 }

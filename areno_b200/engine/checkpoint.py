@@ -376,7 +376,9 @@ def hf_config_from_model_config(c) -> dict:
     }
     if c.num_experts:
         out.update(num_experts=c.num_experts, num_experts_per_tok=c.num_experts_per_tok,
-                   moe_intermediate_size=c.moe_intermediate_size, norm_topk_prob=c.norm_topk_prob)
+                   moe_intermediate_size=c.moe_intermediate_size, norm_topk_prob=c.norm_topk_prob,
+                   decoder_sparse_step=(c.extra or {}).get("decoder_sparse_step", 1),
+                   mlp_only_layers=(c.extra or {}).get("mlp_only_layers", []))
     return out
 
 

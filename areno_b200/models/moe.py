@@ -1,0 +1,102 @@
+"""Sparse mixture-of-experts decoder (Qwen3-MoE family): softmax top-k router with fp32 gate, experts
+sharded over the TP group (every rank sees all tokens and serves the routes that hit its experts,
+then the partial outputs are summed over the group), grouped tcgen05 GEMMs over expert-sorted rows.
+
+Structure of ``areno/models/qwen3/model.py:75-231`` in the reference; the per-expert cuBLAS loop,
+the host sync for offsets and the Triton inference path are replaced by the device-side plan and
+the grouped GEMM of ``ops/moe.py``, used for training and inference alike.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from ..engine.config import ModelConfig
+from ..ops import activation, moe as moe_ops
+from ..parallel import collectives as coll
+from ..parallel.context import get_context
+from .dense import DecoderLayer, DenseCausalLM
+from .layers import GatedMLP, _param
+
+
+class TopKRouter(nn.Module):
+    """``logits = x @ gate^T`` in fp32 (the gate is kept in fp32 and replicated over TP)."""
+
+    def __init__(self, cfg: ModelConfig, device):
+        super().__init__()
+        self.k = cfg.num_experts_per_tok
+        self.renorm = cfg.norm_topk_prob
+        self.weight = _param((cfg.num_experts, cfg.hidden_size), torch.float32, device)
+        self.weight.tp_replicated_grad = True
+
+    def forward(self, x):
+        logits = torch.nn.functional.linear(x.float(), self.weight)
+        return moe_ops.topk_softmax(logits, self.k, self.renorm)
+
+
+class Experts(nn.Module):
+    def __init__(self, cfg: ModelConfig, dtype, device):
+        super().__init__()
+        ctx = get_context()
+        e = cfg.num_experts
+        assert e % ctx.tp_size == 0, "num_experts must be divisible by the TP size"
+        self.e_local = e // ctx.tp_size
+        self.e_lo = ctx.tp_rank * self.e_local
+        self.inter = cfg.moe_intermediate_size
+        self.act = cfg.hidden_act
+        self.gate_up = _param((self.e_local, 2 * self.inter, cfg.hidden_size), dtype, device)
+        self.down = _param((self.e_local, cfg.hidden_size, self.inter), dtype, device)
+        # dim-0 (expert) sharding: same slicing as a column-parallel weight
+        self.gate_up.tp_shard = ("col", None)
+        self.down.tp_shard = ("col", None)
+
+    def forward(self, x, weights, ids):
+        plan = moe_ops.align(ids, self.e_lo, self.e_local)
+        xs = moe_ops.permute(x, plan)
+        gu = moe_ops.grouped_linear(xs, self.gate_up, plan)
+        a = activation.silu_and_mul(gu) if self.act == "silu" else activation.gelu_tanh_and_mul(gu)
+        ys = moe_ops.grouped_linear(a, self.down, plan)
+        out = moe_ops.combine(ys, plan, weights)
+        return coll.reduce_from_tp(out), plan
+
+
+class SparseMoeBlock(nn.Module):
+    def __init__(self, cfg: ModelConfig, dtype, device):
+        super().__init__()
+        self.router = TopKRouter(cfg, device)
+        self.experts = Experts(cfg, dtype, device)
+        self.shared = None
+        if cfg.shared_expert_intermediate_size:
+            self.shared = GatedMLP(cfg.hidden_size, cfg.shared_expert_intermediate_size, cfg.hidden_act, False, dtype,
+                                   device)
+        self.last_counts = None  # tokens per local expert of the latest forward (device tensor, for metrics)
+
+    def forward(self, x):
+        weights, ids = self.router(x)
+        out, plan = self.experts(x, weights, ids)
+        self.last_counts = plan.counts
+        if self.shared is not None:
+            out = out + self.shared(x)
+        return out
+
+
+def is_sparse_layer(cfg: ModelConfig, i: int) -> bool:
+    if not cfg.num_experts:
+        return False
+    extra = cfg.extra or {}
+    if i in set(extra.get("mlp_only_layers") or []):
+        return False
+    step = int(extra.get("decoder_sparse_step", 1) or 1)
+    return (i + 1) % step == 0
+
+
+class MoeCausalLM(DenseCausalLM):
+    def _make_layer(self, i, dtype, device):
+        cfg = self.cfg
+        mlp = SparseMoeBlock(cfg, dtype, device) if is_sparse_layer(cfg, i) else None
+        return DecoderLayer(cfg, i, dtype, device, mlp=mlp)
+
+    def finalize_router_expert_bias(self, tp_group=None, dp_group=None) -> None:
+        """Softmax routers carry no selection bias: nothing to update after a step."""
+        return None
