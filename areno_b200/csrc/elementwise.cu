@@ -634,6 +634,75 @@ extern "C" int areno_headnorm_bwd(const void* dy, long long dy_stride, const voi
 }
 
 // ---------------------------------------------------------------------------------
+// Fold of split-K partials fused with the residual add and the RMSNorm that follows a
+// row-parallel projection in a decoder block:
+//   h = residual + sum_s ws[s];  y = h * rsqrt(mean h^2 + eps) * (w + w_offset)
+// ws: fp32 [splits, rows, H] as left by areno_gemm_bf16_partials.  One block per row.
+// ---------------------------------------------------------------------------------
+template <int THREADS, int VPT>
+__global__ void __launch_bounds__(THREADS)
+splitk_residual_rmsnorm_kernel(const float* __restrict__ ws, int splits, long long split_stride,
+                               const __nv_bfloat16* __restrict__ residual, const void* __restrict__ w, int wf32,
+                               float w_offset, __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ h_out,
+                               int rows, int H, float eps) {
+  __shared__ float red[32];
+  const int nvec = H >> 3;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const size_t base = (size_t)row * H;
+    float v[VPT][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int vi = threadIdx.x + i * THREADS;
+      if (vi < nvec) {
+        if (residual != nullptr) {
+          load8(residual + base + vi * 8, v[i]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[i][j] = 0.f;
+        }
+        for (int s = 0; s < splits; ++s) {
+          const float* p = ws + s * split_stride + base + vi * 8;
+          const float4 a = *reinterpret_cast<const float4*>(p);
+          const float4 b = *reinterpret_cast<const float4*>(p + 4);
+          v[i][0] += a.x; v[i][1] += a.y; v[i][2] += a.z; v[i][3] += a.w;
+          v[i][4] += b.x; v[i][5] += b.y; v[i][6] += b.z; v[i][7] += b.w;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i][j] = __bfloat162float(__float2bfloat16_rn(v[i][j]));
+        if (h_out != nullptr) store8(h_out + base + vi * 8, v[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += v[i][j] * v[i][j];
+      }
+    }
+    const float tot = block_sum<THREADS>(ss, red);
+    const float inv = rsqrtf(tot / (float)H + eps);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int vi = threadIdx.x + i * THREADS;
+      if (vi < nvec) {
+        float wv[8], o[8];
+        load8w(w, wf32, vi * 8, wv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = v[i][j] * inv * (wv[j] + w_offset);
+        store8(y + base + vi * 8, o);
+      }
+    }
+  }
+}
+
+extern "C" int areno_splitk_residual_rmsnorm(const float* ws, int splits, long long split_stride, const void* residual,
+                                             const void* w, int wf32, float w_offset, void* y, void* h_out,
+                                             long long rows, int H, float eps, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (H % 8 != 0 || splits < 1 || w == nullptr) return -3;
+  const int grid = (int)(rows < 148 * 32 ? rows : 148 * 32);
+  RMS_DISPATCH(splitk_residual_rmsnorm_kernel, H, ws, splits, split_stride, (const __nv_bfloat16*)residual, w, wf32,
+               w_offset, (__nv_bfloat16*)y, (__nv_bfloat16*)h_out, (int)rows, H, eps);
+  return (int)cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------
 // RMSNorm backward with library-owned scratch (declared in no_alloc.h).
 // The partial-dW rows go to a fixed device array instead of a caller buffer, so the call
 // needs no allocator.  `g_rmsnorm_bwd_scratch` below is the host-side handle of that array,

@@ -192,8 +192,10 @@ class InferenceEngine:
         self.active.zero_()
         self.finish.zero_()
         self.calls += 1
-        self.call_seed = params.seed if params.seed is not None else (self.seed * 1000003 + self.calls)
-        self._graph_key = (params.temperature, params.top_k, params.top_p, params.min_new_tokens, self.call_seed)
+        # The per-call seed travels in the high word of each row's random-stream id (device memory), not
+        # as a kernel argument: captured decode graphs stay valid from one call to the next.
+        self.call_seed = (params.seed if params.seed is not None else (self.seed * 1000003 + self.calls)) & 0x7FFFFFFF
+        self._graph_key = (params.temperature, params.top_k, params.top_p, params.min_new_tokens)
         self.step_count = 0
         self.decode_tokens = 0
 
@@ -342,7 +344,8 @@ class InferenceEngine:
             return
         uid = torch.tensor(fin_uid, dtype=torch.int64, device=dev)
         slots_t = torch.tensor(fin_slots, dtype=torch.int32, device=dev)
-        stream = torch.tensor(fin_stream, dtype=torch.int64, device=dev)
+        stream = torch.tensor([(self.call_seed << 32) | (int(x) & 0xFFFFFFFF) for x in fin_stream], dtype=torch.int64,
+                              device=dev)
         self.row_uid[slots_t.long()] = stream
         self.uid32[slots_t.long()] = (uid & 0x7FFFFFFF).to(torch.int32)
         zero_gen = torch.zeros(n, dtype=torch.int32, device=dev)
@@ -385,7 +388,7 @@ class InferenceEngine:
         view = logits[:, :valid]
         if ctx.tp_size == 1:
             return sampling_ops.sample(view, p.temperature, p.top_k, p.top_p, cls=self.cls, gen_count=gen_count,
-                                       min_new=p.min_new_tokens, seed=self.call_seed, row_uid=row_uid,
+                                       min_new=p.min_new_tokens, seed=self.seed, row_uid=row_uid,
                                        out_token=out_token, out_logprob=out_logprob)
         if (p.top_k > 0 or p.top_p < 1.0) and p.temperature > 0:
             # truncated sampling needs the whole distribution on one rank
@@ -393,11 +396,11 @@ class InferenceEngine:
             dist.all_gather_into_tensor(full, view.contiguous(), group=ctx.tp_group)
             full = full.view(ctx.tp_size, *view.shape).permute(1, 0, 2).reshape(view.shape[0], -1)[:, : self.vocab].contiguous()
             return sampling_ops.sample(full, p.temperature, p.top_k, p.top_p, cls=self.cls, gen_count=gen_count,
-                                       min_new=p.min_new_tokens, seed=self.call_seed, row_uid=row_uid,
+                                       min_new=p.min_new_tokens, seed=self.seed, row_uid=row_uid,
                                        out_token=out_token, out_logprob=out_logprob)
         part = torch.empty((view.shape[0], 6), dtype=torch.float32, device=view.device)
         sampling_ops.sample(view, p.temperature, p.top_k, p.top_p, cls=self.cls, gen_count=gen_count,
-                            min_new=p.min_new_tokens, seed=self.call_seed, row_uid=row_uid,
+                            min_new=p.min_new_tokens, seed=self.seed, row_uid=row_uid,
                             vocab_start=lm.vocab_start, part=part)
         parts = torch.empty((ctx.tp_size * part.shape[0], 6), dtype=torch.float32, device=view.device)
         dist.all_gather_into_tensor(parts, part, group=ctx.tp_group)

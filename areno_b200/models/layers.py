@@ -40,6 +40,10 @@ class RMSNorm(nn.Module):
             self.weight.tp_replicated_grad = True
 
     def forward(self, x, residual=None):
+        if isinstance(x, gemm.SplitKPartial):
+            # a decode-sized row-parallel GEMM left its split-K partials for us: fold, add, normalise
+            y, h = norm_ops.splitk_residual_rmsnorm(x, residual, self.weight, self.eps, self.offset)
+            return (y, h) if residual is not None else y
         if isinstance(x, TpPartial):
             # x is a row-parallel partial still spread over the TP group's inboxes: reduce it, add the
             # residual stream and normalise in one kernel
@@ -150,6 +154,9 @@ class RowParallelLinear(nn.Module):
     def forward(self, x):
         ctx = get_context()
         if ctx.tp_size == 1:
+            if (self.defer_reduce and self.bias is None and x.is_cuda and not torch.is_grad_enabled()
+                    and x.dim() == 2 and x.shape[0] <= 128 and self.weight.dtype == torch.bfloat16):
+                return gemm.gemm_partials(x, self.weight)
             return gemm.linear(x, self.weight, self.bias)
         if self.defer_reduce and self.bias is None and x.is_cuda and not torch.is_grad_enabled():
             comm = get_tp_comm(ctx)

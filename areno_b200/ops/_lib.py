@@ -26,6 +26,8 @@ _SIG_CODES = {
 _SIGNATURES: dict[str, str] = {
     "areno_gemm_bf16": "ppppiiillliiiiplpp",
     "areno_rmsnorm_fwd": "pppifppplifp",
+    "areno_gemm_bf16_partials": "pppiiilllplppp",
+    "areno_splitk_residual_rmsnorm": "pilppifpplifp",
     "areno_rmsnorm_bwd_blocks": "l",
     "areno_rmsnorm_bwd": "pppifpppppilip",
     "areno_gated_act_fwd": "ppliip",

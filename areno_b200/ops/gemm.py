@@ -11,6 +11,9 @@ reference (a cuBLAS wrapper there; a hand-written TMA + tcgen05 + TMEM kernel he
 
 from __future__ import annotations
 
+import ctypes
+from dataclasses import dataclass
+
 import torch
 
 from . import _lib
@@ -99,6 +102,36 @@ def gemm(
 
 
 _WORKSPACES: dict[int, torch.Tensor] = {}
+
+
+@dataclass
+class SplitKPartial:
+    """A skinny GEMM whose split-K partials (fp32 ``[splits, rows, n]``) still sit in the shared
+    workspace.  Must be consumed (``ops.norm.splitk_residual_rmsnorm``) before the next GEMM on the
+    same device, which reuses that workspace."""
+
+    ws: torch.Tensor
+    splits: int
+    rows: int
+    n: int
+
+
+def gemm_partials(x: torch.Tensor, weight: torch.Tensor):
+    """``x [rows, K] @ weight[N, K]^T`` for decode-sized ``rows``: returns a ``SplitKPartial`` when the
+    kernel split K (the fold is left to a fused consumer) or the finished bf16 tensor otherwise."""
+    rows, k = x.shape
+    n = weight.shape[0]
+    if not x.is_contiguous():
+        x = x.contiguous()
+    out = torch.empty((rows, n), dtype=torch.bfloat16, device=x.device)
+    ws = _workspace(x.device, 16 * rows * n * 4)
+    splits = ctypes.c_int(1)
+    _lib.call("areno_gemm_bf16_partials", x.data_ptr(), weight.data_ptr(), out.data_ptr(), rows, n, k, x.stride(0),
+              weight.stride(0), n, ws.data_ptr(), ws.numel(), ctypes.byref(splits), _lib.status_buffer(x.device).data_ptr(),
+              _lib.stream())
+    if splits.value <= 1:
+        return out
+    return SplitKPartial(ws, int(splits.value), rows, n)
 
 
 def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:

@@ -101,6 +101,21 @@ class _RMSNorm(torch.autograd.Function):
         return dxv, dw, (dxv if ctx.has_res else None), None, None
 
 
+def splitk_residual_rmsnorm(part, residual, weight, eps: float = 1e-6, w_offset: float = 0.0):
+    """Fold the split-K partials of a skinny GEMM, add the residual stream and apply RMSNorm in one
+    kernel (inference only).  Returns ``(y, h)`` with ``h = residual + sum of partials``."""
+    rows, n = part.rows, part.n
+    dev = part.ws.device
+    h = torch.empty((rows, n), dtype=torch.bfloat16, device=dev)
+    y = torch.empty_like(h)
+    if residual is not None and not residual.is_contiguous():
+        residual = residual.contiguous()
+    _lib.call("areno_splitk_residual_rmsnorm", part.ws.data_ptr(), part.splits, rows * n, _lib.ptr(residual),
+              weight.data_ptr(), int(weight.dtype == torch.float32), float(w_offset), y.data_ptr(), h.data_ptr(), rows, n,
+              float(eps), _lib.stream())
+    return y, h
+
+
 def rmsnorm(x, weight, eps: float = 1e-6, residual=None, w_offset: float = 0.0):
     """``y = h · rsqrt(mean h² + eps) · (w + w_offset)`` with ``h = x (+ residual)``.
 

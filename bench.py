@@ -221,6 +221,8 @@ def run_ours(args):
         stats = worker.train(packs)
         torch.cuda.synchronize()
         t4 = time.time()
+        if os.environ.get("ARENO_BENCH_VERBOSE"):
+            print(f"[bench] rank {rank} step {step}: rollout {t2 - t1:.3f}s train {t4 - t3:.3f}s", file=sys.stderr, flush=True)
         phase["rollout_s"] += t2 - t1
         phase["train_s"] += t4 - t3
         phase["host_s"] += (t1 - t0) + (t3 - t2)

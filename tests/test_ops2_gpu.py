@@ -235,3 +235,25 @@ def test_policy_loss_tokens(kl_type, use_old):
     (g,) = torch.autograd.grad(tot, lp)
     (gr,) = torch.autograd.grad(totr, lpr)
     assert _rel_err(g, gr) < 1e-4
+
+
+@pytest.mark.parametrize("rows,n,k", [(64, 3584, 3584), (128, 3584, 18944), (1, 3584, 3584), (64, 1024, 256)])
+def test_splitk_partials_residual_rmsnorm(rows, n, k):
+    """Skinny GEMM leaving split-K partials + fused fold/residual/RMSNorm == GEMM, add, norm."""
+    from areno_b200.ops import gemm, norm
+
+    torch.manual_seed(11)
+    x = torch.randn(rows, k, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(n, k, device="cuda") * 0.03).to(torch.bfloat16)
+    res = torch.randn(rows, n, device="cuda").to(torch.bfloat16)
+    nw = (1 + 0.1 * torch.randn(n, device="cuda")).to(torch.bfloat16)
+    part = gemm.gemm_partials(x, w)
+    h_ref = ((x.float() @ w.float().t()) + res.float()).to(torch.bfloat16).float()
+    y_ref = h_ref * torch.rsqrt(h_ref.pow(2).mean(-1, keepdim=True) + 1e-6) * nw.float()
+    if isinstance(part, gemm.SplitKPartial):
+        assert part.splits > 1
+        y, h = norm.splitk_residual_rmsnorm(part, res, nw, 1e-6)
+    else:
+        y, h = norm.rmsnorm(part, nw, 1e-6, residual=res)
+    rel = lambda a, b: float((a.float() - b).norm() / b.norm())
+    assert rel(h, h_ref) < 8e-3 and rel(y, y_ref) < 8e-3
