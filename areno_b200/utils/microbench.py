@@ -1,0 +1,283 @@
+"""Single-kernel micro-benchmarks of the hot ops at the benchmark model's shapes.
+
+    python -m areno_b200.utils.microbench --case gemm_fwd --iters 5 --warmup 3
+    python -m areno_b200.utils.microbench --list
+
+Every case builds inputs larger than the 126 MB L2 (or rotates between several weight copies when
+one operand is smaller), times ``iters`` launches with CUDA events after ``warmup`` launches, and
+prints achieved TFLOP/s and GB/s together with the fraction of the measured roofline found in
+``MEASURED_PEAKS.json`` at the repository root (cuBLAS bf16 burst throughput and STREAM-style copy
+bandwidth of this machine).  The same command line is what the profiler captures are taken from;
+cases hold at most a few GB on the device.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "hbm_gbs": 6650.0}
+
+
+def load_peaks() -> tuple[dict, str]:
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    path = os.path.join(root, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            data = json.load(f)
+        return {"bf16_tflops": float(data["bf16_tflops"]), "hbm_gbs": float(data["hbm_gbs"])}, "measured"
+    except Exception:
+        return dict(FALLBACK_PEAKS), "fallback"
+
+
+def _bf16(*shape, scale=1.0):
+    return (torch.randn(*shape, device="cuda") * scale).to(torch.bfloat16)
+
+
+# Each case returns (callable, flops_per_call, bytes_per_call, note)
+def case_gemm_fwd():
+    from ..ops import gemm
+
+    m, n, k = 4096, 37888, 3584  # gate_up projection of one 4096-token micro-batch
+    a, w = _bf16(m, k), _bf16(n, k, scale=0.02)
+    out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+    return (lambda: gemm.gemm(a, w, out=out)), 2.0 * m * n * k, 2.0 * (m * k + n * k + m * n), f"M={m} N={n} K={k}"
+
+
+def case_gemm_dgrad():
+    from ..ops import gemm
+
+    m, n, k = 4096, 3584, 37888  # dX = dY[M, 37888] @ W[37888, 3584]
+    dy, w = _bf16(m, k), _bf16(k, n, scale=0.02)
+    out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+    return (lambda: gemm.gemm(dy, w, out=out, b_mn=True)), 2.0 * m * n * k, 2.0 * (m * k + n * k + m * n), \
+        f"M={m} N={n} K={k} (B MN-major)"
+
+
+def case_gemm_wgrad():
+    from ..ops import gemm
+
+    tokens, n, k = 4096, 37888, 3584  # dW[N, K] += dY^T[N, T] @ X[T, K], fp32 accumulate
+    dy, x = _bf16(tokens, n), _bf16(tokens, k)
+    out = torch.zeros(n, k, device="cuda", dtype=torch.float32)
+    return (lambda: gemm.gemm(dy, x, out=out, a_mn=True, b_mn=True, accumulate=True)), 2.0 * tokens * n * k, \
+        2.0 * tokens * (n + k) + 8.0 * n * k, f"M={n} N={k} K={tokens} (A, B MN-major; fp32 accumulate)"
+
+
+def _rotating_weights(n, k, min_bytes=400e6):
+    copies = max(2, int(min_bytes // (n * k * 2)) + 1)
+    return [_bf16(n, k, scale=0.02) for _ in range(copies)]
+
+
+def case_gemm_decode_down():
+    from ..ops import gemm
+
+    m, n, k = 64, 3584, 18944
+    a = _bf16(m, k)
+    ws = _rotating_weights(n, k)
+    state = {"i": 0}
+
+    def run():
+        w = ws[state["i"] % len(ws)]
+        state["i"] += 1
+        return gemm.gemm(a, w)
+
+    return run, 2.0 * m * n * k, 2.0 * (n * k + m * k + m * n), f"M={m} N={n} K={k} split-K, {len(ws)} weight copies"
+
+
+def case_gemm_decode_gate_up():
+    from ..ops import gemm
+
+    m, n, k = 64, 37888, 3584
+    a = _bf16(m, k)
+    ws = _rotating_weights(n, k)
+    state = {"i": 0}
+
+    def run():
+        w = ws[state["i"] % len(ws)]
+        state["i"] += 1
+        return gemm.gemm(a, w)
+
+    return run, 2.0 * m * n * k, 2.0 * (n * k + m * k + m * n), f"M={m} N={n} K={k}, {len(ws)} weight copies"
+
+
+def case_splitk_rmsnorm():
+    from ..ops import gemm, norm
+
+    m, n, k = 64, 3584, 3584
+    a, res, nw = _bf16(m, k), _bf16(m, n), torch.ones(n, device="cuda", dtype=torch.bfloat16)
+    ws = _rotating_weights(n, k)
+    state = {"i": 0}
+
+    def run():
+        w = ws[state["i"] % len(ws)]
+        state["i"] += 1
+        part = gemm.gemm_partials(a, w)
+        if isinstance(part, gemm.SplitKPartial):
+            return norm.splitk_residual_rmsnorm(part, res, nw, 1e-6)
+        return norm.rmsnorm(part, nw, 1e-6, residual=res)
+
+    return run, 2.0 * m * n * k, 2.0 * (n * k + m * k + 3 * m * n), f"o_proj M={m} N={n} K={k} + fold/residual/RMSNorm"
+
+
+def _attn_inputs(lens, hq=28, hkv=4, d=128):
+    from ..ops import attention as attn
+
+    t = sum(lens)
+    qkv = _bf16(t, (hq + 2 * hkv) * d)
+    q = qkv[:, : hq * d].unflatten(1, (hq, d))
+    k = qkv[:, hq * d:(hq + hkv) * d].unflatten(1, (hkv, d))
+    v = qkv[:, (hq + hkv) * d:].unflatten(1, (hkv, d))
+    meta = attn.build_varlen_meta(lens, device="cuda")
+    flops = sum(4.0 * hq * d * (n * (n + 1) / 2) for n in lens)  # causal QK^T and PV
+    return q, k, v, meta, flops
+
+
+def case_attn_fwd():
+    from ..ops import attention as attn
+
+    lens = [1536] * 16  # 24.6k tokens: q/k/v 180 MB
+    q, k, v, meta, flops = _attn_inputs(lens)
+    out = torch.empty_like(q.contiguous())
+    return (lambda: attn.attention_forward(q, k, v, meta, 128 ** -0.5, True, 0, out=out)), flops, \
+        2.0 * sum(lens) * 128 * (28 * 2 + 8), f"{len(lens)} x {lens[0]} tokens, 28 q / 4 kv heads, d=128, causal"
+
+
+def case_attn_bwd():
+    from ..ops import attention as attn
+
+    lens = [1536] * 16
+    q, k, v, meta, flops = _attn_inputs(lens)
+    o, lse = attn.attention_forward(q, k, v, meta, 128 ** -0.5, True, 0)
+    do = torch.randn_like(o)
+    dq, dk, dv = torch.empty_like(o), torch.empty_like(k.contiguous()), torch.empty_like(v.contiguous())
+    return (lambda: attn.attention_backward(q, k, v, o, do, lse, meta, 128 ** -0.5, True, 0, dq, dk, dv)), 2.5 * flops, \
+        2.0 * sum(lens) * 128 * (28 * 4 + 16), "backward of attn_fwd (delta + dK/dV + dQ kernels)"
+
+
+def case_paged_decode(fp8: bool = False):
+    from ..ops import paged_attention as pa
+
+    b, hq, hkv, d, ctx = 64, 28, 4, 128, 1024
+    pages_per_seq = ctx // pa.PAGE
+    num_pages = b * pages_per_seq * 4  # 4x the live pages: 1 GB of bf16 KV so that L2 cannot hold it
+    kc, vc, ks, vs = pa.alloc_kv_cache(num_pages, hkv, d, "cuda", fp8=fp8)
+    if fp8:
+        kc.random_(0, 120)
+        vc.random_(0, 120)
+    else:
+        kc.normal_()
+        vc.normal_()
+    perm = torch.randperm(num_pages, device="cuda").to(torch.int32)
+    tables = [perm[i * b * pages_per_seq:(i + 1) * b * pages_per_seq].view(b, pages_per_seq).contiguous() for i in range(4)]
+    lens = torch.full((b,), ctx, dtype=torch.int32, device="cuda")
+    q = _bf16(b, hq, d)
+    state = {"i": 0}
+
+    def run():
+        bt = tables[state["i"] % 4]
+        state["i"] += 1
+        return pa.paged_decode(q, kc, vc, ks, vs, bt, lens, d ** -0.5, max_context=ctx)
+
+    elt = 1 if fp8 else 2
+    return run, 4.0 * b * hq * d * ctx, 2.0 * b * hkv * ctx * d * elt, f"B={b} ctx={ctx} 28 q / 4 kv heads, {'fp8' if fp8 else 'bf16'} pages"
+
+
+def case_sampler():
+    from ..ops import sampling
+
+    b, v = 64, 152064
+    logits = torch.randn(b * 8, v, device="cuda")  # 8 row groups, 311 MB
+    uid = torch.arange(b, device="cuda", dtype=torch.int64)
+    gen = torch.zeros(b, dtype=torch.int32, device="cuda")
+    state = {"i": 0}
+
+    def run():
+        i = state["i"] % 8
+        state["i"] += 1
+        return sampling.sample(logits[i * b:(i + 1) * b], 1.0, -1, 1.0, gen_count=gen, seed=1, row_uid=uid)
+
+    return run, 0.0, 4.0 * b * v, f"B={b} V={v} fp32 logits, temperature 1"
+
+
+def case_adamw():
+    from ..ops import optim
+
+    n = 256 * 1024 * 1024  # 1 GiB per fp32 tensor
+    master, m, v, g = (torch.zeros(n, device="cuda") for _ in range(4))
+    g.normal_()
+    out = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    return (lambda: optim.adamw_fp32(master, m, v, g, out, 1e-5, 0.9, 0.999, 1e-8, 0.01, 1)), 0.0, \
+        n * (4 * 4 + 3 * 4 + 2.0), f"{n} elements, fp32 master/m/v"
+
+
+def case_moe_grouped():
+    from ..ops import moe
+
+    tokens, e, k, h, inter = 4096, 128, 8, 2048, 768
+    ids = torch.stack([torch.randperm(e, device="cuda")[:k] for _ in range(tokens)]).to(torch.int32)
+    plan = moe.align(ids, 0, e)
+    xs = moe.permute(_bf16(tokens, h), plan)
+    w = _bf16(e, 2 * inter, h, scale=0.02)
+    return (lambda: moe.grouped_linear(xs, w, plan)), 2.0 * tokens * k * 2 * inter * h, \
+        2.0 * (e * 2 * inter * h + tokens * k * (h + 2 * inter)), f"{tokens} tokens x top-{k} of {e} experts, {h}->{2 * inter}"
+
+
+CASES = {
+    "gemm_fwd": case_gemm_fwd, "gemm_dgrad": case_gemm_dgrad, "gemm_wgrad": case_gemm_wgrad,
+    "gemm_decode_down": case_gemm_decode_down, "gemm_decode_gate_up": case_gemm_decode_gate_up,
+    "splitk_rmsnorm": case_splitk_rmsnorm, "attn_fwd": case_attn_fwd, "attn_bwd": case_attn_bwd,
+    "paged_decode": case_paged_decode, "paged_decode_fp8": lambda: case_paged_decode(True), "sampler": case_sampler,
+    "adamw": case_adamw, "moe_grouped": case_moe_grouped,
+}
+
+
+def run_case(name: str, iters: int, warmup: int) -> dict:
+    fn, flops, nbytes, note = CASES[name]()
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(iters):
+        fn()
+    end.record()
+    torch.cuda.synchronize()
+    us = start.elapsed_time(end) * 1e3 / iters
+    peaks, origin = load_peaks()
+    out = {"case": name, "shape": note, "us_per_call": round(us, 2), "peaks": origin}
+    if flops:
+        tf = flops / us / 1e6
+        out["tflops"] = round(tf, 1)
+        out["frac_of_bf16_peak"] = round(tf / peaks["bf16_tflops"], 3)
+    gbs = nbytes / us / 1e3
+    out["gb_per_s"] = round(gbs, 1)
+    out["frac_of_hbm_peak"] = round(gbs / peaks["hbm_gbs"], 3)
+    from ..ops import _lib
+
+    _lib.check_status()
+    return out
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    ap.add_argument("--case", default="all")
+    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--list", action="store_true")
+    args = ap.parse_args(argv)
+    if args.list:
+        print("\n".join(CASES))
+        return 0
+    names = list(CASES) if args.case == "all" else [c.strip() for c in args.case.split(",")]
+    for name in names:
+        print(json.dumps(run_case(name, args.iters, args.warmup)), flush=True)
+        torch.cuda.empty_cache()
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
