@@ -53,6 +53,11 @@ struct GemmParams {
   long long b_group_rows;
   long long c_group_stride;
   int num_groups;
+  // Tile order: 0 = consecutive work items walk M first, 1 = N first.  The CTAs running at the same
+  // time then span all tiles of the SHORT dimension and a few of the long one, which keeps both
+  // operand working sets inside L2 (otherwise a weight-gradient GEMM re-reads dY from DRAM once per
+  // N tile).
+  int n_fast;
 };
 
 struct WorkItem {
@@ -74,8 +79,8 @@ __device__ __forceinline__ WorkItem decode_work(const GemmParams& p, int work, i
     const int tiles = p.tiles_m * p.tiles_n;
     const int e = work / tiles;
     const int tile = work - e * tiles;
-    w.m0 = (tile % p.tiles_m) * kBM;
-    w.n0 = (tile / p.tiles_m) * BN;
+    w.m0 = (p.n_fast ? tile / p.tiles_n : tile % p.tiles_m) * kBM;
+    w.n0 = (p.n_fast ? tile % p.tiles_n : tile / p.tiles_m) * BN;
     w.split = 0;
     w.kb_lo = p.expert_rows[2 * e] / kBK;
     w.kb_hi = w.kb_lo + p.expert_rows[2 * e + 1] / kBK;
@@ -88,9 +93,9 @@ __device__ __forceinline__ WorkItem decode_work(const GemmParams& p, int work, i
   }
   const int tile = work / p.splits;
   w.split = work - tile * p.splits;
-  const int m_tile = tile % p.tiles_m;
+  const int m_tile = p.n_fast ? tile / p.tiles_n : tile % p.tiles_m;
   w.m0 = m_tile * kBM;
-  w.n0 = (tile / p.tiles_m) * BN;
+  w.n0 = (p.n_fast ? tile % p.tiles_n : tile / p.tiles_m) * BN;
   w.kb_lo = w.split * p.kb_per_split;
   w.kb_hi = min(num_kb, w.kb_lo + p.kb_per_split);
   if (p.group_mode == 1) {
@@ -539,6 +544,7 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, const void* bia
   p.tiles_m = (M + kBM - 1) / kBM;
   p.tiles_n = (N + bn - 1) / bn;
   p.epi = epi;
+  p.n_fast = p.tiles_n < p.tiles_m ? 1 : 0;
   p.splits = 1;
   p.kb_per_split = (K + kBK - 1) / kBK;
   p.split_stride = 0;
