@@ -158,6 +158,8 @@ class InferenceEngine:
         self.params = SamplingParams()
 
     def ensure_kv_cache(self):
+        if hasattr(self.model, "set_max_slots"):
+            self.model.set_max_slots(self.max_slots)   # models with per-slot recurrent state
         if getattr(self.model, "_kv_spec", None) != (self.num_pages, self.kv_fp8):
             self.model.allocate_kv_caches(self.num_pages, self.kv_fp8)
             self._graphs.clear()
@@ -295,9 +297,12 @@ class InferenceEngine:
         ids, pos, slots_map, q_lens, k_lens = [], [], [], [], []
         logit_rows, fin_slots, fin_prompt, fin_budget, fin_uid, fin_stream = [], [], [], [], [], []
         hist_slots = []
+        seq_slots, seq_fresh = [], []
         has_history = False
         row = 0
         for slot, rid, start, length, last in entries:
+            seq_slots.append(slot)
+            seq_fresh.append(1 if start == 0 else 0)
             req = self._requests[rid]
             req.slot = slot
             pages = self.sched.slot_pages(slot)
@@ -331,7 +336,9 @@ class InferenceEngine:
         if self.cuda:
             ids_t, pos_t, slot_t = (t.pin_memory().to(dev, non_blocking=True) for t in (ids_t, pos_t, slot_t))
         meta = InferMeta(mode="prefill", slot_mapping=slot_t,
-                         varlen=attn_ops.build_varlen_meta(q_lens, k_lens, device=dev), has_history=has_history)
+                         varlen=attn_ops.build_varlen_meta(q_lens, k_lens, device=dev), has_history=has_history,
+                         seq_slots=torch.tensor(seq_slots, dtype=torch.int32, device=dev),
+                         seq_fresh=torch.tensor(seq_fresh, dtype=torch.int32, device=dev))
         if has_history:
             meta.history = torch.from_numpy(np.concatenate(hist_slots)).to(dev)
         if logit_rows:

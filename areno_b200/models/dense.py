@@ -53,6 +53,8 @@ class InferMeta:
     logit_rows: torch.Tensor | None = None      # prefill: row indices whose logits are needed
     has_history: bool = False                   # prefill chunk continues sequences with cached tokens
     history: Any = None                         # (page index tensor, lengths) used to gather cached K/V
+    seq_slots: torch.Tensor | None = None       # prefill: int32 [num_seqs] engine slot of every packed sequence
+    seq_fresh: torch.Tensor | None = None       # prefill: int32 [num_seqs] 1 when the chunk starts its sequence
 
 
 @dataclass
@@ -84,17 +86,20 @@ class Attention(nn.Module):
         self.kv_cache = None  # (k_cache, v_cache, k_scale, v_scale)
 
     def forward(self, x, positions, meta):
+        return self.o(self.attend(x, positions, meta))
+
+    def attend(self, x, positions, meta):
+        """Attention output ``[T, hq * d]`` before the output projection."""
         cfg = self.cfg
         qkv = self.qkv(x)
         qw = self.q_norm.weight if self.q_norm is not None else None
         kw = self.k_norm.weight if self.k_norm is not None else None
         if isinstance(meta, TrainMeta):
-            o = attn_ops.qkv_attention(
+            return attn_ops.qkv_attention(
                 qkv, positions, meta.varlen, self.hq, self.hkv, self.d, scale=self.scale, theta=cfg.rope_theta,
                 rot_dim=cfg.rotary_dim, interleaved=cfg.rope_interleaved, causal=True, window=self.window,
                 q_norm_w=qw, k_norm_w=kw, norm_eps=cfg.rms_norm_eps, norm_offset=cfg.norm_weight_offset)
-            return self.o(o)
-        return self.o(self._infer(qkv, positions, meta, qw, kw))
+        return self._infer(qkv, positions, meta, qw, kw)
 
     def _infer(self, qkv, positions, meta: InferMeta, qw, kw):
         cfg = self.cfg
@@ -140,15 +145,18 @@ def _gather_history(kv_cache, meta: InferMeta, hkv: int, d: int):
 
 
 class DecoderLayer(nn.Module):
-    def __init__(self, cfg: ModelConfig, layer_idx: int, dtype, device, mlp: nn.Module | None = None):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, dtype, device, mlp: nn.Module | None = None,
+                 attn: nn.Module | None = None):
         super().__init__()
         self.input_norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device, cfg.norm_weight_offset)
-        self.attn = Attention(cfg, layer_idx, dtype, device)
+        self.attn = attn if attn is not None else Attention(cfg, layer_idx, dtype, device)
         self.post_norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device, cfg.norm_weight_offset)
         self.mlp = mlp if mlp is not None else GatedMLP(cfg.hidden_size, cfg.intermediate_size, cfg.hidden_act,
                                                         cfg.use_bias, dtype, device)
         # both row-parallel outputs of this block feed an RMSNorm with residual
-        self.attn.o.defer_reduce = True
+        out_proj = getattr(self.attn, "o", None) or getattr(self.attn, "out_proj", None)
+        if out_proj is not None:
+            out_proj.defer_reduce = True
         if isinstance(self.mlp, GatedMLP):
             self.mlp.down.defer_reduce = True
 

@@ -1,0 +1,251 @@
+"""Adapters of the hybrid (softmax + Gated DeltaNet) text models: ``qwen3_5`` and the text trunk of
+``minicpmv4_6`` (reference: ``areno/models/qwen3_5/model.py:805-880``, ``checkpoint.py:36-100,560-675``;
+``areno/models/minicpmv46/model.py:655-717``).
+
+Checkpoint layout handled here (tensor-parallel size 1): HF stores the attention output gate
+interleaved with the queries in ``q_proj`` (``[heads, 2, head_dim]`` rows) and the linear-attention
+input projections as four tensors (``in_proj_qkv``, ``in_proj_z``, ``in_proj_b``, ``in_proj_a``);
+they are regrouped into this package's fused parameters on load and split again on save.  Tensors
+outside the text trunk (vision tower, projector) pass through untouched when saving from a source
+directory."""
+
+from __future__ import annotations
+
+import json
+import os
+from typing import Any
+
+import torch
+
+from ..engine.config import ModelConfig
+from .base import ModelAdapter
+from .dense_adapters import _DTYPES
+from .hybrid import GatedDeltaNet, HybridCausalLM
+
+
+def _layer_types(n: int, interval: int) -> list[str]:
+    return ["full_attention" if (i + 1) % interval == 0 else "linear_attention" for i in range(n)]
+
+
+def _text_config(hf: dict[str, Any], name: str, prefix: str) -> ModelConfig:
+    text = hf.get("text_config") or hf
+    rope = text.get("rope_parameters") or text.get("rope_scaling") or {}
+    n = int(text["num_hidden_layers"])
+    heads = int(text["num_attention_heads"])
+    dtype = _DTYPES.get(str(text.get("torch_dtype") or text.get("dtype") or hf.get("torch_dtype") or hf.get("dtype")
+                            or "bfloat16"), torch.bfloat16)
+    return ModelConfig(
+        model_type=name, checkpoint_prefix=prefix, vocab_size=int(text["vocab_size"]), hidden_size=int(text["hidden_size"]),
+        intermediate_size=int(text["intermediate_size"]), num_hidden_layers=n, num_attention_heads=heads,
+        num_key_value_heads=int(text.get("num_key_value_heads", heads)),
+        head_dim=int(text.get("head_dim", int(text["hidden_size"]) // heads)),
+        rms_norm_eps=float(text.get("rms_norm_eps", 1e-6)),
+        rope_theta=float(rope.get("rope_theta", text.get("rope_theta", 10_000.0))),
+        max_position_embeddings=int(text.get("max_position_embeddings", 262144)),
+        tie_word_embeddings=bool(text.get("tie_word_embeddings", hf.get("tie_word_embeddings", True))),
+        qkv_bias=bool(text.get("attention_bias", False)), qk_norm=True, dtype=dtype,
+        hidden_act=str(text.get("hidden_act", "silu")),
+        layer_types=list(text.get("layer_types") or _layer_types(n, int(text.get("full_attention_interval", 1)))),
+        partial_rotary_factor=float(rope.get("partial_rotary_factor", text.get("partial_rotary_factor", 0.25))),
+        attn_output_gate=bool(text.get("attn_output_gate", True)),
+        linear_conv_kernel_dim=int(text.get("linear_conv_kernel_dim", 4)),
+        linear_key_head_dim=int(text.get("linear_key_head_dim", 128)),
+        linear_value_head_dim=int(text.get("linear_value_head_dim", 128)),
+        linear_num_key_heads=int(text.get("linear_num_key_heads", 16)),
+        linear_num_value_heads=int(text.get("linear_num_value_heads", 32)),
+    )
+
+
+def _hf_text_config(c: ModelConfig) -> dict[str, Any]:
+    return {
+        "model_type": c.model_type, "vocab_size": c.vocab_size, "hidden_size": c.hidden_size,
+        "intermediate_size": c.intermediate_size, "num_hidden_layers": c.num_hidden_layers,
+        "num_attention_heads": c.num_attention_heads, "num_key_value_heads": c.num_key_value_heads, "head_dim": c.head_dim,
+        "rms_norm_eps": c.rms_norm_eps, "rope_theta": c.rope_theta, "max_position_embeddings": c.max_position_embeddings,
+        "tie_word_embeddings": c.tie_word_embeddings, "attention_bias": c.qkv_bias, "hidden_act": c.hidden_act,
+        "torch_dtype": str(c.dtype).replace("torch.", ""), "layer_types": list(c.layer_types or []),
+        "partial_rotary_factor": c.partial_rotary_factor, "attn_output_gate": c.attn_output_gate,
+        "linear_conv_kernel_dim": c.linear_conv_kernel_dim, "linear_key_head_dim": c.linear_key_head_dim,
+        "linear_value_head_dim": c.linear_value_head_dim, "linear_num_key_heads": c.linear_num_key_heads,
+        "linear_num_value_heads": c.linear_num_value_heads,
+    }
+
+
+def _prefix_in(index, candidates: tuple[str, ...]) -> str:
+    for p in candidates:
+        if f"{p}.embed_tokens.weight" in index:
+            return p
+    raise KeyError(f"no embedding found under any of {candidates}")
+
+
+class _HybridAdapter(ModelAdapter):
+    prefixes: tuple[str, ...] = ("model", "model.language_model")
+
+    def build(self, config, device="cpu"):
+        return HybridCausalLM(config, device=device)
+
+    # ------------------------------------------------------------------ load
+    @torch.no_grad()
+    def load_weights(self, model, path, config):
+        from ..engine.checkpoint import SafetensorsIndex, logger
+        from ..parallel.context import get_context
+
+        if get_context().tp_size != 1:
+            raise NotImplementedError("hybrid checkpoints load at tp_size == 1")
+        index = SafetensorsIndex(path)
+        pre = _prefix_in(index, self.prefixes)
+        used = 0
+
+        def put(param, tensor):
+            nonlocal used
+            if tuple(param.shape) != tuple(tensor.shape):
+                raise ValueError(f"shape mismatch: checkpoint {tuple(tensor.shape)} vs parameter {tuple(param.shape)}")
+            param.copy_(tensor.to(param.dtype))
+            used += 1
+
+        vocab = config.vocab_size
+        emb = index.get(f"{pre}.embed_tokens.weight")
+        model.embed.weight.zero_()
+        model.embed.weight[:vocab].copy_(emb.to(model.embed.weight.dtype))
+        put(model.norm.weight, index.get(f"{pre}.norm.weight"))
+        if not config.tie_word_embeddings:
+            key = next(k for k in (f"{pre}.lm_head.weight", "lm_head.weight") if k in index)
+            model.lm_head.weight.zero_()
+            model.lm_head.weight[:vocab].copy_(index.get(key).to(model.lm_head.weight.dtype))
+        for i, layer in enumerate(model.layers):
+            lp = f"{pre}.layers.{i}"
+            put(layer.input_norm.weight, index.get(f"{lp}.input_layernorm.weight"))
+            put(layer.post_norm.weight, index.get(f"{lp}.post_attention_layernorm.weight"))
+            put(layer.mlp.gate_up.weight, torch.cat([index.get(f"{lp}.mlp.gate_proj.weight"),
+                                                     index.get(f"{lp}.mlp.up_proj.weight")], 0))
+            put(layer.mlp.down.weight, index.get(f"{lp}.mlp.down_proj.weight"))
+            a = layer.attn
+            if isinstance(a, GatedDeltaNet):
+                la = f"{lp}.linear_attn"
+                put(a.in_qkvz, torch.cat([index.get(f"{la}.in_proj_qkv.weight"), index.get(f"{la}.in_proj_z.weight")], 0))
+                put(a.in_ba, torch.cat([index.get(f"{la}.in_proj_b.weight"), index.get(f"{la}.in_proj_a.weight")], 0))
+                put(a.conv_weight, index.get(f"{la}.conv1d.weight").reshape(a.conv_dim, a.k))
+                put(a.dt_bias, index.get(f"{la}.dt_bias"))
+                put(a.A_log, index.get(f"{la}.A_log"))
+                put(a.norm_weight, index.get(f"{la}.norm.weight"))
+                put(a.out_proj.weight, index.get(f"{la}.out_proj.weight"))
+            else:
+                sa = f"{lp}.self_attn"
+                qw = index.get(f"{sa}.q_proj.weight")
+                d, hq = a.d, a.hq
+                if a.gate is not None:
+                    qg = qw.view(hq, 2, d, qw.shape[-1])
+                    qw = qg[:, 0].reshape(hq * d, -1)
+                    put(a.gate.weight, qg[:, 1].reshape(hq * d, -1))
+                put(a.qkv.weight, torch.cat([qw, index.get(f"{sa}.k_proj.weight"), index.get(f"{sa}.v_proj.weight")], 0))
+                put(a.o.weight, index.get(f"{sa}.o_proj.weight"))
+                put(a.q_norm.weight, index.get(f"{sa}.q_norm.weight"))
+                put(a.k_norm.weight, index.get(f"{sa}.k_norm.weight"))
+            if i % 8 == 7:
+                index.drop()
+        index.drop()
+        logger.info("checkpoint loaded path=%s tensors=%d prefix=%s", path, used, pre)
+
+    # ------------------------------------------------------------------ save
+    @torch.no_grad()
+    def save_weights(self, model, path, config, source_path=None):
+        from safetensors.torch import save_file
+
+        from ..engine.checkpoint import _passthrough_untouched, copy_assets
+        from ..parallel.context import get_context
+
+        ctx = get_context()
+        if ctx.tp_size != 1:
+            raise NotImplementedError("hybrid checkpoints save at tp_size == 1")
+        if ctx.dp_rank != 0:
+            return
+        os.makedirs(path, exist_ok=True)
+        pre = config.checkpoint_prefix or "model"
+        out: dict[str, torch.Tensor] = {}
+
+        def cpu(t):
+            return t.detach().to("cpu", copy=True).contiguous()
+
+        vocab = config.vocab_size
+        out[f"{pre}.embed_tokens.weight"] = cpu(model.embed.weight[:vocab])
+        out[f"{pre}.norm.weight"] = cpu(model.norm.weight)
+        if not config.tie_word_embeddings:
+            out["lm_head.weight"] = cpu(model.lm_head.weight[:vocab])
+        for i, layer in enumerate(model.layers):
+            lp = f"{pre}.layers.{i}"
+            out[f"{lp}.input_layernorm.weight"] = cpu(layer.input_norm.weight)
+            out[f"{lp}.post_attention_layernorm.weight"] = cpu(layer.post_norm.weight)
+            inter = layer.mlp.gate_up.weight.shape[0] // 2
+            out[f"{lp}.mlp.gate_proj.weight"] = cpu(layer.mlp.gate_up.weight[:inter])
+            out[f"{lp}.mlp.up_proj.weight"] = cpu(layer.mlp.gate_up.weight[inter:])
+            out[f"{lp}.mlp.down_proj.weight"] = cpu(layer.mlp.down.weight)
+            a = layer.attn
+            if isinstance(a, GatedDeltaNet):
+                la = f"{lp}.linear_attn"
+                out[f"{la}.in_proj_qkv.weight"] = cpu(a.in_qkvz[: a.conv_dim])
+                out[f"{la}.in_proj_z.weight"] = cpu(a.in_qkvz[a.conv_dim:])
+                out[f"{la}.in_proj_b.weight"] = cpu(a.in_ba[: a.hv])
+                out[f"{la}.in_proj_a.weight"] = cpu(a.in_ba[a.hv:])
+                out[f"{la}.conv1d.weight"] = cpu(a.conv_weight.reshape(a.conv_dim, 1, a.k))
+                out[f"{la}.dt_bias"] = cpu(a.dt_bias)
+                out[f"{la}.A_log"] = cpu(a.A_log)
+                out[f"{la}.norm.weight"] = cpu(a.norm_weight)
+                out[f"{la}.out_proj.weight"] = cpu(a.out_proj.weight)
+            else:
+                sa = f"{lp}.self_attn"
+                d, hq, hkv = a.d, a.hq, a.hkv
+                qw = a.qkv.weight[: hq * d]
+                if a.gate is not None:
+                    qw = torch.stack([qw.view(hq, d, -1), a.gate.weight.view(hq, d, -1)], 1).reshape(2 * hq * d, -1)
+                out[f"{sa}.q_proj.weight"] = cpu(qw)
+                out[f"{sa}.k_proj.weight"] = cpu(a.qkv.weight[hq * d:(hq + hkv) * d])
+                out[f"{sa}.v_proj.weight"] = cpu(a.qkv.weight[(hq + hkv) * d:])
+                out[f"{sa}.o_proj.weight"] = cpu(a.o.weight)
+                out[f"{sa}.q_norm.weight"] = cpu(a.q_norm.weight)
+                out[f"{sa}.k_norm.weight"] = cpu(a.k_norm.weight)
+        fname = "model-00001-of-00001.safetensors"
+        save_file(out, os.path.join(path, fname), metadata={"format": "pt"})
+        weight_map = {k: fname for k in out}
+        if source_path and os.path.isdir(source_path):
+            _passthrough_untouched(source_path, path, weight_map)
+        total = sum(t.numel() * t.element_size() for t in out.values())
+        with open(os.path.join(path, "model.safetensors.index.json"), "w") as f:
+            json.dump({"metadata": {"total_size": total, "areno_checkpoint_writer": "distributed_tp"},
+                       "weight_map": dict(sorted(weight_map.items()))}, f, indent=2)
+        copy_assets(source_path, path, None)
+        if not os.path.exists(os.path.join(path, "config.json")):
+            with open(os.path.join(path, "config.json"), "w") as f:
+                json.dump(self.hf_config(config), f, indent=2)
+
+    def hf_config(self, config: ModelConfig) -> dict[str, Any]:
+        return _hf_text_config(config)
+
+
+class Qwen35Adapter(_HybridAdapter):
+    name = "qwen3_5"
+
+    def match_hf_config(self, hf):
+        return str(hf.get("model_type", "")).lower() == "qwen3_5" or \
+            "Qwen3_5ForConditionalGeneration" in set(hf.get("architectures") or [])
+
+    def config_from_hf(self, hf):
+        return _text_config(hf, self.name, "model")
+
+
+class MiniCPMV46Adapter(_HybridAdapter):
+    """Text trunk of the MiniCPM-V 4.6 vision-language model; vision tensors pass through on save."""
+
+    name = "minicpmv46"
+    prefixes = ("model.language_model", "model")
+
+    def match_hf_config(self, hf):
+        return str(hf.get("model_type", "")).lower() == "minicpmv4_6"
+
+    def config_from_hf(self, hf):
+        return _text_config(hf, self.name, "model.language_model")
+
+    def hf_config(self, config):
+        return {"model_type": "minicpmv4_6", "text_config": _hf_text_config(config)}
+
+
+ADAPTERS = [Qwen35Adapter, MiniCPMV46Adapter]
