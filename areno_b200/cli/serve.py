@@ -362,7 +362,7 @@ def create_app(*, model_path: str, tp_size: int = 1, world_size: int = 1, max_ru
 @click.option("--world-size", type=int, default=1, show_default=True, help="Total number of local worker ranks.")
 @click.option("--host", default="0.0.0.0", show_default=True, help="HTTP bind host.")
 @click.option("--port", type=int, default=8000, show_default=True, help="HTTP bind port.")
-@click.option("--max-running-prompts", type=int, default=64, show_default=True,
+@click.option("--max-running-prompts", type=int, default=16, show_default=True,
               help="Upper bound of sequences decoded concurrently per data-parallel row.")
 @click.option("--default-max-tokens", type=int, default=1024, show_default=True, help="Default max generated tokens.")
 @click.option("--decode-progress-interval-s", type=float, default=0.0, show_default=True,
