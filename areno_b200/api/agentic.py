@@ -449,6 +449,8 @@ class RolloutSession:
     async def complete_chat(self, body: dict[str, Any]) -> dict[str, Any]:
         """One chat completion through the trainer's async rollout path."""
         messages = normalize_messages(body.get("messages") or [])
+        if not messages:
+            raise ValueError("messages must be non-empty")
         tools = list(body.get("tools") or [])
         tool_choice = body.get("tool_choice")
         params = self._sampling_params.model_copy() if hasattr(self._sampling_params, "model_copy") \

@@ -109,6 +109,20 @@ def _build_packs(torch, rows, responses, logprobs, advantages, rows_per_pack: in
     return packs
 
 
+_LAUNCHER_VARS = ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT", "GROUP_RANK", "LOCAL_WORLD_SIZE",
+                  "ROLE_RANK", "ROLE_WORLD_SIZE", "ROLE_NAME", "GROUP_WORLD_SIZE", "OMP_NUM_THREADS")
+
+
+def _mark(stage: str) -> None:
+    """Progress marker on stderr (and in a file the parent reads if the run has to be abandoned)."""
+    line = f"[reference-arm {time.strftime('%H:%M:%S')}] {stage}"
+    print(line, file=sys.stderr, flush=True)
+    path = os.environ.get("ARENO_REF_STAGE_FILE")
+    if path:
+        with open(path, "w") as f:
+            f.write(stage)
+
+
 def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
@@ -117,9 +131,11 @@ def run_reference(args) -> None:
     if not os.path.isdir(os.path.join(REF, "areno")):
         _emit({"impl": "reference", "unavailable": "baseline/_ref is not installed (pip install --target baseline/_ref failed or was not run)"})
         return
+    if os.environ.get("ARENO_REF_CHILD") != "1" and (world > 1 or "TORCHELASTIC_RUN_ID" in os.environ):
+        _run_isolated(args, max(world, args.gpus))
+        return
     # the reference's workers are separate processes: drop the launcher's rendezvous variables
-    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT", "TORCHELASTIC_RUN_ID", "GROUP_RANK",
-              "LOCAL_WORLD_SIZE", "ROLE_RANK", "ROLE_WORLD_SIZE"):
+    for k in _LAUNCHER_VARS:
         os.environ.pop(k, None)
     sys.path.insert(0, REF)
     try:
@@ -128,6 +144,36 @@ def run_reference(args) -> None:
         tb = traceback.format_exc().strip().splitlines()
         _emit({"impl": "reference", "unavailable": f"reference run failed: {type(exc).__name__}: {str(exc)[:300]}",
                "trace_tail": tb[-6:]})
+
+
+def _run_isolated(args, n_gpus: int) -> None:
+    """Under a multi-rank launcher the reference is driven from a fresh interpreter with none of the
+    launcher's environment (its own engine spawns and rendezvouses its workers), and with a deadline:
+    a run that does not finish is reported as unavailable with the stage it had reached."""
+    import subprocess
+    import tempfile
+
+    env = {k: v for k, v in os.environ.items() if k not in _LAUNCHER_VARS and not k.startswith("TORCHELASTIC")}
+    env["ARENO_REF_CHILD"] = "1"
+    stage_file = tempfile.NamedTemporaryFile(prefix="areno_ref_stage_", delete=False).name
+    env["ARENO_REF_STAGE_FILE"] = stage_file
+    cmd = [sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", str(n_gpus), "--steps",
+           str(args.steps), "--warmup", str(args.warmup)] + (["--small"] if args.small else [])
+    deadline = float(os.environ.get("ARENO_REF_DEADLINE_S", 240 + 45 * (args.steps + args.warmup)))
+    try:
+        proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=deadline, start_new_session=True)
+    except subprocess.TimeoutExpired as exc:
+        stage = open(stage_file).read() if os.path.exists(stage_file) else "start"
+        sys.stderr.write((exc.stderr or b"").decode(errors="replace")[-2000:] if isinstance(exc.stderr, bytes) else str(exc.stderr or "")[-2000:])
+        _emit({"impl": "reference", "unavailable": f"reference run did not finish within {deadline:.0f} s at {n_gpus} GPUs "
+                                                   f"(last stage: {stage})"})
+        return
+    sys.stderr.write(proc.stderr[-4000:])
+    lines = [ln for ln in proc.stdout.splitlines() if ln.startswith("{")]
+    if lines:
+        print(lines[-1], flush=True)
+    else:
+        _emit({"impl": "reference", "unavailable": f"reference child exited with code {proc.returncode} and no result line"})
 
 
 def _run(args, n_gpus: int) -> None:
@@ -147,14 +193,17 @@ def _run(args, n_gpus: int) -> None:
         new_tokens, pmin, pmax = 64, 32, 96
     ckpt = os.path.join("/tmp", f"areno_ref_ckpt_{'small' if args.small else '7b'}")
     t0 = time.time()
+    _mark("writing checkpoint")
     _write_random_checkpoint(ckpt, model)
     ckpt_s = time.time() - t0
+    _mark(f"starting engine on {n_gpus} GPU(s)")
     attn_backend = os.environ.get("ARENO_REF_ATTN", "flash")
     engine = ArenoEngine.from_pretrained(
         ckpt, tp_size=1, dp_size=n_gpus, devices=list(range(n_gpus)),
         optimizer_config=OptimizerConfig(lr=1e-6, betas=(0.9, 0.999), weight_decay=0.01, grad_clip_norm=1.0),
         runtime_config=RuntimeConfig(attn_backend=attn_backend, activation_checkpointing=True),
         loss_fn=grpo_loss_fn)
+    _mark("engine ready")
     params = SamplingParams(temperature=1.0, top_p=1.0, top_k=0, suppress_special_tokens=False)
     rows_per_rank = n_prompts * bench.GROUP
 
@@ -163,6 +212,7 @@ def _run(args, n_gpus: int) -> None:
         for r in range(n_gpus):
             prompts = bench.make_prompts(step, r, model["vocab_size"], n_prompts, pmin, pmax)
             rows.extend(p for p in prompts for _ in range(bench.GROUP))
+        _mark(f"step {step}: rollout")
         engine.begin_rollout_session()
         out = engine.generate_rollout(rows, max_new_tokens=new_tokens, max_running_prompts=rows_per_rank * n_gpus,
                                       eos_token_id=None, sampling_params=params)
@@ -177,6 +227,7 @@ def _run(args, n_gpus: int) -> None:
         adv = bench.group_advantages(rewards, bench.GROUP)
         # ~3 sequences (about 4096 tokens) per rank per micro-batch, rows strided over DP by the engine
         packs = _build_packs(torch, rows, responses, resp_lp, adv, rows_per_pack=3 * n_gpus)
+        _mark(f"step {step}: train")
         stats = engine.step(packs, gradient_accumulation_steps=None)
         tokens = sum(len(p) + len(t) for p, t in zip(rows, responses))
         last = stats[-1]

@@ -1,0 +1,210 @@
+"""Smaller SDK pieces: algorithm registry, tool-call parsers, metrics writer, model references,
+sampling reference (distribution and determinism), layering of imports, bundled examples."""
+
+from __future__ import annotations
+
+import ast
+import importlib.util
+import os
+import pathlib
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+ROOT = pathlib.Path(__file__).resolve().parents[1]
+
+
+# ---------------------------------------------------------------- algorithm registry
+def test_algorithm_registry_and_loss_binding():
+    from areno_b200.api.algorithms import AlgorithmSpec, get_algorithm, list_algorithms, register_algorithm
+    from areno_b200.api.loss_fns import grpo_loss_fn
+    from areno_b200.api.trainer_config import PolicyTrainerConfig
+
+    names = set(list_algorithms())
+    assert {"sft", "dpo", "gspo", "grpo", "ppo"} <= names
+    assert get_algorithm(" GRPO ").name == "grpo" and get_algorithm("sft").requires_rollout is False
+    cfg = PolicyTrainerConfig(algo="gspo", ckpt="m", dataset_path="d", gspo_clip_eps=0.123)
+    bound = get_algorithm("gspo").make_loss_fn(cfg)
+    assert bound.keywords == {"clip_eps": 0.123}
+    assert get_algorithm("ppo").resolve_trainer_cls().__name__ == "PPOTrainer"
+    with pytest.raises(ValueError, match="unknown algorithm"):
+        get_algorithm("nope")
+    spec = AlgorithmSpec("my_algo", lambda: object, grpo_loss_fn, requires_rollout=True, experimental=True)
+    register_algorithm(spec)
+    with pytest.raises(ValueError, match="already registered"):
+        register_algorithm(spec)
+    register_algorithm(spec, replace=True)
+    assert get_algorithm("my_algo").experimental
+
+
+# ------------------------------------------------------------------ tool-call parsers
+TOOLS = [{"type": "function", "function": {"name": "get_weather", "parameters": {
+    "type": "object", "properties": {"city": {"type": "string"}, "unit": {"type": "string", "enum": ["c", "f"]}}}}},
+    {"type": "function", "function": {"name": "add", "parameters": {"type": "object", "properties": {
+        "a": {"type": "integer"}, "b": {"type": "integer"}}}}}]
+
+
+def test_tool_call_parsers():
+    import json
+
+    from areno_b200.api.tool_call_parser import get_tool_call_parser, list_tool_call_parsers
+
+    assert {"json", "qwen", "gemma4", "minicpm"} <= set(list_tool_call_parsers())
+    q = get_tool_call_parser("qwen")
+    res = q.parse('thinking...\n<tool_call>\n{"name": "add", "arguments": {"a": 1, "b": 2}}\n</tool_call>', TOOLS, None)
+    assert [c["function"]["name"] for c in res.tool_calls] == ["add"]
+    assert json.loads(res.tool_calls[0]["function"]["arguments"]) == {"a": 1, "b": 2}
+    two = q.parse('<tool_call>{"name":"add","arguments":{"a":1,"b":2}}</tool_call>'
+                  '<tool_call>{"name":"get_weather","arguments":{"city":"Oslo"}}</tool_call>', TOOLS, None)
+    assert [c["function"]["name"] for c in two.tool_calls] == ["add", "get_weather"]
+    # unknown tools and a forced tool_choice are respected
+    assert q.parse('<tool_call>{"name":"rm_rf","arguments":{}}</tool_call>', TOOLS, None).tool_calls == []
+    forced = {"type": "function", "function": {"name": "add"}}
+    only = q.parse('<tool_call>{"name":"get_weather","arguments":{"city":"x"}}</tool_call>', TOOLS, forced)
+    assert all(c["function"]["name"] == "add" for c in only.tool_calls)
+    j = get_tool_call_parser("json")
+    assert j.parse('{"name": "get_weather", "arguments": {"city": "Rome"}}', TOOLS, None).tool_calls[0]["function"]["name"] == "get_weather"
+    assert j.parse("no tools here", TOOLS, None).tool_calls == []
+    assert get_tool_call_parser(None).__class__ is j.__class__
+
+
+# ---------------------------------------------------------------------------- metrics
+def test_metrics_recorder_writes_event_files(tmp_path):
+    from areno_b200.api import TrainSequence
+    from areno_b200.api.metrics import MetricsRecorder
+
+    batch = [TrainSequence(tokens=[1, 2, 3, 4], prompt_mask=[True, True, False, False], logprobs=[0, 0, -1.0, -2.0],
+                           advantages=[0, 0, 1.0, 1.0], reward=1.0),
+             TrainSequence(tokens=[1, 2, 3], prompt_mask=[True, False, False], logprobs=[0, -1.0, -0.5],
+                           advantages=[0, -1.0, -1.0], reward=0.0)]
+    with MetricsRecorder(str(tmp_path)) as rec:
+        rec.record_train_step(step=1, train_result={"loss": 0.5, "grad_norm": 1.0, "lr": 1e-6}, train_batch=batch,
+                              timings={"rollout": 1.0, "train": 2.0})
+    assert any(name.startswith("events.out.tfevents") for name in os.listdir(tmp_path))
+
+
+# ---------------------------------------------------------------------- model references
+def test_model_refs(tmp_path):
+    from areno_b200.api.trainer_config import PPOTrainerConfig
+    from areno_b200.cli.model_refs import resolve_model_path, resolve_model_refs_for_config
+
+    d = tmp_path / "m"
+    d.mkdir()
+    assert resolve_model_path(str(d)) == str(d) and resolve_model_path(None) is None
+    with pytest.raises(FileNotFoundError):
+        resolve_model_path("./definitely/not/here")
+    cfg = PPOTrainerConfig(algo="ppo", ckpt=str(d), dataset_path="x", ref_ckpt=str(d), reward_ckpt=None)
+    out = resolve_model_refs_for_config(cfg)
+    assert out.ckpt == str(d) and out.ref_ckpt == str(d) and out.reward_ckpt is None and out is not cfg
+
+
+# ------------------------------------------------------------------- sampling reference
+def test_keyed_sampling_is_reproducible_shard_consistent_and_distributed_correctly():
+    from areno_b200.ops import sampling
+
+    torch.manual_seed(0)
+    logits = torch.randn(6, 64)
+    uid = torch.arange(6)
+    step = torch.zeros(6, dtype=torch.int32)
+    a, lp_a = sampling.sample(logits, 1.0, seed=7, row_uid=uid, gen_count=step)
+    b, _ = sampling.sample(logits, 1.0, seed=7, row_uid=uid, gen_count=step)
+    c, _ = sampling.sample(logits, 1.0, seed=8, row_uid=uid, gen_count=step)
+    assert torch.equal(a, b) and not torch.equal(a, c)
+    assert torch.allclose(lp_a, torch.log_softmax(logits, -1).gather(1, a[:, None]).squeeze(1), atol=1e-5)
+    # two vocabulary shards combine to the same draw as the full row
+    parts = []
+    for r in range(2):
+        rec = torch.empty(6, 6)
+        sampling.sample(logits[:, r * 32:(r + 1) * 32].contiguous(), 1.0, seed=7, row_uid=uid, gen_count=step,
+                        vocab_start=r * 32, part=rec)
+        parts.append(rec)
+    tok, lp = sampling.combine_shards(torch.stack(parts))
+    assert torch.equal(tok, a) and torch.allclose(lp, lp_a, atol=1e-5)
+    # empirical distribution of one row follows softmax; top-k never leaves the k best
+    row = torch.tensor([[2.0, 1.0, 0.0, -1.0]]).repeat(4000, 1)
+    draws, _ = sampling.sample(row, 1.0, seed=1, row_uid=torch.arange(4000), gen_count=torch.zeros(4000, dtype=torch.int32))
+    freq = torch.bincount(draws, minlength=4).float() / 4000
+    assert torch.allclose(freq, torch.softmax(row[0], -1), atol=0.03)
+    topk, _ = sampling.sample(row, 1.0, top_k=2, seed=1, row_uid=torch.arange(4000), gen_count=torch.zeros(4000, dtype=torch.int32))
+    assert set(topk.tolist()) == {0, 1}
+    greedy, _ = sampling.sample(logits, 0.0)
+    assert torch.equal(greedy, logits.argmax(-1))
+
+
+# --------------------------------------------------------------------- import layering
+def _imports(path: pathlib.Path) -> set[str]:
+    out = set()
+    tree = ast.parse(path.read_text())
+    pkg = ".".join(path.relative_to(ROOT).with_suffix("").parts[:-1])
+    for node in ast.walk(tree):
+        if isinstance(node, ast.Import):
+            out.update(a.name for a in node.names)
+        elif isinstance(node, ast.ImportFrom):
+            if node.level:
+                base = pkg.split(".")[: len(pkg.split(".")) - node.level + 1]
+                out.add(".".join(base + ([node.module] if node.module else [])))
+            elif node.module:
+                out.add(node.module)
+    return out
+
+
+def test_layering_ops_and_engine_do_not_import_the_sdk_or_cli():
+    """Lower layers never import upper ones: ops < models/parallel < engine < api < cli."""
+    for layer, banned in (("ops", ("areno_b200.engine", "areno_b200.api", "areno_b200.cli", "areno_b200.models")),
+                          ("parallel", ("areno_b200.engine", "areno_b200.api", "areno_b200.cli", "areno_b200.models")),
+                          ("models", ("areno_b200.api", "areno_b200.cli")),
+                          ("engine", ("areno_b200.api",))):
+        for path in (ROOT / "areno_b200" / layer).rglob("*.py"):
+            for mod in _imports(path):
+                bad = [b for b in banned if mod == b or mod.startswith(b + ".")]
+                if layer == "engine" and mod.startswith("areno_b200.cli.model_refs"):
+                    continue  # path resolution helper shared with the CLI
+                assert not bad, f"{path.relative_to(ROOT)} imports {mod}"
+
+
+def test_nothing_committed_imports_working_files():
+    import re
+
+    for path in list((ROOT / "areno_b200").rglob("*.py")) + [ROOT / "bench.py", ROOT / "__graft_entry__.py"]:
+        assert not re.search(r"(^|[\"'/\s.])_work(/|\b\.|[\"'])", path.read_text()), path
+
+
+# ---------------------------------------------------------------------------- examples
+def _load(path: str):
+    spec = importlib.util.spec_from_file_location(pathlib.Path(path).stem, path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def test_examples_pass_the_cli_preflight_and_behave(tmp_path):
+    from areno_b200.cli.train import trainer_config_from_options
+
+    ex = ROOT / "examples"
+    cfg = trainer_config_from_options(
+        algo="grpo", ckpt="m", dataset_path="tictactoe:8",
+        dataset_loader_fn=str(ex / "agentic/tictactoe/dataset_loader.py"),
+        agent_fn=str(ex / "agentic/tictactoe/run_agent.py"), reward_fn_path=str(ex / "agentic/tictactoe/reward.py"))
+    assert cfg.agent_fn.endswith("run_agent.py")
+    trainer_config_from_options(algo="sft", ckpt="m", dataset_path="alpaca",
+                                dataset_loader_fn=str(ex / "sft/alpaca/dataset_loader.py"))
+    trainer_config_from_options(algo="gspo", ckpt="m", dataset_path="gsm8k",
+                                dataset_loader_fn=str(ex / "math/dataset_loader.py"),
+                                reward_fn_path=str(ex / "math/reward.py"))
+    rows = _load(str(ex / "math/dataset_loader.py")).load_training_dataset(
+        "x", default_loader=lambda p: [{"question": "1+1?", "answer": "so #### 2"}], load_dataset=None, load_from_disk=None)
+    assert rows == [{"prompt": rows[0]["prompt"], "answer": "2"}] and "1+1?" in rows[0]["prompt"]
+    reward = _load(str(ex / "math/reward.py")).reward_fn
+    assert reward(SimpleNamespace(completion="it is #### 2", answer="2")) == 1.0
+    assert reward(SimpleNamespace(completion="it is 3", answer="2")) == 0.0
+    sft = _load(str(ex / "sft/alpaca/dataset_loader.py")).load_training_dataset(
+        "x", default_loader=lambda p: [{"instruction": "Say hi", "input": "", "output": "hi"}, {"instruction": "", "output": "x"}],
+        load_dataset=None, load_from_disk=None)
+    assert sft == [{"prompt": "Say hi", "response": "hi"}]
+    games = _load(str(ex / "agentic/tictactoe/dataset_loader.py")).load_training_dataset(
+        "tictactoe:8", default_loader=None, load_dataset=None, load_from_disk=None)
+    assert len(games) == 8
+    ttt_reward = _load(str(ex / "agentic/tictactoe/reward.py")).reward_fn
+    assert ttt_reward(SimpleNamespace(tool_results=[{"content": '{"result": "win"}'}])) == 1.0
+    assert ttt_reward(SimpleNamespace(tool_results=[])) == 0.0

@@ -1,0 +1,72 @@
+"""Native (C++) request scheduler and sequence packer."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+
+from areno_b200.engine._runtime import Scheduler, pack_indices
+
+
+def test_fifo_admission_chunked_prefill_and_page_accounting():
+    s = Scheduler(max_slots=2, num_pages=16, page_size=64, max_pages_per_seq=8, max_prefill_tokens=100)
+    s.add(10, 150, 100)  # needs two prefill chunks (100 + 50)
+    s.add(11, 30, 60)
+    s.add(12, 40, 10)    # waits: only two slots
+    assert (s.num_waiting, s.num_running) == (3, 0)
+    plan = s.plan_prefill()
+    assert plan == [(0, 10, 0, 100, False)]          # budget spent on the first request
+    assert (s.num_running, s.num_waiting) == (1, 2)
+    plan = s.plan_prefill()
+    assert plan[0] == (0, 10, 100, 50, True)
+    assert plan[1] == (1, 11, 0, 30, True)           # FIFO: next request fills the rest of the budget
+    assert s.num_decoding == 2 and s.num_waiting == 1
+    assert len(s.slot_pages(0)) == 3 and len(s.slot_pages(1)) == 1   # ceil(150/64), ceil(30/64)
+    free_before = s.num_free_pages
+    assert s.slot_seq_len(0) == 150 and s.slot_request(1) == 11
+    # decoding past a page boundary allocates exactly one page for that slot
+    updates = []
+    for _ in range(45):
+        updates += s.reserve_decode(1)
+        s.advance(1)
+    # slot 1 crosses 64 tokens after 34 steps, slot 0 crosses 192 after 42
+    assert sorted((u[0], u[1]) for u in updates) == [(0, 3), (1, 1)]
+    assert s.num_free_pages == free_before - len(updates)
+    # finishing a slot returns its pages and admits the waiting request into the freed slot
+    s.finish(1)
+    assert s.num_running == 1
+    plan = s.plan_prefill()
+    assert plan == [(1, 12, 0, 40, True)]
+    assert s.active_extent == 2
+    s.finish(0)
+    s.finish(1)
+    assert s.num_free_pages == 16 and s.num_running == 0
+
+
+def test_rejects_requests_that_cannot_fit_and_reports_memory_pressure():
+    s = Scheduler(max_slots=4, num_pages=4, page_size=64, max_pages_per_seq=2, max_prefill_tokens=512)
+    with pytest.raises(ValueError, match="page limit"):
+        s.add(1, 100, 100)          # 200 tokens > 2 pages
+    with pytest.raises(ValueError, match="empty prompt"):
+        s.add(2, 0, 4)
+    for rid in (3, 4, 5, 6):
+        s.add(rid, 60, 60)          # each may grow to two pages; four pages in total
+    assert len(s.plan_prefill()) == 4 and s.num_free_pages == 0
+    for _ in range(4):
+        s.reserve_decode(1)
+        s.advance(1)
+    with pytest.raises(MemoryError) as err:   # the fifth token of each sequence needs a second page
+        s.reserve_decode(1)
+    victim = int(err.value.args[0])
+    assert 0 <= victim < 4
+    assert s.clear_waiting() == 0
+
+
+def test_pack_indices_maps_padded_rows_to_packed_tokens():
+    lens = np.array([3, 1, 2, 9], dtype=np.int64)
+    rows, cols, aidx, arows = pack_indices(lens, 4)          # the last row is clipped to the padded width
+    assert rows.tolist() == [0, 0, 0, 1, 2, 2, 3, 3, 3, 3]
+    assert cols.tolist() == [0, 1, 2, 0, 0, 1, 0, 1, 2, 3]
+    # actions: every packed position whose successor belongs to the same row
+    assert aidx.tolist() == [0, 1, 4, 6, 7, 8]
+    assert arows.tolist() == [0, 0, 2, 3, 3, 3]
