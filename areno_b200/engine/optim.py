@@ -69,10 +69,12 @@ class ShardedAdamW:
         params.reverse()
         cap = max(int(self.cfg.fp32_master_bucket_numel), 1)
         granule = _ALIGN * self.dp
-        groups = {False: [], True: []}
+        # one bucket family per (TP-replicated?, dtype): fp32 parameters (router gates, decay rates, conv
+        # taps) keep their precision instead of being folded into a bf16 buffer
+        groups: dict[tuple, list] = {}
         for p in params:
-            groups[bool(getattr(p, "tp_replicated_grad", False))].append(p)
-        for replicated, plist in groups.items():
+            groups.setdefault((bool(getattr(p, "tp_replicated_grad", False)), p.dtype), []).append(p)
+        for (replicated, _dtype), plist in groups.items():
             cur = _Bucket(replicated=replicated)
             for p in plist:
                 n = (p.numel() + _ALIGN - 1) // _ALIGN * _ALIGN
@@ -104,7 +106,12 @@ class ShardedAdamW:
         for b in self.buckets:
             lo = self.dp_rank * b.shard
             dev = b.param_flat.device
-            if self.cfg.adam_8bit:
+            if b.param_flat.dtype == torch.float32:
+                # fp32 parameters are their own master copy: the update runs in place on the local shard
+                b.master = b.param_flat[lo:lo + b.shard]
+                b.m = torch.zeros(b.shard, dtype=torch.float32, device=dev)
+                b.v = torch.zeros(b.shard, dtype=torch.float32, device=dev)
+            elif self.cfg.adam_8bit:
                 nb = (b.shard + optim_ops.Q_BLOCK - 1) // optim_ops.Q_BLOCK
                 b.m = torch.zeros(b.shard, dtype=torch.int8, device=dev)
                 b.v = torch.zeros(b.shard, dtype=torch.uint8, device=dev)
@@ -189,7 +196,10 @@ class ShardedAdamW:
             lo = self.dp_rank * b.shard
             g = self._grad_shard(b)
             out = b.param_flat[lo:lo + b.shard]
-            if self.cfg.adam_8bit:
+            if b.param_flat.dtype == torch.float32:
+                optim_ops.adamw_fp32(b.master, b.m, b.v, g, None, lr, b1, b2, self.cfg.eps, self.cfg.weight_decay,
+                                     self.step_count, 1.0 / self.dp, coef)
+            elif self.cfg.adam_8bit:
                 optim_ops.adamw_8bit(None, b.m, b.v, b.m_scale, b.v_scale, g, out, lr, b1, b2, self.cfg.eps,
                                      self.cfg.weight_decay, self.step_count, 1.0 / self.dp, coef)
             else:
@@ -205,7 +215,11 @@ class ShardedAdamW:
     # --------------------------------------------------------------- offload
     def offload_state(self):
         for b in self.buckets:
+            own_master = b.param_flat is not None and b.param_flat.dtype == torch.float32
             for name in ("master", "m", "v", "m_scale", "v_scale", "grad_flat"):
+                if name == "master" and own_master:
+                    b.master = None   # a view of the parameters themselves: rebuilt on onload
+                    continue
                 t = getattr(b, name)
                 if t is not None and t.is_cuda:
                     setattr(b, name, t.to("cpu"))
@@ -219,6 +233,9 @@ class ShardedAdamW:
                     setattr(b, name, t.to(device))
             for p, off in zip(b.params, b.offsets):
                 p.main_grad = b.grad_flat[off:off + p.numel()].view(p.shape)
+            if self._state_ready and b.master is None and b.param_flat.dtype == torch.float32:
+                lo = self.dp_rank * b.shard
+                b.master = b.param_flat[lo:lo + b.shard]
         self._offloaded = False
 
     # ------------------------------------------------------------ state dict
