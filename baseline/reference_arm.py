@@ -159,7 +159,7 @@ def _run_isolated(args, n_gpus: int) -> None:
     env["ARENO_REF_STAGE_FILE"] = stage_file
     cmd = [sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", str(n_gpus), "--steps",
            str(args.steps), "--warmup", str(args.warmup)] + (["--small"] if args.small else [])
-    deadline = float(os.environ.get("ARENO_REF_DEADLINE_S", 240 + 45 * (args.steps + args.warmup)))
+    deadline = float(os.environ.get("ARENO_REF_DEADLINE_S", 480 + 60 * (args.steps + args.warmup)))
     try:
         proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=deadline, start_new_session=True)
     except subprocess.TimeoutExpired as exc:
