@@ -17,6 +17,8 @@ Run ``python -m areno_b200.build`` to build explicitly (``--force`` to rebuild,
 
 from __future__ import annotations
 
+import contextlib
+import fcntl
 import hashlib
 import os
 import subprocess
@@ -69,6 +71,26 @@ def _run(cmd: list[str], verbose: bool) -> None:
         print(proc.stdout + proc.stderr)
 
 
+@contextlib.contextmanager
+def _build_lock():
+    """Serialise builds across processes (several ranks may import the package at once): the first
+    one in builds, the others wait and then find the stamp up to date."""
+    LIB.mkdir(parents=True, exist_ok=True)
+    with open(LIB / ".build.lock", "w") as fh:
+        fcntl.flock(fh, fcntl.LOCK_EX)
+        try:
+            yield
+        finally:
+            fcntl.flock(fh, fcntl.LOCK_UN)
+
+
+def _link(cmd_prefix: list[str], out: Path, verbose: bool) -> None:
+    """Link into a temporary name and rename: a concurrent loader never sees a half-written library."""
+    tmp = out.with_suffix(f".tmp{os.getpid()}.so")
+    _run([*cmd_prefix[:1], *cmd_prefix[1:], "-o", str(tmp)], verbose)
+    os.replace(tmp, out)
+
+
 def kernels_lib_path() -> Path:
     return LIB / "libareno_kernels.so"
 
@@ -88,6 +110,13 @@ def build_kernels(force: bool = False, verbose: bool = False) -> Path:
         return out
     if not os.path.exists(NVCC):
         raise RuntimeError(f"nvcc not found at {NVCC}; cannot build {out}")
+    with _build_lock():
+        if not force and out.exists() and stamp.exists() and stamp.read_text() == digest:
+            return out   # another process built it while we waited
+        return _build_kernels_locked(out, cu, headers, digest, stamp, force, verbose)
+
+
+def _build_kernels_locked(out, cu, headers, digest, stamp, force, verbose) -> Path:
     OBJ.mkdir(parents=True, exist_ok=True)
     header_digest = _hash(headers, " ".join(NVCC_FLAGS))
 
@@ -106,7 +135,7 @@ def build_kernels(force: bool = False, verbose: bool = False) -> Path:
 
     with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 4)) as pool:
         objs = list(pool.map(compile_one, cu))
-    _run([NVCC, "-shared", "-o", str(out), *map(str, objs), "-lcudart"], verbose)
+    _link([NVCC, "-shared", *map(str, objs), "-lcudart"], out, verbose)
     stamp.write_text(digest)
     return out
 
@@ -122,10 +151,12 @@ def build_runtime(force: bool = False, verbose: bool = False) -> Path:
     stamp = LIB / "libareno_runtime.stamp"
     if not force and out.exists() and stamp.exists() and stamp.read_text() == digest:
         return out
-    LIB.mkdir(parents=True, exist_ok=True)
-    cxx = os.environ.get("CXX", "g++")
-    _run([cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-pthread", "-o", str(out), *map(str, srcs)], verbose)
-    stamp.write_text(digest)
+    with _build_lock():
+        if not force and out.exists() and stamp.exists() and stamp.read_text() == digest:
+            return out
+        cxx = os.environ.get("CXX", "g++")
+        _link([cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-pthread", *map(str, srcs)], out, verbose)
+        stamp.write_text(digest)
     return out
 
 

@@ -208,3 +208,14 @@ def test_examples_pass_the_cli_preflight_and_behave(tmp_path):
     ttt_reward = _load(str(ex / "agentic/tictactoe/reward.py")).reward_fn
     assert ttt_reward(SimpleNamespace(tool_results=[{"content": '{"result": "win"}'}])) == 1.0
     assert ttt_reward(SimpleNamespace(tool_results=[])) == 0.0
+
+
+def test_native_libraries_are_current():
+    """The in-tree libraries travel with the source; a stale build would be recompiled by every rank."""
+    from areno_b200 import build
+
+    for path in (build.kernels_lib_path(), build.runtime_lib_path()):
+        assert path.exists(), f"{path} missing: run python -m areno_b200.build"
+    before = build.kernels_lib_path().stat().st_mtime_ns
+    build.ensure_built()
+    assert build.kernels_lib_path().stat().st_mtime_ns == before, "kernel library was stale and had to be rebuilt"
