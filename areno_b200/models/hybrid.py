@@ -134,7 +134,12 @@ class HybridDecoderLayer(DecoderLayer):
         kind = cfg.layer_types[layer_idx] if cfg.layer_types else "full_attention"
         mixer = GatedDeltaNet if kind == "linear_attention" else GatedAttention
         attn = mixer(cfg, layer_idx, dtype, device)
-        super().__init__(cfg, layer_idx, dtype, device, attn=attn)
+        mlp = None
+        if cfg.num_experts:
+            from .moe import SparseMoeBlock
+
+            mlp = SparseMoeBlock(cfg, dtype, device)
+        super().__init__(cfg, layer_idx, dtype, device, mlp=mlp, attn=attn)
         self.kind = kind
 
 

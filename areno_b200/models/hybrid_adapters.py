@@ -57,6 +57,15 @@ def _text_config(hf: dict[str, Any], name: str, prefix: str) -> ModelConfig:
 
 
 def _hf_text_config(c: ModelConfig) -> dict[str, Any]:
+    out = _hf_text_config_base(c)
+    if c.num_experts:
+        out.update(num_experts=c.num_experts, num_experts_per_tok=c.num_experts_per_tok,
+                   moe_intermediate_size=c.moe_intermediate_size, norm_topk_prob=c.norm_topk_prob,
+                   shared_expert_intermediate_size=c.shared_expert_intermediate_size)
+    return out
+
+
+def _hf_text_config_base(c: ModelConfig) -> dict[str, Any]:
     return {
         "model_type": c.model_type, "vocab_size": c.vocab_size, "hidden_size": c.hidden_size,
         "intermediate_size": c.intermediate_size, "num_hidden_layers": c.num_hidden_layers,
@@ -76,6 +85,61 @@ def _prefix_in(index, candidates: tuple[str, ...]) -> str:
         if f"{p}.embed_tokens.weight" in index:
             return p
     raise KeyError(f"no embedding found under any of {candidates}")
+
+
+def _load_dense_mlp(index, mlp, mp: str, put) -> None:
+    put(mlp.gate_up.weight, torch.cat([index.get(f"{mp}.gate_proj.weight"), index.get(f"{mp}.up_proj.weight")], 0))
+    put(mlp.down.weight, index.get(f"{mp}.down_proj.weight"))
+
+
+def _load_mlp(index, mlp, mp: str, put) -> int:
+    """Dense SwiGLU, or router + routed experts (packed ``experts.gate_up_proj`` / ``experts.down_proj`` or one
+    tensor per expert) + optional shared expert with its sigmoid gate."""
+    from .moe import SparseMoeBlock
+
+    if not isinstance(mlp, SparseMoeBlock):
+        _load_dense_mlp(index, mlp, mp, put)
+        return 0
+    gate_key = next(k for k in (f"{mp}.gate.weight", f"{mp}.gate", f"{mp}.router.weight") if k in index)
+    put(mlp.router.weight, index.get(gate_key))
+    ex = mlp.experts
+    packed = next(((a, b) for a, b in ((f"{mp}.experts.gate_up_proj.weight", f"{mp}.experts.down_proj.weight"),
+                                       (f"{mp}.experts.gate_up_proj", f"{mp}.experts.down_proj")) if a in index), None)
+    if packed is not None:
+        put(ex.gate_up, index.get(packed[0])[ex.e_lo: ex.e_lo + ex.e_local])
+        put(ex.down, index.get(packed[1])[ex.e_lo: ex.e_lo + ex.e_local])
+    else:
+        for le in range(ex.e_local):
+            e = ex.e_lo + le
+            put(ex.gate_up[le], torch.cat([index.get(f"{mp}.experts.{e}.gate_proj.weight"),
+                                           index.get(f"{mp}.experts.{e}.up_proj.weight")], 0))
+            put(ex.down[le], index.get(f"{mp}.experts.{e}.down_proj.weight"))
+    if mlp.shared is not None:
+        _load_dense_mlp(index, mlp.shared, f"{mp}.shared_expert", put)
+    if mlp.shared_gate is not None:
+        put(mlp.shared_gate, index.get(f"{mp}.shared_expert_gate.weight").reshape(-1))
+    return 0
+
+
+def _save_mlp(out: dict, mlp, mp: str, cpu) -> None:
+    from .moe import SparseMoeBlock
+
+    def dense(m, prefix):
+        inter = m.gate_up.weight.shape[0] // 2
+        out[f"{prefix}.gate_proj.weight"] = cpu(m.gate_up.weight[:inter])
+        out[f"{prefix}.up_proj.weight"] = cpu(m.gate_up.weight[inter:])
+        out[f"{prefix}.down_proj.weight"] = cpu(m.down.weight)
+
+    if not isinstance(mlp, SparseMoeBlock):
+        dense(mlp, mp)
+        return
+    out[f"{mp}.gate.weight"] = cpu(mlp.router.weight)
+    out[f"{mp}.experts.gate_up_proj"] = cpu(mlp.experts.gate_up)
+    out[f"{mp}.experts.down_proj"] = cpu(mlp.experts.down)
+    if mlp.shared is not None:
+        dense(mlp.shared, f"{mp}.shared_expert")
+    if mlp.shared_gate is not None:
+        out[f"{mp}.shared_expert_gate.weight"] = cpu(mlp.shared_gate.reshape(1, -1))
 
 
 class _HybridAdapter(ModelAdapter):
@@ -116,9 +180,7 @@ class _HybridAdapter(ModelAdapter):
             lp = f"{pre}.layers.{i}"
             put(layer.input_norm.weight, index.get(f"{lp}.input_layernorm.weight"))
             put(layer.post_norm.weight, index.get(f"{lp}.post_attention_layernorm.weight"))
-            put(layer.mlp.gate_up.weight, torch.cat([index.get(f"{lp}.mlp.gate_proj.weight"),
-                                                     index.get(f"{lp}.mlp.up_proj.weight")], 0))
-            put(layer.mlp.down.weight, index.get(f"{lp}.mlp.down_proj.weight"))
+            used += _load_mlp(index, layer.mlp, f"{lp}.mlp", put)
             a = layer.attn
             if isinstance(a, GatedDeltaNet):
                 la = f"{lp}.linear_attn"
@@ -175,10 +237,7 @@ class _HybridAdapter(ModelAdapter):
             lp = f"{pre}.layers.{i}"
             out[f"{lp}.input_layernorm.weight"] = cpu(layer.input_norm.weight)
             out[f"{lp}.post_attention_layernorm.weight"] = cpu(layer.post_norm.weight)
-            inter = layer.mlp.gate_up.weight.shape[0] // 2
-            out[f"{lp}.mlp.gate_proj.weight"] = cpu(layer.mlp.gate_up.weight[:inter])
-            out[f"{lp}.mlp.up_proj.weight"] = cpu(layer.mlp.gate_up.weight[inter:])
-            out[f"{lp}.mlp.down_proj.weight"] = cpu(layer.mlp.down.weight)
+            _save_mlp(out, layer.mlp, f"{lp}.mlp", cpu)
             a = layer.attn
             if isinstance(a, GatedDeltaNet):
                 la = f"{lp}.linear_attn"
@@ -248,4 +307,34 @@ class MiniCPMV46Adapter(_HybridAdapter):
         return {"model_type": "minicpmv4_6", "text_config": _hf_text_config(config)}
 
 
-ADAPTERS = [Qwen35Adapter, MiniCPMV46Adapter]
+class Qwen35MoeAdapter(_HybridAdapter):
+    """Qwen3.5-MoE: the hybrid stack with a sparse block in every layer (softmax top-k router, routed
+    experts, shared expert scaled by a per-token sigmoid gate); reference
+    ``areno/models/qwen3_5/model.py:499-547,883-940``."""
+
+    name = "qwen3_5_moe"
+
+    def match_hf_config(self, hf):
+        return str(hf.get("model_type", "")).lower() == "qwen3_5_moe" or \
+            "Qwen3_5MoeForConditionalGeneration" in set(hf.get("architectures") or [])
+
+    def config_from_hf(self, hf):
+        text = hf.get("text_config") or hf
+        hf2 = dict(hf)
+        t2 = dict(text)
+        t2.setdefault("intermediate_size", text.get("shared_expert_intermediate_size", text["moe_intermediate_size"]))
+        if "text_config" in hf:
+            hf2["text_config"] = t2
+        else:
+            hf2 = t2
+        cfg = _text_config(hf2, self.name, "model")
+        cfg.num_experts = int(text["num_experts"])
+        cfg.num_experts_per_tok = int(text.get("num_experts_per_tok", 8))
+        cfg.moe_intermediate_size = int(text["moe_intermediate_size"])
+        cfg.shared_expert_intermediate_size = int(text.get("shared_expert_intermediate_size", 0) or 0)
+        cfg.norm_topk_prob = bool(text.get("norm_topk_prob", True))
+        cfg.extra = dict(cfg.extra or {}, shared_expert_gate=cfg.shared_expert_intermediate_size > 0)
+        return cfg
+
+
+ADAPTERS = [Qwen35MoeAdapter, Qwen35Adapter, MiniCPMV46Adapter]

@@ -67,9 +67,14 @@ class SparseMoeBlock(nn.Module):
         self.router = TopKRouter(cfg, device)
         self.experts = Experts(cfg, dtype, device)
         self.shared = None
+        self.shared_gate = None
         if cfg.shared_expert_intermediate_size:
             self.shared = GatedMLP(cfg.hidden_size, cfg.shared_expert_intermediate_size, cfg.hidden_act, False, dtype,
                                    device)
+            if (cfg.extra or {}).get("shared_expert_gate"):
+                # per-token sigmoid gate on the shared expert's output (Qwen3.5-MoE)
+                self.shared_gate = _param((cfg.hidden_size,), dtype, device)
+                self.shared_gate.tp_replicated_grad = True
         self.last_counts = None  # tokens per local expert of the latest forward (device tensor, for metrics)
 
     def forward(self, x):
@@ -77,7 +82,10 @@ class SparseMoeBlock(nn.Module):
         out, plan = self.experts(x, weights, ids)
         self.last_counts = plan.counts
         if self.shared is not None:
-            out = out + self.shared(x)
+            shared = self.shared(x)
+            if self.shared_gate is not None:
+                shared = shared * torch.sigmoid(torch.nn.functional.linear(x, self.shared_gate.unsqueeze(0)))
+            out = out + shared
         return out
 
 

@@ -117,3 +117,36 @@ def test_checkpoint_round_trip_in_hf_layout(tmp_path):
         adapter.load_weights(model2, path, cfg2)
         for (n1, p1), (n2, p2) in zip(model.named_parameters(), model2.named_parameters()):
             assert n1 == n2 and torch.equal(p1, p2), n1
+
+
+def test_qwen35_moe_round_trip_and_step(tmp_path):
+    from areno_b200.engine.checkpoint import SafetensorsIndex
+    from areno_b200.models import registry
+    from areno_b200.models.moe import SparseMoeBlock
+
+    single_process_context()
+    adapter = registry.get_adapter("qwen3_5_moe")
+    cfg = hybrid_config(model_type="qwen3_5_moe", num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32,
+                        shared_expert_intermediate_size=48, norm_topk_prob=True, extra={"shared_expert_gate": True})
+    model = adapter.build(cfg)
+    adapter.init_random(model, 2)
+    assert all(isinstance(layer.mlp, SparseMoeBlock) and layer.mlp.shared_gate is not None for layer in model.layers)
+    path = str(tmp_path / "q35moe")
+    adapter.save_weights(model, path, cfg)
+    index = SafetensorsIndex(path)
+    assert tuple(index.shape("model.layers.0.mlp.experts.gate_up_proj")) == (4, 64, 128)
+    assert tuple(index.shape("model.layers.0.mlp.shared_expert_gate.weight")) == (1, 128)
+    found, cfg2 = registry.config_from_pretrained(path)
+    assert found.name == "qwen3_5_moe" and cfg2.num_experts == 4 and cfg2.shared_expert_intermediate_size == 48
+    cfg2.dtype = torch.float32
+    model2 = adapter.build(cfg2)
+    adapter.load_weights(model2, path, cfg2)
+    for (n1, p1), (n2, p2) in zip(model.named_parameters(), model2.named_parameters()):
+        assert n1 == n2 and torch.equal(p1, p2), n1
+    from areno_b200.models.dense import TrainMeta
+    from areno_b200.ops.attention import build_varlen_meta
+
+    ids = torch.randint(3, 512, (30,))
+    h = model2(ids, torch.arange(30), TrainMeta(build_varlen_meta([30]), False)).hidden_states
+    h.float().pow(2).mean().backward()
+    assert model2.layers[0].mlp.shared_gate.grad is not None and model2.layers[0].mlp.router.weight.grad is not None
