@@ -17,6 +17,13 @@ def register_models() -> None:
     except ImportError:
         pass
     try:
+        from . import gemma4_adapter
+
+        for cls in gemma4_adapter.ADAPTERS:
+            register_adapter(cls)
+    except ImportError:
+        pass
+    try:
         from . import hybrid_adapters
 
         for cls in hybrid_adapters.ADAPTERS:

@@ -285,6 +285,35 @@ class _QKVAttention(torch.autograd.Function):
         return (dqkv, dwq, dwk) + (None,) * 14
 
 
+class _HeadRmsNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x3, w, offset, eps):
+        y3 = torch.empty_like(x3)
+        inv = _headnorm_fwd(x3, w, offset, y3, eps)
+        ctx.save_for_backward(x3, w, inv)
+        ctx.offset = offset
+        return y3
+
+    @staticmethod
+    def backward(ctx, dy):
+        x3, w, inv = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = torch.empty_like(x3)
+        dw = _headnorm_bwd(dy, x3, w, ctx.offset, inv, dx)
+        return dx, (dw if ctx.needs_input_grad[1] else None), None, None
+
+
+def head_rmsnorm(x3, w, eps: float = 1e-6, offset: float = 0.0):
+    """RMSNorm over the last dim of ``[T, heads, D]`` (per-head q / k / v norms).  ``w=None`` normalises
+    without a learned scale."""
+    if w is None:
+        w = torch.ones(x3.shape[-1], dtype=torch.float32, device=x3.device)
+    if not x3.is_cuda:
+        return _headnorm_reference(x3, w, eps, offset)
+    x3 = x3.contiguous()
+    return _HeadRmsNorm.apply(x3, w, float(offset), float(eps))
+
+
 def _headnorm_reference(x, w, eps, offset):
     xf = x.float()
     y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * (w.float() + offset)
