@@ -1,4 +1,4 @@
-// Variable-length causal attention backward (GQA, head_dim 64/128), deterministic (no atomics):
+// Variable-length causal attention backward (GQA, head_dim 64/128/256), deterministic (no atomics):
 //   1. delta[h, t] = sum_d dO * O
 //   2. dK/dV kernel: one CTA per (key tile, kv head); loops over the q heads of the group and
 //      the query tiles that can see the key tile; works on transposed scores S^T = K Q^T so
@@ -33,7 +33,10 @@ attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __re
   if (lane == 0) delta[(long long)h * total_q + t] = acc;
 }
 
-template <int D>
+// DO = output columns owned by one CTA: head_dim 256 runs as two CTAs (blockIdx.z) that each recompute
+// S and dP over the full head dimension and accumulate one 128-column half of dK / dV (dQ below), so
+// the accumulators stay at the register budget of the 128 case.
+template <int D, int DO>
 __global__ void __launch_bounds__(128)
 attn_bwd_dkv_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
                     const __nv_bfloat16* __restrict__ v, const __nv_bfloat16* __restrict__ d_o,
@@ -98,9 +101,10 @@ attn_bwd_dkv_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   if (n_iter > 0) issue(0, 0);
   cp_async_commit();
 
-  float dk_acc[D / 8][4], dv_acc[D / 8][4];
+  const int c0 = blockIdx.z * (DO / 8);  // first 8-column chunk of this CTA's output slice
+  float dk_acc[DO / 8][4], dv_acc[DO / 8][4];
 #pragma unroll
-  for (int i = 0; i < D / 8; ++i) {
+  for (int i = 0; i < DO / 8; ++i) {
     dk_acc[i][0] = dk_acc[i][1] = dk_acc[i][2] = dk_acc[i][3] = 0.f;
     dv_acc[i][0] = dv_acc[i][1] = dv_acc[i][2] = dv_acc[i][3] = 0.f;
   }
@@ -170,12 +174,12 @@ attn_bwd_dkv_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 #pragma unroll
     for (int kk = 0; kk < BT / 16; ++kk) {
 #pragma unroll
-      for (int dt = 0; dt < D / 16; ++dt) {
+      for (int dt = 0; dt < DO / 16; ++dt) {
         uint32_t b[4];
-        ldsm_b_t<CH>(b, cdO, kk * 16, dt * 2, lane);
+        ldsm_b_t<CH>(b, cdO, kk * 16, c0 + dt * 2, lane);
         mma_bf16(dv_acc[2 * dt], pf[kk], b[0], b[1]);
         mma_bf16(dv_acc[2 * dt + 1], pf[kk], b[2], b[3]);
-        ldsm_b_t<CH>(b, cQ, kk * 16, dt * 2, lane);
+        ldsm_b_t<CH>(b, cQ, kk * 16, c0 + dt * 2, lane);
         mma_bf16(dk_acc[2 * dt], dsf[kk], b[0], b[1]);
         mma_bf16(dk_acc[2 * dt + 1], dsf[kk], b[2], b[3]);
       }
@@ -188,10 +192,10 @@ attn_bwd_dkv_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   for (int h = 0; h < 2; ++h) {
     const int key = key_a + h * 8;
     if (key < lk) {
-      __nv_bfloat16* pk = dk + (long long)(k_beg + key) * dk_stride + (long long)kvh * D;
-      __nv_bfloat16* pv = dv + (long long)(k_beg + key) * dv_stride + (long long)kvh * D;
+      __nv_bfloat16* pk = dk + (long long)(k_beg + key) * dk_stride + (long long)kvh * D + c0 * 8;
+      __nv_bfloat16* pv = dv + (long long)(k_beg + key) * dv_stride + (long long)kvh * D + c0 * 8;
 #pragma unroll
-      for (int i = 0; i < D / 8; ++i) {
+      for (int i = 0; i < DO / 8; ++i) {
         *reinterpret_cast<uint32_t*>(pk + i * 8 + t4 * 2) =
             pack_bf16x2(dk_acc[i][h * 2] * scale, dk_acc[i][h * 2 + 1] * scale);
         *reinterpret_cast<uint32_t*>(pv + i * 8 + t4 * 2) = pack_bf16x2(dv_acc[i][h * 2], dv_acc[i][h * 2 + 1]);
@@ -200,7 +204,7 @@ attn_bwd_dkv_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   }
 }
 
-template <int D>
+template <int D, int DO>
 __global__ void __launch_bounds__(128)
 attn_bwd_dq_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
                    const __nv_bfloat16* __restrict__ v, const __nv_bfloat16* __restrict__ d_o,
@@ -258,9 +262,10 @@ attn_bwd_dq_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     lse_r[h] = r < lq ? lse[(long long)head * total_q + q_beg + r] * 1.4426950408889634f : INFINITY;
     delta_r[h] = r < lq ? delta[(long long)head * total_q + q_beg + r] : 0.f;
   }
-  float dq_acc[D / 8][4];
+  const int c0 = blockIdx.z * (DO / 8);
+  float dq_acc[DO / 8][4];
 #pragma unroll
-  for (int i = 0; i < D / 8; ++i) dq_acc[i][0] = dq_acc[i][1] = dq_acc[i][2] = dq_acc[i][3] = 0.f;
+  for (int i = 0; i < DO / 8; ++i) dq_acc[i][0] = dq_acc[i][1] = dq_acc[i][2] = dq_acc[i][3] = 0.f;
   const float scale_log2 = scale * 1.4426950408889634f;
 
   for (int it = 0; it < n_tiles; ++it) {
@@ -320,9 +325,9 @@ attn_bwd_dq_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 #pragma unroll
     for (int kk = 0; kk < BN / 16; ++kk) {
 #pragma unroll
-      for (int dt = 0; dt < D / 16; ++dt) {
+      for (int dt = 0; dt < DO / 16; ++dt) {
         uint32_t b[4];
-        ldsm_b_t<CH>(b, cK, kk * 16, dt * 2, lane);
+        ldsm_b_t<CH>(b, cK, kk * 16, c0 + dt * 2, lane);
         mma_bf16(dq_acc[2 * dt], dsf[kk], b[0], b[1]);
         mma_bf16(dq_acc[2 * dt + 1], dsf[kk], b[2], b[3]);
       }
@@ -334,9 +339,9 @@ attn_bwd_dq_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   for (int h = 0; h < 2; ++h) {
     const int r = row_a + h * 8;
     if (r < lq) {
-      __nv_bfloat16* p = dq + (long long)(q_beg + r) * dq_stride + (long long)head * D;
+      __nv_bfloat16* p = dq + (long long)(q_beg + r) * dq_stride + (long long)head * D + c0 * 8;
 #pragma unroll
-      for (int i = 0; i < D / 8; ++i)
+      for (int i = 0; i < DO / 8; ++i)
         *reinterpret_cast<uint32_t*>(p + i * 8 + t4 * 2) =
             pack_bf16x2(dq_acc[i][h * 2] * scale, dq_acc[i][h * 2 + 1] * scale);
     }
@@ -353,20 +358,22 @@ static int launch_bwd(const void* q, const void* k, const void* v, const void* o
                       cudaStream_t stream) {
   constexpr int smem_kv = 6 * 64 * D * 2 + 4 * 64 * 4;
   constexpr int smem_q = 6 * 64 * D * 2;
+  constexpr int DO = D > 128 ? 128 : D;
+  constexpr int NZ = D / DO;
   static bool cfg = false;
   if (!cfg) {
-    cudaFuncSetAttribute(attn_bwd_dkv_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_kv);
-    cudaFuncSetAttribute(attn_bwd_dq_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_q);
+    cudaFuncSetAttribute(attn_bwd_dkv_kernel<D, DO>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_kv);
+    cudaFuncSetAttribute(attn_bwd_dq_kernel<D, DO>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_q);
     cfg = true;
   }
   const long long nw = total_q * hq;
   attn_delta_kernel<<<(unsigned)((nw + 7) / 8), 256, 0, stream>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o,
                                                                   delta, total_q, hq, D, o_stride, do_stride);
-  attn_bwd_dkv_kernel<D><<<dim3(total_k_tiles, hkv), 128, smem_kv, stream>>>(
+  attn_bwd_dkv_kernel<D, DO><<<dim3(total_k_tiles, hkv, NZ), 128, smem_kv, stream>>>(
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (const __nv_bfloat16*)d_o, lse,
       delta, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, cu_q, cu_k, tile_prefix_k, num_seqs, hq, hkv, q_stride,
       k_stride, v_stride, do_stride, dk_stride, dv_stride, scale, causal, window);
-  attn_bwd_dq_kernel<D><<<dim3(total_q_tiles, hq), 128, smem_q, stream>>>(
+  attn_bwd_dq_kernel<D, DO><<<dim3(total_q_tiles, hq, NZ), 128, smem_q, stream>>>(
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (const __nv_bfloat16*)d_o, lse,
       delta, (__nv_bfloat16*)dq, cu_q, cu_k, tile_prefix_q, num_seqs, hq, hkv, q_stride, k_stride, v_stride,
       do_stride, dq_stride, scale, causal, window);
@@ -389,6 +396,10 @@ extern "C" int areno_attn_bwd(const void* q, const void* k, const void* v, const
   if (hq % hkv != 0) return -3;
   if (head_dim == 128)
     return launch_bwd<128>(q, k, v, o, d_o, lse, delta, dq, dk, dv, cu_q, cu_k, tile_prefix_q, tile_prefix_k,
+                           num_seqs, total_q_tiles, total_k_tiles, total_q, hq, hkv, q_stride, k_stride, v_stride,
+                           o_stride, do_stride, dq_stride, dk_stride, dv_stride, scale, causal, window, stream);
+  if (head_dim == 256)
+    return launch_bwd<256>(q, k, v, o, d_o, lse, delta, dq, dk, dv, cu_q, cu_k, tile_prefix_q, tile_prefix_k,
                            num_seqs, total_q_tiles, total_k_tiles, total_q, hq, hkv, q_stride, k_stride, v_stride,
                            o_stride, do_stride, dq_stride, dk_stride, dv_stride, scale, causal, window, stream);
   if (head_dim == 64)

@@ -440,6 +440,15 @@ extern "C" int areno_paged_decode(const void* q, const void* k_cache, const void
                                      batch, hq, hkv, max_pages, q_stride, o_stride, scale, pages_per_split, nsplit,
                                      window, stream);
   }
+  if (head_dim == 256) {
+    if (fp8)
+      return launch_decode<256, true>(q, k_cache, v_cache, k_scale, v_scale, block_table, seq_lens, out, part_o,
+                                      part_ml, batch, hq, hkv, max_pages, q_stride, o_stride, scale, pages_per_split,
+                                      nsplit, window, stream);
+    return launch_decode<256, false>(q, k_cache, v_cache, k_scale, v_scale, block_table, seq_lens, out, part_o, part_ml,
+                                     batch, hq, hkv, max_pages, q_stride, o_stride, scale, pages_per_split, nsplit,
+                                     window, stream);
+  }
   if (head_dim == 64) {
     if (fp8)
       return launch_decode<64, true>(q, k_cache, v_cache, k_scale, v_scale, block_table, seq_lens, out, part_o, part_ml,

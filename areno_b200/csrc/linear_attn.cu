@@ -163,16 +163,19 @@ conv1d_silu_decode_kernel(const __nv_bfloat16* __restrict__ x, long long x_strid
 // of the state S[dk, dv] (dk registers), so the per-token products k^T S and q^T S are
 // thread-local and k / q are broadcast from shared memory.
 //   S <- exp(g_t) S;  u = k_t^T S;  d = beta_t (v_t - u);  S <- S + k_t d^T;  o_t = scale * q_t^T S
+// With DELTA == false (beta unused) the delta correction is dropped (d = v_t): decayed linear ("lightning") attention,
+// S <- exp(g) S + k_t v_t^T.  g is read at g[t * g_stride + head]; g_stride == 0 gives a per-head constant.
 // q, k arrive l2-normalised.  state: fp32 [slots, Hv, DK, DV]; a sequence starts from its slot's
 // state unless fresh[seq] != 0 and writes the final state back (when state != nullptr).
 // ----------------------------------------------------------------------------------
-template <int DK>
+template <int DK, bool DELTA>
 __global__ void __launch_bounds__(128)
 gdn_recurrent_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, long long qk_stride,
                      const __nv_bfloat16* __restrict__ v, long long v_stride, const float* __restrict__ g,
-                     const float* __restrict__ beta, const int* __restrict__ cu, const int* __restrict__ slots,
-                     const int* __restrict__ fresh, const int* __restrict__ active, float* __restrict__ state,
-                     int Hk, int Hv, int DV, float scale, __nv_bfloat16* __restrict__ out, long long out_stride) {
+                     long long g_stride, const float* __restrict__ beta, const int* __restrict__ cu,
+                     const int* __restrict__ slots, const int* __restrict__ fresh, const int* __restrict__ active,
+                     float* __restrict__ state, int Hk, int Hv, int DV, float scale, __nv_bfloat16* __restrict__ out,
+                     long long out_stride) {
   const int seq = blockIdx.x / Hv;
   const int hv = blockIdx.x % Hv;
   const int hk = hv / (Hv / Hk);
@@ -194,12 +197,17 @@ gdn_recurrent_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
     }
     __syncthreads();
     if (j < DV) {
-      const float a = __expf(g[(long long)t * Hv + hv]);
-      const float b = beta[(long long)t * Hv + hv];
-      float u = 0.f;
+      const float a = __expf(g[(long long)t * g_stride + hv]);
+      float d = __bfloat162float(v[(long long)t * v_stride + hv * DV + j]);
+      if constexpr (DELTA) {
+        float u = 0.f;
 #pragma unroll
-      for (int i = 0; i < DK; ++i) { S[i] *= a; u += sk[i] * S[i]; }
-      const float d = b * (__bfloat162float(v[(long long)t * v_stride + hv * DV + j]) - u);
+        for (int i = 0; i < DK; ++i) { S[i] *= a; u += sk[i] * S[i]; }
+        d = beta[(long long)t * Hv + hv] * (d - u);
+      } else {
+#pragma unroll
+        for (int i = 0; i < DK; ++i) S[i] *= a;
+      }
       float o = 0.f;
 #pragma unroll
       for (int i = 0; i < DK; ++i) { S[i] += sk[i] * d; o += sq[i] * S[i]; }
@@ -285,6 +293,146 @@ rmsnorm_silu_gate_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bf
   }
 }
 
+// ----------------------------------------------------------------------------------
+// Backward of decayed linear attention  S_t = a S_{t-1} + k_t v_t^T,  o_t = scale q_t^T S_t  (a = exp(-slope_h),
+// state starts at zero).  With G_t = scale q_t dO_t^T + a G_{t+1}:
+//   dq_t = scale S_t dO_t        (forward scan, thread i owns row i of S)
+//   dk_t = G_t v_t               (reverse scan, thread i owns row i of G)
+//   dv_t = G_t^T k_t             (reverse scan, thread j owns column j of G)
+// All three are the same loop  R <- a R + own * A;  out = scale * <R, B>  with different operands, so one
+// kernel runs them as blockIdx.y = 0, 1, 2.  One block per (sequence, head); D = head_dim (q, k, v alike).
+// The broadcast vectors A, B are double-buffered in shared memory: one barrier per token.
+// ----------------------------------------------------------------------------------
+template <int D>
+__global__ void __launch_bounds__(128)
+lightning_bwd_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
+                     const __nv_bfloat16* __restrict__ v, long long qkv_stride, const __nv_bfloat16* __restrict__ d_o,
+                     long long do_stride, const float* __restrict__ slope, const int* __restrict__ cu, int H, float scale,
+                     __nv_bfloat16* __restrict__ dq, __nv_bfloat16* __restrict__ dk, __nv_bfloat16* __restrict__ dv,
+                     long long dqkv_stride) {
+  const int seq = blockIdx.x / H, h = blockIdx.x % H;
+  const int role = blockIdx.y;
+  const int lo = cu[seq], hi = cu[seq + 1];
+  const int n = hi - lo;
+  if (n <= 0) return;
+  const float a = __expf(-slope[h]);
+  const __nv_bfloat16 *own_p, *a_p, *b_p;
+  long long own_s, a_s, b_s;
+  __nv_bfloat16* out_p;
+  if (role == 0) { own_p = k; own_s = qkv_stride; a_p = v; a_s = qkv_stride; b_p = d_o; b_s = do_stride; out_p = dq; }
+  else if (role == 1) { own_p = q; own_s = qkv_stride; a_p = d_o; a_s = do_stride; b_p = v; b_s = qkv_stride; out_p = dk; }
+  else { own_p = d_o; own_s = do_stride; a_p = q; a_s = qkv_stride; b_p = k; b_s = qkv_stride; out_p = dv; }
+  __shared__ float sA[2][D], sB[2][D];
+  float R[D];
+#pragma unroll
+  for (int i = 0; i < D; ++i) R[i] = 0.f;
+  const int tid = threadIdx.x;
+  const long long col = (long long)h * D + tid;
+  for (int s = 0; s < n; ++s) {
+    const long long t = role == 0 ? lo + s : hi - 1 - s;
+    const int buf = s & 1;
+    float own = 0.f;
+    if (tid < D) {
+      sA[buf][tid] = __bfloat162float(a_p[t * a_s + col]);
+      sB[buf][tid] = __bfloat162float(b_p[t * b_s + col]);
+      own = __bfloat162float(own_p[t * own_s + col]);
+    }
+    __syncthreads();
+    if (tid < D) {
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < D; ++i) {
+        R[i] = a * R[i] + own * sA[buf][i];
+        acc += R[i] * sB[buf][i];
+      }
+      out_p[t * dqkv_stride + col] = __float2bfloat16_rn(acc * scale);
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------------
+// Group RMSNorm with a sigmoid gate: the hidden dimension is G groups of W channels, each group is
+// normalised on its own:  y[r, g, c] = x * rsqrt(mean_c x^2 + eps) * w[g, c] * sigmoid(gate[r, g, c]).
+// One warp per (row, group).  Role of areno/engine/layers/norm.py:60-105 in the reference.
+// ----------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+group_rmsnorm_gate_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gate,
+                              long long gate_stride, const float* __restrict__ w, long long rows, int G, int W,
+                              float eps, __nv_bfloat16* __restrict__ y, float* __restrict__ inv_rms) {
+  const int lane = threadIdx.x & 31;
+  const long long total = rows * G;
+  for (long long wid = (long long)blockIdx.x * 8 + (threadIdx.x >> 5); wid < total; wid += (long long)gridDim.x * 8) {
+    const long long r = wid / G;
+    const int g = (int)(wid % G);
+    const __nv_bfloat16* xr = x + (r * G + g) * W;
+    const __nv_bfloat16* gr = gate + r * gate_stride + (long long)g * W;
+    float ss = 0.f;
+    for (int c = lane; c < W; c += 32) { const float xv = __bfloat162float(xr[c]); ss += xv * xv; }
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)W + eps);
+    if (lane == 0 && inv_rms != nullptr) inv_rms[wid] = inv;
+    __nv_bfloat16* yr = y + (r * G + g) * W;
+    for (int c = lane; c < W; c += 32) {
+      const float sg = 1.f / (1.f + __expf(-__bfloat162float(gr[c])));
+      yr[c] = __float2bfloat16_rn(__bfloat162float(xr[c]) * inv * w[g * W + c] * sg);
+    }
+  }
+}
+
+// dx and dgate (one warp per (row, group)).
+__global__ void __launch_bounds__(256)
+group_rmsnorm_gate_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                              const __nv_bfloat16* __restrict__ gate, long long gate_stride,
+                              const float* __restrict__ w, const float* __restrict__ inv_rms, long long rows, int G,
+                              int W, __nv_bfloat16* __restrict__ dx, __nv_bfloat16* __restrict__ dgate) {
+  const int lane = threadIdx.x & 31;
+  const long long total = rows * G;
+  for (long long wid = (long long)blockIdx.x * 8 + (threadIdx.x >> 5); wid < total; wid += (long long)gridDim.x * 8) {
+    const long long r = wid / G;
+    const int g = (int)(wid % G);
+    const long long base = (r * G + g) * W;
+    const __nv_bfloat16* gr = gate + r * gate_stride + (long long)g * W;
+    const float inv = inv_rms[wid];
+    float dot = 0.f;
+    for (int c = lane; c < W; c += 32) {
+      const float sg = 1.f / (1.f + __expf(-__bfloat162float(gr[c])));
+      const float nx = __bfloat162float(x[base + c]) * inv;
+      const float d = __bfloat162float(dy[base + c]);
+      const float wv = w[g * W + c];
+      dgate[base + c] = __float2bfloat16_rn(d * nx * wv * sg * (1.f - sg));
+      dot += d * sg * wv * nx;          // <dn, n>
+    }
+    dot = warp_sum(dot) / (float)W;
+    for (int c = lane; c < W; c += 32) {
+      const float sg = 1.f / (1.f + __expf(-__bfloat162float(gr[c])));
+      const float nx = __bfloat162float(x[base + c]) * inv;
+      const float dn = __bfloat162float(dy[base + c]) * sg * w[g * W + c];
+      dx[base + c] = __float2bfloat16_rn(inv * (dn - nx * dot));
+    }
+  }
+}
+
+// dw partials: thread = channel (of G*W), blockIdx.y = row range; part[blockIdx.y, G*W].
+__global__ void __launch_bounds__(256)
+group_rmsnorm_gate_dw_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                             const __nv_bfloat16* __restrict__ gate, long long gate_stride,
+                             const float* __restrict__ inv_rms, long long rows, int G, int W,
+                             float* __restrict__ part) {
+  const int ch = blockIdx.x * blockDim.x + threadIdx.x;
+  const int GW = G * W;
+  if (ch >= GW) return;
+  const int g = ch / W;
+  const long long per = (rows + gridDim.y - 1) / gridDim.y;
+  const long long lo = (long long)blockIdx.y * per;
+  const long long hi = lo + per < rows ? lo + per : rows;
+  float acc = 0.f;
+  for (long long r = lo; r < hi; ++r) {
+    const float sg = 1.f / (1.f + __expf(-__bfloat162float(gate[r * gate_stride + ch])));
+    acc += __bfloat162float(dy[r * GW + ch]) * sg * __bfloat162float(x[r * GW + ch]) * inv_rms[r * G + g];
+  }
+  part[(size_t)blockIdx.y * GW + ch] = acc;
+}
+
 static inline int grid_for_elems(long long work, int per_block, int cap = 148 * 16) {
   long long g = (work + per_block - 1) / per_block;
   if (g > cap) g = cap;
@@ -354,10 +502,12 @@ extern "C" int areno_gdn_recurrent(const void* q, const void* k, long long qk_st
   if (num_seqs <= 0) return 0;
   if (DV > 128 || Hv % Hk != 0) return -3;
   const int grid = num_seqs * Hv;
+  const long long g_stride = Hv;
 #define GDN_LAUNCH(D)                                                                                             \
-  gdn_recurrent_kernel<D><<<grid, 128, 0, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k, qk_stride, \
-                                                    (const __nv_bfloat16*)v, v_stride, g, beta, cu, slots, fresh, \
-                                                    active, state, Hk, Hv, DV, scale, (__nv_bfloat16*)out, out_stride)
+  gdn_recurrent_kernel<D, true><<<grid, 128, 0, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k, qk_stride, \
+                                                    (const __nv_bfloat16*)v, v_stride, g, g_stride, beta, cu, slots, \
+                                                    fresh, active, state, Hk, Hv, DV, scale, (__nv_bfloat16*)out,  \
+                                                    out_stride)
   if (DK == 128) GDN_LAUNCH(128);
   else if (DK == 64) GDN_LAUNCH(64);
   else if (DK == 32) GDN_LAUNCH(32);
@@ -391,5 +541,76 @@ extern "C" int areno_rmsnorm_silu_gate_bwd(const void* dy, const void* x, const 
   rmsnorm_silu_gate_bwd_kernel<<<areno_rmsnorm_silu_gate_bwd_blocks(rows), 256, 0, stream>>>(
       (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)gate, gate_stride, gate_group, w, inv_rms,
       rows, D, (__nv_bfloat16*)dx, (__nv_bfloat16*)dgate, dgate_stride, dw_partial);
+  return (int)cudaGetLastError();
+}
+
+// Decayed linear attention forward (prefill chunks and decode rows; training forward with state == nullptr).
+// log_decay: fp32 [H] = -slope.  q, k, v: [T, H, D] views sharing `qkv_stride`.
+extern "C" int areno_lightning_recurrent(const void* q, const void* k, const void* v, long long qkv_stride,
+                                         const float* log_decay, const int* cu, const int* slots, const int* fresh,
+                                         const int* active, float* state, int num_seqs, int H, int D, float scale,
+                                         void* out, long long out_stride, cudaStream_t stream) {
+  if (num_seqs <= 0) return 0;
+  if (D > 128) return -3;
+  const int grid = num_seqs * H;
+#define LA_LAUNCH(DD)                                                                                                \
+  gdn_recurrent_kernel<DD, false><<<grid, 128, 0, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k, qkv_stride,  \
+                                                     (const __nv_bfloat16*)v, qkv_stride, log_decay, 0, nullptr, cu, \
+                                                     slots, fresh, active, state, H, H, DD, scale,                   \
+                                                     (__nv_bfloat16*)out, out_stride)
+  if (D == 128) LA_LAUNCH(128);
+  else if (D == 64) LA_LAUNCH(64);
+  else if (D == 32) LA_LAUNCH(32);
+  else return -2;
+#undef LA_LAUNCH
+  return (int)cudaGetLastError();
+}
+
+extern "C" int areno_lightning_bwd(const void* q, const void* k, const void* v, long long qkv_stride, const void* d_o,
+                                   long long do_stride, const float* slope, const int* cu, int num_seqs, int H, int D,
+                                   float scale, void* dq, void* dk, void* dv, long long dqkv_stride,
+                                   cudaStream_t stream) {
+  if (num_seqs <= 0) return 0;
+  const dim3 grid(num_seqs * H, 3);
+#define LB_LAUNCH(DD)                                                                                               \
+  lightning_bwd_kernel<DD><<<grid, 128, 0, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k,              \
+                                                     (const __nv_bfloat16*)v, qkv_stride, (const __nv_bfloat16*)d_o, \
+                                                     do_stride, slope, cu, H, scale, (__nv_bfloat16*)dq,             \
+                                                     (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, dqkv_stride)
+  if (D == 128) LB_LAUNCH(128);
+  else if (D == 64) LB_LAUNCH(64);
+  else if (D == 32) LB_LAUNCH(32);
+  else return -2;
+#undef LB_LAUNCH
+  return (int)cudaGetLastError();
+}
+
+extern "C" int areno_group_rmsnorm_gate_fwd(const void* x, const void* gate, long long gate_stride, const float* w,
+                                            long long rows, int G, int W, float eps, void* y, float* inv_rms,
+                                            cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  group_rmsnorm_gate_fwd_kernel<<<grid_for_elems(rows * G, 8), 256, 0, stream>>>(
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)gate, gate_stride, w, rows, G, W, eps, (__nv_bfloat16*)y, inv_rms);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int areno_group_rmsnorm_gate_dw_blocks(long long rows) {
+  long long b = (rows + 63) / 64;
+  if (b > 64) b = 64;
+  return (int)(b < 1 ? 1 : b);
+}
+
+// dw_partial: fp32 [areno_group_rmsnorm_gate_dw_blocks(rows), G * W], folded by the caller.
+extern "C" int areno_group_rmsnorm_gate_bwd(const void* dy, const void* x, const void* gate, long long gate_stride,
+                                            const float* w, const float* inv_rms, long long rows, int G, int W,
+                                            void* dx, void* dgate, float* dw_partial, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  group_rmsnorm_gate_bwd_kernel<<<grid_for_elems(rows * G, 8), 256, 0, stream>>>(
+      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)gate, gate_stride, w, inv_rms, rows, G, W,
+      (__nv_bfloat16*)dx, (__nv_bfloat16*)dgate);
+  const dim3 grid((G * W + 255) / 256, areno_group_rmsnorm_gate_dw_blocks(rows));
+  group_rmsnorm_gate_dw_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
+                                                         (const __nv_bfloat16*)gate, gate_stride, inv_rms, rows, G, W,
+                                                         dw_partial);
   return (int)cudaGetLastError();
 }

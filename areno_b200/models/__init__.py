@@ -24,6 +24,13 @@ def register_models() -> None:
     except ImportError:
         pass
     try:
+        from . import bailing_adapter
+
+        for cls in bailing_adapter.ADAPTERS:
+            register_adapter(cls)
+    except ImportError:
+        pass
+    try:
         from . import hybrid_adapters
 
         for cls in hybrid_adapters.ADAPTERS:

@@ -80,6 +80,8 @@ class Attention(nn.Module):
             self.q_norm = RMSNorm(cfg.head_dim, cfg.rms_norm_eps, dtype, device, cfg.norm_weight_offset)
             self.k_norm = RMSNorm(cfg.head_dim, cfg.rms_norm_eps, dtype, device, cfg.norm_weight_offset)
         self.scale = cfg.attention_softmax_scale or cfg.head_dim ** -0.5
+        # rotary layout; subclasses may install their own frequency table (e.g. rotation of the trailing channels)
+        self.rot_dim, self.rope_interleaved, self.inv_freq = cfg.rotary_dim, cfg.rope_interleaved, None
         self.window = 0
         if cfg.sliding_window and cfg.layer_types is not None and cfg.layer_types[layer_idx] == "sliding_attention":
             self.window = int(cfg.sliding_window)
@@ -97,8 +99,8 @@ class Attention(nn.Module):
         if isinstance(meta, TrainMeta):
             return attn_ops.qkv_attention(
                 qkv, positions, meta.varlen, self.hq, self.hkv, self.d, scale=self.scale, theta=cfg.rope_theta,
-                rot_dim=cfg.rotary_dim, interleaved=cfg.rope_interleaved, causal=True, window=self.window,
-                q_norm_w=qw, k_norm_w=kw, norm_eps=cfg.rms_norm_eps, norm_offset=cfg.norm_weight_offset)
+                rot_dim=self.rot_dim, inv_freq=self.inv_freq, interleaved=self.rope_interleaved, causal=True,
+                window=self.window, q_norm_w=qw, k_norm_w=kw, norm_eps=cfg.rms_norm_eps, norm_offset=cfg.norm_weight_offset)
         return self._infer(qkv, positions, meta, qw, kw)
 
     def _infer(self, qkv, positions, meta: InferMeta, qw, kw):
@@ -116,7 +118,7 @@ class Attention(nn.Module):
                 k3.copy_(attn_ops._headnorm_reference(k3, kw, cfg.rms_norm_eps, cfg.norm_weight_offset))
         kc, vc, ks, vs = self.kv_cache
         pa.rope_append_kv(qkv, positions, meta.slot_mapping, kc, vc, ks, vs, hq, hkv, d, theta=cfg.rope_theta,
-                          rot_dim=cfg.rotary_dim, interleaved=cfg.rope_interleaved)
+                          rot_dim=self.rot_dim, inv_freq=self.inv_freq, interleaved=self.rope_interleaved)
         q = qkv[:, : hq * d].unflatten(1, (hq, d))
         if meta.mode == "decode":
             out = pa.paged_decode(q, kc, vc, ks, vs, meta.block_table, meta.seq_lens, self.scale,

@@ -1,5 +1,6 @@
-"""Ops of the hybrid (linear-attention) layers: causal depthwise conv1d + SiLU, the gated delta rule
-and RMSNorm with a SiLU gate.
+"""Ops of the hybrid (linear-attention) layers: causal depthwise conv1d + SiLU, the gated delta rule,
+RMSNorm with a SiLU gate, decayed linear ("lightning") attention with forward and backward kernels, and
+group RMSNorm with a sigmoid gate.
 
 Inference (prefill and decode) runs the CUDA kernels of ``csrc/linear_attn.cu`` with per-slot conv
 and recurrent-state caches.  Training uses the CUDA conv / gated-norm kernels (forward and backward);
@@ -24,6 +25,11 @@ _lib.register_signature("areno_conv1d_silu_bwd", "plpppplliiplpp")
 _lib.register_signature("areno_conv1d_update_hist", "plpppiiipp")
 _lib.register_signature("areno_conv1d_silu_decode", "plppiiipplp")
 _lib.register_signature("areno_gdn_recurrent", "pplplpppppppiiiiifplp")
+_lib.register_signature("areno_lightning_recurrent", "ppplppppppiiifplp")
+_lib.register_signature("areno_lightning_bwd", "ppplplppiiifppplp")
+_lib.register_signature("areno_group_rmsnorm_gate_fwd", "pplpliifppp")
+_lib.register_signature("areno_group_rmsnorm_gate_dw_blocks", "l")
+_lib.register_signature("areno_group_rmsnorm_gate_bwd", "ppplppliipppp")
 _lib.register_signature("areno_rmsnorm_silu_gate_fwd", "ppliplifppp")
 _lib.register_signature("areno_rmsnorm_silu_gate_bwd_blocks", "l")
 _lib.register_signature("areno_rmsnorm_silu_gate_bwd", "ppplipplipplpp")
@@ -264,3 +270,118 @@ def rmsnorm_silu_gate(x, gate, w, eps: float):
         return rmsnorm_silu_gate_reference(x, gate, w, eps)
     assert x.is_contiguous() and gate.stride(2) == 1 and gate.stride(1) == x.shape[2] and w.dtype == torch.float32
     return _RmsnormSiluGate.apply(x, gate, w, float(eps))
+
+
+# ---------------------------------------------------------------- decayed linear attention
+def lightning_attention_reference(q, k, v, slope, lens, scale, state=None):
+    """``S_t = exp(-slope_h) S_{t-1} + k_t v_t^T``, ``o_t = scale q_t^T S_t`` per sequence, in fp32 PyTorch
+    (differentiable).  ``q, k, v``: [T, H, D]; ``slope``: [H]; ``state``: optional list of [H, D, D] start
+    states.  Returns ``(out [T, H, D], final states)``.  Semantics of the reference's
+    ``chunk_lightning_attn`` / ``seg_la_fwd`` calls (``areno/models/bailing/model.py:904-1003``)."""
+    decay = torch.exp(-slope.float())[:, None, None]
+    outs, finals, off = [], [], 0
+    for i, n in enumerate(lens):
+        s = torch.zeros((q.shape[1], q.shape[2], v.shape[2]), dtype=torch.float32, device=q.device) \
+            if state is None or state[i] is None else state[i].float()
+        for t in range(off, off + n):
+            s = decay * s + k[t].float()[:, :, None] * v[t].float()[:, None, :]
+            outs.append(torch.einsum("hd,hde->he", q[t].float(), s) * scale)
+        finals.append(s)
+        off += n
+    out = torch.stack(outs, 0) if outs else torch.zeros_like(v, dtype=torch.float32)
+    return out.to(v.dtype), finals
+
+
+def _same_layout(q, k, v):
+    d = q.shape[2]
+    return all(x.stride(2) == 1 and x.stride(1) == d and x.stride(0) == q.stride(0) and x.shape == q.shape for x in (q, k, v))
+
+
+def lightning_recurrent(q, k, v, slope, cu, scale, *, state_cache=None, slots=None, fresh=None, active=None):
+    """CUDA scan (inference prefill chunks, decode rows, training forward).  ``q, k, v``: [T, H, D] views
+    with one shared row stride; ``state_cache`` fp32 [slots, H, D, D] is read unless ``fresh[seq]`` and
+    written in place."""
+    assert _same_layout(q, k, v) and q.dtype == torch.bfloat16
+    t, h, d = q.shape
+    out = torch.empty((t, h, d), dtype=q.dtype, device=q.device)
+    log_decay = (-slope.float()).contiguous()
+    _lib.call("areno_lightning_recurrent", q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), log_decay.data_ptr(),
+              cu.data_ptr(), _lib.ptr(slots), _lib.ptr(fresh), _lib.ptr(active), _lib.ptr(state_cache), cu.numel() - 1,
+              h, d, float(scale), out.data_ptr(), out.stride(0), _lib.stream())
+    return out
+
+
+class _Lightning(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, slope, cu, scale):
+        out = lightning_recurrent(q, k, v, slope, cu, scale)
+        ctx.save_for_backward(q, k, v, slope, cu)
+        ctx.scale = scale
+        return out
+
+    @staticmethod
+    def backward(ctx, d_o):
+        q, k, v, slope, cu = ctx.saved_tensors
+        t, h, d = q.shape
+        d_o = d_o.contiguous()
+        grads = torch.empty((3, t, h, d), dtype=q.dtype, device=q.device)
+        _lib.call("areno_lightning_bwd", q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), d_o.data_ptr(),
+                  d_o.stride(0), slope.data_ptr(), cu.data_ptr(), cu.numel() - 1, h, d, float(ctx.scale),
+                  grads[0].data_ptr(), grads[1].data_ptr(), grads[2].data_ptr(), grads.stride(1), _lib.stream())
+        return grads[0], grads[1], grads[2], None, None, None
+
+
+def lightning_attention(q, k, v, slope, lens, scale, cu=None):
+    """Differentiable decayed linear attention over packed sequences (training).  ``slope`` fp32 [H]."""
+    if not q.is_cuda:
+        return lightning_attention_reference(q, k, v, slope, lens, scale)[0]
+    if cu is None:
+        cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0).tolist()), dtype=torch.int32, device=q.device)
+    if not _same_layout(q, k, v):
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    return _Lightning.apply(q, k, v, slope.float().contiguous(), cu, float(scale))
+
+
+# -------------------------------------------------------------- group rmsnorm * sigmoid(gate)
+def group_rmsnorm_sigmoid_gate_reference(x, gate, w, eps):
+    g, width = w.shape
+    xf = x.float().unflatten(-1, (g, width))
+    y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w.float()
+    return (y.flatten(-2) * torch.sigmoid(gate.float())).to(x.dtype)
+
+
+class _GroupNormGate(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, gate, w, eps):
+        rows = x.shape[0]
+        g, width = w.shape
+        y = torch.empty_like(x)
+        inv = torch.empty(rows * g, dtype=torch.float32, device=x.device)
+        _lib.call("areno_group_rmsnorm_gate_fwd", x.data_ptr(), gate.data_ptr(), gate.stride(0), w.data_ptr(), rows, g,
+                  width, float(eps), y.data_ptr(), inv.data_ptr(), _lib.stream())
+        ctx.save_for_backward(x, gate, w, inv)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, gate, w, inv = ctx.saved_tensors
+        rows = x.shape[0]
+        g, width = w.shape
+        dy = dy.contiguous()
+        dx, dgate = torch.empty_like(x), torch.empty_like(x)
+        nblk = _lib.fn("areno_group_rmsnorm_gate_dw_blocks")(rows)
+        part = torch.empty((nblk, g * width), dtype=torch.float32, device=x.device)
+        _lib.call("areno_group_rmsnorm_gate_bwd", dy.data_ptr(), x.data_ptr(), gate.data_ptr(), gate.stride(0),
+                  w.data_ptr(), inv.data_ptr(), rows, g, width, dx.data_ptr(), dgate.data_ptr(), part.data_ptr(),
+                  _lib.stream())
+        return dx, dgate, part.sum(0).view(g, width).to(w.dtype), None
+
+
+def group_rmsnorm_sigmoid_gate(x, gate, w, eps: float):
+    """``x [T, G*W]`` (contiguous) normalised per group of ``W`` channels, scaled by ``w`` (fp32 [G, W]) and
+    multiplied by ``sigmoid(gate)``; ``gate [T, G*W]`` may have any row stride.  Role of
+    ``GroupRMSNormSigmoidGate`` (``areno/engine/layers/norm.py:60-105``)."""
+    if not x.is_cuda:
+        return group_rmsnorm_sigmoid_gate_reference(x, gate, w, eps)
+    assert x.is_contiguous() and gate.stride(1) == 1 and w.dtype == torch.float32 and w.is_contiguous()
+    return _GroupNormGate.apply(x, gate, w, float(eps))

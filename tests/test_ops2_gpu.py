@@ -41,7 +41,7 @@ def _fill_cache(fp8, hq, hkv, d, lens, theta=1e6):
 
 
 @pytest.mark.parametrize("fp8", [False, True])
-@pytest.mark.parametrize("hq,hkv,d", [(28, 4, 128), (8, 8, 64), (32, 2, 128)])
+@pytest.mark.parametrize("hq,hkv,d", [(28, 4, 128), (8, 8, 64), (32, 2, 128), (8, 2, 256)])
 def test_rope_append_and_paged_decode(fp8, hq, hkv, d):
     lens = [1, 63, 64, 65, 300, 1000]
     qkv, qkv_ref, cache, cache_ref, block_table = _fill_cache(fp8, hq, hkv, d, lens)

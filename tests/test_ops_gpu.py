@@ -194,6 +194,8 @@ ATTN_CASES = [
     ([16, 40], [80, 40], 4, 2, 128, True, 0),
     ([150], None, 2, 1, 128, False, 0),
     ([260, 90], None, 2, 1, 128, True, 96),
+    ([100, 200], None, 4, 2, 256, True, 0),      # head_dim 256: backward runs as two 128-column CTAs
+    ([260, 90], [300, 90], 2, 1, 256, True, 96),
 ]
 
 
