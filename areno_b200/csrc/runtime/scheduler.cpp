@@ -220,6 +220,15 @@ int areno_sched_active_extent(void* h) {
   return ext;
 }
 
+// Longest context among the decoding slots (tokens with KV after the planned step); 0 when none decode.
+int areno_sched_max_seq_len(void* h) {
+  auto* s = static_cast<Scheduler*>(h);
+  int m = 0;
+  for (auto& sl : s->slots)
+    if (sl.used && !sl.prefilling) m = std::max(m, sl.seq_len);
+  return m;
+}
+
 // Number of slots that are decoding (prompt fully prefilled).
 int areno_sched_num_decoding(void* h) {
   auto* s = static_cast<Scheduler*>(h);

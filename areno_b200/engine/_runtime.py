@@ -42,7 +42,7 @@ def lib():
             l.areno_sched_slot_request.argtypes = [_P, _I]
             l.areno_sched_slot_request.restype = _L
             for name in ("num_running", "num_waiting", "num_free_pages", "active_extent", "num_decoding",
-                         "clear_waiting"):
+                         "clear_waiting", "max_seq_len"):
                 getattr(l, f"areno_sched_{name}").argtypes = [_P]
             l.areno_pack_indices.argtypes = [_P, _I, _I, _P, _P, _P, _P, _P]
             l.areno_pack_indices.restype = _L
@@ -143,6 +143,11 @@ class Scheduler:
     @property
     def num_decoding(self) -> int:
         return self._l.areno_sched_num_decoding(self._h)
+
+    @property
+    def max_seq_len(self) -> int:
+        """Longest context among the decoding slots, counting the token of the step being planned."""
+        return self._l.areno_sched_max_seq_len(self._h)
 
     def clear_waiting(self) -> int:
         return self._l.areno_sched_clear_waiting(self._h)

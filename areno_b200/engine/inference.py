@@ -239,7 +239,7 @@ class InferenceEngine:
             if updates:
                 self._push_block_updates(updates)
             extent = self.sched.active_extent
-            self._decode(_pick_bucket(self.buckets, extent))
+            self._decode(_pick_bucket(self.buckets, extent), self._context_bucket(self.sched.max_seq_len + 1))
             self.sched.advance(1)
             self.step_count += 1
             self._snapshot()
@@ -419,7 +419,17 @@ class InferenceEngine:
         return tok, lp
 
     # ----------------------------------------------------------------- decode
-    def _decode_body(self, b: int):
+    def _context_bucket(self, tokens: int) -> int:
+        """Static bound on the context length of a decode step: the next power-of-two number of pages.  The
+        attention launch (number of KV splits) is sized for this bound instead of the model length, and a
+        captured graph is kept per bound."""
+        pages = max(1, (tokens + PAGE - 1) // PAGE)
+        cap = 4
+        while cap < pages:
+            cap *= 2
+        return min(cap * PAGE, self.max_pages * PAGE)
+
+    def _decode_body(self, b: int, ctx_cap: int | None = None):
         if self.cuda:
             klib.call("areno_decode_prepare", self.seq_len.data_ptr(), self.active.data_ptr(),
                       self.last_token.data_ptr(), self.block_table.data_ptr(), self.max_pages, PAGE, b,
@@ -434,7 +444,7 @@ class InferenceEngine:
             self.g_attn_lens[:b] = torch.where(act, pos + 1, torch.zeros_like(pos))
             self.g_input_ids[:b] = torch.where(act, self.last_token[:b], torch.zeros_like(self.last_token[:b]))
         meta = InferMeta(mode="decode", slot_mapping=self.g_slot_mapping[:b], block_table=self.block_table[:b],
-                         seq_lens=self.g_attn_lens[:b], max_context=self.max_model_len)
+                         seq_lens=self.g_attn_lens[:b], max_context=ctx_cap or self.max_model_len)
         out = self.model(self.g_input_ids[:b], self.g_positions[:b], meta)
         self._sample(out.logits_shard, self.gen_count[:b], self.row_uid[:b], self.sampled[:b], self.sampled_lp[:b])
         if self.cuda:
@@ -458,22 +468,22 @@ class InferenceEngine:
                 elif g + 1 >= int(self.max_new[i]):
                     self.finish[i], self.active[i] = 2, 0
 
-    def _decode(self, b: int):
+    def _decode(self, b: int, ctx_cap: int | None = None):
         self.decode_tokens += self.sched.num_decoding
         if self.eager:
-            self._decode_body(b)
+            self._decode_body(b, ctx_cap)
             return
-        key = (b, self._graph_key)
+        key = (b, ctx_cap, self._graph_key)
         entry = self._graphs.get(key)
         if entry is None:
             before = klib.launch_count
-            graph = self._capture(b)
+            graph = self._capture(b, ctx_cap)
             entry = (graph, (klib.launch_count - before) // 3)  # two warm-up passes + the captured one
             self._graphs[key] = entry
         entry[0].replay()
         klib.launch_count += entry[1]
 
-    def _capture(self, b: int):
+    def _capture(self, b: int, ctx_cap: int | None = None):
         # Warm up on a side stream (allocations, lazy module state), then capture.  The warm-up and
         # the capture pass run real decode steps on the slot state, so that state is saved and
         # restored around them.
@@ -485,11 +495,11 @@ class InferenceEngine:
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             for _ in range(2):
-                self._decode_body(b)
+                self._decode_body(b, ctx_cap)
         torch.cuda.current_stream().wait_stream(side)
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            self._decode_body(b)
+            self._decode_body(b, ctx_cap)
         self.active.copy_(active_real)
         for dst, src in zip((self.seq_len, self.active, self.last_token, self.gen_count, self.finish), saved[:5]):
             dst.copy_(src)

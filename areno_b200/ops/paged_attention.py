@@ -129,12 +129,13 @@ def paged_decode(q, k_cache, v_cache, k_scale, v_scale, block_table, seq_lens, s
     fp8 = k_cache.dtype == torch.uint8
     max_pages = block_table.shape[1]
     cap_pages = max_pages if max_context is None else min(max_pages, (max_context + PAGE - 1) // PAGE)
-    pages_per_split = 4
-    nsplit = max(1, (cap_pages + pages_per_split - 1) // pages_per_split)
-    # keep the number of CTAs reasonable for very long capacities
-    while nsplit > 32:
-        pages_per_split *= 2
-        nsplit = (cap_pages + pages_per_split - 1) // pages_per_split
+    # Split the KV range only as far as it takes to fill the machine (two resident CTAs per SM): with enough
+    # (sequence, kv head) pairs every CTA streams its whole context and writes the output itself, and
+    # neither partials nor the merge kernel exist.  A split is never shorter than two pages.
+    base = b * hkv * ((hq // hkv + 15) // 16)
+    want = max(1, min((2 * 148 + base // 2) // base, cap_pages // 2, 32))
+    pages_per_split = (cap_pages + want - 1) // want
+    nsplit = (cap_pages + pages_per_split - 1) // pages_per_split
     if out is None:
         out = torch.empty((b, hq, d), dtype=q.dtype, device=q.device)
     part_o = part_ml = None

@@ -226,7 +226,42 @@ def case_moe_grouped():
         2.0 * (e * 2 * inter * h + tokens * k * (h + 2 * inter)), f"{tokens} tokens x top-{k} of {e} experts, {h}->{2 * inter}"
 
 
+def case_decode_step(batch: int = 64, ctx: int = 512):
+    """One decode step of the benchmark model (Qwen2.5-7B shape, random weights) replayed from its CUDA graph:
+    ``batch`` running sequences with ``ctx`` cached tokens each."""
+    from ..engine.config import ModelConfig
+    from ..engine.inference import InferenceEngine, SamplingParams
+    from ..models.dense import DenseCausalLM, init_weights
+    from ..ops.paged_attention import PAGE
+    from ..parallel.context import single_process_context
+
+    dev = torch.device("cuda", 0)
+    single_process_context(dev)
+    cfg = ModelConfig(model_type="qwen2", vocab_size=152064, hidden_size=3584, intermediate_size=18944,
+                      num_hidden_layers=28, num_attention_heads=28, num_key_value_heads=4, head_dim=128, qkv_bias=True,
+                      qk_norm=False, tie_word_embeddings=False, rope_theta=1e6)
+    model = DenseCausalLM(cfg, device=dev)
+    init_weights(model, 0)
+    eng = InferenceEngine(model, cfg.vocab_size, dev, max_slots=batch, max_model_len=ctx + 512)
+    eng.begin(SamplingParams(temperature=1.0), (), 16)
+    with torch.no_grad():
+        eng.active[:batch] = 1
+        eng.seq_len[:batch] = ctx
+        eng.max_new[:batch] = 4096
+        eng.block_table.copy_(torch.arange(batch * eng.max_pages, dtype=torch.int32, device=dev).view(batch, eng.max_pages))
+    weights = sum(p.numel() * p.element_size() for n, p in model.named_parameters() if not n.startswith("embed"))
+    kv = 28 * 2 * batch * ctx * 4 * 128 * 2
+    assert eng.max_pages * PAGE >= ctx + 64
+
+    def run():
+        with torch.no_grad():
+            eng._decode(batch, eng._context_bucket(ctx + 1))
+
+    return run, 0.0, float(weights + kv), f"B={batch} ctx={ctx}, 7B shape, graph replay (weights {weights / 1e9:.1f} GB + KV {kv / 1e9:.2f} GB)"
+
+
 CASES = {
+    "decode_step": case_decode_step,
     "gemm_fwd": case_gemm_fwd, "gemm_dgrad": case_gemm_dgrad, "gemm_wgrad": case_gemm_wgrad,
     "gemm_decode_down": case_gemm_decode_down, "gemm_decode_gate_up": case_gemm_decode_gate_up,
     "splitk_rmsnorm": case_splitk_rmsnorm, "attn_fwd": case_attn_fwd, "attn_bwd": case_attn_bwd,
@@ -235,7 +270,7 @@ CASES = {
 }
 
 
-def run_case(name: str, iters: int, warmup: int) -> dict:
+def run_case(name: str, iters: int, warmup: int, profile_last: bool = False) -> dict:
     fn, flops, nbytes, note = CASES[name]()
     for _ in range(warmup):
         fn()
@@ -247,6 +282,12 @@ def run_case(name: str, iters: int, warmup: int) -> dict:
     end.record()
     torch.cuda.synchronize()
     us = start.elapsed_time(end) * 1e3 / iters
+    if profile_last:
+        # one more call inside a profiler range (for `ncu --profile-from-start off`); never timed
+        torch.cuda.profiler.start()
+        fn()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
     peaks, origin = load_peaks()
     out = {"case": name, "shape": note, "us_per_call": round(us, 2), "peaks": origin}
     if flops:
@@ -268,13 +309,15 @@ def main(argv=None) -> int:
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--list", action="store_true")
+    ap.add_argument("--profile-last", action="store_true",
+                    help="run one extra, untimed call per case inside a cudaProfilerStart/Stop range")
     args = ap.parse_args(argv)
     if args.list:
         print("\n".join(CASES))
         return 0
     names = list(CASES) if args.case == "all" else [c.strip() for c in args.case.split(",")]
     for name in names:
-        print(json.dumps(run_case(name, args.iters, args.warmup)), flush=True)
+        print(json.dumps(run_case(name, args.iters, args.warmup, args.profile_last)), flush=True)
         torch.cuda.empty_cache()
     return 0
 
