@@ -34,6 +34,8 @@ rope_append_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ posi
                    const int* __restrict__ slot_mapping, const float* __restrict__ inv_freq, void* __restrict__ k_cache,
                    void* __restrict__ v_cache, float* __restrict__ k_scale, float* __restrict__ v_scale, long long tokens,
                    int hq, int hkv, int D, int rot_dim, float theta, int interleaved, int page_size) {
+  pdl_trigger();
+  pdl_wait();
   const int heads = hq + 2 * hkv;
   const long long w = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (w >= tokens * heads) return;
@@ -109,6 +111,8 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const void* __restrict_
   using SM = DecodeSmem<D, FP8>;
   constexpr int CH = D / 8;
   extern __shared__ __align__(128) uint8_t smem_attn[];
+  pdl_trigger();
+  pdl_wait();
   uint8_t* stage_base = smem_attn;
   __nv_bfloat16* deqK = reinterpret_cast<__nv_bfloat16*>(smem_attn + SM::kStages * SM::kStageBytes);
   __nv_bfloat16* deqV = deqK + kPage * D;
@@ -351,6 +355,8 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const void* __restrict_
 __global__ void __launch_bounds__(256)
 decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out,
                     int batch, int hq, int D, int nsplit, long long o_stride, float scale) {
+  pdl_trigger();
+  pdl_wait();
   const int w = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (w >= batch * hq) return;
   const int lane = threadIdx.x & 31;
@@ -390,13 +396,13 @@ static int launch_decode(const void* q, const void* k_cache, const void* v_cache
   }
   const int group = hq / hkv;
   dim3 grid(batch, hkv * ((group + 15) / 16), nsplit);
-  paged_decode_kernel<D, FP8><<<grid, 128, SM::kTotal, stream>>>(
-      (const __nv_bfloat16*)q, k_cache, v_cache, k_scale, v_scale, block_table, seq_lens, (__nv_bfloat16*)out, part_o,
-      part_ml, hq, hkv, max_pages, q_stride, o_stride, scale, pages_per_split, nsplit, window);
-  if (nsplit > 1)
-    decode_merge_kernel<<<(batch * hq + 7) / 8, 256, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, batch, hq, D,
-                                                                 nsplit, o_stride, scale);
-  return (int)cudaGetLastError();
+  cudaError_t e = launch_pdl(paged_decode_kernel<D, FP8>, grid, dim3(128), SM::kTotal, stream, (const __nv_bfloat16*)q,
+                             k_cache, v_cache, k_scale, v_scale, block_table, seq_lens, (__nv_bfloat16*)out, part_o,
+                             part_ml, hq, hkv, max_pages, q_stride, o_stride, scale, pages_per_split, nsplit, window);
+  if (e == cudaSuccess && nsplit > 1)
+    e = launch_pdl(decode_merge_kernel, dim3((batch * hq + 7) / 8), dim3(256), 0, stream, (const float*)part_o,
+                   (const float*)part_ml, (__nv_bfloat16*)out, batch, hq, D, nsplit, o_stride, scale);
+  return (int)e;
 }
 
 }  // namespace areno
@@ -412,15 +418,16 @@ extern "C" int areno_rope_append_kv(void* qkv, const int* positions, const int* 
   if (tokens <= 0) return 0;
   const long long nw = tokens * (hq + 2 * hkv);
   const unsigned grid = (unsigned)((nw + 7) / 8);
+  cudaError_t e;
   if (fp8)
-    rope_append_kernel<true><<<grid, 256, 0, stream>>>((__nv_bfloat16*)qkv, positions, slot_mapping, inv_freq, k_cache,
-                                                       v_cache, k_scale, v_scale, tokens, hq, hkv, head_dim, rot_dim,
-                                                       theta, interleaved, page_size);
+    e = launch_pdl(rope_append_kernel<true>, dim3(grid), dim3(256), 0, stream, (__nv_bfloat16*)qkv, positions,
+                   slot_mapping, inv_freq, k_cache, v_cache, k_scale, v_scale, tokens, hq, hkv, head_dim, rot_dim, theta,
+                   interleaved, page_size);
   else
-    rope_append_kernel<false><<<grid, 256, 0, stream>>>((__nv_bfloat16*)qkv, positions, slot_mapping, inv_freq, k_cache,
-                                                        v_cache, k_scale, v_scale, tokens, hq, hkv, head_dim, rot_dim,
-                                                        theta, interleaved, page_size);
-  return (int)cudaGetLastError();
+    e = launch_pdl(rope_append_kernel<false>, dim3(grid), dim3(256), 0, stream, (__nv_bfloat16*)qkv, positions,
+                   slot_mapping, inv_freq, k_cache, v_cache, k_scale, v_scale, tokens, hq, hkv, head_dim, rot_dim, theta,
+                   interleaved, page_size);
+  return (int)e;
 }
 
 // part_o: fp32 [batch, hq, nsplit, D]; part_ml: fp32 [batch, hq, nsplit, 2] (only used when nsplit > 1).

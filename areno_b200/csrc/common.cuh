@@ -9,6 +9,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 namespace areno {
 
@@ -36,6 +37,43 @@ __device__ __forceinline__ void report_status(int* status, int code, int stage) 
 #ifndef ARENO_WAIT_LIMIT
 #define ARENO_WAIT_LIMIT (1u << 20)
 #endif
+
+// ----------------------------------------------------------------------------------
+// Programmatic dependent launch.  A kernel launched through launch_pdl may become resident while
+// the previous kernel of the stream is still running; it must execute pdl_wait() (which returns
+// once that kernel has completed and its writes are visible) before it touches global memory, in
+// every CTA and before any early return, so that its own completion still implies the
+// completion of everything before it.  pdl_trigger() lets the NEXT kernel of the stream start
+// its prologue; a kernel that acquires TMEM calls it only after the allocation, so that a
+// dependent CTA can never hold TMEM that a not-yet-set-up CTA of this grid still needs.
+// Both are no-ops for kernels launched the ordinary way.  ARENO_PDL=0 turns the launch attribute off.
+// ----------------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("ARENO_PDL");
+    return !(e != nullptr && e[0] == '0');
+  }();
+  return on;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));

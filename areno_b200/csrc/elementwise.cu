@@ -334,6 +334,8 @@ __device__ __forceinline__ float act_bwd(float g, int kind) {
 __global__ void __launch_bounds__(256)
 gated_act_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out, long long rows, int I,
                      int kind) {
+  pdl_trigger();
+  pdl_wait();
   const int nvec = I >> 3;
   const long long total = rows * nvec;
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
@@ -505,6 +507,20 @@ using namespace areno;
     else return -2;                                                              \
   } while (0)
 
+// Same dispatch through launch_pdl (kernels that start with pdl_trigger / pdl_wait).
+#define RMS_DISPATCH_PDL(KERNEL, H, ...)                                                                  \
+  do {                                                                                                    \
+    const int nvec_ = (H) >> 3;                                                                           \
+    cudaError_t e_ = cudaSuccess;                                                                         \
+    if (nvec_ <= 128) e_ = launch_pdl(KERNEL<128, 1>, dim3(grid), dim3(128), 0, stream, __VA_ARGS__);     \
+    else if (nvec_ <= 256) e_ = launch_pdl(KERNEL<128, 2>, dim3(grid), dim3(128), 0, stream, __VA_ARGS__); \
+    else if (nvec_ <= 512) e_ = launch_pdl(KERNEL<256, 2>, dim3(grid), dim3(256), 0, stream, __VA_ARGS__); \
+    else if (nvec_ <= 1024) e_ = launch_pdl(KERNEL<256, 4>, dim3(grid), dim3(256), 0, stream, __VA_ARGS__); \
+    else if (nvec_ <= 2048) e_ = launch_pdl(KERNEL<512, 4>, dim3(grid), dim3(512), 0, stream, __VA_ARGS__); \
+    else return -2;                                                                                       \
+    if (e_ != cudaSuccess) return (int)e_;                                                                \
+  } while (0)
+
 extern "C" int areno_rmsnorm_fwd(const void* x, const void* residual, const void* w, int wf32, float w_offset,
                                  void* y, void* h_out, float* inv_rms, long long rows, int H, float eps,
                                  cudaStream_t stream) {
@@ -544,9 +560,8 @@ extern "C" int areno_rmsnorm_bwd(const void* dy, const void* h, const void* w, i
 extern "C" int areno_gated_act_fwd(const void* x, void* out, long long rows, int I, int kind, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (I % 8 != 0) return -3;
-  gated_act_fwd_kernel<<<grid_for(rows * (I / 8), 256), 256, 0, stream>>>((const __nv_bfloat16*)x,
-                                                                         (__nv_bfloat16*)out, rows, I, kind);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(gated_act_fwd_kernel, dim3(grid_for(rows * (I / 8), 256)), dim3(256), 0, stream,
+                         (const __nv_bfloat16*)x, (__nv_bfloat16*)out, rows, I, kind);
 }
 
 extern "C" int areno_gated_act_bwd(const void* dout, const void* x, void* dx, long long rows, int I, int kind,
@@ -646,6 +661,8 @@ splitk_residual_rmsnorm_kernel(const float* __restrict__ ws, int splits, long lo
                                float w_offset, __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ h_out,
                                int rows, int H, float eps) {
   __shared__ float red[32];
+  pdl_trigger();
+  pdl_wait();
   const int nvec = H >> 3;
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const size_t base = (size_t)row * H;
@@ -711,8 +728,8 @@ extern "C" int areno_splitk_residual_rmsnorm(const float* ws, int splits, long l
   if (rows <= 0) return 0;
   if (H % 8 != 0 || splits < 1 || w == nullptr) return -3;
   const int grid = (int)(rows < 148 * 32 ? rows : 148 * 32);
-  RMS_DISPATCH(splitk_residual_rmsnorm_kernel, H, ws, splits, split_stride, (const __nv_bfloat16*)residual, w, wf32,
-               w_offset, (__nv_bfloat16*)y, (__nv_bfloat16*)h_out, (int)rows, H, eps);
+  RMS_DISPATCH_PDL(splitk_residual_rmsnorm_kernel, H, ws, splits, split_stride, (const __nv_bfloat16*)residual, w, wf32,
+                   w_offset, (__nv_bfloat16*)y, (__nv_bfloat16*)h_out, (int)rows, H, eps);
   return (int)cudaGetLastError();
 }
 

@@ -214,6 +214,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // barriers, TMEM and descriptors are set up: let the next kernel start its own prologue, then wait for
+  // the previous kernel's results (everything below reads or writes global memory)
+  pdl_trigger();
+  pdl_wait();
 
   const int num_kb = (p.K + kBK - 1) / kBK;
   const int num_work = p.tiles_m * p.tiles_n * p.splits * (p.group_mode == 2 ? p.num_groups : 1);
@@ -419,8 +423,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
   }
   int grid = p.tiles_m * p.tiles_n * p.splits;
   if (grid > num_sms()) grid = num_sms();
-  kern<<<grid, kGemmThreads, S::kTotal, stream>>>(ta, tb, p);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_pdl(kern, dim3(grid), dim3(kGemmThreads), S::kTotal, stream, ta, tb, p));
 }
 
 template <bool A_MN, bool B_MN>
@@ -459,6 +462,8 @@ struct ExtraDst {
 __global__ void __launch_bounds__(256)
 splitk_reduce_kernel(const float* __restrict__ ws, __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ bias,
                      int M, int N, long long ldc, long long split_stride, int splits, ExtraDst extra) {
+  pdl_trigger();
+  pdl_wait();
   const int nvec = N >> 2;
   const long long total = (long long)M * nvec;
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
@@ -466,9 +471,14 @@ splitk_reduce_kernel(const float* __restrict__ ws, __nv_bfloat16* __restrict__ o
     const int m = (int)(idx / nvec);
     const int c = (int)(idx % nvec) * 4;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int s = 0; s < splits; ++s) {
-      const float4 v = *reinterpret_cast<const float4*>(ws + s * split_stride + (long long)m * N + c);
-      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    for (int s0 = 0; s0 < splits; s0 += 4) {   // four loads in flight, summed in split order
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        v[u] = s0 + u < splits ? __ldcg(reinterpret_cast<const float4*>(ws + (s0 + u) * split_stride + (long long)m * N + c))
+                               : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) { acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w; }
     }
     if (bias != nullptr) {
       acc.x += __bfloat162float(bias[c]); acc.y += __bfloat162float(bias[c + 1]);
@@ -603,11 +613,10 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, const void* bia
   const long long total = (long long)M * (N / 4);
   int grid = (int)((total + 255) / 256);
   if (grid > 148 * 8) grid = 148 * 8;
-  splitk_reduce_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const float*>(workspace),
-                                                 reinterpret_cast<__nv_bfloat16*>(C),
-                                                 epi == 1 ? reinterpret_cast<const __nv_bfloat16*>(bias) : nullptr, M, N,
-                                                 ldc, p.split_stride, p.splits, xd);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(splitk_reduce_kernel, dim3(grid), dim3(256), 0, stream,
+                         reinterpret_cast<const float*>(workspace), reinterpret_cast<__nv_bfloat16*>(C),
+                         epi == 1 ? reinterpret_cast<const __nv_bfloat16*>(bias) : nullptr, M, N, ldc, p.split_stride,
+                         p.splits, xd);
 }
 
 extern "C" int areno_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
