@@ -28,21 +28,13 @@ constexpr int kPage = 64;  // tokens per page (also the key tile)
 // One warp per (token, head).  Heads [0, hq) are q (rotate only), [hq, hq+hkv) are k (rotate,
 // write back, append), [hq+hkv, hq+2hkv) are v (append).  slot_mapping[t] < 0 skips the append.
 // ---------------------------------------------------------------------------------
+// Per-warp work on one (token, head) row `p` (D bf16 values already in global memory): rotate q / k
+// heads in place, append k / v heads to the paged cache.
 template <bool FP8>
-__global__ void __launch_bounds__(256)
-rope_append_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions,
-                   const int* __restrict__ slot_mapping, const float* __restrict__ inv_freq, void* __restrict__ k_cache,
-                   void* __restrict__ v_cache, float* __restrict__ k_scale, float* __restrict__ v_scale, long long tokens,
-                   int hq, int hkv, int D, int rot_dim, float theta, int interleaved, int page_size) {
-  pdl_trigger();
-  pdl_wait();
-  const int heads = hq + 2 * hkv;
-  const long long w = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (w >= tokens * heads) return;
-  const int lane = threadIdx.x & 31;
-  const long long t = w / heads;
-  const int h = (int)(w % heads);
-  __nv_bfloat16* p = qkv + t * (long long)heads * D + (long long)h * D;
+__device__ __forceinline__ void rope_append_row(__nv_bfloat16* p, int lane, long long t, int h, const int* positions,
+                                                const int* slot_mapping, const float* inv_freq, void* k_cache,
+                                                void* v_cache, float* k_scale, float* v_scale, int hq, int hkv, int D,
+                                                int rot_dim, float theta, int interleaved, int page_size) {
   const bool is_v = h >= hq + hkv;
   const bool is_k = !is_v && h >= hq;
   if (!is_v && rot_dim > 0) {
@@ -81,6 +73,88 @@ rope_append_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ posi
     for (int i = lane * 2; i < D; i += 64)
       *reinterpret_cast<uint32_t*>(dst + i) = *reinterpret_cast<const uint32_t*>(p + i);
   }
+}
+
+template <bool FP8>
+__global__ void __launch_bounds__(256)
+rope_append_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions,
+                   const int* __restrict__ slot_mapping, const float* __restrict__ inv_freq, void* __restrict__ k_cache,
+                   void* __restrict__ v_cache, float* __restrict__ k_scale, float* __restrict__ v_scale, long long tokens,
+                   int hq, int hkv, int D, int rot_dim, float theta, int interleaved, int page_size) {
+  pdl_trigger();
+  pdl_wait();
+  const int heads = hq + 2 * hkv;
+  const long long w = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (w >= tokens * heads) return;
+  const int lane = threadIdx.x & 31;
+  const long long t = w / heads;
+  const int h = (int)(w % heads);
+  __nv_bfloat16* p = qkv + t * (long long)heads * D + (long long)h * D;
+  rope_append_row<FP8>(p, lane, t, h, positions, slot_mapping, inv_freq, k_cache, v_cache, k_scale, v_scale, hq, hkv, D,
+                       rot_dim, theta, interleaved, page_size);
+}
+
+// Decode-sized fused form: the q/k/v projection left split-K partials ws[splits, tokens, heads * D]
+// (fp32); one warp per (token, head) folds them in split order, adds the bias, rounds to bf16 into
+// `qkv`, applies the optional per-head RMSNorm of q / k heads, then rotates and appends as above.
+// Every intermediate passes through the same bf16 rounding as the separate kernels it replaces
+// (split-K fold, head norm, rope + append), so the results are identical.
+template <bool FP8>
+__global__ void __launch_bounds__(256)
+fold_rope_append_kernel(const float* __restrict__ ws, int splits, long long split_stride,
+                        const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ qkv,
+                        const int* __restrict__ positions, const int* __restrict__ slot_mapping,
+                        const float* __restrict__ inv_freq, void* __restrict__ k_cache, void* __restrict__ v_cache,
+                        float* __restrict__ k_scale, float* __restrict__ v_scale, long long tokens, int hq, int hkv, int D,
+                        int rot_dim, float theta, int interleaved, int page_size, const void* __restrict__ q_norm_w,
+                        const void* __restrict__ k_norm_w, int norm_wf32, float norm_offset, float norm_eps) {
+  pdl_trigger();
+  pdl_wait();
+  const int heads = hq + 2 * hkv;
+  const long long w = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (w >= tokens * heads) return;
+  const int lane = threadIdx.x & 31;
+  const long long t = w / heads;
+  const int h = (int)(w % heads);
+  const long long row_off = t * (long long)heads * D + (long long)h * D;
+  __nv_bfloat16* p = qkv + row_off;
+  for (int i = lane * 4; i < D; i += 128) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s0 = 0; s0 < splits; s0 += 4) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        v[u] = s0 + u < splits ? __ldcg(reinterpret_cast<const float4*>(ws + (s0 + u) * split_stride + row_off + i))
+                               : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) { acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w; }
+    }
+    if (bias != nullptr) {
+      const __nv_bfloat16* b = bias + (long long)h * D + i;
+      acc.x += __bfloat162float(b[0]); acc.y += __bfloat162float(b[1]);
+      acc.z += __bfloat162float(b[2]); acc.w += __bfloat162float(b[3]);
+    }
+    uint2 o;
+    o.x = pack_bf16x2(acc.x, acc.y);
+    o.y = pack_bf16x2(acc.z, acc.w);
+    *reinterpret_cast<uint2*>(p + i) = o;
+  }
+  __syncwarp();
+  const void* nw = h < hq ? q_norm_w : (h < hq + hkv ? k_norm_w : nullptr);
+  if (nw != nullptr) {
+    float ss = 0.f;
+    for (int i = lane; i < D; i += 32) { const float x = __bfloat162float(p[i]); ss += x * x; }
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)D + norm_eps);
+    for (int i = lane; i < D; i += 32) {
+      const float wv = norm_wf32 ? reinterpret_cast<const float*>(nw)[i]
+                                 : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(nw)[i]);
+      p[i] = __float2bfloat16_rn(__bfloat162float(p[i]) * inv * (wv + norm_offset));
+    }
+    __syncwarp();
+  }
+  rope_append_row<FP8>(p, lane, t, h, positions, slot_mapping, inv_freq, k_cache, v_cache, k_scale, v_scale, hq, hkv, D,
+                       rot_dim, theta, interleaved, page_size);
 }
 
 // ---------------------------------------------------------------------------------
@@ -427,6 +501,32 @@ extern "C" int areno_rope_append_kv(void* qkv, const int* positions, const int* 
     e = launch_pdl(rope_append_kernel<false>, dim3(grid), dim3(256), 0, stream, (__nv_bfloat16*)qkv, positions,
                    slot_mapping, inv_freq, k_cache, v_cache, k_scale, v_scale, tokens, hq, hkv, head_dim, rot_dim, theta,
                    interleaved, page_size);
+  return (int)e;
+}
+
+// Split-K fold + bias + optional q/k head norm + rope + KV append in one launch (decode).  ws: fp32
+// [splits, tokens, (hq + 2 hkv) * head_dim] partials; qkv: bf16 output of the same row layout.
+extern "C" int areno_fold_rope_append_kv(const float* ws, int splits, long long split_stride, const void* bias, void* qkv,
+                                         const int* positions, const int* slot_mapping, const float* inv_freq,
+                                         void* k_cache, void* v_cache, float* k_scale, float* v_scale, long long tokens,
+                                         int hq, int hkv, int head_dim, int rot_dim, float theta, int interleaved,
+                                         int page_size, int fp8, const void* q_norm_w, const void* k_norm_w,
+                                         int norm_wf32, float norm_offset, float norm_eps, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (splits < 1 || (head_dim % 4) != 0) return -3;
+  const long long nw = tokens * (hq + 2 * hkv);
+  const unsigned grid = (unsigned)((nw + 7) / 8);
+  cudaError_t e;
+  if (fp8)
+    e = launch_pdl(fold_rope_append_kernel<true>, dim3(grid), dim3(256), 0, stream, ws, splits, split_stride,
+                   (const __nv_bfloat16*)bias, (__nv_bfloat16*)qkv, positions, slot_mapping, inv_freq, k_cache, v_cache,
+                   k_scale, v_scale, tokens, hq, hkv, head_dim, rot_dim, theta, interleaved, page_size, q_norm_w, k_norm_w,
+                   norm_wf32, norm_offset, norm_eps);
+  else
+    e = launch_pdl(fold_rope_append_kernel<false>, dim3(grid), dim3(256), 0, stream, ws, splits, split_stride,
+                   (const __nv_bfloat16*)bias, (__nv_bfloat16*)qkv, positions, slot_mapping, inv_freq, k_cache, v_cache,
+                   k_scale, v_scale, tokens, hq, hkv, head_dim, rot_dim, theta, interleaved, page_size, q_norm_w, k_norm_w,
+                   norm_wf32, norm_offset, norm_eps);
   return (int)e;
 }
 

@@ -678,12 +678,12 @@ splitk_residual_rmsnorm_kernel(const float* __restrict__ ws, int splits, long lo
 #pragma unroll
           for (int j = 0; j < 8; ++j) v[i][j] = 0.f;
         }
-        // batches of 4 splits: 8 independent 16-byte loads in flight before the first add (the
+        // batches of 8 splits: 16 independent 16-byte loads in flight before the first add (the
         // partials sit in L2; a one-split-at-a-time loop is a chain of L2 round trips)
-        for (int s0 = 0; s0 < splits; s0 += 4) {
-          float4 a[4], b[4];
+        for (int s0 = 0; s0 < splits; s0 += 8) {
+          float4 a[8], b[8];
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
+          for (int u = 0; u < 8; ++u) {
             if (s0 + u < splits) {
               const float* p = ws + (size_t)(s0 + u) * split_stride + base + vi * 8;
               a[u] = __ldcg(reinterpret_cast<const float4*>(p));
@@ -694,7 +694,7 @@ splitk_residual_rmsnorm_kernel(const float* __restrict__ ws, int splits, long lo
             }
           }
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {   // fixed order: the sum does not depend on the batch size
+          for (int u = 0; u < 8; ++u) {   // fixed order: the sum does not depend on the batch size
             v[i][0] += a[u].x; v[i][1] += a[u].y; v[i][2] += a[u].z; v[i][3] += a[u].w;
             v[i][4] += b[u].x; v[i][5] += b[u].y; v[i][6] += b[u].z; v[i][7] += b[u].w;
           }

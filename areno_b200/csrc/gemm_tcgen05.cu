@@ -58,6 +58,11 @@ struct GemmParams {
   // operand working sets inside L2 (otherwise a weight-gradient GEMM re-reads dY from DRAM once per
   // N tile).
   int n_fast;
+  // Gated-activation epilogue (epi 4 = SiLU, 5 = GELU-tanh; 256-wide tiles, K-major operands): B is a
+  // merged [2 * gate_rows, K] weight (gate rows first, then up rows).  A tile pairs 128 gate rows
+  // with the 128 up rows of the same channels, so both halves of a channel land in one
+  // accumulator and the epilogue stores act(gate) * up: C is [M, gate_rows].
+  long long gate_rows;
 };
 
 struct WorkItem {
@@ -249,6 +254,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
               tma_load_2d(b_dst + j * 8192, &tma_b, &full_bar[stage], n0 + j * 64, k0 + wi.b_off);
+          } else if (p.gate_rows > 0) {
+            // two 128-row boxes (gate, up) stacked into one 256-row K-major tile
+            tma_load_2d(b_dst, &tma_b, &full_bar[stage], k0, n0 / 2);
+            tma_load_2d(b_dst + 128 * 128, &tma_b, &full_bar[stage], k0, static_cast<int>(p.gate_rows) + n0 / 2);
           } else {
             tma_load_2d(b_dst, &tma_b, &full_bar[stage], k0, n0 + wi.b_off);
           }
@@ -333,6 +342,36 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       const int row = m0 + q * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                              static_cast<uint32_t>(acc * BN);
+      if (p.epi >= 4) {
+        if constexpr (BN == 256) {
+#pragma unroll 1
+          for (int c = 0; c < 128; c += 32) {
+            uint32_t rg[32], ru[32];
+            tmem_ld_32x32(t_row + c, rg);
+            tmem_ld_32x32(t_row + 128 + c, ru);
+            tmem_ld_wait();
+            const int col = n0 / 2 + c;
+            const int ncols = min(32, static_cast<int>(p.gate_rows) - col);
+            if (row < p.M && ncols > 0) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                // both halves pass through bf16 first: the same values the unfused path reads back
+                const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(rg[j])));
+                const float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(ru[j])));
+                float a;
+                if (p.epi == 4) {
+                  a = g / (1.f + __expf(-g));
+                } else {
+                  const float t = tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g));
+                  a = 0.5f * g * (1.f + t);
+                }
+                rg[j] = __float_as_uint(a * u);
+              }
+              store_row_bf16(reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col, rg, ncols, nullptr);
+            }
+          }
+        }
+      } else
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t r[32];
@@ -514,8 +553,14 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, const void* bia
                           long long lda, long long ldb, long long ldc, int a_mn, int b_mn, int epi, int bn,
                           void* workspace, long long workspace_bytes, int* status, cudaStream_t stream,
                           void* const* extra, int n_extra, const GroupArgs* group = nullptr, int b_groups = 1,
-                          int* splits_out = nullptr) {
+                          int* splits_out = nullptr, long long gate_rows = 0) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (epi >= 4) {  // gated activation: merged weight, 256-wide tiles only
+    if (a_mn || b_mn || group != nullptr || n_extra != 0 || gate_rows <= 0 || N != 2 * gate_rows || (gate_rows % 8) != 0)
+      return -3;
+    bn = 256;
+    workspace = nullptr;
+  }
   if (n_extra < 0 || n_extra > 7 || (n_extra > 0 && epi > 1)) return -3;
   for (int e = 0; e < n_extra; ++e)
     if (reinterpret_cast<uintptr_t>(extra[e]) & 15) return -3;
@@ -523,7 +568,7 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, const void* bia
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
       (reinterpret_cast<uintptr_t>(C) & 15))
     return -3;
-  if (epi <= 1 ? (ldc % 8) != 0 : (ldc % 4) != 0) return -3;
+  if ((epi <= 1 || epi >= 4) ? (ldc % 8) != 0 : (ldc % 4) != 0) return -3;
   {
     // cuTensorMapEncodeTiled needs a current driver context; threads that have not yet made a
     // runtime call (e.g. autograd workers) get the primary context bound here.
@@ -546,7 +591,8 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, const void* bia
   // grouped mode 1: B holds `b_groups` experts stacked along its outer dimension
   const uint64_t b_mult = (group != nullptr && group->mode == 1) ? (uint64_t)b_groups : 1u;
   if (b_mn) rc = make_tensor_map_2d_bf16(&tb, B, (uint64_t)N, (uint64_t)K * b_mult, (uint64_t)ldb * 2, 64, 64);
-  else rc = make_tensor_map_2d_bf16(&tb, B, (uint64_t)K, (uint64_t)N * b_mult, (uint64_t)ldb * 2, 64, (uint32_t)bn);
+  else rc = make_tensor_map_2d_bf16(&tb, B, (uint64_t)K, (uint64_t)N * b_mult, (uint64_t)ldb * 2, 64,
+                                    epi >= 4 ? 128u : (uint32_t)bn);
   if (rc != 0) return rc;
   GemmParams p;
   p.M = M; p.N = N; p.K = K;
@@ -560,6 +606,7 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, const void* bia
   p.split_stride = 0;
   p.n_extra = n_extra;
   for (int e = 0; e < 7; ++e) p.extra[e] = e < n_extra ? extra[e] : nullptr;
+  p.gate_rows = epi >= 4 ? gate_rows : 0;
   p.group_mode = 0;
   p.tile_expert = nullptr;
   p.expert_rows = nullptr;
@@ -635,6 +682,17 @@ extern "C" int areno_gemm_bf16_push(const void* A, const void* B, void* C, const
                                     void* workspace, long long workspace_bytes, int* status, cudaStream_t stream) {
   return gemm_bf16_impl(A, B, C, bias, M, N, K, lda, ldb, ldc, 0, 0, bias != nullptr ? 1 : 0, 0, workspace,
                         workspace_bytes, status, stream, extra, n_extra);
+}
+
+// Gate / up projection with the gated activation in the epilogue (inference: the pre-activation is not
+// kept).  B: merged weight [2 * I, K] (gate rows, then up rows); C: bf16 [M, I] = act(A Bg^T) * (A Bu^T).
+// act: 0 = SiLU, 1 = GELU-tanh.  Both products are rounded to bf16 before the activation, so the result
+// equals areno_gemm_bf16 followed by areno_gated_act_fwd.
+extern "C" int areno_gemm_bf16_gated(const void* A, const void* B, void* C, int M, int I, int K, long long lda,
+                                     long long ldb, long long ldc, int act, int* status, cudaStream_t stream) {
+  if (act != 0 && act != 1) return -3;
+  return gemm_bf16_impl(A, B, C, nullptr, M, 2 * I, K, lda, ldb, ldc, 0, 0, 4 + act, 256, nullptr, 0, status, stream,
+                        nullptr, 0, nullptr, 1, nullptr, I);
 }
 
 // ---- grouped (mixture-of-experts) entry points; plans come from areno_moe_align -------------------

@@ -93,20 +93,32 @@ class Attention(nn.Module):
     def attend(self, x, positions, meta):
         """Attention output ``[T, hq * d]`` before the output projection."""
         cfg = self.cfg
-        qkv = self.qkv(x)
         qw = self.q_norm.weight if self.q_norm is not None else None
         kw = self.k_norm.weight if self.k_norm is not None else None
         if isinstance(meta, TrainMeta):
             return attn_ops.qkv_attention(
-                qkv, positions, meta.varlen, self.hq, self.hkv, self.d, scale=self.scale, theta=cfg.rope_theta,
+                self.qkv(x), positions, meta.varlen, self.hq, self.hkv, self.d, scale=self.scale, theta=cfg.rope_theta,
                 rot_dim=self.rot_dim, inv_freq=self.inv_freq, interleaved=self.rope_interleaved, causal=True,
                 window=self.window, q_norm_w=qw, k_norm_w=kw, norm_eps=cfg.rms_norm_eps, norm_offset=cfg.norm_weight_offset)
+        if x.is_cuda and x.shape[0] <= 128 and self.qkv.q_mult == 1:
+            # decode-sized: the projection leaves its split-K partials and one kernel folds them, adds the
+            # bias, normalises q / k heads, rotates and appends to the cache
+            part = gemm.gemm_partials(coll.copy_to_tp(x), self.qkv.weight)
+            if isinstance(part, gemm.SplitKPartial):
+                kc, vc, ks, vs = self.kv_cache
+                qkv = pa.fold_rope_append_kv(
+                    part, self.qkv.bias, positions, meta.slot_mapping, kc, vc, ks, vs, self.hq, self.hkv, self.d,
+                    theta=cfg.rope_theta, rot_dim=self.rot_dim, inv_freq=self.inv_freq, interleaved=self.rope_interleaved,
+                    q_norm_w=qw, k_norm_w=kw, norm_eps=cfg.rms_norm_eps, norm_offset=cfg.norm_weight_offset)
+                return self._attend_cached(qkv, meta)
+            qkv = part if self.qkv.bias is None else part + self.qkv.bias
+        else:
+            qkv = self.qkv(x)
         return self._infer(qkv, positions, meta, qw, kw)
 
     def _infer(self, qkv, positions, meta: InferMeta, qw, kw):
         cfg = self.cfg
         hq, hkv, d = self.hq, self.hkv, self.d
-        t = qkv.shape[0]
         if qw is not None:
             q3 = qkv[:, : hq * d].unflatten(1, (hq, d))
             k3 = qkv[:, hq * d:(hq + hkv) * d].unflatten(1, (hkv, d))
@@ -119,6 +131,13 @@ class Attention(nn.Module):
         kc, vc, ks, vs = self.kv_cache
         pa.rope_append_kv(qkv, positions, meta.slot_mapping, kc, vc, ks, vs, hq, hkv, d, theta=cfg.rope_theta,
                           rot_dim=self.rot_dim, inv_freq=self.inv_freq, interleaved=self.rope_interleaved)
+        return self._attend_cached(qkv, meta)
+
+    def _attend_cached(self, qkv, meta: InferMeta):
+        """Attention over the paged cache for a ``qkv`` whose q / k are rotated and whose k / v are appended."""
+        hq, hkv, d = self.hq, self.hkv, self.d
+        t = qkv.shape[0]
+        kc, vc, ks, vs = self.kv_cache
         q = qkv[:, : hq * d].unflatten(1, (hq, d))
         if meta.mode == "decode":
             out = pa.paged_decode(q, kc, vc, ks, vs, meta.block_table, meta.seq_lens, self.scale,

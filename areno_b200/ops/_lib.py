@@ -27,6 +27,7 @@ _SIGNATURES: dict[str, str] = {
     "areno_gemm_bf16": "ppppiiillliiiiplpp",
     "areno_rmsnorm_fwd": "pppifppplifp",
     "areno_gemm_bf16_partials": "pppiiilllplppp",
+    "areno_gemm_bf16_gated": "pppiiilllipp",
     "areno_splitk_residual_rmsnorm": "pilppifpplifp",
     "areno_rmsnorm_bwd_blocks": "l",
     "areno_rmsnorm_bwd": "pppifpppppilip",
@@ -45,6 +46,7 @@ _SIGNATURES: dict[str, str] = {
     "areno_headnorm_bwd": "plplpifpplppiliip",
     "areno_page_size": "",
     "areno_rope_append_kv": "pppppppp" + "l" + "iiii" + "f" + "iii" + "p",
+    "areno_fold_rope_append_kv": "pil" + "ppppppppp" + "l" + "iiii" + "f" + "iii" + "pp" + "i" + "ff" + "p",
     "areno_paged_decode": "pppppppppp" + "iiiii" + "ll" + "f" + "iiii" + "p",
     "areno_logprob_stats": "pilliplppppp",
     "areno_logprob_bwd": "pilliplppppp",

@@ -134,6 +134,23 @@ def gemm_partials(x: torch.Tensor, weight: torch.Tensor):
     return SplitKPartial(ws, int(splits.value), rows, n)
 
 
+def gated_linear(x: torch.Tensor, weight: torch.Tensor, act: str) -> torch.Tensor:
+    """``act(x Wg^T) * (x Wu^T)`` for a merged ``weight = [Wg; Wu]`` (``[2 I, K]``) with the activation in the
+    GEMM epilogue; no autograd (inference).  Equal to ``linear`` followed by the gated activation."""
+    assert x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and not torch.is_grad_enabled()
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    m, k = x.shape
+    inter = weight.shape[0] // 2
+    out = torch.empty((m, inter), dtype=torch.bfloat16, device=x.device)
+    if m == 0:
+        return out
+    _lib.call("areno_gemm_bf16_gated", x.data_ptr(), weight.data_ptr(), out.data_ptr(), m, inter, k, x.stride(0),
+              weight.stride(0), out.stride(0), 0 if act == "silu" else 1, _lib.status_buffer(x.device).data_ptr(),
+              _lib.stream())
+    return out
+
+
 def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
     """Per-device split-K scratch (uint8), grown on demand and reused by every skinny GEMM.
 

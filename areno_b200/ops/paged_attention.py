@@ -85,6 +85,29 @@ def _dequant(cache, scale):
     return cache.view(torch.float8_e4m3fn).float() * scale.unsqueeze(-1)
 
 
+def fold_rope_append_kv(part, bias, positions, slot_mapping, k_cache, v_cache, k_scale, v_scale, hq, hkv, d,
+                        theta=10000.0, rot_dim=None, inv_freq=None, interleaved=False, q_norm_w=None, k_norm_w=None,
+                        norm_eps: float = 1e-6, norm_offset: float = 0.0):
+    """Decode-sized q/k/v projection left as split-K partials (``ops.gemm.SplitKPartial``): fold + bias +
+    optional per-head q / k RMSNorm + rotary embedding + KV append in one launch.  Returns the bf16
+    ``[T, (hq + 2 hkv) d]`` tensor (q rotated, k rotated, v), as ``linear`` + head norms + ``rope_append_kv`` would."""
+    rot = d if rot_dim is None else rot_dim
+    t, n = part.rows, part.n
+    assert n == (hq + 2 * hkv) * d
+    qkv = torch.empty((t, n), dtype=torch.bfloat16, device=k_cache.device)
+    if positions.dtype != torch.int32:
+        positions = positions.to(torch.int32)
+    if slot_mapping.dtype != torch.int32:
+        slot_mapping = slot_mapping.to(torch.int32)
+    wf32 = int(q_norm_w is not None and q_norm_w.dtype == torch.float32)
+    _lib.call("areno_fold_rope_append_kv", part.ws.data_ptr(), part.splits, t * n, _lib.ptr(bias), qkv.data_ptr(),
+              positions.data_ptr(), slot_mapping.data_ptr(), _lib.ptr(inv_freq), k_cache.data_ptr(), v_cache.data_ptr(),
+              _lib.ptr(k_scale), _lib.ptr(v_scale), t, hq, hkv, d, rot, float(theta), int(interleaved), PAGE,
+              int(k_cache.dtype == torch.uint8), _lib.ptr(q_norm_w), _lib.ptr(k_norm_w), wf32, float(norm_offset),
+              float(norm_eps), _lib.stream())
+    return qkv
+
+
 def paged_decode_reference(q, k_cache, v_cache, k_scale, v_scale, block_table, seq_lens, scale, window=0):
     """q: [B, hq, d] -> [B, hq, d] (fp32 math)."""
     b, hq, d = q.shape

@@ -257,3 +257,60 @@ def test_splitk_partials_residual_rmsnorm(rows, n, k):
         y, h = norm.rmsnorm(part, nw, 1e-6, residual=res)
     rel = lambda a, b: float((a.float() - b).norm() / b.norm())
     assert rel(h, h_ref) < 8e-3 and rel(y, y_ref) < 8e-3
+
+
+@pytest.mark.parametrize("m,inter,k,act", [(64, 18944, 3584, "silu"), (300, 1000, 512, "gelu_tanh"), (4096, 4096, 1024, "silu")])
+def test_gated_linear_matches_linear_then_activation(m, inter, k, act):
+    """The gate / up GEMM with the activation in its epilogue against the two-kernel path (same bf16 rounding
+    of the pre-activation, so the results agree to the last bit up to instruction contraction)."""
+    from areno_b200.ops import activation, gemm
+
+    torch.manual_seed(11)
+    x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(2 * inter, k, device="cuda") * k ** -0.5).to(torch.bfloat16)
+    with torch.no_grad():
+        fused = gemm.gated_linear(x, w, act)
+        gu = gemm.linear(x, w)
+        ref = activation.silu_and_mul(gu) if act == "silu" else activation.gelu_tanh_and_mul(gu)
+    _lib.check_status()
+    assert fused.shape == ref.shape == (m, inter)
+    assert _rel_err(fused, ref) < 2e-3
+    assert float((fused == ref).float().mean()) > 0.99
+
+
+@pytest.mark.parametrize("hq,hkv,d,bias,norm,rot,fp8", [(28, 4, 128, True, False, 128, False), (8, 2, 128, False, True, 128, True),
+                                                     (4, 4, 64, True, True, 32, False)])
+def test_fold_rope_append_matches_separate_kernels(hq, hkv, d, bias, norm, rot, fp8):
+    """Split-K fold + bias + head norm + rope + KV append in one launch against the kernels it replaces."""
+    from areno_b200.ops import attention as attn_ops, gemm
+
+    torch.manual_seed(12)
+    t, k = 48, 3584
+    n = (hq + 2 * hkv) * d
+    x = torch.randn(t, k, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(n, k, device="cuda") * k ** -0.5).to(torch.bfloat16)
+    b = torch.randn(n, device="cuda").to(torch.bfloat16) if bias else None
+    qw = (1 + 0.1 * torch.randn(d, device="cuda")) if norm else None
+    kw = (1 + 0.1 * torch.randn(d, device="cuda")) if norm else None
+    positions = torch.randint(0, 500, (t,), dtype=torch.int32, device="cuda")
+    slots = torch.randperm(4 * pa.PAGE, device="cuda")[:t].to(torch.int32)
+    slots[5] = -1
+    cache_a = pa.alloc_kv_cache(4, hkv, d, "cuda", fp8)
+    cache_b = pa.alloc_kv_cache(4, hkv, d, "cuda", fp8)
+    with torch.no_grad():
+        ref = gemm.linear(x, w, b)
+        if norm:
+            q3 = ref[:, : hq * d].unflatten(1, (hq, d))
+            k3 = ref[:, hq * d:(hq + hkv) * d].unflatten(1, (hkv, d))
+            attn_ops._headnorm_fwd(q3, qw, 0.0, q3, 1e-6)
+            attn_ops._headnorm_fwd(k3, kw, 0.0, k3, 1e-6)
+        pa.rope_append_kv(ref, positions, slots, *cache_a, hq, hkv, d, theta=1e6, rot_dim=rot)
+        part = gemm.gemm_partials(x, w)
+        assert isinstance(part, gemm.SplitKPartial) and part.splits > 1
+        out = pa.fold_rope_append_kv(part, b, positions, slots, *cache_b, hq, hkv, d, theta=1e6, rot_dim=rot,
+                                     q_norm_w=qw, k_norm_w=kw, norm_eps=1e-6)
+    _lib.check_status()
+    assert _rel_err(out, ref) < 2e-3 and float((out == ref).float().mean()) > 0.98
+    for ca, cb in zip(cache_a, cache_b):
+        if ca is not None:
+            assert _rel_err(cb.float(), ca.float()) < 5e-3
