@@ -63,10 +63,18 @@ struct GemmParams {
   // with the 128 up rows of the same channels, so both halves of a channel land in one
   // accumulator and the epilogue stores act(gate) * up: C is [M, gate_rows].
   long long gate_rows;
+  // Tail splitting (plain mode, splits == 1): the persistent grid walks `tail_first` whole tiles, then the
+  // remaining `tail_tiles` tiles (less than a wave) are cut into `tail_splits` K ranges of `tail_kb`
+  // k-blocks each so that the last round keeps every SM busy with a fraction of a tile instead of leaving
+  // most of them idle for a whole tile.  Tail partials go to tail_ws[tail tile][split][128][BN] (fp32)
+  // and a small kernel folds them with the requested epilogue.
+  int tail_first, tail_tiles, tail_splits, tail_kb;
+  float* tail_ws;
 };
 
 struct WorkItem {
   int m0, n0, kb_lo, kb_hi, split;
+  int tail;         // index among the tail tiles, or -1 for a whole tile
   int b_off;        // added to B's outer TMA coordinate
   long long c_off;  // elements added to the C pointer
   bool skip;        // nothing to do for any role
@@ -80,6 +88,18 @@ __device__ __forceinline__ WorkItem decode_work(const GemmParams& p, int work, i
   w.c_off = 0;
   w.skip = false;
   w.zero = false;
+  w.tail = -1;
+  if (p.tail_splits > 0 && work >= p.tail_first) {
+    const int r = work - p.tail_first;
+    w.tail = r / p.tail_splits;
+    w.split = r - w.tail * p.tail_splits;
+    const int tile = p.tail_first + w.tail;
+    w.m0 = (p.n_fast ? tile / p.tiles_n : tile % p.tiles_m) * kBM;
+    w.n0 = (p.n_fast ? tile % p.tiles_n : tile / p.tiles_m) * BN;
+    w.kb_lo = w.split * p.tail_kb;
+    w.kb_hi = min(num_kb, w.kb_lo + p.tail_kb);
+    return w;
+  }
   if (p.group_mode == 2) {
     const int tiles = p.tiles_m * p.tiles_n;
     const int e = work / tiles;
@@ -225,7 +245,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   pdl_wait();
 
   const int num_kb = (p.K + kBK - 1) / kBK;
-  const int num_work = p.tiles_m * p.tiles_n * p.splits * (p.group_mode == 2 ? p.num_groups : 1);
+  const int num_work = p.tail_splits > 0 ? p.tail_first + p.tail_tiles * p.tail_splits
+                                         : p.tiles_m * p.tiles_n * p.splits * (p.group_mode == 2 ? p.num_groups : 1);
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -342,7 +363,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       const int row = m0 + q * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                              static_cast<uint32_t>(acc * BN);
-      if (p.epi >= 4) {
+      if (wi.tail >= 0) {
+        // a K slice of a tail tile: the raw fp32 accumulator goes to the compact tail workspace
+        float* tw = p.tail_ws + ((size_t)(wi.tail * p.tail_splits + wi.split) * kBM + (q * 32 + lane)) * BN;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + c, r);
+          tmem_ld_wait();
+          store_row_f32(tw + c, r, 32, false);
+        }
+      } else if (p.epi >= 4) {
         if constexpr (BN == 256) {
 #pragma unroll 1
           for (int c = 0; c < 128; c += 32) {
@@ -496,6 +527,49 @@ struct ExtraDst {
   void* p[7];
 };
 
+// Folds the K slices of the tail tiles (see GemmParams::tail_*) in split order and applies the epilogue the
+// GEMM was asked for: 0 bf16, 1 bf16 + bias, 2 fp32 store, 3 fp32 accumulate.  One thread per 4 columns.
+__global__ void __launch_bounds__(256)
+tail_reduce_kernel(const float* __restrict__ ws, void* __restrict__ C, const __nv_bfloat16* __restrict__ bias, int M,
+                   int N, long long ldc, int epi, int bn, int tiles_m, int tiles_n, int n_fast, int tail_first,
+                   int tail_tiles, int tail_splits) {
+  pdl_trigger();
+  pdl_wait();
+  const int vec_per_tile = kBM * bn / 4;
+  const long long total = (long long)tail_tiles * vec_per_tile;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int tt = (int)(idx / vec_per_tile);
+    const int v = (int)(idx % vec_per_tile);
+    const int r = v / (bn / 4), c = (v % (bn / 4)) * 4;
+    const int tile = tail_first + tt;
+    const int row = (n_fast ? tile / tiles_n : tile % tiles_m) * kBM + r;
+    const int col = (n_fast ? tile % tiles_n : tile / tiles_m) * bn + c;
+    if (row >= M || col >= N) continue;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float* base = ws + ((size_t)tt * tail_splits * kBM + r) * bn + c;
+    for (int s0 = 0; s0 < tail_splits; s0 += 4) {
+      float4 x[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        x[u] = s0 + u < tail_splits ? __ldcg(reinterpret_cast<const float4*>(base + (size_t)(s0 + u) * kBM * bn))
+                                    : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) { acc.x += x[u].x; acc.y += x[u].y; acc.z += x[u].z; acc.w += x[u].w; }
+    }
+    float o[4] = {acc.x, acc.y, acc.z, acc.w};
+    const int ncols = min(4, N - col);
+    if (epi <= 1) {
+      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(C) + (long long)row * ldc + col;
+      for (int j = 0; j < ncols; ++j)
+        dst[j] = __float2bfloat16_rn(o[j] + (epi == 1 ? __bfloat162float(bias[col + j]) : 0.f));
+    } else {
+      float* dst = reinterpret_cast<float*>(C) + (long long)row * ldc + col;
+      for (int j = 0; j < ncols; ++j) dst[j] = epi == 3 ? dst[j] + o[j] : o[j];
+    }
+  }
+}
+
 // out[m, n] = bf16(sum_s ws[s, m, n] (+ bias[n])), fixed summation order; the result is also
 // written to every extra destination (peer inboxes of a TP group).
 __global__ void __launch_bounds__(256)
@@ -607,6 +681,8 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, const void* bia
   p.n_extra = n_extra;
   for (int e = 0; e < 7; ++e) p.extra[e] = e < n_extra ? extra[e] : nullptr;
   p.gate_rows = epi >= 4 ? gate_rows : 0;
+  p.tail_first = p.tail_tiles = p.tail_splits = p.tail_kb = 0;
+  p.tail_ws = nullptr;
   p.group_mode = 0;
   p.tile_expert = nullptr;
   p.expert_rows = nullptr;
@@ -644,6 +720,24 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, const void* bia
       split = true;
     }
   }
+  // Tail splitting: more than one wave of whole tiles and a small remainder.
+  bool tail = false;
+  if (!split && group == nullptr && epi <= 3 && n_extra == 0 && workspace != nullptr && tiles > num_sms()) {
+    const int rem = tiles % num_sms();
+    if (rem > 0 && rem * 3 <= num_sms()) {
+      const int want = num_sms() / rem;
+      const int tkb = (num_kb + want - 1) / want;
+      const int tsplits = (num_kb + tkb - 1) / tkb;
+      if (tsplits >= 3 && (long long)rem * tsplits * kBM * bn * 4 <= workspace_bytes) {
+        p.tail_first = tiles - rem;
+        p.tail_tiles = rem;
+        p.tail_splits = tsplits;
+        p.tail_kb = tkb;
+        p.tail_ws = reinterpret_cast<float*>(workspace);
+        tail = true;
+      }
+    }
+  }
   if (a_mn) {
     if (b_mn) rc = dispatch_bn<true, true>(bn, ta, tb, p, stream);
     else rc = dispatch_bn<true, false>(bn, ta, tb, p, stream);
@@ -652,6 +746,14 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, const void* bia
     else rc = dispatch_bn<false, false>(bn, ta, tb, p, stream);
   }
   if (splits_out != nullptr) *splits_out = split ? p.splits : 1;
+  if (rc == 0 && tail) {
+    const long long total = (long long)p.tail_tiles * kBM * bn / 4;
+    int rgrid = (int)((total + 255) / 256);
+    if (rgrid > 148 * 8) rgrid = 148 * 8;
+    return (int)launch_pdl(tail_reduce_kernel, dim3(rgrid), dim3(256), 0, stream, (const float*)p.tail_ws, C,
+                           reinterpret_cast<const __nv_bfloat16*>(bias), M, N, ldc, epi, bn, p.tiles_m, p.tiles_n, p.n_fast,
+                           p.tail_first, p.tail_tiles, p.tail_splits);
+  }
   if (rc != 0 || !split) return rc;
   if (splits_out != nullptr) return 0;  // the caller folds the partials itself (fused consumer)
   ExtraDst xd;

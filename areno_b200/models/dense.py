@@ -16,6 +16,7 @@ Architecture and lifecycle protocol follow ``areno/models/qwen3/model.py:48-72,2
 
 from __future__ import annotations
 
+import os
 import zlib
 from dataclasses import dataclass, field
 from typing import Any
@@ -32,6 +33,10 @@ from ..parallel import collectives as coll
 from ..parallel.context import get_context
 from .layers import (GatedMLP, QKVParallelLinear, RMSNorm, RowParallelLinear, VocabParallelEmbedding,
                      VocabParallelLMHead)
+
+
+# ARENO_FUSE_QKV_DECODE=0 falls back to the separate fold / head-norm / rope-append kernels (for A/B timing).
+_FUSE_QKV_DECODE = os.environ.get("ARENO_FUSE_QKV_DECODE", "1") != "0"
 
 
 @dataclass
@@ -100,7 +105,7 @@ class Attention(nn.Module):
                 self.qkv(x), positions, meta.varlen, self.hq, self.hkv, self.d, scale=self.scale, theta=cfg.rope_theta,
                 rot_dim=self.rot_dim, inv_freq=self.inv_freq, interleaved=self.rope_interleaved, causal=True,
                 window=self.window, q_norm_w=qw, k_norm_w=kw, norm_eps=cfg.rms_norm_eps, norm_offset=cfg.norm_weight_offset)
-        if x.is_cuda and x.shape[0] <= 128 and self.qkv.q_mult == 1:
+        if x.is_cuda and x.shape[0] <= 128 and self.qkv.q_mult == 1 and _FUSE_QKV_DECODE:
             # decode-sized: the projection leaves its split-K partials and one kernel folds them, adds the
             # bias, normalises q / k heads, rotates and appends to the cache
             part = gemm.gemm_partials(coll.copy_to_tp(x), self.qkv.weight)

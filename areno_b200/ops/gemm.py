@@ -90,7 +90,10 @@ def gemm(
     status = _lib.status_buffer(a.device)
     ws_ptr, ws_bytes = None, 0
     if m <= 128 and epi <= EPI_BF16_BIAS and n <= 18944 and k >= 512:
-        ws = _workspace(a.device, 16 * m * n * 4)
+        ws = _workspace(a.device, 16 * m * n * 4)        # split-K partials of a skinny problem
+        ws_ptr, ws_bytes = ws.data_ptr(), ws.numel()
+    elif m > 128:
+        ws = _workspace(a.device, 0)                      # K slices of the last partial wave (at most 148 tiles)
         ws_ptr, ws_bytes = ws.data_ptr(), ws.numel()
     _lib.call(
         "areno_gemm_bf16",

@@ -68,6 +68,26 @@ def test_gemm_bias_and_accumulate():
     assert _rel_err(acc, ref + 1.0) < 1e-4
 
 
+def test_gemm_tail_wave_split_epilogues():
+    """448 output tiles on 148 SMs: the last 4 tiles are cut along K and folded by the tail kernel; every
+    epilogue (bf16 + bias, fp32 store, fp32 accumulate) must survive that path, twice in a row (shared scratch)."""
+    torch.manual_seed(21)
+    a = torch.randn(4096, 512, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(3584, 512, device="cuda", dtype=torch.bfloat16)
+    bias = torch.randn(3584, device="cuda", dtype=torch.bfloat16)
+    ref = a.float() @ b.float().t()
+    for _ in range(2):
+        assert _rel_err(gemm.gemm(a, b, bias=bias), ref + bias.float()) < 6e-3
+        acc = torch.ones(4096, 3584, device="cuda", dtype=torch.float32)
+        gemm.gemm(a, b, out=acc, accumulate=True)
+        assert _rel_err(acc, ref + 1.0) < 1e-4
+        # weight-gradient layout: both operands MN-major
+        acc2 = torch.zeros(4096, 3584, device="cuda", dtype=torch.float32)
+        gemm.gemm(a.t().contiguous(), b.t().contiguous(), a_mn=True, b_mn=True, out=acc2, accumulate=True)
+        assert _rel_err(acc2, ref) < 1e-4
+    _lib.check_status()
+
+
 def test_linear_autograd_matches_reference():
     torch.manual_seed(3)
     x = torch.randn(4, 96, 512, device="cuda", dtype=torch.bfloat16, requires_grad=True)
