@@ -181,6 +181,74 @@ tp_reduce_rmsnorm_kernel(TpPeers c, const __nv_bfloat16* __restrict__ inbox, lon
 // Barrier only (used to keep the slot alternation even, and by tests).
 __global__ void tp_barrier_kernel(TpPeers c) { tp_block_barrier(c); }
 
+// ----------------------------------------------------------------------------------
+// Data-parallel gradient reduce-scatter over peer memory.
+//
+// Every rank keeps its fp32 gradient buckets in one symmetric region (same layout on every rank).
+// When the gradients of bucket b are final on a rank (its last micro-batch's backward has passed
+// them), that rank raises ready[b][rank] = epoch on every rank (grad_ready_kernel, on the compute
+// stream).  The owner of shard r of bucket b then runs grad_reduce_scatter_kernel on a side stream:
+// it waits until all ranks' ready[b] reached the epoch and sums the shard from every rank's
+// bucket in rank order (peer loads over NVLink), in place into its own bucket - while the compute
+// stream is still producing the gradients of earlier layers.  A cross-rank barrier before the
+// buckets are zeroed for the next step keeps a slow reader safe.
+// ready: uint32 [kMaxBuckets][8] inside the symmetric region of every rank.
+// ----------------------------------------------------------------------------------
+constexpr int kMaxBuckets = 4096;
+
+struct DpPeers {
+  int n, rank;
+  uint32_t* ready[kMaxTp];   // ready[p] = rank p's ready array as mapped here
+  const float* grads[kMaxTp];  // grads[p] = rank p's gradient region as mapped here
+  int* status;
+};
+
+__global__ void grad_ready_kernel(DpPeers c, int bucket, uint32_t epoch) {
+  const int p = threadIdx.x;
+  if (p < c.n) {
+    __threadfence_system();  // gradient stores of earlier kernels of this stream are ordered before the flag
+    st_release_sys(c.ready[p] + bucket * kMaxTp + c.rank, epoch);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+grad_reduce_scatter_kernel(DpPeers c, int bucket, uint32_t epoch, long long offset, long long elems, float* out,
+                           unsigned spin_limit) {
+  __shared__ int sh_ok;
+  if (threadIdx.x == 0) sh_ok = 1;
+  __syncthreads();
+  if (threadIdx.x < c.n) {
+    const uint32_t* mine = c.ready[c.rank] + bucket * kMaxTp + threadIdx.x;
+    unsigned spins = 0;
+    while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
+      if (++spins > spin_limit) {
+        if (atomicCAS(c.status, 0, 8) == 0) {  // 8: a peer's gradients never became ready
+          c.status[1] = bucket;
+          c.status[2] = threadIdx.x;
+          c.status[3] = (int)epoch;
+        }
+        sh_ok = 0;
+        break;
+      }
+      __nanosleep(200);
+    }
+  }
+  __syncthreads();
+  if (!sh_ok) return;  // reported; the host refuses to step on this result
+  const long long nvec = elems >> 2;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 v[kMaxTp];
+#pragma unroll
+    for (int p = 0; p < kMaxTp; ++p)
+      if (p < c.n) v[p] = __ldcg(reinterpret_cast<const float4*>(c.grads[p] + offset) + i);
+#pragma unroll
+    for (int p = 0; p < kMaxTp; ++p)
+      if (p < c.n) { acc.x += v[p].x; acc.y += v[p].y; acc.z += v[p].z; acc.w += v[p].w; }
+    reinterpret_cast<float4*>(out)[i] = acc;
+  }
+}
+
 }  // namespace areno
 
 using namespace areno;
@@ -256,5 +324,52 @@ extern "C" int areno_tp_barrier(int tp, int rank, void* const* flag_ptrs, void* 
   if (rc != 0) return rc;
   if (blocks < 1 || blocks > kMaxBlocks) return -3;
   tp_barrier_kernel<<<blocks, 32, 0, stream>>>(c);
+  return (int)cudaGetLastError();
+}
+
+// ------------------------------- DP gradient reduce-scatter ----------------------------
+extern "C" int areno_dp_max_buckets() { return kMaxBuckets; }
+extern "C" long long areno_dp_ready_bytes() { return (long long)kMaxBuckets * kMaxTp * 4; }
+
+static int fill_dp(DpPeers* c, int n, int rank, void* const* ready_ptrs, void* const* grad_ptrs, int* status) {
+  if (n < 1 || n > kMaxTp || rank < 0 || rank >= n) return -3;
+  c->n = n;
+  c->rank = rank;
+  for (int i = 0; i < kMaxTp; ++i) {
+    c->ready[i] = i < n ? reinterpret_cast<uint32_t*>(ready_ptrs[i]) : nullptr;
+    c->grads[i] = i < n ? reinterpret_cast<const float*>(grad_ptrs[i]) : nullptr;
+  }
+  c->status = status;
+  return 0;
+}
+
+// Announce to every rank that this rank's gradients of `bucket` are final for `epoch`.
+extern "C" int areno_dp_grad_ready(int n, int rank, void* const* ready_ptrs, void* const* grad_ptrs, int* status,
+                                   int bucket, unsigned epoch, cudaStream_t stream) {
+  DpPeers c;
+  const int rc = fill_dp(&c, n, rank, ready_ptrs, grad_ptrs, status);
+  if (rc != 0) return rc;
+  if (bucket < 0 || bucket >= kMaxBuckets) return -3;
+  // ordinary launch: starts only after every earlier kernel of the stream (the gradient producers) completed
+  grad_ready_kernel<<<1, 32, 0, stream>>>(c, bucket, (uint32_t)epoch);
+  return (int)cudaGetLastError();
+}
+
+// out[i] = sum over ranks of grads[rank][offset + i] for i < elems (fp32, rank order), after every rank
+// announced `bucket` for `epoch`.  offset / elems in elements, multiples of 4; out may alias this
+// rank's own region at the same offset.  wait_ms bounds the wait for the slowest peer.
+extern "C" int areno_dp_grad_reduce_scatter(int n, int rank, void* const* ready_ptrs, void* const* grad_ptrs,
+                                            int* status, int bucket, unsigned epoch, long long offset, long long elems,
+                                            void* out, int blocks, int wait_ms, cudaStream_t stream) {
+  if (elems <= 0) return 0;
+  DpPeers c;
+  const int rc = fill_dp(&c, n, rank, ready_ptrs, grad_ptrs, status);
+  if (rc != 0) return rc;
+  if (bucket < 0 || bucket >= kMaxBuckets || (offset & 3) || (elems & 3) || blocks < 1) return -3;
+  if (wait_ms < 1) wait_ms = 1;
+  if (wait_ms > 20000) wait_ms = 20000;
+  const unsigned spin_limit = (unsigned)wait_ms * 4000u;  // ~250 ns per poll (200 ns sleep + the load)
+  grad_reduce_scatter_kernel<<<blocks, 256, 0, stream>>>(c, bucket, (uint32_t)epoch, offset, elems,
+                                                         reinterpret_cast<float*>(out), spin_limit);
   return (int)cudaGetLastError();
 }

@@ -18,6 +18,7 @@ The 8-bit variant keeps int8/uint8 moments with one scale per 32 elements and no
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass, field
 
 import torch
@@ -44,6 +45,8 @@ class _Bucket:
     m_scale: torch.Tensor | None = None
     v_scale: torch.Tensor | None = None
     shard: int = 0
+    grad_offset: int = 0      # element offset of grad_flat inside the symmetric gradient region (peer-memory path)
+    min_layer: int = -1       # lowest decoder-layer index among the parameters (-1: embeddings and the like)
 
 
 class ShardedAdamW:
@@ -56,6 +59,8 @@ class ShardedAdamW:
         self.lr = cfg.lr
         self.buckets: list[_Bucket] = []
         self._state_ready = False
+        self.grad_comm = None       # parallel.grad_comm.GradComm when gradients are reduced over peer memory
+        self._overlap = False
         self._build(model)
 
     # ------------------------------------------------------------------ layout
@@ -86,19 +91,83 @@ class ShardedAdamW:
                 cur.numel += n
             if cur.params:
                 self.buckets.append(cur)
+        layer_of = _layer_index_of(model)
+        off = 0
         for b in self.buckets:
             b.numel = (b.numel + granule - 1) // granule * granule
             b.shard = b.numel // self.dp
+            b.grad_offset = off
+            off += b.numel
+            b.min_layer = min(layer_of.get(id(p), -1) for p in b.params)
+        self.grad_comm = self._make_grad_comm(off)
+        for b in self.buckets:
             dev = b.params[0].device
             dtype = b.params[0].dtype
             b.param_flat = torch.zeros(b.numel, dtype=dtype, device=dev)
-            b.grad_flat = torch.zeros(b.numel, dtype=torch.float32, device=dev)
+            if self.grad_comm is not None:
+                b.grad_flat = self.grad_comm.view(b.grad_offset, b.numel)
+            else:
+                b.grad_flat = torch.zeros(b.numel, dtype=torch.float32, device=dev)
             for p, off in zip(b.params, b.offsets):
                 view = b.param_flat[off:off + p.numel()].view(p.shape)
                 view.copy_(p.data)
                 p.data = view
                 p.main_grad = b.grad_flat[off:off + p.numel()].view(p.shape)
                 p.grad_added_to_main_grad = False
+
+    def _make_grad_comm(self, total_elems: int):
+        """Peer-memory gradient reduce-scatter: CUDA, more than one DP rank, at most 8 (one NVLink domain).
+        ``ARENO_FUSED_GRAD_RS=0`` keeps the NCCL reduce-scatter."""
+        dev = self.buckets[0].params[0].device if self.buckets else None
+        if (self.dp <= 1 or self.dp > 8 or dev is None or dev.type != "cuda" or len(self.buckets) > 4096
+                or os.environ.get("ARENO_FUSED_GRAD_RS", "1") == "0"):
+            return None
+        from ..parallel.grad_comm import GradComm
+
+        comm, err = None, None
+        try:
+            comm = GradComm(self.ctx.dp_group, self.dp, self.dp_rank, total_elems, dev)
+        except Exception as exc:  # e.g. peer access unavailable: every rank must then take the NCCL path
+            err = exc
+        ok = torch.tensor([0 if comm is None else 1], dtype=torch.int32, device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.ctx.dp_group)
+        if int(ok.item()) == 0:
+            if comm is not None:
+                comm.close()
+            if err is not None:
+                import logging
+
+                logging.getLogger("areno").warning("peer-memory gradient reduce-scatter unavailable (%s); using NCCL", err)
+            return None
+        return comm
+
+    # ------------------------------------------------- overlap with backward
+    def begin_overlap(self):
+        """Arm the reduction for the micro-batch whose backward ends the accumulation window.  Returns the
+        hook to pass as ``TrainMeta.layer_grad_hook`` (``None`` when gradients go through NCCL)."""
+        if self.grad_comm is None or self.ctx.tp_size > 1:
+            return None
+        self.grad_comm.begin_step()
+        self._overlap = True
+        return self.on_layer_grad_done
+
+    def on_layer_grad_done(self, layer: int) -> None:
+        """Backward has passed decoder layer ``layer``: every bucket made only of later parameters is final."""
+        if not self._overlap:
+            return
+        for i, b in enumerate(self.buckets):
+            if b.min_layer >= layer and i not in self.grad_comm.launched:
+                self._fold_bucket(b)
+                self.grad_comm.launch(i, b.grad_offset, b.shard)
+
+    @staticmethod
+    def _fold_bucket(b: _Bucket) -> None:
+        for p in b.params:
+            if p.grad is not None:
+                if not getattr(p, "grad_added_to_main_grad", False):
+                    p.main_grad.add_(p.grad.to(torch.float32))
+                p.grad = None
+            p.grad_added_to_main_grad = False
 
     def _ensure_state(self):
         if self._state_ready:
@@ -153,7 +222,14 @@ class ShardedAdamW:
             for b in self.buckets:
                 if b.replicated:
                     dist.all_reduce(b.grad_flat, group=ctx.tp_group)
-        if self.dp > 1:
+        if self.dp > 1 and self.grad_comm is not None:
+            if not self._overlap:
+                self.grad_comm.begin_step()
+            for i, b in enumerate(self.buckets):     # whatever backward did not hand over yet
+                self.grad_comm.launch(i, b.grad_offset, b.shard)
+            self.grad_comm.finish()
+            self._overlap = False
+        elif self.dp > 1:
             works = []
             for b in self.buckets:
                 works.append(dist.reduce_scatter_tensor(self._grad_shard(b), b.grad_flat, group=ctx.dp_group,
@@ -220,6 +296,8 @@ class ShardedAdamW:
                 if name == "master" and own_master:
                     b.master = None   # a view of the parameters themselves: rebuilt on onload
                     continue
+                if name == "grad_flat" and self.grad_comm is not None:
+                    continue          # lives in the peer-mapped region, which stays on the device
                 t = getattr(b, name)
                 if t is not None and t.is_cuda:
                     setattr(b, name, t.to("cpu"))
@@ -262,6 +340,25 @@ class ShardedAdamW:
             for k, t in sb.items():
                 if t is not None:
                     getattr(b, k).copy_(t)
+
+
+def _layer_index_of(model) -> dict[int, int]:
+    """``id(parameter) -> decoder layer index``; final norm / LM head count as one past the last layer
+    (their gradients are the first to be final in backward), everything else (embeddings, per-layer input
+    tables) as -1 (final only when backward ends)."""
+    out: dict[int, int] = {}
+    n_layers = len(getattr(model, "layers", []) or [])
+    for name, p in model.named_parameters():
+        if id(p) in out:
+            continue
+        parts = name.split(".")
+        if parts[0] == "layers" and len(parts) > 1 and parts[1].isdigit():
+            out[id(p)] = int(parts[1])
+        elif parts[0] in ("norm", "lm_head"):
+            out[id(p)] = n_layers
+        else:
+            out[id(p)] = -1
+    return out
 
 
 def lr_for_step(cfg: OptimizerConfig, step: int) -> float:

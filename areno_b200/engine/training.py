@@ -173,7 +173,8 @@ class TrainingManager:
             lens = [cu[i + 1] - cu[i] for i in range(len(cu) - 1)]
         meta = TrainMeta(build_varlen_meta(lens, device=self.device),
                          activation_checkpointing=self.config.runtime.activation_checkpointing,
-                         checkpoint_layers=self._checkpoint_layers(int(ids.numel())))
+                         checkpoint_layers=self._checkpoint_layers(int(ids.numel())),
+                         layer_grad_hook=getattr(self, "_layer_grad_hook", None))
         out = self.model(ids, pos, meta)
         aidx = pack["_action_index"]
         hidden = out.hidden_states.index_select(0, aidx)
@@ -218,7 +219,11 @@ class TrainingManager:
         if loss_fn is None:
             raise ValueError("no loss function: pass loss_fn or stamp '_loss_fn' on the pack")
         pack = to_device(pack, self.device)
+        # last micro-batch of the window: gradient buckets are handed to the reduce-scatter as backward passes them
+        self._layer_grad_hook = self.optimizer.begin_overlap() if allow_step and hasattr(self.optimizer, "begin_overlap") \
+            else None
         logprobs = self.forward_logprobs(pack)
+        self._layer_grad_hook = None
         loss_out = loss_fn(pack, logprobs)
         metrics = None
         if isinstance(loss_out, tuple):

@@ -45,6 +45,9 @@ class TrainMeta:
     activation_checkpointing: bool = True
     packed: bool = True
     checkpoint_layers: int | None = None   # recompute only the first N layers (None = every layer)
+    # called with a layer index from backward once that layer's parameter gradients are final (all later
+    # layers finished before it); the trainer uses it to start reducing gradient buckets during backward
+    layer_grad_hook: Any = None
 
 
 @dataclass
@@ -198,6 +201,12 @@ class DecoderLayer(nn.Module):
         return h, residual
 
 
+def _layer_done(hook, li: int):
+    def fire(_grad):
+        hook(li)   # the gradient itself is left untouched
+    return fire
+
+
 class DenseCausalLM(nn.Module):
     """Embedding -> N x DecoderLayer -> final norm; ``lm_head`` is applied by the caller."""
 
@@ -227,7 +236,10 @@ class DenseCausalLM(nn.Module):
         n_ckpt = len(self.layers)
         if use_ckpt and meta.checkpoint_layers is not None:
             n_ckpt = max(0, min(n_ckpt, int(meta.checkpoint_layers)))
+        grad_hook = meta.layer_grad_hook if isinstance(meta, TrainMeta) and torch.is_grad_enabled() else None
         for li, layer in enumerate(self.layers):
+            if grad_hook is not None and x.requires_grad:
+                x.register_hook(_layer_done(grad_hook, li))
             if use_ckpt and li < n_ckpt:
                 if residual is None:
                     x, residual = checkpoint(_run_first, layer, x, positions, meta, use_reentrant=False)

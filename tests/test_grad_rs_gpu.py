@@ -1,0 +1,110 @@
+"""Two GPUs: gradient reduce-scatter over peer memory against NCCL, bucket by bucket and through the
+sharded optimizer with hand-over during backward.  Skipped with fewer than two GPUs.  NVLS is switched off;
+the kernels use plain peer loads."""
+
+from __future__ import annotations
+
+import os
+import socket
+import traceback
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank, world, port, ret):
+    try:
+        os.environ["NCCL_NVLS_ENABLE"] = "0"
+        import torch.distributed as dist
+
+        from areno_b200.engine.config import ModelConfig, OptimizerConfig
+        from areno_b200.engine.optim import ShardedAdamW
+        from areno_b200.models.dense import DenseCausalLM, TrainMeta, init_weights
+        from areno_b200.ops import _lib
+        from areno_b200.ops.attention import build_varlen_meta
+        from areno_b200.parallel.context import init_parallel
+        from areno_b200.parallel.grad_comm import GradComm
+
+        torch.cuda.set_device(rank)
+        dev = torch.device("cuda", rank)
+        ctx = init_parallel(rank, world, tp_size=1, master_port=port, device=dev, timeout_s=120)
+        # ---- raw communicator: three buckets launched out of order, two steps
+        sizes = [world * 4096, world * 1024 * 1024, world * 256]
+        comm = GradComm(ctx.dp_group, world, rank, sum(sizes), dev)
+        offs = [0, sizes[0], sizes[0] + sizes[1]]
+        errs = []
+        for step in range(2):
+            g = torch.Generator(device=dev).manual_seed(10 * step + rank)
+            comm.grads.copy_(torch.randn(sum(sizes), device=dev, generator=g))
+            ref = comm.grads.clone()
+            dist.all_reduce(ref, group=ctx.dp_group)
+            comm.begin_step()
+            for b in (2, 0, 1):
+                comm.launch(b, offs[b], sizes[b] // world)
+            comm.finish()
+            torch.cuda.synchronize()
+            for b in range(3):
+                lo = offs[b] + rank * (sizes[b] // world)
+                mine, want = comm.grads[lo:lo + sizes[b] // world], ref[lo:lo + sizes[b] // world]
+                errs.append(float((mine - want).abs().max()))
+        _lib.check_status()
+        comm.close()
+
+        # ---- optimizer: same model and data on a fused and an NCCL optimizer; one step with hand-over in backward
+        cfg = ModelConfig(model_type="qwen2", vocab_size=1024, hidden_size=256, intermediate_size=512, num_hidden_layers=3,
+                          num_attention_heads=4, num_key_value_heads=2, head_dim=64, qkv_bias=True, qk_norm=False,
+                          tie_word_embeddings=False, max_position_embeddings=512)
+        results = []
+        for fused in ("1", "0"):
+            os.environ["ARENO_FUSED_GRAD_RS"] = fused
+            model = DenseCausalLM(cfg, device=dev)
+            init_weights(model, 3)
+            opt = ShardedAdamW(model, OptimizerConfig(lr=1e-3, fp32_master_bucket_numel=300_000), ctx)
+            assert (opt.grad_comm is not None) == (fused == "1")
+            gen = torch.Generator().manual_seed(50 + rank)
+            launched_early = 0
+            for micro in range(2):
+                ids = torch.randint(3, 1024, (96,), generator=gen).to(dev)
+                hook = opt.begin_overlap() if micro == 1 else None
+                meta = TrainMeta(build_varlen_meta([40, 56], device=dev), False, layer_grad_hook=hook)
+                h = model(ids, torch.arange(96, device=dev) % 56, meta).hidden_states
+                loss = model.compute_logits(h).float().logsumexp(-1).mean()
+                loss.backward()
+                if opt.grad_comm is not None and micro == 1:
+                    launched_early = len(opt.grad_comm.launched)
+            norm = opt.step()
+            torch.cuda.synchronize()
+            results.append((float(norm), torch.cat([p.detach().float().flatten() for p in model.parameters()]),
+                            launched_early, len(opt.buckets)))
+            if opt.grad_comm is not None:
+                opt.grad_comm.close()
+        _lib.check_status()
+        (n1, p1, early, nb), (n0, p0, _, _) = results
+        ret[rank] = dict(errs=errs, norm=(n1, n0), pdiff=float((p1 - p0).abs().max()), early=early, buckets=nb)
+        dist.barrier()
+    except Exception:
+        ret[rank] = "error: " + traceback.format_exc()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_peer_memory_grad_reduce_scatter_matches_nccl():
+    world = 2
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_rank_main, args=(world, _free_port(), ret), nprocs=world, join=True)
+    for r in range(world):
+        out = ret[r]
+        assert isinstance(out, dict), out
+        assert max(out["errs"]) < 1e-5, out["errs"]                      # two-term fp32 sums: exact up to order
+        assert abs(out["norm"][0] - out["norm"][1]) < 1e-4 * max(1.0, out["norm"][1])
+        assert out["pdiff"] < 1e-5
+        assert out["buckets"] >= 4 and out["early"] >= out["buckets"] - 2   # most buckets left during backward

@@ -219,3 +219,64 @@ def test_native_libraries_are_current():
     before = build.kernels_lib_path().stat().st_mtime_ns
     build.ensure_built()
     assert build.kernels_lib_path().stat().st_mtime_ns == before, "kernel library was stale and had to be rebuilt"
+
+
+def test_gradient_buckets_know_when_they_are_final():
+    """Buckets are handed to the peer-memory reduce-scatter as backward passes the layers they depend on:
+    the layer map, the per-bucket lowest layer and the launch order are checked with a recording stand-in for
+    the communicator (the hook itself fires from autograd on the CPU as well)."""
+    import torch
+
+    from areno_b200.engine.config import OptimizerConfig
+    from areno_b200.engine.optim import ShardedAdamW, _layer_index_of
+    from areno_b200.models.dense import DenseCausalLM, TrainMeta, init_weights
+    from areno_b200.ops.attention import build_varlen_meta
+    from areno_b200.parallel.context import single_process_context
+
+    from .helpers import tiny_config
+
+    single_process_context()
+    model = DenseCausalLM(tiny_config(num_hidden_layers=3, tie_word_embeddings=False))
+    init_weights(model, 0)
+    layer_of = _layer_index_of(model)
+    assert layer_of[id(model.embed.weight)] == -1 and layer_of[id(model.lm_head.weight)] == 3
+    assert layer_of[id(model.layers[1].mlp.down.weight)] == 1 and layer_of[id(model.norm.weight)] == 3
+    opt = ShardedAdamW(model, OptimizerConfig(lr=1e-3, fp32_master_bucket_numel=40_000))
+    assert opt.grad_comm is None and opt.begin_overlap() is None            # one rank: nothing to reduce
+    lows = [b.min_layer for b in opt.buckets]
+    assert -1 in lows and 3 in lows and all(-1 <= v <= 3 for v in lows)
+
+    class Recorder:
+        def __init__(self):
+            self.launched, self.order = set(), []
+
+        def begin_step(self):
+            self.launched.clear()
+
+        def launch(self, i, off, shard):
+            if i not in self.launched:
+                self.launched.add(i)
+                self.order.append(i)
+
+        def finish(self):
+            pass
+
+    opt.grad_comm, opt.dp = Recorder(), 2
+    events = []
+    hook = opt.begin_overlap()
+    assert hook is not None
+
+    def traced(layer):
+        before = len(opt.grad_comm.order)
+        hook(layer)
+        events.append((layer, opt.grad_comm.order[before:]))
+
+    ids = torch.randint(3, 512, (40,))
+    meta = TrainMeta(build_varlen_meta([40]), True, layer_grad_hook=traced)
+    h = model(ids, torch.arange(40), meta).hidden_states
+    model.compute_logits(h).float().logsumexp(-1).mean().backward()
+    assert [layer for layer, _ in events] == [2, 1, 0]                      # backward walks the layers downwards
+    for layer, launched in events:
+        assert launched and all(opt.buckets[i].min_layer >= layer for i in launched)
+    not_yet = [i for i, b in enumerate(opt.buckets) if i not in opt.grad_comm.launched]
+    assert not_yet and all(opt.buckets[i].min_layer == -1 for i in not_yet)   # the embedding leaves at the very end
