@@ -260,8 +260,67 @@ def case_decode_step(batch: int = 64, ctx: int = 512):
     return run, 0.0, float(weights + kv), f"B={batch} ctx={ctx}, 7B shape, graph replay (weights {weights / 1e9:.1f} GB + KV {kv / 1e9:.2f} GB)"
 
 
+def _lightning_inputs(seqs=16, length=1024, h=16, d=128):
+    t = seqs * length
+    wide = _bf16(t, 3 * h * d, scale=0.5)
+    q, k, v = (wide[:, i * h * d:(i + 1) * h * d].unflatten(1, (h, d)) for i in range(3))
+    slope = torch.rand(h, device="cuda") * 0.3 + 0.01
+    cu = torch.arange(0, t + 1, length, dtype=torch.int32, device="cuda")
+    return q, k, v, slope, cu, [length] * seqs
+
+
+def case_lightning_fwd():
+    from ..ops import linear_attn as la
+
+    q, k, v, slope, cu, lens = _lightning_inputs()
+    t, h, d = q.shape
+    return (lambda: la.lightning_recurrent(q, k, v, slope, cu, d ** -0.5)), 4.0 * t * h * d * d, 4.0 * t * h * d * 2, \
+        f"{len(lens)} x {lens[0]} tokens, {h} heads, d={d} (sequential scan per sequence and head)"
+
+
+def case_lightning_bwd():
+    from ..ops import linear_attn as la
+
+    q, k, v, slope, cu, lens = _lightning_inputs()
+    t, h, d = q.shape
+    qg, kg, vg = (x.detach().contiguous().requires_grad_() for x in (q, k, v))
+    o = la.lightning_attention(qg, kg, vg, slope, lens, d ** -0.5, cu=cu)
+    g = torch.randn_like(o)
+
+    def run():
+        torch.autograd.grad(o, (qg, kg, vg), g, retain_graph=True)
+
+    return run, 12.0 * t * h * d * d, 7.0 * t * h * d * 2, "backward of lightning_fwd (three scans in one launch)"
+
+
+def case_group_norm_gate():
+    from ..ops import linear_attn as la
+
+    rows, g, w = 16384, 4, 512
+    x, gate = _bf16(rows, g * w), _bf16(rows, g * w)
+    wt = torch.ones(g, w, device="cuda")
+    return (lambda: la.group_rmsnorm_sigmoid_gate(x, gate, wt, 1e-6)), 0.0, 3.0 * rows * g * w * 2, \
+        f"{rows} rows x {g} groups of {w} (group RMSNorm x sigmoid gate, forward)"
+
+
+def case_gemm_gated():
+    from ..ops import gemm
+
+    m, inter, k = 4096, 18944, 3584
+    x, w = _bf16(m, k), _bf16(2 * inter, k, scale=k ** -0.5)
+
+    def run():
+        with torch.no_grad():
+            gemm.gated_linear(x, w, "silu")
+
+    return run, 2.0 * m * 2 * inter * k, 2.0 * (m * k + 2 * inter * k + m * inter), \
+        f"M={m} I={inter} K={k}: gate/up GEMM with SiLU(gate) * up in the epilogue"
+
+
 CASES = {
     "decode_step": case_decode_step,
+    "lightning_fwd": case_lightning_fwd, "lightning_bwd": case_lightning_bwd, "group_norm_gate": case_group_norm_gate,
+    "gemm_gated": case_gemm_gated,
     "gemm_fwd": case_gemm_fwd, "gemm_dgrad": case_gemm_dgrad, "gemm_wgrad": case_gemm_wgrad,
     "gemm_decode_down": case_gemm_decode_down, "gemm_decode_gate_up": case_gemm_decode_gate_up,
     "splitk_rmsnorm": case_splitk_rmsnorm, "attn_fwd": case_attn_fwd, "attn_bwd": case_attn_bwd,
