@@ -211,6 +211,7 @@ __global__ void grad_ready_kernel(DpPeers c, int bucket, uint32_t epoch) {
   }
 }
 
+template <int UNROLL, int NP>
 __global__ void __launch_bounds__(256)
 grad_reduce_scatter_kernel(DpPeers c, int bucket, uint32_t epoch, long long offset, long long elems, float* out,
                            unsigned spin_limit) {
@@ -235,17 +236,28 @@ grad_reduce_scatter_kernel(DpPeers c, int bucket, uint32_t epoch, long long offs
   }
   __syncthreads();
   if (!sh_ok) return;  // reported; the host refuses to step on this result
+  // NVLink latency is microseconds: every thread keeps UNROLL x n 16-byte loads in flight
   const long long nvec = elems >> 2;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    float4 v[kMaxTp];
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < nvec; i0 += stride * UNROLL) {
+    float4 v[UNROLL][NP];
 #pragma unroll
-    for (int p = 0; p < kMaxTp; ++p)
-      if (p < c.n) v[p] = __ldcg(reinterpret_cast<const float4*>(c.grads[p] + offset) + i);
+    for (int u = 0; u < UNROLL; ++u) {
+      const long long i = i0 + u * stride;
 #pragma unroll
-    for (int p = 0; p < kMaxTp; ++p)
-      if (p < c.n) { acc.x += v[p].x; acc.y += v[p].y; acc.z += v[p].z; acc.w += v[p].w; }
-    reinterpret_cast<float4*>(out)[i] = acc;
+      for (int p = 0; p < NP; ++p)
+        if (p < c.n && i < nvec) v[u][p] = __ldcg(reinterpret_cast<const float4*>(c.grads[p] + offset) + i);
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const long long i = i0 + u * stride;
+      if (i >= nvec) break;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int p = 0; p < NP; ++p)   // rank order: the sum is the same whoever computes it
+        if (p < c.n) { acc.x += v[u][p].x; acc.y += v[u][p].y; acc.z += v[u][p].z; acc.w += v[u][p].w; }
+      reinterpret_cast<float4*>(out)[i] = acc;
+    }
   }
 }
 
@@ -369,7 +381,9 @@ extern "C" int areno_dp_grad_reduce_scatter(int n, int rank, void* const* ready_
   if (wait_ms < 1) wait_ms = 1;
   if (wait_ms > 20000) wait_ms = 20000;
   const unsigned spin_limit = (unsigned)wait_ms * 4000u;  // ~250 ns per poll (200 ns sleep + the load)
-  grad_reduce_scatter_kernel<<<blocks, 256, 0, stream>>>(c, bucket, (uint32_t)epoch, offset, elems,
-                                                         reinterpret_cast<float*>(out), spin_limit);
+  float* o = reinterpret_cast<float*>(out);
+  if (n <= 2) grad_reduce_scatter_kernel<8, 2><<<blocks, 256, 0, stream>>>(c, bucket, (uint32_t)epoch, offset, elems, o, spin_limit);
+  else if (n <= 4) grad_reduce_scatter_kernel<4, 4><<<blocks, 256, 0, stream>>>(c, bucket, (uint32_t)epoch, offset, elems, o, spin_limit);
+  else grad_reduce_scatter_kernel<2, 8><<<blocks, 256, 0, stream>>>(c, bucket, (uint32_t)epoch, offset, elems, o, spin_limit);
   return (int)cudaGetLastError();
 }

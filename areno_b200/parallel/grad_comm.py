@@ -73,7 +73,7 @@ class GradComm:
         self.stream = torch.cuda.Stream(device=device)
         self.epoch = 0
         self.launched: set[int] = set()
-        self.blocks = int(os.environ.get("ARENO_GRAD_RS_BLOCKS", "32"))
+        self.blocks = int(os.environ.get("ARENO_GRAD_RS_BLOCKS", "64"))
         self.wait_ms = int(os.environ.get("ARENO_GRAD_RS_WAIT_MS", "5000"))
         torch.cuda.synchronize(device)
         dist.barrier(group=group)
