@@ -39,6 +39,7 @@ _SIGNATURES: dict[str, str] = {
     "areno_embedding_bwd": "ppplillfp",
     "areno_accumulate_bf16": "pplp",
     "areno_attn_fwd": "pppppppp" + "iiiii" + "llll" + "fiip",
+    "areno_attn_fwd_tc": "pppppppp" + "iiiii" + "llllll" + "fi" + "pp",
     "areno_attn_bwd": "pppppppppp" + "pppp" + "iii" + "l" + "iii" + "llllllll" + "fiip",
     "areno_gemm_workspace_bytes": "iii",
     "areno_headnorm_fwd": "plpifplpliifp",

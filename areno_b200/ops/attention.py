@@ -15,6 +15,8 @@ plays the role of its ``native`` backend as a consistency oracle.
 
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass
 
 import torch
@@ -97,6 +99,10 @@ def _heads_view(t2d, col0, heads, d):
     return t2d[:, col0:col0 + heads * d].unflatten(1, (heads, d))
 
 
+# ARENO_ATTN_TC=0 keeps the mma.sync forward for head size 128 as well (A/B timing).
+_TC_FORWARD = os.environ.get("ARENO_ATTN_TC", "1") != "0"
+
+
 def attention_forward(q, k, v, meta: VarlenMeta, scale, causal=True, window=0, out=None, need_lse=True):
     """Kernel forward on [T, H, D] views (unit stride on D, head stride D, any token stride)."""
     if not q.is_cuda:
@@ -109,6 +115,17 @@ def attention_forward(q, k, v, meta: VarlenMeta, scale, causal=True, window=0, o
     if out is None:
         out = torch.empty((tq, hq, d), dtype=q.dtype, device=q.device)
     lse = torch.empty((hq, tq), dtype=torch.float32, device=q.device) if need_lse else None
+    if d == 128 and not window and _TC_FORWARD:
+        # tcgen05 / TMEM kernel: 128 x 128 tiles, TMA-fed, softmax between the two MMAs
+        _lib.call(
+            "areno_attn_fwd_tc",
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), _lib.ptr(lse),
+            meta.cu_q.data_ptr(), meta.cu_k.data_ptr(), meta.tile_prefix_q.data_ptr(),
+            meta.num_seqs, meta.total_q_tiles, hq, hkv, d, tq, k.shape[0],
+            q.stride(0), k.stride(0), v.stride(0), out.stride(0),
+            float(scale), int(causal), _lib.status_buffer(q.device).data_ptr(), _lib.stream(),
+        )
+        return out, lse
     _lib.call(
         "areno_attn_fwd",
         q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), _lib.ptr(lse),

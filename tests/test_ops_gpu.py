@@ -214,6 +214,8 @@ ATTN_CASES = [
     ([16, 40], [80, 40], 4, 2, 128, True, 0),
     ([150], None, 2, 1, 128, False, 0),
     ([260, 90], None, 2, 1, 128, True, 96),
+    ([1000, 513, 128, 1], None, 8, 2, 128, True, 0),   # many key tiles: every ring / phase of the tcgen05 forward
+    ([700], [1500], 4, 1, 128, True, 0),               # chunked prefill shape: queries see a cached prefix
     ([100, 200], None, 4, 2, 256, True, 0),      # head_dim 256: backward runs as two 128-column CTAs
     ([260, 90], [300, 90], 2, 1, 256, True, 96),
 ]
