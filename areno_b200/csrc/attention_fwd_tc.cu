@@ -8,7 +8,9 @@
 //                             shared tile that the second MMA consumes, then reads O_tile back from TMEM and
 //                             folds it into the running output kept in registers (o = o * corr + O_tile).
 // S of tile i+1 is issued before P V of tile i, so the tensor pipe works on the next scores while the
-// softmax warps are busy.  TMEM: columns [0,128) and [128,256) hold the two S buffers, [256,384) O_tile.
+// softmax warps are busy, and O_tile is double-buffered so that the fold of tile i happens after P of tile
+// i+1 has been handed over (the P V latency is not on the softmax warps' critical path).
+// TMEM: columns [0,128) and [128,256) hold the two S buffers, [256,384) and [384,512) the two O_tile buffers.
 // Shared memory: Q 32 KB, K 2 x 32 KB, V 2 x 32 KB, P 32 KB (all 128-byte swizzle, 1024-byte aligned).
 //
 // Every mbarrier wait is bounded (common.cuh); on expiry the CTA records a status word, lets copies in
@@ -64,9 +66,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   uint64_t* s_empty = bars + 11;    // 2
   uint64_t* p_full = bars + 13;
   uint64_t* p_empty = bars + 14;
-  uint64_t* o_full = bars + 15;
-  uint64_t* o_empty = bars + 16;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
+  uint64_t* o_full = bars + 15;     // 2
+  uint64_t* o_empty = bars + 17;    // 2
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -100,11 +102,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
       mbar_init(&v_empty[s], 1);
       mbar_init(&s_full[s], 1);
       mbar_init(&s_empty[s], 4);
+      mbar_init(&o_full[s], 1);
+      mbar_init(&o_empty[s], 4);
     }
     mbar_init(p_full, 4);
     mbar_init(p_empty, 1);
-    mbar_init(o_full, 1);
-    mbar_init(o_empty, 4);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tma_q);
@@ -186,11 +188,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
       const int st = i & 1;
       if (!mbar_wait(&v_full[st], (i >> 1) & 1, abort_flag, p.status, 16)) { ok = false; break; }
       if (!mbar_wait(p_full, i & 1, abort_flag, p.status, 17)) { ok = false; break; }
-      if (!mbar_wait(o_empty, (i & 1) ^ 1u, abort_flag, p.status, 18)) { ok = false; break; }
+      if (!mbar_wait(&o_empty[st], ((i >> 1) & 1) ^ 1u, abort_flag, p.status, 18)) { ok = false; break; }
       tc_fence_after();
       if (lane == 0) {
         const uint32_t a_base = smem_u32(sP), b_base = smem_u32(sV + st * kTcTile);
-        const uint32_t d_tmem = tmem_base + 256u;
+        const uint32_t d_tmem = tmem_base + 256u + static_cast<uint32_t>(st * kTcD);
 #pragma unroll
         for (int kb = 0; kb < 2; ++kb)
 #pragma unroll
@@ -199,7 +201,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
                      make_smem_desc_sw128(b_base + kb * 16384 + kk * 2048, 8192, 1024), idesc_o, (kb | kk) ? 1u : 0u);
         umma_commit(&v_empty[st]);
         umma_commit(p_empty);
-        umma_commit(o_full);
+        umma_commit(&o_full[st]);
       }
       __syncwarp();
     }
@@ -213,8 +215,26 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     float o_reg[kTcD];
 #pragma unroll
     for (int j = 0; j < kTcD; ++j) o_reg[j] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
+    float m_run = -INFINITY, l_run = 0.f, corr_prev = 0.f;
     bool ok = true;
+    // o = o * c + O_tile(j): runs one tile late, after P of the next tile is on its way
+    auto fold = [&](int j, float c) -> bool {
+      const int ob = j & 1;
+      if (!mbar_wait(&o_full[ob], (j >> 1) & 1, abort_flag, p.status, 21)) return false;
+      tc_fence_after();
+#pragma unroll
+      for (int cc = 0; cc < kTcD; cc += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_lane + 256u + static_cast<uint32_t>(ob * kTcD) + cc, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj) o_reg[cc + jj] = o_reg[cc + jj] * c + __uint_as_float(v[jj]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&o_empty[ob]);
+      return true;
+    };
     for (int i = 0; i < n_tiles && ok; ++i) {
       const int b = i & 1;
       const int kt0 = i * kTcBN;
@@ -272,21 +292,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
       }
       l_run = l_run * corr + rs;
       m_run = m_new;
-      // fold O_tile = P V into the running output
-      if (!mbar_wait(o_full, i & 1, abort_flag, p.status, 21)) { ok = false; break; }
-      tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < kTcD; c += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(t_lane + 256u + c, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) o_reg[c + j] = o_reg[c + j] * corr + __uint_as_float(v[j]);
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(o_empty);
+      if (i > 0 && !fold(i - 1, corr_prev)) { ok = false; break; }
+      corr_prev = corr;
     }
+    if (ok && n_tiles > 0) ok = fold(n_tiles - 1, corr_prev);
     if (ok && qi < lq) {
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       __nv_bfloat16* dst = p.out + (long long)(q_beg + qi) * p.o_stride + (long long)head * kTcD;
