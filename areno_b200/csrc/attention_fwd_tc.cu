@@ -33,7 +33,7 @@ struct AttnTcParams {
   float* lse;
   const int* cu_q;
   const int* cu_k;
-  const int* tile_prefix;  // 64-row query tiles per sequence (prefix sum); even local tiles start a CTA's work
+  const int* tile_prefix;  // 128-row query tiles per sequence (prefix sum)
   int num_seqs, hq, hkv;
   long long o_stride;
   float scale;
@@ -77,15 +77,14 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   // a CTA of this or an earlier launch already gave up on a wait: do not queue up behind the same fault
   if (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) return;
   // ---- work assignment (before any barrier set-up: CTAs without work leave at once)
-  const int tile64 = blockIdx.x;
+  // heavy tiles first: under a causal mask the last query tiles of a sequence see the most keys
+  const int tile = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
   const int head = blockIdx.y;
-  const int seq = find_seq(p.tile_prefix, p.num_seqs, tile64);
+  const int seq = find_seq(p.tile_prefix, p.num_seqs, tile);
   if (seq < 0) return;
-  const int local64 = tile64 - p.tile_prefix[seq];
-  if (local64 & 1) return;  // the CTA of the even 64-row tile covers both halves of the 128-row tile
   const int q_beg = p.cu_q[seq], lq = p.cu_q[seq + 1] - q_beg;
   const int k_beg = p.cu_k[seq], lk = p.cu_k[seq + 1] - k_beg;
-  const int q0 = local64 * 64;
+  const int q0 = (tile - p.tile_prefix[seq]) * kTcBM;
   if (q0 >= lq) return;
   const int shift = lk - lq;
   const int kvh = head / (p.hq / p.hkv);
@@ -252,9 +251,14 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         uint32_t v[32];
         tmem_ld_32x32(t_s + c, v);
         tmem_ld_wait();
+        if (nvis == kTcBN) {   // the whole tile is visible: no per-element test
 #pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (c + j < nvis) mx = fmaxf(mx, __uint_as_float(v[j]));
+          for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(v[j]));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (c + j < nvis) mx = fmaxf(mx, __uint_as_float(v[j]));
+        }
       }
       const float m_new = fmaxf(m_run, mx);
       const float m_use = m_new == -INFINITY ? 0.f : m_new;
@@ -268,12 +272,23 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         tmem_ld_32x32(t_s + c, v);
         tmem_ld_wait();
         uint32_t pk[16];
+        const float mb = m_use * sl2;
+        if (nvis == kTcBN) {
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          const float p0 = c + j < nvis ? ex2_approx((__uint_as_float(v[j]) - m_use) * sl2) : 0.f;
-          const float p1 = c + j + 1 < nvis ? ex2_approx((__uint_as_float(v[j + 1]) - m_use) * sl2) : 0.f;
-          rs += p0 + p1;
-          pk[j >> 1] = pack_bf16x2(p0, p1);
+          for (int j = 0; j < 32; j += 2) {
+            const float p0 = ex2_approx(fmaf(__uint_as_float(v[j]), sl2, -mb));
+            const float p1 = ex2_approx(fmaf(__uint_as_float(v[j + 1]), sl2, -mb));
+            rs += p0 + p1;
+            pk[j >> 1] = pack_bf16x2(p0, p1);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            const float p0 = c + j < nvis ? ex2_approx(fmaf(__uint_as_float(v[j]), sl2, -mb)) : 0.f;
+            const float p1 = c + j + 1 < nvis ? ex2_approx(fmaf(__uint_as_float(v[j + 1]), sl2, -mb)) : 0.f;
+            rs += p0 + p1;
+            pk[j >> 1] = pack_bf16x2(p0, p1);
+          }
         }
         uint8_t* sub = sP + (c >> 6) * 16384 + r * 128;   // 64-key sub-tile, this row
 #pragma unroll

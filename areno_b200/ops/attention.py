@@ -42,25 +42,29 @@ class VarlenMeta:
     max_k: int
     cu_q_host: list[int]
     cu_k_host: list[int]
+    tile_prefix_q128: torch.Tensor | None = None   # int32 [num_seqs + 1]: 128-row query tiles (tcgen05 forward)
+    total_q_tiles128: int = 0
 
 
 def build_varlen_meta(q_lens, k_lens=None, device="cpu") -> VarlenMeta:
     """q_lens / k_lens: python ints per sequence (k_lens defaults to q_lens)."""
     q_lens = [int(x) for x in q_lens]
     k_lens = q_lens if k_lens is None else [int(x) for x in k_lens]
-    cu_q, cu_k, tq, tk = [0], [0], [0], [0]
+    cu_q, cu_k, tq, tk, tq128 = [0], [0], [0], [0], [0]
     for lq, lk in zip(q_lens, k_lens):
         cu_q.append(cu_q[-1] + lq)
         cu_k.append(cu_k[-1] + lk)
         tq.append(tq[-1] + (lq + TILE - 1) // TILE)
         tk.append(tk[-1] + (lk + TILE - 1) // TILE)
-    packed = torch.tensor([cu_q, cu_k, tq, tk], dtype=torch.int32)
+        tq128.append(tq128[-1] + (lq + 127) // 128)
+    packed = torch.tensor([cu_q, cu_k, tq, tk, tq128], dtype=torch.int32)
     if str(device) != "cpu":
         packed = packed.pin_memory().to(device, non_blocking=True) if torch.cuda.is_available() else packed
     return VarlenMeta(
         cu_q=packed[0], cu_k=packed[1], tile_prefix_q=packed[2], tile_prefix_k=packed[3],
         num_seqs=len(q_lens), total_q=cu_q[-1], total_k=cu_k[-1], total_q_tiles=tq[-1], total_k_tiles=tk[-1],
         max_q=max(q_lens) if q_lens else 0, max_k=max(k_lens) if k_lens else 0, cu_q_host=cu_q, cu_k_host=cu_k,
+        tile_prefix_q128=packed[4], total_q_tiles128=tq128[-1],
     )
 
 
@@ -115,13 +119,13 @@ def attention_forward(q, k, v, meta: VarlenMeta, scale, causal=True, window=0, o
     if out is None:
         out = torch.empty((tq, hq, d), dtype=q.dtype, device=q.device)
     lse = torch.empty((hq, tq), dtype=torch.float32, device=q.device) if need_lse else None
-    if d == 128 and not window and _TC_FORWARD:
+    if d == 128 and not window and _TC_FORWARD and meta.tile_prefix_q128 is not None:
         # tcgen05 / TMEM kernel: 128 x 128 tiles, TMA-fed, softmax between the two MMAs
         _lib.call(
             "areno_attn_fwd_tc",
             q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), _lib.ptr(lse),
-            meta.cu_q.data_ptr(), meta.cu_k.data_ptr(), meta.tile_prefix_q.data_ptr(),
-            meta.num_seqs, meta.total_q_tiles, hq, hkv, d, tq, k.shape[0],
+            meta.cu_q.data_ptr(), meta.cu_k.data_ptr(), meta.tile_prefix_q128.data_ptr(),
+            meta.num_seqs, meta.total_q_tiles128, hq, hkv, d, tq, k.shape[0],
             q.stride(0), k.stride(0), v.stride(0), out.stride(0),
             float(scale), int(causal), _lib.status_buffer(q.device).data_ptr(), _lib.stream(),
         )
