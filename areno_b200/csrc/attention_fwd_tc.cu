@@ -1,9 +1,10 @@
 // Variable-length causal attention forward on the 5th-generation tensor cores (head_dim 128, GQA).
 //
-// One CTA per (128 query rows of one sequence, query head), six warps:
+// One CTA per (128 query rows of one sequence, query head), ten warps:
 //   warp 0      TMA producer: Q once, then K and V tiles of 128 keys through two-stage rings
 //   warp 1      MMA issuer:   S = Q K^T  into TMEM (two S buffers), O_tile = P V into TMEM
-//   warps 2-5   softmax:      thread r owns query row r.  It reads its S row from TMEM (tcgen05.ld), applies
+//   warps 2-9   softmax:      two threads per query row (64 keys / 64 output channels each).  A thread reads
+//                             its part of the S row from TMEM (tcgen05.ld), applies
 //                             mask / running max / exp2, writes P (bf16) into a 128-byte-swizzled K-major
 //                             shared tile that the second MMA consumes, then reads O_tile back from TMEM and
 //                             folds it into the running output kept in registers (o = o * corr + O_tile).
@@ -47,10 +48,12 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
                    const __grid_constant__ CUtensorMap tma_v, const AttnTcParams p) {
   extern __shared__ uint8_t smem_raw[];
+  __shared__ float s_max[2][2][kTcBM];   // [tile parity][column half][row]: partial row maxima of a warp pair
+  __shared__ float s_sum[2][kTcBM];      // [column half][row]: partial row sums, exchanged once at the end
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + kTcTile;          // 2 stages
@@ -100,11 +103,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
       mbar_init(&v_full[s], 1);
       mbar_init(&v_empty[s], 1);
       mbar_init(&s_full[s], 1);
-      mbar_init(&s_empty[s], 4);
+      mbar_init(&s_empty[s], 8);
       mbar_init(&o_full[s], 1);
-      mbar_init(&o_empty[s], 4);
+      mbar_init(&o_empty[s], 8);
     }
-    mbar_init(p_full, 4);
+    mbar_init(p_full, 8);
     mbar_init(p_empty, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -206,25 +209,32 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     }
   } else {
     // ------------------------------------ softmax warps ------------------------------------
+    // Eight warps: warps w and w + 4 share a TMEM lane quarter (rows) and split the columns, so every
+    // scheduler has two softmax warps to interleave.  Thread (row r, half h) handles keys [64 h, 64 h + 64)
+    // of each tile and output channels [64 h, 64 h + 64); the two halves of a row exchange their partial
+    // maximum through shared memory once per tile and their partial sums once at the end.
     const int qd = warp & 3;                 // TMEM lane quarter of this warp
+    const int half = (warp - 2) >> 2;        // 0: warps 2-5, 1: warps 6-9
     const int r = qd * 32 + lane;            // query row inside the tile
     const int qi = q0 + r;                   // query index inside the sequence
     const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(qd * 32) << 16);
     const float sl2 = p.scale * 1.4426950408889634f;
-    float o_reg[kTcD];
+    const int key_off = half * 64;
+    float o_reg[64];
 #pragma unroll
-    for (int j = 0; j < kTcD; ++j) o_reg[j] = 0.f;
+    for (int j = 0; j < 64; ++j) o_reg[j] = 0.f;
     float m_run = -INFINITY, l_run = 0.f, corr_prev = 0.f;
     bool ok = true;
+    auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + qd) : "memory"); };
     // o = o * c + O_tile(j): runs one tile late, after P of the next tile is on its way
     auto fold = [&](int j, float c) -> bool {
       const int ob = j & 1;
       if (!mbar_wait(&o_full[ob], (j >> 1) & 1, abort_flag, p.status, 21)) return false;
       tc_fence_after();
 #pragma unroll
-      for (int cc = 0; cc < kTcD; cc += 32) {
+      for (int cc = 0; cc < 64; cc += 32) {
         uint32_t v[32];
-        tmem_ld_32x32(t_lane + 256u + static_cast<uint32_t>(ob * kTcD) + cc, v);
+        tmem_ld_32x32(t_lane + 256u + static_cast<uint32_t>(ob * kTcD + key_off) + cc, v);
         tmem_ld_wait();
 #pragma unroll
         for (int jj = 0; jj < 32; ++jj) o_reg[cc + jj] = o_reg[cc + jj] * c + __uint_as_float(v[jj]);
@@ -239,19 +249,19 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
       const int kt0 = i * kTcBN;
       if (!mbar_wait(&s_full[b], (i >> 1) & 1, abort_flag, p.status, 19)) { ok = false; break; }
       tc_fence_after();
-      const uint32_t t_s = t_lane + static_cast<uint32_t>(b * kTcBN);
-      // keys this row may see in this tile: [kt0, limit)
+      const uint32_t t_s = t_lane + static_cast<uint32_t>(b * kTcBN + key_off);
+      // keys this row may see in this tile: [kt0, limit); this thread's share starts at key_off
       int limit = lk;
       if (p.causal) limit = min(limit, qi + shift + 1);
-      const int nvis = max(0, min(kTcBN, limit - kt0));
-      // pass 1: row maximum
+      const int nvis = max(0, min(64, limit - kt0 - key_off));
+      // pass 1: maximum over this thread's 64 keys, then over the row
       float mx = -INFINITY;
 #pragma unroll 1
-      for (int c = 0; c < kTcBN; c += 32) {
+      for (int c = 0; c < 64; c += 32) {
         uint32_t v[32];
         tmem_ld_32x32(t_s + c, v);
         tmem_ld_wait();
-        if (nvis == kTcBN) {   // the whole tile is visible: no per-element test
+        if (nvis == 64) {   // all visible: no per-element test
 #pragma unroll
           for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(v[j]));
         } else {
@@ -260,20 +270,24 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
             if (c + j < nvis) mx = fmaxf(mx, __uint_as_float(v[j]));
         }
       }
+      s_max[b][half][r] = mx;
+      pair_sync();
+      mx = fmaxf(mx, s_max[b][half ^ 1][r]);
       const float m_new = fmaxf(m_run, mx);
       const float m_use = m_new == -INFINITY ? 0.f : m_new;
       const float corr = ex2_approx((m_run - m_use) * sl2);   // m_run = -inf -> 0
       if (!mbar_wait(p_empty, (i & 1) ^ 1u, abort_flag, p.status, 20)) { ok = false; break; }
-      // pass 2: probabilities -> bf16 P tile (K-major, 128-byte swizzle), row sum
+      // pass 2: probabilities -> bf16 P tile (K-major, 128-byte swizzle), partial row sum
       float rs = 0.f;
+      uint8_t* sub = sP + half * 16384 + r * 128;   // this thread's 64-key sub-tile, this row
+      const float mb = m_use * sl2;
 #pragma unroll 1
-      for (int c = 0; c < kTcBN; c += 32) {
+      for (int c = 0; c < 64; c += 32) {
         uint32_t v[32];
         tmem_ld_32x32(t_s + c, v);
         tmem_ld_wait();
         uint32_t pk[16];
-        const float mb = m_use * sl2;
-        if (nvis == kTcBN) {
+        if (nvis == 64) {
 #pragma unroll
           for (int j = 0; j < 32; j += 2) {
             const float p0 = ex2_approx(fmaf(__uint_as_float(v[j]), sl2, -mb));
@@ -290,10 +304,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
             pk[j >> 1] = pack_bf16x2(p0, p1);
           }
         }
-        uint8_t* sub = sP + (c >> 6) * 16384 + r * 128;   // 64-key sub-tile, this row
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {
-          const int jc = ((c & 63) >> 3) + ch;            // 16-byte chunk index within the 128-byte row
+          const int jc = (c >> 3) + ch;               // 16-byte chunk index within the 128-byte row
           *reinterpret_cast<uint4*>(sub + ((jc ^ (r & 7)) << 4)) =
               make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
         }
@@ -311,11 +324,15 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
       corr_prev = corr;
     }
     if (ok && n_tiles > 0) ok = fold(n_tiles - 1, corr_prev);
+    // total row sum = the two halves' partial sums (both relative to the same final maximum)
+    s_sum[half][r] = l_run;
+    pair_sync();
+    l_run += s_sum[half ^ 1][r];
     if (ok && qi < lq) {
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      __nv_bfloat16* dst = p.out + (long long)(q_beg + qi) * p.o_stride + (long long)head * kTcD;
+      __nv_bfloat16* dst = p.out + (long long)(q_beg + qi) * p.o_stride + (long long)head * kTcD + key_off;
 #pragma unroll
-      for (int c = 0; c < kTcD; c += 8) {
+      for (int c = 0; c < 64; c += 8) {
         uint4 o;
         o.x = pack_bf16x2(o_reg[c] * inv, o_reg[c + 1] * inv);
         o.y = pack_bf16x2(o_reg[c + 2] * inv, o_reg[c + 3] * inv);
@@ -323,7 +340,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         o.w = pack_bf16x2(o_reg[c + 6] * inv, o_reg[c + 7] * inv);
         *reinterpret_cast<uint4*>(dst + c) = o;
       }
-      if (p.lse != nullptr) {
+      if (p.lse != nullptr && half == 0) {
         const long long total_q = p.cu_q[p.num_seqs];
         p.lse[(long long)head * total_q + q_beg + qi] = l_run > 0.f ? m_run * p.scale + logf(l_run) : -INFINITY;
       }
@@ -381,5 +398,5 @@ extern "C" int areno_attn_fwd_tc(const void* q, const void* k, const void* v, vo
     if (e != cudaSuccess) return (int)e;
     cfg = true;
   }
-  return (int)launch_pdl(attn_fwd_tc_kernel, dim3(total_tiles, hq), dim3(192), smem, stream, tq, tk, tv, p);
+  return (int)launch_pdl(attn_fwd_tc_kernel, dim3(total_tiles, hq), dim3(320), smem, stream, tq, tk, tv, p);
 }
