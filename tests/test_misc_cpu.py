@@ -187,6 +187,10 @@ def test_examples_pass_the_cli_preflight_and_behave(tmp_path):
         dataset_loader_fn=str(ex / "agentic/tictactoe/dataset_loader.py"),
         agent_fn=str(ex / "agentic/tictactoe/run_agent.py"), reward_fn_path=str(ex / "agentic/tictactoe/reward.py"))
     assert cfg.agent_fn.endswith("run_agent.py")
+    for name in ("shopping", "duelgrid", "coding"):
+        trainer_config_from_options(
+            algo="gspo", ckpt="m", dataset_path=f"{name}:8", dataset_loader_fn=str(ex / f"agentic/{name}/dataset_loader.py"),
+            agent_fn=str(ex / f"agentic/{name}/run_agent.py"), reward_fn_path=str(ex / f"agentic/{name}/reward.py"))
     trainer_config_from_options(algo="sft", ckpt="m", dataset_path="alpaca",
                                 dataset_loader_fn=str(ex / "sft/alpaca/dataset_loader.py"))
     trainer_config_from_options(algo="gspo", ckpt="m", dataset_path="gsm8k",
@@ -280,3 +284,25 @@ def test_gradient_buckets_know_when_they_are_final():
         assert launched and all(opt.buckets[i].min_layer >= layer for i in launched)
     not_yet = [i for i, b in enumerate(opt.buckets) if i not in opt.grad_comm.launched]
     assert not_yet and all(opt.buckets[i].min_layer == -1 for i in not_yet)   # the embedding leaves at the very end
+
+
+def test_checkpoint_compare_tool(tmp_path):
+    import torch
+    from safetensors.torch import save_file
+
+    from areno_b200.utils.compare_ckpt import compare, main
+
+    a = {"model.w": torch.arange(12, dtype=torch.float32).view(3, 4), "model.b": torch.ones(4), "only.a": torch.zeros(2)}
+    b = {"model.w": a["model.w"].clone(), "model.b": torch.ones(4) * 1.5, "only.b": torch.zeros(2)}
+    b["model.w"][0, 0] = 2.0
+    for name, tensors in (("a", a), ("b", b)):
+        (tmp_path / name).mkdir()
+        save_file(tensors, str(tmp_path / name / "model.safetensors"))
+    rep = compare(str(tmp_path / "a"), str(tmp_path / "b"))
+    assert rep["missing_in_other"] == ["only.a"] and rep["extra_in_other"] == ["only.b"] and not rep["identical"]
+    by_key = {r["key"]: r for r in rep["tensors"]}
+    assert by_key["model.b"]["max_abs"] == 0.5 and by_key["model.w"]["max_abs"] == 2.0
+    assert rep["tensors"][0]["key"] == "model.b"                     # sorted by relative difference
+    assert compare(str(tmp_path / "a"), str(tmp_path / "a"))["identical"]
+    assert main([str(tmp_path / "a"), str(tmp_path / "a"), "--pattern", "model.*"]) == 0
+    assert main([str(tmp_path / "a"), str(tmp_path / "b"), "--json"]) == 1
