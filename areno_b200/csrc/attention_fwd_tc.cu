@@ -75,7 +75,6 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  pdl_trigger();
   pdl_wait();   // before the first global read and before any early return
   // a CTA of this or an earlier launch already gave up on a wait: do not queue up behind the same fault
   if (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) return;
@@ -123,6 +122,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_trigger();   // TMEM is held: a dependent kernel that lands on this SM cannot take it from under this CTA
 
   if (warp == 0) {
     // ------------------------------------ TMA producer ------------------------------------
