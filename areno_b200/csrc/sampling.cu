@@ -208,18 +208,28 @@ __device__ __forceinline__ float block_sum_f(float v, float* red) {
 
 // part (optional, TP mode): float[rows, 6] = {best score, best global id, raw logit at best, raw max,
 // raw sum-exp, unused}; when part == nullptr the kernel finalises token + logprob itself.
+// With gridDim.y > 1 the vocabulary of a row is cut into slices of `slice_len` tokens (a multiple of 4, so
+// the random counters do not move): block (row, slice) writes its record to slice_part[slice][row] and
+// sample_combine_kernel picks the winner - one CTA per row cannot keep a B200 busy at 64 rows.
 template <typename T>
 __global__ void __launch_bounds__(kRowThreads)
 sample_kernel(const T* __restrict__ logits, long long ld, int V, int vocab_start, const signed char* __restrict__ cls,
               const int* __restrict__ gen_count, int min_new, float temperature, int top_k, float top_p,
               unsigned long long seed, const long long* __restrict__ row_uid, long long* __restrict__ out_token,
-              float* __restrict__ out_logprob, float* __restrict__ part) {
+              float* __restrict__ out_logprob, float* __restrict__ part, int slice_len, float* __restrict__ slice_part) {
   __shared__ OnlineLse red_lse[kRowThreads / 32];
   __shared__ Best red_best[kRowThreads / 32];
   __shared__ float red_f[32];
   __shared__ float sh_thresh;
   const long long row = blockIdx.x;
   const T* p = logits + row * ld;
+  if (gridDim.y > 1) {
+    const int v0 = (int)blockIdx.y * slice_len;
+    p += v0;
+    vocab_start += v0;
+    V = min(slice_len, V - v0);
+    part = slice_part + (long long)blockIdx.y * gridDim.x * 6;
+  }
   const int step = gen_count != nullptr ? gen_count[row] : 0;
   const bool mask_eos = step < min_new;
   const bool greedy = temperature <= 0.f;
@@ -347,6 +357,40 @@ sample_kernel(const T* __restrict__ logits, long long ld, int V, int vocab_start
   }
 }
 
+// Winner over the vocabulary slices of a row (records as written by sample_kernel); one thread per row.
+__global__ void sample_combine_kernel(const float* __restrict__ slice_part, int slices, long long rows,
+                                      long long* __restrict__ out_token, float* __restrict__ out_logprob,
+                                      float* __restrict__ part) {
+  const long long row = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= rows) return;
+  Best best;
+  best.v = -INFINITY;
+  best.idx = 0x7fffffff;
+  float raw_best = 0.f, m = -INFINITY, sum = 0.f;
+  for (int s = 0; s < slices; ++s) {
+    const float* q = slice_part + ((long long)s * rows + row) * 6;
+    const int id = __float_as_int(q[1]);
+    const float bv = q[0];
+    if (bv > best.v || (bv == best.v && id < best.idx)) { best.v = bv; best.idx = id; raw_best = q[2]; }
+    const float om = q[3], os = q[4];
+    if (om != -INFINITY) {
+      if (m == -INFINITY) { m = om; sum = os; }
+      else {
+        const float mn = fmaxf(m, om);
+        sum = sum * __expf(m - mn) + os * __expf(om - mn);
+        m = mn;
+      }
+    }
+  }
+  if (part != nullptr) {
+    float* q = part + row * 6;
+    q[0] = best.v; q[1] = __int_as_float(best.idx); q[2] = raw_best; q[3] = m; q[4] = sum; q[5] = 0.f;
+  } else {
+    out_token[row] = (long long)best.idx;
+    if (out_logprob != nullptr) out_logprob[row] = raw_best - (m + __logf(sum));
+  }
+}
+
 }  // namespace areno
 
 using namespace areno;
@@ -381,19 +425,29 @@ extern "C" int areno_logprob_bwd(void* logits, int is_bf16, long long ld, long l
   return (int)cudaGetLastError();
 }
 
+// slice_scratch: optional fp32 [slices, rows, 6]; with slices > 1 (and no top-k / top-p truncation, which needs
+// the whole row in one block) every row is sampled by `slices` blocks and a second tiny kernel picks the winner.
 extern "C" int areno_sample(const void* logits, int is_bf16, long long ld, long long rows, int V, int vocab_start,
                             const signed char* cls, const int* gen_count, int min_new, float temperature, int top_k,
                             float top_p, long long seed, const long long* row_uid, long long* out_token,
-                            float* out_logprob, float* part, cudaStream_t stream) {
+                            float* out_logprob, float* part, float* slice_scratch, int slices, cudaStream_t stream) {
   if (rows <= 0) return 0;
+  const bool truncate = temperature > 0.f && (top_k > 0 || top_p < 1.f);
+  int slice_len = V;
+  if (slice_scratch == nullptr || truncate || slices <= 1 || V < 4096) slices = 1;
+  if (slices > 1) slice_len = ((V + slices - 1) / slices + 3) / 4 * 4;
+  if (slices > 1 && (long long)slice_len * (slices - 1) >= V) slices = (V + slice_len - 1) / slice_len;
+  const dim3 grid((unsigned)rows, (unsigned)slices);
   if (is_bf16)
-    sample_kernel<__nv_bfloat16><<<(unsigned)rows, kRowThreads, 0, stream>>>(
+    sample_kernel<__nv_bfloat16><<<grid, kRowThreads, 0, stream>>>(
         (const __nv_bfloat16*)logits, ld, V, vocab_start, cls, gen_count, min_new, temperature, top_k, top_p,
-        (unsigned long long)seed, row_uid, out_token, out_logprob, part);
+        (unsigned long long)seed, row_uid, out_token, out_logprob, part, slice_len, slice_scratch);
   else
-    sample_kernel<float><<<(unsigned)rows, kRowThreads, 0, stream>>>((const float*)logits, ld, V, vocab_start, cls,
-                                                                    gen_count, min_new, temperature, top_k, top_p,
-                                                                    (unsigned long long)seed, row_uid, out_token,
-                                                                    out_logprob, part);
+    sample_kernel<float><<<grid, kRowThreads, 0, stream>>>((const float*)logits, ld, V, vocab_start, cls, gen_count,
+                                                           min_new, temperature, top_k, top_p, (unsigned long long)seed,
+                                                           row_uid, out_token, out_logprob, part, slice_len, slice_scratch);
+  if (slices > 1)
+    sample_combine_kernel<<<(unsigned)((rows + 127) / 128), 128, 0, stream>>>(slice_scratch, slices, rows, out_token,
+                                                                             out_logprob, part);
   return (int)cudaGetLastError();
 }

@@ -51,7 +51,7 @@ _SIGNATURES: dict[str, str] = {
     "areno_paged_decode": "pppppppppp" + "iiiii" + "ll" + "f" + "iiii" + "p",
     "areno_logprob_stats": "pilliplppppp",
     "areno_logprob_bwd": "pilliplppppp",
-    "areno_sample": "pilliippififlppppp",
+    "areno_sample": "pilliippififlpppp" + "pip",
     "areno_adamw_fp32": "ppppplfffffifpp",
     "areno_adamw_8bit": "ppppppplfffffifpp",
     "areno_sumsq_blocks": "",

@@ -154,13 +154,28 @@ def sample(logits, temperature: float = 1.0, top_k: int = -1, top_p: float = 1.0
         out_token = torch.empty(b, dtype=torch.int64, device=logits.device)
     if out_logprob is None and part is None:
         out_logprob = torch.empty(b, dtype=torch.float32, device=logits.device)
+    # few rows, long vocabulary: several blocks per row (vocabulary slices), winner picked by a second kernel
+    slices = 0 if b * 2 > 148 else min(16, max(1, 296 // max(b, 1)))
+    scratch = _slice_scratch(logits.device, slices * b * 6) if slices > 1 else None
     _lib.call(
         "areno_sample", logits.data_ptr(), int(logits.dtype == torch.bfloat16), logits.stride(0), b, v, vocab_start,
         _lib.ptr(cls), _lib.ptr(gen_count), int(min_new), float(temperature), int(top_k if top_k else -1),
         float(top_p), int(seed), _lib.ptr(row_uid), _lib.ptr(out_token), _lib.ptr(out_logprob), _lib.ptr(part),
-        _lib.stream(),
+        _lib.ptr(scratch), int(slices), _lib.stream(),
     )
     return out_token, out_logprob
+
+
+_SLICE_SCRATCH: dict = {}
+
+
+def _slice_scratch(device, elems: int) -> torch.Tensor:
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    buf = _SLICE_SCRATCH.get(key)
+    if buf is None or buf.numel() < elems:
+        buf = torch.empty(max(elems, 16 * 148 * 6), dtype=torch.float32, device=device)
+        _SLICE_SCRATCH[key] = buf
+    return buf
 
 
 def combine_shards(parts: torch.Tensor):
