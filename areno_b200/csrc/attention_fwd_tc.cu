@@ -1,4 +1,4 @@
-// Variable-length causal attention forward on the 5th-generation tensor cores (head_dim 128, GQA).
+// Variable-length causal attention forward on the 5th-generation tensor cores (head_dim 64 or 128, GQA).
 //
 // One CTA per (128 query rows of one sequence, query head), ten warps:
 //   warp 0      TMA producer: Q once, then K and V tiles of 128 keys through two-stage rings
@@ -12,22 +12,21 @@
 // softmax warps are busy, and O_tile is double-buffered so that the fold of tile i happens after P of tile
 // i+1 has been handed over (the P V latency is not on the softmax warps' critical path).
 // TMEM: columns [0,128) and [128,256) hold the two S buffers, [256,384) and [384,512) the two O_tile buffers.
-// Shared memory: Q 32 KB, K 2 x 32 KB, V 2 x 32 KB, P 32 KB (all 128-byte swizzle, 1024-byte aligned).
+// Shared memory at head_dim 128: Q 32 KB, K 2 x 32 KB, V 2 x 32 KB, P 32 KB (128-byte swizzle, 1024-byte aligned).
 //
 // Every mbarrier wait is bounded (common.cuh); on expiry the CTA records a status word, lets copies in
 // flight land, frees its TMEM and returns.  No multicast loads.
 //
-// Same contract as areno_attn_fwd (attention_fwd.cu) for head_dim 128 without a sliding window; role of
+// Same contract as areno_attn_fwd (attention_fwd.cu) for head_dim 64 / 128 without a sliding window; role of
 // flash_attn_varlen_func in the reference (areno/engine/layers/attention_backend/train.py:135-141).
 #include "attention_common.cuh"
 #include "launch.h"
 
 namespace areno {
 
-constexpr int kTcD = 128;       // head dim
 constexpr int kTcBM = 128;      // query rows per CTA
 constexpr int kTcBN = 128;      // keys per tile
-constexpr uint32_t kTcTile = 128 * 128 * 2;  // bytes of a 128 x 128 bf16 tile
+constexpr uint32_t kTcPTile = 128 * 128 * 2;  // bytes of the 128 x 128 bf16 P tile
 
 struct AttnTcParams {
   __nv_bfloat16* out;
@@ -48,6 +47,7 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
+template <int kTcD>   // head dim: 64 or 128
 __global__ void __launch_bounds__(320, 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
                    const __grid_constant__ CUtensorMap tma_v, const AttnTcParams p) {
@@ -55,11 +55,13 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
   __shared__ float s_max[2][2][kTcBM];   // [tile parity][column half][row]: partial row maxima of a warp pair
   __shared__ float s_sum[2][kTcBM];      // [column half][row]: partial row sums, exchanged once at the end
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  constexpr uint32_t kTcTile = 128 * kTcD * 2;   // bytes of a 128 x D bf16 tile (Q, K, V)
+  constexpr int kSub = kTcD / 64;                // 64-channel sub-tiles per row
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + kTcTile;          // 2 stages
   uint8_t* sV = sK + 2 * kTcTile;      // 2 stages
   uint8_t* sP = sV + 2 * kTcTile;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + kTcTile);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + kTcPTile);
   uint64_t* q_full = bars;          // 1
   uint64_t* k_full = bars + 1;      // 2
   uint64_t* k_empty = bars + 3;     // 2
@@ -128,8 +130,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     // ------------------------------------ TMA producer ------------------------------------
     if (lane == 0) {
       mbar_expect_tx(q_full, kTcTile);
-      tma_load_2d(sQ, &tma_q, q_full, head * kTcD, q_beg + q0);
-      tma_load_2d(sQ + 16384, &tma_q, q_full, head * kTcD + 64, q_beg + q0);
+#pragma unroll
+      for (int j = 0; j < kSub; ++j) tma_load_2d(sQ + j * 16384, &tma_q, q_full, head * kTcD + j * 64, q_beg + q0);
     }
     bool ok = true;
     for (int i = 0; i < n_tiles && ok; ++i) {
@@ -139,8 +141,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
       if (!mbar_wait(&k_empty[st], ph ^ 1u, abort_flag, p.status, 11)) { ok = false; break; }
       if (lane == 0) {
         mbar_expect_tx(&k_full[st], kTcTile);
-        tma_load_2d(sK + st * kTcTile, &tma_k, &k_full[st], kvh * kTcD, krow);
-        tma_load_2d(sK + st * kTcTile + 16384, &tma_k, &k_full[st], kvh * kTcD + 64, krow);
+#pragma unroll
+        for (int j = 0; j < kSub; ++j)
+          tma_load_2d(sK + st * kTcTile + j * 16384, &tma_k, &k_full[st], kvh * kTcD + j * 64, krow);
       }
       if (!mbar_wait(&v_empty[st], ph ^ 1u, abort_flag, p.status, 12)) { ok = false; break; }
       if (lane == 0) {
@@ -149,8 +152,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
 #pragma unroll
         for (int kb = 0; kb < 2; ++kb)
 #pragma unroll
-          for (int nh = 0; nh < 2; ++nh)
-            tma_load_2d(sV + st * kTcTile + kb * 16384 + nh * 8192, &tma_v, &v_full[st], kvh * kTcD + nh * 64,
+          for (int nh = 0; nh < kSub; ++nh)
+            tma_load_2d(sV + st * kTcTile + kb * (kSub * 8192) + nh * 8192, &tma_v, &v_full[st], kvh * kTcD + nh * 64,
                         krow + kb * 64);
       }
       __syncwarp();
@@ -173,7 +176,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
         const uint32_t a_base = smem_u32(sQ), b_base = smem_u32(sK + st * kTcTile);
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(st * kTcBN);
 #pragma unroll
-        for (int kb = 0; kb < 2; ++kb)
+        for (int kb = 0; kb < kSub; ++kb)
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
             umma_f16(d_tmem, make_smem_desc_sw128(a_base + kb * 16384 + kk * 32, 0, 1024),
@@ -200,7 +203,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
             umma_f16(d_tmem, make_smem_desc_sw128(a_base + kb * 16384 + kk * 32, 0, 1024),
-                     make_smem_desc_sw128(b_base + kb * 16384 + kk * 2048, 8192, 1024), idesc_o, (kb | kk) ? 1u : 0u);
+                     make_smem_desc_sw128(b_base + kb * (kSub * 8192) + kk * 2048, 8192, 1024), idesc_o,
+                     (kb | kk) ? 1u : 0u);
         umma_commit(&v_empty[st]);
         umma_commit(p_empty);
         umma_commit(&o_full[st]);
@@ -219,10 +223,12 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     const int qi = q0 + r;                   // query index inside the sequence
     const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(qd * 32) << 16);
     const float sl2 = p.scale * 1.4426950408889634f;
-    const int key_off = half * 64;
-    float o_reg[64];
+    const int key_off = half * 64;            // this thread's keys of every tile
+    constexpr int kOc = kTcD / 2;             // and its output channels
+    const int ch_off = half * kOc;
+    float o_reg[kOc];
 #pragma unroll
-    for (int j = 0; j < 64; ++j) o_reg[j] = 0.f;
+    for (int j = 0; j < kOc; ++j) o_reg[j] = 0.f;
     float m_run = -INFINITY, l_run = 0.f, corr_prev = 0.f;
     bool ok = true;
     auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + qd) : "memory"); };
@@ -232,9 +238,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
       if (!mbar_wait(&o_full[ob], (j >> 1) & 1, abort_flag, p.status, 21)) return false;
       tc_fence_after();
 #pragma unroll
-      for (int cc = 0; cc < 64; cc += 32) {
+      for (int cc = 0; cc < kOc; cc += 32) {
         uint32_t v[32];
-        tmem_ld_32x32(t_lane + 256u + static_cast<uint32_t>(ob * kTcD + key_off) + cc, v);
+        tmem_ld_32x32(t_lane + 256u + static_cast<uint32_t>(ob * kTcD + ch_off) + cc, v);
         tmem_ld_wait();
 #pragma unroll
         for (int jj = 0; jj < 32; ++jj) o_reg[cc + jj] = o_reg[cc + jj] * c + __uint_as_float(v[jj]);
@@ -330,9 +336,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
     l_run += s_sum[half ^ 1][r];
     if (ok && qi < lq) {
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      __nv_bfloat16* dst = p.out + (long long)(q_beg + qi) * p.o_stride + (long long)head * kTcD + key_off;
+      __nv_bfloat16* dst = p.out + (long long)(q_beg + qi) * p.o_stride + (long long)head * kTcD + ch_off;
 #pragma unroll
-      for (int c = 0; c < 64; c += 8) {
+      for (int c = 0; c < kOc; c += 8) {
         uint4 o;
         o.x = pack_bf16x2(o_reg[c] * inv, o_reg[c + 1] * inv);
         o.y = pack_bf16x2(o_reg[c + 2] * inv, o_reg[c + 3] * inv);
@@ -357,7 +363,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_const
 using namespace areno;
 
 // Same arguments as areno_attn_fwd plus the row counts of q and k / v (for the tensor maps) and the status
-// words.  head_dim must be 128 and there is no sliding window; returns -2 otherwise (callers fall back to
+// words.  head_dim must be 64 or 128 and there is no sliding window; returns -2 otherwise (callers fall back to
 // areno_attn_fwd).
 extern "C" int areno_attn_fwd_tc(const void* q, const void* k, const void* v, void* o, float* lse, const int* cu_q,
                                  const int* cu_k, const int* tile_prefix, int num_seqs, int total_tiles, int hq, int hkv,
@@ -365,7 +371,8 @@ extern "C" int areno_attn_fwd_tc(const void* q, const void* k, const void* v, vo
                                  long long k_stride, long long v_stride, long long o_stride, float scale, int causal,
                                  int* status, cudaStream_t stream) {
   if (total_tiles <= 0) return 0;
-  if (head_dim != kTcD) return -2;
+  if (head_dim != 128 && head_dim != 64) return -2;
+  const int kTcD = head_dim;
   if (hq % hkv != 0) return -3;
   if ((q_stride % 8) || (k_stride % 8) || (v_stride % 8) || (o_stride % 8)) return -3;
   if ((reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(k) & 15) ||
@@ -391,12 +398,18 @@ extern "C" int areno_attn_fwd_tc(const void* q, const void* k, const void* v, vo
   p.scale = scale;
   p.causal = causal;
   p.status = status;
-  constexpr int smem = 6 * (int)kTcTile + 256 + 1024;
+  const int smem = 5 * 128 * kTcD * 2 + (int)kTcPTile + 256 + 1024;
   static bool cfg = false;
   if (!cfg) {
-    cudaError_t e = cudaFuncSetAttribute(attn_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         5 * 128 * 128 * 2 + (int)kTcPTile + 256 + 1024);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_fwd_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               5 * 128 * 64 * 2 + (int)kTcPTile + 256 + 1024);
     if (e != cudaSuccess) return (int)e;
     cfg = true;
   }
-  return (int)launch_pdl(attn_fwd_tc_kernel, dim3(total_tiles, hq), dim3(320), smem, stream, tq, tk, tv, p);
+  if (kTcD == 128)
+    return (int)launch_pdl(attn_fwd_tc_kernel<128>, dim3(total_tiles, hq), dim3(320), smem, stream, tq, tk, tv, p);
+  return (int)launch_pdl(attn_fwd_tc_kernel<64>, dim3(total_tiles, hq), dim3(320), smem, stream, tq, tk, tv, p);
 }

@@ -11,6 +11,7 @@ so "weight sync" after a step is free when rollout and training share a layout.
 
 from __future__ import annotations
 
+import json
 import os
 import time
 from typing import Any
@@ -66,6 +67,7 @@ class RankWorker:
         self.trainer: TrainingManager | None = None
         self.infer: InferenceEngine | None = None
         self.roles = None
+        self._resume_state_from = config.model_path if (config.model_path and not config.dummy_load) else None
         self._actor_on_device = True
         self.loss_fn = None
         logger.info("worker ready rank=%d tp=%d/%d dp=%d/%d build_s=%.2f", ctx.rank, ctx.tp_rank, ctx.tp_size,
@@ -77,6 +79,10 @@ class RankWorker:
             self.trainer = TrainingManager(self.model, self.config, self.device, loss_fn=self.loss_fn)
             if self.infer is not None:
                 self.infer._graphs.clear()  # parameters were re-pointed into flat buckets
+            src, self._resume_state_from = self._resume_state_from, None
+            if src and os.path.isdir(os.path.join(src, "areno_state")):
+                if self.load_training_state(src):
+                    logger.info("resumed optimizer state and step counters from %s", src)
         return self.trainer
 
     def inference_engine(self, max_slots: int | None = None, max_model_len: int | None = None) -> InferenceEngine:
@@ -201,6 +207,58 @@ class RankWorker:
 
     def save_checkpoint(self, path: str) -> None:
         self.adapter.save_weights(self.model, path, self.config.model, source_path=self.config.model_path)
+        if os.environ.get("ARENO_SAVE_OPTIMIZER", "0") == "1" and self.trainer is not None:
+            self.save_training_state(path)
+
+    # Side-car next to the Hugging Face files (an extension: the reference resumes weights only,
+    # ``areno/engine/optim/adamw_fp32_master.py:155-237`` has state dicts that nothing calls).  Every rank writes
+    # its own optimizer shards; ``state.json`` carries the step counters and the layout they belong to.
+    def save_training_state(self, path: str) -> None:
+        from safetensors.torch import save_file
+
+        mgr = self.training_manager()
+        state = mgr.optimizer.state_dict()
+        folder = os.path.join(path, "areno_state")
+        os.makedirs(folder, exist_ok=True)
+        tensors = {}
+        for i, bucket in enumerate(state["buckets"]):
+            for key, t in bucket.items():
+                if t is not None:
+                    tensors[f"bucket{i}.{key}"] = t.contiguous()
+        ctx = self.ctx
+        save_file(tensors, os.path.join(folder, f"optimizer-rank{ctx.rank:05d}-of-{ctx.world_size:05d}.safetensors"))
+        if ctx.rank == 0:
+            with open(os.path.join(folder, "state.json"), "w") as f:
+                json.dump({"global_step": mgr.global_step, "optimizer_step": state["step"], "dp_size": state["dp_size"],
+                           "tp_size": ctx.tp_size, "world_size": ctx.world_size, "adam_8bit": bool(state["adam_8bit"]),
+                           "num_buckets": len(state["buckets"])}, f, indent=2)
+
+    def load_training_state(self, path: str) -> bool:
+        """Restore optimizer shards and step counters written by ``save_training_state``; returns False when the
+        folder is absent or was written for another layout (the run then starts from fresh optimizer state)."""
+        from safetensors.torch import load_file
+
+        folder = os.path.join(path, "areno_state")
+        meta_path = os.path.join(folder, "state.json")
+        if not os.path.isfile(meta_path):
+            return False
+        with open(meta_path) as f:
+            meta = json.load(f)
+        ctx = self.ctx
+        mgr = self.training_manager()
+        opt = mgr.optimizer
+        shard = os.path.join(folder, f"optimizer-rank{ctx.rank:05d}-of-{ctx.world_size:05d}.safetensors")
+        if (meta.get("world_size") != ctx.world_size or meta.get("tp_size") != ctx.tp_size
+                or meta.get("num_buckets") != len(opt.buckets) or bool(meta.get("adam_8bit")) != bool(opt.cfg.adam_8bit)
+                or not os.path.isfile(shard)):
+            logger.warning("training state at %s does not match this layout; starting from fresh optimizer state", folder)
+            return False
+        tensors = load_file(shard)
+        buckets = [{k: tensors.get(f"bucket{i}.{k}") for k in ("master", "m", "v", "m_scale", "v_scale")}
+                   for i in range(len(opt.buckets))]
+        opt.load_state_dict({"step": meta["optimizer_step"], "dp_size": meta["dp_size"], "buckets": buckets})
+        mgr.global_step = int(meta["global_step"])
+        return True
 
     def peak_memory_fraction(self) -> float:
         if self.device.type != "cuda":

@@ -119,7 +119,7 @@ def attention_forward(q, k, v, meta: VarlenMeta, scale, causal=True, window=0, o
     if out is None:
         out = torch.empty((tq, hq, d), dtype=q.dtype, device=q.device)
     lse = torch.empty((hq, tq), dtype=torch.float32, device=q.device) if need_lse else None
-    if d == 128 and not window and _TC_FORWARD and meta.tile_prefix_q128 is not None:
+    if d in (64, 128) and not window and _TC_FORWARD and meta.tile_prefix_q128 is not None:
         # tcgen05 / TMEM kernel: 128 x 128 tiles, TMA-fed, softmax between the two MMAs
         _lib.call(
             "areno_attn_fwd_tc",

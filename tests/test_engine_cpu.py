@@ -88,3 +88,56 @@ def test_sampling_is_reproducible_per_seed_and_differs_across_rows():
     a = eng.generate(prompts, SamplingParams(temperature=1.0, seed=11), (), 5)
     b = eng.generate(prompts, SamplingParams(temperature=1.0, seed=11), (), 5)
     assert all(len(t) == 5 for t in a.tokens) and all(len(t) == 5 for t in b.tokens)
+
+
+def test_training_state_sidecar_resumes_optimizer_and_step(tmp_path, monkeypatch):
+    """With ARENO_SAVE_OPTIMIZER=1 a checkpoint also carries the optimizer shards and step counters; a worker
+    started from that checkpoint continues exactly where the first one would have."""
+    import torch
+
+    from areno_b200.api import loss_fns
+    from areno_b200.engine.config import EngineConfig, OptimizerConfig, RuntimeConfig
+    from areno_b200.engine.worker import RankWorker
+    from areno_b200.parallel.context import single_process_context
+
+    from .helpers import tiny_config
+
+    single_process_context()
+
+    def pack(seed):
+        g = torch.Generator().manual_seed(seed)
+        ids = torch.randint(3, 512, (2, 24), generator=g)
+        pm = torch.ones((2, 24), dtype=torch.bool)
+        pm[:, 10:] = False
+        return dict(input_ids=ids, lengths=torch.tensor([24, 24]), prompt_mask=pm, logprobs=torch.zeros((2, 24)),
+                    advantages=torch.where(pm, torch.zeros(()), torch.ones(())) * torch.tensor([[1.0], [-1.0]]))
+
+    cfg = tiny_config()
+    ec = EngineConfig(model=cfg, dummy_load=True, seed=3, optimizer=OptimizerConfig(lr=1e-2),
+                      runtime=RuntimeConfig(max_model_len=64, activation_checkpointing=False))
+    a = RankWorker(ec, "cpu")
+    a.loss_fn = loss_fns.grpo_loss_fn
+    a.train([pack(1)])
+    monkeypatch.setenv("ARENO_SAVE_OPTIMIZER", "1")
+    path = str(tmp_path / "ckpt")
+    a.save_checkpoint(path)
+    import json
+    import os
+    meta = json.load(open(os.path.join(path, "areno_state", "state.json")))
+    assert meta["global_step"] == 1 and meta["optimizer_step"] == 1 and meta["world_size"] == 1
+    ec2 = EngineConfig(model=cfg, model_path=path, seed=99, optimizer=OptimizerConfig(lr=1e-2),
+                       runtime=RuntimeConfig(max_model_len=64, activation_checkpointing=False))
+    b = RankWorker(ec2, "cpu")
+    b.loss_fn = loss_fns.grpo_loss_fn
+    assert b.training_manager().global_step == 1 and b.trainer.optimizer.step_count == 1
+    for ba, bb in zip(a.trainer.optimizer.buckets, b.trainer.optimizer.buckets):
+        assert torch.equal(ba.m, bb.m) and torch.equal(ba.v, bb.v)
+    a.train([pack(2)])
+    b.train([pack(2)])
+    for pa, pb in zip(a.model.parameters(), b.model.parameters()):
+        assert torch.allclose(pa, pb, atol=1e-6)
+    # without the side-car the same checkpoint starts from fresh optimizer state
+    import shutil
+    shutil.rmtree(os.path.join(path, "areno_state"))
+    c = RankWorker(ec2, "cpu")
+    assert c.training_manager().global_step == 0

@@ -216,6 +216,8 @@ ATTN_CASES = [
     ([260, 90], None, 2, 1, 128, True, 96),
     ([1000, 513, 128, 1], None, 8, 2, 128, True, 0),   # many key tiles: every ring / phase of the tcgen05 forward
     ([700], [1500], 4, 1, 128, True, 0),               # chunked prefill shape: queries see a cached prefix
+    ([700, 130, 64], None, 8, 2, 64, True, 0),         # head size 64 on the tcgen05 forward
+    ([300], [900], 4, 4, 64, False, 0),
     ([100, 200], None, 4, 2, 256, True, 0),      # head_dim 256: backward runs as two 128-column CTAs
     ([260, 90], [300, 90], 2, 1, 256, True, 96),
 ]
