@@ -37,6 +37,10 @@ __device__ __forceinline__ void report_status(int* status, int code, int stage) 
 #ifndef ARENO_WAIT_LIMIT
 #define ARENO_WAIT_LIMIT (1u << 20)
 #endif
+// Wall-time bound of the same waits, in nanoseconds (must stay below 2^32).
+#ifndef ARENO_WAIT_NS
+#define ARENO_WAIT_NS 2000000000u
+#endif
 
 // ----------------------------------------------------------------------------------
 // Programmatic dependent launch.  A kernel launched through launch_pdl may become resident while
@@ -121,22 +125,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 
 // Bounded wait on an mbarrier phase.  `abort_flag` is a CTA-shared word: once any role
-// of the CTA has given up, the others stop waiting too.
+// of the CTA has given up, the others stop waiting too.  The bound is both a polling count and
+// wall time: how long one try_wait suspends is left to the hardware, so the count alone does
+// not say how long a lost arrival would be polled for.  The timer is only read once a first
+// poll has failed (the common case returns before it).
+__device__ __forceinline__ uint32_t globaltimer_lo() {
+  uint32_t t;
+  asm volatile("mov.u32 %0, %%globaltimer_lo;" : "=r"(t));
+  return t;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int stage) {
-  uint32_t ok = 0;
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint32_t t0 = globaltimer_lo();   // low word, nanoseconds: differences are exact below 4.29 s
   for (uint32_t it = 0; it < ARENO_WAIT_LIMIT; ++it) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred P;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, P;\n\t"
-        "}\n"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    if (ok) return true;
-    if ((it & 1023u) == 1023u && abort_flag != nullptr && *abort_flag != 0) return false;
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 7u) == 7u) {
+      if (abort_flag != nullptr && *abort_flag != 0) return false;
+      if (globaltimer_lo() - t0 > ARENO_WAIT_NS) break;
+    }
   }
   if (abort_flag != nullptr) *abort_flag = 1;
   report_status(status, kStatusWaitTimeout, stage);
