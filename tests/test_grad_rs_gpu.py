@@ -1,5 +1,5 @@
-"""Two GPUs: gradient reduce-scatter over peer memory against NCCL, bucket by bucket and through the
-sharded optimizer with hand-over during backward.  Skipped with fewer than two GPUs.  NVLS is switched off;
+"""Two, four and eight GPUs (one kernel variant each): gradient reduce-scatter over peer memory against NCCL, bucket by bucket and through the
+sharded optimizer with hand-over during backward.  Each size is skipped on a box with fewer GPUs.  NVLS is switched off;
 the kernels use plain peer loads."""
 
 from __future__ import annotations
@@ -95,16 +95,17 @@ def _rank_main(rank, world, port, ret):
         ret[rank] = "error: " + traceback.format_exc()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_peer_memory_grad_reduce_scatter_matches_nccl():
-    world = 2
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_peer_memory_grad_reduce_scatter_matches_nccl(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     mgr = mp.Manager()
     ret = mgr.dict()
     mp.spawn(_rank_main, args=(world, _free_port(), ret), nprocs=world, join=True)
     for r in range(world):
         out = ret[r]
         assert isinstance(out, dict), out
-        assert max(out["errs"]) < 1e-5, out["errs"]                      # two-term fp32 sums: exact up to order
+        assert max(out["errs"]) < 2e-5, out["errs"]                      # fp32 sums of `world` terms: equal up to order
         assert abs(out["norm"][0] - out["norm"][1]) < 1e-4 * max(1.0, out["norm"][1])
         assert out["pdiff"] < 1e-5
         assert out["buckets"] >= 4 and out["early"] >= out["buckets"] - 2   # most buckets left during backward
