@@ -29,6 +29,7 @@ from ..ops import sampling as sampling_ops
 from ..ops.paged_attention import PAGE
 from ..parallel.context import get_context
 from ..utils.log import get_logger
+from ..utils.tracing import trace_range
 from ._runtime import Scheduler
 
 logger = get_logger()
@@ -229,7 +230,8 @@ class InferenceEngine:
         done = self._poll(block=False)
         entries = self.sched.plan_prefill()
         if entries:
-            self._run_prefill(entries)
+            with trace_range("rollout/prefill"):
+                self._run_prefill(entries)
         if self.sched.num_decoding > 0:
             try:
                 updates = self.sched.reserve_decode(1)
@@ -239,14 +241,16 @@ class InferenceEngine:
             if updates:
                 self._push_block_updates(updates)
             extent = self.sched.active_extent
-            self._decode(_pick_bucket(self.buckets, extent), self._context_bucket(self.sched.max_seq_len + 1))
+            with trace_range("rollout/decode_step"):
+                self._decode(_pick_bucket(self.buckets, extent), self._context_bucket(self.sched.max_seq_len + 1))
             self.sched.advance(1)
             self.step_count += 1
             self._snapshot()
         elif not entries:
             if not self._snapshots:
                 self._snapshot()
-            done += self._poll(block=True)
+            with trace_range("rollout/wait_results"):
+                done += self._poll(block=True)
         return done
 
     def run_until_done(self, progress_interval_s: float = 0.0, on_finished: Callable | None = None) -> None:

@@ -26,6 +26,7 @@ import torch.distributed as dist
 
 from ..ops import optim as optim_ops
 from ..parallel.context import ParallelContext, get_context
+from ..utils.tracing import trace_range
 from .config import OptimizerConfig
 
 _ALIGN = 256  # elements; keeps every shard boundary 16-byte aligned for all dtypes
@@ -258,9 +259,11 @@ class ShardedAdamW:
         """Reduce, clip, update, all-gather.  Returns the gradient norm (device scalar tensor)."""
         self._ensure_state()
         self.fold_param_grads()
-        self.reduce_gradients()
+        with trace_range("optimizer/reduce_gradients"):
+            self.reduce_gradients()
         lr = self.lr if lr is None else lr
-        norm = torch.sqrt(self.grad_norm_sq())
+        with trace_range("optimizer/grad_norm"):
+            norm = torch.sqrt(self.grad_norm_sq())
         coef = None
         clip = self.cfg.grad_clip_norm if clip_norm is None else clip_norm
         if clip is not None and clip > 0:
@@ -283,8 +286,9 @@ class ShardedAdamW:
                                      self.step_count, 1.0 / self.dp, coef)
             if self.dp > 1:
                 gathers.append(dist.all_gather_into_tensor(b.param_flat, out, group=self.ctx.dp_group, async_op=True))
-        for w in gathers:
-            w.wait()
+        with trace_range("optimizer/param_all_gather_wait"):
+            for w in gathers:
+                w.wait()
         self.zero_grad()
         return norm
 

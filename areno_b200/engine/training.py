@@ -24,6 +24,7 @@ from ..models.dense import TrainMeta
 from ..ops.attention import build_varlen_meta
 from ..parallel.context import get_context
 from ..utils.log import get_logger
+from ..utils.tracing import trace_range
 from . import _runtime
 from .config import EngineConfig
 from .logprobs import lm_head_logprobs
@@ -218,13 +219,16 @@ class TrainingManager:
         loss_fn = pack.get("_loss_fn") or self.loss_fn
         if loss_fn is None:
             raise ValueError("no loss function: pass loss_fn or stamp '_loss_fn' on the pack")
-        pack = to_device(pack, self.device)
+        with trace_range("train/h2d"):
+            pack = to_device(pack, self.device)
         # last micro-batch of the window: gradient buckets are handed to the reduce-scatter as backward passes them
         self._layer_grad_hook = self.optimizer.begin_overlap() if allow_step and hasattr(self.optimizer, "begin_overlap") \
             else None
-        logprobs = self.forward_logprobs(pack)
+        with trace_range("train/forward"):
+            logprobs = self.forward_logprobs(pack)
         self._layer_grad_hook = None
-        loss_out = loss_fn(pack, logprobs)
+        with trace_range("train/loss"):
+            loss_out = loss_fn(pack, logprobs)
         metrics = None
         if isinstance(loss_out, tuple):
             loss, metrics = loss_out
@@ -232,7 +236,8 @@ class TrainingManager:
             loss = loss_out
         if not isinstance(loss, torch.Tensor):
             raise TypeError("train_loss_fn must return a torch.Tensor")
-        (loss / max(grad_scale, 1)).backward()
+        with trace_range("train/backward"):
+            (loss / max(grad_scale, 1)).backward()
         grad_norm = None
         lr = self.optimizer.lr
         if allow_step:
@@ -240,10 +245,12 @@ class TrainingManager:
                 self.model.finalize_router_expert_bias(ctx.tp_group, ctx.dp_group)
             lr = lr_for_step(self.config.optimizer, self.global_step + 1)
             self.optimizer.lr = lr
-            grad_norm = self.optimizer.step(lr=lr, clip_norm=self.grad_clip_norm)
+            with trace_range("train/optimizer_step"):
+                grad_norm = self.optimizer.step(lr=lr, clip_norm=self.grad_clip_norm)
             self.global_step += 1
         else:
-            self.optimizer.fold_param_grads()
+            with trace_range("train/fold_grads"):
+                self.optimizer.fold_param_grads()
         out_metrics = dict(metrics) if metrics else {}
         out_metrics["lr"] = lr
         if grad_norm is not None:

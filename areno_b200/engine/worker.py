@@ -21,6 +21,7 @@ import torch
 from ..models import registry as model_registry
 from ..parallel.context import get_context, use_context
 from ..utils.log import get_logger
+from ..utils.tracing import trace_range
 from .config import EngineConfig
 from .inference import InferenceEngine, RolloutOutput, SamplingParams
 from .training import TrainingManager
@@ -109,7 +110,8 @@ class RankWorker:
             return 0
         from ..parallel.reshard import reshard_into
 
-        n = reshard_into(self.rollout_model, self.model, self.rollout_ctx.tp_rank, self.rollout_ctx.tp_size)
+        with trace_range("weight_sync/reshard"):
+            n = reshard_into(self.rollout_model, self.model, self.rollout_ctx.tp_rank, self.rollout_ctx.tp_size)
         self._rollout_stale = False
         return n
 
@@ -143,7 +145,8 @@ class RankWorker:
         interval = self.config.decode_progress_interval_s if progress_interval_s is None else progress_interval_s
         with use_context(rctx):
             eng = self.inference_engine(slots, need_len)
-            out = eng.generate(prompts, params, eos_token_ids, max_new_tokens, progress_interval_s=interval)
+            with trace_range("rollout"):
+                out = eng.generate(prompts, params, eos_token_ids, max_new_tokens, progress_interval_s=interval)
         if (lo, hi) != (0, len(prompts)):
             out = RolloutOutput(tokens=out.tokens[lo:hi], logprobs=out.logprobs[lo:hi],
                                 finish_reasons=out.finish_reasons[lo:hi], stats=out.stats)
@@ -153,7 +156,8 @@ class RankWorker:
     def train(self, packs: list, gradient_accumulation_steps: int | None = None) -> list[dict]:
         self.prepare_for_train()
         self._rollout_stale = True
-        return self.training_manager().train(packs, gradient_accumulation_steps)
+        with trace_range("train"):
+            return self.training_manager().train(packs, gradient_accumulation_steps)
 
     # ---------------------------------------------------------- GPU residency
     def prepare_for_train(self):
@@ -163,9 +167,10 @@ class RankWorker:
 
     def prepare_actor_onloaded(self):
         if not self._actor_on_device:
-            self.model.onload_train_weights(self.device)
-            if self.trainer is not None:
-                self.trainer.optimizer.onload_state(self.device)
+            with trace_range("offload/onload_actor"):
+                self.model.onload_train_weights(self.device)
+                if self.trainer is not None:
+                    self.trainer.optimizer.onload_state(self.device)
             self._actor_on_device = True
 
     def prepare_actor_offloaded(self):
@@ -206,7 +211,8 @@ class RankWorker:
                 "dp_size": self.ctx.dp_size}
 
     def save_checkpoint(self, path: str) -> None:
-        self.adapter.save_weights(self.model, path, self.config.model, source_path=self.config.model_path)
+        with trace_range("checkpoint/save_weights"):
+            self.adapter.save_weights(self.model, path, self.config.model, source_path=self.config.model_path)
         if os.environ.get("ARENO_SAVE_OPTIMIZER", "0") == "1" and self.trainer is not None:
             self.save_training_state(path)
 

@@ -306,3 +306,64 @@ def test_checkpoint_compare_tool(tmp_path):
     assert compare(str(tmp_path / "a"), str(tmp_path / "a"))["identical"]
     assert main([str(tmp_path / "a"), str(tmp_path / "a"), "--pattern", "model.*"]) == 0
     assert main([str(tmp_path / "a"), str(tmp_path / "b"), "--json"]) == 1
+
+
+def test_trace_ranges_off_by_default_and_timed_when_enabled():
+    import contextlib
+    import time
+
+    from areno_b200.utils import tracing
+
+    tracing.configure(nvtx=False, timers=False)
+    assert isinstance(tracing.trace_range("x"), contextlib.nullcontext)   # shared no-op: nothing allocated
+    assert tracing.trace_range("x") is tracing.trace_range("y")
+    tracing.configure(timers=True)
+    try:
+        for _ in range(3):
+            with tracing.trace_range("phase/a"):
+                time.sleep(0.002)
+
+        @tracing.traced("phase/b")
+        def work(v):
+            return v + 1
+
+        assert work(1) == 2
+        rep = tracing.phase_report()
+        assert rep["phase/a"]["count"] == 3 and rep["phase/a"]["ms"] >= 5.0
+        assert rep["phase/b"]["count"] == 1
+        assert tracing.phase_report() == {}                  # the report resets the counters
+        with tracing.trace_range("phase/c"):
+            pass
+        merged = tracing.phase_report_max()                  # no process group: the local report
+        assert set(merged) == {"phase/c"}
+        assert "phase/c" in tracing.format_report(merged)
+    finally:
+        tracing.configure(nvtx=False, timers=False)
+
+
+def test_rollout_loop_reports_named_phases():
+    """A CPU generate call leaves prefill and decode ranges in the phase report."""
+    import torch
+
+    from areno_b200.engine.config import ModelConfig
+    from areno_b200.engine.inference import InferenceEngine, SamplingParams
+    from areno_b200.models.dense import DenseCausalLM, init_weights
+    from areno_b200.parallel.context import single_process_context
+    from areno_b200.utils import tracing
+
+    single_process_context()
+    cfg = ModelConfig(model_type="qwen2", vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=32, rope_theta=1e4, qk_norm=False,
+                      qkv_bias=True, dtype=torch.float32)
+    model = DenseCausalLM(cfg)
+    init_weights(model, 0)
+    eng = InferenceEngine(model, 512, "cpu", max_slots=2, max_model_len=64, max_prefill_tokens=64)
+    tracing.configure(timers=True)
+    try:
+        tracing.phase_report()
+        eng.generate([[5, 6, 7], [9, 10]], SamplingParams(temperature=0.0), max_new_tokens=4)
+        rep = tracing.phase_report()
+    finally:
+        tracing.configure(nvtx=False, timers=False)
+    assert rep["rollout/prefill"]["count"] >= 1
+    assert rep["rollout/decode_step"]["count"] >= 3
