@@ -32,12 +32,30 @@ from .config import OptimizerConfig
 _ALIGN = 256  # elements; keeps every shard boundary 16-byte aligned for all dtypes
 
 
+def _tp_grad_kind(p) -> str:
+    """How a parameter's gradient relates to the TP group, from its ``tp_replicated_grad`` annotation.
+
+    ``"sharded"``  no annotation: the parameter is a TP shard and its gradient is complete.
+    ``"partial"``  ``True``: the parameter is replicated and each rank computed the part of the gradient that
+                   flows through its own heads / experts; the ranks' gradients are summed.
+    ``"same"``     ``"same"``: replicated, and every rank already holds the full gradient because the gradient
+                   of the parameter's output was summed upstream (norm scales in front of a column-parallel
+                   layer, biases added after a row-parallel reduce, scalar heads on the replicated hidden
+                   state); nothing is reduced, and the norm counts it once.
+    """
+    flag = getattr(p, "tp_replicated_grad", False)
+    if flag == "same":
+        return "same"
+    return "partial" if flag else "sharded"
+
+
 @dataclass
 class _Bucket:
     params: list = field(default_factory=list)
     offsets: list = field(default_factory=list)
     numel: int = 0            # padded
     replicated: bool = False  # parameters replicated over TP (norm scales, biases of row-parallel layers)
+    tp_sum: bool = False      # replicated, and each TP rank holds only its part of the gradient (sum over TP needed)
     param_flat: torch.Tensor | None = None
     grad_flat: torch.Tensor | None = None
     master: torch.Tensor | None = None
@@ -79,14 +97,15 @@ class ShardedAdamW:
         # taps) keep their precision instead of being folded into a bf16 buffer
         groups: dict[tuple, list] = {}
         for p in params:
-            groups.setdefault((bool(getattr(p, "tp_replicated_grad", False)), p.dtype), []).append(p)
-        for (replicated, _dtype), plist in groups.items():
-            cur = _Bucket(replicated=replicated)
+            groups.setdefault((_tp_grad_kind(p), p.dtype), []).append(p)
+        for (kind, _dtype), plist in groups.items():
+            replicated = kind != "sharded"
+            cur = _Bucket(replicated=replicated, tp_sum=kind == "partial")
             for p in plist:
                 n = (p.numel() + _ALIGN - 1) // _ALIGN * _ALIGN
                 if cur.params and cur.numel + n > cap:
                     self.buckets.append(cur)
-                    cur = _Bucket(replicated=replicated)
+                    cur = _Bucket(replicated=replicated, tp_sum=kind == "partial")
                 cur.params.append(p)
                 cur.offsets.append(cur.numel)
                 cur.numel += n
@@ -217,12 +236,14 @@ class ShardedAdamW:
         return b.grad_flat[lo:lo + b.shard]
 
     def reduce_gradients(self):
-        """TP all-reduce of replicated-parameter gradients, then DP reduce-scatter (sum) in place."""
+        """TP all-reduce of the replicated parameters whose ranks hold partial gradients, then DP reduce-scatter (sum)
+        in place."""
         ctx = self.ctx
         if ctx.tp_size > 1:
             for b in self.buckets:
-                if b.replicated:
+                if b.tp_sum:      # "same" buckets already hold the full gradient on every rank
                     dist.all_reduce(b.grad_flat, group=ctx.tp_group)
+            self._sum_replicated_kv_grads()
         if self.dp > 1 and self.grad_comm is not None:
             if not self._overlap:
                 self.grad_comm.begin_step()
@@ -238,6 +259,25 @@ class ShardedAdamW:
             for w in works:
                 w.wait()
 
+    def _sum_replicated_kv_grads(self):
+        """K / V rows of a fused qkv projection are copies of one another on ``rep`` neighbouring ranks when the TP
+        size exceeds the KV head count (``kv_replicated`` on the parameter).  Each copy only sees the gradient of
+        its own query heads; summing over the copies keeps them identical."""
+        ctx = self.ctx
+        tp = ctx.tp_size
+        for b in self.buckets:
+            for p, off in zip(b.params, b.offsets):
+                rep = int(getattr(p, "kv_replicated", 0) or 0)
+                if rep <= 1:
+                    continue
+                hq_rows, _hkv, d, _ = p.tp_shard[1]
+                inner = p.numel() // p.shape[0]
+                g = b.grad_flat[off + hq_rows * d * inner: off + p.numel()]
+                buf = g.new_zeros((tp // rep, g.numel()))
+                buf[ctx.tp_rank // rep].copy_(g)
+                dist.all_reduce(buf, group=ctx.tp_group)
+                g.copy_(buf[ctx.tp_rank // rep])
+
     def grad_norm_sq(self) -> torch.Tensor:
         """Squared global gradient norm (of the DP-averaged gradient) as a 1-element device tensor."""
         ctx = self.ctx
@@ -246,6 +286,17 @@ class ShardedAdamW:
         repl = torch.zeros(1, dtype=torch.float32, device=dev)
         for b in self.buckets:
             optim_ops.sumsq(self._grad_shard(b), repl if b.replicated else sharded, accumulate=True)
+            if ctx.tp_size > 1 and not b.replicated:
+                # K / V rows that exist on `rep` ranks would be counted `rep` times by the TP sum below
+                lo = self.dp_rank * b.shard
+                for p, off in zip(b.params, b.offsets):
+                    rep = int(getattr(p, "kv_replicated", 0) or 0)
+                    if rep > 1:
+                        hq_rows, _hkv, d, _ = p.tp_shard[1]
+                        a0 = max(off + hq_rows * d * (p.numel() // p.shape[0]), lo)
+                        a1 = min(off + p.numel(), lo + b.shard)
+                        if a1 > a0:
+                            sharded -= b.grad_flat[a0:a1].pow(2).sum() * ((rep - 1) / rep)
         total = sharded + repl / max(1, ctx.tp_size)
         total = total / float(self.dp * self.dp)
         if self.dp > 1:

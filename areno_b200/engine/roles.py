@@ -168,7 +168,7 @@ class RoleManager:
                 else:
                     head.weight.zero_()
             for p in head.parameters():
-                p.tp_replicated_grad = True
+                p.tp_replicated_grad = "same"     # scalar head on the replicated hidden state: same gradient on every rank
         optimizer = None
         if spec.trainable:
             ocfg = OptimizerConfig(**{**w.config.optimizer.__dict__})

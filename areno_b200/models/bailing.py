@@ -176,6 +176,9 @@ class BailingLinearAttention(nn.Module):
         self.g_norm_weight = _param((hd,), torch.float32, device)      # viewed as [groups, hd / groups]
         self.q_norm = RMSNorm(self.d, cfg.rms_norm_eps, torch.float32, device) if cfg.qk_norm else None
         self.k_norm = RMSNorm(self.d, cfg.rms_norm_eps, torch.float32, device) if cfg.qk_norm else None
+        for n in (self.q_norm, self.k_norm):
+            if n is not None:
+                n.weight.tp_replicated_grad = True     # local heads only
         self.rot = int(self.d * cfg.partial_rotary_factor)
         self.silu = bool(cfg.linear_silu)
         self.eps = cfg.rms_norm_eps

@@ -87,6 +87,9 @@ class Attention(nn.Module):
         if cfg.qk_norm:
             self.q_norm = RMSNorm(cfg.head_dim, cfg.rms_norm_eps, dtype, device, cfg.norm_weight_offset)
             self.k_norm = RMSNorm(cfg.head_dim, cfg.rms_norm_eps, dtype, device, cfg.norm_weight_offset)
+            # per-head norms act on this rank's heads only: each rank holds a part of the gradient
+            self.q_norm.weight.tp_replicated_grad = True
+            self.k_norm.weight.tp_replicated_grad = True
         self.scale = cfg.attention_softmax_scale or cfg.head_dim ** -0.5
         # rotary layout; subclasses may install their own frequency table (e.g. rotation of the trailing channels)
         self.rot_dim, self.rope_interleaved, self.inv_freq = cfg.rotary_dim, cfg.rope_interleaved, None

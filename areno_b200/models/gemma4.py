@@ -71,6 +71,7 @@ class Gemma4Attention(nn.Module):
         self.o = RowParallelLinear(cfg.num_attention_heads * self.d, cfg.hidden_size, cfg.qkv_bias, dtype, device)
         self.q_norm = RMSNorm(self.d, cfg.rms_norm_eps, torch.float32, device)
         self.k_norm = RMSNorm(self.d, cfg.rms_norm_eps, torch.float32, device)
+        self.q_norm.weight.tp_replicated_grad = self.k_norm.weight.tp_replicated_grad = True   # local heads only
         self.v_norm = bool(cfg.v_norm)
         self.window = int(cfg.sliding_window) if sliding and cfg.sliding_window else 0   # inclusive of the current token
         self.scale = float(cfg.attention_softmax_scale or self.d ** -0.5)

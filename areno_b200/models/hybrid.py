@@ -7,7 +7,11 @@ Counterpart of ``areno/models/qwen3_5/model.py:90-467`` in the reference.  Diffe
 halves of HF's ``q_proj`` are two projections here (split at load time), linear-attention state lives
 in per-slot caches indexed by the engine's slot id instead of ``block_table[:, 0]``, and the
 recurrence / conv / gated-norm are this package's CUDA kernels (``ops/linear_attn.py``) instead of FLA.
-The linear-attention layers are not tensor-parallel yet (``tp_size == 1``).
+Tensor parallelism: both kinds of layer shard their heads over the TP group.  A Gated DeltaNet layer keeps
+``linear_num_key_heads / tp`` key heads with the value heads that belong to them (value heads are grouped
+consecutively per key head, so rank ``r`` owns one contiguous run of each), slices the fused projections, the
+depthwise conv filters, ``A_log`` and ``dt_bias`` accordingly, and reduces after ``out_proj``
+(reference: ``areno/models/qwen3_5/model.py:90-190`` shards the same tensors).
 """
 
 from __future__ import annotations
@@ -18,6 +22,7 @@ import torch.nn.functional as F
 
 from ..engine.config import ModelConfig
 from ..ops import gemm, linear_attn as la
+from ..parallel import collectives as coll
 from ..parallel.context import get_context
 from .dense import Attention, DecoderLayer, DenseCausalLM, InferMeta, TrainMeta
 from .layers import ColumnParallelLinear, RowParallelLinear, _param
@@ -42,11 +47,13 @@ class GatedAttention(Attention):
 class GatedDeltaNet(nn.Module):
     def __init__(self, cfg: ModelConfig, layer_idx: int, dtype, device):
         super().__init__()
-        if get_context().tp_size != 1:
-            raise NotImplementedError("Gated DeltaNet layers are not tensor-parallel yet (use tp_size == 1)")
+        tp = get_context().tp_size
+        if cfg.linear_num_key_heads % tp or cfg.linear_num_value_heads % tp:
+            raise ValueError(f"linear-attention heads ({cfg.linear_num_key_heads} key, {cfg.linear_num_value_heads} value) "
+                             f"must divide tp_size {tp}")
         self.cfg = cfg
         self.layer_idx = layer_idx
-        self.hk, self.hv = cfg.linear_num_key_heads, cfg.linear_num_value_heads
+        self.hk, self.hv = cfg.linear_num_key_heads // tp, cfg.linear_num_value_heads // tp   # local heads
         self.dk, self.dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
         self.key_dim, self.value_dim = self.hk * self.dk, self.hv * self.dv
         self.conv_dim = 2 * self.key_dim + self.value_dim
@@ -58,7 +65,14 @@ class GatedDeltaNet(nn.Module):
         self.dt_bias = _param((self.hv,), torch.float32, device)
         self.A_log = _param((self.hv,), torch.float32, device)
         self.norm_weight = _param((self.dv,), torch.float32, device)
-        self.out_proj = RowParallelLinear(self.value_dim, h, False, dtype, device)
+        self.norm_weight.tp_replicated_grad = True     # applied to this rank's heads: partial gradient
+        # how the local tensors sit in the full ones (used when a TP rollout layout is cut out of a tp=1 replica)
+        self.in_qkvz.tp_shard = ("merged", [self.key_dim, self.key_dim, self.value_dim, self.value_dim])
+        self.in_ba.tp_shard = ("merged", [self.hv, self.hv])
+        self.conv_weight.tp_shard = ("merged", [self.key_dim, self.key_dim, self.value_dim])
+        self.dt_bias.tp_shard = ("col", None)
+        self.A_log.tp_shard = ("col", None)
+        self.out_proj = RowParallelLinear(self.value_dim * tp, h, False, dtype, device)
         self.eps = cfg.rms_norm_eps
         self.scale = self.dk ** -0.5
         self.conv_cache = None    # fp32 [slots, conv_dim, K-1]
@@ -85,6 +99,7 @@ class GatedDeltaNet(nn.Module):
     def forward(self, x, positions, meta):
         del positions
         t = x.shape[0]
+        x = coll.copy_to_tp(x)   # identity forward, gradient summed over the TP group
         qkvz = gemm.linear(x, self.in_qkvz)
         g, beta = self._gates(gemm.linear(x, self.in_ba))
         conv_in = qkvz[:, : self.conv_dim]

@@ -2,12 +2,14 @@
 ``minicpmv4_6`` (reference: ``areno/models/qwen3_5/model.py:805-880``, ``checkpoint.py:36-100,560-675``;
 ``areno/models/minicpmv46/model.py:655-717``).
 
-Checkpoint layout handled here (tensor-parallel size 1): HF stores the attention output gate
+Checkpoint layout handled here: HF stores the attention output gate
 interleaved with the queries in ``q_proj`` (``[heads, 2, head_dim]`` rows) and the linear-attention
 input projections as four tensors (``in_proj_qkv``, ``in_proj_z``, ``in_proj_b``, ``in_proj_a``);
 they are regrouped into this package's fused parameters on load and split again on save.  Tensors
 outside the text trunk (vision tower, projector) pass through untouched when saving from a source
-directory."""
+directory.  At tensor-parallel size > 1 every rank cuts its heads / features / experts out of the HF tensors on
+load; on save the shards are gathered inside the TP group and TP rank 0 of the first data-parallel replica writes
+one file in the same HF layout."""
 
 from __future__ import annotations
 
@@ -87,9 +89,51 @@ def _prefix_in(index, candidates: tuple[str, ...]) -> str:
     raise KeyError(f"no embedding found under any of {candidates}")
 
 
+def _tp():
+    from ..parallel.context import get_context
+
+    ctx = get_context()
+    return ctx.tp_size, ctx.tp_rank
+
+
+def _sh0(t: torch.Tensor) -> torch.Tensor:
+    """This rank's equal share of dim 0."""
+    tp, r = _tp()
+    return t if tp == 1 else t.chunk(tp, 0)[r]
+
+
+def _sh1(t: torch.Tensor) -> torch.Tensor:
+    tp, r = _tp()
+    return t if tp == 1 else t.chunk(tp, 1)[r]
+
+
+def _full(t: torch.Tensor, dim: int = 0) -> torch.Tensor:
+    """All TP shards of ``t`` concatenated along ``dim`` (on every rank of the group)."""
+    from ..parallel.context import get_context
+
+    ctx = get_context()
+    if ctx.tp_size == 1:
+        return t
+    import torch.distributed as dist
+
+    t = t.detach().contiguous()
+    parts = [torch.empty_like(t) for _ in range(ctx.tp_size)]
+    dist.all_gather(parts, t, group=ctx.tp_group)
+    return torch.cat(parts, dim=dim)
+
+
+def _full_kv(t: torch.Tensor, rep: int) -> torch.Tensor:
+    """Gather K / V rows whose heads are replicated ``rep`` times over neighbouring ranks: keep one copy of each."""
+    full = _full(t, 0)
+    if rep <= 1:
+        return full
+    tp, _ = _tp()
+    return full.view(tp // rep, rep, t.shape[0], *full.shape[1:])[:, 0].reshape(-1, *full.shape[1:])
+
+
 def _load_dense_mlp(index, mlp, mp: str, put) -> None:
-    put(mlp.gate_up.weight, torch.cat([index.get(f"{mp}.gate_proj.weight"), index.get(f"{mp}.up_proj.weight")], 0))
-    put(mlp.down.weight, index.get(f"{mp}.down_proj.weight"))
+    put(mlp.gate_up.weight, torch.cat([_sh0(index.get(f"{mp}.gate_proj.weight")), _sh0(index.get(f"{mp}.up_proj.weight"))], 0))
+    put(mlp.down.weight, _sh1(index.get(f"{mp}.down_proj.weight")))
 
 
 def _load_mlp(index, mlp, mp: str, put) -> int:
@@ -126,16 +170,16 @@ def _save_mlp(out: dict, mlp, mp: str, cpu) -> None:
 
     def dense(m, prefix):
         inter = m.gate_up.weight.shape[0] // 2
-        out[f"{prefix}.gate_proj.weight"] = cpu(m.gate_up.weight[:inter])
-        out[f"{prefix}.up_proj.weight"] = cpu(m.gate_up.weight[inter:])
-        out[f"{prefix}.down_proj.weight"] = cpu(m.down.weight)
+        out[f"{prefix}.gate_proj.weight"] = cpu(_full(m.gate_up.weight[:inter], 0))
+        out[f"{prefix}.up_proj.weight"] = cpu(_full(m.gate_up.weight[inter:], 0))
+        out[f"{prefix}.down_proj.weight"] = cpu(_full(m.down.weight, 1))
 
     if not isinstance(mlp, SparseMoeBlock):
         dense(mlp, mp)
         return
     out[f"{mp}.gate.weight"] = cpu(mlp.router.weight)
-    out[f"{mp}.experts.gate_up_proj"] = cpu(mlp.experts.gate_up)
-    out[f"{mp}.experts.down_proj"] = cpu(mlp.experts.down)
+    out[f"{mp}.experts.gate_up_proj"] = cpu(_full(mlp.experts.gate_up, 0))
+    out[f"{mp}.experts.down_proj"] = cpu(_full(mlp.experts.down, 0))
     if mlp.shared is not None:
         dense(mlp.shared, f"{mp}.shared_expert")
     if mlp.shared_gate is not None:
@@ -151,11 +195,9 @@ class _HybridAdapter(ModelAdapter):
     # ------------------------------------------------------------------ load
     @torch.no_grad()
     def load_weights(self, model, path, config):
-        from ..engine.checkpoint import SafetensorsIndex, logger
-        from ..parallel.context import get_context
+        from ..engine.checkpoint import Rule, SafetensorsIndex, load_rule, logger
 
-        if get_context().tp_size != 1:
-            raise NotImplementedError("hybrid checkpoints load at tp_size == 1")
+        tp, rank = _tp()
         index = SafetensorsIndex(path)
         pre = _prefix_in(index, self.prefixes)
         used = 0
@@ -167,15 +209,15 @@ class _HybridAdapter(ModelAdapter):
             param.copy_(tensor.to(param.dtype))
             used += 1
 
-        vocab = config.vocab_size
-        emb = index.get(f"{pre}.embed_tokens.weight")
-        model.embed.weight.zero_()
-        model.embed.weight[:vocab].copy_(emb.to(model.embed.weight.dtype))
+        def put_vocab(param, key):
+            nonlocal used
+            load_rule(index, param, Rule("", (key,), "vocab"), (key,))   # this rank's rows, zero padded
+            used += 1
+
+        put_vocab(model.embed.weight, f"{pre}.embed_tokens.weight")
         put(model.norm.weight, index.get(f"{pre}.norm.weight"))
         if not config.tie_word_embeddings:
-            key = next(k for k in (f"{pre}.lm_head.weight", "lm_head.weight") if k in index)
-            model.lm_head.weight.zero_()
-            model.lm_head.weight[:vocab].copy_(index.get(key).to(model.lm_head.weight.dtype))
+            put_vocab(model.lm_head.weight, next(k for k in (f"{pre}.lm_head.weight", "lm_head.weight") if k in index))
         for i, layer in enumerate(model.layers):
             lp = f"{pre}.layers.{i}"
             put(layer.input_norm.weight, index.get(f"{lp}.input_layernorm.weight"))
@@ -184,23 +226,31 @@ class _HybridAdapter(ModelAdapter):
             a = layer.attn
             if isinstance(a, GatedDeltaNet):
                 la = f"{lp}.linear_attn"
-                put(a.in_qkvz, torch.cat([index.get(f"{la}.in_proj_qkv.weight"), index.get(f"{la}.in_proj_z.weight")], 0))
-                put(a.in_ba, torch.cat([index.get(f"{la}.in_proj_b.weight"), index.get(f"{la}.in_proj_a.weight")], 0))
-                put(a.conv_weight, index.get(f"{la}.conv1d.weight").reshape(a.conv_dim, a.k))
-                put(a.dt_bias, index.get(f"{la}.dt_bias"))
-                put(a.A_log, index.get(f"{la}.A_log"))
+                kd, vd = a.key_dim * tp, a.value_dim * tp        # full widths in the checkpoint
+                q, k, v = index.get(f"{la}.in_proj_qkv.weight").split([kd, kd, vd], 0)
+                put(a.in_qkvz, torch.cat([_sh0(q), _sh0(k), _sh0(v), _sh0(index.get(f"{la}.in_proj_z.weight"))], 0))
+                put(a.in_ba, torch.cat([_sh0(index.get(f"{la}.in_proj_b.weight")), _sh0(index.get(f"{la}.in_proj_a.weight"))], 0))
+                cq, ck, cv = index.get(f"{la}.conv1d.weight").reshape(2 * kd + vd, a.k).split([kd, kd, vd], 0)
+                put(a.conv_weight, torch.cat([_sh0(cq), _sh0(ck), _sh0(cv)], 0))
+                put(a.dt_bias, _sh0(index.get(f"{la}.dt_bias")))
+                put(a.A_log, _sh0(index.get(f"{la}.A_log")))
                 put(a.norm_weight, index.get(f"{la}.norm.weight"))
-                put(a.out_proj.weight, index.get(f"{la}.out_proj.weight"))
+                put(a.out_proj.weight, _sh1(index.get(f"{la}.out_proj.weight")))
             else:
                 sa = f"{lp}.self_attn"
                 qw = index.get(f"{sa}.q_proj.weight")
-                d, hq = a.d, a.hq
+                d, hq, hkv, rep = a.d, a.hq, a.hkv, a.qkv.kv_rep     # local head counts
                 if a.gate is not None:
-                    qg = qw.view(hq, 2, d, qw.shape[-1])
+                    qg = qw.view(hq * tp, 2, d, qw.shape[-1])[rank * hq:(rank + 1) * hq]
                     qw = qg[:, 0].reshape(hq * d, -1)
                     put(a.gate.weight, qg[:, 1].reshape(hq * d, -1))
-                put(a.qkv.weight, torch.cat([qw, index.get(f"{sa}.k_proj.weight"), index.get(f"{sa}.v_proj.weight")], 0))
-                put(a.o.weight, index.get(f"{sa}.o_proj.weight"))
+                else:
+                    qw = _sh0(qw)
+                kv_lo = (rank // rep) * hkv * d
+                kw = index.get(f"{sa}.k_proj.weight")[kv_lo:kv_lo + hkv * d]
+                vw = index.get(f"{sa}.v_proj.weight")[kv_lo:kv_lo + hkv * d]
+                put(a.qkv.weight, torch.cat([qw, kw, vw], 0))
+                put(a.o.weight, _sh1(index.get(f"{sa}.o_proj.weight")))
                 put(a.q_norm.weight, index.get(f"{sa}.q_norm.weight"))
                 put(a.k_norm.weight, index.get(f"{sa}.k_norm.weight"))
             if i % 8 == 7:
@@ -217,22 +267,26 @@ class _HybridAdapter(ModelAdapter):
         from ..parallel.context import get_context
 
         ctx = get_context()
-        if ctx.tp_size != 1:
-            raise NotImplementedError("hybrid checkpoints save at tp_size == 1")
+        import torch.distributed as dist
+
         if ctx.dp_rank != 0:
+            if ctx.world_size > 1:
+                dist.barrier()
             return
+        writer = ctx.tp_rank == 0          # every rank of the group takes part in the gathers, one writes
+        tp = ctx.tp_size
         os.makedirs(path, exist_ok=True)
         pre = config.checkpoint_prefix or "model"
         out: dict[str, torch.Tensor] = {}
 
         def cpu(t):
-            return t.detach().to("cpu", copy=True).contiguous()
+            return t.detach().to("cpu", copy=True).contiguous() if writer else t
 
         vocab = config.vocab_size
-        out[f"{pre}.embed_tokens.weight"] = cpu(model.embed.weight[:vocab])
+        out[f"{pre}.embed_tokens.weight"] = cpu(_full(model.embed.weight, 0)[:vocab])
         out[f"{pre}.norm.weight"] = cpu(model.norm.weight)
         if not config.tie_word_embeddings:
-            out["lm_head.weight"] = cpu(model.lm_head.weight[:vocab])
+            out["lm_head.weight"] = cpu(_full(model.lm_head.weight, 0)[:vocab])
         for i, layer in enumerate(model.layers):
             lp = f"{pre}.layers.{i}"
             out[f"{lp}.input_layernorm.weight"] = cpu(layer.input_norm.weight)
@@ -241,27 +295,33 @@ class _HybridAdapter(ModelAdapter):
             a = layer.attn
             if isinstance(a, GatedDeltaNet):
                 la = f"{lp}.linear_attn"
-                out[f"{la}.in_proj_qkv.weight"] = cpu(a.in_qkvz[: a.conv_dim])
-                out[f"{la}.in_proj_z.weight"] = cpu(a.in_qkvz[a.conv_dim:])
-                out[f"{la}.in_proj_b.weight"] = cpu(a.in_ba[: a.hv])
-                out[f"{la}.in_proj_a.weight"] = cpu(a.in_ba[a.hv:])
-                out[f"{la}.conv1d.weight"] = cpu(a.conv_weight.reshape(a.conv_dim, 1, a.k))
-                out[f"{la}.dt_bias"] = cpu(a.dt_bias)
-                out[f"{la}.A_log"] = cpu(a.A_log)
+                kd, vd = a.key_dim, a.value_dim       # local widths
+                q, k, v, z = a.in_qkvz.split([kd, kd, vd, vd], 0)
+                out[f"{la}.in_proj_qkv.weight"] = cpu(torch.cat([_full(q), _full(k), _full(v)], 0))
+                out[f"{la}.in_proj_z.weight"] = cpu(_full(z))
+                out[f"{la}.in_proj_b.weight"] = cpu(_full(a.in_ba[: a.hv]))
+                out[f"{la}.in_proj_a.weight"] = cpu(_full(a.in_ba[a.hv:]))
+                cq, ck, cv = a.conv_weight.split([kd, kd, vd], 0)
+                out[f"{la}.conv1d.weight"] = cpu(torch.cat([_full(cq), _full(ck), _full(cv)], 0).reshape(-1, 1, a.k))
+                out[f"{la}.dt_bias"] = cpu(_full(a.dt_bias))
+                out[f"{la}.A_log"] = cpu(_full(a.A_log))
                 out[f"{la}.norm.weight"] = cpu(a.norm_weight)
-                out[f"{la}.out_proj.weight"] = cpu(a.out_proj.weight)
+                out[f"{la}.out_proj.weight"] = cpu(_full(a.out_proj.weight, 1))
             else:
                 sa = f"{lp}.self_attn"
-                d, hq, hkv = a.d, a.hq, a.hkv
+                d, hq, hkv, rep = a.d, a.hq, a.hkv, a.qkv.kv_rep
                 qw = a.qkv.weight[: hq * d]
                 if a.gate is not None:
                     qw = torch.stack([qw.view(hq, d, -1), a.gate.weight.view(hq, d, -1)], 1).reshape(2 * hq * d, -1)
-                out[f"{sa}.q_proj.weight"] = cpu(qw)
-                out[f"{sa}.k_proj.weight"] = cpu(a.qkv.weight[hq * d:(hq + hkv) * d])
-                out[f"{sa}.v_proj.weight"] = cpu(a.qkv.weight[(hq + hkv) * d:])
-                out[f"{sa}.o_proj.weight"] = cpu(a.o.weight)
+                out[f"{sa}.q_proj.weight"] = cpu(_full(qw))
+                out[f"{sa}.k_proj.weight"] = cpu(_full_kv(a.qkv.weight[hq * d:(hq + hkv) * d], rep))
+                out[f"{sa}.v_proj.weight"] = cpu(_full_kv(a.qkv.weight[(hq + hkv) * d:], rep))
+                out[f"{sa}.o_proj.weight"] = cpu(_full(a.o.weight, 1))
                 out[f"{sa}.q_norm.weight"] = cpu(a.q_norm.weight)
                 out[f"{sa}.k_norm.weight"] = cpu(a.k_norm.weight)
+        if not writer:
+            dist.barrier()
+            return
         fname = "model-00001-of-00001.safetensors"
         save_file(out, os.path.join(path, fname), metadata={"format": "pt"})
         weight_map = {k: fname for k in out}
@@ -275,6 +335,8 @@ class _HybridAdapter(ModelAdapter):
         if not os.path.exists(os.path.join(path, "config.json")):
             with open(os.path.join(path, "config.json"), "w") as f:
                 json.dump(self.hf_config(config), f, indent=2)
+        if ctx.world_size > 1:
+            dist.barrier()
 
     def hf_config(self, config: ModelConfig) -> dict[str, Any]:
         return _hf_text_config(config)

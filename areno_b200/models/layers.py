@@ -7,7 +7,10 @@ the trainer and the checkpoint code:
 
 * ``tp_shard``: ``("col" | "row" | "vocab" | "qkv" | "merged" | None, meta)`` describing how the
   local tensor maps onto the full HF tensor(s);
-* ``tp_replicated_grad``: gradient must be summed over TP (norm weights, router gates, ...).
+* ``tp_replicated_grad``: the parameter is replicated over TP.  ``True``: each rank holds only the part of the
+  gradient that flows through its own heads / experts and the trainer sums them (per-head q / k norms, router
+  gates); ``"same"``: every rank already holds the full gradient (norm scales in front of a column-parallel
+  layer, biases added after the row-parallel reduce) and nothing is reduced.
 
 Role of ``areno/engine/layers/{linear,vocab,mlp,norm}.py`` in the reference.
 """
@@ -37,7 +40,9 @@ class RMSNorm(nn.Module):
         self.offset = offset
         self.weight = _param((hidden,), dtype, device) if with_scale else None
         if self.weight is not None:
-            self.weight.tp_replicated_grad = True
+            # default: the norm runs on a replicated activation and feeds a layer that sums the input gradient
+            # over TP; owners that apply it to their local heads switch the annotation to True (partial)
+            self.weight.tp_replicated_grad = "same"
 
     def forward(self, x, residual=None):
         if isinstance(x, gemm.SplitKPartial):
@@ -127,6 +132,8 @@ class QKVParallelLinear(nn.Module):
         if self.kv_rep > 1:
             # k/v rows are replicated over `kv_rep` ranks: their grads must be summed over replicas
             self.weight.kv_replicated = self.kv_rep
+            if self.bias is not None:
+                self.bias.kv_replicated = self.kv_rep
 
     def forward(self, x):
         return gemm.linear(coll.copy_to_tp(x), self.weight, self.bias)
@@ -149,7 +156,7 @@ class RowParallelLinear(nn.Module):
         self.weight.tp_shard = ("row", None)
         self.bias = _param((out_features,), dtype, device) if bias else None
         if self.bias is not None:
-            self.bias.tp_replicated_grad = True
+            self.bias.tp_replicated_grad = "same"
 
     def forward(self, x):
         ctx = get_context()

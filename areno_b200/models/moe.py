@@ -74,12 +74,17 @@ class SparseMoeBlock(nn.Module):
             if (cfg.extra or {}).get("shared_expert_gate"):
                 # per-token sigmoid gate on the shared expert's output (Qwen3.5-MoE)
                 self.shared_gate = _param((cfg.hidden_size,), dtype, device)
-                self.shared_gate.tp_replicated_grad = True
+                self.shared_gate.tp_replicated_grad = "same"
         self.last_counts = None  # tokens per local expert of the latest forward (device tensor, for metrics)
 
     def forward(self, x):
-        weights, ids = self.router(x)
-        out, plan = self.experts(x, weights, ids)
+        # Router and routed experts see the token through copy_to_tp: each rank back-propagates only the routes of
+        # its own experts (into the token and, through the routing weights, into the router), and the TP sum in
+        # copy_to_tp's backward completes the token gradient.  The shared expert sums its own input gradient, and
+        # its sigmoid gate is computed identically on every rank, so both read the token directly.
+        x_tp = coll.copy_to_tp(x)
+        weights, ids = self.router(x_tp)
+        out, plan = self.experts(x_tp, weights, ids)
         self.last_counts = plan.counts
         if self.shared is not None:
             shared = self.shared(x)
