@@ -14,7 +14,7 @@ ROOT = Path(__file__).resolve().parents[1]
 
 
 def _load(path: Path, name: str):
-    for mod in ("game", "tasks", "coding_tools"):      # each example ships its own helper modules of these names
+    for mod in ("game", "tasks", "coding_tools", "dataset_generator", "reward_no_tool"):      # each example ships its own helper modules of these names
         sys.modules.pop(mod, None)
     spec = importlib.util.spec_from_file_location(name, path)
     mod = importlib.util.module_from_spec(spec)
@@ -158,3 +158,61 @@ def test_coding_example():
     assert reward(SimpleNamespace(tool_results=passed)) == 1.0
     failed = [{"content": json.dumps(t)} for t in tool_msgs] + [{"content": json.dumps({"submitted": True, "tests_passed": False, "status": "solved"})}]
     assert reward(SimpleNamespace(tool_results=failed)) == 0.1 and reward(SimpleNamespace(tool_results=[])) == 0.0
+
+
+def test_tictactoe_one_step_task_and_web_ui():
+    import threading
+    import urllib.request
+    from http.server import ThreadingHTTPServer
+
+    base = ROOT / "examples" / "agentic" / "tictactoe"
+    gen = _load(base / "dataset_generator.py", "ttt_gen")
+    rows = gen.generate(60, seed=1)
+    assert len(rows) == 60 and len({r["board"] for r in rows}) == 60
+    assert sum(r["kind"] != "free" for r in rows) >= 35                       # mostly tactical positions
+    for r in rows:
+        assert r["board"].count("X") == r["board"].count("O") and all(r["board"][m - 1] == "." for m in r["answer"])
+    loader = _load(base / "dataset_loader_no_tool.py", "ttt_loader")
+    assert len(loader.load_training_dataset("tictactoe:16", default_loader=None, load_dataset=None, load_from_disk=None)) == 16
+
+    reward = _load(base / "reward_no_tool.py", "ttt_reward")
+    row = next(r for r in rows if r["kind"] == "win")
+    good = row["answer"][0]
+    other = next(i + 1 for i, c in enumerate(row["board"]) if c == "." and i + 1 not in row["answer"])
+    taken = row["board"].index("X") + 1
+    rec = lambda text: SimpleNamespace(completion=text, source_record=row, answer=row["answer"])   # noqa: E731
+    assert reward.reward_fn(rec(f"I win with <move>{good}</move>")) == 1.0
+    assert reward.reward_fn(rec(f"<move>{other}</move>")) == 0.2
+    assert reward.reward_fn(rec(f"<move>{taken}</move>")) == 0.0 and reward.reward_fn(rec("no tag")) == 0.0
+
+    agent = _load(base / "run_agent_no_tool.py", "ttt_agent")
+    session = ScriptedSession(lambda messages: {"role": "assistant", "content": "<move>5</move>"})
+    trajs = asyncio.run(agent.run_agent(session, _batch(rows[:4])))
+    assert len(trajs) == 4 and session.calls == 4 and all(len(t.turns) == 1 for t in trajs)
+
+    ui = _load(base / "web_ui.py", "ttt_ui")
+    games = ui.Games(base_url=None)
+    server = ThreadingHTTPServer(("127.0.0.1", 0), ui.make_handler(games))
+    threading.Thread(target=server.serve_forever, daemon=True).start()
+    url = f"http://127.0.0.1:{server.server_address[1]}"
+
+    def post(path, body):
+        req = urllib.request.Request(url + path, data=json.dumps(body).encode(), headers={"Content-Type": "application/json"})
+        return json.loads(urllib.request.urlopen(req, timeout=10).read())
+
+    try:
+        assert b"tic-tac-toe" in urllib.request.urlopen(url + "/", timeout=10).read()
+        g = post("/api/new", {"human": "X"})
+        assert g["board"] == "." * 9 and g["status"] == "playing"
+        res = post("/api/move", {"id": g["id"], "cell": 4})
+        assert res["board"][4] == "X" and res["board"].count("O") == 1 and res["reply"]["source"] == "rule opponent"
+        assert "error" in post("/api/move", {"id": g["id"], "cell": 4})
+        g2 = post("/api/new", {"human": "O"})
+        assert g2["board"].count("X") == 1                                      # the other side opened
+        for _ in range(6):                                                       # play the first free square to the end
+            if res["status"] != "playing":
+                break
+            res = post("/api/move", {"id": g["id"], "cell": res["board"].index(".")})
+        assert res["status"] in ("O wins", "X wins", "draw")
+    finally:
+        server.shutdown()
