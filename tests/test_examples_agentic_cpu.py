@@ -216,3 +216,33 @@ def test_tictactoe_one_step_task_and_web_ui():
         assert res["status"] in ("O wins", "X wins", "draw")
     finally:
         server.shutdown()
+
+
+def test_coding_cli_applies_reference_fix_and_dataset_file_matches_generator(tmp_path):
+    base = ROOT / "examples" / "agentic" / "coding"
+    sys.modules.pop("agent_loop", None)
+    cli = _load(base / "code_cli.py", "coding_cli")
+    assert cli.main(["--reference-fix", "--task", "2"]) == 0            # known fix -> tests pass -> exit code 0
+    out = tmp_path / "d.jsonl"
+    assert cli.main(["--dump-dataset", str(out), "--n", "24"]) == 0
+    assert out.read_text() == (base / "dataset.jsonl").read_text()      # the shipped file is the generator's output
+    assert cli.main(["--reference-fix", "--dataset", str(out), "--task", "5"]) == 0
+
+
+def test_duelgrid_web_ui_plays_full_turns():
+    base = ROOT / "examples" / "agentic" / "duelgrid"
+    ui = _load(base / "web_ui.py", "duel_ui")
+    duels = ui.Duels(base_url=None)
+    s = duels.new(seed=7)
+    assert len(s["grid"]) == 6 and sum(row.count("A") + row.count("U") for row in s["grid"]) == 2 and s["outcome"] is None
+    gid = s["id"]
+    s2 = duels.act(gid, s["legal"][-1])
+    assert s2["turn"] == 1 and s2["last"]["legal"] is True
+    s3 = duels.act(gid, {"action": "teleport"})
+    assert s3["turn"] == 2 and s3["last"]["legal"] is False               # an illegal answer costs the turn
+    assert "error" in duels.model_move(gid) and "error" in duels.act("nope", {"action": "wait"})
+    for _ in range(20):
+        if s3["outcome"]:
+            break
+        s3 = duels.act(gid, {"action": "wait"})
+    assert s3["outcome"] in ("win", "loss", "draw") and s3["legal"] == []
