@@ -34,9 +34,7 @@ _EXPORTS = {
     "sft_loss_fn": "areno_b200.api.loss_fns",
 }
 def __getattr__(name: str):
-    if name in ("Areno",):
-        return importlib.import_module("areno_b200.api.trainer").Trainer
-    if name == "DefaultBackend":
+    if name in ("Areno", "DefaultBackend"):     # the backend selector, as in ``areno/api/__init__.py:34-35``
         return importlib.import_module("areno_b200.api.models").BackendType.Areno
     if name in _EXPORTS:
         return getattr(importlib.import_module(_EXPORTS[name]), name)

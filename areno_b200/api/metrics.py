@@ -6,14 +6,39 @@ from __future__ import annotations
 import numpy as np
 
 
+class JsonlScalarWriter:
+    """Stand-in for ``SummaryWriter`` when no TensorBoard package is installed: one JSON object per scalar
+    (``{"tag", "value", "step", "time"}``) appended to ``<log_dir>/metrics.jsonl``."""
+
+    def __init__(self, log_dir: str):
+        import os
+
+        os.makedirs(log_dir, exist_ok=True)
+        self.path = os.path.join(log_dir, "metrics.jsonl")
+        self._fh = open(self.path, "a")
+
+    def add_scalar(self, tag: str, value, step: int) -> None:
+        import json
+        import time
+
+        self._fh.write(json.dumps({"tag": tag, "value": float(value), "step": int(step), "time": time.time()}) + "\n")
+
+    def flush(self) -> None:
+        self._fh.flush()
+
+    def close(self) -> None:
+        if not self._fh.closed:
+            self._fh.close()
+
+
 def create_tensorboard_writer(log_dir: str):
     try:
         from torch.utils.tensorboard import SummaryWriter
     except ImportError:
         try:
             from tensorboardX import SummaryWriter
-        except ImportError as exc:
-            raise ImportError("install TensorBoard: pip install tensorboard or pip install tensorboardX") from exc
+        except ImportError:
+            return JsonlScalarWriter(log_dir)
     return SummaryWriter(log_dir=log_dir)
 
 

@@ -269,6 +269,8 @@ class InferenceEngine:
         for req in self._poll(block=True, drain=True):
             if on_finished is not None:
                 on_finished(req)
+        if self.device.type == "cuda":
+            klib.check_status(self.device)   # bounded waits that ran out during this rollout surface here
 
     def generate(self, prompts: list[list[int]], params: SamplingParams, eos_token_ids=(), max_new_tokens: int = 16,
                  progress_interval_s: float = 0.0) -> RolloutOutput:

@@ -162,7 +162,12 @@ class TrainingManager:
             group = min(accum, remaining)
             allow_step = group_pos == group - 1
             results.append(self.train_step(shards, allow_step=allow_step, grad_scale=group, defer_sync=True))
-        return [_materialize(r) for r in results]
+        out = [_materialize(r) for r in results]
+        if self.device.type == "cuda":
+            from ..ops import _lib
+
+            _lib.check_status(self.device)   # a kernel that gave up on a bounded wait must fail the step, not pass silently
+        return out
 
     def forward_logprobs(self, pack: dict, need_entropy: bool = False):
         """Packed forward to per-action log-probs ``[num_actions]`` (fp32)."""

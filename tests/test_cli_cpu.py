@@ -262,3 +262,18 @@ def test_main_group_and_diagnostics():
     report["gpus"] = [{"index": 0, "name": "H100", "capability": "9.0", "memory_gb": 80, "sm_count": 132}]
     rows = {r.name: r for r in run_checks(report)}
     assert rows["GPUs are sm_100 (B200 class)"].status == "FAIL"
+
+
+def test_train_smoke_script_runs_the_cli_path_end_to_end():
+    """``ci/train_smoke.py`` drives option validation -> dataset -> trainer factory -> fit -> save on CPU."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1]
+    proc = subprocess.run([sys.executable, str(root / "ci" / "train_smoke.py"), "--algo", "grpo", "--steps", "2", "--device", "cpu"],
+                          capture_output=True, text=True, timeout=600, cwd=str(root))
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    out = json.loads(proc.stdout.strip().splitlines()[-1])
+    assert out["steps_done"] == 2 and out["checkpoints"] and out["metric_files"]

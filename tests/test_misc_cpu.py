@@ -367,3 +367,26 @@ def test_rollout_loop_reports_named_phases():
         tracing.configure(nvtx=False, timers=False)
     assert rep["rollout/prefill"]["count"] >= 1
     assert rep["rollout/decode_step"]["count"] >= 3
+
+
+def test_metrics_fall_back_to_jsonl_without_tensorboard(tmp_path, monkeypatch):
+    import builtins
+    import json
+
+    from areno_b200.api import metrics
+
+    real_import = builtins.__import__
+
+    def no_tensorboard(name, *args, **kwargs):
+        if name.startswith("torch.utils.tensorboard") or name.startswith("tensorboardX"):
+            raise ImportError(name)
+        return real_import(name, *args, **kwargs)
+
+    monkeypatch.setattr(builtins, "__import__", no_tensorboard)
+    writer = metrics.create_tensorboard_writer(str(tmp_path))
+    assert isinstance(writer, metrics.JsonlScalarWriter)
+    writer.add_scalar("train/loss", 0.5, 3)
+    writer.flush()
+    writer.close()
+    rows = [json.loads(line) for line in open(tmp_path / "metrics.jsonl")]
+    assert rows[0]["tag"] == "train/loss" and rows[0]["value"] == 0.5 and rows[0]["step"] == 3
