@@ -156,10 +156,14 @@ class Gemma4Attention(nn.Module):
 
 
 class ReplicatedLinear(nn.Module):
-    def __init__(self, in_features: int, out_features: int, dtype, device):
+    """A projection every TP rank holds whole.  ``grad``: ``"same"`` when all ranks compute the same gradient (the
+    projection sits on the replicated residual stream), ``True`` when each rank only sees the part that flows through
+    its own experts (the router) and the trainer sums them."""
+
+    def __init__(self, in_features: int, out_features: int, dtype, device, grad="same"):
         super().__init__()
         self.weight = _param((out_features, in_features), dtype, device)
-        self.weight.tp_replicated_grad = True
+        self.weight.tp_replicated_grad = grad
 
     def forward(self, x):
         return gemm.linear(x, self.weight)
@@ -173,7 +177,7 @@ class Gemma4Router(nn.Module):
         self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype, device, with_scale=False)
         self.scale = _param((cfg.hidden_size,), torch.float32, device)
         self.scale.tp_replicated_grad = True
-        self.proj = ReplicatedLinear(cfg.hidden_size, int(cfg.num_experts), dtype, device)
+        self.proj = ReplicatedLinear(cfg.hidden_size, int(cfg.num_experts), dtype, device, grad=True)
         self.root = cfg.hidden_size ** -0.5
 
     def forward(self, x):
@@ -236,7 +240,11 @@ class Gemma4DecoderLayer(nn.Module):
         x = x + self.post_attn_norm(a)
         dense = self.mlp(self.pre_ff_norm(x))
         if self.moe is not None:
-            routed = self.moe(self.pre_ff_norm_2(x), self.router(x))
+            # experts are sharded over TP: each rank back-propagates its own routes into the token and the router,
+            # copy_to_tp sums those parts (identity in forward)
+            expert_in = coll.copy_to_tp(self.pre_ff_norm_2(x))
+            router_in = coll.copy_to_tp(x)
+            routed = self.moe(expert_in, self.router(router_in))
             ff = self.post_ff_norm_1(dense) + self.post_ff_norm_2(routed)
         else:
             ff = dense

@@ -23,7 +23,11 @@ _LAYER_NORMS = (("input_norm", "input_layernorm"), ("post_attn_norm", "post_atte
 
 
 def _tensor_plan(model: Gemma4CausalLM, cfg: ModelConfig, pre: str):
-    """Yield ``(hf_key, getter, setter)`` triples describing every tensor of the text trunk."""
+    """Yield ``(hf_key, getter, setter, kind)`` describing every tensor of the text trunk.  ``getter`` / ``setter``
+    address this rank's part; ``kind`` says how that part sits in the full tensor: ``rep`` (replicated), ``rows`` /
+    ``cols`` (equal shares of dim 0 / dim 1 in rank order; experts are rows), ``vocab:<n>`` (row shares of a table
+    padded beyond its ``n`` valid rows) and ``kv:<rep>`` (row shares that ``rep`` neighbouring ranks hold copies of).
+    """
     vocab = cfg.vocab_size
 
     def whole(param):
@@ -32,42 +36,84 @@ def _tensor_plan(model: Gemma4CausalLM, cfg: ModelConfig, pre: str):
     def rows(param, lo, hi):
         return (lambda: param.detach()[lo:hi]), (lambda t: param[lo:hi].copy_(t.to(param.dtype)))
 
-    yield (f"{pre}.embed_tokens.weight", *rows(model.embed.weight, 0, vocab))
-    yield (f"{pre}.norm.weight", *whole(model.norm.weight))
+    yield (f"{pre}.embed_tokens.weight", *whole(model.embed.weight), f"vocab:{vocab}")
+    yield (f"{pre}.norm.weight", *whole(model.norm.weight), "rep")
     if not cfg.tie_word_embeddings:
-        yield ("lm_head.weight", *rows(model.lm_head.weight, 0, vocab))
+        yield ("lm_head.weight", *whole(model.lm_head.weight), f"vocab:{vocab}")
     if model.ple > 0:
-        yield (f"{pre}.embed_tokens_per_layer.weight", *rows(model.embed_per_layer.weight, 0, model.ple_vocab))
-        yield (f"{pre}.per_layer_model_projection.weight", *whole(model.per_layer_model_projection.weight))
-        yield (f"{pre}.per_layer_projection_norm.weight", *whole(model.per_layer_projection_norm.weight))
+        yield (f"{pre}.embed_tokens_per_layer.weight", *whole(model.embed_per_layer.weight), f"vocab:{model.ple_vocab}")
+        yield (f"{pre}.per_layer_model_projection.weight", *whole(model.per_layer_model_projection.weight), "rep")
+        yield (f"{pre}.per_layer_projection_norm.weight", *whole(model.per_layer_projection_norm.weight), "rep")
     for i, layer in enumerate(model.layers):
         lp = f"{pre}.layers.{i}"
         for attr, name in _LAYER_NORMS:
             mod = getattr(layer, attr)
             if mod is not None:
-                yield (f"{lp}.{name}.weight", *whole(mod.weight))
+                yield (f"{lp}.{name}.weight", *whole(mod.weight), "rep")
         a = layer.attn
         q, kv = a.hq * a.d, a.hkv * a.d
-        yield (f"{lp}.self_attn.q_proj.weight", *rows(a.qkv.weight, 0, q))
-        yield (f"{lp}.self_attn.k_proj.weight", *rows(a.qkv.weight, q, q + kv))
-        yield (f"{lp}.self_attn.v_proj.weight", *rows(a.qkv.weight, q + kv, q + 2 * kv))
-        yield (f"{lp}.self_attn.o_proj.weight", *whole(a.o.weight))
-        yield (f"{lp}.self_attn.q_norm.weight", *whole(a.q_norm.weight))
-        yield (f"{lp}.self_attn.k_norm.weight", *whole(a.k_norm.weight))
+        yield (f"{lp}.self_attn.q_proj.weight", *rows(a.qkv.weight, 0, q), "rows")
+        yield (f"{lp}.self_attn.k_proj.weight", *rows(a.qkv.weight, q, q + kv), f"kv:{a.qkv.kv_rep}")
+        yield (f"{lp}.self_attn.v_proj.weight", *rows(a.qkv.weight, q + kv, q + 2 * kv), f"kv:{a.qkv.kv_rep}")
+        yield (f"{lp}.self_attn.o_proj.weight", *whole(a.o.weight), "cols")
+        yield (f"{lp}.self_attn.q_norm.weight", *whole(a.q_norm.weight), "rep")
+        yield (f"{lp}.self_attn.k_norm.weight", *whole(a.k_norm.weight), "rep")
         inter = layer.mlp.gate_up.weight.shape[0] // 2
-        yield (f"{lp}.mlp.gate_proj.weight", *rows(layer.mlp.gate_up.weight, 0, inter))
-        yield (f"{lp}.mlp.up_proj.weight", *rows(layer.mlp.gate_up.weight, inter, 2 * inter))
-        yield (f"{lp}.mlp.down_proj.weight", *whole(layer.mlp.down.weight))
+        yield (f"{lp}.mlp.gate_proj.weight", *rows(layer.mlp.gate_up.weight, 0, inter), "rows")
+        yield (f"{lp}.mlp.up_proj.weight", *rows(layer.mlp.gate_up.weight, inter, 2 * inter), "rows")
+        yield (f"{lp}.mlp.down_proj.weight", *whole(layer.mlp.down.weight), "cols")
         if layer.ple_gate is not None:
-            yield (f"{lp}.per_layer_input_gate.weight", *whole(layer.ple_gate.weight))
-            yield (f"{lp}.per_layer_projection.weight", *whole(layer.ple_proj.weight))
-        yield (f"{lp}.layer_scalar", *whole(layer.layer_scalar))
+            yield (f"{lp}.per_layer_input_gate.weight", *whole(layer.ple_gate.weight), "rep")
+            yield (f"{lp}.per_layer_projection.weight", *whole(layer.ple_proj.weight), "rep")
+        yield (f"{lp}.layer_scalar", *whole(layer.layer_scalar), "rep")
         if layer.moe is not None:
-            yield (f"{lp}.router.scale", *whole(layer.router.scale))
-            yield (f"{lp}.router.proj.weight", *whole(layer.router.proj.weight))
-            yield (f"{lp}.router.per_expert_scale", *whole(layer.moe.per_expert_scale))
-            yield (f"{lp}.experts.gate_up_proj", *whole(layer.moe.gate_up))
-            yield (f"{lp}.experts.down_proj", *whole(layer.moe.down))
+            yield (f"{lp}.router.scale", *whole(layer.router.scale), "rep")
+            yield (f"{lp}.router.proj.weight", *whole(layer.router.proj.weight), "rep")
+            yield (f"{lp}.router.per_expert_scale", *whole(layer.moe.per_expert_scale), "rep")
+            yield (f"{lp}.experts.gate_up_proj", *whole(layer.moe.gate_up), "rows")
+            yield (f"{lp}.experts.down_proj", *whole(layer.moe.down), "rows")
+
+
+def _local_part(full: torch.Tensor, local_shape, kind: str, tp: int, rank: int) -> torch.Tensor:
+    """This rank's part of a checkpoint tensor, shaped like the local parameter (slice)."""
+    if tp == 1 and not kind.startswith("vocab"):
+        return full.reshape(local_shape)
+    if kind == "rep":
+        return full.reshape(local_shape)
+    if kind == "rows":
+        return full.chunk(tp, 0)[rank].reshape(local_shape)
+    if kind == "cols":
+        return full.chunk(tp, 1)[rank].reshape(local_shape)
+    if kind.startswith("kv:"):
+        rep = int(kind[3:])
+        n = local_shape[0]
+        lo = (rank // rep) * n
+        return full[lo:lo + n].reshape(local_shape)
+    if kind.startswith("vocab:"):
+        valid, per = int(kind[6:]), local_shape[0]
+        out = torch.zeros(local_shape, dtype=full.dtype)
+        lo, hi = min(rank * per, valid), min((rank + 1) * per, valid)
+        if hi > lo:
+            out[: hi - lo] = full[lo:hi]
+        return out
+    raise ValueError(f"unknown kind {kind}")
+
+
+def _full_tensor(local: torch.Tensor, kind: str) -> torch.Tensor:
+    """The checkpoint tensor rebuilt from the ranks' parts (a collective inside the TP group)."""
+    from .hybrid_adapters import _full, _full_kv
+
+    if kind == "rep":
+        return local
+    if kind == "rows":
+        return _full(local, 0)
+    if kind == "cols":
+        return _full(local, 1)
+    if kind.startswith("kv:"):
+        return _full_kv(local, int(kind[3:]))
+    if kind.startswith("vocab:"):
+        return _full(local, 0)[: int(kind[6:])]
+    raise ValueError(f"unknown kind {kind}")
 
 
 # keys that older / alternative exports use for the same tensor
@@ -148,18 +194,17 @@ class Gemma4Adapter(ModelAdapter):
         from ..engine.checkpoint import SafetensorsIndex, logger
         from ..parallel.context import get_context
 
-        if get_context().tp_size != 1:
-            raise NotImplementedError("Gemma-4 checkpoints load at tp_size == 1")
+        ctx = get_context()
         index = SafetensorsIndex(path)
         pre = next(p for p in (config.checkpoint_prefix, "model", "model.language_model") if f"{p}.embed_tokens.weight" in index)
         used = 0
-        for n_seen, (key, _get, put) in enumerate(_tensor_plan(model, config, pre)):
+        for n_seen, (key, _get, put, kind) in enumerate(_tensor_plan(model, config, pre)):
             found = self._find(index, pre, key, config)
             if found is None:
                 if key.rsplit(".", 1)[-1] in _OPTIONAL or key.endswith(_OPTIONAL):
                     continue
                 raise KeyError(f"checkpoint is missing {key}")
-            put(index.get(found).reshape(_get().shape))
+            put(_local_part(index.get(found), tuple(_get().shape), kind, ctx.tp_size, ctx.tp_rank))
             used += 1
             if n_seen % 256 == 255:
                 index.drop()
@@ -173,14 +218,24 @@ class Gemma4Adapter(ModelAdapter):
         from ..engine.checkpoint import _passthrough_untouched, copy_assets
         from ..parallel.context import get_context
 
+        import torch.distributed as dist
+
         ctx = get_context()
-        if ctx.tp_size != 1:
-            raise NotImplementedError("Gemma-4 checkpoints save at tp_size == 1")
         if ctx.dp_rank != 0:
+            if ctx.world_size > 1:
+                dist.barrier()
             return
         os.makedirs(path, exist_ok=True)
         pre = config.checkpoint_prefix or "model"
-        out = {key: get().to("cpu", copy=True).contiguous() for key, get, _put in _tensor_plan(model, config, pre)}
+        writer = ctx.tp_rank == 0        # every rank of the TP group takes part in the gathers, one writes
+        out = {}
+        for key, get, _put, kind in _tensor_plan(model, config, pre):
+            full = _full_tensor(get(), kind)
+            if writer:
+                out[key] = full.to("cpu", copy=True).contiguous()
+        if not writer:
+            dist.barrier()
+            return
         fname = "model-00001-of-00001.safetensors"
         save_file(out, os.path.join(path, fname), metadata={"format": "pt"})
         weight_map = {k: fname for k in out}
@@ -194,6 +249,8 @@ class Gemma4Adapter(ModelAdapter):
         if not os.path.exists(os.path.join(path, "config.json")):
             with open(os.path.join(path, "config.json"), "w") as f:
                 json.dump(self.hf_config(config), f, indent=2)
+        if ctx.world_size > 1:
+            dist.barrier()
 
     @staticmethod
     def hf_config(c: ModelConfig) -> dict[str, Any]:

@@ -230,6 +230,10 @@ def combine(ys: torch.Tensor, plan: MoePlan, weights: torch.Tensor) -> torch.Ten
 # ------------------------------------------------------------------------ grouped GEMMs
 def grouped_linear_reference(xs, w, plan: MoePlan):
     out = torch.zeros((plan.max_rows, w.shape[1]), dtype=xs.dtype, device=xs.device)
+    if torch.is_grad_enabled() and (xs.requires_grad or w.requires_grad):
+        # stay on the autograd graph even when no local expert received a row: under tensor parallelism every
+        # rank must run the same backward collectives, whatever the routing gave it
+        out = out + (xs.sum() * 0 + w.sum() * 0).to(out.dtype)
     er = plan.expert_rows.tolist()
     for e in range(plan.e_count):
         lo, n = er[2 * e], er[2 * e + 1]

@@ -166,13 +166,17 @@ def test_hybrid_tp2_matches_single_process(tmp_path, variant):
 def _plain_cfg(kind: str):
     from .helpers import tiny_config
 
+    if kind == "gemma4":           # sliding + global layers (global KV head replicated), KV-shared tail, PLE, MoE branch
+        from .test_gemma4_cpu import gemma_config
+
+        return gemma_config()
     if kind == "dense_kv_rep":     # qkv bias, one KV head on two ranks, per-head norms
         return tiny_config(model_type="qwen3", num_key_value_heads=1, qkv_bias=True, qk_norm=True, num_hidden_layers=2)
     return tiny_config(model_type="qwen3_moe", qk_norm=True, qkv_bias=False, num_experts=4, num_experts_per_tok=2,
                        moe_intermediate_size=32, norm_topk_prob=True, num_hidden_layers=2)
 
 
-def _plain_rank(rank, world, port, ret, src, kind):
+def _plain_rank(rank, world, port, ret, src, kind, dst=None):
     try:
         os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
         from areno_b200.models import registry
@@ -186,14 +190,17 @@ def _plain_rank(rank, world, port, ret, src, kind):
         adapter.load_weights(model, src, cfg)
         ids = torch.randint(3, 512, (40,), generator=torch.Generator().manual_seed(3))
         h, loss = _run(model, ids, [25, 15])
+        if dst is not None:
+            adapter.save_weights(model, dst, cfg)
         ret[rank] = dict(h=h, loss=loss, grad_norm=_optimizer_grad_norm(model))
         destroy_parallel()
     except BaseException:  # noqa: BLE001
         ret[rank] = traceback.format_exc()
 
 
-@pytest.mark.parametrize("kind", ["dense_kv_rep", "moe"])
+@pytest.mark.parametrize("kind", ["dense_kv_rep", "moe", "gemma4"])
 def test_tp2_gradient_norm_matches_single_process(tmp_path, kind):
+    from areno_b200.engine.checkpoint import SafetensorsIndex
     from areno_b200.models import registry
 
     single_process_context()
@@ -201,15 +208,24 @@ def test_tp2_gradient_norm_matches_single_process(tmp_path, kind):
     adapter = registry.get_adapter(cfg.model_type)
     ref = adapter.build(cfg)
     adapter.init_random(ref, 5)
-    src = str(tmp_path / "src")
+    if kind == "gemma4":
+        with torch.no_grad():          # spread the routing over all experts (a zero router scale sends every token the same way)
+            for layer in ref.layers:
+                layer.router.scale.fill_(1.0)
+                layer.moe.per_expert_scale.copy_(torch.linspace(0.8, 1.2, layer.moe.per_expert_scale.numel()))
+    src, dst = str(tmp_path / "src"), str(tmp_path / "dst")
     adapter.save_weights(ref, src, cfg)
     ids = torch.randint(3, 512, (40,), generator=torch.Generator().manual_seed(3))
     h_ref, loss_ref = _run(ref, ids, [25, 15])
     norm_ref = _optimizer_grad_norm(ref)
     ret = mp.Manager().dict()
-    mp.spawn(_plain_rank, args=(2, _free_port(), ret, src, kind), nprocs=2, join=True)
+    mp.spawn(_plain_rank, args=(2, _free_port(), ret, src, kind, dst), nprocs=2, join=True)
     for r in range(2):
         out = ret[r]
         assert isinstance(out, dict), out
         assert torch.allclose(out["h"], h_ref, atol=2e-5, rtol=1e-4)
         assert abs(out["grad_norm"] - norm_ref) < 1e-4 * norm_ref, (out["grad_norm"], norm_ref)
+    a, b = SafetensorsIndex(src), SafetensorsIndex(dst)       # written from the shards == loaded from
+    assert sorted(a.keys()) == sorted(b.keys())
+    for key in a.keys():
+        assert torch.equal(a.get(key), b.get(key)), key
