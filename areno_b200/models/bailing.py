@@ -13,7 +13,7 @@ inference alike (no separate fused-inference weights to prepare); linear attenti
 kernel with a hand-written backward (``ops/linear_attn.py``) instead of FLA's chunked Triton kernel for
 training and ``seg_la`` for inference; recurrent state is indexed by the engine's slot id; latent
 attention pads q / k / v with zero channels to the next kernel head size (192 -> 256) instead of
-calling flash-attn with unequal q-k and v widths.  Linear-attention layers require ``tp_size == 1``.
+calling flash-attn with unequal q-k and v widths.  All layer kinds shard their heads (and norm groups) over TP.
 """
 
 from __future__ import annotations
@@ -27,9 +27,10 @@ import torch.nn.functional as F
 from ..engine.config import ModelConfig
 from ..ops import attention as attn_ops
 from ..ops import gemm, linear_attn as la, moe as moe_ops, paged_attention as pa, rope as rope_ops
+from ..parallel import collectives as coll
 from ..parallel.context import get_context
 from .dense import Attention, DecoderLayer, DenseCausalLM, InferMeta, TrainMeta, _gather_history
-from .layers import ColumnParallelLinear, GatedMLP, RMSNorm, RowParallelLinear, _param
+from .layers import ColumnParallelLinear, GatedMLP, MergedColumnParallelLinear, RMSNorm, RowParallelLinear, _param
 from .moe import Experts
 
 
@@ -106,7 +107,7 @@ class BailingMLAttention(nn.Module):
         self.hq = self.hkv = self.h
         self.q_proj = ColumnParallelLinear(cfg.hidden_size, heads * self.dqk, False, dtype, device)
         self.kv_a = _param((self.lora + self.rope, cfg.hidden_size), dtype, device)
-        self.kv_a.tp_replicated_grad = True
+        self.kv_a.tp_replicated_grad = "same"     # both of its outputs get their gradient summed over TP downstream
         self.kv_a_norm = RMSNorm(self.lora, cfg.rms_norm_eps, dtype, device)
         self.kv_b = ColumnParallelLinear(self.lora, heads * (self.nope + self.vd), False, dtype, device)
         self.o = RowParallelLinear(heads * self.vd, cfg.hidden_size, cfg.use_bias, dtype, device)
@@ -122,7 +123,8 @@ class BailingMLAttention(nn.Module):
         t, h = x.shape[0], self.h
         q = self.q_proj(x).view(t, h, self.dqk)
         kv_a = gemm.linear(x, self.kv_a)
-        k_rope = self._rotate(kv_a[:, self.lora:].reshape(t, 1, self.rope), positions)
+        # the rotary key block is shared by all heads: each rank back-propagates its own heads' part, copy_to_tp sums them
+        k_rope = self._rotate(coll.copy_to_tp(kv_a[:, self.lora:]).reshape(t, 1, self.rope), positions)
         kv = self.kv_b(self.kv_a_norm(kv_a[:, : self.lora].contiguous())).view(t, h, self.nope + self.vd)
         q_rope = self._rotate(q[..., self.nope:], positions)
         pad_qk = q.new_zeros((t, h, self.d - self.dqk))
@@ -160,20 +162,30 @@ class BailingLinearAttention(nn.Module):
 
     def __init__(self, cfg: ModelConfig, layer_idx: int, dtype, device):
         super().__init__()
-        if get_context().tp_size != 1:
-            raise NotImplementedError("Bailing linear-attention layers are not tensor-parallel yet (use tp_size == 1)")
+        ctx = get_context()
+        tp = ctx.tp_size
         if str((cfg.extra or {}).get("linear_backend", "seg_la")) != "seg_la":
             raise ValueError("Bailing linear attention expects linear_backend='seg_la'")
         self.cfg, self.layer_idx = cfg, layer_idx
-        self.h, self.d = cfg.num_attention_heads, cfg.head_dim
+        heads = cfg.num_attention_heads
+        if heads % tp:
+            raise ValueError(f"{heads} attention heads do not divide tp_size {tp}")
+        self.h, self.d = heads // tp, cfg.head_dim          # heads of this TP rank
+        hd_full = heads * self.d
         hd = self.h * self.d
-        self.qkv = ColumnParallelLinear(cfg.hidden_size, 3 * hd, cfg.qkv_bias, dtype, device)
-        self.g_proj = ColumnParallelLinear(cfg.hidden_size, hd, False, dtype, device)
-        self.out_proj = RowParallelLinear(hd, cfg.hidden_size, cfg.use_bias, dtype, device)
-        self.groups = int(cfg.group_norm_size) if cfg.group_norm_size > 1 else 1
-        if hd % self.groups != 0:
-            raise ValueError(f"hidden width {hd} must be divisible by group_norm_size={self.groups}")
-        self.g_norm_weight = _param((hd,), torch.float32, device)      # viewed as [groups, hd / groups]
+        # q | k | v are three projections fused into one GEMM, each sharded by heads
+        self.qkv = MergedColumnParallelLinear(cfg.hidden_size, [hd_full] * 3, cfg.qkv_bias, dtype, device)
+        self.g_proj = ColumnParallelLinear(cfg.hidden_size, hd_full, False, dtype, device)
+        self.out_proj = RowParallelLinear(hd_full, cfg.hidden_size, cfg.use_bias, dtype, device)
+        groups_full = int(cfg.group_norm_size) if cfg.group_norm_size > 1 else 1
+        if hd_full % groups_full != 0:
+            raise ValueError(f"hidden width {hd_full} must be divisible by group_norm_size={groups_full}")
+        if groups_full % tp:
+            raise ValueError(f"group_norm_size {groups_full} must be a multiple of tp_size {tp}: a norm group cannot "
+                             "straddle two ranks")
+        self.groups = groups_full // tp
+        self.g_norm_weight = _param((hd,), torch.float32, device)      # viewed as [groups, hd / groups]; this rank's channels
+        self.g_norm_weight.tp_shard = ("col", None)
         self.q_norm = RMSNorm(self.d, cfg.rms_norm_eps, torch.float32, device) if cfg.qk_norm else None
         self.k_norm = RMSNorm(self.d, cfg.rms_norm_eps, torch.float32, device) if cfg.qk_norm else None
         for n in (self.q_norm, self.k_norm):
@@ -183,7 +195,8 @@ class BailingLinearAttention(nn.Module):
         self.silu = bool(cfg.linear_silu)
         self.eps = cfg.rms_norm_eps
         self.scale = self.d ** -0.5
-        self.register_buffer("slope", build_slopes(self.h, layer_idx, cfg.num_hidden_layers).to(device), persistent=False)
+        slopes = build_slopes(heads, layer_idx, cfg.num_hidden_layers)[ctx.tp_rank * self.h:(ctx.tp_rank + 1) * self.h]
+        self.register_buffer("slope", slopes.contiguous().to(device), persistent=False)
         self.state_cache = None   # fp32 [slots, heads, d, d]
 
     # pieces ------------------------------------------------------------------
@@ -311,8 +324,9 @@ class BailingSparseMoeBlock(nn.Module):
         self.last_counts = None
 
     def forward(self, x):
-        w, ids = self.gate(x)
-        out, plan = self.experts(x, w, ids)
+        x_tp = coll.copy_to_tp(x)      # experts are sharded over TP: sum the token gradient of the ranks' routes
+        w, ids = self.gate(x_tp)
+        out, plan = self.experts(x_tp, w, ids)
         self.last_counts = plan.counts
         if self.shared is not None:
             out = out + self.shared(x)

@@ -5,7 +5,8 @@
 ``attention.dense``, ``attention.g_proj`` / ``g_norm`` on linear layers, ``mlp.gate.weight`` /
 ``mlp.gate.expert_bias``, one ``mlp.experts.{e}.{gate,up,down}_proj`` triple per routed expert and
 ``mlp.shared_experts``.  Both ``attention`` and ``self_attn`` are accepted as the attention prefix on load.
-Loads and saves at tensor-parallel size 1."""
+At tensor-parallel size > 1 every rank cuts its heads / features / experts out of the HF tensors on load and the
+shards are gathered inside the TP group on save (TP rank 0 writes)."""
 
 from __future__ import annotations
 
@@ -36,7 +37,9 @@ def _dtype(name: Any, default=torch.bfloat16):
 
 
 def _tensor_plan(model: BailingCausalLM, cfg: ModelConfig):
-    """Yield ``(hf_key, getter, setter)`` for every tensor; attention keys carry ``{attn}`` for the prefix alias."""
+    """Yield ``(hf_key, getter, setter, kind)`` for every tensor; attention keys carry ``{attn}`` for the prefix alias.
+    ``getter`` / ``setter`` address this rank's part, ``kind`` says how it sits in the full tensor (the kinds of
+    ``gemma4_adapter._local_part``; ``expert`` marks one routed expert's matrix, whose key carries the global index)."""
 
     def whole(t):
         return (lambda: t.detach()), (lambda v: t.copy_(v.reshape(t.shape).to(t.dtype)))
@@ -47,54 +50,63 @@ def _tensor_plan(model: BailingCausalLM, cfg: ModelConfig):
     def expert(t, e, lo, hi):
         return (lambda: t.detach()[e, lo:hi]), (lambda v: t[e, lo:hi].copy_(v.to(t.dtype)))
 
-    yield ("model.word_embeddings.weight", *rows(model.embed.weight, 0, cfg.vocab_size))
-    yield ("model.norm.weight", *whole(model.norm.weight))
+    yield ("model.word_embeddings.weight", *whole(model.embed.weight), f"vocab:{cfg.vocab_size}")
+    yield ("model.norm.weight", *whole(model.norm.weight), "rep")
     if not cfg.tie_word_embeddings:
-        yield ("lm_head.weight", *rows(model.lm_head.weight, 0, cfg.vocab_size))
+        yield ("lm_head.weight", *whole(model.lm_head.weight), f"vocab:{cfg.vocab_size}")
     for i, layer in enumerate(model.layers):
         lp = f"model.layers.{i}"
-        yield (f"{lp}.input_layernorm.weight", *whole(layer.input_norm.weight))
-        yield (f"{lp}.post_attention_layernorm.weight", *whole(layer.post_norm.weight))
+        yield (f"{lp}.input_layernorm.weight", *whole(layer.input_norm.weight), "rep")
+        yield (f"{lp}.post_attention_layernorm.weight", *whole(layer.post_norm.weight), "rep")
         a, ap = layer.attn, f"{lp}.{{attn}}"
         if isinstance(a, BailingMLAttention):
-            yield (f"{ap}.q_proj.weight", *whole(a.q_proj.weight))
-            yield (f"{ap}.kv_a_proj_with_mqa.weight", *whole(a.kv_a))
-            yield (f"{ap}.kv_a_layernorm.weight", *whole(a.kv_a_norm.weight))
-            yield (f"{ap}.kv_b_proj.weight", *whole(a.kv_b.weight))
+            yield (f"{ap}.q_proj.weight", *whole(a.q_proj.weight), "rows")
+            yield (f"{ap}.kv_a_proj_with_mqa.weight", *whole(a.kv_a), "rep")
+            yield (f"{ap}.kv_a_layernorm.weight", *whole(a.kv_a_norm.weight), "rep")
+            yield (f"{ap}.kv_b_proj.weight", *whole(a.kv_b.weight), "rows")
             out = a.o
         else:
-            yield (f"{ap}.query_key_value.weight", *whole(a.qkv.weight))
-            if a.qkv.bias is not None:
-                yield (f"{ap}.query_key_value.bias", *whole(a.qkv.bias))
-            if a.q_norm is not None:
-                yield (f"{ap}.query_layernorm.weight", *whole(a.q_norm.weight))
-                yield (f"{ap}.key_layernorm.weight", *whole(a.k_norm.weight))
             if isinstance(a, BailingLinearAttention):
-                yield (f"{ap}.g_proj.weight", *whole(a.g_proj.weight))
-                yield (f"{ap}.g_norm.weight", *whole(a.g_norm_weight))
+                fused = "parts:3"
+            else:
+                fused = f"qkv:{a.hq * a.d}:{a.hkv * a.d}:{a.qkv.kv_rep}"
+            yield (f"{ap}.query_key_value.weight", *whole(a.qkv.weight), fused)
+            if a.qkv.bias is not None:
+                yield (f"{ap}.query_key_value.bias", *whole(a.qkv.bias), fused)
+            if a.q_norm is not None:
+                yield (f"{ap}.query_layernorm.weight", *whole(a.q_norm.weight), "rep")
+                yield (f"{ap}.key_layernorm.weight", *whole(a.k_norm.weight), "rep")
+            if isinstance(a, BailingLinearAttention):
+                yield (f"{ap}.g_proj.weight", *whole(a.g_proj.weight), "rows")
+                yield (f"{ap}.g_norm.weight", *whole(a.g_norm_weight), "rows")
                 out = a.out_proj
             else:
                 out = a.o
-        yield (f"{ap}.dense.weight", *whole(out.weight))
+        yield (f"{ap}.dense.weight", *whole(out.weight), "cols")
         if out.bias is not None:
-            yield (f"{ap}.dense.bias", *whole(out.bias))
+            yield (f"{ap}.dense.bias", *whole(out.bias), "rep")
         mlp = layer.mlp
         if isinstance(mlp, BailingSparseMoeBlock):
-            yield (f"{lp}.mlp.gate.weight", *whole(mlp.gate.weight))
-            yield (f"{lp}.mlp.gate.expert_bias", *whole(mlp.gate.expert_bias))
+            yield (f"{lp}.mlp.gate.weight", *whole(mlp.gate.weight), "rep")
+            yield (f"{lp}.mlp.gate.expert_bias", *whole(mlp.gate.expert_bias), "rep")
             inter = cfg.moe_intermediate_size
             for e in range(mlp.experts.e_local):
-                yield (f"{lp}.mlp.experts.{e}.gate_proj.weight", *expert(mlp.experts.gate_up, e, 0, inter))
-                yield (f"{lp}.mlp.experts.{e}.up_proj.weight", *expert(mlp.experts.gate_up, e, inter, 2 * inter))
-                yield (f"{lp}.mlp.experts.{e}.down_proj.weight", *expert(mlp.experts.down, e, 0, cfg.hidden_size))
+                ge = "{expert" + str(e) + "}"      # filled in with the global expert index of the rank that owns it
+                yield (f"{lp}.mlp.experts.{ge}.gate_proj.weight", *expert(mlp.experts.gate_up, e, 0, inter), f"expert:{e}")
+                yield (f"{lp}.mlp.experts.{ge}.up_proj.weight", *expert(mlp.experts.gate_up, e, inter, 2 * inter), f"expert:{e}")
+                yield (f"{lp}.mlp.experts.{ge}.down_proj.weight", *expert(mlp.experts.down, e, 0, cfg.hidden_size), f"expert:{e}")
             dense, dp = mlp.shared, f"{lp}.mlp.shared_experts"
         else:
             dense, dp = mlp, f"{lp}.mlp"
         if dense is not None:
             half = dense.gate_up.weight.shape[0] // 2
-            yield (f"{dp}.gate_proj.weight", *rows(dense.gate_up.weight, 0, half))
-            yield (f"{dp}.up_proj.weight", *rows(dense.gate_up.weight, half, 2 * half))
-            yield (f"{dp}.down_proj.weight", *whole(dense.down.weight))
+            yield (f"{dp}.gate_proj.weight", *rows(dense.gate_up.weight, 0, half), "rows")
+            yield (f"{dp}.up_proj.weight", *rows(dense.gate_up.weight, half, 2 * half), "rows")
+            yield (f"{dp}.down_proj.weight", *whole(dense.down.weight), "cols")
+
+
+def _expert_key(key: str, local_e: int, e_local: int, rank: int) -> str:
+    return key.replace("{expert" + str(local_e) + "}", str(rank * e_local + local_e))
 
 
 _OPTIONAL_SUFFIXES = ("mlp.gate.expert_bias",)
@@ -166,11 +178,17 @@ class BailingMoeLinearV2Adapter(ModelAdapter):
         from ..engine.checkpoint import SafetensorsIndex, logger
         from ..parallel.context import get_context
 
-        if get_context().tp_size != 1:
-            raise NotImplementedError("Bailing checkpoints load at tp_size == 1")
+        from .gemma4_adapter import _local_part
+
+        ctx = get_context()
+        tp, rank = ctx.tp_size, ctx.tp_rank
+        e_local = int(config.num_experts) // tp if config.num_experts else 0
         index = SafetensorsIndex(path)
         used = 0
-        for n_seen, (key, _get, put) in enumerate(_tensor_plan(model, config)):
+        for n_seen, (key, _get, put, kind) in enumerate(_tensor_plan(model, config)):
+            if kind.startswith("expert:"):
+                key = _expert_key(key, int(kind[7:]), e_local, rank)
+                kind = "rep"
             found = next((k for k in (key.format(attn="attention"), key.format(attn="self_attn")) if k in index), None)
             if found is None and key.endswith("query_key_value.weight"):
                 alt = key.replace("query_key_value", "qkv")
@@ -179,7 +197,7 @@ class BailingMoeLinearV2Adapter(ModelAdapter):
                 if key.endswith(_OPTIONAL_SUFFIXES):
                     continue
                 raise KeyError(f"checkpoint is missing {key.format(attn='attention')}")
-            put(index.get(found))
+            put(_local_part(index.get(found), tuple(_get().shape), kind, tp, rank))
             used += 1
             if n_seen % 256 == 255:
                 index.drop()
@@ -193,13 +211,36 @@ class BailingMoeLinearV2Adapter(ModelAdapter):
         from ..engine.checkpoint import _passthrough_untouched, copy_assets
         from ..parallel.context import get_context
 
+        import torch.distributed as dist
+
+        from .gemma4_adapter import _full_tensor
+        from .hybrid_adapters import _full
+
         ctx = get_context()
-        if ctx.tp_size != 1:
-            raise NotImplementedError("Bailing checkpoints save at tp_size == 1")
         if ctx.dp_rank != 0:
+            if ctx.world_size > 1:
+                dist.barrier()
             return
         os.makedirs(path, exist_ok=True)
-        out = {key.format(attn="attention"): get().to("cpu", copy=True).contiguous() for key, get, _put in _tensor_plan(model, config)}
+        tp = ctx.tp_size
+        writer = ctx.tp_rank == 0          # every rank of the TP group takes part in the gathers, one writes
+        e_local = int(config.num_experts) // tp if config.num_experts else 0
+        out = {}
+        for key, get, _put, kind in _tensor_plan(model, config):
+            if kind.startswith("expert:"):
+                local = get().contiguous()
+                stacked = _full(local.unsqueeze(0), 0)             # [tp, ...]: the same local expert slot of every rank
+                if writer:
+                    for r in range(tp):
+                        name = _expert_key(key, int(kind[7:]), e_local, r).replace("{attn}", "attention")
+                        out[name] = stacked[r].to("cpu", copy=True).contiguous()
+                continue
+            full = _full_tensor(get(), kind)
+            if writer:
+                out[key.replace("{attn}", "attention")] = full.to("cpu", copy=True).contiguous()
+        if not writer:
+            dist.barrier()
+            return
         fname = "model-00001-of-00001.safetensors"
         save_file(out, os.path.join(path, fname), metadata={"format": "pt"})
         weight_map = {k: fname for k in out}
@@ -213,6 +254,8 @@ class BailingMoeLinearV2Adapter(ModelAdapter):
         if not os.path.exists(os.path.join(path, "config.json")):
             with open(os.path.join(path, "config.json"), "w") as f:
                 json.dump(self.hf_config(config), f, indent=2)
+        if ctx.world_size > 1:
+            dist.barrier()
 
     @staticmethod
     def hf_config(c: ModelConfig) -> dict[str, Any]:

@@ -27,6 +27,8 @@ def _tensor_plan(model: Gemma4CausalLM, cfg: ModelConfig, pre: str):
     address this rank's part; ``kind`` says how that part sits in the full tensor: ``rep`` (replicated), ``rows`` /
     ``cols`` (equal shares of dim 0 / dim 1 in rank order; experts are rows), ``vocab:<n>`` (row shares of a table
     padded beyond its ``n`` valid rows) and ``kv:<rep>`` (row shares that ``rep`` neighbouring ranks hold copies of).
+    ``_local_part`` / ``_full_tensor`` also know ``parts:<n>`` (``n`` equal row blocks, each shared out by rows) and
+    ``qkv:<q>:<kv>:<rep>`` (a fused q | k | v tensor: ``q`` local query rows, ``kv`` local key rows, replication).
     """
     vocab = cfg.vocab_size
 
@@ -89,6 +91,15 @@ def _local_part(full: torch.Tensor, local_shape, kind: str, tp: int, rank: int) 
         n = local_shape[0]
         lo = (rank // rep) * n
         return full[lo:lo + n].reshape(local_shape)
+    if kind.startswith("parts:"):
+        n = int(kind[6:])
+        return torch.cat([part.chunk(tp, 0)[rank] for part in full.chunk(n, 0)], 0).reshape(local_shape)
+    if kind.startswith("qkv:"):
+        q, kv, rep = (int(v) for v in kind[4:].split(":"))
+        q_full, kv_full = q * tp, kv * (tp // rep)
+        k_lo = q_full + (rank // rep) * kv
+        v_lo = q_full + kv_full + (rank // rep) * kv
+        return torch.cat([full[rank * q:(rank + 1) * q], full[k_lo:k_lo + kv], full[v_lo:v_lo + kv]], 0).reshape(local_shape)
     if kind.startswith("vocab:"):
         valid, per = int(kind[6:]), local_shape[0]
         out = torch.zeros(local_shape, dtype=full.dtype)
@@ -111,6 +122,11 @@ def _full_tensor(local: torch.Tensor, kind: str) -> torch.Tensor:
         return _full(local, 1)
     if kind.startswith("kv:"):
         return _full_kv(local, int(kind[3:]))
+    if kind.startswith("parts:"):
+        return torch.cat([_full(part, 0) for part in local.chunk(int(kind[6:]), 0)], 0)
+    if kind.startswith("qkv:"):
+        q, kv, rep = (int(v) for v in kind[4:].split(":"))
+        return torch.cat([_full(local[:q], 0), _full_kv(local[q:q + kv], rep), _full_kv(local[q + kv:], rep)], 0)
     if kind.startswith("vocab:"):
         return _full(local, 0)[: int(kind[6:])]
     raise ValueError(f"unknown kind {kind}")

@@ -170,6 +170,10 @@ def _plain_cfg(kind: str):
         from .test_gemma4_cpu import gemma_config
 
         return gemma_config()
+    if kind in ("bailing_gqa", "bailing_mla"):   # lightning-attention layers + GQA or latent attention, grouped sigmoid router
+        from .test_bailing_cpu import bailing_config
+
+        return bailing_config(mla=kind == "bailing_mla", qkv_bias=True)
     if kind == "dense_kv_rep":     # qkv bias, one KV head on two ranks, per-head norms
         return tiny_config(model_type="qwen3", num_key_value_heads=1, qkv_bias=True, qk_norm=True, num_hidden_layers=2)
     return tiny_config(model_type="qwen3_moe", qk_norm=True, qkv_bias=False, num_experts=4, num_experts_per_tok=2,
@@ -198,7 +202,7 @@ def _plain_rank(rank, world, port, ret, src, kind, dst=None):
         ret[rank] = traceback.format_exc()
 
 
-@pytest.mark.parametrize("kind", ["dense_kv_rep", "moe", "gemma4"])
+@pytest.mark.parametrize("kind", ["dense_kv_rep", "moe", "gemma4", "bailing_gqa", "bailing_mla"])
 def test_tp2_gradient_norm_matches_single_process(tmp_path, kind):
     from areno_b200.engine.checkpoint import SafetensorsIndex
     from areno_b200.models import registry
