@@ -45,6 +45,9 @@ class RuntimeConfig:
     kv_cache_fraction: float = 0.9
     max_model_len: int | None = None
     logprob_chunk: int = 4096             # rows per lm_head + log-prob chunk
+    # training at tp_size > 1: shard the activations between the TP seams by tokens (all-gather + reduce-scatter in
+    # place of the all-reduces); ARENO_SEQUENCE_PARALLEL=1 switches it on as well
+    sequence_parallel: bool = False
     deterministic: bool = False
 
     def __post_init__(self) -> None:

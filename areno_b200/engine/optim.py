@@ -69,8 +69,13 @@ class _Bucket:
 
 
 class ShardedAdamW:
-    def __init__(self, model: torch.nn.Module, cfg: OptimizerConfig, ctx: ParallelContext | None = None):
+    def __init__(self, model: torch.nn.Module, cfg: OptimizerConfig, ctx: ParallelContext | None = None,
+                 sequence_parallel: bool = False):
+        """``sequence_parallel``: the model runs its norms and residual stream on 1 / tp of the rows, so replicated
+        parameters annotated ``"same"`` (norm scales, row-parallel biases) only see their own rows' gradient and are
+        summed over TP like the ``partial`` ones."""
         self.cfg = cfg
+        self.sequence_parallel = bool(sequence_parallel)
         self.ctx = ctx or get_context()
         self.dp = max(1, self.ctx.dp_size)
         self.dp_rank = self.ctx.dp_rank
@@ -100,12 +105,13 @@ class ShardedAdamW:
             groups.setdefault((_tp_grad_kind(p), p.dtype), []).append(p)
         for (kind, _dtype), plist in groups.items():
             replicated = kind != "sharded"
-            cur = _Bucket(replicated=replicated, tp_sum=kind == "partial")
+            tp_sum = kind == "partial" or (kind == "same" and self.sequence_parallel)
+            cur = _Bucket(replicated=replicated, tp_sum=tp_sum)
             for p in plist:
                 n = (p.numel() + _ALIGN - 1) // _ALIGN * _ALIGN
                 if cur.params and cur.numel + n > cap:
                     self.buckets.append(cur)
-                    cur = _Bucket(replicated=replicated, tp_sum=kind == "partial")
+                    cur = _Bucket(replicated=replicated, tp_sum=tp_sum)
                 cur.params.append(p)
                 cur.offsets.append(cur.numel)
                 cur.numel += n

@@ -146,7 +146,10 @@ class TrainingManager:
         self.config = config
         self.device = torch.device(device)
         self.loss_fn = loss_fn
-        self.optimizer = ShardedAdamW(model, config.optimizer)
+        ctx = get_context()
+        want_sp = config.runtime.sequence_parallel or os.environ.get("ARENO_SEQUENCE_PARALLEL", "0") == "1"
+        self.sequence_parallel = bool(want_sp and ctx.tp_size > 1 and getattr(model, "supports_sequence_parallel", False))
+        self.optimizer = ShardedAdamW(model, config.optimizer, sequence_parallel=self.sequence_parallel)
         self.global_step = 0
         self.grad_clip_norm = config.optimizer.grad_clip_norm
 
@@ -180,7 +183,8 @@ class TrainingManager:
         meta = TrainMeta(build_varlen_meta(lens, device=self.device),
                          activation_checkpointing=self.config.runtime.activation_checkpointing,
                          checkpoint_layers=self._checkpoint_layers(int(ids.numel())),
-                         layer_grad_hook=getattr(self, "_layer_grad_hook", None))
+                         layer_grad_hook=getattr(self, "_layer_grad_hook", None),
+                         sequence_parallel=self.sequence_parallel)
         out = self.model(ids, pos, meta)
         aidx = pack["_action_index"]
         hidden = out.hidden_states.index_select(0, aidx)

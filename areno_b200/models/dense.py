@@ -16,6 +16,7 @@ Architecture and lifecycle protocol follow ``areno/models/qwen3/model.py:48-72,2
 
 from __future__ import annotations
 
+import dataclasses
 import os
 import zlib
 from dataclasses import dataclass, field
@@ -48,6 +49,10 @@ class TrainMeta:
     # called with a layer index from backward once that layer's parameter gradients are final (all later
     # layers finished before it); the trainer uses it to start reducing gradient buckets during backward
     layer_grad_hook: Any = None
+    # Megatron-style sequence parallelism over the TP group: activations between the TP seams are sharded by tokens
+    # (norms, residual adds and dropout-free element-wise work run on 1 / tp of the rows; all-reduces become
+    # all-gather + reduce-scatter).  Ignored at tp_size 1.
+    sequence_parallel: bool = False
 
 
 @dataclass
@@ -193,14 +198,22 @@ class DecoderLayer(nn.Module):
             self.mlp.down.defer_reduce = True
 
     def forward(self, x, residual, positions, meta):
-        if residual is None:
-            residual = x
-            h = self.input_norm(x)
-        else:
-            h, residual = self.input_norm(x, residual)
-        h = self.attn(h, positions, meta)
-        h, residual = self.post_norm(h, residual)
-        h = self.mlp(h)
+        sp = isinstance(meta, TrainMeta) and meta.sequence_parallel
+        # the region is opened here, not by the caller, so that a recompute under activation checkpointing sees it too
+        with coll.sequence_parallel_region(sp):
+            sp = coll.in_sequence_parallel()
+            if residual is None:
+                residual = x
+                h = self.input_norm(x)
+            else:
+                h, residual = self.input_norm(x, residual)
+            if sp:
+                h = coll.gather_rows(h)          # [T / tp, H] -> [T, H]; backward reduce-scatters the input gradient
+            h = self.attn(h, positions, meta)    # row-parallel output: reduce-scattered back to [T / tp, H] when sp
+            h, residual = self.post_norm(h, residual)
+            if sp:
+                h = coll.gather_rows(h)
+            h = self.mlp(h)
         return h, residual
 
 
@@ -212,6 +225,8 @@ def _layer_done(hook, li: int):
 
 class DenseCausalLM(nn.Module):
     """Embedding -> N x DecoderLayer -> final norm; ``lm_head`` is applied by the caller."""
+
+    supports_sequence_parallel = True     # subclasses with their own forward loop switch this off
 
     def __init__(self, cfg: ModelConfig, device="cpu", dtype: torch.dtype | None = None):
         super().__init__()
@@ -233,7 +248,24 @@ class DenseCausalLM(nn.Module):
         positions = position_ids.reshape(-1)
         if positions.dtype != torch.int32:
             positions = positions.to(torch.int32)
-        x = self.embed(ids)
+        sp = (isinstance(meta, TrainMeta) and meta.sequence_parallel and self.supports_sequence_parallel
+              and get_context().tp_size > 1)
+        tokens = ids.numel()
+        if isinstance(meta, TrainMeta) and meta.sequence_parallel != sp:
+            meta = dataclasses.replace(meta, sequence_parallel=sp)
+        if sp:
+            # rows are dealt out in equal shares: pad the packed batch with one throw-away sequence
+            pad = (-tokens) % get_context().tp_size
+            if pad:
+                ids = torch.cat([ids, ids.new_zeros(pad)])
+                positions = torch.cat([positions, torch.arange(pad, dtype=positions.dtype, device=positions.device)])
+                host = meta.varlen.cu_q_host
+                lens = [b - a for a, b in zip(host[:-1], host[1:])] + [pad]
+                meta = dataclasses.replace(meta, varlen=attn_ops.build_varlen_meta(lens, device=ids.device))
+            with coll.sequence_parallel_region(True):
+                x = self.embed(ids)            # the vocabulary-parallel sum becomes a reduce-scatter: [T / tp, H]
+        else:
+            x = self.embed(ids)
         residual = None
         use_ckpt = isinstance(meta, TrainMeta) and meta.activation_checkpointing and torch.is_grad_enabled()
         n_ckpt = len(self.layers)
@@ -251,6 +283,9 @@ class DenseCausalLM(nn.Module):
             else:
                 x, residual = layer(x, residual, positions, meta)
         h, _ = self.norm(x, residual)
+        if sp:
+            # every rank needs all rows for the loss; the log-prob op hands back the complete gradient on every rank
+            h = coll.gather_rows_same_grad(h)[:tokens]
         out = CausalLMOutput(hidden_states=h)
         if isinstance(meta, InferMeta):
             rows = h if meta.logit_rows is None else h.index_select(0, meta.logit_rows)

@@ -256,6 +256,8 @@ class Gemma4DecoderLayer(nn.Module):
 
 
 class Gemma4CausalLM(DenseCausalLM):
+    supports_sequence_parallel = False     # own layer loop (KV sharing, per-layer inputs): activations stay replicated
+
     def __init__(self, cfg: ModelConfig, device="cpu", dtype: torch.dtype | None = None):
         cfg = dataclasses.replace(cfg, embed_scale=math.sqrt(cfg.hidden_size))
         super().__init__(cfg, device=device, dtype=dtype)

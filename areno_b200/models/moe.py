@@ -89,7 +89,8 @@ class SparseMoeBlock(nn.Module):
         if self.shared is not None:
             shared = self.shared(x)
             if self.shared_gate is not None:
-                shared = shared * torch.sigmoid(torch.nn.functional.linear(x, self.shared_gate.unsqueeze(0)))
+                # under sequence parallelism `shared` holds this rank's rows only, `x` all of them
+                shared = shared * coll.local_rows(torch.sigmoid(torch.nn.functional.linear(x, self.shared_gate.unsqueeze(0))))
             out = out + shared
         return out
 
