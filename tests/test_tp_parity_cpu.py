@@ -196,7 +196,8 @@ def _plain_rank(rank, world, port, ret, src, kind, dst=None):
         h, loss = _run(model, ids, [25, 15])
         if dst is not None:
             adapter.save_weights(model, dst, cfg)
-        ret[rank] = dict(h=h, loss=loss, grad_norm=_optimizer_grad_norm(model))
+        tokens = _greedy(model, [[5, 9, 77, 130], [200, 3, 8]], 5)      # cached inference with sharded heads / state
+        ret[rank] = dict(h=h, loss=loss, grad_norm=_optimizer_grad_norm(model), tokens=tokens)
         destroy_parallel()
     except BaseException:  # noqa: BLE001
         ret[rank] = traceback.format_exc()
@@ -221,6 +222,7 @@ def test_tp2_gradient_norm_matches_single_process(tmp_path, kind):
     adapter.save_weights(ref, src, cfg)
     ids = torch.randint(3, 512, (40,), generator=torch.Generator().manual_seed(3))
     h_ref, loss_ref = _run(ref, ids, [25, 15])
+    tokens_ref = _greedy(ref, [[5, 9, 77, 130], [200, 3, 8]], 5)
     norm_ref = _optimizer_grad_norm(ref)
     ret = mp.Manager().dict()
     mp.spawn(_plain_rank, args=(2, _free_port(), ret, src, kind, dst), nprocs=2, join=True)
@@ -229,6 +231,7 @@ def test_tp2_gradient_norm_matches_single_process(tmp_path, kind):
         assert isinstance(out, dict), out
         assert torch.allclose(out["h"], h_ref, atol=2e-5, rtol=1e-4)
         assert abs(out["grad_norm"] - norm_ref) < 1e-4 * norm_ref, (out["grad_norm"], norm_ref)
+        assert out["tokens"] == tokens_ref
     a, b = SafetensorsIndex(src), SafetensorsIndex(dst)       # written from the shards == loaded from
     assert sorted(a.keys()) == sorted(b.keys())
     for key in a.keys():
