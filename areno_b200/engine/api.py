@@ -196,8 +196,11 @@ class ArenoEngine:
         packs_by_dp = [split_data_pack_by_dp(p, dp) for p in packs]
         results = self.cluster.call(Op.TRAIN_VALUES, TrainValuesPayload(role, packs_by_dp, gradient_accumulation_steps,
                                                                        cliprange_value, value_loss_coef))
-        merged = [merge_train_stats(dp_rank0_results(list(s), self.config.tp_size, dp)) for s in zip(*results)]
-        return merged[-1] if merged else {}
+        # every rank answers with one flat dict of critic statistics for the whole call: mean over the DP replicas
+        per_dp = [r for r in dp_rank0_results(list(results), self.config.tp_size, dp) if r]
+        if not per_dp:
+            return {}
+        return {k: sum(float(r[k]) for r in per_dp if k in r) / sum(1 for r in per_dp if k in r) for k in per_dp[0]}
 
     # -------------------------------------------------------------------- misc
     def save_checkpoint(self, path: str) -> str:

@@ -2,6 +2,9 @@
 
     python ci/train_smoke.py --algo gspo --steps 2 --device cpu
     python ci/train_smoke.py --algo grpo --steps 3 --device cuda --world-size 2
+    python ci/train_smoke.py --algo ppo --steps 2        # reference and critic roles from the same tiny checkpoint
+    python ci/train_smoke.py --algo dpo --steps 2        # preference pairs, reference role
+    python ci/train_smoke.py --algo sft --steps 2        # prompt / response rows through this file's loader
 
 Everything is made on the spot in a temporary directory, so the job needs no network: a tiny random-weight
 ``qwen2`` checkpoint, a word-level tokenizer saved in the Hugging Face format, a JSONL dataset of additions and this
@@ -75,17 +78,26 @@ def write_checkpoint(path: str, vocab: int, seed: int = 0) -> None:
 
 
 def write_dataset(path: str, n: int, seed: int = 0) -> None:
+    """Rows carry every column any algorithm reads: ``answer`` (RL), ``response`` (SFT), ``chosen`` / ``rejected`` (DPO)."""
     rng = random.Random(seed)
     with open(path, "w") as f:
         for _ in range(n):
             a, b = rng.randrange(100), rng.randrange(100)
-            f.write(json.dumps({"prompt": f"what is {a} plus {b} ?", "answer": str(a + b)}) + "\n")
+            good, bad = f"the answer : {a + b}", f"the answer : {(a + b + 1 + rng.randrange(50)) % 200}"
+            f.write(json.dumps({"prompt": f"what is {a} plus {b} ?", "answer": str(a + b), "response": good,
+                                "chosen": good, "rejected": bad}) + "\n")
+
+
+def load_training_dataset(dataset_path, *, default_loader, load_dataset, load_from_disk):
+    """Loader for ``--dataset-loader-fn ci/train_smoke.py`` (SFT requires one): the JSONL rows as they are."""
+    with open(dataset_path) as f:
+        return [json.loads(line) for line in f if line.strip()]
 
 
 # ------------------------------------------------------------------ run
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.splitlines()[0])
-    ap.add_argument("--algo", default="gspo", choices=["gspo", "grpo"])
+    ap.add_argument("--algo", default="gspo", choices=["gspo", "grpo", "ppo", "dpo", "sft"])
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--device", default="cpu", choices=["cpu", "cuda"])
     ap.add_argument("--world-size", type=int, default=1)
@@ -103,11 +115,21 @@ def main(argv=None) -> int:
         os.makedirs(ckpt, exist_ok=True)
         write_checkpoint(ckpt, write_tokenizer(ckpt))
         write_dataset(data, 64)
-        config = cli_train.trainer_config_from_options(
-            algo=args.algo, ckpt=ckpt, dataset_path=data, reward_fn_path=os.path.abspath(__file__), save_path=save,
+        options = dict(
+            algo=args.algo, ckpt=ckpt, dataset_path=data, save_path=save,
             save_interval=args.steps, metrics_log_dir=logs, epochs=1, max_steps=args.steps, tp_size=1,
             world_size=args.world_size, batch_size=4, n_samples=4, mini_bs=8, max_prompt_tokens=32, max_new_tokens=8,
             lr=1e-4, activation_checkpointing=False)
+        me = os.path.abspath(__file__)
+        if args.algo in ("gspo", "grpo", "ppo"):
+            options["reward_fn_path"] = me
+        if args.algo == "ppo":
+            options.update(ref_ckpt=ckpt, critic_ckpt=ckpt, critic_warmup_steps=0)
+        if args.algo == "dpo":
+            options.update(ref_ckpt=ckpt, dataset_loader_fn=me)
+        if args.algo == "sft":
+            options.update(dataset_loader_fn=me)
+        config = cli_train.trainer_config_from_options(**options)
         trainer = cli_train.run(config)
         steps_done = int(getattr(trainer, "global_step", getattr(trainer, "step", args.steps)))
         saved = [d for d in (os.listdir(save) if os.path.isdir(save) else [])]
