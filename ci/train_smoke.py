@@ -5,6 +5,7 @@
     python ci/train_smoke.py --algo ppo --steps 2        # reference and critic roles from the same tiny checkpoint
     python ci/train_smoke.py --algo dpo --steps 2        # preference pairs, reference role
     python ci/train_smoke.py --algo sft --steps 2        # prompt / response rows through this file's loader
+    python ci/train_smoke.py --algo grpo --steps 2 --agentic   # agent function + local OpenAI-compatible proxy
 
 Everything is made on the spot in a temporary directory, so the job needs no network: a tiny random-weight
 ``qwen2`` checkpoint, a word-level tokenizer saved in the Hugging Face format, a JSONL dataset of additions and this
@@ -101,6 +102,9 @@ def main(argv=None) -> int:
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--device", default="cpu", choices=["cpu", "cuda"])
     ap.add_argument("--world-size", type=int, default=1)
+    ap.add_argument("--agentic", action="store_true",
+                    help="rollouts through an agent function and the local OpenAI-compatible proxy (the one-step "
+                         "tic-tac-toe example) instead of plain prompt -> completion")
     ap.add_argument("--keep", default=None, help="directory to keep the artefacts in (default: a temporary one)")
     args = ap.parse_args(argv)
     if args.device == "cpu":
@@ -129,6 +133,14 @@ def main(argv=None) -> int:
             options.update(ref_ckpt=ckpt, dataset_loader_fn=me)
         if args.algo == "sft":
             options.update(dataset_loader_fn=me)
+        if args.agentic:
+            if args.algo not in ("gspo", "grpo"):
+                ap.error("--agentic goes with --algo gspo or grpo")
+            ex = os.path.join(ROOT, "examples", "agentic", "tictactoe")
+            options.update(dataset_path="tictactoe:16", dataset_loader_fn=os.path.join(ex, "dataset_loader_no_tool.py"),
+                           agent_fn=os.path.join(ex, "run_agent_no_tool.py"),
+                           reward_fn_path=os.path.join(ex, "reward_no_tool.py"), max_prompt_tokens=128,
+                           agent_timeout_s=120)
         config = cli_train.trainer_config_from_options(**options)
         trainer = cli_train.run(config)
         steps_done = int(getattr(trainer, "global_step", getattr(trainer, "step", args.steps)))

@@ -264,17 +264,18 @@ def test_main_group_and_diagnostics():
     assert rows["GPUs are sm_100 (B200 class)"].status == "FAIL"
 
 
-@pytest.mark.parametrize("algo", ["grpo", "ppo", "dpo", "sft"])
+@pytest.mark.parametrize("algo", ["grpo", "ppo", "dpo", "sft", "grpo --agentic"])
 def test_train_smoke_script_runs_the_cli_path_end_to_end(algo):
     """``ci/train_smoke.py`` drives option validation -> dataset -> trainer factory -> fit -> save on CPU, for the
-    rollout algorithms, PPO with its reference and critic roles, and the two offline algorithms."""
+    rollout algorithms, PPO with its reference and critic roles, the two offline algorithms, and an agent function
+    behind the local proxy."""
     import json
     import subprocess
     import sys
     from pathlib import Path
 
     root = Path(__file__).resolve().parents[1]
-    proc = subprocess.run([sys.executable, str(root / "ci" / "train_smoke.py"), "--algo", algo, "--steps", "2", "--device", "cpu"],
+    proc = subprocess.run([sys.executable, str(root / "ci" / "train_smoke.py"), "--algo", *algo.split(), "--steps", "2", "--device", "cpu"],
                           capture_output=True, text=True, timeout=600, cwd=str(root))
     assert proc.returncode == 0, proc.stderr[-2000:]
     out = json.loads(proc.stdout.strip().splitlines()[-1])
