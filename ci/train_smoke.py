@@ -102,6 +102,7 @@ def main(argv=None) -> int:
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--device", default="cpu", choices=["cpu", "cuda"])
     ap.add_argument("--world-size", type=int, default=1)
+    ap.add_argument("--tp-size", type=int, default=1)
     ap.add_argument("--agentic", action="store_true",
                     help="rollouts through an agent function and the local OpenAI-compatible proxy (the one-step "
                          "tic-tac-toe example) instead of plain prompt -> completion")
@@ -121,7 +122,7 @@ def main(argv=None) -> int:
         write_dataset(data, 64)
         options = dict(
             algo=args.algo, ckpt=ckpt, dataset_path=data, save_path=save,
-            save_interval=args.steps, metrics_log_dir=logs, epochs=1, max_steps=args.steps, tp_size=1,
+            save_interval=args.steps, metrics_log_dir=logs, epochs=1, max_steps=args.steps, tp_size=args.tp_size,
             world_size=args.world_size, batch_size=4, n_samples=4, mini_bs=8, max_prompt_tokens=32, max_new_tokens=8,
             lr=1e-4, activation_checkpointing=False)
         me = os.path.abspath(__file__)

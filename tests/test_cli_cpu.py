@@ -264,11 +264,11 @@ def test_main_group_and_diagnostics():
     assert rows["GPUs are sm_100 (B200 class)"].status == "FAIL"
 
 
-@pytest.mark.parametrize("algo", ["grpo", "ppo", "dpo", "sft", "grpo --agentic"])
+@pytest.mark.parametrize("algo", ["grpo", "ppo", "dpo", "sft", "grpo --agentic", "ppo --world-size 2 --tp-size 2"])
 def test_train_smoke_script_runs_the_cli_path_end_to_end(algo):
     """``ci/train_smoke.py`` drives option validation -> dataset -> trainer factory -> fit -> save on CPU, for the
     rollout algorithms, PPO with its reference and critic roles, the two offline algorithms, and an agent function
-    behind the local proxy."""
+    behind the local proxy; the last case runs PPO tensor parallel over two spawned gloo ranks."""
     import json
     import subprocess
     import sys
