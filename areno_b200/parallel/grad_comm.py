@@ -74,7 +74,10 @@ class GradComm:
         self.epoch = 0
         self.launched: set[int] = set()
         self.blocks = int(os.environ.get("ARENO_GRAD_RS_BLOCKS", "64"))
-        self.wait_ms = int(os.environ.get("ARENO_GRAD_RS_WAIT_MS", "5000"))
+        # how long a reducer waits for a peer's gradients; ranks only meet here once per step, so the bound has to
+        # cover the skew that a whole rollout + backward can build up between them (power capping alone gives
+        # several per cent), while still ending a wait for a rank that is gone
+        self.wait_ms = int(os.environ.get("ARENO_GRAD_RS_WAIT_MS", "20000"))
         torch.cuda.synchronize(device)
         dist.barrier(group=group)
 
