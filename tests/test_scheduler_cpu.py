@@ -70,3 +70,35 @@ def test_pack_indices_maps_padded_rows_to_packed_tokens():
     # actions: every packed position whose successor belongs to the same row
     assert aidx.tolist() == [0, 1, 4, 6, 7, 8]
     assert arows.tolist() == [0, 0, 2, 3, 3, 3]
+
+
+def test_longest_sequence_waiting_queue_and_slot_reuse():
+    s = Scheduler(max_slots=3, num_pages=32, page_size=64, max_pages_per_seq=8, max_prefill_tokens=512)
+    assert s.max_seq_len == 0 and s.active_extent == 0
+    for rid, n in ((1, 20), (2, 200), (3, 70), (4, 10), (5, 10)):
+        s.add(rid, n, 32)
+    plan = s.plan_prefill()
+    assert [(p[0], p[1]) for p in plan] == [(0, 1), (1, 2), (2, 3)] and s.num_waiting == 2
+    assert s.max_seq_len == 200                              # the decode graph's context bucket follows the longest row
+    s.reserve_decode(1)
+    s.advance(1)
+    assert s.max_seq_len == 201 and s.slot_seq_len(0) == 21
+    s.finish(1)                                              # the longest leaves: the bound drops to the next one
+    assert s.max_seq_len == 71 and s.active_extent == 3      # slot 2 is still the highest active slot
+    plan = s.plan_prefill()
+    assert plan == [(1, 4, 0, 10, True)]                     # the freed slot is reused by the next waiting request
+    assert s.clear_waiting() == 1 and s.num_waiting == 0     # request 5 never started
+    for slot in (0, 1, 2):
+        s.finish(slot)
+    assert s.num_running == 0 and s.num_free_pages == 32 and s.max_seq_len == 0
+
+
+def test_multi_step_reservation_allocates_all_pages_up_front():
+    s = Scheduler(max_slots=1, num_pages=8, page_size=64, max_pages_per_seq=8, max_prefill_tokens=512)
+    s.add(7, 60, 300)
+    s.plan_prefill()
+    updates = s.reserve_decode(100)                          # 60 -> 160 tokens: pages 2 and 3 at once
+    assert [(u[0], u[1]) for u in updates] == [(0, 1), (0, 2)]
+    s.advance(100)
+    assert s.slot_seq_len(0) == 160 and len(s.slot_pages(0)) == 3
+    assert s.reserve_decode(1) == []                         # still inside the third page
