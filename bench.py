@@ -242,6 +242,9 @@ def run_ours(args):
     klib.launch_count = 0
     for k in phase:
         phase[k] = 0.0
+    from areno_b200.utils import tracing
+
+    tracing.phase_report()      # ARENO_PHASE_TIMERS=1: drop what the warm-up steps recorded
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_wall = time.time()
     start.record()
@@ -265,6 +268,8 @@ def run_ours(args):
         ms, wall, total_tokens = float(mx[0]), float(mx[2]), float(sm[1])
     value = total_tokens / (ms / 1e3)
     klib.check_status()
+    # device-side time of every named phase (CUDA events, max over ranks); only with ARENO_PHASE_TIMERS=1
+    phases = tracing.phase_report_max() if tracing.enabled() else None
 
     e2e = None
     if not args.no_e2e:
@@ -278,6 +283,8 @@ def run_ours(args):
             "dtype": "bf16", "data": "synthetic (uniform random token ids, random-init weights, seeded-hash reward)",
             "impl": "ours", "clocks": clocks, "gpu_launches": launches, "e2e": e2e, "last_loss": loss,
             "phase_s_per_step": {k: v / args.steps for k, v in phase.items()},
+            **({"device_phase_ms_per_step": {k: round(v["ms"] / args.steps, 3) for k, v in sorted(phases.items())}}
+               if phases else {}),
             "config": {
                 "model": "Qwen2.5-7B-shaped" if not args.small else "small-debug", "global_batch": n_prompts * GROUP * world,
                 "prompts_per_gpu": n_prompts, "group": GROUP, "prompt_len": [pmin, pmax], "new_tokens": new_tokens,
