@@ -268,6 +268,12 @@ class Trainer:
             result["step_train_time_s"] = self._metric_timings["train"]
             if self._step_wall_start is not None:
                 result["step_e2e_time_s"] = time.perf_counter() - self._step_wall_start
+            from ..utils import tracing
+
+            if tracing.enabled():
+                # ARENO_PHASE_TIMERS=1 with an in-process backend: device time of every named phase of this step
+                for name, rec in tracing.phase_report().items():
+                    result[f"device_ms/{name}"] = rec["ms"]
         if self._metrics is not None:
             self._metrics.record_train_step(step=ctx.global_step, train_result=result, train_batch=batch_data,
                                             timings=self._metric_timings)

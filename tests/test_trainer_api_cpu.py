@@ -173,3 +173,19 @@ def test_metrics_are_recorded_per_train_call(tmp_path, monkeypatch):
     tags = {r["tag"] for r in rows}
     assert {"rollout/rewards_mean", "rollout/num_sequences", "train/loss", "time/train", "time/rollout"} <= tags
     assert all(r["step"] == 0 for r in rows)
+
+
+def test_phase_timers_show_up_in_the_train_result():
+    from areno_b200.utils import tracing
+
+    t = _trainer()
+    tracing.configure(timers=True)
+    try:
+        tracing.phase_report()
+        with tracing.trace_range("train/forward"):
+            pass
+        out = t.train([_seq()], lambda pack, lp: lp.sum())
+    finally:
+        tracing.configure(nvtx=False, timers=False)
+    assert "device_ms/train/forward" in out
+    assert not any(k.startswith("device_ms/") for k in t.train([_seq()], lambda pack, lp: lp.sum()))
