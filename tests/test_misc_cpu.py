@@ -390,3 +390,15 @@ def test_metrics_fall_back_to_jsonl_without_tensorboard(tmp_path, monkeypatch):
     writer.close()
     rows = [json.loads(line) for line in open(tmp_path / "metrics.jsonl")]
     assert rows[0]["tag"] == "train/loss" and rows[0]["value"] == 0.5 and rows[0]["step"] == 3
+
+
+def test_importing_the_sdk_and_cli_entry_points_stays_light():
+    """``import areno_b200.api`` / the CLI group must not pull in torch, transformers, the engine or the kernels:
+    ``areno --help``, ``areno env`` and option validation have to work (and be fast) on a machine without a GPU stack."""
+    import subprocess
+
+    code = ("import sys; import areno_b200.api; import areno_b200.cli.main; "
+            "print([m for m in ('torch', 'transformers', 'fastapi', 'datasets', 'areno_b200.engine', 'areno_b200.ops', "
+            "'areno_b200.models') if m in sys.modules])")
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd=str(ROOT), timeout=120)
+    assert out.returncode == 0 and out.stdout.strip() == "[]", out.stdout + out.stderr
