@@ -396,6 +396,7 @@ def test_importing_the_sdk_and_cli_entry_points_stays_light():
     """``import areno_b200.api`` / the CLI group must not pull in torch, transformers, the engine or the kernels:
     ``areno --help``, ``areno env`` and option validation have to work (and be fast) on a machine without a GPU stack."""
     import subprocess
+    import sys
 
     code = ("import sys; import areno_b200.api; import areno_b200.cli.main; "
             "print([m for m in ('torch', 'transformers', 'fastapi', 'datasets', 'areno_b200.engine', 'areno_b200.ops', "
