@@ -248,3 +248,23 @@ def test_data_utils_build_prompt_response_rows():
     assert mask[:n_prompt] == [True] * n_prompt and not any(mask[n_prompt:])       # True marks prompt positions
     assert has_any({"question": "q"}, ("prompt", "question")) and not has_any({"x": 1}, ("prompt",))
     assert first_text({"question": " q "}, ("prompt", "question")).strip() == "q"
+
+
+# ----------------------------------------------------------------------------------------- rewards
+def test_reward_functions_are_loaded_from_files_and_records_carry_the_row(tmp_path):
+    from areno_b200.api.rewards import compute_group_advantages, load_reward_fn, make_reward_record
+
+    good = tmp_path / "r.py"
+    good.write_text("def reward_fn(record):\n    return float(record.completion.strip() == str(record.answer))\n")
+    fn = load_reward_fn(str(good))
+    rec = make_reward_record(prompt="2+2", completion=" 4 ", source_record={"answer": 4, "extra": "kept"}, answer=4,
+                             tokens=[7], logprobs=[-0.25], loss_mask=[True], metadata={"turns": 1})
+    assert fn(rec) == 1.0 and rec.final_answer == " 4 " and rec.source_record["extra"] == "kept"
+    assert rec.tokens == [7] and rec.logprobs == [-0.25] and rec.metadata == {"turns": 1} and rec.tool_calls == []
+    bad = tmp_path / "bad.py"
+    bad.write_text("reward_fn = 3\n")
+    with pytest.raises(ValueError, match="reward_fn"):
+        load_reward_fn(str(bad))
+    adv = compute_group_advantages([1.0, 0.0, 0.0, 1.0])
+    assert adv == pytest.approx([1.0, -1.0, -1.0, 1.0], abs=1e-4) and sum(adv) == pytest.approx(0.0, abs=1e-6)
+    assert compute_group_advantages([0.5, 0.5, 0.5]) == pytest.approx([0.0, 0.0, 0.0])      # no signal: no gradient
