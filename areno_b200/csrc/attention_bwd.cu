@@ -360,7 +360,8 @@ static int launch_bwd(const void* q, const void* k, const void* v, const void* o
   constexpr int smem_q = 6 * 64 * D * 2;
   constexpr int DO = D > 128 ? 128 : D;
   constexpr int NZ = D / DO;
-  static bool cfg = false;
+  static bool cfg_dev[kMaxDevices] = {};
+    bool& cfg = per_device_flag(cfg_dev);
   if (!cfg) {
     cudaFuncSetAttribute(attn_bwd_dkv_kernel<D, DO>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_kv);
     cudaFuncSetAttribute(attn_bwd_dq_kernel<D, DO>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_q);

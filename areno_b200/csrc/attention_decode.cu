@@ -463,7 +463,8 @@ static int launch_decode(const void* q, const void* k_cache, const void* v_cache
                          long long o_stride, float scale, int pages_per_split, int nsplit, int window,
                          cudaStream_t stream) {
   using SM = DecodeSmem<D, FP8>;
-  static bool cfg = false;
+  static bool cfg_dev[kMaxDevices] = {};
+    bool& cfg = per_device_flag(cfg_dev);
   if (!cfg) {
     cudaFuncSetAttribute(paged_decode_kernel<D, FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kTotal);
     cfg = true;

@@ -205,21 +205,24 @@ extern "C" int areno_attn_fwd(const void* q, const void* k, const void* v, void*
   dim3 grid(total_tiles, hq);
   if (head_dim == 128) {
     constexpr int smem = 5 * 64 * 128 * 2;
-    static bool cfg = false;
+    static bool cfg_dev[kMaxDevices] = {};
+    bool& cfg = per_device_flag(cfg_dev);
     if (!cfg) { cudaFuncSetAttribute(attn_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); cfg = true; }
     attn_fwd_kernel<128><<<grid, 128, smem, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k,
         (const __nv_bfloat16*)v, (__nv_bfloat16*)o, lse, cu_q, cu_k, tile_prefix, num_seqs, hq, hkv, q_stride,
         k_stride, v_stride, o_stride, scale, causal, window);
   } else if (head_dim == 64) {
     constexpr int smem = 5 * 64 * 64 * 2;
-    static bool cfg = false;
+    static bool cfg_dev[kMaxDevices] = {};
+    bool& cfg = per_device_flag(cfg_dev);
     if (!cfg) { cudaFuncSetAttribute(attn_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); cfg = true; }
     attn_fwd_kernel<64><<<grid, 128, smem, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k,
         (const __nv_bfloat16*)v, (__nv_bfloat16*)o, lse, cu_q, cu_k, tile_prefix, num_seqs, hq, hkv, q_stride,
         k_stride, v_stride, o_stride, scale, causal, window);
   } else if (head_dim == 256) {
     constexpr int smem = 5 * 64 * 256 * 2;
-    static bool cfg = false;
+    static bool cfg_dev[kMaxDevices] = {};
+    bool& cfg = per_device_flag(cfg_dev);
     if (!cfg) { cudaFuncSetAttribute(attn_fwd_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); cfg = true; }
     attn_fwd_kernel<256><<<grid, 128, smem, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k,
         (const __nv_bfloat16*)v, (__nv_bfloat16*)o, lse, cu_q, cu_k, tile_prefix, num_seqs, hq, hkv, q_stride,

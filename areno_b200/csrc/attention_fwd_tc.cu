@@ -399,7 +399,8 @@ extern "C" int areno_attn_fwd_tc(const void* q, const void* k, const void* v, vo
   p.causal = causal;
   p.status = status;
   const int smem = 5 * 128 * kTcD * 2 + (int)kTcPTile + 256 + 1024;
-  static bool cfg = false;
+  static bool cfg_dev[kMaxDevices] = {};
+    bool& cfg = per_device_flag(cfg_dev);
   if (!cfg) {
     cudaError_t e = cudaFuncSetAttribute(attn_fwd_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          5 * 128 * 128 * 2 + (int)kTcPTile + 256 + 1024);

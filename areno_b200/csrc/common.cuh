@@ -79,6 +79,18 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// Host-side once-per-device bookkeeping: kernel attributes (cudaFuncSetAttribute) and device
+// properties belong to one device, so a process that drives several GPUs must set / query them on
+// each.  `flags` is a function-local static array; the returned reference is the slot of the device
+// that is current on the calling thread.
+constexpr int kMaxDevices = 64;
+inline int current_device_slot() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return (dev >= 0 && dev < kMaxDevices) ? dev : 0;
+}
+inline bool& per_device_flag(bool (&flags)[kMaxDevices]) { return flags[current_device_slot()]; }
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

@@ -748,8 +748,7 @@ static __device__ __align__(256) float
     g_rmsnorm_bwd_scratch[(size_t)ARENO_RMSNORM_BWD_STATIC_BLOCKS * ARENO_RMSNORM_BWD_STATIC_MAX_H];
 
 namespace {
-constexpr int kMaxDevices = 64;
-float* g_scratch_addr[kMaxDevices] = {};  // filled lazily, one slot per device ordinal
+float* g_scratch_addr[areno::kMaxDevices] = {};  // filled lazily, one slot per device ordinal
 std::mutex g_scratch_mutex;
 
 // Returns 0 and the device address of the scratch on the current device, or an error code.
@@ -757,7 +756,7 @@ int static_scratch_for_current_device(float** out) {
   int dev = -1;
   cudaError_t rc = cudaGetDevice(&dev);
   if (rc != cudaSuccess) return (int)rc;
-  if (dev < 0 || dev >= kMaxDevices) return ARENO_NOALLOC_ERR_DEVICE;
+  if (dev < 0 || dev >= areno::kMaxDevices) return ARENO_NOALLOC_ERR_DEVICE;
   std::lock_guard<std::mutex> guard(g_scratch_mutex);
   if (g_scratch_addr[dev] == nullptr) {
     float* p = nullptr;
@@ -775,7 +774,7 @@ extern "C" const char* areno_no_alloc_strerror(int code) {
   switch (code) {
     case 0: return "ok";
     case -2: return "hidden size not supported by the RMSNorm kernels";
-    case -3: return "hidden size must be a multiple of 8";
+    case -3: return "hidden size must be a multiple of 8 and dy, h, inv_rms, dx must not be null";
     case ARENO_NOALLOC_ERR_H_TOO_LARGE:
       return "hidden size exceeds ARENO_RMSNORM_BWD_STATIC_MAX_H (8192): the fixed scratch cannot hold it; "
              "use areno_rmsnorm_bwd with caller-provided scratch";
@@ -794,6 +793,7 @@ extern "C" int areno_rmsnorm_bwd_static(const void* dy, const void* h, const voi
   const int rc = static_scratch_for_current_device(&scratch);  // set-up on the first call per device
   if (rc != 0) return rc;
   if (rows <= 0) return 0;
+  if (dy == nullptr || h == nullptr || inv_rms == nullptr || dx == nullptr) return -3;  // w, dres_in, dw may be null
   const int grid = (int)(rows < ARENO_RMSNORM_BWD_STATIC_BLOCKS ? rows : ARENO_RMSNORM_BWD_STATIC_BLOCKS);
   // Each of the `grid` blocks writes its whole H-wide row of the scratch (zeros included), and the
   // fold reads exactly those rows, so leftovers of earlier calls are never read.

@@ -472,7 +472,8 @@ int make_tensor_map_2d_bf16(CUtensorMap* out, const void* ptr, uint64_t inner, u
 }
 
 static int num_sms() {
-  static int n = 0;
+  static int n_dev[kMaxDevices] = {};
+  int& n = n_dev[current_device_slot()];
   if (n == 0) {
     int dev = 0;
     cudaGetDevice(&dev);
@@ -485,7 +486,8 @@ template <int BN, int STAGES, bool A_MN, bool B_MN>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream) {
   using S = GemmSmem<BN, STAGES>;
   auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN>;
-  static bool configured = false;
+  static bool configured_dev[kMaxDevices] = {};
+  bool& configured = per_device_flag(configured_dev);
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
     if (e != cudaSuccess) return static_cast<int>(e);

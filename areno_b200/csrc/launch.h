@@ -1,7 +1,10 @@
 // C ABI of the sm_100a kernel library (libareno_kernels.so).  Every entry point takes raw
 // device pointers and a CUDA stream, launches asynchronously and returns 0 or an error code
-// (negative: argument / configuration error, positive: CUDA error).  No entry point
-// allocates device memory; scratch is passed in by the caller.
+// (negative: argument / configuration error, positive: CUDA error).  The compute entry points
+// allocate no device memory: scratch is passed in by the caller, except for the one variant in
+// no_alloc.h that keeps its scratch in a fixed device array of the library.  The only allocating
+// calls are the symmetric-memory set-up routines of comm.cu (areno_symm_* / areno_vmm_*), which
+// run once at start-up.
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>

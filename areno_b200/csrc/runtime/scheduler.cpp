@@ -5,7 +5,8 @@
 // FIFO of waiting requests.  It never looks at device memory: sequence lengths advance
 // deterministically by one token per decode step, so page demand is known on the host; the
 // engine tells it when a slot finished.  Admission respects the slot limit, the page budget
-// (prompt pages up front, decode pages on demand) and a per-step prefill token budget; prompts
+// (all pages of the prompt are reserved at admission, also when the prompt is prefilled in several
+// chunks; decode pages on demand) and a per-step prefill token budget; prompts
 // longer than the budget are prefilled in chunks.
 //
 // Behaviourally this is the role of InferenceBatchState in the reference
@@ -31,6 +32,7 @@ struct Slot {
   int prefilled = 0;    // prompt tokens already run through the model
   int seq_len = 0;      // tokens with KV in the cache (after the current step is planned)
   int max_len = 0;      // prompt_len + max_new
+  long long admit_order = 0;  // position in the admission sequence (larger = admitted later)
   std::vector<int> pages;
 };
 
@@ -126,7 +128,9 @@ int areno_sched_plan_prefill(void* h, int max_out, int* out_slot, long long* out
       if (!s->slots[i].used) { free_slot = i; break; }
     if (free_slot < 0) break;
     const Request r = s->waiting.front();
-    // admit only if the whole prompt (plus one decode token) fits in free pages right now
+    // Admit only if the whole prompt (plus one decode token) fits in free pages right now, and take
+    // those pages immediately: a prompt that is prefilled over several steps keeps its claim, so a
+    // later admission or a growing decoder cannot leave it stranded half-way.
     if (s->pages_for(r.prompt_len + 1) > static_cast<int>(s->free_pages.size())) break;
     Slot& sl = s->slots[free_slot];
     sl.used = true;
@@ -136,7 +140,8 @@ int areno_sched_plan_prefill(void* h, int max_out, int* out_slot, long long* out
     sl.prefilled = 0;
     sl.seq_len = 0;
     sl.max_len = r.prompt_len + r.max_new;
-    if (!emit(free_slot)) {
+    sl.admit_order = s->admitted_total;
+    if (!s->grow(sl, r.prompt_len + 1) || !emit(free_slot)) {
       s->release(sl);
       break;
     }
@@ -149,18 +154,34 @@ int areno_sched_plan_prefill(void* h, int max_out, int* out_slot, long long* out
 
 // Reserve KV room for `steps` more decoded tokens on every slot that is decoding (not mid-prompt).
 // New (slot, page index, page id) triples are written to the update arrays.  Returns the number of
-// updates, or -(slot+1) of the first slot that could not grow (caller must finish or preempt).
+// updates.  The call either serves every slot or changes nothing: when the free pages do not cover
+// the demand it returns -(slot+1) of the first slot (in index order) whose share would not fit, and
+// when the update arrays are too short it returns -(max_slots+1); in both cases no page has moved, so
+// the caller can make room (preempt a sequence) and call again without losing an update.
 int areno_sched_reserve_decode(void* h, int steps, int max_upd, int* upd_slot, int* upd_index, int* upd_page) {
   auto* s = static_cast<Scheduler*>(h);
+  long long need_total = 0;
+  const long long have = static_cast<long long>(s->free_pages.size());
+  for (int i = 0; i < s->max_slots; ++i) {
+    const Slot& sl = s->slots[i];
+    if (!sl.used || sl.prefilling) continue;
+    const int target = std::min(sl.seq_len + steps, sl.max_len);
+    const int need = s->pages_for(target);
+    if (need > s->max_pages_per_seq) return -(i + 1);
+    const int extra = need - static_cast<int>(sl.pages.size());
+    if (extra <= 0) continue;
+    need_total += extra;
+    if (need_total > have) return -(i + 1);
+  }
+  if (need_total > max_upd) return -(s->max_slots + 1);
   int n = 0;
   for (int i = 0; i < s->max_slots; ++i) {
     Slot& sl = s->slots[i];
     if (!sl.used || sl.prefilling) continue;
     const int target = std::min(sl.seq_len + steps, sl.max_len);
     const size_t before = sl.pages.size();
-    if (!s->grow(sl, target)) return -(i + 1);
+    s->grow(sl, target);  // cannot fail: the demand was checked above
     for (size_t k = before; k < sl.pages.size(); ++k) {
-      if (n >= max_upd) return n;
       upd_slot[n] = i;
       upd_index[n] = static_cast<int>(k);
       upd_page[n] = sl.pages[k];
@@ -168,6 +189,33 @@ int areno_sched_reserve_decode(void* h, int steps, int max_upd, int* upd_slot, i
     }
   }
   return n;
+}
+
+// The decoding slot that was admitted last (the cheapest one to send back to the queue), or -1 when
+// fewer than two sequences are decoding (evicting the only one would make no room for anybody).
+int areno_sched_preempt_victim(void* h) {
+  auto* s = static_cast<Scheduler*>(h);
+  int victim = -1, decoding = 0;
+  for (int i = 0; i < s->max_slots; ++i) {
+    const Slot& sl = s->slots[i];
+    if (!sl.used || sl.prefilling) continue;
+    ++decoding;
+    if (victim < 0 || sl.admit_order > s->slots[victim].admit_order) victim = i;
+  }
+  return decoding >= 2 ? victim : -1;
+}
+
+// Send the sequence in `slot` back to the head of the waiting queue: its pages are freed and it will
+// be admitted again as a request with `prompt_len` prompt tokens (the original prompt plus whatever
+// it had generated) and `max_new` tokens still to produce.
+int areno_sched_requeue(void* h, int slot, int prompt_len, int max_new) {
+  auto* s = static_cast<Scheduler*>(h);
+  if (slot < 0 || slot >= s->max_slots || !s->slots[slot].used || prompt_len <= 0) return -1;
+  const long long id = s->slots[slot].req_id;
+  s->release(s->slots[slot]);
+  --s->running;
+  s->waiting.push_front(Request{id, prompt_len, std::max(max_new, 0)});
+  return 0;
 }
 
 // Account for `steps` decode steps having been launched (every decoding slot grew by that much,

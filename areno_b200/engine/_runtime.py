@@ -37,6 +37,8 @@ def lib():
             l.areno_sched_advance.argtypes = [_P, _I]
             l.areno_sched_advance.restype = None
             l.areno_sched_finish.argtypes = [_P, _I]
+            l.areno_sched_preempt_victim.argtypes = [_P]
+            l.areno_sched_requeue.argtypes = [_P, _I, _I, _I]
             l.areno_sched_slot_pages.argtypes = [_P, _I, _P, _I]
             l.areno_sched_slot_seq_len.argtypes = [_P, _I]
             l.areno_sched_slot_request.argtypes = [_P, _I]
@@ -101,9 +103,12 @@ class Scheduler:
                 for i in range(n)]
 
     def reserve_decode(self, steps: int):
-        """-> list of (slot, page_index, page_id) newly allocated; raises MemoryError with the slot."""
+        """-> list of (slot, page_index, page_id) newly allocated.  All or nothing: when the free pages do not
+        cover every decoding slot's demand it raises ``MemoryError(slot)`` and no page has moved."""
         n = self._l.areno_sched_reserve_decode(self._h, steps, len(self._us), _np_ptr(self._us), _np_ptr(self._ui),
                                                _np_ptr(self._up))
+        if n == -(self.max_slots + 1):
+            raise RuntimeError("scheduler: page-update buffer too small for one decode step")
         if n < 0:
             raise MemoryError(-n - 1)
         return [(int(self._us[i]), int(self._ui[i]), int(self._up[i])) for i in range(n)]
@@ -113,6 +118,15 @@ class Scheduler:
 
     def finish(self, slot: int) -> None:
         self._l.areno_sched_finish(self._h, slot)
+
+    def preempt_victim(self) -> int:
+        """The decoding slot admitted last, or -1 when fewer than two sequences decode."""
+        return int(self._l.areno_sched_preempt_victim(self._h))
+
+    def requeue(self, slot: int, prompt_len: int, max_new: int) -> None:
+        """Free the slot's pages and put its request back at the head of the waiting queue."""
+        if self._l.areno_sched_requeue(self._h, slot, prompt_len, max_new) != 0:
+            raise ValueError(f"slot {slot} cannot be re-queued")
 
     def slot_pages(self, slot: int) -> list[int]:
         n = self._l.areno_sched_slot_pages(self._h, slot, _np_ptr(self._pages), len(self._pages))

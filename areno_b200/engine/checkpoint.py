@@ -110,6 +110,8 @@ def _resolve(module, attr: str):
 
 
 def _shard_bounds(total: int, tp: int, rank: int) -> tuple[int, int]:
+    if total % tp != 0:
+        raise ValueError(f"a dimension of {total} cannot be split evenly over tp={tp}")
     per = total // tp
     return rank * per, (rank + 1) * per
 
@@ -308,7 +310,8 @@ def save_with_rules(model, path: str, config, top_rules: list[Rule], layer_rules
         if expert_export is not None:
             tensors.update(expert_export(layers[i], i))
     tp = ctx.tp_size
-    fname = f"model-{ctx.tp_rank + 1:05d}-of-{tp:05d}.safetensors"
+    # single-writer checkpoints use the plain Hugging Face file name (as ``areno/engine/checkpoints/io.py:610``)
+    fname = "model.safetensors" if tp == 1 else f"model-{ctx.tp_rank + 1:05d}-of-{tp:05d}.safetensors"
     save_file(tensors, os.path.join(path, fname), metadata={"format": "pt"})
     local = {k: fname for k in tensors}
     size = sum(t.numel() * t.element_size() for t in tensors.values())
@@ -324,7 +327,7 @@ def save_with_rules(model, path: str, config, top_rules: list[Rule], layer_rules
             weight_map.update(m)
             total += s
         if source_path and os.path.isdir(source_path):
-            _passthrough_untouched(source_path, path, weight_map)
+            total += _passthrough_untouched(source_path, path, weight_map)
         with open(os.path.join(path, "model.safetensors.index.json"), "w") as f:
             json.dump({"metadata": {"total_size": total, "areno_checkpoint_writer": "distributed_tp"},
                        "weight_map": dict(sorted(weight_map.items()))}, f, indent=2)
@@ -333,22 +336,23 @@ def save_with_rules(model, path: str, config, top_rules: list[Rule], layer_rules
         dist.barrier()
 
 
-def _passthrough_untouched(source_path: str, out_path: str, weight_map: dict[str, str]) -> None:
+def _passthrough_untouched(source_path: str, out_path: str, weight_map: dict[str, str]) -> int:
     """Tensors of the source checkpoint that the text model does not own (e.g. a vision tower) are
-    copied through unchanged into an extra shard."""
+    copied through unchanged into an extra shard.  Returns their size in bytes (counted in ``total_size``)."""
     from safetensors.torch import save_file
 
     try:
         src = SafetensorsIndex(source_path)
     except (FileNotFoundError, OSError):
-        return
+        return 0
     extra = {k: src.get(k) for k in src.keys() if k not in weight_map}
     if not extra:
-        return
+        return 0
     fname = "model-passthrough.safetensors"
     save_file(extra, os.path.join(out_path, fname), metadata={"format": "pt"})
     for k in extra:
         weight_map[k] = fname
+    return sum(t.numel() * t.element_size() for t in extra.values())
 
 
 def copy_assets(source_path: str | None, out_path: str, config=None) -> None:

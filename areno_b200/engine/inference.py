@@ -88,6 +88,14 @@ class _Request:
     reason: str = ""
     tag: object = None
     stream: int = -1  # random-stream id keyed into the sampler; defaults to rid
+    # tokens generated before the sequence was sent back to the queue for lack of KV pages; on re-admission they
+    # are prefilled together with the prompt and the final result is the concatenation
+    kept_tokens: list[int] = field(default_factory=list)
+    kept_logprobs: list[float] = field(default_factory=list)
+
+    @property
+    def context(self) -> list[int]:
+        return self.prompt + self.kept_tokens if self.kept_tokens else self.prompt
 
 
 def _pick_bucket(buckets: list[int], n: int) -> int:
@@ -233,11 +241,17 @@ class InferenceEngine:
             with trace_range("rollout/prefill"):
                 self._run_prefill(entries)
         if self.sched.num_decoding > 0:
-            try:
-                updates = self.sched.reserve_decode(1)
-            except MemoryError as exc:
-                self._preempt(int(exc.args[0]))
-                updates = self.sched.reserve_decode(1)
+            updates = None
+            while updates is None:
+                try:
+                    updates = self.sched.reserve_decode(1)
+                except MemoryError as exc:
+                    # nothing was allocated; make room and ask again (each round frees at least one sequence)
+                    done += self._preempt(int(exc.args[0]))
+                    if self.sched.num_decoding == 0:
+                        updates = []
+            if self.sched.num_decoding == 0:
+                return done
             if updates:
                 self._push_block_updates(updates)
             extent = self.sched.active_extent
@@ -313,7 +327,7 @@ class InferenceEngine:
             req.slot = slot
             pages = self.sched.slot_pages(slot)
             self.h_block_table[slot, : len(pages)] = torch.tensor(pages, dtype=torch.int32)
-            chunk = req.prompt[start:start + length]
+            chunk = req.context[start:start + length]
             ids.extend(chunk)
             p = np.arange(start, start + length)
             pos.append(p)
@@ -329,8 +343,8 @@ class InferenceEngine:
             if last:
                 logit_rows.append(row - 1)
                 fin_slots.append(slot)
-                fin_prompt.append(len(req.prompt))
-                fin_budget.append(req.max_new)
+                fin_prompt.append(len(req.context))
+                fin_budget.append(req.max_new - len(req.kept_tokens))
                 fin_uid.append(rid)
                 fin_stream.append(req.stream)
         touched = sorted({e[0] for e in entries})
@@ -582,8 +596,8 @@ class InferenceEngine:
         if self.cuda:
             torch.cuda.current_stream().synchronize()
         for slot, req, f, g in finished_slots:
-            req.tokens = self.h_out_tokens[slot, :g].tolist()
-            req.logprobs = self.h_out_logprobs[slot, :g].tolist()
+            req.tokens = req.kept_tokens + self.h_out_tokens[slot, :g].tolist()
+            req.logprobs = req.kept_logprobs + self.h_out_logprobs[slot, :g].tolist()
             req.reason = FINISH_NAMES.get(f, "stop")
             req.done = True
             self.finish[slot] = 0
@@ -591,9 +605,36 @@ class InferenceEngine:
             done.append(req)
         return done
 
-    def _preempt(self, slot: int):
-        """Out of KV pages: finish the offending sequence early with reason ``length``."""
-        self.finish[slot] = 2
-        self.active[slot] = 0
-        self._snapshot()
-        self._poll(block=True, drain=True)
+    def _preempt(self, slot: int) -> list[_Request]:
+        """Out of KV pages while reserving the next decode step (``slot`` is the first one that did not fit).
+
+        The sequence admitted last goes back to the head of the waiting queue with what it has generated so far:
+        its pages are freed now, and when pages are available again it is prefilled as prompt + generated tokens and
+        carries on, so the caller still gets a complete response.  (The reference raises "paged KV cache exhausted
+        during decode", ``areno/engine/data/rollout_state.py:212-225``.)  Only when a single sequence is decoding,
+        so that evicting it would make room for nobody, is it finished early with reason ``length``.  Returns the
+        requests that completed while making room."""
+        victim = self.sched.preempt_victim()
+        if self.cuda:
+            torch.cuda.current_stream().synchronize()   # the device state below is final for every launched step
+        if victim < 0:
+            self.finish[slot] = 2
+            self.active[slot] = 0
+            self._snapshot()
+            return self._poll(block=True, drain=True)
+        rid = self.sched.slot_request(victim)
+        req = self._requests.get(rid)
+        fin, g = int(self.finish[victim]), int(self.gen_count[victim])
+        if req is None or fin != 0:
+            # it finished in a step the host has not seen yet: collecting it frees its pages
+            self._snapshot()
+            return self._poll(block=True, drain=True)
+        req.kept_tokens = req.kept_tokens + self.out_tokens[victim, :g].tolist()
+        req.kept_logprobs = req.kept_logprobs + self.out_logprobs[victim, :g].tolist()
+        self.active[victim] = 0
+        self.gen_count[victim] = 0
+        req.slot = -1
+        self._snapshots.clear()     # older snapshots describe the evicted occupant of this slot
+        self.sched.requeue(victim, len(req.context), req.max_new - len(req.kept_tokens))
+        logger.info("KV pages exhausted: request %d re-queued after %d generated tokens", rid, len(req.kept_tokens))
+        return []

@@ -322,12 +322,12 @@ class _HybridAdapter(ModelAdapter):
         if not writer:
             dist.barrier()
             return
-        fname = "model-00001-of-00001.safetensors"
+        fname = "model.safetensors"
         save_file(out, os.path.join(path, fname), metadata={"format": "pt"})
         weight_map = {k: fname for k in out}
-        if source_path and os.path.isdir(source_path):
-            _passthrough_untouched(source_path, path, weight_map)
         total = sum(t.numel() * t.element_size() for t in out.values())
+        if source_path and os.path.isdir(source_path):
+            total += _passthrough_untouched(source_path, path, weight_map)
         with open(os.path.join(path, "model.safetensors.index.json"), "w") as f:
             json.dump({"metadata": {"total_size": total, "areno_checkpoint_writer": "distributed_tp"},
                        "weight_map": dict(sorted(weight_map.items()))}, f, indent=2)

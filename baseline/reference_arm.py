@@ -6,7 +6,7 @@ about 4096 tokens per rank, one AdamW step.
 
 Reference limits that shape the run (recorded in the JSON line): the Qwen2.5-7B shape has to be
 presented as ``model_type: qwen3`` with ``attention_bias`` on and ``qk_layernorm`` off; 28 Q / 4 KV
-heads allow tp in {1, 2, 4} only, so the layout is tp=1 x dp=N; weights are replicated and only the
+heads allow tp in {1, 2, 4} only, and the default layout is tp=1 x dp=N (``ARENO_REF_TP`` picks another); weights are replicated and only the
 optimizer state is sharded; there is no separate weight sync because rollout and training share
 one module.  The reference runs its workers in its own spawned processes, so the step is timed by
 wall clock around its blocking API calls (which return after every rank has finished).
@@ -128,8 +128,11 @@ def run_reference(args) -> None:
     world = int(os.environ.get("WORLD_SIZE", 1))
     if rank != 0:
         return  # the reference spawns and drives its own per-GPU workers from one driver process
-    if not os.path.isdir(os.path.join(REF, "areno")):
-        _emit({"impl": "reference", "unavailable": "baseline/_ref is not installed (pip install --target baseline/_ref failed or was not run)"})
+    from baseline.install_reference import ensure_installed
+
+    ok, why = ensure_installed()      # no-op when the build step already installed it
+    if not ok:
+        _emit({"impl": "reference", "unavailable": f"baseline/_ref is not installed and could not be installed here: {why}"})
         return
     if os.environ.get("ARENO_REF_CHILD") != "1" and (world > 1 or "TORCHELASTIC_RUN_ID" in os.environ):
         _run_isolated(args, max(world, args.gpus))
@@ -198,8 +201,14 @@ def _run(args, n_gpus: int) -> None:
     ckpt_s = time.time() - t0
     _mark(f"starting engine on {n_gpus} GPU(s)")
     attn_backend = os.environ.get("ARENO_REF_ATTN", "flash")
+    # Layout of the reference: tp must divide the 4 KV heads and the GPU count.  tp=1 x dp=N is the default
+    # (ARENO_REF_TP selects tp 2 or 4 for comparison runs).
+    ref_tp = int(os.environ.get("ARENO_REF_TP", "1"))
+    if ref_tp not in (1, 2, 4) or n_gpus % ref_tp != 0:
+        ref_tp = 1
+    ref_dp = n_gpus // ref_tp
     engine = ArenoEngine.from_pretrained(
-        ckpt, tp_size=1, dp_size=n_gpus, devices=list(range(n_gpus)),
+        ckpt, tp_size=ref_tp, dp_size=ref_dp, devices=list(range(n_gpus)),
         optimizer_config=OptimizerConfig(lr=1e-6, betas=(0.9, 0.999), weight_decay=0.01, grad_clip_norm=1.0),
         runtime_config=RuntimeConfig(attn_backend=attn_backend, activation_checkpointing=True),
         loss_fn=grpo_loss_fn)
@@ -226,7 +235,7 @@ def _run(args, n_gpus: int) -> None:
         rewards = np.array([bench.hash_reward(t) for t in responses])
         adv = bench.group_advantages(rewards, bench.GROUP)
         # ~3 sequences (about 4096 tokens) per rank per micro-batch, rows strided over DP by the engine
-        packs = _build_packs(torch, rows, responses, resp_lp, adv, rows_per_pack=3 * n_gpus)
+        packs = _build_packs(torch, rows, responses, resp_lp, adv, rows_per_pack=3 * ref_dp)
         _mark(f"step {step}: train")
         stats = engine.step(packs, gradient_accumulation_steps=None)
         tokens = sum(len(p) + len(t) for p, t in zip(rows, responses))
@@ -264,7 +273,7 @@ def _run(args, n_gpus: int) -> None:
             "model": "Qwen2.5-7B-shaped (as model_type qwen3, attention_bias on, qk_layernorm off)" if not args.small else "small-debug",
             "global_batch": rows_per_rank * n_gpus, "prompt_len": [pmin, pmax], "new_tokens": new_tokens,
             "seq_len": pmax + new_tokens, "micro_batch_tokens": bench.MICRO_TOKENS,
-            "parallelism": f"tp1 x dp{n_gpus}, replicated bf16 weights + ZeRO-1 optimizer, attn_backend={attn_backend}",
+            "parallelism": f"tp{ref_tp} x dp{ref_dp}, replicated bf16 weights + ZeRO-1 optimizer, attn_backend={attn_backend}",
             "timing": "wall clock around blocking engine calls (workers are separate processes)",
             "checkpoint_write_s": ckpt_s,
         },

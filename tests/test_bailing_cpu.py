@@ -146,13 +146,13 @@ def test_checkpoint_round_trip_and_prefix_alias(tmp_path):
         adapter = registry.get_adapter("bailing_moe_linear_v2")
         path = str(tmp_path / f"ckpt{int(mla)}")
         adapter.save_weights(model, path, cfg)
-        tensors = load_file(f"{path}/model-00001-of-00001.safetensors")
+        tensors = load_file(f"{path}/model.safetensors")
         assert "model.word_embeddings.weight" in tensors and "model.layers.1.mlp.experts.7.down_proj.weight" in tensors
         assert "model.layers.0.attention.g_norm.weight" in tensors and "model.layers.1.mlp.gate.expert_bias" in tensors
         assert ("model.layers.1.attention.kv_a_proj_with_mqa.weight" in tensors) == mla
         # rewrite with the other attention prefix: the loader accepts both
         save_file({k.replace(".attention.", ".self_attn."): v for k, v in tensors.items()},
-                  f"{path}/model-00001-of-00001.safetensors", metadata={"format": "pt"})
+                  f"{path}/model.safetensors", metadata={"format": "pt"})
         import json
         with open(f"{path}/model.safetensors.index.json") as f:
             idx = json.load(f)

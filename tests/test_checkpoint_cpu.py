@@ -15,7 +15,7 @@ def test_save_load_round_trip_and_hf_layout(tmp_path):
     cfg = write_tiny_checkpoint(path, seed=3)
     index = json.load(open(os.path.join(path, "model.safetensors.index.json")))
     assert index["metadata"]["areno_checkpoint_writer"] == "distributed_tp"
-    assert os.path.exists(os.path.join(path, "model-00001-of-00001.safetensors"))
+    assert os.path.exists(os.path.join(path, "model.safetensors"))
     keys = set(index["weight_map"])
     assert {"model.embed_tokens.weight", "model.norm.weight", "lm_head.weight",
             "model.layers.0.self_attn.q_proj.weight", "model.layers.0.self_attn.k_proj.bias",
@@ -74,7 +74,7 @@ def test_missing_and_mismatched_tensors_are_reported(tmp_path):
 
     path = str(tmp_path / "ckpt")
     cfg = write_tiny_checkpoint(path, seed=1)
-    fname = os.path.join(path, "model-00001-of-00001.safetensors")
+    fname = os.path.join(path, "model.safetensors")
     tensors = {k: v.clone() for k, v in load_file(fname).items()}     # private copies: the file is rewritten below
     single_process_context()
     # a required tensor is gone
@@ -90,7 +90,7 @@ def test_missing_and_mismatched_tensors_are_reported(tmp_path):
     wrong = dict(tensors)
     wrong["model.layers.0.self_attn.o_proj.weight"] = torch.zeros(7, 7)
     save_file(wrong, fname, metadata={"format": "pt"})
-    index["weight_map"]["model.layers.0.self_attn.o_proj.weight"] = "model-00001-of-00001.safetensors"
+    index["weight_map"]["model.layers.0.self_attn.o_proj.weight"] = "model.safetensors"
     json.dump(index, open(os.path.join(path, "model.safetensors.index.json"), "w"))
     with pytest.raises(ValueError, match="shape mismatch"):
         load_dense_checkpoint(DenseCausalLM(tiny_config()), path, cfg)

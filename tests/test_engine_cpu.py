@@ -141,3 +141,21 @@ def test_training_state_sidecar_resumes_optimizer_and_step(tmp_path, monkeypatch
     shutil.rmtree(os.path.join(path, "areno_state"))
     c = RankWorker(ec2, "cpu")
     assert c.training_manager().global_step == 0
+
+
+def test_sequence_evicted_for_lack_of_kv_pages_is_requeued_and_completes():
+    single_process_context()
+    model = DenseCausalLM(tiny_config())
+    init_weights(model, 3)
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(3, 512, (n,), generator=g).tolist() for n in (60, 61, 30)]
+    roomy = _engine(model).generate(prompts, SamplingParams(temperature=0.0), (), 24)
+    # 4 pages of 64 tokens: the two 60-token prompts fit one page each until their contexts cross 64 tokens together
+    tight = _engine(model, num_pages=4)
+    out = tight.generate(prompts, SamplingParams(temperature=0.0), (), 24)
+    assert [len(t) for t in out.tokens] == [24, 24, 24]
+    assert out.finish_reasons == ["length"] * 3
+    assert out.tokens == roomy.tokens
+    for a, b in zip(out.logprobs, roomy.logprobs):
+        assert torch.allclose(torch.tensor(a), torch.tensor(b), atol=2e-2)
+    assert any(r.kept_tokens for r in tight._requests.values())     # an eviction really happened

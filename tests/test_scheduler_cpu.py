@@ -102,3 +102,57 @@ def test_multi_step_reservation_allocates_all_pages_up_front():
     s.advance(100)
     assert s.slot_seq_len(0) == 160 and len(s.slot_pages(0)) == 3
     assert s.reserve_decode(1) == []                         # still inside the third page
+
+
+def test_reserve_decode_is_all_or_nothing_when_pages_run_out():
+    # two sequences cross a page boundary on the same step and only one page is free: neither may be served,
+    # and after room is made the retry reports the new pages of both
+    s = Scheduler(max_slots=2, num_pages=3, page_size=4, max_pages_per_seq=4, max_prefill_tokens=64)
+    s.add(1, 3, 8)
+    s.add(2, 3, 8)
+    assert len(s.plan_prefill()) == 2 and s.num_free_pages == 1      # one page each (prompt + first token)
+    assert s.reserve_decode(1) == []                                 # token 4 still fits the first page
+    s.advance(1)
+    before = [s.slot_pages(0), s.slot_pages(1)]
+    with pytest.raises(MemoryError) as err:
+        s.reserve_decode(1)                                          # both need a second page, one is free
+    assert int(err.value.args[0]) == 1                               # the slot whose share did not fit
+    assert [s.slot_pages(0), s.slot_pages(1)] == before and s.num_free_pages == 1
+    assert s.preempt_victim() == 1                                   # admitted last
+    s.requeue(1, 3 + 2, 8 - 2)
+    assert s.num_waiting == 1 and s.num_running == 1 and s.num_free_pages == 2
+    ups = s.reserve_decode(1)
+    assert [(u[0], u[1]) for u in ups] == [(0, 1)] and s.slot_pages(0)[1] == ups[0][2]
+    s.finish(0)
+    plan = s.plan_prefill()                                          # the evicted request comes back first
+    assert [(p[1], p[3]) for p in plan] == [(2, 5)]
+
+
+def test_preempt_victim_needs_two_decoding_sequences():
+    s = Scheduler(max_slots=2, num_pages=2, page_size=4, max_pages_per_seq=2, max_prefill_tokens=64)
+    s.add(7, 3, 5)
+    s.plan_prefill()
+    assert s.preempt_victim() == -1
+
+
+def test_chunked_prompt_keeps_its_pages_between_chunks():
+    # prefill budget below the prompt length: the first prompt is admitted and reserves all of its pages, so the
+    # second long prompt has to wait instead of being admitted against pages the first still needs
+    s = Scheduler(max_slots=4, num_pages=6, page_size=8, max_pages_per_seq=6, max_prefill_tokens=8)
+    s.add(1, 30, 4)      # 31 tokens -> 4 pages
+    s.add(2, 30, 4)
+    plan = s.plan_prefill()
+    assert [(p[1], p[2], p[3], p[4]) for p in plan] == [(1, 0, 8, False)]
+    assert s.num_free_pages == 2 and s.num_running == 1 and s.num_waiting == 1
+    admitted_second_at = None
+    for step in range(40):
+        plan = s.plan_prefill()
+        if any(p[1] == 2 for p in plan) and admitted_second_at is None:
+            admitted_second_at = step
+            assert s.slot_request(0) != 1          # only after the first sequence had left
+        if s.num_decoding:
+            s.reserve_decode(1)                    # never raises: a mid-prompt sequence cannot be stranded
+            s.advance(1)
+        if s.slot_request(0) == 1 and s.slot_seq_len(0) >= 34:
+            s.finish(0)
+    assert admitted_second_at is not None
