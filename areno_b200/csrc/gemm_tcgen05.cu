@@ -700,13 +700,16 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, const void* bia
     p.num_groups = group->num_groups;
     workspace = nullptr;  // no split-K in grouped modes
   }
-  // Split-K for skinny problems (decode): too few output tiles to fill the GPU, long K.
+  // Split-K for problems with too few output tiles to fill the GPU and a long K: decode (one M tile), and
+  // the few-hundred-row batches of a tensor-parallel decode step, whose per-rank N or K is a fraction of the
+  // layer's (two to four M tiles).
   const int num_kb = (K + kBK - 1) / kBK;
   const int tiles = p.tiles_m * p.tiles_n;
   bool split = false;
-  if (epi <= 1 && p.tiles_m == 1 && tiles * 2 <= num_sms() && num_kb >= 8 && workspace != nullptr && (N % 4) == 0) {
+  if (epi <= 1 && M <= 4 * kBM && tiles * 2 <= num_sms() && num_kb >= 8 && workspace != nullptr && (N % 4) == 0) {
     int want = num_sms() / tiles;
     if (want > 16) want = 16;
+    if (M > kBM && want > 8) want = 8;   // the fold reads every partial back: keep it a fraction of the GEMM
     int kbps = (num_kb + want - 1) / want;
     if (kbps < 4) kbps = 4;
     const int splits = (num_kb + kbps - 1) / kbps;

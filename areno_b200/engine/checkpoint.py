@@ -146,6 +146,8 @@ def load_rule(index: SafetensorsIndex, param: torch.Tensor, rule: Rule, keys: tu
             parts.append(index.get_rows(k, lo, hi))
         t = torch.cat(parts, dim=0)
     elif rule.kind == "qkv":
+        if len(qkv_meta) > 4:
+            raise ValueError("an uneven (padded) head layout is inference-only and is filled from a full replica")
         hq_rows, hkv, d, rep = qkv_meta          # local q rows (heads * q_mult), local kv heads, head_dim, kv replication
         q_rows = hq_rows * d
         q = index.get_rows(keys[0], r * q_rows, (r + 1) * q_rows)
@@ -263,6 +265,8 @@ def export_rule(param: torch.Tensor, rule: Rule, keys: tuple[str, ...], qkv_meta
             yield k, _gather_to(owner_rank(k, tp), t[off:off + n], 0)
             off += n
     elif rule.kind == "qkv":
+        if len(qkv_meta) > 4:
+            raise ValueError("an uneven (padded) head layout is inference-only and cannot be saved")
         hq_rows, hkv, d, rep = qkv_meta
         q_rows = hq_rows * d
         yield keys[0], _gather_to(owner_rank(keys[0], tp), t[:q_rows], 0)

@@ -141,16 +141,22 @@ class ModelConfig:
             return 1
         return tp_size // self.num_key_value_heads
 
-    def validate_tp(self, tp_size: int) -> None:
+    def validate_tp(self, tp_size: int, inference_only: bool = False) -> None:
         """Shapes must split evenly over TP; KV heads may instead be replicated when ``tp_size`` is a
         multiple of them (the reference allows that only for three families,
-        ``areno/engine/config.py:159-171``)."""
+        ``areno/engine/config.py:159-171``).  A layout that is used for inference only (a separate rollout
+        layout) may also be wider than the query heads divide, as long as it is a multiple of the KV heads: the
+        query heads of one KV group are then dealt out unevenly over the ranks that share the group's KV head
+        and the short ranks carry zero-weight padding heads (28 query / 4 KV heads at tp 8: 4 + 3 per pair)."""
         if tp_size < 1:
             raise ValueError("tp_size must be >= 1")
-        if self.num_attention_heads % tp_size != 0:
-            raise ValueError(
-                f"num_attention_heads={self.num_attention_heads} must be divisible by tp_size={tp_size}")
         kv = self.num_key_value_heads
+        if self.num_attention_heads % tp_size != 0:
+            padded_ok = (inference_only and self.model_type in ("llama", "qwen2", "qwen3") and kv > 0
+                         and tp_size % kv == 0 and self.num_attention_heads % kv == 0)
+            if not padded_ok:
+                raise ValueError(
+                    f"num_attention_heads={self.num_attention_heads} must be divisible by tp_size={tp_size}")
         if kv % tp_size != 0 and tp_size % kv != 0:
             raise ValueError(f"num_key_value_heads={kv} must divide or be divisible by tp_size={tp_size}")
         if self.intermediate_size and self.intermediate_size % tp_size != 0:
@@ -199,7 +205,7 @@ class EngineConfig:
                 raise ValueError("rollout_tp_size requires tp_size == 1 for training")
             if self.rollout_tp_size < 1 or world % self.rollout_tp_size != 0:
                 raise ValueError(f"world size {world} must be a multiple of rollout_tp_size={self.rollout_tp_size}")
-            self.model.validate_tp(self.rollout_tp_size)
+            self.model.validate_tp(self.rollout_tp_size, inference_only=True)
         if self.runtime.kv_block_size % 16 != 0:
             raise ValueError("runtime.kv_block_size must be a multiple of 16")
 

@@ -14,6 +14,7 @@ raw-logit log-softmax at temperature 1, new requests may join a running session 
 
 from __future__ import annotations
 
+import os
 import time
 from dataclasses import dataclass, field
 from typing import Callable
@@ -39,6 +40,22 @@ klib.register_signature("areno_decode_commit", "ppppppppppp" + "iip")
 klib.register_signature("areno_prefill_commit", "pppppp" + "i" + "pppppppp" + "ip")
 
 FINISH_NAMES = {0: "running", 1: "stop", 2: "length", 3: "cancelled"}
+
+# Debug guard (``ARENO_CHECK_TOKEN_IDS=1``, as ``areno/engine/runtime/common.py:19,143-159``): every sampled token id
+# is range-checked when its sequence is collected, so a degenerate sampler fails loudly instead of feeding ids
+# outside the vocabulary to the embedding of the next step or to training.
+_CHECK_TOKEN_IDS = os.environ.get("ARENO_CHECK_TOKEN_IDS", "0").lower() in {"1", "true", "yes", "on"}
+
+
+def _check_token_ids(tokens: list[int], vocab_size: int, name: str) -> None:
+    if not tokens:
+        return
+    lo, hi = min(tokens), max(tokens)
+    if lo >= 0 and hi < vocab_size:
+        return
+    bad = [t for t in tokens if t < 0 or t >= vocab_size]
+    raise RuntimeError(f"{name} out of vocab range [0, {vocab_size}): min={lo} max={hi} bad_min={min(bad)} "
+                       f"bad_max={max(bad)} count={len(bad)} of {len(tokens)}")
 
 
 @dataclass
@@ -137,6 +154,7 @@ class InferenceEngine:
         self._snapshots: list = []
         self.step_count = 0
         self.decode_tokens = 0
+        self._peer_waits = False
 
     # ------------------------------------------------------------------ state
     def _alloc_state(self):
@@ -209,6 +227,9 @@ class InferenceEngine:
         self._graph_key = (params.temperature, params.top_k, params.top_p, params.min_new_tokens)
         self.step_count = 0
         self.decode_tokens = 0
+        from ..parallel.symm import get_tp_comm
+
+        self._peer_waits = self.cuda and get_tp_comm(get_context()) is not None
 
     def add_request(self, prompt: list[int], max_new_tokens: int | None = None, tag=None,
                     stream: int | None = None) -> int:
@@ -260,6 +281,10 @@ class InferenceEngine:
             self.sched.advance(1)
             self.step_count += 1
             self._snapshot()
+            if self._peer_waits and self.step_count % 256 == 0:
+                # kernels that wait on other GPUs report a wait that ran out through the status word: look at it
+                # regularly, not only once the rollout is over
+                klib.check_status(self.device)
         elif not entries:
             if not self._snapshots:
                 self._snapshot()
@@ -598,6 +623,8 @@ class InferenceEngine:
         for slot, req, f, g in finished_slots:
             req.tokens = req.kept_tokens + self.h_out_tokens[slot, :g].tolist()
             req.logprobs = req.kept_logprobs + self.h_out_logprobs[slot, :g].tolist()
+            if _CHECK_TOKEN_IDS:
+                _check_token_ids(req.tokens, self.vocab, f"sampled tokens of request {req.rid}")
             req.reason = FINISH_NAMES.get(f, "stop")
             req.done = True
             self.finish[slot] = 0

@@ -265,6 +265,28 @@ class ShardedAdamW:
             for w in works:
                 w.wait()
 
+    @torch.no_grad()
+    def self_check_reduce_scatter(self, bucket: int = 0) -> float | None:
+        """Reduce one bucket of random gradients with the peer-memory kernel and with NCCL's
+        ``reduce_scatter_tensor`` and return the largest absolute difference on this rank's shard (``None`` when the
+        NCCL path is in use).  Must be called between steps (the bucket is zeroed afterwards)."""
+        if self.grad_comm is None or self.dp <= 1 or not self.buckets:
+            return None
+        b = self.buckets[min(bucket, len(self.buckets) - 1)]
+        i = self.buckets.index(b)
+        g = torch.Generator(device=b.grad_flat.device).manual_seed(4321 + self.dp_rank)
+        b.grad_flat.copy_(torch.randn(b.grad_flat.shape, device=b.grad_flat.device, generator=g))
+        want = torch.empty(b.shard, dtype=torch.float32, device=b.grad_flat.device)
+        dist.reduce_scatter_tensor(want, b.grad_flat.clone(), group=self.ctx.dp_group)
+        self.grad_comm.begin_step()
+        self.grad_comm.launch(i, b.grad_offset, b.shard)
+        self.grad_comm.finish()
+        err = float((self._grad_shard(b) - want).abs().max())
+        torch.cuda.synchronize()
+        dist.barrier(group=self.ctx.dp_group)       # nobody zeroes the bucket while a peer may still be reading it
+        b.grad_flat.zero_()
+        return err
+
     def _sum_replicated_kv_grads(self):
         """K / V rows of a fused qkv projection are copies of one another on ``rep`` neighbouring ranks when the TP
         size exceeds the KV head count (``kv_replicated`` on the parameter).  Each copy only sees the gradient of

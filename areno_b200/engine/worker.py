@@ -64,7 +64,10 @@ class RankWorker:
             # peer-memory communicator for the fused GEMM -> all-reduce -> residual -> RMSNorm path
             from ..parallel.symm import setup_tp_comm
 
-            self.tp_comm = setup_tp_comm(rctx, config.model.hidden_size, 512)
+            # sized for the largest batch one forward pass can see: a prefill chunk or every decode slot of the group
+            rows = max(int(config.runtime.max_prefill_tokens), int(config.max_running_seqs) * rctx.tp_size, 512)
+            rows = min(rows, int(os.environ.get("ARENO_TP_COMM_MAX_ROWS", "16384")))
+            self.tp_comm = setup_tp_comm(rctx, config.model.hidden_size, rows)
         self.trainer: TrainingManager | None = None
         self.infer: InferenceEngine | None = None
         self.roles = None
@@ -184,6 +187,22 @@ class RankWorker:
             self._actor_on_device = False
             if self.device.type == "cuda":
                 torch.cuda.empty_cache()
+
+    def close(self) -> None:
+        """Release what other ranks have mapped (symmetric heaps) after a group barrier; the worker is unusable
+        afterwards.  Every rank of the job must call it."""
+        if self.infer is not None:
+            self.infer._graphs.clear()
+        if self.tp_comm is not None:
+            from ..parallel import symm
+
+            symm._COMMS.pop(id(self.rollout_ctx), None)
+            self.tp_comm.close()
+            self.tp_comm = None
+        opt = getattr(self.trainer, "optimizer", None)
+        if opt is not None and getattr(opt, "grad_comm", None) is not None:
+            opt.grad_comm.close()
+            opt.grad_comm = None
 
     def role_manager(self):
         if self.roles is None:

@@ -32,6 +32,7 @@ from ..ops import gemm, paged_attention as pa
 from ..ops.attention import VarlenMeta
 from ..parallel import collectives as coll
 from ..parallel.context import get_context
+from ..parallel.symm import TpPartial
 from .layers import (GatedMLP, QKVParallelLinear, RMSNorm, RowParallelLinear, VocabParallelEmbedding,
                      VocabParallelLMHead)
 
@@ -87,7 +88,12 @@ class Attention(nn.Module):
         self.qkv = QKVParallelLinear(cfg.hidden_size, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
                                      cfg.qkv_bias, dtype, device)
         self.hq, self.hkv = self.qkv.hq, self.qkv.hkv
-        self.o = RowParallelLinear(cfg.num_attention_heads * cfg.head_dim, cfg.hidden_size, False, dtype, device)
+        o_range = None
+        if cfg.num_attention_heads % get_context().tp_size != 0:
+            # padded heads (inference-only layout): the projection reads this rank's real heads, padding columns are zero
+            o_range = (self.hq * cfg.head_dim, self.qkv.q_lo * cfg.head_dim, self.qkv.q_n * cfg.head_dim)
+        self.o = RowParallelLinear(cfg.num_attention_heads * cfg.head_dim, cfg.hidden_size, False, dtype, device,
+                                   in_range=o_range)
         self.q_norm = self.k_norm = None
         if cfg.qk_norm:
             self.q_norm = RMSNorm(cfg.head_dim, cfg.rms_norm_eps, dtype, device, cfg.norm_weight_offset)
@@ -202,7 +208,10 @@ class DecoderLayer(nn.Module):
         # the region is opened here, not by the caller, so that a recompute under activation checkpointing sees it too
         with coll.sequence_parallel_region(sp):
             sp = coll.in_sequence_parallel()
-            if residual is None:
+            if residual is None and isinstance(x, TpPartial):
+                # the embedding lookup is still spread over the TP group: its sum is the residual stream
+                h, residual = self.input_norm(x, None, want_sum=True)
+            elif residual is None:
                 residual = x
                 h = self.input_norm(x)
             else:
@@ -238,6 +247,10 @@ class DenseCausalLM(nn.Module):
         self.lm_head = VocabParallelLMHead(cfg.vocab_size, cfg.hidden_size, dtype, device,
                                            tied_to=self.embed if cfg.tie_word_embeddings else None)
         self._kv_spec = None
+        # layer 0 starts with ``input_norm`` of the embedding output, so that norm can take the embedding lookup
+        # un-reduced; only claimed for the stock layer / model forward (families with their own are left alone)
+        self._first_norm_takes_partial = (type(self.layers[0]).forward is DecoderLayer.forward
+                                          and type(self).forward is DenseCausalLM.forward)
 
     def _make_layer(self, i, dtype, device):
         return DecoderLayer(self.cfg, i, dtype, device)
@@ -265,7 +278,8 @@ class DenseCausalLM(nn.Module):
             with coll.sequence_parallel_region(True):
                 x = self.embed(ids)            # the vocabulary-parallel sum becomes a reduce-scatter: [T / tp, H]
         else:
-            x = self.embed(ids)
+            # inference with a peer-memory communicator: the first norm folds the vocabulary-parallel sum in
+            x = self.embed(ids, defer_reduce=isinstance(meta, InferMeta) and self._first_norm_takes_partial)
         residual = None
         use_ckpt = isinstance(meta, TrainMeta) and meta.activation_checkpointing and torch.is_grad_enabled()
         n_ckpt = len(self.layers)

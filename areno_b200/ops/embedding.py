@@ -60,7 +60,18 @@ class _Embedding(torch.autograd.Function):
         return None, dw, None, None
 
 
-def embedding(ids, table, vocab_start: int = 0, scale: float = 1.0):
+def embedding(ids, table, vocab_start: int = 0, scale: float = 1.0, out: torch.Tensor | None = None):
+    """``out`` (inference only, CUDA): write the rows into this contiguous ``[ids.numel(), H]`` tensor."""
     if not table.is_cuda:
-        return embedding_reference(ids, table, vocab_start, scale)
+        res = embedding_reference(ids, table, vocab_start, scale)
+        return res if out is None else out.copy_(res)
+    if out is not None:
+        flat = ids.reshape(-1)
+        if flat.dtype != torch.int64:
+            flat = flat.to(torch.int64)
+        flat = flat.contiguous()
+        assert out.is_contiguous() and out.shape == (flat.numel(), table.shape[1]) and out.dtype == table.dtype
+        _lib.call("areno_embedding_fwd", flat.data_ptr(), table.data_ptr(), out.data_ptr(), flat.numel(), table.shape[1],
+                  vocab_start, vocab_start + table.shape[0], float(scale), _lib.stream())
+        return out
     return _Embedding.apply(ids, table, vocab_start, scale)

@@ -89,8 +89,9 @@ def gemm(
         assert bias.dtype == torch.bfloat16 and bias.is_contiguous() and bias.numel() == n
     status = _lib.status_buffer(a.device)
     ws_ptr, ws_bytes = None, 0
-    if m <= 128 and epi <= EPI_BF16_BIAS and n <= 18944 and k >= 512:
-        ws = _workspace(a.device, 16 * m * n * 4)        # split-K partials of a skinny problem
+    if m <= 512 and epi <= EPI_BF16_BIAS and n <= 18944 and k >= 512 and (m <= 128 or not b_mn):
+        # split-K partials of a problem with few output tiles (at most 16 splits; fewer as rows grow)
+        ws = _workspace(a.device, 16 * m * n * 4 if m <= 128 else min(8 * m * n * 4, 64 << 20))
         ws_ptr, ws_bytes = ws.data_ptr(), ws.numel()
     elif m > 128:
         ws = _workspace(a.device, 0)                      # K slices of the last partial wave (at most 148 tiles)

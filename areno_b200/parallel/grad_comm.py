@@ -23,7 +23,7 @@ import torch
 import torch.distributed as dist
 
 from ..ops import _lib
-from .symm import _check
+from .symm import TpDesc, _check, _ptr_array
 
 _lib.register_signature("areno_dp_grad_ready", "iipppiip")
 _lib.register_signature("areno_dp_grad_reduce_scatter", "iipppiillpiip")
@@ -68,7 +68,6 @@ class GradComm:
         self._ready_ptrs = (ctypes.c_void_p * self.n)(*[b + self.barrier_bytes for b in self.bases])
         self._grad_ptrs = (ctypes.c_void_p * self.n)(*[b + self.header for b in self.bases])
         self.grads = torch.as_tensor(_Blob32(self._local_base + self.header, self.total_elems), device=device)
-        self.barrier_epoch = torch.zeros(int(lib.areno_tp_max_blocks()), dtype=torch.int32, device=device)
         self.status = _lib.status_buffer(device)
         self.stream = torch.cuda.Stream(device=device)
         self.epoch = 0
@@ -78,6 +77,9 @@ class GradComm:
         # cover the skew that a whole rollout + backward can build up between them (power capping alone gives
         # several per cent), while still ending a wait for a rank that is gone
         self.wait_ms = int(os.environ.get("ARENO_GRAD_RS_WAIT_MS", "20000"))
+        # the rendezvous after the reduction uses the same bound: it is the only guard before the buckets are zeroed
+        self._barrier_desc = TpDesc(self.n, self.rank, _ptr_array(self.bases), None, None, None, None, None, None,
+                                    self.status.data_ptr(), self.wait_ms)
         torch.cuda.synchronize(device)
         dist.barrier(group=group)
 
@@ -114,8 +116,7 @@ class GradComm:
         cur = torch.cuda.current_stream(self.device)
         cur.wait_stream(self.stream)
         _lib.check_status()   # host read of the status word: a timed-out wait must not reach the optimizer
-        _lib.call("areno_tp_barrier", self.n, self.rank, self._barrier_ptrs, self.barrier_epoch.data_ptr(),
-                  self.status.data_ptr(), 1, cur.cuda_stream)
+        _lib.call("areno_tp_barrier", ctypes.addressof(self._barrier_desc), cur.cuda_stream)
 
     def close(self) -> None:
         if not self.bases:

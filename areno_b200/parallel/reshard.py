@@ -28,6 +28,9 @@ def shard_of(full: torch.Tensor, like: torch.Tensor, shard, tp_rank: int, tp_siz
         n = like.shape[0]
         return [(0, n, full[r * n:(r + 1) * n])]
     if kind == "row":
+        if meta is not None:   # uneven head layout: (first real input feature, real features); the rest stays zero
+            lo, n = meta
+            return [(0, like.shape[0], full[:, lo:lo + n], n)]
         n = like.shape[1]
         return [(0, like.shape[0], full[:, r * n:(r + 1) * n])]
     if kind == "vocab":
@@ -42,13 +45,18 @@ def shard_of(full: torch.Tensor, like: torch.Tensor, shard, tp_rank: int, tp_siz
             src += n * tp_size
         return out
     if kind == "qkv":
-        hq_rows, hkv, d, rep = meta  # local q rows (heads x q_mult), local kv heads, head_dim, kv replication
+        hq_rows, hkv, d, rep = meta[:4]  # local q rows (heads x q_mult), local kv heads, head_dim, kv replication
         q_rows, kv_rows = hq_rows * d, hkv * d
         q_full = q_rows * tp_size
         kv_full = kv_rows * (tp_size // rep)
         kv_rank = r // rep
+        q_piece = (0, q_rows, full[r * q_rows:(r + 1) * q_rows])
+        if len(meta) > 4:      # uneven head layout: real q rows [q_lo, q_lo + q_n) of q_all, local padding rows stay zero
+            q_lo, q_n, q_all = (int(x) * d for x in meta[4:7])
+            q_full = q_all
+            q_piece = (0, q_n, full[q_lo:q_lo + q_n])
         return [
-            (0, q_rows, full[r * q_rows:(r + 1) * q_rows]),
+            q_piece,
             (q_rows, q_rows + kv_rows, full[q_full + kv_rank * kv_rows: q_full + (kv_rank + 1) * kv_rows]),
             (q_rows + kv_rows, q_rows + 2 * kv_rows,
              full[q_full + kv_full + kv_rank * kv_rows: q_full + kv_full + (kv_rank + 1) * kv_rows]),
@@ -70,12 +78,20 @@ def reshard_into(dst_model: torch.nn.Module, src_model: torch.nn.Module, tp_rank
         full = src.get(name)
         if full is None:
             raise KeyError(f"rollout parameter {name} has no training counterpart")
-        pieces = shard_of(full.data, p.data, getattr(p, "tp_shard", None), tp_rank, tp_size)
+        shard = getattr(p, "tp_shard", None)
+        pieces = shard_of(full.data, p.data, shard, tp_rank, tp_size)
+        uneven = bool(shard) and ((shard[0] == "qkv" and len(shard[1]) > 4) or (shard[0] == "row" and shard[1] is not None))
+        if uneven:
+            p.data.zero_()            # padding heads: rows / columns that no piece covers must be zero
         covered = 0
-        for lo, hi, view in pieces:
-            p.data[lo:hi].copy_(view)
+        for piece in pieces:
+            lo, hi, view = piece[:3]
+            if len(piece) > 3:        # column-limited piece (row-parallel weight behind padded heads)
+                p.data[lo:hi, : piece[3]].copy_(view)
+            else:
+                p.data[lo:hi].copy_(view)
             covered += hi - lo
-        if covered < p.shape[0]:
+        if covered < p.shape[0] and not uneven:
             p.data[covered:].zero_()  # vocabulary padding rows
         written += p.numel() * p.element_size()
     return written

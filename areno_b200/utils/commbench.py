@@ -1,4 +1,11 @@
-"""Collective micro-benchmarks over the data-parallel group (launch with ``python -m torch.distributed.run``).
+"""Collective micro-benchmarks (launch with ``python -m torch.distributed.run``).
+
+``tp_fused``: the fused row-parallel path of a tensor-parallel decoder block (GEMM partial into the symmetric heap,
+then one kernel: reduce over the group + residual add + RMSNorm + publish; ``parallel/symm.py``) against the same
+GEMM followed by NCCL ``all_reduce`` and the residual RMSNorm kernel, over all ranks of the job as one TP group, at
+decode and prefill row counts.  The roofline of a call is the slower of the GEMM FLOPs at the measured cuBLAS
+bf16 rate and the bytes that have to enter each GPU over NVLink (reduce-scatter of the partial plus all-gather of the
+residual stream and the normalised rows: ``3 (tp - 1) / tp`` of ``rows x H`` bf16) at the measured peer-copy rate.
 
 ``grad_rs``: reduce-scatter of fp32 gradient buckets over peer memory (``parallel/grad_comm.py``) against
 NCCL's ``reduce_scatter_tensor`` on the same sizes.  Timed with CUDA events on the launching stream after
@@ -66,8 +73,80 @@ def bench_grad_rs(ctx, mib: int, iters: int, warmup: int) -> dict:
             "fused_frac_of_peer_copy": round(pulled / t_fused / 1e6 / PEER_COPY_GBS, 3)}
 
 
+def bench_tp_fused(ctx, rows: int, hidden: int, k_full: int, iters: int, warmup: int, comm, peaks: dict) -> dict:
+    from ..ops import gemm, norm as norm_ops
+
+    tp, dev = ctx.tp_size, ctx.device
+    k_local = k_full // tp
+    g = torch.Generator(device=dev).manual_seed(11 + ctx.tp_rank)
+    x = torch.randn(rows, k_local, device=dev, generator=g).to(torch.bfloat16)
+    w = (torch.randn(hidden, k_local, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+    res = torch.randn(rows, hidden, device=dev, generator=torch.Generator(device=dev).manual_seed(5)).to(torch.bfloat16)
+    nw = torch.ones(hidden, device=dev, dtype=torch.bfloat16)
+    flush = torch.empty(192 << 20, dtype=torch.uint8, device=dev)   # larger than L2: weights come from HBM every call
+
+    def fused():
+        flush.zero_()
+        part = comm.row_linear(x, w)
+        comm.reduce_rmsnorm(part, res, nw, 1e-6)
+
+    def fused_collective_only():
+        part = comm.new_partial(rows)
+        comm.reduce_rmsnorm(part, res, nw, 1e-6)
+
+    def nccl():
+        flush.zero_()
+        y = gemm.gemm(x, w)
+        dist.all_reduce(y, group=ctx.tp_group)
+        norm_ops.rmsnorm(y, nw, 1e-6, residual=res)
+
+    buf = torch.empty(rows, hidden, device=dev, dtype=torch.bfloat16)
+
+    def nccl_collective_only():
+        dist.all_reduce(buf, group=ctx.tp_group)
+        norm_ops.rmsnorm(buf, nw, 1e-6, residual=res)
+
+    def flush_only():
+        flush.zero_()
+
+    t_flush = _timed(flush_only, iters, warmup, ctx.tp_group)
+    out = {"case": "tp_fused", "tp": tp, "rows": rows, "hidden": hidden, "k_local": k_local,
+           "multimem": bool(comm.use_mc), "heap": comm.heap.kind}
+    t_f = _timed(fused, iters, warmup, ctx.tp_group) - t_flush
+    t_n = _timed(nccl, iters, warmup, ctx.tp_group) - t_flush
+    t_fc = _timed(fused_collective_only, iters, warmup, ctx.tp_group)
+    t_nc = _timed(nccl_collective_only, iters, warmup, ctx.tp_group)
+    flops = 2.0 * rows * hidden * k_local
+    link_bytes = 3.0 * (tp - 1) / tp * rows * hidden * 2
+    weight_bytes = 2.0 * hidden * k_local
+    t_roof = max(flops / (peaks["bf16_tflops"] * 1e12), link_bytes / (PEER_COPY_GBS * 1e9),
+                 weight_bytes / (peaks["hbm_gbs"] * 1e9)) * 1e3
+    t_roof_coll = link_bytes / (PEER_COPY_GBS * 1e9) * 1e3
+    out.update({"fused_us": round(t_f * 1e3, 1), "nccl_us": round(t_n * 1e3, 1), "speedup": round(t_n / t_f, 2),
+                "roofline_us": round(t_roof * 1e3, 1), "fused_frac_of_roofline": round(t_roof / t_f, 3),
+                "reduce_kernel_us": round(t_fc * 1e3, 1), "nccl_allreduce_norm_us": round(t_nc * 1e3, 1),
+                "collective_roofline_us": round(t_roof_coll * 1e3, 1),
+                "collective_frac_of_link": round(t_roof_coll / t_fc, 3)})
+    return out
+
+
+def _peaks() -> dict:
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return {"bf16_tflops": float(p["bf16_tflops"]), "hbm_gbs": float(p["hbm_gbs"]), "source": "measured"}
+    except (OSError, KeyError, ValueError):
+        return {"bf16_tflops": 1590.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    ap.add_argument("--case", default="grad_rs", choices=["grad_rs", "tp_fused"])
+    ap.add_argument("--rows", type=int, nargs="*", default=[64, 256, 512, 2048, 4096])
+    ap.add_argument("--hidden", type=int, default=3584)
+    ap.add_argument("--k", type=int, nargs="*", default=[18944, 3584], help="full (unsharded) input widths")
+    ap.add_argument("--multimem", type=int, default=-1, help="1 / 0 forces the multimem or the plain peer path")
     ap.add_argument("--mib", type=int, nargs="*", default=[256, 1024])
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
@@ -77,8 +156,30 @@ def main(argv=None) -> int:
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", rank))
     torch.cuda.set_device(local)
-    ctx = init_parallel(rank, world, tp_size=1, master_addr=os.environ.get("MASTER_ADDR", "127.0.0.1"),
+    ctx = init_parallel(rank, world, tp_size=world if args.case == "tp_fused" else 1,
+                        master_addr=os.environ.get("MASTER_ADDR", "127.0.0.1"),
                         master_port=int(os.environ.get("MASTER_PORT", "29500")), device=torch.device("cuda", local))
+    if args.case == "tp_fused":
+        from ..ops import _lib
+        from ..parallel.symm import setup_tp_comm
+
+        comm = setup_tp_comm(ctx, args.hidden, max(args.rows))
+        modes = [comm.use_mc] if args.multimem < 0 else [bool(args.multimem) and comm.use_mc]
+        if args.multimem < 0 and comm.use_mc:
+            modes = [True, False]
+        peaks = _peaks()
+        for use_mc in modes:
+            comm.use_mc = use_mc
+            for k_full in args.k:
+                for rows in args.rows:
+                    out = bench_tp_fused(ctx, rows, args.hidden, k_full, args.iters, args.warmup, comm, peaks)
+                    out["peaks"] = peaks["source"]
+                    if rank == 0:
+                        print(json.dumps(out), flush=True)
+        _lib.check_status()
+        comm.close()
+        dist.barrier()
+        os._exit(0)
     for mib in args.mib:
         out = bench_grad_rs(ctx, mib, args.iters, args.warmup)
         if rank == 0:

@@ -58,9 +58,17 @@ def parse_args():
     return ap.parse_args()
 
 
+# Rollout TP width per GPU count, from the measured rollout time of each layout on this workload
+# (``profiles/bench_7b_grpo_scaling.md``); ``ARENO_BENCH_ROLLOUT_TP`` or ``--rollout-tp`` override it.
+ROLLOUT_TP_BY_WORLD = {1: 1, 2: 1, 4: 1, 8: 1}
+
+
 def pick_rollout_tp(world: int) -> int:
-    """Rollout layout for the benchmark model (28 query heads, 4 KV heads: TP must divide 4)."""
-    return 1
+    """Rollout layout for the benchmark model.  28 query / 4 KV heads split evenly over tp 2 and 4; tp 8 uses the
+    uneven head split of the rollout-only layout (4 + 3 query heads per KV pair)."""
+    env = os.environ.get("ARENO_BENCH_ROLLOUT_TP")
+    tp = int(env) if env else ROLLOUT_TP_BY_WORLD.get(world, 1)
+    return tp if tp >= 1 and world % tp == 0 else 1
 
 
 # ------------------------------------------------------------------------- synthetic data
@@ -234,6 +242,23 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    # Multi-GPU correctness evidence, taken before the first step: one gradient bucket reduced with the peer-memory
+    # kernel against NCCL's reduce-scatter, and (tensor-parallel rollout) one fused row-parallel call against
+    # GEMM + NCCL all-reduce + RMSNorm.
+    checks = {}
+    if world > 1:
+        err = worker.training_manager().optimizer.self_check_reduce_scatter()
+        if err is not None:
+            t = torch.tensor([err], dtype=torch.float64, device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            checks["grad_rs_max_abs"] = float(t[0])
+            assert checks["grad_rs_max_abs"] < 1e-3, f"peer-memory gradient reduce-scatter differs from NCCL: {checks}"
+        if worker.tp_comm is not None:
+            checks["tp_fused_rel"] = worker.tp_comm.self_check()
+            checks["tp_heap"] = worker.tp_comm.heap.kind
+            checks["tp_multimem"] = bool(worker.tp_comm.use_mc)
+            assert checks["tp_fused_rel"] < 1e-2, f"fused row-parallel reduce differs from NCCL: {checks}"
+        klib.check_status()
     for w in range(args.warmup):
         one_step(w)
     barrier()
@@ -281,7 +306,7 @@ def run_ours(args):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": (value / BASELINE_PUBLISHED) if BASELINE_PUBLISHED else None,
             "dtype": "bf16", "data": "synthetic (uniform random token ids, random-init weights, seeded-hash reward)",
-            "impl": "ours", "clocks": clocks, "gpu_launches": launches, "e2e": e2e, "last_loss": loss,
+            "impl": "ours", "clocks": clocks, "gpu_launches": launches, "e2e": e2e, "last_loss": loss, "checks": checks,
             "phase_s_per_step": {k: v / args.steps for k, v in phase.items()},
             **({"device_phase_ms_per_step": {k: round(v["ms"] / args.steps, 3) for k, v in sorted(phases.items())}}
                if phases else {}),
@@ -291,13 +316,16 @@ def run_ours(args):
                 "seq_len": pmax + new_tokens, "micro_batch_tokens": MICRO_TOKENS,
                 "parallelism": f"rollout dp{world // rollout_tp} x tp{rollout_tp} (paged bf16 KV, CUDA-graph decode), "
                                f"train dp{world} sharded grads+optimizer, weight sync: "
-                               + ("in place (shared buffers)" if rollout_tp == 1 else "local reshard of the DP replica"),
+                               + ("in place (shared buffers)" if rollout_tp == 1 else
+                                  "local reshard of the DP replica into the TP shards; row-parallel all-reduce fused with "
+                                  "residual + RMSNorm over the symmetric heap"),
                 "tokens_counted": "prompt+response tokens per sequence, once per step",
                 "l2": "inputs larger than L2 (15 GB of weights streamed every decode step / micro-batch)",
                 "wall_s_timed_region": wall,
             },
         }
         print(json.dumps(result), flush=True)
+    worker.close()
     if world > 1:
         # Leave without tearing the communicators down: captured decode graphs still reference them, and
         # destroying a communicator in that state can block forever.  The barrier keeps ranks together

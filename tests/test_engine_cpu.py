@@ -1,5 +1,6 @@
 """CPU end-to-end checks of the inference loop against a full (non-cached) forward."""
 
+import pytest
 import torch
 
 from areno_b200.engine.config import ModelConfig
@@ -159,3 +160,21 @@ def test_sequence_evicted_for_lack_of_kv_pages_is_requeued_and_completes():
     for a, b in zip(out.logprobs, roomy.logprobs):
         assert torch.allclose(torch.tensor(a), torch.tensor(b), atol=2e-2)
     assert any(r.kept_tokens for r in tight._requests.values())     # an eviction really happened
+
+
+def test_check_token_ids_guard_reports_out_of_range_samples(monkeypatch):
+    from areno_b200.engine import inference
+
+    inference._check_token_ids([0, 5, 511], 512, "ok")
+    with pytest.raises(RuntimeError, match=r"out of vocab range \[0, 512\).*bad_max=600"):
+        inference._check_token_ids([3, 600, -2], 512, "sampled tokens")
+    # wired into collection: with the guard on, a vocabulary smaller than what the sampler can emit is caught
+    single_process_context()
+    model = DenseCausalLM(tiny_config())
+    init_weights(model, 0)
+    eng = _engine(model)
+    monkeypatch.setattr(inference, "_CHECK_TOKEN_IDS", True)
+    eng.generate([[5, 6, 7]], SamplingParams(temperature=0.0), (), 4)      # in range: passes
+    eng.vocab = 1
+    with pytest.raises(RuntimeError, match="out of vocab range"):
+        eng.generate([[5, 6, 7]], SamplingParams(temperature=0.0), (), 4)

@@ -169,3 +169,67 @@ def test_reshard_matches_checkpoint_slicing(tp, kv):
                 per = p.shape[0]
                 lo, hi = min(r * per, 512), min((r + 1) * per, 512)
                 assert torch.equal(p[: hi - lo], f[lo:hi])
+
+
+def test_split_heads_deals_query_heads_over_ranks_sharing_a_kv_head():
+    from areno_b200.models.layers import split_heads
+
+    # 28 query / 4 KV heads at tp 8: two ranks per KV head, 4 + 3 query heads, one padding head on the second
+    got = [split_heads(28, 4, 8, r) for r in range(8)]
+    assert [g[0] for g in got] == [4] * 8 and [g[3:] for g in got] == [(1, 2)] * 8
+    assert [(g[1], g[2]) for g in got] == [(0, 4), (4, 3), (7, 4), (11, 3), (14, 4), (18, 3), (21, 4), (25, 3)]
+    covered = sorted(h for g in got for h in range(g[1], g[1] + g[2]))
+    assert covered == list(range(28))
+    # even layouts are untouched
+    assert split_heads(28, 4, 4, 3) == (7, 21, 7, 1, 1)
+    assert split_heads(32, 8, 16, 5) == (2, 10, 2, 1, 2)
+
+
+def _uneven_rank(rank, world, port, ret):
+    try:
+        os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+        from areno_b200.engine.inference import SamplingParams
+        from areno_b200.parallel.context import destroy_parallel, init_parallel
+
+        init_parallel(rank, world, tp_size=1, master_port=port, backend="gloo", device=torch.device("cpu"),
+                      rollout_tp_size=4, timeout_s=120)
+        worker = _uneven_worker(dict(tp_size=1, dp_size=4, rollout_tp_size=4))
+        a = worker.rollout_model.layers[0].attn
+        assert (a.hq, a.hkv) == (2, 1) and a.qkv.q_n == (2 if rank % 2 == 0 else 1)
+        out = worker.rollout(_prompts()[rank:rank + 1], SamplingParams(temperature=0.0), (), 6, gather_tp=True)
+        ret[rank] = dict(tokens=out.tokens, lp=out.logprobs)
+        destroy_parallel()
+    except BaseException:  # noqa: BLE001
+        ret[rank] = traceback.format_exc()
+
+
+def _uneven_worker(cfg_kw):
+    from areno_b200.engine.config import EngineConfig, RuntimeConfig
+    from areno_b200.engine.worker import RankWorker
+
+    cfg = EngineConfig(model=tiny_config(num_attention_heads=6, num_key_value_heads=2), model_path="", dummy_load=True,
+                       seed=3, runtime=RuntimeConfig(eager_decode=True, max_model_len=128), max_running_seqs=8, **cfg_kw)
+    return RankWorker(cfg, "cpu")
+
+
+def test_rollout_layout_wider_than_the_query_heads_divide_matches_single_process():
+    """6 query / 2 KV heads on a 4-wide rollout layout: ranks get 2 + 1 query heads per KV group, the short ranks a
+    zero-weight padding head.  Greedy tokens and log-probs equal the single-process model; training layouts
+    still refuse the shape."""
+    from areno_b200.engine.config import EngineConfig
+    from areno_b200.engine.inference import SamplingParams
+    from areno_b200.parallel.context import single_process_context
+
+    with pytest.raises(ValueError, match="divisible by tp_size"):
+        EngineConfig(model=tiny_config(num_attention_heads=6, num_key_value_heads=2), tp_size=4, dp_size=1)
+    port = _free_port()
+    ret = mp.Manager().dict()
+    mp.spawn(_uneven_rank, args=(4, port, ret), nprocs=4, join=True)
+    for r in range(4):
+        assert isinstance(ret[r], dict), ret[r]
+    single_process_context()
+    worker = _uneven_worker({})
+    ref = worker.rollout(_prompts(), SamplingParams(temperature=0.0), (), 6)
+    assert [ret[r]["tokens"][0] for r in range(4)] == ref.tokens
+    for r in range(4):
+        assert torch.allclose(torch.tensor(ret[r]["lp"][0]), torch.tensor(ref.logprobs[r]), atol=1e-4)
