@@ -6,6 +6,7 @@ first lookup miss (``areno/api/algorithms.py:25-208`` in the reference)."""
 from __future__ import annotations
 
 import importlib
+import importlib.util
 import pkgutil
 from collections.abc import Callable
 from dataclasses import dataclass, replace as dc_replace
@@ -49,17 +50,19 @@ def register_algorithm(spec: AlgorithmSpec, *, replace: bool = False) -> None:
 
 
 def load_experimental_algorithms() -> None:
+    """Import every sub-package of ``areno_b200.experimental`` once; each registers its algorithms on import.
+    A missing or empty experimental package is not an error."""
     global _EXPERIMENTAL_LOADED
     if _EXPERIMENTAL_LOADED:
         return
     _EXPERIMENTAL_LOADED = True
-    try:
-        package = importlib.import_module("areno_b200.experimental")
-    except ModuleNotFoundError:
+    root = "areno_b200.experimental"
+    if importlib.util.find_spec(root) is None:
         return
-    for module in pkgutil.iter_modules(getattr(package, "__path__", None) or []):
-        if module.ispkg:
-            importlib.import_module(f"{package.__name__}.{module.name}")
+    search_path = list(getattr(importlib.import_module(root), "__path__", ()))
+    for info in pkgutil.iter_modules(search_path):
+        if info.ispkg:
+            importlib.import_module(root + "." + info.name)
 
 
 def get_algorithm(name: str) -> AlgorithmSpec:

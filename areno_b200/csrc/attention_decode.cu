@@ -7,8 +7,9 @@
 //
 // Decode: one CTA per (sequence, kv head, split).  All q heads of the GQA group share each K/V
 // tile (padded to the 16-row MMA tile), so the cache is read once per group rather than once
-// per q head.  Pages stream through a 3-stage cp.async pipeline; fp8 pages are dequantised to
-// bf16 in shared memory before the MMAs.  Split partials are merged by a second kernel.
+// per q head.  Pages stream through a 3-stage cp.async pipeline; fp8 pages are expanded to fp16 in
+// shared memory (e4m3 -> fp16 is exact: one conversion and one fp16 multiply by the token's scale per
+// pair) and the MMAs of that variant run on fp16 operands.  Split partials are merged by a second kernel.
 // Everything is driven by device-side `seq_lens` / `block_table`, so the launch shape is static
 // and the kernel is CUDA-graph friendly.
 //
@@ -217,6 +218,16 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const void* __restrict_
     const int r = idx / CH, ch = idx % CH;
     uint4 val = make_uint4(0, 0, 0, 0);
     if (r < rows_valid) val = *reinterpret_cast<const uint4*>(q + (long long)b * q_stride + (long long)(head0 + r) * D + ch * 8);
+    if constexpr (FP8) {
+      // the fp8 cache is expanded to fp16 (exact), so q joins it in fp16 and the MMAs run on fp16 operands
+      uint32_t u[4] = {val.x, val.y, val.z, val.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack_bf16x2(u[j]);
+        u[j] = pack_f16x2(f.x, f.y);
+      }
+      val = make_uint4(u[0], u[1], u[2], u[3]);
+    }
     *reinterpret_cast<uint4*>(sQ + swz<CH>(r, ch)) = val;
   }
 
@@ -271,19 +282,17 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const void* __restrict_
         const int r = idx / CH, ch = idx % CH;
         const uint2 rk = *reinterpret_cast<const uint2*>(sb + r * D + ch * 8);
         const uint2 rv = *reinterpret_cast<const uint2*>(sb + SM::kRaw + r * D + ch * 8);
-        const float sk = ks[r], sv = vs[r];
+        // e4m3 -> fp16 is exact and one instruction per pair; the per-token scale is applied in fp16
+        const uint32_t sk = pack_f16x2(ks[r], ks[r]), sv = pack_f16x2(vs[r], vs[r]);
         uint32_t ok[4], ov[4];
-        const __nv_fp8x2_storage_t* pk = reinterpret_cast<const __nv_fp8x2_storage_t*>(&rk);
-        const __nv_fp8x2_storage_t* pv = reinterpret_cast<const __nv_fp8x2_storage_t*>(&rv);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const __half2_raw hk = __nv_cvt_fp8x2_to_halfraw2(pk[j], __NV_E4M3);
-          const __half2_raw hv = __nv_cvt_fp8x2_to_halfraw2(pv[j], __NV_E4M3);
-          const float2 fk = __half22float2(*reinterpret_cast<const __half2*>(&hk));
-          const float2 fv = __half22float2(*reinterpret_cast<const __half2*>(&hv));
-          ok[j] = pack_bf16x2(fk.x * sk, fk.y * sk);
-          ov[j] = pack_bf16x2(fv.x * sv, fv.y * sv);
-        }
+        ok[0] = hmul2_u32(cvt_e4m3x2_f16x2(rk.x), sk);
+        ok[1] = hmul2_u32(cvt_e4m3x2_f16x2(rk.x >> 16), sk);
+        ok[2] = hmul2_u32(cvt_e4m3x2_f16x2(rk.y), sk);
+        ok[3] = hmul2_u32(cvt_e4m3x2_f16x2(rk.y >> 16), sk);
+        ov[0] = hmul2_u32(cvt_e4m3x2_f16x2(rv.x), sv);
+        ov[1] = hmul2_u32(cvt_e4m3x2_f16x2(rv.x >> 16), sv);
+        ov[2] = hmul2_u32(cvt_e4m3x2_f16x2(rv.y), sv);
+        ov[3] = hmul2_u32(cvt_e4m3x2_f16x2(rv.y >> 16), sv);
         *reinterpret_cast<uint4*>(deqK + swz<CH>(r, ch)) = make_uint4(ok[0], ok[1], ok[2], ok[3]);
         *reinterpret_cast<uint4*>(deqV + swz<CH>(r, ch)) = make_uint4(ov[0], ov[1], ov[2], ov[3]);
       }
@@ -304,8 +313,13 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const void* __restrict_
         uint32_t a[4], bb[4];
         ldsm_a<CH>(a, sQ, 0, ks * 2, lane);
         ldsm_b_nt<CH>(bb, cK, warp * 16, ks * 2, lane);
-        mma_bf16(s[0], a, bb[0], bb[1]);
-        mma_bf16(s[1], a, bb[2], bb[3]);
+        if constexpr (FP8) {
+          mma_f16(s[0], a, bb[0], bb[1]);
+          mma_f16(s[1], a, bb[2], bb[3]);
+        } else {
+          mma_bf16(s[0], a, bb[0], bb[1]);
+          mma_bf16(s[1], a, bb[2], bb[3]);
+        }
       }
       float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -336,8 +350,8 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const void* __restrict_
         const float p3 = exp2f((s[nt][3] - m_use[1]) * scale_log2);
         rs[0] += p0 + p1;
         rs[1] += p2 + p3;
-        pf[nt * 2 + 0] = pack_bf16x2(p0, p1);
-        pf[nt * 2 + 1] = pack_bf16x2(p2, p3);
+        pf[nt * 2 + 0] = FP8 ? pack_f16x2(p0, p1) : pack_bf16x2(p0, p1);
+        pf[nt * 2 + 1] = FP8 ? pack_f16x2(p2, p3) : pack_bf16x2(p2, p3);
       }
       l_run[0] = l_run[0] * corr[0] + rs[0];
       l_run[1] = l_run[1] * corr[1] + rs[1];
@@ -350,8 +364,13 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const void* __restrict_
       for (int dt = 0; dt < D / 16; ++dt) {
         uint32_t bb[4];
         ldsm_b_t<CH>(bb, cV, warp * 16, dt * 2, lane);
-        mma_bf16(o_acc[2 * dt], pf, bb[0], bb[1]);
-        mma_bf16(o_acc[2 * dt + 1], pf, bb[2], bb[3]);
+        if constexpr (FP8) {
+          mma_f16(o_acc[2 * dt], pf, bb[0], bb[1]);
+          mma_f16(o_acc[2 * dt + 1], pf, bb[2], bb[3]);
+        } else {
+          mma_bf16(o_acc[2 * dt], pf, bb[0], bb[1]);
+          mma_bf16(o_acc[2 * dt + 1], pf, bb[2], bb[3]);
+        }
       }
     }
     __syncthreads();

@@ -70,6 +70,15 @@ struct GemmParams {
   // and a small kernel folds them with the requested epilogue.
   int tail_first, tail_tiles, tail_splits, tail_kb;
   float* tail_ws;
+  // Log-sum-exp epilogue (epi 6; LM head): nothing is stored for the [M, N] product.  Every row of a tile is
+  // reduced on the fly to (max, sum exp(x - max), sum exp(x - max) x, x[target]) over the tile's columns below
+  // `lse_valid`, with x rounded to bf16 first (and soft-capped when lse_softcap > 0), and written to
+  // lse_out[(n_tile * M + row) * 4 ...]; a small kernel merges the tiles of a row.
+  const long long* lse_targets;   // global token id per row
+  long long lse_vocab_start;      // id of column 0
+  int lse_valid;                  // columns >= lse_valid are padding
+  float lse_softcap;
+  float* lse_out;
 };
 
 struct WorkItem {
@@ -373,6 +382,43 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           tmem_ld_wait();
           store_row_f32(tw + c, r, 32, false);
         }
+      } else if (p.epi == 6) {
+        const long long tgt = row < p.M ? p.lse_targets[row] - p.lse_vocab_start : -1;
+        float m = -INFINITY, s = 0.f, sx = 0.f, tg = 0.f;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          const int col0 = n0 + c;
+          const int ncols = min(32, p.lse_valid - col0);
+          if (ncols <= 0) break;      // the same for the whole warp
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + c, r);
+          tmem_ld_wait();
+          float x[32];
+          float cmax = -INFINITY;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float v = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[j])));
+            if (p.lse_softcap > 0.f) v = __bfloat162float(__float2bfloat16_rn(p.lse_softcap * tanhf(v / p.lse_softcap)));
+            x[j] = j < ncols ? v : -INFINITY;
+            cmax = fmaxf(cmax, x[j]);
+            if (tgt == (long long)(col0 + j) && j < ncols) tg = v;
+          }
+          const float mn = fmaxf(m, cmax);
+          const float rescale = m == -INFINITY ? 0.f : __expf(m - mn);
+          s *= rescale;
+          sx *= rescale;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (j < ncols) {
+              const float e = __expf(x[j] - mn);
+              s += e;
+              sx += e * x[j];
+            }
+          }
+          m = mn;
+        }
+        if (row < p.M)
+          *reinterpret_cast<float4*>(p.lse_out + ((size_t)(n0 / BN) * p.M + row) * 4) = make_float4(m, s, sx, tg);
       } else if (p.epi >= 4) {
         if constexpr (BN == 256) {
 #pragma unroll 1
@@ -606,6 +652,46 @@ splitk_reduce_kernel(const float* __restrict__ ws, __nv_bfloat16* __restrict__ o
   }
 }
 
+// Merge the per-tile log-sum-exp statistics of every row (see GemmParams::lse_*): one warp per row.
+__global__ void __launch_bounds__(256)
+lse_combine_kernel(const float* __restrict__ part, int tiles_n, int M, float* __restrict__ out_max,
+                   float* __restrict__ out_sum, float* __restrict__ out_sumx, float* __restrict__ out_tgt) {
+  pdl_wait();
+  const int row = (int)((blockIdx.x * (unsigned)blockDim.x + threadIdx.x) >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= M) return;
+  float m = -INFINITY, s = 0.f, sx = 0.f, tg = 0.f;
+  for (int t = lane; t < tiles_n; t += 32) {
+    const float4 v = __ldcg(reinterpret_cast<const float4*>(part + ((size_t)t * M + row) * 4));
+    tg += v.w;
+    if (v.x == -INFINITY) continue;
+    const float mn = fmaxf(m, v.x);
+    const float a = m == -INFINITY ? 0.f : __expf(m - mn), b = __expf(v.x - mn);
+    s = s * a + v.y * b;
+    sx = sx * a + v.z * b;
+    m = mn;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float om = __shfl_xor_sync(0xffffffffu, m, o), os = __shfl_xor_sync(0xffffffffu, s, o);
+    const float osx = __shfl_xor_sync(0xffffffffu, sx, o);
+    tg += __shfl_xor_sync(0xffffffffu, tg, o);
+    const float mn = fmaxf(m, om);
+    if (mn != -INFINITY) {
+      const float a = m == -INFINITY ? 0.f : __expf(m - mn), b = om == -INFINITY ? 0.f : __expf(om - mn);
+      s = s * a + os * b;
+      sx = sx * a + osx * b;
+    }
+    m = mn;
+  }
+  if (lane == 0) {
+    out_max[row] = m;
+    out_sum[row] = s;
+    out_sumx[row] = sx;
+    out_tgt[row] = tg;
+  }
+}
+
 }  // namespace areno
 
 using namespace areno;
@@ -625,12 +711,28 @@ struct GroupArgs {
   int num_groups;
 };
 
+struct LseArgs {
+  const long long* targets;
+  long long vocab_start;
+  int valid;
+  float softcap;
+  float* out;
+};
+
 static int gemm_bf16_impl(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
                           long long lda, long long ldb, long long ldc, int a_mn, int b_mn, int epi, int bn,
                           void* workspace, long long workspace_bytes, int* status, cudaStream_t stream,
                           void* const* extra, int n_extra, const GroupArgs* group = nullptr, int b_groups = 1,
-                          int* splits_out = nullptr, long long gate_rows = 0) {
+                          int* splits_out = nullptr, long long gate_rows = 0, const LseArgs* lse = nullptr) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((epi == 6) != (lse != nullptr)) return -3;
+  if (epi == 6) {
+    if (a_mn || b_mn || group != nullptr || n_extra != 0 || lse->out == nullptr || lse->targets == nullptr ||
+        lse->valid < 1 || lse->valid > N)
+      return -3;
+    bn = 256;
+    workspace = nullptr;
+  }
   if (epi >= 4) {  // gated activation: merged weight, 256-wide tiles only
     if (a_mn || b_mn || group != nullptr || n_extra != 0 || gate_rows <= 0 || N != 2 * gate_rows || (gate_rows % 8) != 0)
       return -3;
@@ -644,7 +746,7 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, const void* bia
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
       (reinterpret_cast<uintptr_t>(C) & 15))
     return -3;
-  if ((epi <= 1 || epi >= 4) ? (ldc % 8) != 0 : (ldc % 4) != 0) return -3;
+  if (epi != 6 && ((epi <= 1 || epi >= 4) ? (ldc % 8) != 0 : (ldc % 4) != 0)) return -3;
   {
     // cuTensorMapEncodeTiled needs a current driver context; threads that have not yet made a
     // runtime call (e.g. autograd workers) get the primary context bound here.
@@ -685,6 +787,11 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, const void* bia
   p.gate_rows = epi >= 4 ? gate_rows : 0;
   p.tail_first = p.tail_tiles = p.tail_splits = p.tail_kb = 0;
   p.tail_ws = nullptr;
+  p.lse_targets = lse != nullptr ? lse->targets : nullptr;
+  p.lse_vocab_start = lse != nullptr ? lse->vocab_start : 0;
+  p.lse_valid = lse != nullptr ? lse->valid : 0;
+  p.lse_softcap = lse != nullptr ? lse->softcap : 0.f;
+  p.lse_out = lse != nullptr ? lse->out : nullptr;
   p.group_mode = 0;
   p.tile_expert = nullptr;
   p.expert_rows = nullptr;
@@ -838,4 +945,29 @@ extern "C" int areno_gemm_bf16_partials(const void* A, const void* B, void* C, i
   *splits_out = 1;
   return gemm_bf16_impl(A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0, 0, 0, 0, workspace, workspace_bytes, status, stream,
                         nullptr, 0, nullptr, 1, splits_out);
+}
+
+// LM head fused with the per-row log-sum-exp statistics of the selected-token log-prob (and entropy): the
+// [M, N] logits are never written.  A: hidden [M, K], B: head weight [N, K] (row n = token vocab_start + n),
+// columns >= valid are padding.  Logits are rounded to bf16 (and soft-capped when softcap > 0) before they are
+// reduced, exactly as if they had been stored and read back.  partials: fp32 scratch of
+// areno_gemm_lse_partials_elems(M, N) elements.  Outputs (fp32 [M] each): row max, sum exp(x - max),
+// sum exp(x - max) x, x[target] (0 when the target is outside [vocab_start, vocab_start + valid)).
+extern "C" long long areno_gemm_lse_partials_elems(int M, int N) { return (long long)((N + 255) / 256) * M * 4; }
+
+extern "C" int areno_gemm_bf16_lse(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb,
+                                   const long long* targets, long long vocab_start, int valid, float softcap,
+                                   float* partials, float* out_max, float* out_sum, float* out_sumx, float* out_tgt,
+                                   int* status, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (partials == nullptr || out_max == nullptr || out_sum == nullptr || out_sumx == nullptr || out_tgt == nullptr)
+    return -3;
+  LseArgs lse{targets, vocab_start, valid, softcap, partials};
+  const int rc = gemm_bf16_impl(A, B, partials, nullptr, M, N, K, lda, ldb, 8, 0, 0, 6, 256, nullptr, 0, status, stream,
+                                nullptr, 0, nullptr, 1, nullptr, 0, &lse);
+  if (rc != 0) return rc;
+  const int tiles_n = (N + 255) / 256;
+  const long long threads = (long long)M * 32;
+  return (int)launch_pdl(lse_combine_kernel, dim3((unsigned)((threads + 255) / 256)), dim3(256), 0, stream,
+                         (const float*)partials, tiles_n, M, out_max, out_sum, out_sumx, out_tgt);
 }

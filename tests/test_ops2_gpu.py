@@ -314,3 +314,78 @@ def test_fold_rope_append_matches_separate_kernels(hq, hkv, d, bias, norm, rot, 
     for ca, cb in zip(cache_a, cache_b):
         if ca is not None:
             assert _rel_err(cb.float(), ca.float()) < 5e-3
+
+
+@pytest.mark.parametrize("rows,k,n,valid,softcap", [(300, 512, 1000, 1000, 0.0), (129, 256, 520, 515, 0.0),
+                                                    (64, 384, 4104, 4100, 30.0), (5, 128, 256, 256, 0.0)])
+def test_lm_head_statistics_from_the_gemm_epilogue(rows, k, n, valid, softcap):
+    """Selected-token log-prob and entropy straight from the LM-head GEMM epilogue (no logits tensor) against
+    fp32 log_softmax().gather() of the bf16-rounded logits; also as two vocabulary shards that combine."""
+    torch.manual_seed(3)
+    h = torch.randn(rows, k, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(n, k, device="cuda") * 0.2).to(torch.bfloat16)
+    t = torch.randint(0, valid, (rows,), device="cuda")
+    z = (h.float() @ w.float().t()).to(torch.bfloat16).float()[:, :valid]
+    if softcap:
+        z = (softcap * torch.tanh(z / softcap)).to(torch.bfloat16).float()
+    logp = torch.log_softmax(z, -1)
+    lp_ref = logp.gather(-1, t[:, None]).squeeze(-1)
+    ent_ref = -(logp.exp() * logp).sum(-1)
+    st = logprob.fused_head_stats(h, w, t, 0, valid, softcap)
+    lp, lse, ex = logprob._combine(st, None)
+    assert _rel_err(lp, lp_ref) < 2e-3
+    assert _rel_err(lse - ex, ent_ref) < 2e-3
+    if valid == n and n % 16 == 0:
+        half = n // 2
+        parts = [logprob.fused_head_stats(h, w[i * half:(i + 1) * half].contiguous(), t, i * half, half, softcap)
+                 for i in range(2)]
+        m = torch.stack([p[0] for p in parts]).max(0).values
+        ssum = sum(p[1] * torch.exp(p[0] - m) for p in parts)
+        tgt = sum(p[3] for p in parts)
+        assert _rel_err(tgt - (m + torch.log(ssum)), lp_ref) < 2e-3
+    _lib.check_status()
+
+
+@pytest.mark.parametrize("softcap", [0.0, 20.0])
+def test_lm_head_logprobs_fused_forward_and_gradients(softcap, monkeypatch):
+    """``lm_head_logprobs`` (forward from the GEMM epilogue when no logits are kept, backward through recomputed
+    logits, soft-cap included) against PyTorch autograd on fp32."""
+    from areno_b200.engine.logprobs import lm_head_logprobs
+    from areno_b200.models.layers import VocabParallelLMHead
+    from areno_b200.parallel.context import single_process_context
+
+    single_process_context("cuda")
+    torch.manual_seed(4)
+    rows, k, vocab = 200, 256, 1003
+    head = VocabParallelLMHead(vocab, k, torch.bfloat16, "cuda")
+    with torch.no_grad():
+        head.weight.copy_((torch.randn_like(head.weight.float()) * 0.3).to(torch.bfloat16))
+    base = torch.randn(rows, k, device="cuda").to(torch.bfloat16)
+    t = torch.randint(0, vocab, (rows,), device="cuda")
+    g1, g2 = torch.randn(rows, device="cuda"), 0.1 * torch.randn(rows, device="cuda")
+
+    def reference():
+        x = base.float().clone().requires_grad_()
+        w = head.weight.detach().float().clone().requires_grad_()
+        z = (x @ w.t())[:, :vocab]
+        if softcap:
+            z = softcap * torch.tanh(z / softcap)
+        logp = torch.log_softmax(z, -1)
+        lp = logp.gather(-1, t[:, None]).squeeze(-1)
+        ent = -(logp.exp() * logp).sum(-1)
+        gx, gw = torch.autograd.grad([lp, ent], [x, w], [g1, g2])
+        return lp.detach(), ent.detach(), gx, gw
+
+    lp_r, ent_r, gx_r, gw_r = reference()
+    with torch.no_grad():          # scoring path: statistics from the epilogue
+        lp0, ent0 = lm_head_logprobs(head, base, t, chunk=128, need_entropy=True, softcap=softcap or None)
+    assert _rel_err(lp0, lp_r) < 5e-3 and _rel_err(ent0, ent_r) < 5e-3
+    for keep in ("0", "1"):        # training path with and without the logits kept from forward
+        monkeypatch.setenv("ARENO_LOGPROB_KEEP_LOGITS", keep)
+        x = base.clone().requires_grad_()
+        head.weight.grad = None
+        lp, ent = lm_head_logprobs(head, x, t, chunk=128, need_entropy=True, softcap=softcap or None)
+        assert _rel_err(lp, lp_r) < 5e-3 and _rel_err(ent, ent_r) < 5e-3
+        gx, gw = torch.autograd.grad([lp, ent], [x, head.weight], [g1, g2])
+        assert _rel_err(gx, gx_r) < 3e-2 and _rel_err(gw, gw_r) < 3e-2
+    _lib.check_status()
