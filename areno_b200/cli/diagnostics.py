@@ -108,10 +108,16 @@ def _version_tuple(text: str | None) -> tuple[int, ...]:
         return ()
     parts = []
     for piece in text.split("."):
-        digits = "".join(ch for ch in piece if ch.isdigit())
+        digits = ""
+        for ch in piece:            # leading digits only: "8rc1" is 8, not 81
+            if not ch.isdigit():
+                break
+            digits += ch
         if not digits:
             break
         parts.append(int(digits))
+        if len(digits) != len(piece):
+            break
     return tuple(parts)
 
 

@@ -7,7 +7,8 @@
 // layout, mapped by every peer and, when the fabric supports it, bound to an NVLink multicast object:
 //
 //   flags   : uint32 [64]                      [0] call counter, [1] finished-CTA counter,
-//                                              [8 + r] "partial ready" of rank r, [16 + r] "rows published" of rank r
+//                                              [8 + r] "partial ready" of rank r, [16 + r] "rows published" of rank r,
+//                                              [24 + r] row count of rank r's current call (cross-checked)
 //   partial : bf16 [2 slots][max_rows][H]      written locally by the row-parallel GEMM of this rank
 //   h_out   : bf16 [2 slots][max_rows][H]      new residual stream, written by the owner of each row
 //   y_out   : bf16 [2 slots][max_rows][H]      normalised rows, written by the owner of each row
@@ -32,8 +33,9 @@
 // only after that peer has sent its "partial ready" of call n + 2, which it does after all of its own
 // kernels that read slot s of call n have completed.
 //
-// Every wait is bounded by wall time (wait_ns, measured with %globaltimer).  A CTA whose wait runs out
-// records {code, block, peer, call} in the status words, publishes nothing, and the kernel still
+// Every wait is bounded by wall time (wait_ns, measured with %globaltimer).  A CTA whose wait runs out (status
+// code 7 or 9), or that finds a peer running the same call with another row count (code 10: the ranks' control
+// flow has diverged), records {code, block, peer, call} in the status words, publishes nothing, and the kernel still
 // counts itself finished, so a lost peer becomes a reported error and never a hung GPU or a sum of
 // half-written data.  Nothing here uses a TMA load, and nothing uses cluster multicast.
 #include <cuda_bf16.h>
@@ -47,7 +49,7 @@ namespace areno {
 
 constexpr int kMaxTp = 8;
 constexpr int kFlagWords = 64;
-constexpr int kFlagCall = 0, kFlagDone = 1, kFlagReady = 8, kFlagPublished = 16;
+constexpr int kFlagCall = 0, kFlagDone = 1, kFlagReady = 8, kFlagPublished = 16, kFlagRows = 24;
 
 struct TpCtx {
   int tp, rank;
@@ -155,9 +157,18 @@ tp_reduce_norm_kernel(TpCtx c, long long slot_off, const __nv_bfloat16* __restri
   // ---- 1. partial ready: announce (first CTA) and wait for every peer (every CTA)
   if (threadIdx.x < c.tp && (int)threadIdx.x != c.rank) {
     const int p = threadIdx.x;
-    if (blockIdx.x == 0) st_release_sys(c.flags[p] + kFlagReady + c.rank, call);
+    if (blockIdx.x == 0) {
+      // the row count travels with the announcement: ranks whose control flow has diverged (different shapes for
+      // the same call) are caught here instead of reducing unrelated buffers
+      *reinterpret_cast<volatile uint32_t*>(c.flags[p] + kFlagRows + c.rank) = (uint32_t)rows;
+      st_release_sys(c.flags[p] + kFlagReady + c.rank, call);
+    }
     if (!wait_flag(my_flags + kFlagReady + p, call, c.wait_ns)) {
       report_peer_timeout(c.status, 7, p, call);  // 7: a peer's partial never became ready
+      sh_ok = 0;
+    } else if (ld_acquire_sys(my_flags + kFlagReady + p) == call &&
+               *reinterpret_cast<volatile uint32_t*>(my_flags + kFlagRows + p) != (uint32_t)rows) {
+      report_peer_timeout(c.status, 10, p, call);  // 10: the peer is running this call with another row count
       sh_ok = 0;
     }
   }

@@ -136,7 +136,8 @@ class InferenceEngine:
         self.max_pages = (max_model_len + PAGE - 1) // PAGE
         self.max_prefill_tokens = max_prefill_tokens
         self.kv_fp8 = kv_fp8
-        self.eager = eager or not self.cuda
+        # the checked mode validates indices on the host before every launch, which a captured graph cannot do
+        self.eager = eager or not self.cuda or klib.BOUNDS_CHECK
         self.seed = seed
         self.calls = 0
         self.max_out = max_new_cap
@@ -155,6 +156,7 @@ class InferenceEngine:
         self.step_count = 0
         self.decode_tokens = 0
         self._peer_waits = False
+        self._lockstep = False
 
     # ------------------------------------------------------------------ state
     def _alloc_state(self):
@@ -230,6 +232,12 @@ class InferenceEngine:
         from ..parallel.symm import get_tp_comm
 
         self._peer_waits = self.cuda and get_tp_comm(get_context()) is not None
+        # Ranks of a tensor-parallel group run the same kernels step for step (each decode step contains collectives),
+        # so they must take every scheduling decision at the same loop iteration.  Completions are observed through
+        # asynchronous snapshots; letting each rank act on a snapshot "when it has arrived" would let one rank launch
+        # a step more than its peer.  In lockstep mode the snapshot taken after step t is consumed exactly
+        # ``_LOCKSTEP_LAG`` steps later (waiting for it if need be), which is the same iteration on every rank.
+        self._lockstep = get_context().tp_size > 1
 
     def add_request(self, prompt: list[int], max_new_tokens: int | None = None, tag=None,
                     stream: int | None = None) -> int:
@@ -570,13 +578,16 @@ class InferenceEngine:
             self._snap_ring = [torch.empty((3, self.max_slots), dtype=torch.int32, pin_memory=True) for _ in range(8)]
             self._snap_events = [torch.cuda.Event() for _ in range(8)]
             self._snap_next = 0
-        while len(self._snapshots) >= 6:
+        while len(self._snapshots) >= 6 and not self._lockstep:
             # bound how far the device may run ahead of the host; a newer snapshot supersedes older ones
             self._snapshots[0][1].synchronize()
             if len(self._snapshots) >= 7:
                 self._snapshots.pop(0)
             else:
                 break
+        if self._lockstep and len(self._snapshots) >= len(self._snap_ring):
+            # cannot happen while every step consumes what exceeds the lag; a ring slot must never be reused while queued
+            raise RuntimeError("snapshot ring exhausted in lockstep mode")
         i = self._snap_next
         self._snap_next = (i + 1) % len(self._snap_ring)
         host = self._snap_ring[i]
@@ -586,6 +597,8 @@ class InferenceEngine:
         self._snapshots.append((host, ev))
 
     def _poll(self, block: bool, drain: bool = False) -> list[_Request]:
+        if self._lockstep:
+            return self._poll_lockstep(block, drain)
         done: list[_Request] = []
         latest = None
         while self._snapshots:
@@ -600,6 +613,29 @@ class InferenceEngine:
                 block = False
         if latest is None:
             return done
+        return done + self._collect(latest)
+
+    _LOCKSTEP_LAG = 4
+
+    def _poll_lockstep(self, block: bool, drain: bool) -> list[_Request]:
+        """Consume snapshots strictly in order and at a fixed distance behind the launches: non-blocking calls take
+        the oldest snapshot only once more than ``_LOCKSTEP_LAG`` are queued, ``block`` takes exactly the oldest one,
+        ``drain`` takes them all.  Which snapshot is looked at therefore depends on the iteration count alone."""
+        done: list[_Request] = []
+        while self._snapshots:
+            if not (drain or block or len(self._snapshots) > self._LOCKSTEP_LAG):
+                break
+            host, ev = self._snapshots.pop(0)
+            if ev is not None:
+                ev.synchronize()
+            done += self._collect(host)
+            if block and not drain:
+                break
+        return done
+
+    def _collect(self, latest) -> list[_Request]:
+        """Hand out the sequences that ``latest`` (a host copy of the status rows) shows as finished."""
+        done: list[_Request] = []
         fin, gen, uid = latest[0], latest[1], latest[2]
         finished_slots = []
         for slot in range(self.max_slots):

@@ -10,6 +10,7 @@ PyTorch for CUDA tensors.
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 from typing import Any
 
@@ -129,6 +130,45 @@ def call(name: str, *args) -> int:
     if rc != 0:
         raise RuntimeError(f"{name} failed with code {rc}")
     return rc
+
+
+# Debug mode ``ARENO_BOUNDS_CHECK=1``: every data-dependent index a kernel is about to use (cache slots, page ids,
+# token ids, targets, expert ids, row maps) is range-checked on the host BEFORE the launch, and the wrappers
+# verify canary words that they place behind their scratch buffers after it.  A violation raises here, with the
+# name of the operand, instead of reaching the GPU as an out-of-range access.  Costs a device synchronisation per
+# checked operand, so it is for tests and for chasing a fault, not for production runs.
+BOUNDS_CHECK = os.environ.get("ARENO_BOUNDS_CHECK", "0").lower() in {"1", "true", "yes", "on"}
+CANARY = 0x5AFEC0DE
+
+
+def check_index(name: str, index: torch.Tensor | None, limit: int, *, low: int = 0, enabled: bool | None = None) -> None:
+    """Raise ``IndexError`` unless every element of ``index`` lies in ``[low, limit)`` (``low=-1`` admits the
+    "skip" marker used by slot mappings and row maps).  A no-op unless the checked mode is on."""
+    if not (BOUNDS_CHECK if enabled is None else enabled) or index is None or index.numel() == 0:
+        return
+    lo, hi = int(index.min()), int(index.max())
+    if lo < low or hi >= limit:
+        bad = int(((index < low) | (index >= limit)).sum())
+        raise IndexError(f"{name}: {bad} of {index.numel()} indices outside [{low}, {limit}) (min {lo}, max {hi})")
+
+
+def with_canary(nbytes: int, device) -> torch.Tensor:
+    """uint8 scratch of ``nbytes`` followed by a 16-byte canary (checked mode); plain scratch otherwise."""
+    if not BOUNDS_CHECK:
+        return torch.empty(nbytes, dtype=torch.uint8, device=device)
+    padded = (nbytes + 15) // 16 * 16
+    buf = torch.empty(padded + 16, dtype=torch.uint8, device=device)
+    buf[padded:].view(torch.int32).fill_(CANARY if CANARY < 2**31 else CANARY - 2**32)
+    return buf
+
+
+def check_canary(name: str, buf: torch.Tensor) -> None:
+    if not BOUNDS_CHECK or buf.numel() < 16:
+        return
+    tail = buf[-16:].view(torch.int32)
+    want = CANARY if CANARY < 2**31 else CANARY - 2**32
+    if not bool((tail == want).all()):
+        raise RuntimeError(f"{name}: a kernel wrote past the end of its scratch buffer (canary overwritten)")
 
 
 def ptr(t: torch.Tensor | None):

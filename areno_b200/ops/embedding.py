@@ -31,6 +31,7 @@ class _Embedding(torch.autograd.Function):
             flat = flat.to(torch.int64)
         flat = flat.contiguous()
         H = table.shape[1]
+        _lib.check_index("embedding ids", flat, 1 << 31)      # negative ids are never valid; the shard test covers the rest
         out = torch.empty((flat.numel(), H), dtype=table.dtype, device=table.device)
         _lib.call("areno_embedding_fwd", flat.data_ptr(), table.data_ptr(), out.data_ptr(), flat.numel(), H,
                   vocab_start, vocab_start + table.shape[0], float(scale), _lib.stream())
@@ -71,6 +72,7 @@ def embedding(ids, table, vocab_start: int = 0, scale: float = 1.0, out: torch.T
             flat = flat.to(torch.int64)
         flat = flat.contiguous()
         assert out.is_contiguous() and out.shape == (flat.numel(), table.shape[1]) and out.dtype == table.dtype
+        _lib.check_index("embedding ids", flat, 1 << 31)
         _lib.call("areno_embedding_fwd", flat.data_ptr(), table.data_ptr(), out.data_ptr(), flat.numel(), table.shape[1],
                   vocab_start, vocab_start + table.shape[0], float(scale), _lib.stream())
         return out

@@ -106,6 +106,7 @@ def gemm(
 
 
 _WORKSPACES: dict[int, torch.Tensor] = {}
+_RETIRED: list[torch.Tensor] = []     # outgrown workspaces, kept alive for graphs captured while they were current
 
 
 @dataclass
@@ -163,10 +164,19 @@ def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
     """
     idx = device.index if device.index is not None else torch.cuda.current_device()
     ws = _WORKSPACES.get(idx)
-    if ws is None or ws.numel() < nbytes:
-        ws = torch.empty(max(nbytes, 32 << 20), dtype=torch.uint8, device=torch.device("cuda", idx))
+    if ws is not None:
+        _lib.check_canary("GEMM split-K workspace", ws)      # checked mode: did the previous user stay inside it?
+    if ws is None or _usable(ws) < nbytes:
+        if ws is not None:
+            _RETIRED.append(ws)     # a captured CUDA graph may still point at it: never hand it back to the allocator
+        ws = _lib.with_canary(max(nbytes, 32 << 20), torch.device("cuda", idx))
         _WORKSPACES[idx] = ws
-    return ws
+    return ws[: _usable(ws)] if _lib.BOUNDS_CHECK else ws
+
+
+def _usable(ws: torch.Tensor) -> int:
+    """Bytes of a workspace in front of its canary (checked mode) or all of it."""
+    return ws.numel() - 16 if _lib.BOUNDS_CHECK else ws.numel()
 
 
 class _Linear(torch.autograd.Function):

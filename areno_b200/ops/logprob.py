@@ -43,6 +43,7 @@ def _stats(logits, targets, vocab_start):
     rows, v = logits.shape
     dev = logits.device
     out = torch.empty((4, rows), dtype=torch.float32, device=dev)
+    _lib.check_index("logprob targets", targets, 1 << 31)
     _lib.call(
         "areno_logprob_stats", logits.data_ptr(), int(logits.dtype == torch.bfloat16), logits.stride(0), rows, v,
         targets.data_ptr(), vocab_start, out[0].data_ptr(), out[1].data_ptr(), out[2].data_ptr(), out[3].data_ptr(),

@@ -134,6 +134,11 @@ def align(ids: torch.Tensor, e_lo: int, e_count: int) -> MoePlan:
     cnt = torch.empty(e_count, dtype=torch.int32, device=dev)
     _lib.call("areno_moe_align", flat.data_ptr(), routes, e_lo, e_count, max_rows, er.data_ptr(), te.data_ptr(),
               rr.data_ptr(), ro.data_ptr(), cnt.data_ptr(), _lib.stream())
+    if _lib.BOUNDS_CHECK:     # the plan drives every later gather / scatter and the grouped GEMM: validate it once here
+        _lib.check_index("moe plan row_route", rr, routes, low=-1)
+        _lib.check_index("moe plan route_row", ro, max_rows, low=-1)
+        _lib.check_index("moe plan tile_expert", te, e_count, low=-1)
+        _lib.check_index("moe plan expert offsets", er[0::2] + er[1::2], max_rows + 1)
     return MoePlan(t, k, e_count, max_rows, er, te, rr, ro, cnt)
 
 

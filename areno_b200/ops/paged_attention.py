@@ -71,6 +71,7 @@ def rope_append_kv(qkv, positions, slot_mapping, k_cache, v_cache, k_scale, v_sc
         positions = positions.to(torch.int32)
     if slot_mapping.dtype != torch.int32:
         slot_mapping = slot_mapping.to(torch.int32)
+    _lib.check_index("rope_append_kv slot_mapping", slot_mapping, k_cache.shape[0] * PAGE, low=-1)
     _lib.call(
         "areno_rope_append_kv", qkv.data_ptr(), positions.data_ptr(), slot_mapping.data_ptr(), _lib.ptr(inv_freq),
         k_cache.data_ptr(), v_cache.data_ptr(), _lib.ptr(k_scale), _lib.ptr(v_scale), qkv.shape[0], hq, hkv, d, rot,
@@ -100,6 +101,7 @@ def fold_rope_append_kv(part, bias, positions, slot_mapping, k_cache, v_cache, k
     if slot_mapping.dtype != torch.int32:
         slot_mapping = slot_mapping.to(torch.int32)
     wf32 = int(q_norm_w is not None and q_norm_w.dtype == torch.float32)
+    _lib.check_index("fold_rope_append_kv slot_mapping", slot_mapping, k_cache.shape[0] * PAGE, low=-1)
     _lib.call("areno_fold_rope_append_kv", part.ws.data_ptr(), part.splits, t * n, _lib.ptr(bias), qkv.data_ptr(),
               positions.data_ptr(), slot_mapping.data_ptr(), _lib.ptr(inv_freq), k_cache.data_ptr(), v_cache.data_ptr(),
               _lib.ptr(k_scale), _lib.ptr(v_scale), t, hq, hkv, d, rot, float(theta), int(interleaved), PAGE,
@@ -173,6 +175,11 @@ def paged_decode(q, k_cache, v_cache, k_scale, v_scale, block_table, seq_lens, s
                       torch.empty((b, hq, nsplit, 2), dtype=torch.float32, device=q.device))
                 _SCRATCH[key] = sc
             part_o, part_ml = sc
+    if _lib.BOUNDS_CHECK:
+        _lib.check_index("paged_decode seq_lens", seq_lens, max_pages * PAGE + 1)
+        # only the pages below each sequence's length are read: check exactly those entries of the table
+        used = (torch.arange(max_pages, device=q.device)[None, :] * PAGE) < seq_lens[:, None]
+        _lib.check_index("paged_decode block_table", block_table[used], k_cache.shape[0])
     _lib.call(
         "areno_paged_decode", q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _lib.ptr(k_scale),
         _lib.ptr(v_scale), block_table.data_ptr(), seq_lens.data_ptr(), out.data_ptr(), _lib.ptr(part_o),

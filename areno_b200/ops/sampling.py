@@ -167,12 +167,15 @@ def sample(logits, temperature: float = 1.0, top_k: int = -1, top_p: float = 1.0
 
 
 _SLICE_SCRATCH: dict = {}
+_RETIRED: list = []
 
 
 def _slice_scratch(device, elems: int) -> torch.Tensor:
     key = device.index if device.index is not None else torch.cuda.current_device()
     buf = _SLICE_SCRATCH.get(key)
     if buf is None or buf.numel() < elems:
+        if buf is not None:
+            _RETIRED.append(buf)      # captured decode graphs may still point at the outgrown buffer
         buf = torch.empty(max(elems, 16 * 148 * 6), dtype=torch.float32, device=device)
         _SLICE_SCRATCH[key] = buf
     return buf

@@ -342,7 +342,10 @@ class TpComm:
         self.off_part, self.off_h, self.off_y = self.HEADER, self.HEADER + self.buf_bytes, self.HEADER + 2 * self.buf_bytes
         self.status = _lib.status_buffer(device)
         mc = self.heap.mc_base
-        self.use_mc = bool(mc)
+        # multimem (in-switch reduction / broadcast) pays from four ranks on; between two GPUs plain peer loads and
+        # stores were measured faster (one remote operand instead of a round trip through the switch for both).
+        # ARENO_TP_MULTIMEM=1 forces it wherever a multicast mapping exists, =0 never sets one up.
+        self.use_mc = bool(mc) and (self.tp >= 4 or os.environ.get("ARENO_TP_MULTIMEM") == "1")
         self.wait_ms = int(os.environ.get("ARENO_TP_WAIT_MS", "2000"))
         self._arrays = [_ptr_array([b + off for b in bases]) for off in (0, self.off_part, self.off_h, self.off_y)]
         self.desc = TpDesc(self.tp, self.rank, self._arrays[0], self._arrays[1], self._arrays[2], self._arrays[3],

@@ -26,18 +26,33 @@ import torch.distributed as dist
 PEER_COPY_GBS = 770.0
 
 
-def _timed(fn, iters: int, warmup: int, group) -> float:
+def _timed(fn, iters: int, warmup: int, group, graph: bool = False) -> float:
+    """Milliseconds per call of ``fn`` (CUDA events on the launching stream, max over ranks).  With ``graph`` the call
+    is captured four times into one CUDA graph and the graph is replayed, so that microsecond-scale kernels are
+    timed as they run inside a captured decode step and not at the rate the host can launch them."""
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
     dist.barrier(group=group)
+    per = 1
+    run = fn
+    if graph:
+        per = 4
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(per):
+                fn()
+        run = g.replay
+        run()
+        torch.cuda.synchronize()
+        dist.barrier(group=group)
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for _ in range(iters):
-        fn()
+        run()
     end.record()
     torch.cuda.synchronize()
-    ms = torch.tensor([start.elapsed_time(end) / iters], device="cuda")
+    ms = torch.tensor([start.elapsed_time(end) / (iters * per)], device="cuda")
     dist.all_reduce(ms, op=dist.ReduceOp.MAX, group=group)
     return float(ms)
 
@@ -109,13 +124,14 @@ def bench_tp_fused(ctx, rows: int, hidden: int, k_full: int, iters: int, warmup:
     def flush_only():
         flush.zero_()
 
-    t_flush = _timed(flush_only, iters, warmup, ctx.tp_group)
+    g = rows <= 1024      # decode-sized calls live inside captured graphs; time them that way
+    t_flush = _timed(flush_only, iters, warmup, ctx.tp_group, g)
     out = {"case": "tp_fused", "tp": tp, "rows": rows, "hidden": hidden, "k_local": k_local,
-           "multimem": bool(comm.use_mc), "heap": comm.heap.kind}
-    t_f = _timed(fused, iters, warmup, ctx.tp_group) - t_flush
-    t_n = _timed(nccl, iters, warmup, ctx.tp_group) - t_flush
-    t_fc = _timed(fused_collective_only, iters, warmup, ctx.tp_group)
-    t_nc = _timed(nccl_collective_only, iters, warmup, ctx.tp_group)
+           "multimem": bool(comm.use_mc), "heap": comm.heap.kind, "timed_in_cuda_graph": g}
+    t_f = _timed(fused, iters, warmup, ctx.tp_group, g) - t_flush
+    t_n = _timed(nccl, iters, warmup, ctx.tp_group, g) - t_flush
+    t_fc = _timed(fused_collective_only, iters, warmup, ctx.tp_group, g)
+    t_nc = _timed(nccl_collective_only, iters, warmup, ctx.tp_group, g)
     flops = 2.0 * rows * hidden * k_local
     link_bytes = 3.0 * (tp - 1) / tp * rows * hidden * 2
     weight_bytes = 2.0 * hidden * k_local
@@ -164,9 +180,8 @@ def main(argv=None) -> int:
         from ..parallel.symm import setup_tp_comm
 
         comm = setup_tp_comm(ctx, args.hidden, max(args.rows))
-        modes = [comm.use_mc] if args.multimem < 0 else [bool(args.multimem) and comm.use_mc]
-        if args.multimem < 0 and comm.use_mc:
-            modes = [True, False]
+        has_mc = bool(comm.heap.mc_base)
+        modes = ([True, False] if has_mc else [False]) if args.multimem < 0 else [bool(args.multimem) and has_mc]
         peaks = _peaks()
         for use_mc in modes:
             comm.use_mc = use_mc

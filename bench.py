@@ -93,21 +93,22 @@ def group_advantages(rewards: np.ndarray, group: int) -> np.ndarray:
     return adv.reshape(-1)
 
 
-def build_micro_batches(prompts, responses, logprobs, advantages, micro_tokens: int):
-    """Greedy fill of padded (B, T) packs holding at most ``micro_tokens`` real tokens."""
+def build_micro_batches(prompts, responses, logprobs, advantages, micro_tokens: int, groups=None):
+    """Padded (B, T) packs holding at most ``micro_tokens`` real tokens: greedy fill in input order, or the given
+    ``groups`` of sequence indices."""
     import torch
 
-    order = list(range(len(prompts)))
-    groups, cur, cur_tokens = [], [], 0
-    for i in order:
-        n = len(prompts[i]) + len(responses[i])
-        if cur and cur_tokens + n > micro_tokens:
+    if groups is None:
+        groups, cur, cur_tokens = [], [], 0
+        for i in range(len(prompts)):
+            n = len(prompts[i]) + len(responses[i])
+            if cur and cur_tokens + n > micro_tokens:
+                groups.append(cur)
+                cur, cur_tokens = [], 0
+            cur.append(i)
+            cur_tokens += n
+        if cur:
             groups.append(cur)
-            cur, cur_tokens = [], 0
-        cur.append(i)
-        cur_tokens += n
-    if cur:
-        groups.append(cur)
     packs = []
     for g in groups:
         width = max(len(prompts[i]) + len(responses[i]) for i in g)
@@ -183,10 +184,12 @@ def run_ours(args):
     from areno_b200.api import loss_fns
     from areno_b200.engine.config import EngineConfig, ModelConfig, OptimizerConfig, RuntimeConfig
     from areno_b200.engine.inference import SamplingParams
+    from areno_b200.engine.training import balanced_partition, pack_into_bins
     from areno_b200.engine.worker import RankWorker
     from areno_b200.ops import _lib as klib
     from areno_b200.parallel.context import init_parallel
 
+    balance = os.environ.get("ARENO_BENCH_BALANCE", "1") != "0"
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
@@ -226,7 +229,21 @@ def run_ours(args):
         t2 = time.time()
         rewards = np.array([hash_reward(t) for t in out.tokens])
         adv = group_advantages(rewards, GROUP)
-        packs = build_micro_batches(rows, out.tokens, out.logprobs, adv, MICRO_TOKENS)
+        tokens = sum(len(p) + len(t) for p, t in zip(rows, out.tokens))
+        seqs = (rows, out.tokens, out.logprobs, [float(a) for a in adv])
+        groups = None
+        if world > 1 and balance:
+            # Deal the job's sequences out again so that every rank trains on the same number of sequences, nearly the
+            # same number of tokens, and the same number of micro-batches (the slowest rank sets the step time).
+            gathered = [None] * world
+            dist.all_gather_object(gathered, seqs)
+            flat = [[x for part in gathered for x in part[k]] for k in range(4)]
+            lengths = [len(p) + len(t) for p, t in zip(flat[0], flat[1])]
+            plan = balanced_partition(lengths, world)
+            n_bins = max(len(pack_into_bins([lengths[i] for i in plan[r]], MICRO_TOKENS)) for r in range(world))
+            seqs = tuple([col[i] for i in plan[rank]] for col in flat)
+            groups = pack_into_bins([lengths[i] for i in plan[rank]], MICRO_TOKENS, n_bins)
+        packs = build_micro_batches(seqs[0], seqs[1], seqs[2], seqs[3], MICRO_TOKENS, groups)
         t3 = time.time()
         stats = worker.train(packs)
         torch.cuda.synchronize()
@@ -236,7 +253,6 @@ def run_ours(args):
         phase["rollout_s"] += t2 - t1
         phase["train_s"] += t4 - t3
         phase["host_s"] += (t1 - t0) + (t3 - t2)
-        tokens = sum(len(p) + len(t) for p, t in zip(rows, out.tokens))
         return tokens, stats[-1]["loss"]
 
     def barrier():
@@ -322,6 +338,8 @@ def run_ours(args):
                                   "local reshard of the DP replica into the TP shards; row-parallel all-reduce fused with "
                                   "residual + RMSNorm over the symmetric heap"),
                 "tokens_counted": "prompt+response tokens per sequence, once per step",
+                "train_sharding": ("sequences re-dealt over ranks by token count before training" if world > 1 and balance
+                                   else "each rank trains on the sequences it generated"),
                 "l2": "inputs larger than L2 (15 GB of weights streamed every decode step / micro-batch)",
                 "wall_s_timed_region": wall,
             },

@@ -166,3 +166,18 @@ def test_balanced_partition_and_bins_even_out_tokens_and_micro_batch_counts():
         assert max(sum(ls[i] for i in b) for b in bins) <= 4096
     assert pack_into_bins([5000, 10], 4096) == [[0], [1]]                     # an over-long sequence gets its own bin
     assert balanced_partition([3, 1, 2], 2) in ([[0], [1, 2]], [[0, 1], [2]]) or True
+
+
+def test_checked_mode_index_validation_names_the_operand():
+    import pytest
+
+    from areno_b200.ops import _lib
+
+    ok = torch.tensor([0, 5, -1, 63])
+    _lib.check_index("slots", ok, 64, low=-1, enabled=True)
+    _lib.check_index("slots", ok, 4, enabled=False)                       # off: never raises
+    with pytest.raises(IndexError, match=r"slots: 1 of 4 indices outside \[0, 64\) \(min -1, max 63\)"):
+        _lib.check_index("slots", ok, 64, enabled=True)
+    with pytest.raises(IndexError, match="max 63"):
+        _lib.check_index("pages", ok, 63, low=-1, enabled=True)
+    _lib.check_index("empty", torch.zeros(0, dtype=torch.int64), 1, enabled=True)

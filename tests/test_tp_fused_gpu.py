@@ -41,7 +41,7 @@ def _rank_main(rank, world, port, ret):
         ctx = init_parallel(rank, world, tp_size=world, master_port=port, device=dev, timeout_s=120)
         H, eps = 3584, 1e-6
         comm = setup_tp_comm(ctx, H, 4096)
-        has_mc = comm.use_mc
+        has_mc = bool(comm.heap.mc_base)      # exercise both paths wherever a multicast mapping exists
         g = torch.Generator(device=dev).manual_seed(100 + rank)
         shared = torch.Generator(device=dev).manual_seed(7)
         errs = []
