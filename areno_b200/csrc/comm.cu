@@ -25,7 +25,13 @@
 //   4. the last CTA to finish tells every peer "my rows are published" and waits for theirs, so that
 //      when the kernel completes the local h_out / y_out hold all rows.
 // Each element crosses NVLink once in each direction per rank (reduce-scatter + all-gather), every
-// row is normalised once, and all ranks see bit-identical results.  This replaces GEMM + NCCL
+// row is normalised once, and all ranks see bit-identical results.
+//
+// One-shot variant (the default wherever it moves no more bytes, and for every decode-sized call): after step 1
+// every rank reduces ALL rows for itself and keeps the results locally; there is nothing to publish and no second
+// flag exchange.  With multimem the switch hands each rank the finished sums (rows x H bf16 inbound whatever the
+// group size); with plain loads a rank reads tp - 1 remote partials, which is the cheaper choice for two ranks
+// and for a few hundred rows, where the call is bound by the flag round trip and not by bytes.  This replaces GEMM + NCCL
 // all-reduce + residual RMSNorm of the reference (areno/engine/parallel/collectives.py:143-155,
 // areno/engine/layers/linear.py:235-244).
 //
@@ -139,7 +145,9 @@ __device__ __forceinline__ void load8_cg(const __nv_bfloat16* p, float (&f)[8]) 
 // One call of the fused reduce.  `slot_off`: element offset of the slot inside the three buffers.
 // Rows [row_lo, row_hi) belong to this rank; one CTA per row, grid-stride.  residual: local bf16
 // [rows, H] or null; w: norm scale (bf16 or fp32) or null; want_y = 0 skips the norm (h only).
-template <int THREADS, int VPT, bool MC>
+// ONESHOT: every rank reduces ALL rows itself (one flag exchange, nothing to publish, results written locally);
+// otherwise the two-shot scheme above (each rank reduces the rows it owns and publishes them to the group).
+template <int THREADS, int VPT, bool MC, bool ONESHOT>
 __global__ void __launch_bounds__(THREADS)
 tp_reduce_norm_kernel(TpCtx c, long long slot_off, const __nv_bfloat16* __restrict__ residual,
                       const void* __restrict__ w, int wf32, float w_offset, int want_y, int rows, int row_lo,
@@ -177,7 +185,8 @@ tp_reduce_norm_kernel(TpCtx c, long long slot_off, const __nv_bfloat16* __restri
   // ---- 2 + 3. reduce my rows, add the residual, normalise, publish to every rank
   const int nvec = H >> 3;
   if (ok) {
-    for (int row = row_lo + blockIdx.x; row < row_hi; row += gridDim.x) {
+    const int r_first = ONESHOT ? 0 : row_lo, r_end = ONESHOT ? rows : row_hi;
+    for (int row = r_first + blockIdx.x; row < r_end; row += gridDim.x) {
       const size_t base = (size_t)row * H;
       float v[VPT][8];
       float ss = 0.f;
@@ -213,7 +222,9 @@ tp_reduce_norm_kernel(TpCtx c, long long slot_off, const __nv_bfloat16* __restri
           // the stream is kept in bf16: norm statistics are taken on the rounded values
           const uint4 hv = pack8(v[i]);
           unpack8(hv, v[i]);
-          if constexpr (MC) {
+          if constexpr (ONESHOT) {
+            *reinterpret_cast<uint4*>(c.h_out[c.rank] + off) = hv;
+          } else if constexpr (MC) {
             multimem_st_bf16x8(c.h_mc + off, hv);
           } else {
 #pragma unroll
@@ -256,7 +267,9 @@ tp_reduce_norm_kernel(TpCtx c, long long slot_off, const __nv_bfloat16* __restri
             }
             const uint4 yv = pack8(o);
             const size_t off = (size_t)slot_off + base + (size_t)vi * 8;
-            if constexpr (MC) {
+            if constexpr (ONESHOT) {
+              *reinterpret_cast<uint4*>(c.y_out[c.rank] + off) = yv;
+            } else if constexpr (MC) {
               multimem_st_bf16x8(c.y_mc + off, yv);
             } else {
 #pragma unroll
@@ -271,11 +284,21 @@ tp_reduce_norm_kernel(TpCtx c, long long slot_off, const __nv_bfloat16* __restri
   // ---- 4. rows published: the last CTA of this rank tells the peers and waits for theirs
   __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence_system();   // this CTA's stores (all threads, ordered by the barrier above) before the count
+    if constexpr (!ONESHOT) __threadfence_system();   // this CTA's stores (ordered by the barrier above) before the count
     sh_last = atomicAdd(my_flags + kFlagDone, 1u) == gridDim.x - 1 ? 1 : 0;
   }
   __syncthreads();
   if (!sh_last) return;
+  if constexpr (ONESHOT) {
+    // nothing was published: the peers only ever read this rank's partial, and they are held off its reuse by the
+    // announcement of the next call.  Advance the call counter and leave.
+    if (threadIdx.x == 0) {
+      my_flags[kFlagDone] = 0;
+      my_flags[kFlagCall] = call;
+      __threadfence();
+    }
+    return;
+  }
   __threadfence_system();     // the other CTAs' stores are ordered before their counts, which we have seen
   if (threadIdx.x < c.tp && (int)threadIdx.x != c.rank) {
     const int p = threadIdx.x;
@@ -464,36 +487,44 @@ static void owned_rows(int M, int tp, int rank, int* lo, int* hi) {
 // of every rank must already be in slot `slot_off` of its `partial` buffer (stream order on each
 // rank).  After the kernel, h_out / y_out of this rank hold all `rows` rows at the same offset.
 // use_mc: 1 = multimem instructions (needs the multicast addresses), 0 = plain peer loads / stores.
+// oneshot: 1 = every rank reduces all rows for itself (one flag exchange; the choice for decode-sized calls and,
+// with multimem, for any size: the switch hands each rank the finished sums), 0 = the two-shot scheme.
 extern "C" int areno_tp_reduce_norm(const ArenoTpDesc* desc, long long slot_off, const void* residual, const void* w,
                                     int wf32, float w_offset, int want_y, long long rows, int H, float eps,
-                                    int use_mc, cudaStream_t stream) {
+                                    int use_mc, int oneshot, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (H % 8 != 0 || (slot_off & 7) != 0) return -3;
   TpCtx c;
   const int rc = fill_ctx(&c, desc);
   if (rc != 0) return rc;
-  if (use_mc && (c.part_mc == nullptr || c.h_mc == nullptr || c.y_mc == nullptr)) return -3;
+  if (use_mc && (c.part_mc == nullptr || (!oneshot && (c.h_mc == nullptr || c.y_mc == nullptr)))) return -3;
   if (!use_mc)
     for (int i = 0; i < c.tp; ++i)
       if (c.part[i] == nullptr || c.h_out[i] == nullptr || c.y_out[i] == nullptr) return -3;
   int lo, hi;
   owned_rows((int)rows, c.tp, c.rank, &lo, &hi);
-  int grid = hi - lo;
+  int grid = oneshot ? (int)rows : hi - lo;
   if (grid > 148 * 4) grid = 148 * 4;
   if (grid < 1) grid = 1;   // a rank without rows still takes part in both flag exchanges
   const int nvec = H >> 3;
   cudaError_t e;
-#define TP_LAUNCH(T, V)                                                                                       \
-  e = use_mc ? launch_pdl(tp_reduce_norm_kernel<T, V, true>, dim3(grid), dim3(T), 0, stream, c, slot_off,     \
-                          (const __nv_bfloat16*)residual, w, wf32, w_offset, want_y, (int)rows, lo, hi, H, eps) \
-             : launch_pdl(tp_reduce_norm_kernel<T, V, false>, dim3(grid), dim3(T), 0, stream, c, slot_off,    \
-                          (const __nv_bfloat16*)residual, w, wf32, w_offset, want_y, (int)rows, lo, hi, H, eps)
+#define TP_ARGS c, slot_off, (const __nv_bfloat16*)residual, w, wf32, w_offset, want_y, (int)rows, lo, hi, H, eps
+#define TP_LAUNCH(T, V)                                                                                          \
+  do {                                                                                                           \
+    if (oneshot)                                                                                                 \
+      e = use_mc ? launch_pdl(tp_reduce_norm_kernel<T, V, true, true>, dim3(grid), dim3(T), 0, stream, TP_ARGS)   \
+                 : launch_pdl(tp_reduce_norm_kernel<T, V, false, true>, dim3(grid), dim3(T), 0, stream, TP_ARGS); \
+    else                                                                                                         \
+      e = use_mc ? launch_pdl(tp_reduce_norm_kernel<T, V, true, false>, dim3(grid), dim3(T), 0, stream, TP_ARGS)  \
+                 : launch_pdl(tp_reduce_norm_kernel<T, V, false, false>, dim3(grid), dim3(T), 0, stream, TP_ARGS);\
+  } while (0)
   if (nvec <= 128) TP_LAUNCH(128, 1);
   else if (nvec <= 256) TP_LAUNCH(256, 1);
   else if (nvec <= 512) TP_LAUNCH(512, 1);
   else if (nvec <= 1024) TP_LAUNCH(512, 2);
   else if (nvec <= 2048) TP_LAUNCH(512, 4);
   else return -2;
+#undef TP_ARGS
 #undef TP_LAUNCH
   return (int)e;
 }

@@ -733,7 +733,7 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, const void* bia
     bn = 256;
     workspace = nullptr;
   }
-  if (epi >= 4) {  // gated activation: merged weight, 256-wide tiles only
+  if (epi == 4 || epi == 5) {  // gated activation: merged weight, 256-wide tiles only
     if (a_mn || b_mn || group != nullptr || n_extra != 0 || gate_rows <= 0 || N != 2 * gate_rows || (gate_rows % 8) != 0)
       return -3;
     bn = 256;
@@ -770,7 +770,7 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, const void* bia
   const uint64_t b_mult = (group != nullptr && group->mode == 1) ? (uint64_t)b_groups : 1u;
   if (b_mn) rc = make_tensor_map_2d_bf16(&tb, B, (uint64_t)N, (uint64_t)K * b_mult, (uint64_t)ldb * 2, 64, 64);
   else rc = make_tensor_map_2d_bf16(&tb, B, (uint64_t)K, (uint64_t)N * b_mult, (uint64_t)ldb * 2, 64,
-                                    epi >= 4 ? 128u : (uint32_t)bn);
+                                    (epi == 4 || epi == 5) ? 128u : (uint32_t)bn);
   if (rc != 0) return rc;
   GemmParams p;
   p.M = M; p.N = N; p.K = K;
@@ -784,7 +784,7 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, const void* bia
   p.split_stride = 0;
   p.n_extra = n_extra;
   for (int e = 0; e < 7; ++e) p.extra[e] = e < n_extra ? extra[e] : nullptr;
-  p.gate_rows = epi >= 4 ? gate_rows : 0;
+  p.gate_rows = (epi == 4 || epi == 5) ? gate_rows : 0;
   p.tail_first = p.tail_tiles = p.tail_splits = p.tail_kb = 0;
   p.tail_ws = nullptr;
   p.lse_targets = lse != nullptr ? lse->targets : nullptr;

@@ -227,10 +227,11 @@ grouped_sigmoid_topk_kernel(const float* __restrict__ logits, const float* __res
 __global__ void __launch_bounds__(1024)
 moe_align_kernel(const int* __restrict__ ids, int routes, int e_lo, int e_count, int max_rows,
                  int* __restrict__ expert_rows, int* __restrict__ tile_expert, int* __restrict__ row_route,
-                 int* __restrict__ route_row, int* __restrict__ counts_out) {
-  extern __shared__ int sh[];  // [e_count] counts, [e_count] offsets
+                 int* __restrict__ route_row, int* __restrict__ counts_out, int* __restrict__ dropped_out) {
+  extern __shared__ int sh[];  // [e_count] counts, [e_count] offsets, [e_count] rows that fit
   int* cnt = sh;
   int* off = sh + e_count;
+  int* fit = sh + 2 * e_count;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nwarps = blockDim.x >> 5;
   for (int i = threadIdx.x; i < max_rows; i += blockDim.x) row_route[i] = -1;
@@ -246,16 +247,24 @@ moe_align_kernel(const int* __restrict__ ids, int routes, int e_lo, int e_count,
   }
   __syncthreads();
   if (threadIdx.x == 0) {
-    int o = 0;
+    // max_rows covers every case when it was sized from the static bound (routes + experts * 127).  A caller
+    // that sizes it from an expected load instead (expert parallelism: a capacity factor over the mean) may
+    // see more routes than fit: the surplus routes of an expert are dropped (their route_row stays -1, the
+    // token simply gets no contribution from that expert) and counted in dropped_out.
+    int o = 0, dropped = 0;
     for (int e = 0; e < e_count; ++e) {
-      const int padded = (cnt[e] + kMoeTile - 1) / kMoeTile * kMoeTile;
+      int padded = (cnt[e] + kMoeTile - 1) / kMoeTile * kMoeTile;
+      if (o + padded > max_rows) padded = (max_rows - o) / kMoeTile * kMoeTile;
+      fit[e] = min(cnt[e], padded);
+      dropped += cnt[e] - fit[e];
       off[e] = o;
       expert_rows[2 * e] = o;
       expert_rows[2 * e + 1] = padded;
-      if (counts_out != nullptr) counts_out[e] = cnt[e];
+      if (counts_out != nullptr) counts_out[e] = fit[e];
       for (int tile = o / kMoeTile; tile < (o + padded) / kMoeTile; ++tile) tile_expert[tile] = e;
       o += padded;
     }
+    if (dropped_out != nullptr) *dropped_out = dropped;
   }
   __syncthreads();
   for (int e = warp; e < e_count; e += nwarps) {
@@ -266,8 +275,12 @@ moe_align_kernel(const int* __restrict__ ids, int routes, int e_lo, int e_count,
       const uint32_t m = __ballot_sync(0xffffffffu, hit);
       if (hit) {
         const int row = pos + __popc(m & ((1u << lane) - 1u));
-        row_route[row] = r;
-        route_row[r] = row;
+        if (row < off[e] + fit[e]) {
+          row_route[row] = r;
+          route_row[r] = row;
+        } else {
+          route_row[r] = -1;
+        }
       }
       pos += __popc(m);
     }
@@ -427,8 +440,21 @@ extern "C" int areno_moe_align(const int* ids, long long routes, int e_lo, int e
                                int* expert_rows, int* tile_expert, int* row_route, int* route_row, int* counts,
                                cudaStream_t stream) {
   if (e_count < 1 || e_count > 4096 || max_rows % kMoeTile != 0) return -3;
-  moe_align_kernel<<<1, 1024, 2 * e_count * sizeof(int), stream>>>(ids, (int)routes, e_lo, e_count, (int)max_rows,
-                                                                  expert_rows, tile_expert, row_route, route_row, counts);
+  moe_align_kernel<<<1, 1024, 3 * e_count * sizeof(int), stream>>>(ids, (int)routes, e_lo, e_count, (int)max_rows,
+                                                                  expert_rows, tile_expert, row_route, route_row, counts,
+                                                                  nullptr);
+  return (int)cudaGetLastError();
+}
+
+// Same plan, for a row buffer that is smaller than the static bound: routes that do not fit are dropped and
+// *dropped (device int) receives their number.
+extern "C" int areno_moe_align_capped(const int* ids, long long routes, int e_lo, int e_count, long long max_rows,
+                                      int* expert_rows, int* tile_expert, int* row_route, int* route_row, int* counts,
+                                      int* dropped, cudaStream_t stream) {
+  if (e_count < 1 || e_count > 4096 || max_rows % kMoeTile != 0 || max_rows < kMoeTile) return -3;
+  moe_align_kernel<<<1, 1024, 3 * e_count * sizeof(int), stream>>>(ids, (int)routes, e_lo, e_count, (int)max_rows,
+                                                                  expert_rows, tile_expert, row_route, route_row, counts,
+                                                                  dropped);
   return (int)cudaGetLastError();
 }
 

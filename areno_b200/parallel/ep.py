@@ -1,0 +1,232 @@
+"""Expert parallelism over peer memory: the all-to-all that takes every token to the ranks owning its experts
+and brings the expert outputs back (``csrc/ep.cu``), wrapped as two differentiable ops.
+
+Layout: the ranks of ``group`` each own ``E / n`` consecutive experts and their own tokens (the group is the
+data-parallel group of the job).  ``EpComm`` keeps, in a symmetric heap (``parallel/symm.py``), two slots of
+
+* ``pub``      bf16 ``[cap * k, H]``: rows this rank publishes for its peers to pull (tokens on the way out,
+  gradients of the combined rows on the way back);
+* ``inbox``    bf16 ``[cap * k, H]``: one row per (token, slot) of this rank, stored there by the expert owners;
+* ``ids_all``  int32 ``[n, cap * k]``: the routing tables of all ranks (every rank stores its own into everybody's).
+
+``dispatch(x, ids)`` returns the expert-sorted rows that hit the local experts plus the plan;
+``combine(ys, weights, plan)`` returns the weighted sum per local token.  Their backward passes are each other's
+data movement with the roles swapped, so training works through ordinary autograd:
+
+    rows, plan = ep.dispatch(x, ids)                 # publish -> barrier -> align -> pull
+    rows = grouped_linear(...act(grouped_linear(rows, w_gate_up, plan))..., w_down, plan)
+    out = ep.combine(rows, weights, plan)            # push -> barrier -> weighted sum
+
+Every rank of the group must make the same sequence of calls with the same ``cap`` (the row counts themselves may
+differ and stay on the device).  The expert-sorted buffer is sized for ``capacity`` times the mean load; routes
+beyond it are dropped by the plan and counted (``EpComm.dropped()``), which callers treat as an error unless they
+opted into token dropping.  Waits inside the barrier kernel are bounded and report through the status word.
+
+The reference has no counterpart: it shards experts over TP, replicates the tokens and all-reduces
+(``areno/models/qwen3/model.py:99-116``).
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from dataclasses import dataclass
+
+import torch
+
+from ..ops import _lib
+from ..ops import moe as moe_ops
+from .symm import SymmHeap, TpDesc, _as_tensor, _Blob, _ptr_array
+
+_lib.register_signature("areno_ep_publish_ids", "iippllp")
+_lib.register_signature("areno_ep_pull_rows", "ipplii" + "plip")
+_lib.register_signature("areno_ep_push_rows", "ippl" + "plip")
+_lib.register_signature("areno_moe_align_capped", "pliilppppppp")
+
+
+@dataclass
+class EpPlan:
+    """Routing plan of one MoE call on this rank: ``moe`` sorts the routes of all ranks that hit a local expert;
+    ``slot`` is the heap slot the call's buffers live in."""
+
+    moe: moe_ops.MoePlan
+    slot: int
+    tokens: int
+    k: int
+
+
+class EpComm:
+    HEADER = 4096
+
+    def __init__(self, group, size: int, rank: int, hidden: int, cap_tokens: int, k: int, num_experts: int,
+                 device: torch.device, capacity: float = 2.0):
+        if hidden % 8 != 0 or num_experts % size != 0:
+            raise ValueError("hidden must be a multiple of 8 and num_experts a multiple of the group size")
+        self.group, self.n, self.rank, self.device = group, int(size), int(rank), device
+        self.hidden, self.cap, self.k = int(hidden), int(cap_tokens), int(k)
+        self.e_local = num_experts // self.n
+        self.e_lo = self.rank * self.e_local
+        self.cap_routes = self.cap * self.k
+        # rows of the expert-sorted buffer: `capacity` times the mean number of routes per rank, never less than a
+        # tile per expert and never more than the static bound that covers every routing
+        mean = self.cap_routes
+        bound = moe_ops.max_rows_for(self.n * self.cap_routes, self.e_local)
+        want = int(capacity * mean) + self.e_local * moe_ops.TILE
+        self.max_rows = min(bound, (want + moe_ops.TILE - 1) // moe_ops.TILE * moe_ops.TILE)
+        row_bytes = self.cap_routes * self.hidden * 2
+        self.row_bytes = (row_bytes + 4095) // 4096 * 4096
+        self.ids_bytes = (self.n * self.cap_routes * 4 + 4095) // 4096 * 4096
+        self.slot_bytes = 2 * self.row_bytes + self.ids_bytes
+        total = self.HEADER + 2 * self.slot_bytes
+        self.heap = SymmHeap(group, self.n, self.rank, total, device, multicast=False)
+        self.status = _lib.status_buffer(device)
+        self.wait_ms = int(os.environ.get("ARENO_EP_WAIT_MS", "20000"))
+        bases = self.heap.bases
+        self._flag_array = _ptr_array(bases)
+        self._desc = TpDesc(self.n, self.rank, self._flag_array, None, None, None, None, None, None,
+                            self.status.data_ptr(), self.wait_ms)
+        self._pub, self._inbox, self._ids, self._ptrs = [], [], [], []
+        local = self.heap.local_base
+        for s in range(2):
+            off = self.HEADER + s * self.slot_bytes
+            self._pub.append(_as_tensor(local + off, self.cap_routes * self.hidden, device).view(self.cap_routes, self.hidden))
+            self._inbox.append(_as_tensor(local + off + self.row_bytes, self.cap_routes * self.hidden, device)
+                               .view(self.cap_routes, self.hidden))
+            ids = torch.as_tensor(_Blob(local + off + 2 * self.row_bytes, self.n * self.cap_routes, "<i4"), device=device)
+            self._ids.append(ids.view(self.n, self.cap_routes))
+            self._ptrs.append({"pub": _ptr_array([b + off for b in bases]),
+                               "inbox": _ptr_array([b + off + self.row_bytes for b in bases]),
+                               "ids": _ptr_array([b + off + 2 * self.row_bytes for b in bases])})
+        self._dropped = torch.zeros(1, dtype=torch.int32, device=device)
+        self._dropped_total = torch.zeros(1, dtype=torch.int64, device=device)
+        self.calls = 0
+
+    # ------------------------------------------------------------------------------ pieces
+    def _next_slot(self) -> int:
+        s = self.calls & 1
+        self.calls += 1
+        return s
+
+    def barrier(self) -> None:
+        _lib.call("areno_tp_barrier", ctypes.addressof(self._desc), _lib.stream())
+
+    def dropped(self) -> int:
+        """Routes dropped so far because an expert-sorted buffer was full (synchronising read)."""
+        return int(self._dropped_total.item())
+
+    def _plan(self, slot: int, tokens: int) -> EpPlan:
+        ids_all = self._ids[slot]
+        routes = self.n * self.cap_routes
+        dev = self.device
+        er = torch.empty(2 * self.e_local, dtype=torch.int32, device=dev)
+        te = torch.empty(self.max_rows // moe_ops.TILE, dtype=torch.int32, device=dev)
+        rr = torch.empty(self.max_rows, dtype=torch.int32, device=dev)
+        ro = torch.empty(routes, dtype=torch.int32, device=dev)
+        cnt = torch.empty(self.e_local, dtype=torch.int32, device=dev)
+        _lib.call("areno_moe_align_capped", ids_all.data_ptr(), routes, self.e_lo, self.e_local, self.max_rows,
+                  er.data_ptr(), te.data_ptr(), rr.data_ptr(), ro.data_ptr(), cnt.data_ptr(), self._dropped.data_ptr(),
+                  _lib.stream())
+        self._dropped_total += self._dropped
+        plan = moe_ops.MoePlan(self.n * self.cap, self.k, self.e_local, self.max_rows, er, te, rr, ro, cnt)
+        return EpPlan(plan, slot, tokens, self.k)
+
+    def _pull(self, slot: int, plan: EpPlan, per_token: bool) -> torch.Tensor:
+        rows = torch.empty((self.max_rows, self.hidden), dtype=torch.bfloat16, device=self.device)
+        _lib.call("areno_ep_pull_rows", self.n, self._ptrs[slot]["pub"], plan.moe.row_route.data_ptr(), self.cap_routes,
+                  self.k, int(per_token), rows.data_ptr(), self.max_rows, self.hidden, _lib.stream())
+        return rows
+
+    def _push(self, slot: int, plan: EpPlan, rows: torch.Tensor) -> None:
+        rows = rows.contiguous()
+        _lib.call("areno_ep_push_rows", self.n, self._ptrs[slot]["inbox"], plan.moe.row_route.data_ptr(), self.cap_routes,
+                  rows.data_ptr(), self.max_rows, self.hidden, _lib.stream())
+
+    # --------------------------------------------------------------------------------- ops
+    def dispatch(self, x: torch.Tensor, ids: torch.Tensor):
+        """``x [T, H]`` bf16, ``ids [T, k]`` int32 global expert ids -> (expert-sorted rows ``[max_rows, H]``, plan)."""
+        if x.shape[0] > self.cap or x.shape[1] != self.hidden or ids.shape != (x.shape[0], self.k):
+            raise ValueError(f"dispatch: x {tuple(x.shape)} / ids {tuple(ids.shape)} do not fit cap={self.cap}, "
+                             f"hidden={self.hidden}, k={self.k}")
+        slot = self._next_slot()
+        t = x.shape[0]
+        flat = ids.reshape(-1).to(torch.int32).contiguous()
+        _lib.call("areno_ep_publish_ids", self.n, self.rank, self._ptrs[slot]["ids"], flat.data_ptr(), t * self.k,
+                  self.cap_routes, _lib.stream())
+        plan_holder: list = []
+        rows = _Dispatch.apply(x, self, slot, plan_holder)
+        return rows, plan_holder[0]
+
+    def combine(self, ys: torch.Tensor, weights: torch.Tensor, plan: EpPlan) -> torch.Tensor:
+        """Expert outputs ``ys [max_rows, H]`` -> ``[T, H]``: ``sum_j weights[t, j] * y(t, j)``."""
+        return _Combine.apply(ys, weights, self, plan)
+
+    def close(self) -> None:
+        self.heap.close()
+
+
+def _identity(routes: int, device) -> torch.Tensor:
+    """Route map in which route (t, j) lives in row t * k + j: lets the local combine kernels run on an inbox."""
+    return torch.arange(routes, dtype=torch.int32, device=device)
+
+
+def _weighted_sum(rows: torch.Tensor, weights: torch.Tensor | None, tokens: int, k: int) -> torch.Tensor:
+    """``out[t] = sum_j weights[t, j] * rows[t * k + j]`` (plain sum without weights)."""
+    out = torch.empty((tokens, rows.shape[1]), dtype=rows.dtype, device=rows.device)
+    _lib.call("areno_moe_combine", rows.data_ptr(), _identity(tokens * k, rows.device).data_ptr(), _lib.ptr(weights),
+              tokens, k, rows.shape[1], out.data_ptr(), _lib.stream())
+    return out
+
+
+class _Dispatch(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, comm: EpComm, slot: int, plan_holder: list):
+        t = x.shape[0]
+        comm._pub[slot][:t].copy_(x)                 # tokens on the way out: one row per token
+        comm.barrier()                               # every rank's tokens and routing tables are in place
+        plan = comm._plan(slot, t)
+        rows = comm._pull(slot, plan, per_token=True)
+        plan_holder.append(plan)
+        ctx.comm, ctx.plan = comm, plan
+        return rows
+
+    @staticmethod
+    def backward(ctx, d_rows):
+        comm, plan = ctx.comm, ctx.plan
+        slot = comm._next_slot()
+        comm._push(slot, plan, d_rows)               # gradient of a pull is a push to the rows' owners
+        comm.barrier()
+        t, k = plan.tokens, plan.k
+        dx = _weighted_sum(comm._inbox[slot][: t * k], None, t, k)      # sum over the k routes of a token
+        return dx, None, None, None
+
+
+class _Combine(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ys, weights, comm: EpComm, plan: EpPlan):
+        comm._push(plan.slot, plan, ys)              # every output row to the rank that owns its token
+        comm.barrier()
+        t, k = plan.tokens, plan.k
+        inbox = comm._inbox[plan.slot][: t * k]
+        weights = weights.float().contiguous()
+        out = _weighted_sum(inbox, weights, t, k)
+        if ctx.needs_input_grad[0] or ctx.needs_input_grad[1]:
+            ctx.save_for_backward(inbox.clone(), weights)   # the slot is reused two calls later
+        ctx.comm, ctx.plan = comm, plan
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        comm, plan = ctx.comm, ctx.plan
+        rows_in, weights = ctx.saved_tensors
+        t, k = plan.tokens, plan.k
+        d_rows_local = torch.empty_like(rows_in)
+        dweights = torch.empty((t, k), dtype=torch.float32, device=dout.device)
+        _lib.call("areno_moe_combine_bwd", dout.contiguous().data_ptr(), rows_in.data_ptr(),
+                  _identity(t * k, dout.device).data_ptr(), weights.data_ptr(), k, t * k, t * k, rows_in.shape[1],
+                  d_rows_local.data_ptr(), dweights.data_ptr(), _lib.stream())
+        slot = comm._next_slot()
+        comm._pub[slot][: t * k].copy_(d_rows_local)         # one row per route, for the expert owners to pull
+        comm.barrier()
+        d_ys = comm._pull(slot, plan, per_token=False)
+        comm.barrier()       # the pulls are done before anybody republishes (the next call may come at once)
+        return d_ys, dweights, None, None

@@ -60,7 +60,7 @@ _lib.register_signature("areno_mc_import", "ip")
 _lib.register_signature("areno_mc_add_device", "l")
 _lib.register_signature("areno_mc_bind", "lllp" + "p")
 _lib.register_signature("areno_mc_release", "lpli")
-_lib.register_signature("areno_tp_reduce_norm", "plppifilifip")
+_lib.register_signature("areno_tp_reduce_norm", "plppifilifiip")
 _lib.register_signature("areno_tp_barrier", "pp")
 
 
@@ -364,6 +364,16 @@ class TpComm:
         self.calls += 1
         return slot
 
+    def one_shot(self, rows: int) -> bool:
+        """One flag exchange and every rank reduces all rows itself, or the two-shot reduce-scatter + all-gather?
+        One-shot moves ``rows x H`` into each rank with multimem and ``(tp - 1)`` times that with plain loads, against
+        ``3 (tp - 1) / tp`` for two-shot: it wins always with multimem or two ranks, and for decode-sized calls, which
+        are bound by the flag round trip.  ``ARENO_TP_ONESHOT`` = 0 / 1 forces a choice."""
+        forced = os.environ.get("ARENO_TP_ONESHOT")
+        if forced in ("0", "1"):
+            return forced == "1"
+        return self.use_mc or self.tp == 2 or rows <= 1024
+
     def partial_view(self, slot: int, rows: int) -> torch.Tensor:
         lo = slot * self.slot_elems
         return self._part[lo: lo + rows * self.hidden].view(rows, self.hidden)
@@ -397,7 +407,8 @@ class TpComm:
         if residual is not None and not residual.is_contiguous():
             residual = residual.contiguous()
         _lib.call("areno_tp_reduce_norm", ctypes.addressof(self.desc), lo, _lib.ptr(residual), _lib.ptr(weight), wf32,
-                  float(w_offset), int(want_y), rows, n, float(eps), int(self.use_mc), _lib.stream())
+                  float(w_offset), int(want_y), rows, n, float(eps), int(self.use_mc), int(self.one_shot(rows)),
+                  _lib.stream())
         h = self._h[lo: lo + rows * n].view(rows, n)
         y = self._y[lo: lo + rows * n].view(rows, n) if want_y else None
         return y, h

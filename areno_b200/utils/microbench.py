@@ -317,8 +317,51 @@ def case_gemm_gated():
         f"M={m} I={inter} K={k}: gate/up GEMM with SiLU(gate) * up in the epilogue"
 
 
+def case_lm_head_lse(fused: bool = True):
+    """LM-head scoring of one 4096-row chunk: statistics from the GEMM epilogue (no logits tensor) against GEMM to
+    bf16 logits followed by the row-statistics kernel."""
+    from ..ops import gemm, logprob
+
+    m, n, k = 4096, 152064, 3584
+    h, w = _bf16(m, k), _bf16(n, k, scale=0.02)
+    t = torch.randint(0, n, (m,), device="cuda")
+
+    def run_fused():
+        logprob.fused_head_stats(h, w, t, 0, n)
+
+    def run_unfused():
+        logits = gemm.gemm(h, w)
+        logprob._stats(logits, t, 0)
+
+    nbytes = 2.0 * (m * k + n * k) + (0.0 if fused else 2.0 * 2.0 * m * n)
+    return (run_fused if fused else run_unfused), 2.0 * m * n * k, nbytes, \
+        f"M={m} N={n} K={k}: " + ("log-sum-exp statistics in the epilogue" if fused else "bf16 logits written and read back")
+
+
+def _tp_local_gemm(m, n, k):
+    from ..ops import gemm
+
+    a = _bf16(m, k)
+    ws = _rotating_weights(n, k)
+    out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+    state = {"i": 0}
+
+    def run():
+        w = ws[state["i"] % len(ws)]
+        state["i"] += 1
+        gemm.gemm(a, w, out=out)
+
+    return run, 2.0 * m * n * k, 2.0 * (m * k + n * k + m * n), f"M={m} N={n} K={k} (per-rank shape of a TP decode step)"
+
+
 CASES = {
     "decode_step": case_decode_step,
+    "lm_head_lse": case_lm_head_lse, "lm_head_unfused": lambda: case_lm_head_lse(False),
+    # per-rank GEMM shapes of a tensor-parallel decode step of the 7B model: tp 4 with 256 pooled rows, tp 8 with 512
+    "tp4_gate_up": lambda: _tp_local_gemm(256, 9472, 3584), "tp4_down": lambda: _tp_local_gemm(256, 3584, 4736),
+    "tp4_qkv": lambda: _tp_local_gemm(256, 1152, 3584), "tp4_o": lambda: _tp_local_gemm(256, 3584, 896),
+    "tp8_gate_up": lambda: _tp_local_gemm(512, 4736, 3584), "tp8_down": lambda: _tp_local_gemm(512, 3584, 2368),
+    "tp8_qkv": lambda: _tp_local_gemm(512, 768, 3584), "tp8_o": lambda: _tp_local_gemm(512, 3584, 512),
     "lightning_fwd": case_lightning_fwd, "lightning_bwd": case_lightning_bwd, "group_norm_gate": case_group_norm_gate,
     "gemm_gated": case_gemm_gated,
     "gemm_fwd": case_gemm_fwd, "gemm_dgrad": case_gemm_dgrad, "gemm_wgrad": case_gemm_wgrad,

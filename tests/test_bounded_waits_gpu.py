@@ -32,7 +32,8 @@ def _status(dev):
     return vals
 
 
-def test_fused_reduce_gives_up_on_a_silent_peer_and_publishes_nothing():
+@pytest.mark.parametrize("oneshot", [0, 1])
+def test_fused_reduce_gives_up_on_a_silent_peer_and_publishes_nothing(oneshot):
     dev = torch.device("cuda", 0)
     rows, H = 8, 1024
     flags0 = torch.zeros(64, dtype=torch.int32, device=dev)
@@ -45,14 +46,15 @@ def test_fused_reduce_gives_up_on_a_silent_peer_and_publishes_nothing():
     desc, keep = _desc(flags0, flags1, part, h, y, status, wait_ms=3)
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
-    _lib.call("areno_tp_reduce_norm", ctypes.addressof(desc), 0, None, None, 0, 0.0, 1, rows, H, 1e-6, 0, _lib.stream())
+    _lib.call("areno_tp_reduce_norm", ctypes.addressof(desc), 0, None, None, 0, 0.0, 1, rows, H, 1e-6, 0, oneshot, _lib.stream())
     end.record()
     vals = _status(dev)
     assert vals[0] == 7 and vals[2] == 1, vals          # code 7: the partial of peer 1 never became ready
     assert 2.0 < start.elapsed_time(end) < 500.0        # waited for the bound, not for ever
     assert torch.all(h == 7.0) and torch.all(y == 7.0)  # nothing was summed or published
     assert int(flags0[0]) == 1                          # the call counter still advanced: the next call is well-formed
-    assert int(flags1[8]) == 1 and int(flags1[16]) == 1  # both announcements reached the "peer"
+    assert int(flags1[8]) == 1                          # the announcement reached the "peer"
+    assert int(flags1[16]) == (0 if oneshot else 1)     # two-shot also announces (empty) publication, so nobody waits on it
     with pytest.raises(RuntimeError, match="status code=7"):
         status[0] = 7
         _lib.check_status(dev)

@@ -379,13 +379,13 @@ def test_lm_head_logprobs_fused_forward_and_gradients(softcap, monkeypatch):
     lp_r, ent_r, gx_r, gw_r = reference()
     with torch.no_grad():          # scoring path: statistics from the epilogue
         lp0, ent0 = lm_head_logprobs(head, base, t, chunk=128, need_entropy=True, softcap=softcap or None)
-    assert _rel_err(lp0, lp_r) < 5e-3 and _rel_err(ent0, ent_r) < 5e-3
+    assert _rel_err(lp0, lp_r) < 5e-3 and _rel_err(ent0, ent_r) < 1e-2
     for keep in ("0", "1"):        # training path with and without the logits kept from forward
         monkeypatch.setenv("ARENO_LOGPROB_KEEP_LOGITS", keep)
         x = base.clone().requires_grad_()
         head.weight.grad = None
         lp, ent = lm_head_logprobs(head, x, t, chunk=128, need_entropy=True, softcap=softcap or None)
-        assert _rel_err(lp, lp_r) < 5e-3 and _rel_err(ent, ent_r) < 5e-3
+        assert _rel_err(lp, lp_r) < 5e-3 and _rel_err(ent, ent_r) < 1e-2
         gx, gw = torch.autograd.grad([lp, ent], [x, head.weight], [g1, g2])
         assert _rel_err(gx, gx_r) < 3e-2 and _rel_err(gw, gw_r) < 3e-2
     _lib.check_status()

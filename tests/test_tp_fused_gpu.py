@@ -45,12 +45,14 @@ def _rank_main(rank, world, port, ret):
         g = torch.Generator(device=dev).manual_seed(100 + rank)
         shared = torch.Generator(device=dev).manual_seed(7)
         errs = []
-        modes = [False, True] if has_mc else [False]
+        # (multimem, one-shot): plain two-shot and one-shot always; both multimem variants where a mapping exists
+        modes = [(False, "0"), (False, "1")] + ([(True, "0"), (True, "1")] if has_mc else [])
         # decode-shaped (split-K), a single row, fewer rows than ranks, multi-tile, a prefill-sized chunk, and an
         # embedding-style call without residual
         shapes = [(64, 1792), (1, 9472), (3, 512), (300, 1792), (128, 9472), (2500, 896), (64, 1792), (17, 512)]
-        for use_mc in modes:
+        for use_mc, oneshot in modes:
             comm.use_mc = use_mc
+            os.environ["ARENO_TP_ONESHOT"] = oneshot
             for i, (rows, k_local) in enumerate(shapes):
                 x = torch.randn(rows, k_local, device=dev, generator=g).to(torch.bfloat16)
                 w = (torch.randn(H, k_local, device=dev, generator=g) * 0.05).to(torch.bfloat16)
@@ -72,6 +74,7 @@ def _rank_main(rank, world, port, ret):
                 both = [torch.empty_like(y) for _ in range(world)]
                 dist.all_gather(both, y, group=ctx.tp_group)
                 assert all(torch.equal(both[0], b) for b in both[1:])
+        os.environ.pop("ARENO_TP_ONESHOT", None)
         comm.barrier()
         torch.cuda.synchronize()
         _lib.check_status(dev)
