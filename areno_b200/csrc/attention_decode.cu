@@ -163,7 +163,10 @@ fold_rope_append_kernel(const float* __restrict__ ws, int splits, long long spli
 // ---------------------------------------------------------------------------------
 template <int D, bool FP8>
 struct DecodeSmem {
-  static constexpr int kStages = 3;
+  // fp8 pages are copied out of their stage into the expanded fp16 tiles before the MMAs, so a stage is free again
+  // early: two stages suffice there, which lets three CTAs share an SM (the kernel is latency-bound: half the bytes
+  // of bf16 pages for the same number of dependent steps per page)
+  static constexpr int kStages = FP8 ? 2 : 3;
   static constexpr int kTile = kPage * D * 2;                 // bf16 tile bytes
   static constexpr int kRaw = FP8 ? kPage * D : 0;            // fp8 staging bytes
   static constexpr int kStageBytes = FP8 ? 2 * kRaw + 2 * kPage * 4 : 2 * kTile;

@@ -204,6 +204,76 @@ __device__ __forceinline__ void store_row_f32(float* dst, const uint32_t (&r)[32
   }
 }
 
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// One 32-column chunk of a row for the log-sum-exp epilogue: x = accumulator rounded to bf16 (soft-capped and rounded
+// again when CAP), online update of (max, sum exp(x - max), sum exp(x - max) * x) and pick-up of the target logit.
+// The accumulations run as four independent chains and the exponent is one FMA + ex2; columns beyond `ncols`
+// (vocabulary padding) take a large negative finite value so that they add exact zeros.  `tj` is the target's column
+// relative to this chunk (outside [0, 32) when it lies elsewhere).
+template <bool CAP>
+__device__ __forceinline__ void lse_chunk(const uint32_t (&r)[32], int ncols, int tj, float cap, float& m, float& s,
+                                          float& sx, float& tg) {
+  constexpr float kLog2e = 1.4426950408889634f, kMasked = -1e30f;
+  float x[32];
+#pragma unroll
+  for (int j = 0; j < 32; j += 2) {
+    float a = __uint_as_float(r[j]), b = __uint_as_float(r[j + 1]);
+    if constexpr (CAP) {
+      const float inv = 1.f / cap;
+      a = cap * tanhf(__bfloat162float(__float2bfloat16_rn(a)) * inv);
+      b = cap * tanhf(__bfloat162float(__float2bfloat16_rn(b)) * inv);
+    }
+    const __nv_bfloat162 pk = __floats2bfloat162_rn(a, b);       // .x = a (low half), .y = b
+    const uint32_t u = *reinterpret_cast<const uint32_t*>(&pk);
+    x[j] = __uint_as_float(u << 16);
+    x[j + 1] = __uint_as_float(u & 0xffff0000u);
+  }
+  if (ncols < 32) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j >= ncols) x[j] = kMasked;
+  }
+  float c0 = fmaxf(x[0], x[1]), c1 = fmaxf(x[2], x[3]), c2 = fmaxf(x[4], x[5]), c3 = fmaxf(x[6], x[7]);
+#pragma unroll
+  for (int j = 8; j < 32; j += 4) {
+    c0 = fmaxf(c0, x[j]);
+    c1 = fmaxf(c1, x[j + 1]);
+    c2 = fmaxf(c2, x[j + 2]);
+    c3 = fmaxf(c3, x[j + 3]);
+  }
+  const float mn = fmaxf(m, fmaxf(fmaxf(c0, c1), fmaxf(c2, c3)));
+  const float ml2 = mn * kLog2e;
+  const float rescale = m == -INFINITY ? 0.f : ex2_approx(fmaf(m, kLog2e, -ml2));
+  float s0 = s * rescale, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  float t0 = sx * rescale, t1 = 0.f, t2 = 0.f, t3 = 0.f;
+#pragma unroll
+  for (int j = 0; j < 32; j += 4) {
+    const float e0 = ex2_approx(fmaf(x[j], kLog2e, -ml2)), e1 = ex2_approx(fmaf(x[j + 1], kLog2e, -ml2));
+    const float e2 = ex2_approx(fmaf(x[j + 2], kLog2e, -ml2)), e3 = ex2_approx(fmaf(x[j + 3], kLog2e, -ml2));
+    s0 += e0;
+    s1 += e1;
+    s2 += e2;
+    s3 += e3;
+    t0 = fmaf(e0, x[j], t0);
+    t1 = fmaf(e1, x[j + 1], t1);
+    t2 = fmaf(e2, x[j + 2], t2);
+    t3 = fmaf(e3, x[j + 3], t3);
+  }
+  s = (s0 + s1) + (s2 + s3);
+  sx = (t0 + t1) + (t2 + t3);
+  m = mn;
+  if (__any_sync(0xffffffffu, static_cast<unsigned>(tj) < 32u)) {   // rare: 32 rows, one target column each
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (tj == j) tg = x[j];
+  }
+}
+
 template <int BN, int STAGES, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
@@ -383,39 +453,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           store_row_f32(tw + c, r, 32, false);
         }
       } else if (p.epi == 6) {
-        const long long tgt = row < p.M ? p.lse_targets[row] - p.lse_vocab_start : -1;
+        const long long tgt = row < p.M ? p.lse_targets[row] - p.lse_vocab_start - n0 : -1;
+        const int tcol = tgt >= 0 && tgt < BN ? (int)tgt : -1;      // target column inside this tile, if any
         float m = -INFINITY, s = 0.f, sx = 0.f, tg = 0.f;
+        const bool capped = p.lse_softcap > 0.f;
 #pragma unroll 1
         for (int c = 0; c < BN; c += 32) {
-          const int col0 = n0 + c;
-          const int ncols = min(32, p.lse_valid - col0);
+          const int ncols = min(32, p.lse_valid - (n0 + c));
           if (ncols <= 0) break;      // the same for the whole warp
           uint32_t r[32];
           tmem_ld_32x32(t_row + c, r);
           tmem_ld_wait();
-          float x[32];
-          float cmax = -INFINITY;
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float v = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[j])));
-            if (p.lse_softcap > 0.f) v = __bfloat162float(__float2bfloat16_rn(p.lse_softcap * tanhf(v / p.lse_softcap)));
-            x[j] = j < ncols ? v : -INFINITY;
-            cmax = fmaxf(cmax, x[j]);
-            if (tgt == (long long)(col0 + j) && j < ncols) tg = v;
-          }
-          const float mn = fmaxf(m, cmax);
-          const float rescale = m == -INFINITY ? 0.f : __expf(m - mn);
-          s *= rescale;
-          sx *= rescale;
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if (j < ncols) {
-              const float e = __expf(x[j] - mn);
-              s += e;
-              sx += e * x[j];
-            }
-          }
-          m = mn;
+          if (capped) lse_chunk<true>(r, ncols, tcol - c, p.lse_softcap, m, s, sx, tg);
+          else lse_chunk<false>(r, ncols, tcol - c, 0.f, m, s, sx, tg);
         }
         if (row < p.M)
           *reinterpret_cast<float4*>(p.lse_out + ((size_t)(n0 / BN) * p.M + row) * 4) = make_float4(m, s, sx, tg);

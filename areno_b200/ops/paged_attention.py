@@ -158,7 +158,8 @@ def paged_decode(q, k_cache, v_cache, k_scale, v_scale, block_table, seq_lens, s
     # (sequence, kv head) pairs every CTA streams its whole context and writes the output itself, and
     # neither partials nor the merge kernel exist.  A split is never shorter than two pages.
     base = b * hkv * ((hq // hkv + 15) // 16)
-    want = max(1, min((2 * 148 + base // 2) // base, cap_pages // 2, 32))
+    # fp8 pages: three resident CTAs per SM and half the bytes per page, so the range is split one step further
+    want = max(1, min(((4 if fp8 else 2) * 148 + base // 2) // base, cap_pages // 2, 32))
     pages_per_split = (cap_pages + want - 1) // want
     nsplit = (cap_pages + pages_per_split - 1) // pages_per_split
     if out is None:

@@ -179,7 +179,7 @@ def run_dpo(args) -> None:
                        runtime=RuntimeConfig(activation_checkpointing=True, max_model_len=prompt_len + resp_len),
                        max_running_seqs=8, decode_progress_interval_s=0.0, seed=1234)
     worker = RankWorker(cfg, device)
-    trainer = Trainer.from_worker(worker, world_size=world)
+    trainer = Trainer.from_worker(worker, world_size=world, eos_ids=(0,))     # pad id for scoring batches
     trainer.ensure_roles({"ref": ModelRole("ref", "", trainable=False)})
     loss_fn = partial(dpo_loss_fn, beta=0.1)
     n_pairs = pairs_per_gpu * world
