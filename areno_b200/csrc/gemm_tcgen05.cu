@@ -16,6 +16,8 @@
 #include "common.cuh"
 #include "launch.h"
 
+#include <algorithm>
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -70,6 +72,10 @@ struct GemmParams {
   // and a small kernel folds them with the requested epilogue.
   int tail_first, tail_tiles, tail_splits, tail_kb;
   float* tail_ws;
+  // Weight-streaming GEMMs (few rows): number of B boxes (one k-block of one N tile) every CTA asks L2 to fetch
+  // for its own first work items BEFORE it waits for the previous kernel of the stream.  The weights do not depend
+  // on that kernel, so HBM keeps streaming while a short latency-bound kernel (norm, activation, rope) runs.
+  int b_prefetch;
   // Log-sum-exp epilogue (epi 6; LM head): nothing is stored for the [M, N] product.  Every row of a tile is
   // reduced on the fly to (max, sum exp(x - max), sum exp(x - max) x, x[target]) over the tile's columns below
   // `lse_valid`, with x rounded to bf16 first (and soft-capped when lse_softcap > 0), and written to
@@ -321,11 +327,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   // barriers, TMEM and descriptors are set up: let the next kernel start its own prologue, then wait for
   // the previous kernel's results (everything below reads or writes global memory)
   pdl_trigger();
-  pdl_wait();
-
   const int num_kb = (p.K + kBK - 1) / kBK;
   const int num_work = p.tail_splits > 0 ? p.tail_first + p.tail_tiles * p.tail_splits
                                          : p.tiles_m * p.tiles_n * p.splits * (p.group_mode == 2 ? p.num_groups : 1);
+  if constexpr (!B_MN) {
+    if (threadIdx.x == 0 && p.b_prefetch > 0) {
+      // plain mode only (the host sets b_prefetch for nothing else): decode_work reads nothing but `p`
+      int left = p.b_prefetch;
+      for (int work = blockIdx.x; work < num_work && left > 0; work += gridDim.x) {
+        const WorkItem wi = decode_work<BN>(p, work, num_kb);
+        for (int kb = wi.kb_lo; kb < wi.kb_hi && left > 0; ++kb, --left)
+          tma_prefetch_l2_2d(&tma_b, kb * kBK, wi.n0);
+      }
+    }
+  }
+  pdl_wait();
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -578,6 +594,15 @@ static int num_sms() {
   return n;
 }
 
+// ARENO_GEMM_L2_PREFETCH=0 switches the pre-wait weight prefetch off (for A/B timing).
+static bool l2_prefetch_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("ARENO_GEMM_L2_PREFETCH");
+    return v == nullptr || v[0] != '0';
+  }();
+  return on;
+}
+
 template <int BN, int STAGES, bool A_MN, bool B_MN>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream) {
   using S = GemmSmem<BN, STAGES>;
@@ -591,7 +616,14 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
   }
   int grid = p.tiles_m * p.tiles_n * p.splits;
   if (grid > num_sms()) grid = num_sms();
-  return static_cast<int>(launch_pdl(kern, dim3(grid), dim3(kGemmThreads), S::kTotal, stream, ta, tb, p));
+  GemmParams q = p;
+  q.b_prefetch = 0;
+  if (!B_MN && p.group_mode == 0 && p.gate_rows == 0 && p.M <= 4 * kBM && l2_prefetch_enabled()) {
+    // at most ~40 MB per launch: what L2 keeps beside the running kernel's own stream
+    const long long box = (long long)BN * kBK * 2;
+    q.b_prefetch = (int)std::min<long long>(4096, (40ll << 20) / (box * grid));
+  }
+  return static_cast<int>(launch_pdl(kern, dim3(grid), dim3(kGemmThreads), S::kTotal, stream, ta, tb, q));
 }
 
 template <bool A_MN, bool B_MN>

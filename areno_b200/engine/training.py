@@ -77,11 +77,10 @@ def pack_train_data(data_pack: dict[str, Any]) -> dict[str, Any]:
         "_action_index": aidx_t,
         "_seq_lengths": [int(x) for x in len_np],
     })
-    ref, values, returns = (data_pack.get(k) for k in ("ref_logprobs", "values", "returns"))
-    if all(isinstance(x, torch.Tensor) for x in (ref, values, returns)):
-        packed["packed_ref_logprobs"] = ref.detach().cpu()[a_rows, a_cols].float()
-        packed["packed_values"] = values.detach().cpu()[a_rows, a_cols].float()
-        packed["packed_returns"] = returns.detach().cpu()[a_rows, a_cols].float()
+    for key in ("ref_logprobs", "values", "returns"):        # each optional signal on its own
+        extra = data_pack.get(key)
+        if isinstance(extra, torch.Tensor):
+            packed["packed_" + key] = extra.detach().cpu()[a_rows, a_cols].float()
     return packed
 
 

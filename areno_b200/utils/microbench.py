@@ -260,6 +260,46 @@ def case_decode_step(batch: int = 64, ctx: int = 512):
     return run, 0.0, float(weights + kv), f"B={batch} ctx={ctx}, 7B shape, graph replay (weights {weights / 1e9:.1f} GB + KV {kv / 1e9:.2f} GB)"
 
 
+def case_train_microbatch(layers: int = 4, lens=(1536, 1408, 1152)):
+    """Forward + backward of one packed training micro-batch (4096 tokens in three sequences) through ``layers``
+    layers of the benchmark model plus its LM head and the per-token log-prob op, activations kept (no recompute):
+    the kernel sequence of a training step at a size that a profiler can walk."""
+    from ..engine.config import ModelConfig
+    from ..engine.logprobs import lm_head_logprobs
+    from ..models.dense import DenseCausalLM, TrainMeta, init_weights
+    from ..ops.attention import build_varlen_meta
+    from ..parallel.context import single_process_context
+
+    dev = torch.device("cuda", 0)
+    single_process_context(dev)
+    cfg = ModelConfig(model_type="qwen2", vocab_size=152064, hidden_size=3584, intermediate_size=18944,
+                      num_hidden_layers=layers, num_attention_heads=28, num_key_value_heads=4, head_dim=128, qkv_bias=True,
+                      qk_norm=False, tie_word_embeddings=False, rope_theta=1e6)
+    model = DenseCausalLM(cfg, device=dev)
+    init_weights(model, 0)
+    t = sum(lens)
+    ids = torch.randint(3, cfg.vocab_size, (t,), device=dev)
+    pos = torch.cat([torch.arange(n, device=dev) for n in lens])
+    keep = torch.ones(t, dtype=torch.bool, device=dev)
+    ends = torch.tensor(lens, device=dev).cumsum(0) - 1
+    keep[ends] = False                                   # the last token of a sequence predicts nothing
+    aidx = keep.nonzero().squeeze(1)
+    targets = ids.index_select(0, aidx + 1)
+    meta = TrainMeta(build_varlen_meta(list(lens), device=dev), activation_checkpointing=True, checkpoint_layers=0)
+    weight = torch.randn(aidx.numel(), device=dev)
+    per_layer = 3584 * (4608 + 3584 + 3 * 18944)
+    flops = 6.0 * t * per_layer * layers + 8.0 * aidx.numel() * 3584 * 152064   # LM head: logits recomputed in backward
+
+    def run():
+        out = model(ids, pos, meta)
+        lp = lm_head_logprobs(model.lm_head, out.hidden_states.index_select(0, aidx), targets, 4096)
+        (lp * weight).sum().backward()
+        for prm in model.parameters():
+            prm.grad = None
+
+    return run, flops, 0.0, f"{t} tokens in {len(lens)} sequences, {layers} layers of the 7B shape + LM head, forward + backward"
+
+
 def _lightning_inputs(seqs=16, length=1024, h=16, d=128):
     t = seqs * length
     wide = _bf16(t, 3 * h * d, scale=0.5)
@@ -356,6 +396,7 @@ def _tp_local_gemm(m, n, k):
 
 CASES = {
     "decode_step": case_decode_step,
+    "train_microbatch": case_train_microbatch,
     "lm_head_lse": case_lm_head_lse, "lm_head_unfused": lambda: case_lm_head_lse(False),
     # per-rank GEMM shapes of a tensor-parallel decode step of the 7B model: tp 4 with 256 pooled rows, tp 8 with 512
     "tp4_gate_up": lambda: _tp_local_gemm(256, 9472, 3584), "tp4_down": lambda: _tp_local_gemm(256, 3584, 4736),

@@ -37,7 +37,10 @@ def test_padded_rows_are_packed_with_per_action_signals_read_at_the_target_token
     assert p["packed_response_mask"].tolist() == [False, True, True, True, True, False, False, True, True, True]
     assert p["packed_advantages"].tolist() == pytest.approx([0.1, 0.2, 0.3, 0.7, 0.8, 1.3, 1.4, 1.5, 1.6, 1.7])
     assert p["packed_logprobs"][0].item() == pytest.approx(-0.01)
-    # an extra loss mask narrows the response mask; PPO extras are packed when all three are present
+    # a reference log-prob row on its own (DPO without values / returns) is packed too
+    p1 = pack_train_data(dict(src, ref_logprobs=src["logprobs"] * 2))
+    assert p1["packed_ref_logprobs"][0].item() == pytest.approx(-0.02) and "packed_values" not in p1
+    # an extra loss mask narrows the response mask; the PPO extras travel the same way
     src2 = dict(src, loss_mask=torch.ones(3, 6, dtype=torch.bool))
     src2["loss_mask"][0, 2] = False
     src2.update(ref_logprobs=src["logprobs"] * 2, values=src["advantages"], returns=src["advantages"] + 1)
