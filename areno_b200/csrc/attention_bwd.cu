@@ -44,7 +44,8 @@ attn_bwd_dkv_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
                     __nv_bfloat16* __restrict__ dk, __nv_bfloat16* __restrict__ dv, const int* __restrict__ cu_q,
                     const int* __restrict__ cu_k, const int* __restrict__ tile_prefix_k, int num_seqs, int hq,
                     int hkv, long long q_stride, long long k_stride, long long v_stride, long long do_stride,
-                    long long dk_stride, long long dv_stride, float scale, int causal, int window) {
+                    long long dk_stride, long long dv_stride, float scale, int causal, int window,
+                    float* __restrict__ ws, long long total_k) {
   constexpr int BT = 64;
   constexpr int CH = D / 8;
   constexpr int TILE = BT * D;
@@ -56,9 +57,15 @@ attn_bwd_dkv_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   float* sLse = reinterpret_cast<float*>(sdO + 2 * TILE);  // 2 x 64
   float* sDelta = sLse + 2 * BT;                           // 2 x 64
 
+  // With a workspace every CTA takes ONE query head of the group (blockIdx.y = kv head * group + head in group) and
+  // stores its fp32 partial of dK / dV; attn_dkv_reduce_kernel adds the heads of a group in a fixed order.  A key
+  // tile then costs a seventh of the loop at 28 / 4 heads, and the longest CTA no longer sets the kernel's time.
   const int tile = blockIdx.x;
-  const int kvh = blockIdx.y;
   const int group = hq / hkv;
+  const int hsplit = ws != nullptr ? group : 1;
+  const int kvh = blockIdx.y / hsplit;
+  const int h_first = blockIdx.y % hsplit;
+  const int heads_here = group / hsplit;
   const int seq = find_seq(tile_prefix_k, num_seqs, tile);
   if (seq < 0) return;
   const int k_tile = tile - tile_prefix_k[seq];
@@ -78,7 +85,7 @@ attn_bwd_dkv_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   const int qt_lo = q_lo / BT;
   const int qt_hi = (q_hi + BT - 1) / BT;           // exclusive
   const int n_qt = max(0, qt_hi - qt_lo);
-  const int n_iter = n_qt * group;
+  const int n_iter = n_qt * heads_here;
 
   const __nv_bfloat16* kp = k + (long long)(k_beg + kt0) * k_stride + (long long)kvh * D;
   const __nv_bfloat16* vp = v + (long long)(k_beg + kt0) * v_stride + (long long)kvh * D;
@@ -86,7 +93,7 @@ attn_bwd_dkv_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   load_tile_async<D, BT>(sV, vp, v_stride, lk - kt0);
 
   auto issue = [&](int it, int buf) {
-    const int hh = kvh * group + it / n_qt;
+    const int hh = kvh * group + h_first + it / n_qt;
     const int qs = (qt_lo + it % n_qt) * BT;
     const __nv_bfloat16* qp = q + (long long)(q_beg + qs) * q_stride + (long long)hh * D;
     const __nv_bfloat16* dop = d_o + (long long)(q_beg + qs) * do_stride + (long long)hh * D;
@@ -188,6 +195,23 @@ attn_bwd_dkv_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   }
   if (n_iter == 0) cp_async_wait<0>();
 
+  if (ws != nullptr) {
+    const long long row_w = (long long)hkv * D;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int key = key_a + h * 8;
+      if (key < lk) {
+        float* pk = ws + ((long long)h_first * total_k + k_beg + key) * row_w + (long long)kvh * D + c0 * 8;
+        float* pv = pk + (long long)group * total_k * row_w;
+#pragma unroll
+        for (int i = 0; i < DO / 8; ++i) {
+          *reinterpret_cast<float2*>(pk + i * 8 + t4 * 2) = make_float2(dk_acc[i][h * 2] * scale, dk_acc[i][h * 2 + 1] * scale);
+          *reinterpret_cast<float2*>(pv + i * 8 + t4 * 2) = make_float2(dv_acc[i][h * 2], dv_acc[i][h * 2 + 1]);
+        }
+      }
+    }
+    return;
+  }
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int key = key_a + h * 8;
@@ -201,6 +225,31 @@ attn_bwd_dkv_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
         *reinterpret_cast<uint32_t*>(pv + i * 8 + t4 * 2) = pack_bf16x2(dv_acc[i][h * 2], dv_acc[i][h * 2 + 1]);
       }
     }
+  }
+}
+
+// dK / dV = sum over the query heads of a group of the fp32 partials written by attn_bwd_dkv_kernel
+// (ws: [2][group][total_k][hkv * D]); one thread per four columns, heads added in index order.
+__global__ void __launch_bounds__(256)
+attn_dkv_reduce_kernel(const float* __restrict__ ws, __nv_bfloat16* __restrict__ dk, __nv_bfloat16* __restrict__ dv,
+                       long long total_k, int group, int row_w, int D, long long dk_stride, long long dv_stride) {
+  const long long per = total_k * (row_w / 4);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < 2 * per; i += (long long)gridDim.x * blockDim.x) {
+    const int which = i >= per;
+    const long long j = which ? i - per : i;
+    const long long token = j / (row_w / 4);
+    const int col = (int)(j % (row_w / 4)) * 4;
+    const float* p = ws + ((long long)which * group * total_k + token) * row_w + col;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int g = 0; g < group; ++g) {
+      const float4 v = __ldcs(reinterpret_cast<const float4*>(p + (long long)g * total_k * row_w));
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    __nv_bfloat16* out = (which ? dv + token * dv_stride : dk + token * dk_stride) + col;
+    uint2 o;
+    o.x = pack_bf16x2(acc.x, acc.y);
+    o.y = pack_bf16x2(acc.z, acc.w);
+    *reinterpret_cast<uint2*>(out) = o;
   }
 }
 
@@ -221,7 +270,9 @@ attn_bwd_dq_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   __nv_bfloat16* sK = sdO + TILE;      // 2 buffers
   __nv_bfloat16* sV = sK + 2 * TILE;   // 2 buffers
 
-  const int tile = blockIdx.x;
+  // causal: later query tiles see more keys, so the grid walks the tiles from the last to the first and the
+  // long CTAs start first (the short ones fill the tail of the last wave)
+  const int tile = causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
   const int head = blockIdx.y;
   const int kvh = head / (hq / hkv);
   const int seq = find_seq(tile_prefix, num_seqs, tile);
@@ -354,8 +405,8 @@ static int launch_bwd(const void* q, const void* k, const void* v, const void* o
                       const int* tile_prefix_q, const int* tile_prefix_k, int num_seqs, int total_q_tiles,
                       int total_k_tiles, long long total_q, int hq, int hkv, long long q_stride, long long k_stride,
                       long long v_stride, long long o_stride, long long do_stride, long long dq_stride,
-                      long long dk_stride, long long dv_stride, float scale, int causal, int window,
-                      cudaStream_t stream) {
+                      long long dk_stride, long long dv_stride, float scale, int causal, int window, float* dkv_ws,
+                      long long total_k, cudaStream_t stream) {
   constexpr int smem_kv = 6 * 64 * D * 2 + 4 * 64 * 4;
   constexpr int smem_q = 6 * 64 * D * 2;
   constexpr int DO = D > 128 ? 128 : D;
@@ -370,10 +421,19 @@ static int launch_bwd(const void* q, const void* k, const void* v, const void* o
   const long long nw = total_q * hq;
   attn_delta_kernel<<<(unsigned)((nw + 7) / 8), 256, 0, stream>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o,
                                                                   delta, total_q, hq, D, o_stride, do_stride);
-  attn_bwd_dkv_kernel<D, DO><<<dim3(total_k_tiles, hkv, NZ), 128, smem_kv, stream>>>(
+  const int group = hq / hkv;
+  if (group == 1 || total_k <= 0) dkv_ws = nullptr;
+  attn_bwd_dkv_kernel<D, DO><<<dim3(total_k_tiles, dkv_ws != nullptr ? hq : hkv, NZ), 128, smem_kv, stream>>>(
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (const __nv_bfloat16*)d_o, lse,
       delta, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, cu_q, cu_k, tile_prefix_k, num_seqs, hq, hkv, q_stride,
-      k_stride, v_stride, do_stride, dk_stride, dv_stride, scale, causal, window);
+      k_stride, v_stride, do_stride, dk_stride, dv_stride, scale, causal, window, dkv_ws, total_k);
+  if (dkv_ws != nullptr) {
+    const long long work = 2 * total_k * (hkv * D / 4);
+    long long blocks = (work + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    attn_dkv_reduce_kernel<<<(unsigned)blocks, 256, 0, stream>>>(dkv_ws, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, total_k,
+                                                                 group, hkv * D, D, dk_stride, dv_stride);
+  }
   attn_bwd_dq_kernel<D, DO><<<dim3(total_q_tiles, hq, NZ), 128, smem_q, stream>>>(
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (const __nv_bfloat16*)d_o, lse,
       delta, (__nv_bfloat16*)dq, cu_q, cu_k, tile_prefix_q, num_seqs, hq, hkv, q_stride, k_stride, v_stride,
@@ -385,27 +445,30 @@ static int launch_bwd(const void* q, const void* k, const void* v, const void* o
 
 using namespace areno;
 
-// `delta` is fp32 scratch of hq * total_q elements.
+// `delta` is fp32 scratch of hq * total_q elements.  `dkv_ws` (optional): fp32 scratch of
+// 2 * (hq / hkv) * total_k * hkv * head_dim elements; with it the dK / dV kernel runs one CTA per (key tile, query
+// head) and a second kernel adds the heads of every group (grouped-query attention only).
 extern "C" int areno_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
                               const float* lse, float* delta, void* dq, void* dk, void* dv, const int* cu_q,
                               const int* cu_k, const int* tile_prefix_q, const int* tile_prefix_k, int num_seqs,
                               int total_q_tiles, int total_k_tiles, long long total_q, int hq, int hkv, int head_dim,
                               long long q_stride, long long k_stride, long long v_stride, long long o_stride,
                               long long do_stride, long long dq_stride, long long dk_stride, long long dv_stride,
-                              float scale, int causal, int window, cudaStream_t stream) {
+                              float scale, int causal, int window, float* dkv_ws, long long total_k,
+                              cudaStream_t stream) {
   if (total_q <= 0) return 0;
   if (hq % hkv != 0) return -3;
   if (head_dim == 128)
     return launch_bwd<128>(q, k, v, o, d_o, lse, delta, dq, dk, dv, cu_q, cu_k, tile_prefix_q, tile_prefix_k,
                            num_seqs, total_q_tiles, total_k_tiles, total_q, hq, hkv, q_stride, k_stride, v_stride,
-                           o_stride, do_stride, dq_stride, dk_stride, dv_stride, scale, causal, window, stream);
+                           o_stride, do_stride, dq_stride, dk_stride, dv_stride, scale, causal, window, dkv_ws, total_k, stream);
   if (head_dim == 256)
     return launch_bwd<256>(q, k, v, o, d_o, lse, delta, dq, dk, dv, cu_q, cu_k, tile_prefix_q, tile_prefix_k,
                            num_seqs, total_q_tiles, total_k_tiles, total_q, hq, hkv, q_stride, k_stride, v_stride,
-                           o_stride, do_stride, dq_stride, dk_stride, dv_stride, scale, causal, window, stream);
+                           o_stride, do_stride, dq_stride, dk_stride, dv_stride, scale, causal, window, dkv_ws, total_k, stream);
   if (head_dim == 64)
     return launch_bwd<64>(q, k, v, o, d_o, lse, delta, dq, dk, dv, cu_q, cu_k, tile_prefix_q, tile_prefix_k,
                           num_seqs, total_q_tiles, total_k_tiles, total_q, hq, hkv, q_stride, k_stride, v_stride,
-                          o_stride, do_stride, dq_stride, dk_stride, dv_stride, scale, causal, window, stream);
+                          o_stride, do_stride, dq_stride, dk_stride, dv_stride, scale, causal, window, dkv_ws, total_k, stream);
   return -2;
 }

@@ -163,20 +163,31 @@ fold_rope_append_kernel(const float* __restrict__ ws, int splits, long long spli
 // ---------------------------------------------------------------------------------
 template <int D, bool FP8>
 struct DecodeSmem {
-  // fp8 pages are copied out of their stage into the expanded fp16 tiles before the MMAs, so a stage is free again
-  // early: two stages suffice there, which lets three CTAs share an SM (the kernel is latency-bound: half the bytes
-  // of bf16 pages for the same number of dependent steps per page)
-  static constexpr int kStages = FP8 ? 2 : 3;
+  // fp8 pages stay as bytes in shared memory and are expanded to fp16 in registers, fragment by fragment, so there
+  // is no second copy of a page and no extra barrier: a stage is half the size of a bf16 stage and four of them
+  // (three pages in flight per CTA, three CTAs per SM) keep as many bytes in flight as the bf16 pipeline does
+  static constexpr int kStages = FP8 ? 4 : 3;
   static constexpr int kTile = kPage * D * 2;                 // bf16 tile bytes
-  static constexpr int kRaw = FP8 ? kPage * D : 0;            // fp8 staging bytes
-  static constexpr int kStageBytes = FP8 ? 2 * kRaw + 2 * kPage * 4 : 2 * kTile;
-  static constexpr int kDeq = FP8 ? 2 * kTile : 0;            // dequantised K, V tiles
-  static constexpr int kQ = 16 * D * 2;
+  static constexpr int kRaw = FP8 ? kPage * D : 0;            // fp8 page bytes (K or V)
+  static constexpr int kStageBytes = FP8 ? 2 * kRaw + 2 * kPage * 4 : 2 * kTile;   // fp8: K, V, k scales, v scales
+  static constexpr int kQ = FP8 ? 0 : 16 * D * 2;             // fp8: q lives in registers
   static constexpr int kMerge = 4 * 16 * (D + 2) * 4;         // per-warp partial O, m, l (fp32)
   // the merge buffer aliases the (by then idle) pipeline stages
   static_assert(kMerge <= kStages * kStageBytes, "merge buffer must fit in the stage area");
-  static constexpr int kTotal = kStages * kStageBytes + kDeq + kQ;
+  static constexpr int kTotal = kStages * kStageBytes + kQ;
 };
+
+// Position of 16-byte chunk `c` of row `r` inside a row of an fp8 page in shared memory: the XOR spreads the eight
+// rows that one quarter-warp (K fragments) or one ldmatrix phase (V fragments) touches over all banks.
+template <int CHB>
+__device__ __forceinline__ int fp8_chunk(int r, int c) {
+  return CHB >= 8 ? (c ^ (((r & 1) << 2) | ((r >> 1) & 3))) : c;
+}
+__device__ __forceinline__ uint32_t prmt_u32(uint32_t a, uint32_t sel) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %1, %2;" : "=r"(r) : "r"(a), "r"(sel));
+  return r;
+}
 
 template <int D, bool FP8>
 __global__ void __launch_bounds__(128)
@@ -192,10 +203,9 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const void* __restrict_
   pdl_trigger();
   pdl_wait();
   uint8_t* stage_base = smem_attn;
-  __nv_bfloat16* deqK = reinterpret_cast<__nv_bfloat16*>(smem_attn + SM::kStages * SM::kStageBytes);
-  __nv_bfloat16* deqV = deqK + kPage * D;
-  __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_attn + SM::kStages * SM::kStageBytes + SM::kDeq);
+  __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_attn + SM::kStages * SM::kStageBytes);   // bf16 path only
   float* sMerge = reinterpret_cast<float*>(stage_base);
+  constexpr int CHB = D / 16;      // 16-byte chunks per row of an fp8 page
 
   const int b = blockIdx.x;
   const int group = hq / hkv;
@@ -217,32 +227,53 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const void* __restrict_
   const int n_pages = max(0, page_hi - page_lo);
 
   // Q tile: 16 rows (q heads of the group, zero padded) x D
-  for (int idx = threadIdx.x; idx < 16 * CH; idx += 128) {
-    const int r = idx / CH, ch = idx % CH;
-    uint4 val = make_uint4(0, 0, 0, 0);
-    if (r < rows_valid) val = *reinterpret_cast<const uint4*>(q + (long long)b * q_stride + (long long)(head0 + r) * D + ch * 8);
-    if constexpr (FP8) {
-      // the fp8 cache is expanded to fp16 (exact), so q joins it in fp16 and the MMAs run on fp16 operands
-      uint32_t u[4] = {val.x, val.y, val.z, val.w};
+  // fp8: q goes to registers as fp16 A fragments (e4m3 expands to fp16 exactly, so the MMAs run on fp16).  The
+  // contraction index is permuted so that one 16-byte load of a K row feeds four MMA steps: step (j, s) of lane
+  // quarter t4 covers channels j * 64 + 16 * t4 + 4 * s + {0, 1} (first half of k) and + {2, 3} (second half).
+  uint32_t qf[FP8 ? D / 64 : 1][4][4];
+  if constexpr (FP8) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 f = unpack_bf16x2(u[j]);
-        u[j] = pack_f16x2(f.x, f.y);
+    for (int j = 0; j < D / 64; ++j) {
+#pragma unroll
+      for (int hr = 0; hr < 2; ++hr) {
+        const int r = g + hr * 8;
+        uint4 lo = make_uint4(0, 0, 0, 0), hi = make_uint4(0, 0, 0, 0);
+        if (r < rows_valid) {
+          const __nv_bfloat16* qp = q + (long long)b * q_stride + (long long)(head0 + r) * D + j * 64 + 16 * t4;
+          lo = *reinterpret_cast<const uint4*>(qp);
+          hi = *reinterpret_cast<const uint4*>(qp + 8);
+        }
+        const uint32_t u[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+        for (int sidx = 0; sidx < 4; ++sidx) {
+          const float2 f0 = unpack_bf16x2(u[2 * sidx]), f1 = unpack_bf16x2(u[2 * sidx + 1]);
+          qf[j][sidx][hr] = pack_f16x2(f0.x, f0.y);
+          qf[j][sidx][2 + hr] = pack_f16x2(f1.x, f1.y);
+        }
       }
-      val = make_uint4(u[0], u[1], u[2], u[3]);
     }
-    *reinterpret_cast<uint4*>(sQ + swz<CH>(r, ch)) = val;
+  } else {
+    for (int idx = threadIdx.x; idx < 16 * CH; idx += 128) {
+      const int r = idx / CH, ch = idx % CH;
+      uint4 val = make_uint4(0, 0, 0, 0);
+      if (r < rows_valid) val = *reinterpret_cast<const uint4*>(q + (long long)b * q_stride + (long long)(head0 + r) * D + ch * 8);
+      *reinterpret_cast<uint4*>(sQ + swz<CH>(r, ch)) = val;
+    }
   }
 
-  auto issue = [&](int pi, int st) {
-    const int page = block_table[(long long)b * max_pages + page_lo + pi];
+  // Page ids come from the block table in global memory; a load inside the loop would put its latency in front
+  // of every copy.  The ids of the first pages are fetched together, later ones one iteration before their use.
+  const int* bt = block_table + (long long)b * max_pages + page_lo;
+  auto issue = [&](int page, int st) {
     uint8_t* sb = stage_base + st * SM::kStageBytes;
     if constexpr (FP8) {
       const uint8_t* kp = reinterpret_cast<const uint8_t*>(k_cache) + ((long long)page * hkv + kvh) * kPage * D;
       const uint8_t* vp = reinterpret_cast<const uint8_t*>(v_cache) + ((long long)page * hkv + kvh) * kPage * D;
-      for (int idx = threadIdx.x; idx < kPage * D / 16; idx += 128) {
-        cp_async16(sb + idx * 16, kp + idx * 16);
-        cp_async16(sb + SM::kRaw + idx * 16, vp + idx * 16);
+      for (int idx = threadIdx.x; idx < kPage * CHB; idx += 128) {
+        const int r = idx / CHB, c = idx % CHB;
+        const int off = r * D + fp8_chunk<CHB>(r, c) * 16;
+        cp_async16(sb + off, kp + idx * 16);
+        cp_async16(sb + SM::kRaw + off, vp + idx * 16);
       }
       if (threadIdx.x < kPage / 4) {
         const long long srow = ((long long)page * hkv + kvh) * kPage;
@@ -257,11 +288,15 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const void* __restrict_
     }
   };
 
+  int first_pages[SM::kStages];
+#pragma unroll
+  for (int s = 0; s < SM::kStages; ++s) first_pages[s] = s < n_pages ? bt[s] : 0;
 #pragma unroll
   for (int s = 0; s < SM::kStages - 1; ++s) {
-    if (s < n_pages) issue(s, s);
+    if (s < n_pages) issue(first_pages[s], s);
     cp_async_commit();
   }
+  int page_next = first_pages[SM::kStages - 1];      // id of page pi + kStages - 1 at the top of iteration pi
 
   float o_acc[D / 8][4];
 #pragma unroll
@@ -271,68 +306,69 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const void* __restrict_
 
   for (int pi = 0; pi < n_pages; ++pi) {
     const int st = pi % SM::kStages;
-    if (pi + SM::kStages - 1 < n_pages) issue(pi + SM::kStages - 1, (pi + SM::kStages - 1) % SM::kStages);
-    cp_async_commit();
-    cp_async_wait<SM::kStages - 1>();
-    __syncthreads();
-    const uint8_t* sb = stage_base + st * SM::kStageBytes;
-    const __nv_bfloat16* cK;
-    const __nv_bfloat16* cV;
     if constexpr (FP8) {
-      const float* ks = reinterpret_cast<const float*>(sb + 2 * SM::kRaw);
-      const float* vs = ks + kPage;
-      for (int idx = threadIdx.x; idx < kPage * CH; idx += 128) {
-        const int r = idx / CH, ch = idx % CH;
-        const uint2 rk = *reinterpret_cast<const uint2*>(sb + r * D + ch * 8);
-        const uint2 rv = *reinterpret_cast<const uint2*>(sb + SM::kRaw + r * D + ch * 8);
-        // e4m3 -> fp16 is exact and one instruction per pair; the per-token scale is applied in fp16
-        const uint32_t sk = pack_f16x2(ks[r], ks[r]), sv = pack_f16x2(vs[r], vs[r]);
-        uint32_t ok[4], ov[4];
-        ok[0] = hmul2_u32(cvt_e4m3x2_f16x2(rk.x), sk);
-        ok[1] = hmul2_u32(cvt_e4m3x2_f16x2(rk.x >> 16), sk);
-        ok[2] = hmul2_u32(cvt_e4m3x2_f16x2(rk.y), sk);
-        ok[3] = hmul2_u32(cvt_e4m3x2_f16x2(rk.y >> 16), sk);
-        ov[0] = hmul2_u32(cvt_e4m3x2_f16x2(rv.x), sv);
-        ov[1] = hmul2_u32(cvt_e4m3x2_f16x2(rv.x >> 16), sv);
-        ov[2] = hmul2_u32(cvt_e4m3x2_f16x2(rv.y), sv);
-        ov[3] = hmul2_u32(cvt_e4m3x2_f16x2(rv.y >> 16), sv);
-        *reinterpret_cast<uint4*>(deqK + swz<CH>(r, ch)) = make_uint4(ok[0], ok[1], ok[2], ok[3]);
-        *reinterpret_cast<uint4*>(deqV + swz<CH>(r, ch)) = make_uint4(ov[0], ov[1], ov[2], ov[3]);
-      }
+      // one barrier per page: after it every thread has left page pi - 1, whose stage the next copy overwrites
+      cp_async_wait<SM::kStages - 2>();
       __syncthreads();
-      cK = deqK;
-      cV = deqV;
+      const int page_now = page_next;
+      if (pi + SM::kStages < n_pages) page_next = bt[pi + SM::kStages];
+      if (pi + SM::kStages - 1 < n_pages) issue(page_now, (pi + SM::kStages - 1) % SM::kStages);
+      cp_async_commit();
     } else {
-      cK = reinterpret_cast<const __nv_bfloat16*>(sb);
-      cV = reinterpret_cast<const __nv_bfloat16*>(sb + SM::kTile);
+      const int page_now = page_next;
+      if (pi + SM::kStages < n_pages) page_next = bt[pi + SM::kStages];
+      if (pi + SM::kStages - 1 < n_pages) issue(page_now, (pi + SM::kStages - 1) % SM::kStages);
+      cp_async_commit();
+      cp_async_wait<SM::kStages - 1>();
+      __syncthreads();
     }
+    const uint8_t* sb = stage_base + st * SM::kStageBytes;
+    const __nv_bfloat16* cK = reinterpret_cast<const __nv_bfloat16*>(sb);
+    const __nv_bfloat16* cV = reinterpret_cast<const __nv_bfloat16*>(sb + SM::kTile);
+    const float* ksc = reinterpret_cast<const float*>(sb + 2 * SM::kRaw);      // fp8: per-token scales of the page
+    const float* vsc = ksc + kPage;
 
     // this warp: keys [warp*16, warp*16+16) of the page
     const int key0 = (page_lo + pi) * kPage + warp * 16;
     if (key0 < ctx && key0 + 16 > first_key) {
       float s[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
+      if constexpr (FP8) {
 #pragma unroll
-      for (int ks = 0; ks < D / 16; ++ks) {
-        uint32_t a[4], bb[4];
-        ldsm_a<CH>(a, sQ, 0, ks * 2, lane);
-        ldsm_b_nt<CH>(bb, cK, warp * 16, ks * 2, lane);
-        if constexpr (FP8) {
-          mma_f16(s[0], a, bb[0], bb[1]);
-          mma_f16(s[1], a, bb[2], bb[3]);
-        } else {
+        for (int nt = 0; nt < 2; ++nt) {
+          const int r = warp * 16 + nt * 8 + g;
+#pragma unroll
+          for (int j = 0; j < D / 64; ++j) {
+            const uint4 kw = *reinterpret_cast<const uint4*>(sb + r * D + fp8_chunk<CHB>(r, j * 4 + t4) * 16);
+            const uint32_t w[4] = {kw.x, kw.y, kw.z, kw.w};
+#pragma unroll
+            for (int sidx = 0; sidx < 4; ++sidx)
+              mma_f16(s[nt], qf[j][sidx], cvt_e4m3x2_f16x2(w[sidx]), cvt_e4m3x2_f16x2(w[sidx] >> 16));
+          }
+#pragma unroll
+          for (int e = 0; e < 4; ++e) s[nt][e] *= ksc[warp * 16 + nt * 8 + t4 * 2 + (e & 1)];
+        }
+      } else {
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          uint32_t a[4], bb[4];
+          ldsm_a<CH>(a, sQ, 0, ks * 2, lane);
+          ldsm_b_nt<CH>(bb, cK, warp * 16, ks * 2, lane);
           mma_bf16(s[0], a, bb[0], bb[1]);
           mma_bf16(s[1], a, bb[2], bb[3]);
         }
       }
-      float mx[2] = {-INFINITY, -INFINITY};
+      if (key0 + 16 > ctx || key0 < first_key) {      // only the pages at the two ends of the range have masked keys
 #pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
+        for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int c = key0 + nt * 8 + t4 * 2 + (e & 1);
-          if (c >= ctx || c < first_key) s[nt][e] = -INFINITY;
-          mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
-        }
+          for (int e = 0; e < 4; ++e) {
+            const int c = key0 + nt * 8 + t4 * 2 + (e & 1);
+            if (c >= ctx || c < first_key) s[nt][e] = -INFINITY;
+          }
+      }
+      float mx[2];
+      mx[0] = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+      mx[1] = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
       float corr[2], m_use[2];
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
@@ -353,30 +389,57 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const void* __restrict_
         const float p3 = exp2f((s[nt][3] - m_use[1]) * scale_log2);
         rs[0] += p0 + p1;
         rs[1] += p2 + p3;
-        pf[nt * 2 + 0] = FP8 ? pack_f16x2(p0, p1) : pack_bf16x2(p0, p1);
-        pf[nt * 2 + 1] = FP8 ? pack_f16x2(p2, p3) : pack_bf16x2(p2, p3);
+        if constexpr (FP8) {
+          // the per-token scale of V rides on P (the row sums above use the unscaled probabilities)
+          const float v0 = vsc[warp * 16 + nt * 8 + t4 * 2], v1 = vsc[warp * 16 + nt * 8 + t4 * 2 + 1];
+          pf[nt * 2 + 0] = pack_f16x2(p0 * v0, p1 * v1);
+          pf[nt * 2 + 1] = pack_f16x2(p2 * v0, p3 * v1);
+        } else {
+          pf[nt * 2 + 0] = pack_bf16x2(p0, p1);
+          pf[nt * 2 + 1] = pack_bf16x2(p2, p3);
+        }
       }
       l_run[0] = l_run[0] * corr[0] + rs[0];
       l_run[1] = l_run[1] * corr[1] + rs[1];
+      // the running maxima settle after the first pages; the accumulators are rescaled only when one moved
+      if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {
 #pragma unroll
-      for (int i = 0; i < D / 8; ++i) {
-        o_acc[i][0] *= corr[0]; o_acc[i][1] *= corr[0];
-        o_acc[i][2] *= corr[1]; o_acc[i][3] *= corr[1];
+        for (int i = 0; i < D / 8; ++i) {
+          o_acc[i][0] *= corr[0]; o_acc[i][1] *= corr[0];
+          o_acc[i][2] *= corr[1]; o_acc[i][3] *= corr[1];
+        }
       }
+      if constexpr (FP8) {
+        // V fragments: a transposing ldmatrix over the page's BYTES read as 16-bit elements hands every lane, for
+        // its two keys, the byte pair of channels (2g, 2g + 1) of a 16-channel chunk; a byte permute separates the
+        // even and the odd channel, which become two n-tiles.  Accumulator tile 2c + par, element e of lane
+        // quarter t4 therefore holds channel c * 16 + 4 * t4 + 2 * (e & 1) + par.
+        const uint8_t* sV8 = sb + SM::kRaw;
+        const int mat = lane >> 3;
+        const int vrow = warp * 16 + (mat & 1) * 8 + (lane & 7);
 #pragma unroll
-      for (int dt = 0; dt < D / 16; ++dt) {
-        uint32_t bb[4];
-        ldsm_b_t<CH>(bb, cV, warp * 16, dt * 2, lane);
-        if constexpr (FP8) {
-          mma_f16(o_acc[2 * dt], pf, bb[0], bb[1]);
-          mma_f16(o_acc[2 * dt + 1], pf, bb[2], bb[3]);
-        } else {
+        for (int cp = 0; cp < CHB / 2; ++cp) {
+          uint32_t rr[4];
+          ldsm_x4_t(rr, sV8 + vrow * D + fp8_chunk<CHB>(vrow, cp * 2 + (mat >> 1)) * 16);
+#pragma unroll
+          for (int hc = 0; hc < 2; ++hc) {
+            const int c = cp * 2 + hc;
+            const uint32_t u0 = prmt_u32(rr[hc * 2], 0x3120u), u1 = prmt_u32(rr[hc * 2 + 1], 0x3120u);
+            mma_f16(o_acc[2 * c], pf, cvt_e4m3x2_f16x2(u0), cvt_e4m3x2_f16x2(u1));
+            mma_f16(o_acc[2 * c + 1], pf, cvt_e4m3x2_f16x2(u0 >> 16), cvt_e4m3x2_f16x2(u1 >> 16));
+          }
+        }
+      } else {
+#pragma unroll
+        for (int dt = 0; dt < D / 16; ++dt) {
+          uint32_t bb[4];
+          ldsm_b_t<CH>(bb, cV, warp * 16, dt * 2, lane);
           mma_bf16(o_acc[2 * dt], pf, bb[0], bb[1]);
           mma_bf16(o_acc[2 * dt + 1], pf, bb[2], bb[3]);
         }
       }
     }
-    __syncthreads();
+    if constexpr (!FP8) __syncthreads();
   }
   cp_async_wait<0>();
   __syncthreads();
@@ -393,8 +456,10 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const void* __restrict_
     const int r = g + h * 8;
 #pragma unroll
     for (int i = 0; i < D / 8; ++i) {
-      wbuf[r * (D + 2) + i * 8 + t4 * 2] = o_acc[i][h * 2];
-      wbuf[r * (D + 2) + i * 8 + t4 * 2 + 1] = o_acc[i][h * 2 + 1];
+      // channel of element 0 of this tile (bf16: consecutive pairs; fp8: see the V fragments above)
+      const int d0 = FP8 ? (i >> 1) * 16 + 4 * t4 + (i & 1) : i * 8 + t4 * 2;
+      wbuf[r * (D + 2) + d0] = o_acc[i][h * 2];
+      wbuf[r * (D + 2) + d0 + (FP8 ? 2 : 1)] = o_acc[i][h * 2 + 1];
     }
     if (t4 == 0) {
       wbuf[r * (D + 2) + D] = m_run[h];

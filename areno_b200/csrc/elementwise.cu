@@ -431,6 +431,50 @@ rope_kernel(__nv_bfloat16* __restrict__ x, const int* __restrict__ positions, co
   }
 }
 
+// The same rotation for the usual layout (rotate-half pairing, 16-byte aligned heads, rot_dim a multiple of 16):
+// one thread owns eight consecutive frequencies of one token, computes their sines and cosines once and applies
+// them to `kHeadsPerThread` heads with 16-byte loads and stores.  The sine / cosine expressions are the ones of
+// rope_kernel, so both kernels give the same bits.
+constexpr int kRopeHeadsPerThread = 4;
+__global__ void __launch_bounds__(256)
+rope_vec_kernel(__nv_bfloat16* __restrict__ x, const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                long long tokens, int heads, int head_dim, int rot_dim, long long row_stride, float theta, float sign) {
+  const int half = rot_dim >> 1;
+  const int chunks = half >> 3;
+  const int hgroups = (heads + kRopeHeadsPerThread - 1) / kRopeHeadsPerThread;
+  const long long total = tokens * hgroups * chunks;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int ch = (int)(idx % chunks);
+    const long long r = idx / chunks;
+    const int hg = (int)(r % hgroups);
+    const long long t = r / hgroups;
+    const float pos = (float)positions[t];
+    float c[8], sn[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int i = ch * 8 + j;
+      const float f = inv_freq != nullptr ? inv_freq[i] : __powf(theta, -2.f * (float)i / (float)rot_dim);
+      sincosf(pos * f, &sn[j], &c[j]);
+      sn[j] *= sign;
+    }
+    const int h_end = min(heads, (hg + 1) * kRopeHeadsPerThread);
+    for (int hd = hg * kRopeHeadsPerThread; hd < h_end; ++hd) {
+      __nv_bfloat16* p = x + t * row_stride + (long long)hd * head_dim + ch * 8;
+      float a[8], b[8], oa[8], ob[8];
+      load8(p, a);
+      load8(p + half, b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        oa[j] = a[j] * c[j] - b[j] * sn[j];
+        ob[j] = b[j] * c[j] + a[j] * sn[j];
+      }
+      store8(p, oa);
+      store8(p + half, ob);
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------
 // Vocab-parallel embedding: out[t] = ids[t] in [v0, v1) ? table[ids[t]-v0] : 0
 // backward: dtable[ids[t]-v0] += dout[t]  (fp32 atomics into the main-grad buffer)
@@ -585,6 +629,13 @@ extern "C" int areno_rope(void* x, const int* positions, const float* inv_freq, 
                           int head_dim, int rot_dim, long long row_stride, float theta, float sign,
                           int interleaved, cudaStream_t stream) {
   if (tokens <= 0) return 0;
+  if (!interleaved && rot_dim % 16 == 0 && head_dim % 8 == 0 && row_stride % 8 == 0 &&
+      (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    const long long threads = tokens * ((heads + kRopeHeadsPerThread - 1) / kRopeHeadsPerThread) * (rot_dim / 16);
+    rope_vec_kernel<<<grid_for(threads, 256), 256, 0, stream>>>((__nv_bfloat16*)x, positions, inv_freq, tokens, heads,
+                                                                head_dim, rot_dim, row_stride, theta, sign);
+    return (int)cudaGetLastError();
+  }
   rope_kernel<<<grid_for(tokens * heads * (rot_dim / 2), 256), 256, 0, stream>>>(
       (__nv_bfloat16*)x, positions, inv_freq, tokens, heads, head_dim, rot_dim, row_stride, theta, sign,
       interleaved);

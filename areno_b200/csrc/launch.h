@@ -59,5 +59,5 @@ int areno_attn_bwd(const void* q, const void* k, const void* v, const void* o, c
                    int total_k_tiles, long long total_q, int hq, int hkv, int head_dim, long long q_stride,
                    long long k_stride, long long v_stride, long long o_stride, long long do_stride,
                    long long dq_stride, long long dk_stride, long long dv_stride, float scale, int causal,
-                   int window, cudaStream_t stream);
+                   int window, float* dkv_ws, long long total_k, cudaStream_t stream);
 }

@@ -41,7 +41,7 @@ _SIGNATURES: dict[str, str] = {
     "areno_accumulate_bf16": "pplp",
     "areno_attn_fwd": "pppppppp" + "iiiii" + "llll" + "fiip",
     "areno_attn_fwd_tc": "pppppppp" + "iiiii" + "llllll" + "fi" + "pp",
-    "areno_attn_bwd": "pppppppppp" + "pppp" + "iii" + "l" + "iii" + "llllllll" + "fiip",
+    "areno_attn_bwd": "pppppppppp" + "pppp" + "iii" + "l" + "iii" + "llllllll" + "fiiplp",
     "areno_gemm_workspace_bytes": "iii",
     "areno_headnorm_fwd": "plpifplpliifp",
     "areno_headnorm_bwd_blocks": "l",
@@ -117,7 +117,7 @@ def fn(name: str):
 
 
 # Kernel launches issued through this module (an entry point may launch more than one kernel).
-_KERNELS_PER_CALL = {"areno_attn_bwd": 3, "areno_paged_decode": 2, "areno_rmsnorm_bwd": 2, "areno_sumsq": 2,
+_KERNELS_PER_CALL = {"areno_attn_bwd": 4, "areno_paged_decode": 2, "areno_rmsnorm_bwd": 2, "areno_sumsq": 2,
                      "areno_headnorm_bwd": 2}
 launch_count = 0
 

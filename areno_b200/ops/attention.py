@@ -147,6 +147,10 @@ def attention_backward(q, k, v, o, do, lse, meta: VarlenMeta, scale, causal, win
     if do.stride(2) != 1 or do.stride(1) != d:
         do = do.contiguous()
     delta = torch.empty((hq, tq), dtype=torch.float32, device=q.device)
+    # grouped-query attention: dK / dV are computed per query head (seven times the CTAs at 28 / 4 heads, no
+    # CTA that loops over the whole group) and summed over the group from this fp32 scratch
+    tk, group = k.shape[0], hq // hkv
+    ws = torch.empty((2, group, tk, hkv * d), dtype=torch.float32, device=q.device) if group > 1 else None
     _lib.call(
         "areno_attn_bwd",
         q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(), delta.data_ptr(),
@@ -154,7 +158,7 @@ def attention_backward(q, k, v, o, do, lse, meta: VarlenMeta, scale, causal, win
         meta.cu_q.data_ptr(), meta.cu_k.data_ptr(), meta.tile_prefix_q.data_ptr(), meta.tile_prefix_k.data_ptr(),
         meta.num_seqs, meta.total_q_tiles, meta.total_k_tiles, meta.total_q, hq, hkv, d,
         q.stride(0), k.stride(0), v.stride(0), o.stride(0), do.stride(0), dq.stride(0), dk.stride(0), dv.stride(0),
-        float(scale), int(causal), int(window or 0), _lib.stream(),
+        float(scale), int(causal), int(window or 0), ws.data_ptr() if ws is not None else None, tk, _lib.stream(),
     )
 
 

@@ -10,6 +10,8 @@ Replaces ``flash_attn_with_kvcache`` and the index_put KV scatter of the referen
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import _lib
@@ -138,6 +140,10 @@ def paged_decode_reference(q, k_cache, v_cache, k_scale, v_scale, block_table, s
 _SCRATCH: dict = {}
 
 
+# ARENO_DECODE_SPLITS=n forces the number of KV splits of the decode kernel (tuning aid; 0 = heuristic)
+_FORCED_SPLITS = int(os.environ.get("ARENO_DECODE_SPLITS", "0") or 0)
+
+
 def paged_decode(q, k_cache, v_cache, k_scale, v_scale, block_table, seq_lens, scale, max_context: int | None = None,
                  window: int = 0, out=None, scratch=None):
     """Decode attention for one new token per sequence.
@@ -158,8 +164,9 @@ def paged_decode(q, k_cache, v_cache, k_scale, v_scale, block_table, seq_lens, s
     # (sequence, kv head) pairs every CTA streams its whole context and writes the output itself, and
     # neither partials nor the merge kernel exist.  A split is never shorter than two pages.
     base = b * hkv * ((hq // hkv + 15) // 16)
-    # fp8 pages: three resident CTAs per SM and half the bytes per page, so the range is split one step further
-    want = max(1, min(((4 if fp8 else 2) * 148 + base // 2) // base, cap_pages // 2, 32))
+    want = max(1, min((2 * 148 + base // 2) // base, cap_pages // 2, 32))
+    if _FORCED_SPLITS > 0:
+        want = max(1, min(_FORCED_SPLITS, cap_pages))
     pages_per_split = (cap_pages + want - 1) // want
     nsplit = (cap_pages + pages_per_split - 1) // pages_per_split
     if out is None:

@@ -413,18 +413,40 @@ CASES = {
 }
 
 
-def run_case(name: str, iters: int, warmup: int, profile_last: bool = False) -> dict:
+def run_case(name: str, iters: int, warmup: int, profile_last: bool = False, graph: bool = False) -> dict:
     fn, flops, nbytes, note = CASES[name]()
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for _ in range(iters):
-        fn()
-    end.record()
-    torch.cuda.synchronize()
-    us = start.elapsed_time(end) * 1e3 / iters
+    if graph:
+        # kernels of a few tens of microseconds: an eager loop measures the host's launch rate, so the `iters` calls
+        # are captured once and the graph is replayed (as the decode step does)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                for _ in range(iters):
+                    fn()
+            for _ in range(2):
+                g.replay()
+            side.synchronize()
+            reps = 5
+            start.record(side)
+            for _ in range(reps):
+                g.replay()
+            end.record(side)
+            side.synchronize()
+        us = start.elapsed_time(end) * 1e3 / (iters * reps)
+        note += " [graph replay]"
+    else:
+        start.record()
+        for _ in range(iters):
+            fn()
+        end.record()
+        torch.cuda.synchronize()
+        us = start.elapsed_time(end) * 1e3 / iters
     if profile_last:
         # one more call inside a profiler range (for `ncu --profile-from-start off`); never timed
         torch.cuda.profiler.start()
@@ -452,6 +474,8 @@ def main(argv=None) -> int:
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--list", action="store_true")
+    ap.add_argument("--graph", action="store_true",
+                    help="capture the timed calls into one CUDA graph and time its replay (for kernels shorter than a launch)")
     ap.add_argument("--profile-last", action="store_true",
                     help="run one extra, untimed call per case inside a cudaProfilerStart/Stop range")
     args = ap.parse_args(argv)
@@ -460,7 +484,7 @@ def main(argv=None) -> int:
         return 0
     names = list(CASES) if args.case == "all" else [c.strip() for c in args.case.split(",")]
     for name in names:
-        print(json.dumps(run_case(name, args.iters, args.warmup, args.profile_last)), flush=True)
+        print(json.dumps(run_case(name, args.iters, args.warmup, args.profile_last, args.graph)), flush=True)
         torch.cuda.empty_cache()
     return 0
 
