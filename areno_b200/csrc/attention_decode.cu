@@ -164,17 +164,19 @@ fold_rope_append_kernel(const float* __restrict__ ws, int splits, long long spli
 template <int D, bool FP8>
 struct DecodeSmem {
   // fp8 pages stay as bytes in shared memory and are expanded to fp16 in registers, fragment by fragment, so there
-  // is no second copy of a page and no extra barrier: a stage is half the size of a bf16 stage and four of them
-  // (three pages in flight per CTA, three CTAs per SM) keep as many bytes in flight as the bf16 pipeline does
-  static constexpr int kStages = FP8 ? 4 : 3;
+  // is no second copy of a page and no extra barrier: a stage is half the size of a bf16 stage
+  // fp8: the kernel is bound by the dependent instruction chain of a page, not by bytes, so a CTA runs TWO groups
+  // of four warps that take alternate pages (own stages, own named barrier) and twice the warps hide the chain
+  static constexpr int kGroups = FP8 ? 2 : 1;
+  static constexpr int kStages = 3;
   static constexpr int kTile = kPage * D * 2;                 // bf16 tile bytes
   static constexpr int kRaw = FP8 ? kPage * D : 0;            // fp8 page bytes (K or V)
   static constexpr int kStageBytes = FP8 ? 2 * kRaw + 2 * kPage * 4 : 2 * kTile;   // fp8: K, V, k scales, v scales
   static constexpr int kQ = FP8 ? 0 : 16 * D * 2;             // fp8: q lives in registers
-  static constexpr int kMerge = 4 * 16 * (D + 2) * 4;         // per-warp partial O, m, l (fp32)
+  static constexpr int kMerge = 4 * kGroups * 16 * (D + 2) * 4;   // per-warp partial O, m, l (fp32)
   // the merge buffer aliases the (by then idle) pipeline stages
-  static_assert(kMerge <= kStages * kStageBytes, "merge buffer must fit in the stage area");
-  static constexpr int kTotal = kStages * kStageBytes + kQ;
+  static_assert(kMerge <= kGroups * kStages * kStageBytes, "merge buffer must fit in the stage area");
+  static constexpr int kTotal = kGroups * kStages * kStageBytes + kQ;
 };
 
 // Position of 16-byte chunk `c` of row `r` inside a row of an fp8 page in shared memory: the XOR spreads the eight
@@ -190,7 +192,7 @@ __device__ __forceinline__ uint32_t prmt_u32(uint32_t a, uint32_t sel) {
 }
 
 template <int D, bool FP8>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(FP8 ? 256 : 128, FP8 && D <= 128 ? 2 : 1)
 paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const void* __restrict__ k_cache,
                     const void* __restrict__ v_cache, const float* __restrict__ k_scale,
                     const float* __restrict__ v_scale, const int* __restrict__ block_table,
@@ -202,9 +204,17 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const void* __restrict_
   extern __shared__ __align__(128) uint8_t smem_attn[];
   pdl_trigger();
   pdl_wait();
-  uint8_t* stage_base = smem_attn;
-  __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_attn + SM::kStages * SM::kStageBytes);   // bf16 path only
-  float* sMerge = reinterpret_cast<float*>(stage_base);
+  constexpr int NWG = SM::kGroups;
+  const int wg = threadIdx.x >> 7;                 // warp group (0 unless fp8)
+  const int tid = threadIdx.x & 127;               // thread inside its group
+  uint8_t* stage_base = smem_attn + wg * SM::kStages * SM::kStageBytes;
+  __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_attn + NWG * SM::kStages * SM::kStageBytes);   // bf16 path only
+  float* sMerge = reinterpret_cast<float*>(smem_attn);
+  auto group_sync = [&]() {
+    if constexpr (NWG == 1) __syncthreads();
+    else if (wg == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+    else asm volatile("bar.sync 2, 128;" ::: "memory");
+  };
   constexpr int CHB = D / 16;      // 16-byte chunks per row of an fp8 page
 
   const int b = blockIdx.x;
@@ -214,7 +224,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const void* __restrict_
   const int gt = blockIdx.y % gtiles;
   const int split = blockIdx.z;
   const int ctx = seq_lens[b];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = (threadIdx.x >> 5) & 3, lane = threadIdx.x & 31;      // warp inside its group
   const int g = lane >> 2, t4 = lane & 3;
   const int rows_valid = min(16, group - gt * 16);
   const int head0 = kvh * group + gt * 16;
@@ -224,7 +234,8 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const void* __restrict_
   const int total_pages = (ctx + kPage - 1) / kPage;
   const int page_lo = max(split * pages_per_split, first_key / kPage);
   const int page_hi = min(total_pages, (split + 1) * pages_per_split);
-  const int n_pages = max(0, page_hi - page_lo);
+  const int n_pages_all = max(0, page_hi - page_lo);
+  const int n_pages = n_pages_all > wg ? (n_pages_all - wg + NWG - 1) / NWG : 0;   // pages wg, wg + NWG, ... of the range
 
   // Q tile: 16 rows (q heads of the group, zero padded) x D
   // fp8: q goes to registers as fp16 A fragments (e4m3 expands to fp16 exactly, so the MMAs run on fp16).  The
@@ -253,7 +264,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const void* __restrict_
       }
     }
   } else {
-    for (int idx = threadIdx.x; idx < 16 * CH; idx += 128) {
+    for (int idx = tid; idx < 16 * CH; idx += 128) {
       const int r = idx / CH, ch = idx % CH;
       uint4 val = make_uint4(0, 0, 0, 0);
       if (r < rows_valid) val = *reinterpret_cast<const uint4*>(q + (long long)b * q_stride + (long long)(head0 + r) * D + ch * 8);
@@ -269,16 +280,16 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const void* __restrict_
     if constexpr (FP8) {
       const uint8_t* kp = reinterpret_cast<const uint8_t*>(k_cache) + ((long long)page * hkv + kvh) * kPage * D;
       const uint8_t* vp = reinterpret_cast<const uint8_t*>(v_cache) + ((long long)page * hkv + kvh) * kPage * D;
-      for (int idx = threadIdx.x; idx < kPage * CHB; idx += 128) {
+      for (int idx = tid; idx < kPage * CHB; idx += 128) {
         const int r = idx / CHB, c = idx % CHB;
         const int off = r * D + fp8_chunk<CHB>(r, c) * 16;
         cp_async16(sb + off, kp + idx * 16);
         cp_async16(sb + SM::kRaw + off, vp + idx * 16);
       }
-      if (threadIdx.x < kPage / 4) {
+      if (tid < kPage / 4) {
         const long long srow = ((long long)page * hkv + kvh) * kPage;
-        cp_async16(sb + 2 * SM::kRaw + threadIdx.x * 16, k_scale + srow + threadIdx.x * 4);
-        cp_async16(sb + 2 * SM::kRaw + kPage * 4 + threadIdx.x * 16, v_scale + srow + threadIdx.x * 4);
+        cp_async16(sb + 2 * SM::kRaw + tid * 16, k_scale + srow + tid * 4);
+        cp_async16(sb + 2 * SM::kRaw + kPage * 4 + tid * 16, v_scale + srow + tid * 4);
       }
     } else {
       const __nv_bfloat16* kp = reinterpret_cast<const __nv_bfloat16*>(k_cache) + ((long long)page * hkv + kvh) * kPage * D;
@@ -290,7 +301,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const void* __restrict_
 
   int first_pages[SM::kStages];
 #pragma unroll
-  for (int s = 0; s < SM::kStages; ++s) first_pages[s] = s < n_pages ? bt[s] : 0;
+  for (int s = 0; s < SM::kStages; ++s) first_pages[s] = s < n_pages ? bt[s * NWG + wg] : 0;
 #pragma unroll
   for (int s = 0; s < SM::kStages - 1; ++s) {
     if (s < n_pages) issue(first_pages[s], s);
@@ -309,14 +320,14 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const void* __restrict_
     if constexpr (FP8) {
       // one barrier per page: after it every thread has left page pi - 1, whose stage the next copy overwrites
       cp_async_wait<SM::kStages - 2>();
-      __syncthreads();
+      group_sync();
       const int page_now = page_next;
-      if (pi + SM::kStages < n_pages) page_next = bt[pi + SM::kStages];
+      if (pi + SM::kStages < n_pages) page_next = bt[(pi + SM::kStages) * NWG + wg];
       if (pi + SM::kStages - 1 < n_pages) issue(page_now, (pi + SM::kStages - 1) % SM::kStages);
       cp_async_commit();
     } else {
       const int page_now = page_next;
-      if (pi + SM::kStages < n_pages) page_next = bt[pi + SM::kStages];
+      if (pi + SM::kStages < n_pages) page_next = bt[(pi + SM::kStages) * NWG + wg];
       if (pi + SM::kStages - 1 < n_pages) issue(page_now, (pi + SM::kStages - 1) % SM::kStages);
       cp_async_commit();
       cp_async_wait<SM::kStages - 1>();
@@ -329,7 +340,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const void* __restrict_
     const float* vsc = ksc + kPage;
 
     // this warp: keys [warp*16, warp*16+16) of the page
-    const int key0 = (page_lo + pi) * kPage + warp * 16;
+    const int key0 = (page_lo + pi * NWG + wg) * kPage + warp * 16;
     if (key0 < ctx && key0 + 16 > first_key) {
       float s[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
       if constexpr (FP8) {
@@ -450,7 +461,8 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const void* __restrict_
     l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
     l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
   }
-  float* wbuf = sMerge + warp * 16 * (D + 2);
+  constexpr int NW = 4 * NWG;                      // partials to merge: one per warp of the CTA
+  float* wbuf = sMerge + (wg * 4 + warp) * 16 * (D + 2);
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = g + h * 8;
@@ -467,20 +479,21 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const void* __restrict_
     }
   }
   __syncthreads();
-  // 128 threads: thread -> (row r = tid / 8, column group cg = tid % 8 covering D/8 columns)
+  // thread -> (row r, column group cg covering D / (8 NWG) columns)
   {
-    const int r = threadIdx.x >> 3, cg = threadIdx.x & 7;
+    constexpr int CG = 8 * NWG, COLS = D / CG;
+    const int r = threadIdx.x / CG, cg = threadIdx.x % CG;
     if (r < rows_valid) {
-      float mw[4], lw[4], mmax = -INFINITY;
+      float mw[NW], lw[NW], mmax = -INFINITY;
 #pragma unroll
-      for (int w = 0; w < 4; ++w) {
+      for (int w = 0; w < NW; ++w) {
         mw[w] = sMerge[(w * 16 + r) * (D + 2) + D];
         lw[w] = sMerge[(w * 16 + r) * (D + 2) + D + 1];
         mmax = fmaxf(mmax, mw[w]);
       }
-      float wgt[4], ltot = 0.f;
+      float wgt[NW], ltot = 0.f;
 #pragma unroll
-      for (int w = 0; w < 4; ++w) {
+      for (int w = 0; w < NW; ++w) {
         wgt[w] = mw[w] == -INFINITY ? 0.f : exp2f((mw[w] - mmax) * scale_log2);
         ltot += lw[w] * wgt[w];
       }
@@ -488,18 +501,18 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const void* __restrict_
       if (nsplit == 1) {
         const float inv = ltot > 0.f ? 1.f / ltot : 0.f;
         __nv_bfloat16* op = out + (long long)b * o_stride + (long long)head * D;
-        for (int c = cg * (D / 8); c < (cg + 1) * (D / 8); ++c) {
+        for (int c = cg * COLS; c < (cg + 1) * COLS; ++c) {
           float acc = 0.f;
 #pragma unroll
-          for (int w = 0; w < 4; ++w) acc += sMerge[(w * 16 + r) * (D + 2) + c] * wgt[w];
+          for (int w = 0; w < NW; ++w) acc += sMerge[(w * 16 + r) * (D + 2) + c] * wgt[w];
           op[c] = __float2bfloat16_rn(acc * inv);
         }
       } else {
         float* po = part_o + (((long long)b * hq + head) * nsplit + split) * D;
-        for (int c = cg * (D / 8); c < (cg + 1) * (D / 8); ++c) {
+        for (int c = cg * COLS; c < (cg + 1) * COLS; ++c) {
           float acc = 0.f;
 #pragma unroll
-          for (int w = 0; w < 4; ++w) acc += sMerge[(w * 16 + r) * (D + 2) + c] * wgt[w];
+          for (int w = 0; w < NW; ++w) acc += sMerge[(w * 16 + r) * (D + 2) + c] * wgt[w];
           po[c] = acc;
         }
         if (cg == 0) {
@@ -558,7 +571,7 @@ static int launch_decode(const void* q, const void* k_cache, const void* v_cache
   }
   const int group = hq / hkv;
   dim3 grid(batch, hkv * ((group + 15) / 16), nsplit);
-  cudaError_t e = launch_pdl(paged_decode_kernel<D, FP8>, grid, dim3(128), SM::kTotal, stream, (const __nv_bfloat16*)q,
+  cudaError_t e = launch_pdl(paged_decode_kernel<D, FP8>, grid, dim3(128 * SM::kGroups), SM::kTotal, stream, (const __nv_bfloat16*)q,
                              k_cache, v_cache, k_scale, v_scale, block_table, seq_lens, (__nv_bfloat16*)out, part_o,
                              part_ml, hq, hkv, max_pages, q_stride, o_stride, scale, pages_per_split, nsplit, window);
   if (e == cudaSuccess && nsplit > 1)

@@ -158,10 +158,10 @@ def case_attn_bwd():
         2.0 * sum(lens) * 128 * (28 * 4 + 16), "backward of attn_fwd (delta + dK/dV + dQ kernels)"
 
 
-def case_paged_decode(fp8: bool = False):
+def case_paged_decode(fp8: bool = False, ctx: int = 1024):
     from ..ops import paged_attention as pa
 
-    b, hq, hkv, d, ctx = 64, 28, 4, 128, 1024
+    b, hq, hkv, d = 64, 28, 4, 128
     pages_per_seq = ctx // pa.PAGE
     num_pages = b * pages_per_seq * 4  # 4x the live pages: 1 GB of bf16 KV so that L2 cannot hold it
     kc, vc, ks, vs = pa.alloc_kv_cache(num_pages, hkv, d, "cuda", fp8=fp8)
@@ -287,6 +287,9 @@ def case_train_microbatch(layers: int = 4, lens=(1536, 1408, 1152)):
     targets = ids.index_select(0, aidx + 1)
     meta = TrainMeta(build_varlen_meta(list(lens), device=dev), activation_checkpointing=True, checkpoint_layers=0)
     weight = torch.randn(aidx.numel(), device=dev)
+    for prm in model.parameters():          # as in the trainer: weight gradients accumulate into fp32 buffers
+        prm.main_grad = torch.zeros(prm.shape, dtype=torch.float32, device=dev)
+        prm.grad_added_to_main_grad = False
     per_layer = 3584 * (4608 + 3584 + 3 * 18944)
     flops = 6.0 * t * per_layer * layers + 8.0 * aidx.numel() * 3584 * 152064   # LM head: logits recomputed in backward
 
@@ -408,7 +411,9 @@ CASES = {
     "gemm_fwd": case_gemm_fwd, "gemm_dgrad": case_gemm_dgrad, "gemm_wgrad": case_gemm_wgrad,
     "gemm_decode_down": case_gemm_decode_down, "gemm_decode_gate_up": case_gemm_decode_gate_up,
     "splitk_rmsnorm": case_splitk_rmsnorm, "attn_fwd": case_attn_fwd, "attn_bwd": case_attn_bwd,
-    "paged_decode": case_paged_decode, "paged_decode_fp8": lambda: case_paged_decode(True), "sampler": case_sampler,
+    "paged_decode": case_paged_decode, "paged_decode_fp8": lambda: case_paged_decode(True),
+    "paged_decode_4k": lambda: case_paged_decode(False, 4096), "paged_decode_fp8_4k": lambda: case_paged_decode(True, 4096),
+    "paged_decode_256": lambda: case_paged_decode(False, 256), "paged_decode_fp8_256": lambda: case_paged_decode(True, 256), "sampler": case_sampler,
     "adamw": case_adamw, "moe_grouped": case_moe_grouped,
 }
 
