@@ -285,12 +285,16 @@ def save_with_rules(model, path: str, config, top_rules: list[Rule], layer_rules
     from safetensors.torch import save_file
 
     ctx = get_context()
-    if ctx.dp_rank != 0:
+    # expert parallelism: every data-parallel rank owns different experts and writes them to a file of its own;
+    # everything else is written by data-parallel rank 0 as usual
+    ep = ctx.ep_size > 1 and expert_export is not None
+    if ctx.dp_rank != 0 and not ep:
         if ctx.world_size > 1:
             dist.barrier()
         return
     os.makedirs(path, exist_ok=True)
     tensors: dict[str, torch.Tensor] = {}
+    experts_only = ep and ctx.dp_rank != 0
 
     def emit(rule: Rule, obj, fmt: dict):
         try:
@@ -305,26 +309,34 @@ def save_with_rules(model, path: str, config, top_rules: list[Rule], layer_rules
             if full is not None:
                 tensors[k] = full.to("cpu", copy=True).contiguous()
 
-    for rule in top_rules:
-        emit(rule, model, {})
+    if not experts_only:
+        for rule in top_rules:
+            emit(rule, model, {})
     layers = _resolve(model, layers_attr)
     for i in range(num_layers):
-        for rule in layer_rules:
-            emit(rule, layers[i], {"layer": i})
+        if not experts_only:
+            for rule in layer_rules:
+                emit(rule, layers[i], {"layer": i})
         if expert_export is not None:
             tensors.update(expert_export(layers[i], i))
     tp = ctx.tp_size
     # single-writer checkpoints use the plain Hugging Face file name (as ``areno/engine/checkpoints/io.py:610``)
-    fname = "model.safetensors" if tp == 1 else f"model-{ctx.tp_rank + 1:05d}-of-{tp:05d}.safetensors"
+    if ep:
+        fname = f"model-{ctx.ep_rank + 1:05d}-of-{ctx.ep_size:05d}.safetensors"
+    else:
+        fname = "model.safetensors" if tp == 1 else f"model-{ctx.tp_rank + 1:05d}-of-{tp:05d}.safetensors"
     save_file(tensors, os.path.join(path, fname), metadata={"format": "pt"})
     local = {k: fname for k in tensors}
     size = sum(t.numel() * t.element_size() for t in tensors.values())
-    if tp > 1:
+    if ep:
+        maps = [None] * ctx.ep_size
+        dist.all_gather_object(maps, (local, size), group=ctx.ep_ctl_group)
+    elif tp > 1:
         maps = [None] * tp
         dist.all_gather_object(maps, (local, size), group=ctx.tp_group)
     else:
         maps = [(local, size)]
-    if ctx.tp_rank == 0:
+    if ctx.tp_rank == 0 and ctx.dp_rank == 0:
         weight_map: dict[str, str] = {}
         total = 0
         for m, s in maps:

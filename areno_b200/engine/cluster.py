@@ -187,7 +187,8 @@ def _spawn_entry(rank: int, config: EngineConfig, port: int, cmd_q, result_q) ->
             torch.cuda.set_device(device)
         torch.set_float32_matmul_precision("high")
         init_parallel(rank, config.world_size, config.tp_size, master_addr="127.0.0.1", master_port=port,
-                      backend=config.backend, device=device, rollout_tp_size=config.rollout_tp_size)
+                      backend=config.backend, device=device, rollout_tp_size=config.rollout_tp_size,
+                      expert_parallel=config.expert_parallel)
         worker = RankWorker(config, device)
         result_q.put(WorkerResult(rank, -1, True, "READY"))
     except BaseException:  # noqa: BLE001
@@ -381,7 +382,7 @@ class SPMDCluster(_ClusterBase):
                 torch.cuda.set_device(device)
             if get_context().world_size != world:
                 init_parallel(rank, world, config.tp_size, backend=config.backend, device=device,
-                              rollout_tp_size=config.rollout_tp_size)
+                              rollout_tp_size=config.rollout_tp_size, expert_parallel=config.expert_parallel)
             worker = RankWorker(config, device)
         self._worker = worker
         self.rank = rank

@@ -177,6 +177,9 @@ class EngineConfig:
     # training layout to be pure data parallel (tp_size == 1): every rank then owns a full replica and
     # cuts its rollout shard locally.
     rollout_tp_size: int | None = None
+    # Expert parallelism for mixture-of-experts models: the experts are dealt out over the data-parallel ranks and
+    # tokens are exchanged with their owners in every MoE layer, in training and in rollout alike (tp_size 1).
+    expert_parallel: bool = False
     devices: list[int] | None = None
     dummy_load: bool = False
     max_running_seqs: int = 64
@@ -206,6 +209,11 @@ class EngineConfig:
             if self.rollout_tp_size < 1 or world % self.rollout_tp_size != 0:
                 raise ValueError(f"world size {world} must be a multiple of rollout_tp_size={self.rollout_tp_size}")
             self.model.validate_tp(self.rollout_tp_size, inference_only=True)
+        if self.expert_parallel:
+            if self.tp_size != 1 or self.rollout_tp_size not in (None, 1):
+                raise ValueError("expert_parallel shards the experts over the data-parallel group: tp_size must be 1")
+            if not self.model.num_experts or self.model.num_experts % world != 0:
+                raise ValueError(f"expert_parallel needs num_experts divisible by the {world} ranks")
         if self.runtime.kv_block_size % 16 != 0:
             raise ValueError("runtime.kv_block_size must be a multiple of 16")
 

@@ -157,6 +157,10 @@ class InferenceEngine:
         self.decode_tokens = 0
         self._peer_waits = False
         self._lockstep = False
+        ctx = get_context()
+        # expert-parallel models exchange tokens in every forward pass: see step()
+        self._ep = ctx.ep_runtime if (ctx.ep_size > 1 and hasattr(model, "ep_idle_forward")) else None
+        self._ep_busy = True
 
     # ------------------------------------------------------------------ state
     def _alloc_state(self):
@@ -238,6 +242,11 @@ class InferenceEngine:
         # a step more than its peer.  In lockstep mode the snapshot taken after step t is consumed exactly
         # ``_LOCKSTEP_LAG`` steps later (waiting for it if need be), which is the same iteration on every rank.
         self._lockstep = get_context().tp_size > 1
+        if self._ep is not None:
+            self._ep_busy = True
+            self._peer_waits = self._peer_waits or self.cuda
+            with self._ep.pinned(self.max_slots):
+                self._ep.comm(1)     # the decode-sized communicator exists before a graph capture could need it
 
     def add_request(self, prompt: list[int], max_new_tokens: int | None = None, tag=None,
                     stream: int | None = None) -> int:
@@ -263,14 +272,31 @@ class InferenceEngine:
     @torch.no_grad()
     def step(self) -> list[_Request]:
         """One scheduler iteration: poll completions, prefill newly admitted prompts, run one decode
-        step.  Returns the requests that completed since the last call."""
+        step.  Returns the requests that completed since the last call.
+
+        Expert parallelism: every forward pass is an exchange among all ranks, whose engines hold different
+        requests.  Before each of the two passes of an iteration the ranks agree (a host all-reduce of a few
+        integers) on whether anybody runs it and at which size; a rank without work of its own joins a prefill
+        with an idle pass and a decode step with all slots inactive, so that all ranks launch (and capture) the
+        same sequence of exchanges."""
         done = self._poll(block=False)
         entries = self.sched.plan_prefill()
-        if entries:
+        ep = self._ep
+        if ep is not None:
+            g_pre, g_busy = ep.agree_max([sum(int(e[3]) for e in entries) if entries else 0, int(not self.idle)])
+            self._ep_busy = bool(g_busy)
+            if g_pre > 0:
+                with trace_range("rollout/prefill"), ep.pinned(g_pre):
+                    if entries:
+                        self._run_prefill(entries)
+                    else:
+                        self.model.ep_idle_forward()
+        elif entries:
             with trace_range("rollout/prefill"):
                 self._run_prefill(entries)
-        if self.sched.num_decoding > 0:
-            updates = None
+        updates = None
+        had_decoding = self.sched.num_decoding > 0
+        if had_decoding:
             while updates is None:
                 try:
                     updates = self.sched.reserve_decode(1)
@@ -279,21 +305,31 @@ class InferenceEngine:
                     done += self._preempt(int(exc.args[0]))
                     if self.sched.num_decoding == 0:
                         updates = []
-            if self.sched.num_decoding == 0:
-                return done
+        decoding = self.sched.num_decoding > 0
+        bucket = _pick_bucket(self.buckets, self.sched.active_extent) if decoding else 0
+        ctx_cap = self._context_bucket(self.sched.max_seq_len + 1) if decoding else 0
+        run_decode = decoding
+        if ep is not None:
+            g_dec, bucket, ctx_cap = ep.agree_max([int(decoding), bucket, ctx_cap])
+            run_decode = bool(g_dec)
+        if run_decode:
             if updates:
                 self._push_block_updates(updates)
-            extent = self.sched.active_extent
             with trace_range("rollout/decode_step"):
-                self._decode(_pick_bucket(self.buckets, extent), self._context_bucket(self.sched.max_seq_len + 1))
-            self.sched.advance(1)
-            self.step_count += 1
-            self._snapshot()
-            if self._peer_waits and self.step_count % 256 == 0:
-                # kernels that wait on other GPUs report a wait that ran out through the status word: look at it
-                # regularly, not only once the rollout is over
-                klib.check_status(self.device)
-        elif not entries:
+                if ep is not None:
+                    with ep.pinned(self.max_slots):
+                        self._decode(bucket, ctx_cap)
+                else:
+                    self._decode(bucket, ctx_cap)
+            if decoding:
+                self.sched.advance(1)
+                self.step_count += 1
+                self._snapshot()
+                if self._peer_waits and self.step_count % 256 == 0:
+                    # kernels that wait on other GPUs report a wait that ran out through the status word: look at
+                    # it regularly, not only once the rollout is over
+                    klib.check_status(self.device)
+        elif not entries and not had_decoding and not self.idle:
             if not self._snapshots:
                 self._snapshot()
             with trace_range("rollout/wait_results"):
@@ -303,7 +339,9 @@ class InferenceEngine:
     def run_until_done(self, progress_interval_s: float = 0.0, on_finished: Callable | None = None) -> None:
         t_last = time.time()
         tok_last = 0
-        while not self.idle:
+        while self._ep is not None or not self.idle:
+            if self._ep is not None and not self._ep_busy:
+                break             # expert parallel: the loop ends when no rank has work left (agreed in step())
             for req in self.step():
                 if on_finished is not None:
                     on_finished(req)

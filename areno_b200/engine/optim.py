@@ -66,6 +66,9 @@ class _Bucket:
     shard: int = 0
     grad_offset: int = 0      # element offset of grad_flat inside the symmetric gradient region (peer-memory path)
     min_layer: int = -1       # lowest decoder-layer index among the parameters (-1: embeddings and the like)
+    # expert-parallel parameters: every data-parallel rank owns different experts, whose gradient is already the
+    # sum over all ranks' tokens.  The bucket is not sharded (shard == numel), never reduced and never gathered.
+    local: bool = False
 
 
 class ShardedAdamW:
@@ -102,16 +105,16 @@ class ShardedAdamW:
         # taps) keep their precision instead of being folded into a bf16 buffer
         groups: dict[tuple, list] = {}
         for p in params:
-            groups.setdefault((_tp_grad_kind(p), p.dtype), []).append(p)
-        for (kind, _dtype), plist in groups.items():
+            groups.setdefault((_tp_grad_kind(p), p.dtype, bool(getattr(p, "ep_local", False))), []).append(p)
+        for (kind, _dtype, local), plist in groups.items():
             replicated = kind != "sharded"
             tp_sum = kind == "partial" or (kind == "same" and self.sequence_parallel)
-            cur = _Bucket(replicated=replicated, tp_sum=tp_sum)
+            cur = _Bucket(replicated=replicated, tp_sum=tp_sum, local=local)
             for p in plist:
                 n = (p.numel() + _ALIGN - 1) // _ALIGN * _ALIGN
                 if cur.params and cur.numel + n > cap:
                     self.buckets.append(cur)
-                    cur = _Bucket(replicated=replicated, tp_sum=tp_sum)
+                    cur = _Bucket(replicated=replicated, tp_sum=tp_sum, local=local)
                 cur.params.append(p)
                 cur.offsets.append(cur.numel)
                 cur.numel += n
@@ -120,17 +123,20 @@ class ShardedAdamW:
         layer_of = _layer_index_of(model)
         off = 0
         for b in self.buckets:
+            b.min_layer = min(layer_of.get(id(p), -1) for p in b.params)
+            if b.local:
+                b.shard = b.numel
+                continue
             b.numel = (b.numel + granule - 1) // granule * granule
             b.shard = b.numel // self.dp
             b.grad_offset = off
             off += b.numel
-            b.min_layer = min(layer_of.get(id(p), -1) for p in b.params)
         self.grad_comm = self._make_grad_comm(off)
         for b in self.buckets:
             dev = b.params[0].device
             dtype = b.params[0].dtype
             b.param_flat = torch.zeros(b.numel, dtype=dtype, device=dev)
-            if self.grad_comm is not None:
+            if self.grad_comm is not None and not b.local:
                 b.grad_flat = self.grad_comm.view(b.grad_offset, b.numel)
             else:
                 b.grad_flat = torch.zeros(b.numel, dtype=torch.float32, device=dev)
@@ -141,11 +147,15 @@ class ShardedAdamW:
                 p.main_grad = b.grad_flat[off:off + p.numel()].view(p.shape)
                 p.grad_added_to_main_grad = False
 
+    def _lo(self, b: _Bucket) -> int:
+        """First element of this rank's shard of the bucket."""
+        return 0 if b.local else self.dp_rank * b.shard
+
     def _make_grad_comm(self, total_elems: int):
         """Peer-memory gradient reduce-scatter: CUDA, more than one DP rank, at most 8 (one NVLink domain).
         ``ARENO_FUSED_GRAD_RS=0`` keeps the NCCL reduce-scatter."""
         dev = self.buckets[0].params[0].device if self.buckets else None
-        if (self.dp <= 1 or self.dp > 8 or dev is None or dev.type != "cuda" or len(self.buckets) > 4096
+        if (self.dp <= 1 or total_elems <= 0 or self.dp > 8 or dev is None or dev.type != "cuda" or len(self.buckets) > 4096
                 or os.environ.get("ARENO_FUSED_GRAD_RS", "1") == "0"):
             return None
         from ..parallel.grad_comm import GradComm
@@ -182,7 +192,7 @@ class ShardedAdamW:
         if not self._overlap:
             return
         for i, b in enumerate(self.buckets):
-            if b.min_layer >= layer and i not in self.grad_comm.launched:
+            if not b.local and b.min_layer >= layer and i not in self.grad_comm.launched:
                 self._fold_bucket(b)
                 self.grad_comm.launch(i, b.grad_offset, b.shard)
 
@@ -199,7 +209,7 @@ class ShardedAdamW:
         if self._state_ready:
             return
         for b in self.buckets:
-            lo = self.dp_rank * b.shard
+            lo = self._lo(b)
             dev = b.param_flat.device
             if b.param_flat.dtype == torch.float32:
                 # fp32 parameters are their own master copy: the update runs in place on the local shard
@@ -238,7 +248,7 @@ class ShardedAdamW:
                 p.grad_added_to_main_grad = False
 
     def _grad_shard(self, b: _Bucket) -> torch.Tensor:
-        lo = self.dp_rank * b.shard
+        lo = self._lo(b)
         return b.grad_flat[lo:lo + b.shard]
 
     def reduce_gradients(self):
@@ -254,12 +264,15 @@ class ShardedAdamW:
             if not self._overlap:
                 self.grad_comm.begin_step()
             for i, b in enumerate(self.buckets):     # whatever backward did not hand over yet
-                self.grad_comm.launch(i, b.grad_offset, b.shard)
+                if not b.local:
+                    self.grad_comm.launch(i, b.grad_offset, b.shard)
             self.grad_comm.finish()
             self._overlap = False
         elif self.dp > 1:
             works = []
             for b in self.buckets:
+                if b.local:
+                    continue
                 works.append(dist.reduce_scatter_tensor(self._grad_shard(b), b.grad_flat, group=ctx.dp_group,
                                                         async_op=True))
             for w in works:
@@ -272,7 +285,10 @@ class ShardedAdamW:
         NCCL path is in use).  Must be called between steps (the bucket is zeroed afterwards)."""
         if self.grad_comm is None or self.dp <= 1 or not self.buckets:
             return None
-        b = self.buckets[min(bucket, len(self.buckets) - 1)]
+        shared = [x for x in self.buckets if not x.local]
+        if not shared:
+            return None
+        b = shared[min(bucket, len(shared) - 1)]
         i = self.buckets.index(b)
         g = torch.Generator(device=b.grad_flat.device).manual_seed(4321 + self.dp_rank)
         b.grad_flat.copy_(torch.randn(b.grad_flat.shape, device=b.grad_flat.device, generator=g))
@@ -316,7 +332,7 @@ class ShardedAdamW:
             optim_ops.sumsq(self._grad_shard(b), repl if b.replicated else sharded, accumulate=True)
             if ctx.tp_size > 1 and not b.replicated:
                 # K / V rows that exist on `rep` ranks would be counted `rep` times by the TP sum below
-                lo = self.dp_rank * b.shard
+                lo = self._lo(b)
                 for p, off in zip(b.params, b.offsets):
                     rep = int(getattr(p, "kv_replicated", 0) or 0)
                     if rep > 1:
@@ -351,7 +367,7 @@ class ShardedAdamW:
         b1, b2 = self.cfg.betas
         gathers = []
         for b in self.buckets:
-            lo = self.dp_rank * b.shard
+            lo = self._lo(b)
             g = self._grad_shard(b)
             out = b.param_flat[lo:lo + b.shard]
             if b.param_flat.dtype == torch.float32:
@@ -363,7 +379,7 @@ class ShardedAdamW:
             else:
                 optim_ops.adamw_fp32(b.master, b.m, b.v, g, out, lr, b1, b2, self.cfg.eps, self.cfg.weight_decay,
                                      self.step_count, 1.0 / self.dp, coef)
-            if self.dp > 1:
+            if self.dp > 1 and not b.local:
                 gathers.append(dist.all_gather_into_tensor(b.param_flat, out, group=self.ctx.dp_group, async_op=True))
         with trace_range("optimizer/param_all_gather_wait"):
             for w in gathers:
@@ -395,7 +411,7 @@ class ShardedAdamW:
             for p, off in zip(b.params, b.offsets):
                 p.main_grad = b.grad_flat[off:off + p.numel()].view(p.shape)
             if self._state_ready and b.master is None and b.param_flat.dtype == torch.float32:
-                lo = self.dp_rank * b.shard
+                lo = self._lo(b)
                 b.master = b.param_flat[lo:lo + b.shard]
         self._offloaded = False
 

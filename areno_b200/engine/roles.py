@@ -229,6 +229,31 @@ class RoleManager:
         if cur:
             yield cur
 
+    def _ep_aligned(self, model, rows, microbatches):
+        """Expert parallelism: the ranks score different rows in different numbers of micro-batches, but every
+        forward pass is a group-wide exchange.  The ranks agree on the number of rounds and on the largest
+        micro-batch of each; a rank that has run out of rows takes part with an idle pass.  Yields the local
+        micro-batches (index lists) with the round's communicator size pinned."""
+        from ..parallel.context import get_context
+
+        ctx = get_context()
+        if ctx.ep_size <= 1 or not hasattr(model, "ep_idle_forward"):
+            yield from microbatches
+            return
+        rt = ctx.ep_runtime
+        mbs = list(microbatches)
+        sizes = [sum(max(len(rows[i]), 1) for i in idx) for idx in mbs]
+        rounds = rt.agree_max([len(mbs)])[0]
+        if rounds == 0:
+            return
+        caps = rt.agree_max(sizes + [0] * (rounds - len(sizes)))
+        for r in range(rounds):
+            with rt.pinned(caps[r]):
+                if r < len(mbs):
+                    yield mbs[r]
+                else:
+                    model.ep_idle_forward()
+
     def _packed_forward(self, model, rows: list[list[int]]):
         dev = self.worker.device
         lens = [max(len(r), 1) for r in rows]
@@ -245,7 +270,7 @@ class RoleManager:
         model, _ = self._activate(role)
         model.eval()
         out: list[list[float]] = [[] for _ in rows]
-        for idx in self._microbatches(rows, microbatch_size):
+        for idx in self._ep_aligned(model, rows, self._microbatches(rows, microbatch_size)):
             sub = [rows[i] for i in idx]
             hidden, ids, lens = self._packed_forward(model, sub)
             starts = [0]
@@ -272,7 +297,7 @@ class RoleManager:
             raise RuntimeError(f"role {role!r} has no value head")
         model.eval()
         out: list[list[float]] = [[] for _ in rows]
-        for idx in self._microbatches(rows, microbatch_size):
+        for idx in self._ep_aligned(model, rows, self._microbatches(rows, microbatch_size)):
             sub = [rows[i] for i in idx]
             hidden, _ids, lens = self._packed_forward(model, sub)
             values = r.value_head(hidden)

@@ -247,10 +247,12 @@ class TrainingManager:
         mc = self.model.cfg
         n_layers = mc.num_hidden_layers
         cached = getattr(self, "_ckpt_cache", None)
-        if cached is not None and cached[0] >= tokens:
-            return cached[1]
-        self.optimizer._ensure_state()
         ctx = get_context()
+        if cached is not None and (cached[0] >= tokens or ctx.ep_size > 1):
+            return cached[1]      # expert parallel: decided once for all ranks (see below)
+        self.optimizer._ensure_state()
+        if ctx.ep_size > 1:
+            tokens = ctx.ep_runtime.agree_max([tokens])[0]
         tp = max(1, ctx.tp_size)
         qkv_w = (mc.num_attention_heads + 2 * mc.num_key_value_heads) * mc.head_dim // tp
         inter = (mc.moe_intermediate_size * max(1, mc.num_experts_per_tok) if mc.num_experts else mc.intermediate_size)
@@ -261,6 +263,10 @@ class TrainingManager:
         reserve = int(float(os.environ.get("ARENO_CKPT_RESERVE_GB", "26")) * (1 << 30))
         keep = max(0, int((free - reserve) // max(per_layer, 1)))
         n_ckpt = max(0, n_layers - keep)
+        if ctx.ep_size > 1:
+            # a recomputed layer repeats its token exchange in backward: every rank must recompute the same layers.
+            # The first micro-batch of a run reaches this point on every rank, later ones use the cached answer.
+            n_ckpt = ctx.ep_runtime.agree_max([n_ckpt])[0]
         self._ckpt_cache = (tokens, n_ckpt)
         logger.info("activation checkpointing: recompute %d of %d layers (free=%.1f GB, per-layer=%.2f GB)", n_ckpt,
                     n_layers, free / 2**30, per_layer / 2**30)
@@ -279,20 +285,30 @@ class TrainingManager:
         # last micro-batch of the window: gradient buckets are handed to the reduce-scatter as backward passes them
         self._layer_grad_hook = self.optimizer.begin_overlap() if allow_step and hasattr(self.optimizer, "begin_overlap") \
             else None
-        with trace_range("train/forward"):
-            logprobs = self.forward_logprobs(pack)
-        self._layer_grad_hook = None
-        with trace_range("train/loss"):
-            loss_out = loss_fn(pack, logprobs)
-        metrics = None
-        if isinstance(loss_out, tuple):
-            loss, metrics = loss_out
-        else:
-            loss = loss_out
-        if not isinstance(loss, torch.Tensor):
-            raise TypeError("train_loss_fn must return a torch.Tensor")
-        with trace_range("train/backward"):
-            (loss / max(grad_scale, 1)).backward()
+        # Expert parallelism: the ranks' micro-batches differ in size, but every MoE call of this forward, of a
+        # recomputed forward and of the backward must use the communicator of one common size
+        ep_rt = ctx.ep_runtime if ctx.ep_size > 1 else None
+        pin = ep_rt.pinned(ep_rt.agree_max([int(pack["input_ids"].numel())])[0]) if ep_rt is not None else None
+        if pin is not None:
+            pin.__enter__()
+        try:
+            with trace_range("train/forward"):
+                logprobs = self.forward_logprobs(pack)
+            self._layer_grad_hook = None
+            with trace_range("train/loss"):
+                loss_out = loss_fn(pack, logprobs)
+            metrics = None
+            if isinstance(loss_out, tuple):
+                loss, metrics = loss_out
+            else:
+                loss = loss_out
+            if not isinstance(loss, torch.Tensor):
+                raise TypeError("train_loss_fn must return a torch.Tensor")
+            with trace_range("train/backward"):
+                (loss / max(grad_scale, 1)).backward()
+        finally:
+            if pin is not None:
+                pin.__exit__(None, None, None)
         grad_norm = None
         lr = self.optimizer.lr
         if allow_step:

@@ -145,6 +145,9 @@ class RankWorker:
         longest = max((len(p) for p in prompts), default=1) + max_new_tokens
         need_len = (longest + 63) // 64 * 64
         slots = min(max_running or self.config.max_running_seqs, max(len(prompts), 1))
+        if rctx.ep_size > 1 and rctx.ep_runtime is not None:
+            # expert parallel: the ranks' engines step together and share graph shapes, so they are sized alike
+            slots, need_len = rctx.ep_runtime.agree_max([slots, need_len])
         interval = self.config.decode_progress_interval_s if progress_interval_s is None else progress_interval_s
         with use_context(rctx):
             eng = self.inference_engine(slots, need_len)

@@ -382,6 +382,18 @@ def init_weights(model: nn.Module, seed: int = 0, std: float = 0.02) -> None:
     gen_cpu = torch.Generator().manual_seed(seed)
     with torch.no_grad():
         for name, p in model.named_parameters():
+            rng = getattr(p, "expert_range", None)
+            if rng is not None:
+                # stacked expert weights: expert e gets the same values whichever rank holds it (expert-parallel,
+                # TP-sharded or all on one device), from a generator seeded by the parameter name and e
+                base = seed + (zlib.crc32(name.encode()) % 100003)
+                for le in range(p.shape[0]):
+                    g = torch.Generator(device=p.device if p.is_cuda else "cpu").manual_seed(base + 7919 * (rng[0] + le + 1))
+                    if p.is_cuda:
+                        p[le].normal_(0.0, std, generator=g)
+                    else:
+                        p[le].copy_(torch.randn(p.shape[1:], generator=g) * std)
+                continue
             if p.dim() >= 2:
                 if p.is_cuda:
                     g = torch.Generator(device=p.device).manual_seed(seed + (zlib.crc32(name.encode()) % 100003))

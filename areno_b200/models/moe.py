@@ -1,6 +1,8 @@
 """Sparse mixture-of-experts decoder (Qwen3-MoE family): softmax top-k router with fp32 gate, experts
 sharded over the TP group (every rank sees all tokens and serves the routes that hit its experts,
-then the partial outputs are summed over the group), grouped tcgen05 GEMMs over expert-sorted rows.
+then the partial outputs are summed over the group) or, with expert parallelism, over the data-parallel
+group (tokens are exchanged with the experts' owners over peer memory and the outputs come back the same
+way), grouped tcgen05 GEMMs over expert-sorted rows.
 
 Structure of ``areno/models/qwen3/model.py:75-231`` in the reference; the per-expert cuBLAS loop,
 the host sync for offsets and the Triton inference path are replaced by the device-side plan and
@@ -40,18 +42,43 @@ class Experts(nn.Module):
         super().__init__()
         ctx = get_context()
         e = cfg.num_experts
-        assert e % ctx.tp_size == 0, "num_experts must be divisible by the TP size"
-        self.e_local = e // ctx.tp_size
-        self.e_lo = ctx.tp_rank * self.e_local
+        # Expert parallelism: the experts are dealt out over the data-parallel group and the TOKENS travel to them
+        # (parallel/ep.py); otherwise they are sharded over the TP group, whose ranks all see every token.
+        self.ep = ctx.ep_size > 1
+        ways, rank = (ctx.ep_size, ctx.ep_rank) if self.ep else (ctx.tp_size, ctx.tp_rank)
+        assert e % ways == 0, "num_experts must be divisible by the size of the group that shards the experts"
+        self.e_local = e // ways
+        self.e_lo = rank * self.e_local
         self.inter = cfg.moe_intermediate_size
         self.act = cfg.hidden_act
         self.gate_up = _param((self.e_local, 2 * self.inter, cfg.hidden_size), dtype, device)
         self.down = _param((self.e_local, cfg.hidden_size, self.inter), dtype, device)
-        # dim-0 (expert) sharding: same slicing as a column-parallel weight
-        self.gate_up.tp_shard = ("col", None)
-        self.down.tp_shard = ("col", None)
+        self.gate_up.expert_range = (self.e_lo, e)      # read by the seeded random init
+        self.down.expert_range = (self.e_lo, e)
+        if self.ep:
+            # every data-parallel rank owns different experts: the optimizer neither reduces nor gathers these
+            self.gate_up.ep_local = True
+            self.down.ep_local = True
+            if ctx.ep_runtime is None:
+                from ..parallel.ep import EpRuntime
+
+                ctx.ep_runtime = EpRuntime(ctx, cfg.hidden_size, cfg.num_experts_per_tok, e, device)
+        else:
+            # dim-0 (expert) sharding: same slicing as a column-parallel weight
+            self.gate_up.tp_shard = ("col", None)
+            self.down.tp_shard = ("col", None)
+
+    def _forward_ep(self, x, weights, ids):
+        comm = get_context().ep_runtime.comm(x.shape[0])
+        rows, plan = comm.dispatch(x, ids)
+        gu = moe_ops.grouped_linear(rows, self.gate_up, plan.moe)
+        a = activation.silu_and_mul(gu) if self.act == "silu" else activation.gelu_tanh_and_mul(gu)
+        ys = moe_ops.grouped_linear(a, self.down, plan.moe)
+        return comm.combine(ys, weights, plan), plan.moe
 
     def forward(self, x, weights, ids):
+        if self.ep:
+            return self._forward_ep(x, weights, ids)
         plan = moe_ops.align(ids, self.e_lo, self.e_local)
         xs = moe_ops.permute(x, plan)
         gu = moe_ops.grouped_linear(xs, self.gate_up, plan)
@@ -114,3 +141,20 @@ class MoeCausalLM(DenseCausalLM):
     def finalize_router_expert_bias(self, tp_group=None, dp_group=None) -> None:
         """Softmax routers carry no selection bias: nothing to update after a step."""
         return None
+
+    @torch.no_grad()
+    def ep_idle_forward(self) -> None:
+        """Expert parallelism: take part in one forward pass of the OTHER ranks without tokens of one's own.  Every
+        MoE layer still has to publish a routing table, serve the routes that hit the local experts and answer
+        the exchange; attention and the dense parts have nothing to do.  One zero token with zero routing weights
+        stands in for the batch."""
+        cfg = self.cfg
+        dev = self.embed_tokens.weight.device
+        k = cfg.num_experts_per_tok
+        x = torch.zeros((1, cfg.hidden_size), dtype=self.embed_tokens.weight.dtype, device=dev)
+        w = torch.zeros((1, k), dtype=torch.float32, device=dev)
+        ids = torch.arange(k, dtype=torch.int32, device=dev).unsqueeze(0)
+        for layer in self.layers:
+            mlp = getattr(layer, "mlp", None)
+            if isinstance(mlp, SparseMoeBlock) and mlp.experts.ep:
+                mlp.experts(x, w, ids)

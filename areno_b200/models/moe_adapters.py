@@ -40,7 +40,8 @@ def _export_layer_experts(layer, i: int) -> dict[str, torch.Tensor]:
     if not isinstance(mlp, SparseMoeBlock):
         return {}
     out: dict[str, torch.Tensor] = {}
-    if get_context().tp_rank == 0:
+    ctx = get_context()
+    if ctx.tp_rank == 0 and (ctx.ep_size == 1 or ctx.ep_rank == 0):      # the router is replicated: one writer
         out[_GATE.format(layer=i)] = mlp.router.weight.detach().to("cpu", copy=True)
     ex = mlp.experts
     inter = ex.inter

@@ -32,6 +32,15 @@ class ParallelContext:
     dp_group: Any = None
     device: torch.device = torch.device("cpu")
     rollout: "ParallelContext | None" = None  # second layout for the inference engine (None: same as training)
+    # Expert parallelism: the experts of a mixture-of-experts layer are dealt out over the data-parallel group
+    # (every rank keeps its own tokens and E / ep_size experts); requires tp_size == 1.  ``ep_ctl_group`` is a
+    # CPU (gloo) group over the same ranks for the host-side agreements of the engine loop; ``ep_runtime`` owns
+    # the communicators (parallel/ep.py) once a model that needs them exists.
+    ep_size: int = 1
+    ep_rank: int = 0
+    ep_group: Any = None
+    ep_ctl_group: Any = None
+    ep_runtime: Any = None
 
     @property
     def is_tp_first(self) -> bool:
@@ -96,9 +105,11 @@ def _layout(rank: int, world_size: int, tp_size: int, backend: str, device) -> P
 
 def init_parallel(rank: int, world_size: int, tp_size: int, *, master_addr: str = "127.0.0.1", master_port: int = 0,
                   backend: str | None = None, device: torch.device | None = None,
-                  timeout_s: float = 1800.0, rollout_tp_size: int | None = None) -> ParallelContext:
+                  timeout_s: float = 1800.0, rollout_tp_size: int | None = None,
+                  expert_parallel: bool = False) -> ParallelContext:
     """Create the default group plus TP / DP sub-groups and install the global context.  With
-    ``rollout_tp_size`` different from ``tp_size`` a second layout is created as ``ctx.rollout``."""
+    ``rollout_tp_size`` different from ``tp_size`` a second layout is created as ``ctx.rollout``.  With
+    ``expert_parallel`` the data-parallel group doubles as the expert-parallel group (``tp_size`` must be 1)."""
     if device is None:
         device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
     if backend is None:
@@ -113,6 +124,13 @@ def init_parallel(rank: int, world_size: int, tp_size: int, *, master_addr: str 
     ctx = _layout(rank, world_size, tp_size, backend, device)
     if rollout_tp_size and rollout_tp_size != tp_size:
         ctx.rollout = _layout(rank, world_size, rollout_tp_size, backend, device)
+    if expert_parallel and world_size > 1:
+        if tp_size != 1 or ctx.rollout is not None:
+            raise ValueError("expert parallelism runs over the data-parallel group: tp_size and rollout_tp_size must be 1")
+        ctx.ep_size, ctx.ep_rank, ctx.ep_group = ctx.dp_size, ctx.dp_rank, ctx.dp_group
+        # collective: every rank creates the control group (host tensors, so never queued behind GPU work)
+        ctx.ep_ctl_group = ctx.dp_group if backend == "gloo" else dist.new_group(ranks=list(range(world_size)),
+                                                                                 backend="gloo")
     set_context(ctx)
     return ctx
 

@@ -230,3 +230,210 @@ class _Combine(torch.autograd.Function):
         d_ys = comm._pull(slot, plan, per_token=False)
         comm.barrier()       # the pulls are done before anybody republishes (the next call may come at once)
         return d_ys, dweights, None, None
+
+
+# ------------------------------------------------------------------------------------------------------------
+# Collective fallback and the per-model runtime
+# ------------------------------------------------------------------------------------------------------------
+class _GroupGatherRows(torch.autograd.Function):
+    """All-gather along dim 0 over ``group``; the backward is the matching reduce-scatter (sum)."""
+
+    @staticmethod
+    def forward(ctx, x, group, size):
+        ctx.group, ctx.size = group, size
+        x = x.contiguous()
+        out = torch.empty((x.shape[0] * size, *x.shape[1:]), dtype=x.dtype, device=x.device)
+        torch.distributed.all_gather_into_tensor(out, x, group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous()
+        out = torch.empty((g.shape[0] // ctx.size, *g.shape[1:]), dtype=g.dtype, device=g.device)
+        torch.distributed.reduce_scatter_tensor(out, g, group=ctx.group)
+        return out, None, None
+
+
+class _GroupReduceScatterRows(torch.autograd.Function):
+    """Reduce-scatter (sum) along dim 0 over ``group``; the backward is the matching all-gather."""
+
+    @staticmethod
+    def forward(ctx, x, group, size):
+        ctx.group, ctx.size = group, size
+        x = x.contiguous()
+        out = torch.empty((x.shape[0] // size, *x.shape[1:]), dtype=x.dtype, device=x.device)
+        torch.distributed.reduce_scatter_tensor(out, x, group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous()
+        out = torch.empty((g.shape[0] * ctx.size, *g.shape[1:]), dtype=g.dtype, device=g.device)
+        torch.distributed.all_gather_into_tensor(out, g, group=ctx.group)
+        return out, None, None
+
+
+def _reduce_scatter_any(x, group, size):
+    """``reduce_scatter_tensor`` where the backend has it, all-reduce + slice otherwise (gloo)."""
+    if x.is_cuda:
+        return _GroupReduceScatterRows.apply(x, group, size)
+    return _ReduceScatterViaAllReduce.apply(x, group, size)
+
+
+def _gather_any(x, group, size):
+    if x.is_cuda:
+        return _GroupGatherRows.apply(x, group, size)
+    return _GatherViaAllGather.apply(x, group, size)
+
+
+class _GatherViaAllGather(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group, size):
+        ctx.group, ctx.size = group, size
+        ctx.rank = torch.distributed.get_rank(group)
+        parts = [torch.empty_like(x) for _ in range(size)]
+        torch.distributed.all_gather(parts, x.contiguous(), group=group)
+        return torch.cat(parts, dim=0)
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous().clone()
+        torch.distributed.all_reduce(g, group=ctx.group)
+        n = g.shape[0] // ctx.size
+        return g[ctx.rank * n:(ctx.rank + 1) * n], None, None
+
+
+class _ReduceScatterViaAllReduce(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group, size):
+        ctx.group, ctx.size = group, size
+        ctx.rank = torch.distributed.get_rank(group)
+        x = x.contiguous().clone()
+        torch.distributed.all_reduce(x, group=group)
+        n = x.shape[0] // size
+        return x[ctx.rank * n:(ctx.rank + 1) * n].clone()
+
+    @staticmethod
+    def backward(ctx, g):
+        parts = [torch.empty_like(g) for _ in range(ctx.size)]
+        torch.distributed.all_gather(parts, g.contiguous(), group=ctx.group)
+        return torch.cat(parts, dim=0), None, None
+
+
+class EpCommCollective:
+    """Expert parallelism on library collectives: tokens, routing tables and routing weights are all-gathered
+    (padded to ``cap`` rows per rank), every rank serves the routes that hit its experts, and the partial outputs
+    are reduce-scattered back to the tokens' owners.  Same interface as ``EpComm``; it is the baseline the
+    peer-memory path is measured against, the path CPU (gloo) runs take, and differentiable through the
+    collectives' own backward rules."""
+
+    kind = "collective"
+
+    def __init__(self, group, size: int, rank: int, hidden: int, cap_tokens: int, k: int, num_experts: int, device):
+        self.group, self.n, self.rank, self.device = group, int(size), int(rank), device
+        self.hidden, self.cap, self.k = int(hidden), int(cap_tokens), int(k)
+        self.e_local = num_experts // self.n
+        self.e_lo = self.rank * self.e_local
+
+    def dispatch(self, x: torch.Tensor, ids: torch.Tensor):
+        t = x.shape[0]
+        if t > self.cap:
+            raise ValueError(f"dispatch: {t} tokens do not fit cap={self.cap}")
+        pad = self.cap - t
+        xp = torch.nn.functional.pad(x, (0, 0, 0, pad)) if pad else x
+        idp = torch.nn.functional.pad(ids.to(torch.int32), (0, 0, 0, pad), value=-1) if pad else ids.to(torch.int32)
+        x_all = _gather_any(xp, self.group, self.n)
+        ids_all = _gather_any(idp.contiguous(), self.group, self.n)
+        plan = moe_ops.align(ids_all, self.e_lo, self.e_local)
+        rows = moe_ops.permute(x_all, plan)
+        return rows, EpPlan(plan, 0, t, self.k)
+
+    def combine(self, ys: torch.Tensor, weights: torch.Tensor, plan: EpPlan) -> torch.Tensor:
+        t = plan.tokens
+        pad = self.cap - t
+        wp = torch.nn.functional.pad(weights.float(), (0, 0, 0, pad)) if pad else weights.float()
+        w_all = _gather_any(wp.contiguous(), self.group, self.n)
+        partial = moe_ops.combine(ys, plan.moe, w_all)              # [n * cap, H]: this rank's experts only
+        mine = _reduce_scatter_any(partial, self.group, self.n)     # [cap, H]
+        return mine[:t]
+
+    def dropped(self) -> int:
+        return 0
+
+    def barrier(self) -> None:
+        torch.distributed.barrier(group=self.group)
+
+    def close(self) -> None:
+        pass
+
+
+class EpRuntime:
+    """The expert-parallel communicators of one process.  A communicator is sized for a token capacity; forward
+    passes of different sizes (a training micro-batch, a prefill chunk, a decode step) use different ones, picked
+    by power-of-two bucket.  Every rank of the group must run the same sequence of MoE calls with the same
+    bucket, so callers that cannot know the other ranks' sizes agree on them first (``agree_max``) and pin the
+    bucket for the pass (``with runtime.pinned(tokens)``)."""
+
+    MIN_CAP = 64
+
+    def __init__(self, ctx, hidden: int, k: int, num_experts: int, device, capacity: float | None = None,
+                 impl: str | None = None):
+        self.ctx, self.hidden, self.k, self.num_experts = ctx, int(hidden), int(k), int(num_experts)
+        self.device = torch.device(device)
+        self.capacity = float(capacity if capacity is not None else os.environ.get("ARENO_EP_CAPACITY", "2.0"))
+        impl = impl or os.environ.get("ARENO_EP_IMPL", "peer")
+        self.impl = impl if self.device.type == "cuda" else "collective"
+        self._comms: dict[int, object] = {}
+        self._pinned: int | None = None
+
+    @staticmethod
+    def bucket(tokens: int) -> int:
+        cap = EpRuntime.MIN_CAP
+        while cap < tokens:
+            cap *= 2
+        return cap
+
+    def comm(self, tokens: int):
+        cap = self.bucket(self._pinned if self._pinned is not None else tokens)
+        if tokens > cap:
+            raise ValueError(f"{tokens} tokens exceed the bucket pinned for this pass ({cap})")
+        c = self._comms.get(cap)
+        if c is None:
+            ctx = self.ctx
+            if self.impl == "collective":
+                c = EpCommCollective(ctx.ep_group, ctx.ep_size, ctx.ep_rank, self.hidden, cap, self.k,
+                                     self.num_experts, self.device)
+            else:
+                c = EpComm(ctx.ep_group, ctx.ep_size, ctx.ep_rank, self.hidden, cap, self.k, self.num_experts,
+                           self.device, capacity=self.capacity)
+            self._comms[cap] = c
+        return c
+
+    def pinned(self, tokens: int):
+        """Context manager: every MoE call inside uses the bucket of ``tokens`` (the group-wide maximum)."""
+        rt = self
+
+        class _Pin:
+            def __enter__(self_inner):
+                self_inner.prev = rt._pinned
+                rt._pinned = int(tokens)
+
+            def __exit__(self_inner, *exc):
+                rt._pinned = self_inner.prev
+                return False
+
+        return _Pin()
+
+    def agree_max(self, values: list[int]) -> list[int]:
+        """Element-wise maximum of ``values`` over the group, computed on the host (gloo)."""
+        t = torch.tensor(list(values), dtype=torch.int64)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX, group=self.ctx.ep_ctl_group)
+        return [int(v) for v in t.tolist()]
+
+    def dropped(self) -> int:
+        return sum(int(c.dropped()) for c in self._comms.values())
+
+    def close(self) -> None:
+        for c in self._comms.values():
+            c.close()
+        self._comms.clear()

@@ -367,12 +367,21 @@ class TpComm:
     def one_shot(self, rows: int) -> bool:
         """One flag exchange and every rank reduces all rows itself, or the two-shot reduce-scatter + all-gather?
         One-shot moves ``rows x H`` into each rank with multimem and ``(tp - 1)`` times that with plain loads, against
-        ``3 (tp - 1) / tp`` for two-shot: it wins always with multimem or two ranks, and for decode-sized calls, which
-        are bound by the flag round trip.  ``ARENO_TP_ONESHOT`` = 0 / 1 forces a choice."""
+        ``3 (tp - 1) / tp`` for two-shot.  Measured: one-shot wins between two ranks and for decode-sized calls, which
+        are bound by the flag round trip (1.5x NCCL at 128 rows on 8 GPUs); from a few thousand rows on every rank
+        pulling every row through the switch loses to the two-shot kernel on plain peer loads (4096 rows on 8 GPUs:
+        502 us against 218 us, NCCL 248 us).  ``ARENO_TP_ONESHOT`` = 0 / 1 forces a choice."""
         forced = os.environ.get("ARENO_TP_ONESHOT")
         if forced in ("0", "1"):
             return forced == "1"
-        return self.use_mc or self.tp == 2 or rows <= 1024
+        return self.tp == 2 or rows <= 1024
+
+    def multimem(self, rows: int) -> bool:
+        """Switch-side reduction for this call?  Only with the one-shot kernel (see ``one_shot``), unless
+        ``ARENO_TP_MULTIMEM=1`` asks for it everywhere."""
+        if not self.use_mc:
+            return False
+        return self.one_shot(rows) or os.environ.get("ARENO_TP_MULTIMEM") == "1"
 
     def partial_view(self, slot: int, rows: int) -> torch.Tensor:
         lo = slot * self.slot_elems
@@ -407,7 +416,7 @@ class TpComm:
         if residual is not None and not residual.is_contiguous():
             residual = residual.contiguous()
         _lib.call("areno_tp_reduce_norm", ctypes.addressof(self.desc), lo, _lib.ptr(residual), _lib.ptr(weight), wf32,
-                  float(w_offset), int(want_y), rows, n, float(eps), int(self.use_mc), int(self.one_shot(rows)),
+                  float(w_offset), int(want_y), rows, n, float(eps), int(self.multimem(rows)), int(self.one_shot(rows)),
                   _lib.stream())
         h = self._h[lo: lo + rows * n].view(rows, n)
         y = self._y[lo: lo + rows * n].view(rows, n) if want_y else None

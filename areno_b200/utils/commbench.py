@@ -128,7 +128,7 @@ def bench_tp_fused(ctx, rows: int, hidden: int, k_full: int, iters: int, warmup:
     g = rows <= 1024      # decode-sized calls live inside captured graphs; time them that way
     t_flush = _timed(flush_only, iters, warmup, ctx.tp_group, g)
     out = {"case": "tp_fused", "tp": tp, "rows": rows, "hidden": hidden, "k_local": k_local,
-           "multimem": bool(comm.use_mc), "one_shot": bool(comm.one_shot(rows)), "heap": comm.heap.kind,
+           "multimem": bool(comm.multimem(rows)), "one_shot": bool(comm.one_shot(rows)), "heap": comm.heap.kind,
            "timed_in_cuda_graph": g}
     t_f = _timed(fused, iters, warmup, ctx.tp_group, g) - t_flush
     t_n = _timed(nccl, iters, warmup, ctx.tp_group, g) - t_flush
@@ -136,7 +136,7 @@ def bench_tp_fused(ctx, rows: int, hidden: int, k_full: int, iters: int, warmup:
     t_nc = _timed(nccl_collective_only, iters, warmup, ctx.tp_group, g)
     flops = 2.0 * rows * hidden * k_local
     if comm.one_shot(rows):      # every rank takes in the finished sums (multimem) or tp - 1 remote partials
-        link_bytes = (1.0 if comm.use_mc else float(tp - 1)) * rows * hidden * 2
+        link_bytes = (1.0 if comm.multimem(rows) else float(tp - 1)) * rows * hidden * 2
     else:
         link_bytes = 3.0 * (tp - 1) / tp * rows * hidden * 2
     weight_bytes = 2.0 * hidden * k_local
@@ -181,7 +181,7 @@ def bench_tp_layer(ctx, rows: int, iters: int, warmup: int, comm, ctx_len: int =
     meta = InferMeta(mode="decode", slot_mapping=slots, block_table=table, seq_lens=lens, max_context=ctx_len + 64)
     h = (torch.randn(rows, mcfg.hidden_size, device=dev) * 0.5).to(torch.bfloat16)
     res = h.clone()
-    out: dict = {"case": "tp_layer", "tp": ctx.tp_size, "rows": rows, "ctx": ctx_len, "multimem": bool(comm.use_mc),
+    out: dict = {"case": "tp_layer", "tp": ctx.tp_size, "rows": rows, "ctx": ctx_len, "multimem": bool(comm.multimem(rows)),
                  "one_shot": bool(comm.one_shot(rows))}
     state: dict = {}
 

@@ -107,5 +107,7 @@ def test_peer_memory_grad_reduce_scatter_matches_nccl(world):
         assert isinstance(out, dict), out
         assert max(out["errs"]) < 2e-5, out["errs"]                      # fp32 sums of `world` terms: equal up to order
         assert abs(out["norm"][0] - out["norm"][1]) < 1e-4 * max(1.0, out["norm"][1])
-        assert out["pdiff"] < 1e-5
+        # parameters after the step: the two paths add the ranks' gradients in different orders, which may flip the
+        # bf16 rounding of single elements (one bf16 step at the weights' magnitude is 1.5e-5)
+        assert out["pdiff"] < 4e-5
         assert out["buckets"] >= 4 and out["early"] >= out["buckets"] - 2   # most buckets left during backward
