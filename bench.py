@@ -43,6 +43,16 @@ NEW_TOKENS = 1024
 MICRO_TOKENS = 4096
 BASELINE_PUBLISHED = None  # the reference publishes no number for this metric
 
+# --config moe30b: Qwen3-30B-A3B shape, expert parallel over all ranks, 4 prompts x group 8 per GPU (32 x 8 on 8 GPUs),
+# 2048 new tokens.  The full 48 layers need the 8-GPU layout (3.6 G expert parameters per rank with their fp32
+# optimizer state); with fewer GPUs the layer count shrinks in proportion so that the per-rank footprint stays.
+MOE_MODEL = dict(model_type="qwen3_moe", vocab_size=151936, hidden_size=2048, intermediate_size=6144,
+                 num_hidden_layers=48, num_attention_heads=32, num_key_value_heads=4, head_dim=128,
+                 rms_norm_eps=1e-6, rope_theta=1_000_000.0, max_position_embeddings=32768, qkv_bias=False,
+                 qk_norm=True, tie_word_embeddings=False, num_experts=128, num_experts_per_tok=8,
+                 moe_intermediate_size=768, norm_topk_prob=True)
+MOE_PROMPTS_PER_GPU, MOE_NEW_TOKENS = 4, 2048
+
 
 def parse_args():
     ap = argparse.ArgumentParser()
@@ -50,8 +60,9 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", default="grpo7b", choices=["grpo7b", "serve8b", "dpo7b"],
-                    help="grpo7b: the headline RL step (default); serve8b / dpo7b: see bench_extra.py")
+    ap.add_argument("--config", default="grpo7b", choices=["grpo7b", "moe30b", "serve8b", "dpo7b"],
+                    help="grpo7b: the headline RL step (default); moe30b: the same step on a Qwen3-30B-A3B-shaped "
+                         "mixture-of-experts model with expert parallelism; serve8b / dpo7b: see bench_extra.py")
     ap.add_argument("--small", action="store_true", help="tiny model / short rollout (functional check only)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--adam-8bit", action="store_true")
@@ -197,18 +208,30 @@ def run_ours(args):
         raise SystemExit(f"--gpus {args.gpus} does not match WORLD_SIZE {world}")
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
-    rollout_tp = args.rollout_tp or pick_rollout_tp(world)
-    ctx = init_parallel(rank, world, tp_size=1, device=device, rollout_tp_size=rollout_tp)
+    moe = args.config == "moe30b"
+    ep = moe and world > 1
+    rollout_tp = 1 if moe else (args.rollout_tp or pick_rollout_tp(world))
+    ctx = init_parallel(rank, world, tp_size=1, device=device, rollout_tp_size=rollout_tp, expert_parallel=ep)
+    balance = balance or ep      # expert parallel: every rank must run the same number of micro-batches
 
-    model_kw = dict(MODEL)
+    model_kw = dict(MOE_MODEL if moe else MODEL)
     new_tokens, pmin, pmax, n_prompts = NEW_TOKENS, PROMPT_MIN, PROMPT_MAX, PROMPTS_PER_GPU
-    if args.small:
+    if moe:
+        new_tokens, n_prompts = MOE_NEW_TOKENS, MOE_PROMPTS_PER_GPU
+        if world < 8:
+            model_kw["num_hidden_layers"] = 6 * world
+    if args.small and moe:
+        model_kw.update(hidden_size=512, num_hidden_layers=4, num_attention_heads=8, num_key_value_heads=2, head_dim=64,
+                        vocab_size=32000, num_experts=16, num_experts_per_tok=4, moe_intermediate_size=256)
+        new_tokens, pmin, pmax = 64, 32, 96
+    elif args.small:
         model_kw.update(hidden_size=512, intermediate_size=1536, num_hidden_layers=4, num_attention_heads=4,
                         num_key_value_heads=2, vocab_size=32000)
         new_tokens, pmin, pmax = 64, 32, 96
     mcfg = ModelConfig(**model_kw)
     cfg = EngineConfig(
-        model=mcfg, tp_size=1, dp_size=world, rollout_tp_size=rollout_tp, devices=list(range(world)), dummy_load=True,
+        model=mcfg, tp_size=1, dp_size=world, rollout_tp_size=None if moe else rollout_tp, expert_parallel=ep,
+        devices=list(range(world)), dummy_load=True,
         optimizer=OptimizerConfig(lr=1e-6, betas=(0.9, 0.999), weight_decay=0.01, grad_clip_norm=1.0,
                                   adam_8bit=args.adam_8bit),
         runtime=RuntimeConfig(activation_checkpointing=True, max_model_len=(pmax + new_tokens + 63) // 64 * 64),
@@ -315,7 +338,10 @@ def run_ours(args):
     phases = tracing.phase_report_max() if tracing.enabled() else None
 
     e2e = None
-    if not args.no_e2e:
+    if ep:
+        checks["ep_impl"] = ctx.ep_runtime.impl
+        checks["ep_dropped_routes"] = ctx.ep_runtime.dropped()
+    if not args.no_e2e and not moe:
         e2e = run_e2e(args, worker, mcfg, params, rank, world, device, n_prompts, pmin, pmax, new_tokens)
 
     if rank == 0:
@@ -329,10 +355,14 @@ def run_ours(args):
             **({"device_phase_ms_per_step": {k: round(v["ms"] / args.steps, 3) for k, v in sorted(phases.items())}}
                if phases else {}),
             "config": {
-                "model": "Qwen2.5-7B-shaped" if not args.small else "small-debug", "global_batch": n_prompts * GROUP * world,
+                "model": ("small-debug" if args.small else
+                          (f"Qwen3-30B-A3B-shaped, {mcfg.num_hidden_layers} of 48 layers" if moe else "Qwen2.5-7B-shaped")),
+                "global_batch": n_prompts * GROUP * world,
                 "prompts_per_gpu": n_prompts, "group": GROUP, "prompt_len": [pmin, pmax], "new_tokens": new_tokens,
                 "seq_len": pmax + new_tokens, "micro_batch_tokens": MICRO_TOKENS,
-                "parallelism": f"rollout dp{world // rollout_tp} x tp{rollout_tp} (paged bf16 KV, CUDA-graph decode), "
+                "parallelism": (f"ep{world}: 128 experts dealt out over the ranks, tokens exchanged over peer memory in "
+                                f"every MoE layer of rollout and training; dense parts dp{world}; " if ep else "")
+                               + f"rollout dp{world // rollout_tp} x tp{rollout_tp} (paged bf16 KV, CUDA-graph decode), "
                                f"train dp{world} sharded grads+optimizer, weight sync: "
                                + ("in place (shared buffers)" if rollout_tp == 1 else
                                   "local reshard of the DP replica into the TP shards; row-parallel all-reduce fused with "

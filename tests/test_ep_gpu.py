@@ -1,4 +1,4 @@
-"""Two and four GPUs: the expert-parallel MoE path (routing tables and tokens exchanged over peer memory, grouped
+"""Two, four and eight GPUs: the expert-parallel MoE path (routing tables and tokens exchanged over peer memory, grouped
 tcgen05 GEMMs on the expert owners, outputs scattered back) against a single-device fp32 computation on the gathered
 tokens with all experts, forward and backward.  Skipped on a box with fewer GPUs."""
 
@@ -96,7 +96,7 @@ def _rank_main(rank, world, port, ret):
             pass
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_expert_parallel_moe_matches_all_experts_on_one_device(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
