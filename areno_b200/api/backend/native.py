@@ -255,13 +255,15 @@ class NativeBackend(Backend):
             raise ValueError("train batch is empty")
         mini_bs = max(int(mini_bs), 1)
         packs, counts = [], []
+        sft = _is_sft(loss_fn)
         for s in range(0, len(batch_data), mini_bs):
             chunk = batch_data[s:s + mini_bs]
             pack = make_train_pack(chunk)
             pack["_loss_fn"] = loss_fn
             packs.append(pack)
-            counts.append(sft_target_token_count(chunk))
-        if _is_sft(loss_fn):
+            if sft:      # a walk over every token on the host: only the token-mean SFT loss needs the counts
+                counts.append(sft_target_token_count(chunk))
+        if sft:
             annotate_sft_token_mean_packs(packs, counts, gradient_accumulation_steps=gradient_accumulation_steps)
         stats = self._require().step(packs, gradient_accumulation_steps=gradient_accumulation_steps)
         return self._reduce_stats(stats, time.perf_counter() - t0)

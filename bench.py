@@ -407,13 +407,16 @@ def run_e2e(args, worker, mcfg, params, rank, world, device, n_prompts, pmin, pm
     loss_fn = partial(grpo_loss_fn, clip_eps=0.2)
     steps = max(1, min(args.steps, 2))
     counters = {"h2d": 0, "d2h": 0}
+    wall = {"rollout_call_s": 0.0, "build_batch_s": 0.0, "train_call_s": 0.0}
 
     def step(i):
         prompts = []
         for r in range(world):
             prompts.extend(make_prompts(10_000 + i, r, mcfg.vocab_size, n_prompts, pmin, pmax))
+        t_a = time.time()
         with trainer.rollout_session(sampling_params=api_params):
             results = trainer.rollout_token_batch(prompts, GROUP, api_params)
+        t_b = time.time()
         batch = []
         ntok = 0
         for p, res in zip(prompts, results):
@@ -424,7 +427,12 @@ def run_e2e(args, worker, mcfg, params, rank, world, device, n_prompts, pmin, pm
                                            logprobs=[0.0] * len(p) + s.resp_logprobs,
                                            advantages=[0.0] * len(p) + [adv] * n_r, reward=rew, eos_token_id=0))
                 ntok += len(p) + n_r
+        t_c = time.time()
         stats = trainer.train(batch, loss_fn, mini_bs=3 * world)
+        t_d = time.time()
+        wall["rollout_call_s"] += t_b - t_a
+        wall["build_batch_s"] += t_c - t_b
+        wall["train_call_s"] += t_d - t_c
         my_share = 1.0 / world
         # per rank: prompt ids (int64) for prefill; ids, positions (int64), 2 float32 signals, mask, seq ids for training
         counters["h2d"] += int(my_share * (sum(len(p) for p in prompts) * GROUP * 8 + ntok * (8 + 8 + 4 + 4 + 1 + 8)))
@@ -433,6 +441,8 @@ def run_e2e(args, worker, mcfg, params, rank, world, device, n_prompts, pmin, pm
 
     step(-1)
     counters["h2d"] = counters["d2h"] = 0
+    for k in wall:
+        wall[k] = 0.0
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
@@ -454,6 +464,7 @@ def run_e2e(args, worker, mcfg, params, rank, world, device, n_prompts, pmin, pm
             "h2d_bytes_per_step": counters["h2d"] // steps, "d2h_bytes_per_step": counters["d2h"] // steps,
             "timing": "wall clock around Trainer.rollout_token_batch + Trainer.train, max over ranks",
             "step_rollout_time_s": stats.get("step_rollout_time_s"), "step_train_time_s": stats.get("step_train_time_s"),
+            "wall_s_per_step_rank0": {k: round(v / steps, 3) for k, v in wall.items()},
             "loss": stats.get("loss")}
 
 
