@@ -182,7 +182,7 @@ class NativeBackend(Backend):
             cfg.model_path or ctx.model_path, tp_size=tp, dp_size=dp, devices=devices, dummy_load=cfg.dummy_load,
             optimizer_config=OptimizerConfig(**cfg.optimizer), runtime_config=RuntimeConfig(**cfg.runtime),
             model_config=cfg.model_config, launcher=cfg.launcher, max_running_seqs=cfg.max_running_prompts,
-            seed=cfg.seed, rollout_tp_size=cfg.rollout_tp_size)
+            seed=cfg.seed, rollout_tp_size=cfg.rollout_tp_size, expert_parallel=cfg.expert_parallel)
 
     def close(self) -> None:
         engine, self._engine = self._engine, None

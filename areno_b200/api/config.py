@@ -18,6 +18,9 @@ class ArenoConfig:
     dp_size: int | None = None
     # decode tensor-parallel over this many GPUs while training stays data parallel (needs tp_size == 1)
     rollout_tp_size: int | None = None
+    # mixture-of-experts models: deal the experts out over the data-parallel ranks and exchange tokens with their
+    # owners in every MoE layer, in rollout and training (needs tp_size == 1 and num_experts divisible by the ranks)
+    expert_parallel: bool = False
     devices: list[int] | None = None
     dummy_load: bool = False
     optimizer: dict[str, Any] = field(default_factory=dict)

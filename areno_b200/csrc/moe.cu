@@ -12,6 +12,8 @@
 //   route_row[T*k]     : sorted row of each route, or -1 if its expert is not local
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+
+#include <algorithm>
 #include <stdint.h>
 
 #include "common.cuh"
@@ -292,6 +294,120 @@ moe_align_kernel(const int* __restrict__ ids, int routes, int e_lo, int e_count,
   }
 }
 
+// ----------------------------------------------------------------------------------
+// The same plan from three launches, for many routes (a training micro-batch of an expert-parallel group has
+// 8 x 32768 of them, and the single-CTA kernel above walks all of them once per expert at one dependent
+// load per step).  Every warp owns a chunk of kAlignChunk consecutive routes:
+//   count   per-chunk histogram over the local experts (chunk_cnt[chunk][e]); row_route / tile_expert reset
+//   scan    one CTA: per-expert totals -> padded segments (capacity as above), then every chunk's counter is
+//           replaced by the first row of that chunk inside the expert's segment (exclusive prefix in chunk order)
+//   place   every warp walks its chunk again and hands out rows in route order
+// Rows are assigned in route order inside every expert, exactly as the single-CTA kernel does, so both give
+// the same plan.
+// ----------------------------------------------------------------------------------
+constexpr int kAlignChunk = 512;
+
+__global__ void __launch_bounds__(256)
+moe_align_count_kernel(const int* __restrict__ ids, int routes, int e_lo, int e_count, int max_rows,
+                       int* __restrict__ chunk_cnt, int* __restrict__ row_route, int* __restrict__ tile_expert) {
+  const int gtid = blockIdx.x * blockDim.x + threadIdx.x, gsize = gridDim.x * blockDim.x;
+  for (int i = gtid; i < max_rows; i += gsize) row_route[i] = -1;
+  for (int i = gtid; i < max_rows / kMoeTile; i += gsize) tile_expert[i] = -1;
+  const int lane = threadIdx.x & 31;
+  const int nchunks = (routes + kAlignChunk - 1) / kAlignChunk;
+  for (int chunk = gtid >> 5; chunk < nchunks; chunk += gsize >> 5) {
+    int* cnt = chunk_cnt + (size_t)chunk * e_count;
+    for (int e = lane; e < e_count; e += 32) cnt[e] = 0;
+    __syncwarp();
+    const int base = chunk * kAlignChunk;
+    for (int r0 = 0; r0 < kAlignChunk; r0 += 32) {
+      const int r = base + r0 + lane;
+      int e = r < routes ? ids[r] - e_lo : -1;
+      if (e >= e_count) e = -1;
+      const uint32_t m = __match_any_sync(0xffffffffu, e);
+      if (e >= 0 && lane == __ffs(m) - 1) cnt[e] += __popc(m);     // one writer per expert and step
+      __syncwarp();
+    }
+  }
+}
+
+__global__ void __launch_bounds__(1024)
+moe_align_scan_kernel(int routes, int e_count, int max_rows, int* __restrict__ chunk_cnt, int* __restrict__ limit,
+                      int* __restrict__ expert_rows, int* __restrict__ tile_expert, int* __restrict__ counts_out,
+                      int* __restrict__ dropped_out) {
+  extern __shared__ int sh[];  // [e_count] totals, [e_count] offsets
+  int* tot = sh;
+  int* off = sh + e_count;
+  const int nchunks = (routes + kAlignChunk - 1) / kAlignChunk;
+  for (int e = threadIdx.x; e < e_count; e += blockDim.x) {
+    int c = 0;
+    for (int ch = 0; ch < nchunks; ++ch) c += chunk_cnt[(size_t)ch * e_count + e];
+    tot[e] = c;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int o = 0, dropped = 0;
+    for (int e = 0; e < e_count; ++e) {
+      int padded = (tot[e] + kMoeTile - 1) / kMoeTile * kMoeTile;
+      if (o + padded > max_rows) padded = (max_rows - o) / kMoeTile * kMoeTile;
+      const int fit = min(tot[e], padded);
+      dropped += tot[e] - fit;
+      off[e] = o;
+      limit[e] = o + fit;
+      expert_rows[2 * e] = o;
+      expert_rows[2 * e + 1] = padded;
+      if (counts_out != nullptr) counts_out[e] = fit;
+      for (int tile = o / kMoeTile; tile < (o + padded) / kMoeTile; ++tile) tile_expert[tile] = e;
+      o += padded;
+    }
+    if (dropped_out != nullptr) *dropped_out = dropped;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < e_count; e += blockDim.x) {
+    int run = off[e];
+    for (int ch = 0; ch < nchunks; ++ch) {
+      const size_t i = (size_t)ch * e_count + e;
+      const int c = chunk_cnt[i];
+      chunk_cnt[i] = run;
+      run += c;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+moe_align_place_kernel(const int* __restrict__ ids, int routes, int e_lo, int e_count, int* __restrict__ chunk_cnt,
+                       const int* __restrict__ limit, int* __restrict__ row_route, int* __restrict__ route_row) {
+  const int gtid = blockIdx.x * blockDim.x + threadIdx.x, gsize = gridDim.x * blockDim.x;
+  const int lane = threadIdx.x & 31;
+  const int nchunks = (routes + kAlignChunk - 1) / kAlignChunk;
+  for (int chunk = gtid >> 5; chunk < nchunks; chunk += gsize >> 5) {
+    int* next = chunk_cnt + (size_t)chunk * e_count;       // next free row of every expert for this chunk
+    const int base = chunk * kAlignChunk;
+    for (int r0 = 0; r0 < kAlignChunk; r0 += 32) {
+      const int r = base + r0 + lane;
+      int e = r < routes ? ids[r] - e_lo : -1;
+      if (e >= e_count) e = -1;
+      const uint32_t m = __match_any_sync(0xffffffffu, e);
+      const int leader = __ffs(m) - 1;
+      int first = (e >= 0 && lane == leader) ? next[e] : 0;
+      first = __shfl_sync(0xffffffffu, first, leader);
+      if (e >= 0) {
+        const int row = first + __popc(m & ((1u << lane) - 1u));
+        if (row < limit[e]) {
+          row_route[row] = r;
+          route_row[r] = row;
+        } else {
+          route_row[r] = -1;
+        }
+        if (lane == leader) next[e] = first + __popc(m);
+      } else if (r < routes) {
+        route_row[r] = -1;      // the expert lives on another rank
+      }
+      __syncwarp();
+    }
+  }
+}
+
 // xs[row] = x[row_route[row] / k]  (zeros for padding rows)
 __global__ void __launch_bounds__(256)
 moe_permute_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ row_route, int k, int max_rows, int H,
@@ -443,6 +559,32 @@ extern "C" int areno_moe_align(const int* ids, long long routes, int e_lo, int e
   moe_align_kernel<<<1, 1024, 3 * e_count * sizeof(int), stream>>>(ids, (int)routes, e_lo, e_count, (int)max_rows,
                                                                   expert_rows, tile_expert, row_route, route_row, counts,
                                                                   nullptr);
+  return (int)cudaGetLastError();
+}
+
+// The plan from the three-launch path above.  scratch: int32 [areno_moe_align_scratch_ints(routes, e_count)];
+// dropped may be null (then max_rows must cover every case).
+extern "C" long long areno_moe_align_scratch_ints(long long routes, int e_count) {
+  return ((routes + kAlignChunk - 1) / kAlignChunk + 1) * (long long)e_count;
+}
+
+extern "C" int areno_moe_align_par(const int* ids, long long routes, int e_lo, int e_count, long long max_rows,
+                                   int* expert_rows, int* tile_expert, int* row_route, int* route_row, int* counts,
+                                   int* dropped, int* scratch, cudaStream_t stream) {
+  if (e_count < 1 || e_count > 4096 || max_rows % kMoeTile != 0 || max_rows < kMoeTile || routes < 1 ||
+      scratch == nullptr)
+    return -3;
+  const long long nchunks = (routes + kAlignChunk - 1) / kAlignChunk;
+  int* chunk_cnt = scratch;
+  int* limit = scratch + nchunks * e_count;
+  const int warps = (int)std::min<long long>(nchunks, 148 * 16);
+  const int grid = std::max((warps + 7) / 8, std::min<int>(148, (int)((max_rows + 255) / 256)));
+  moe_align_count_kernel<<<grid, 256, 0, stream>>>(ids, (int)routes, e_lo, e_count, (int)max_rows, chunk_cnt, row_route,
+                                                   tile_expert);
+  moe_align_scan_kernel<<<1, 1024, 2 * e_count * sizeof(int), stream>>>((int)routes, e_count, (int)max_rows, chunk_cnt,
+                                                                        limit, expert_rows, tile_expert, counts, dropped);
+  moe_align_place_kernel<<<(warps + 7) / 8, 256, 0, stream>>>(ids, (int)routes, e_lo, e_count, chunk_cnt, limit, row_route,
+                                                             route_row);
   return (int)cudaGetLastError();
 }
 

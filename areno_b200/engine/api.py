@@ -59,7 +59,8 @@ class ArenoEngine:
                         optimizer_config: OptimizerConfig | None = None, runtime_config: RuntimeConfig | None = None,
                         loss_fn: Callable | None = None, model_config: ModelConfig | None = None,
                         launcher: str | None = None, max_running_seqs: int = 64, seed: int = 0,
-                        backend: str | None = None, rollout_tp_size: int | None = None) -> "ArenoEngine":
+                        backend: str | None = None, rollout_tp_size: int | None = None,
+                        expert_parallel: bool = False) -> "ArenoEngine":
         if model_config is None:
             if model is None:
                 raise ValueError("from_pretrained() requires a local model path or an explicit model_config")
@@ -70,7 +71,7 @@ class ArenoEngine:
         cfg = EngineConfig(model=model_config, model_path=model or "", tp_size=tp_size, dp_size=dp_size, devices=devices,
                            dummy_load=dummy_load or not model, optimizer=optimizer_config or OptimizerConfig(),
                            runtime=runtime_config or RuntimeConfig(), max_running_seqs=max_running_seqs, seed=seed,
-                           backend=backend, rollout_tp_size=rollout_tp_size)
+                           backend=backend, rollout_tp_size=rollout_tp_size, expert_parallel=expert_parallel)
         return cls(cfg, loss_fn=loss_fn, launcher=launcher)
 
     # ---------------------------------------------------------------- sessions

@@ -23,6 +23,14 @@ _lib.register_signature("areno_topk_softmax_fwd", "piliiippp")
 _lib.register_signature("areno_topk_softmax_bwd", "pipppliiipp")
 _lib.register_signature("areno_grouped_sigmoid_topk", "ppliiiiifppp")
 _lib.register_signature("areno_moe_align", "pliilpppppp")
+_lib.register_signature("areno_moe_align_par", "pliilpppppppp")
+# from this many routes on the plan is built by the three-launch kernels (one warp per 512 routes) instead of the
+# single-CTA kernel, whose time grows with routes x experts
+PAR_ALIGN_MIN_ROUTES = 4096
+
+
+def align_scratch(routes: int, e_count: int, device) -> torch.Tensor:
+    return torch.empty(((routes + 511) // 512 + 1) * e_count, dtype=torch.int32, device=device)
 _lib.register_signature("areno_moe_permute", "ppilipp")
 _lib.register_signature("areno_moe_combine", "pppliipp")
 _lib.register_signature("areno_moe_combine_bwd", "ppppillippp")
@@ -132,8 +140,13 @@ def align(ids: torch.Tensor, e_lo: int, e_count: int) -> MoePlan:
     rr = torch.empty(max_rows, dtype=torch.int32, device=dev)
     ro = torch.empty(routes, dtype=torch.int32, device=dev)
     cnt = torch.empty(e_count, dtype=torch.int32, device=dev)
-    _lib.call("areno_moe_align", flat.data_ptr(), routes, e_lo, e_count, max_rows, er.data_ptr(), te.data_ptr(),
-              rr.data_ptr(), ro.data_ptr(), cnt.data_ptr(), _lib.stream())
+    if routes >= PAR_ALIGN_MIN_ROUTES:
+        scratch = align_scratch(routes, e_count, dev)
+        _lib.call("areno_moe_align_par", flat.data_ptr(), routes, e_lo, e_count, max_rows, er.data_ptr(), te.data_ptr(),
+                  rr.data_ptr(), ro.data_ptr(), cnt.data_ptr(), None, scratch.data_ptr(), _lib.stream())
+    else:
+        _lib.call("areno_moe_align", flat.data_ptr(), routes, e_lo, e_count, max_rows, er.data_ptr(), te.data_ptr(),
+                  rr.data_ptr(), ro.data_ptr(), cnt.data_ptr(), _lib.stream())
     if _lib.BOUNDS_CHECK:     # the plan drives every later gather / scatter and the grouped GEMM: validate it once here
         _lib.check_index("moe plan row_route", rr, routes, low=-1)
         _lib.check_index("moe plan route_row", ro, max_rows, low=-1)

@@ -123,9 +123,15 @@ class EpComm:
         rr = torch.empty(self.max_rows, dtype=torch.int32, device=dev)
         ro = torch.empty(routes, dtype=torch.int32, device=dev)
         cnt = torch.empty(self.e_local, dtype=torch.int32, device=dev)
-        _lib.call("areno_moe_align_capped", ids_all.data_ptr(), routes, self.e_lo, self.e_local, self.max_rows,
-                  er.data_ptr(), te.data_ptr(), rr.data_ptr(), ro.data_ptr(), cnt.data_ptr(), self._dropped.data_ptr(),
-                  _lib.stream())
+        if routes >= moe_ops.PAR_ALIGN_MIN_ROUTES:
+            scratch = moe_ops.align_scratch(routes, self.e_local, dev)
+            _lib.call("areno_moe_align_par", ids_all.data_ptr(), routes, self.e_lo, self.e_local, self.max_rows,
+                      er.data_ptr(), te.data_ptr(), rr.data_ptr(), ro.data_ptr(), cnt.data_ptr(),
+                      self._dropped.data_ptr(), scratch.data_ptr(), _lib.stream())
+        else:
+            _lib.call("areno_moe_align_capped", ids_all.data_ptr(), routes, self.e_lo, self.e_local, self.max_rows,
+                      er.data_ptr(), te.data_ptr(), rr.data_ptr(), ro.data_ptr(), cnt.data_ptr(),
+                      self._dropped.data_ptr(), _lib.stream())
         self._dropped_total += self._dropped
         plan = moe_ops.MoePlan(self.n * self.cap, self.k, self.e_local, self.max_rows, er, te, rr, ro, cnt)
         return EpPlan(plan, slot, tokens, self.k)

@@ -141,3 +141,35 @@ def test_wgrad_accumulates_into_main_grad():
     for e, (lo, n) in enumerate(er):
         ref[e] += dys[lo:lo + n].float().t() @ xs[lo:lo + n].float()
     assert _rel(w.main_grad, ref) < 1e-2
+
+
+@pytest.mark.parametrize("routes,E,e_lo,e_count,max_rows,drops", [
+    (65536, 128, 16, 16, 4096, True), (262144, 128, 0, 16, 16384, True), (5000, 64, 0, 64, 4096, True),
+    (9000, 32, 8, 8, 16384, False)])
+def test_three_launch_align_matches_the_single_cta_kernel_with_capacity(routes, E, e_lo, e_count, max_rows, drops):
+    """Plan built by count / scan / place kernels against the single-CTA kernel, for a row buffer smaller than the
+    static bound (routes are dropped) and with -1 entries (padding of an expert-parallel routing table)."""
+    from areno_b200.parallel import ep  # noqa: F401  (registers the capped entry point)
+
+    torch.manual_seed(5)
+    ids = torch.randint(0, E, (routes,), dtype=torch.int32, device="cuda")
+    ids[torch.rand(routes, device="cuda") < 0.1] = -1
+    plans = []
+    for name in ("areno_moe_align_capped", "areno_moe_align_par"):
+        er = torch.empty(2 * e_count, dtype=torch.int32, device="cuda")
+        te = torch.empty(max_rows // 128, dtype=torch.int32, device="cuda")
+        rr = torch.empty(max_rows, dtype=torch.int32, device="cuda")
+        ro = torch.empty(routes, dtype=torch.int32, device="cuda")
+        cnt = torch.empty(e_count, dtype=torch.int32, device="cuda")
+        dropped = torch.zeros(1, dtype=torch.int32, device="cuda")
+        args = [ids.data_ptr(), routes, e_lo, e_count, max_rows, er.data_ptr(), te.data_ptr(), rr.data_ptr(), ro.data_ptr(),
+                cnt.data_ptr(), dropped.data_ptr()]
+        if name.endswith("par"):
+            scratch = moe_ops.align_scratch(routes, e_count, "cuda")
+            args.append(scratch.data_ptr())
+        _lib.call(name, *args, _lib.stream())
+        torch.cuda.synchronize()
+        plans.append([t.cpu() for t in (er, te, rr, ro, cnt, dropped)])
+    for a, b in zip(*plans):
+        assert torch.equal(a, b)
+    assert (int(plans[0][5]) > 0) == drops                 # the small buffers really dropped routes, the last case none
