@@ -97,6 +97,7 @@ class EpComm:
             self._ptrs.append({"pub": _ptr_array([b + off for b in bases]),
                                "inbox": _ptr_array([b + off + self.row_bytes for b in bases]),
                                "ids": _ptr_array([b + off + 2 * self.row_bytes for b in bases])})
+        self._route_index = torch.arange(self.cap_routes, dtype=torch.int32, device=device)    # see _identity
         self._dropped = torch.zeros(1, dtype=torch.int32, device=device)
         self._dropped_total = torch.zeros(1, dtype=torch.int64, device=device)
         self.calls = 0
@@ -170,15 +171,17 @@ class EpComm:
         self.heap.close()
 
 
-def _identity(routes: int, device) -> torch.Tensor:
+def _identity(routes: int, device, comm=None) -> torch.Tensor:
     """Route map in which route (t, j) lives in row t * k + j: lets the local combine kernels run on an inbox."""
+    if comm is not None and routes <= comm.cap_routes:
+        return comm._route_index[:routes]
     return torch.arange(routes, dtype=torch.int32, device=device)
 
 
-def _weighted_sum(rows: torch.Tensor, weights: torch.Tensor | None, tokens: int, k: int) -> torch.Tensor:
+def _weighted_sum(rows: torch.Tensor, weights: torch.Tensor | None, tokens: int, k: int, comm=None) -> torch.Tensor:
     """``out[t] = sum_j weights[t, j] * rows[t * k + j]`` (plain sum without weights)."""
     out = torch.empty((tokens, rows.shape[1]), dtype=rows.dtype, device=rows.device)
-    _lib.call("areno_moe_combine", rows.data_ptr(), _identity(tokens * k, rows.device).data_ptr(), _lib.ptr(weights),
+    _lib.call("areno_moe_combine", rows.data_ptr(), _identity(tokens * k, rows.device, comm).data_ptr(), _lib.ptr(weights),
               tokens, k, rows.shape[1], out.data_ptr(), _lib.stream())
     return out
 
@@ -202,7 +205,7 @@ class _Dispatch(torch.autograd.Function):
         comm._push(slot, plan, d_rows)               # gradient of a pull is a push to the rows' owners
         comm.barrier()
         t, k = plan.tokens, plan.k
-        dx = _weighted_sum(comm._inbox[slot][: t * k], None, t, k)      # sum over the k routes of a token
+        dx = _weighted_sum(comm._inbox[slot][: t * k], None, t, k, comm)      # sum over the k routes of a token
         return dx, None, None, None
 
 
@@ -214,7 +217,7 @@ class _Combine(torch.autograd.Function):
         t, k = plan.tokens, plan.k
         inbox = comm._inbox[plan.slot][: t * k]
         weights = weights.float().contiguous()
-        out = _weighted_sum(inbox, weights, t, k)
+        out = _weighted_sum(inbox, weights, t, k, comm)
         if ctx.needs_input_grad[0] or ctx.needs_input_grad[1]:
             ctx.save_for_backward(inbox.clone(), weights)   # the slot is reused two calls later
         ctx.comm, ctx.plan = comm, plan
@@ -228,7 +231,7 @@ class _Combine(torch.autograd.Function):
         d_rows_local = torch.empty_like(rows_in)
         dweights = torch.empty((t, k), dtype=torch.float32, device=dout.device)
         _lib.call("areno_moe_combine_bwd", dout.contiguous().data_ptr(), rows_in.data_ptr(),
-                  _identity(t * k, dout.device).data_ptr(), weights.data_ptr(), k, t * k, t * k, rows_in.shape[1],
+                  _identity(t * k, dout.device, comm).data_ptr(), weights.data_ptr(), k, t * k, t * k, rows_in.shape[1],
                   d_rows_local.data_ptr(), dweights.data_ptr(), _lib.stream())
         slot = comm._next_slot()
         comm._pub[slot][: t * k].copy_(d_rows_local)         # one row per route, for the expert owners to pull

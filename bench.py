@@ -449,8 +449,11 @@ def run_e2e(args, worker, mcfg, params, rank, world, device, n_prompts, pmin, pm
     t0 = time.time()
     tokens = 0
     stats = {}
+    per_step = []
     for i in range(steps):
+        t_s = time.time()
         n, stats = step(i)
+        per_step.append(round(time.time() - t_s, 3))
         tokens += n
     torch.cuda.synchronize()
     if world > 1:
@@ -464,7 +467,7 @@ def run_e2e(args, worker, mcfg, params, rank, world, device, n_prompts, pmin, pm
             "h2d_bytes_per_step": counters["h2d"] // steps, "d2h_bytes_per_step": counters["d2h"] // steps,
             "timing": "wall clock around Trainer.rollout_token_batch + Trainer.train, max over ranks",
             "step_rollout_time_s": stats.get("step_rollout_time_s"), "step_train_time_s": stats.get("step_train_time_s"),
-            "wall_s_per_step_rank0": {k: round(v / steps, 3) for k, v in wall.items()},
+            "wall_s_per_step_rank0": {k: round(v / steps, 3) for k, v in wall.items()}, "step_wall_s_rank0": per_step,
             "loss": stats.get("loss")}
 
 
