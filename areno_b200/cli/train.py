@@ -1,7 +1,7 @@
 """``areno train``: option surface, validation, hook pre-flight, config build and the run loop.
 
 The 62 options, their defaults and their five help groups (Basic / Rollout / Train / Checkpoint /
-Observability) are those of the reference CLI (``areno/cli/train.py:46-128,942-1093``); ``--kv-dtype``
+Observability) are those of the reference CLI (``areno/cli/train.py:46-128,942-1093``); ``--kv-dtype`` and ``--expert-parallel``
 is an addition (fp8 KV pages).  User hook files (``--dataset-loader-fn``, ``--reward-fn-path``,
 ``--agent-fn``) are checked by parsing their AST before any model is loaded; they are never executed
 during validation.
@@ -51,6 +51,8 @@ OPTIONS = [
     ("--eager-decode", dict(is_flag=True, default=False, help="Disable CUDA-graph decode."), "Rollout"),
     ("--attn-backend", dict(default="flash", show_default=True, type=click.Choice(["flash", "native"])), "Rollout"),
     ("--kv-dtype", dict(default="bf16", show_default=True, type=click.Choice(["bf16", "fp8"])), "Rollout"),
+    ("--expert-parallel", dict(is_flag=True, default=False,
+                               help="Mixture-of-experts models: deal the experts out over the GPUs (needs --tp-size 1)."), "Rollout"),
     ("--disable-thinking", dict(is_flag=True, default=False), "Rollout"),
     ("--agent-fn", dict(default=None, help="Python file defining run_agent(ctx, batch)."), "Rollout"),
     ("--agent-timeout-s", dict(default=300.0, show_default=True, type=float), "Rollout"),
@@ -317,6 +319,7 @@ def summary_sections(config, *, reward_ckpt: str | None = None) -> list[tuple[st
         ("Runtime", [("world_size", str(config.world_size)), ("tp_size", str(config.tp_size)),
                      ("dp_size", str(config.world_size // config.tp_size) if config.tp_size else "n/a"),
                      ("attn_backend", config.attn_backend), ("kv_dtype", config.kv_dtype),
+                     ("expert_parallel", _yn(config.expert_parallel)),
                      ("decode", "eager" if config.eager_decode else "cuda-graph"),
                      ("keep_rollout_state", _yn(config.keep_rollout_state)),
                      ("activation_checkpointing", _yn(config.activation_checkpointing)),

@@ -30,7 +30,7 @@ def _base(tmp_path, **kw):
 
 def test_option_surface_and_defaults():
     names = [cli_train.option_name(f) for f, _kw, _g in cli_train.OPTIONS]
-    assert len(names) == len(set(names)) == 63  # 62 reference options + kv-dtype
+    assert len(names) == len(set(names)) == 64  # 62 reference options + kv-dtype + expert-parallel
     d = cli_train._defaults()
     assert (d["algo"], d["tp_size"], d["world_size"], d["batch_size"], d["n_samples"]) == ("gspo", 4, 8, 32, 8)
     assert (d["max_prompt_tokens"], d["max_new_tokens"], d["mini_bs"], d["score_micro_bs"]) == (1024, 3071, 16, 8)
@@ -62,7 +62,11 @@ def test_config_class_per_algorithm(tmp_path):
                                                         dataset_loader_fn=str(loader)))
     assert type(cfg) is TrainerConfig and not hasattr(cfg, "reward_fn_path")
     ac = cfg.areno_config()
-    assert ac.tp_size == 4 and ac.optimizer["lr"] == 1e-6 and ac.runtime["kv_dtype"] == "bf16"
+    assert ac.tp_size == 4 and ac.optimizer["lr"] == 1e-6 and ac.runtime["kv_dtype"] == "bf16" and not ac.expert_parallel
+    cfg = cli_train.trainer_config_from_options(**_base(tmp_path, algo="grpo", tp_size=1, expert_parallel=True))
+    assert cfg.expert_parallel and cfg.areno_config().expert_parallel
+    with pytest.raises(ValueError, match="tp_size must be 1"):
+        cli_train.trainer_config_from_options(**_base(tmp_path, algo="grpo", tp_size=2, expert_parallel=True))
 
 
 @pytest.mark.parametrize("override,needle", [
