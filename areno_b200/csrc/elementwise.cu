@@ -351,6 +351,31 @@ gated_act_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restr
   }
 }
 
+// The same activation for an expert-sorted row buffer at inference: rows without a route (padding up to whole
+// tiles; a decode step of 256 routes over 128 experts is 98 % padding) are neither read nor written.  Their
+// content only ever reaches output rows that nobody gathers.
+__global__ void __launch_bounds__(256)
+gated_act_fwd_rows_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out,
+                          const int* __restrict__ row_route, long long rows, int I, int kind) {
+  pdl_trigger();
+  pdl_wait();
+  const int nvec = I >> 3;
+  const int lane = threadIdx.x & 31;
+  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long r = warp; r < rows; r += nwarps) {
+    if (row_route[r] < 0) continue;
+    for (int v = lane; v < nvec; v += 32) {
+      float g[8], u[8], o[8];
+      load8(x + r * 2 * I + v * 8, g);
+      load8(x + r * 2 * I + I + v * 8, u);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = act_fwd(g[j], kind) * u[j];
+      store8(out + r * I + v * 8, o);
+    }
+  }
+}
+
 __global__ void __launch_bounds__(256)
 gated_act_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ x,
                      __nv_bfloat16* __restrict__ dx, long long rows, int I, int kind) {
@@ -606,6 +631,14 @@ extern "C" int areno_gated_act_fwd(const void* x, void* out, long long rows, int
   if (I % 8 != 0) return -3;
   return (int)launch_pdl(gated_act_fwd_kernel, dim3(grid_for(rows * (I / 8), 256)), dim3(256), 0, stream,
                          (const __nv_bfloat16*)x, (__nv_bfloat16*)out, rows, I, kind);
+}
+
+extern "C" int areno_gated_act_fwd_rows(const void* x, void* out, const int* row_route, long long rows, int I, int kind,
+                                        cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (I % 8 != 0 || row_route == nullptr) return -3;
+  return (int)launch_pdl(gated_act_fwd_rows_kernel, dim3(grid_for(rows * 32, 256, 148 * 8)), dim3(256), 0, stream,
+                         (const __nv_bfloat16*)x, (__nv_bfloat16*)out, row_route, rows, I, kind);
 }
 
 extern "C" int areno_gated_act_bwd(const void* dout, const void* x, void* dx, long long rows, int I, int kind,

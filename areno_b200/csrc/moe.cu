@@ -345,7 +345,39 @@ moe_align_scan_kernel(int routes, int e_count, int max_rows, int* __restrict__ c
     tot[e] = c;
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
+  // Segment layout.  Common case (at most 1024 experts, everything fits): an exclusive scan of the padded sizes,
+  // every thread writes its own expert.  Otherwise thread 0 walks the experts and applies the capacity.
+  __shared__ int scan[1024];
+  __shared__ int sh_fits;
+  bool laid_out = false;
+  if (e_count <= 1024) {
+    const int e = threadIdx.x;
+    const int padded = e < e_count ? (tot[e] + kMoeTile - 1) / kMoeTile * kMoeTile : 0;
+    scan[e] = padded;
+    __syncthreads();
+    for (int d = 1; d < 1024; d <<= 1) {
+      const int v = e >= d ? scan[e - d] : 0;
+      __syncthreads();
+      scan[e] += v;
+      __syncthreads();
+    }
+    if (e == 0) sh_fits = scan[1023] <= max_rows;
+    __syncthreads();
+    if (sh_fits) {
+      laid_out = true;
+      if (e < e_count) {
+        const int o = scan[e] - padded;
+        off[e] = o;
+        limit[e] = o + tot[e];
+        expert_rows[2 * e] = o;
+        expert_rows[2 * e + 1] = padded;
+        if (counts_out != nullptr) counts_out[e] = tot[e];
+        for (int tile = o / kMoeTile; tile < (o + padded) / kMoeTile; ++tile) tile_expert[tile] = e;
+      }
+      if (e == 0 && dropped_out != nullptr) *dropped_out = 0;
+    }
+  }
+  if (!laid_out && threadIdx.x == 0) {
     int o = 0, dropped = 0;
     for (int e = 0; e < e_count; ++e) {
       int padded = (tot[e] + kMoeTile - 1) / kMoeTile * kMoeTile;
@@ -420,6 +452,62 @@ moe_permute_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ 
     uint4 val = make_uint4(0, 0, 0, 0);
     if (route >= 0) val = *reinterpret_cast<const uint4*>(x + (size_t)(route / k) * H + v * 8);
     *reinterpret_cast<uint4*>(xs + (size_t)row * H + v * 8) = val;
+  }
+}
+
+// Inference variant: one warp per row, padding rows are left untouched (a GEMM row only feeds its own output row,
+// and nobody gathers the output of a padding row), so a decode step copies its few hundred real rows instead
+// of zero-filling a tile per expert.
+__global__ void __launch_bounds__(256)
+moe_permute_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ row_route, int k, int max_rows,
+                        int H, __nv_bfloat16* __restrict__ xs) {
+  const int nvec = H >> 3;
+  const int lane = threadIdx.x & 31;
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = (gridDim.x * blockDim.x) >> 5;
+  for (int row = warp; row < max_rows; row += nwarps) {
+    const int route = row_route[row];
+    if (route < 0) continue;
+    const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(route / k) * H);
+    uint4* dst = reinterpret_cast<uint4*>(xs + (size_t)row * H);
+    for (int v = lane; v < nvec; v += 32) dst[v] = src[v];
+  }
+}
+
+// Router logits for a handful of tokens: logits[t, e] = sum_h x[t, h] * w[e, h] with fp32 weights and fp32
+// accumulation.  One CTA per (token, block of 16 experts) keeps the token in shared memory as fp32; every warp
+// takes two experts and keeps four 16-byte loads of the weight row in flight.  Replaces a cast kernel + a library
+// SGEMM + its split-K reduction (30 us for 32 tokens x 128 experts) in the decode step.
+constexpr int kRouterExpertsPerCta = 16;
+__global__ void __launch_bounds__(256)
+router_logits_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w, float* __restrict__ logits, int H,
+                     int E) {
+  extern __shared__ float sx[];
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) sx[i] = __bfloat162float(x[(size_t)t * H + i]);
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const float4* s4 = reinterpret_cast<const float4*>(sx);
+  const int n4 = H >> 2;
+  for (int e = blockIdx.y * kRouterExpertsPerCta + warp; e < min(E, (int)(blockIdx.y + 1) * kRouterExpertsPerCta);
+       e += blockDim.x >> 5) {
+    const float4* w4 = reinterpret_cast<const float4*>(w + (size_t)e * H);
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int i0 = lane; i0 < n4; i0 += 128) {
+      float4 b[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) b[u] = i0 + u * 32 < n4 ? __ldg(w4 + i0 + u * 32) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (i0 + u * 32 < n4) {
+          const float4 a = s4[i0 + u * 32];
+          acc[u] += a.x * b[u].x + a.y * b[u].y + a.z * b[u].z + a.w * b[u].w;
+        }
+      }
+    }
+    float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane == 0) logits[(size_t)t * E + e] = sum;
   }
 }
 
@@ -606,6 +694,32 @@ extern "C" int areno_moe_permute(const void* x, const int* row_route, int k, lon
   if (H % 8 != 0) return -3;
   moe_permute_kernel<<<grid_1d(max_rows * (H / 8), 256), 256, 0, stream>>>((const __nv_bfloat16*)x, row_route, k,
                                                                             (int)max_rows, H, (__nv_bfloat16*)xs);
+  return (int)cudaGetLastError();
+}
+
+// Inference: copy only the rows that have a route (see moe_permute_rows_kernel).
+extern "C" int areno_moe_permute_rows(const void* x, const int* row_route, int k, long long max_rows, int H, void* xs,
+                                      cudaStream_t stream) {
+  if (max_rows <= 0) return 0;
+  if (H % 8 != 0) return -3;
+  moe_permute_rows_kernel<<<grid_1d(max_rows * 32, 256), 256, 0, stream>>>((const __nv_bfloat16*)x, row_route, k,
+                                                                           (int)max_rows, H, (__nv_bfloat16*)xs);
+  return (int)cudaGetLastError();
+}
+
+// x: bf16 [tokens, H]; w: fp32 [E, H]; logits: fp32 [tokens, E].  For a few hundred tokens at most.
+extern "C" int areno_router_logits(const void* x, const float* w, float* logits, long long tokens, int H, int E,
+                                   cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (H % 4 != 0 || H > 12288 || E < 1 || (reinterpret_cast<uintptr_t>(w) & 15)) return -3;
+  static bool cfg_dev[kMaxDevices] = {};
+  bool& cfg = per_device_flag(cfg_dev);
+  if (!cfg) {
+    cudaFuncSetAttribute(router_logits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 12288 * 4);
+    cfg = true;
+  }
+  const dim3 grid((unsigned)tokens, (unsigned)((E + kRouterExpertsPerCta - 1) / kRouterExpertsPerCta));
+  router_logits_kernel<<<grid, 256, H * sizeof(float), stream>>>((const __nv_bfloat16*)x, w, logits, H, E);
   return (int)cudaGetLastError();
 }
 

@@ -33,8 +33,7 @@ class TopKRouter(nn.Module):
         self.weight.tp_replicated_grad = True
 
     def forward(self, x):
-        logits = torch.nn.functional.linear(x.float(), self.weight)
-        return moe_ops.topk_softmax(logits, self.k, self.renorm)
+        return moe_ops.topk_softmax(moe_ops.router_logits(x, self.weight), self.k, self.renorm)
 
 
 class Experts(nn.Module):
@@ -72,7 +71,8 @@ class Experts(nn.Module):
         comm = get_context().ep_runtime.comm(x.shape[0])
         rows, plan = comm.dispatch(x, ids)
         gu = moe_ops.grouped_linear(rows, self.gate_up, plan.moe)
-        a = activation.silu_and_mul(gu) if self.act == "silu" else activation.gelu_tanh_and_mul(gu)
+        act = activation.silu_and_mul if self.act == "silu" else activation.gelu_tanh_and_mul
+        a = act(gu, plan.moe.row_route)
         ys = moe_ops.grouped_linear(a, self.down, plan.moe)
         return comm.combine(ys, weights, plan), plan.moe
 
@@ -82,7 +82,8 @@ class Experts(nn.Module):
         plan = moe_ops.align(ids, self.e_lo, self.e_local)
         xs = moe_ops.permute(x, plan)
         gu = moe_ops.grouped_linear(xs, self.gate_up, plan)
-        a = activation.silu_and_mul(gu) if self.act == "silu" else activation.gelu_tanh_and_mul(gu)
+        act = activation.silu_and_mul if self.act == "silu" else activation.gelu_tanh_and_mul
+        a = act(gu, plan.row_route)
         ys = moe_ops.grouped_linear(a, self.down, plan)
         out = moe_ops.combine(ys, plan, weights)
         return coll.reduce_from_tp(out), plan

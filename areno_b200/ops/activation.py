@@ -47,17 +47,35 @@ class _GatedAct(torch.autograd.Function):
         return dx.view(ctx.shape), None
 
 
-def silu_and_mul(x):
-    """``silu(x[..., :I]) * x[..., I:]``."""
+_lib.register_signature("areno_gated_act_fwd_rows", "ppplii" + "p")
+
+
+def _gated_rows(x, kind: int, row_route):
+    """Inference on an expert-sorted buffer: only rows with a route are computed, the rest stays unspecified."""
+    I = x.shape[-1] // 2
+    x2 = x.contiguous()
+    out = torch.empty((x2.shape[0], I), dtype=x.dtype, device=x.device)
+    _lib.call("areno_gated_act_fwd_rows", x2.data_ptr(), out.data_ptr(), row_route.data_ptr(), x2.shape[0], I, kind,
+              _lib.stream())
+    return out
+
+
+def silu_and_mul(x, row_route=None):
+    """``silu(x[..., :I]) * x[..., I:]``.  ``row_route`` (int32 per row, negative = padding) restricts the work to
+    the routed rows of an expert-sorted buffer; only honoured when no gradient is needed."""
     if not x.is_cuda:
         return gated_act_reference(x, "silu")
+    if row_route is not None and x.dim() == 2 and not torch.is_grad_enabled():
+        return _gated_rows(x, 0, row_route)
     return _GatedAct.apply(x, 0)
 
 
-def gelu_tanh_and_mul(x):
-    """``gelu_tanh(x[..., :I]) * x[..., I:]``."""
+def gelu_tanh_and_mul(x, row_route=None):
+    """``gelu_tanh(x[..., :I]) * x[..., I:]`` (``row_route``: see ``silu_and_mul``)."""
     if not x.is_cuda:
         return gated_act_reference(x, "gelu_tanh")
+    if row_route is not None and x.dim() == 2 and not torch.is_grad_enabled():
+        return _gated_rows(x, 1, row_route)
     return _GatedAct.apply(x, 1)
 
 

@@ -25,8 +25,9 @@ _lib.register_signature("areno_grouped_sigmoid_topk", "ppliiiiifppp")
 _lib.register_signature("areno_moe_align", "pliilpppppp")
 _lib.register_signature("areno_moe_align_par", "pliilpppppppp")
 # from this many routes on the plan is built by the three-launch kernels (one warp per 512 routes) instead of the
-# single-CTA kernel, whose time grows with routes x experts
-PAR_ALIGN_MIN_ROUTES = 4096
+# single-CTA kernel, whose time grows with routes x experts (a decode step of 64 sequences x 8 routes over 128
+# experts already spends tens of microseconds there)
+PAR_ALIGN_MIN_ROUTES = 128
 
 
 def align_scratch(routes: int, e_count: int, device) -> torch.Tensor:
@@ -209,11 +210,45 @@ class _Permute(torch.autograd.Function):
         return dx, None
 
 
+_lib.register_signature("areno_moe_permute_rows", "ppilipp")
+_lib.register_signature("areno_router_logits", "ppplii" + "p")
+# inference: the largest token count for which the router's logits come from the small fp32 kernel
+ROUTER_KERNEL_MAX_TOKENS = 256
+
+
+def inference_rows_only(*tensors) -> bool:
+    """True when no gradient will flow through the MoE ops of this call: padding rows of the expert-sorted buffers
+    may then stay uninitialised (a GEMM row only feeds its own output row and nobody gathers a padding row), which
+    turns the per-layer work of a decode step from one tile per expert into the routed rows themselves."""
+    del tensors      # decided by the autograd mode alone: any grad-enabled pass (training, recompute) fills the padding
+    return not torch.is_grad_enabled()
+
+
 def permute(x: torch.Tensor, plan: MoePlan) -> torch.Tensor:
-    """``[T, H] -> [max_rows, H]`` in expert-sorted order (padding rows are zero)."""
+    """``[T, H] -> [max_rows, H]`` in expert-sorted order (padding rows are zero; unspecified at inference)."""
     if not x.is_cuda:
         return _gather_rows_reference(x, plan)
+    if inference_rows_only(x):
+        x = x.contiguous()
+        xs = torch.empty((plan.max_rows, x.shape[1]), dtype=x.dtype, device=x.device)
+        _lib.call("areno_moe_permute_rows", x.data_ptr(), plan.row_route.data_ptr(), plan.k, plan.max_rows, x.shape[1],
+                  xs.data_ptr(), _lib.stream())
+        return xs
     return _Permute.apply(x.contiguous(), plan)
+
+
+def router_logits(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """``x @ weight^T`` in fp32 (``weight`` fp32 ``[E, H]``).  A few tokens without gradient take a small kernel
+    of this library instead of a cast + library SGEMM."""
+    if (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.float32 and x.dim() == 2
+            and 0 < x.shape[0] <= ROUTER_KERNEL_MAX_TOKENS and x.shape[1] % 4 == 0 and x.shape[1] <= 12288
+            and inference_rows_only(x, weight)):
+        x = x.contiguous()
+        out = torch.empty((x.shape[0], weight.shape[0]), dtype=torch.float32, device=x.device)
+        _lib.call("areno_router_logits", x.data_ptr(), weight.data_ptr(), out.data_ptr(), x.shape[0], x.shape[1],
+                  weight.shape[0], _lib.stream())
+        return out
+    return torch.nn.functional.linear(x.float(), weight)
 
 
 class _Combine(torch.autograd.Function):

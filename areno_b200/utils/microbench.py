@@ -303,6 +303,40 @@ def case_train_microbatch(layers: int = 4, lens=(1536, 1408, 1152)):
     return run, flops, 0.0, f"{t} tokens in {len(lens)} sequences, {layers} layers of the 7B shape + LM head, forward + backward"
 
 
+def case_decode_step_moe(batch: int = 32, ctx: int = 1024, layers: int = 4):
+    """One decode step of ``layers`` layers of the Qwen3-30B-A3B shape (128 experts, top 8, all experts on this
+    GPU) replayed from its CUDA graph: the kernel sequence of a mixture-of-experts decode step without the
+    expert-parallel exchange."""
+    from ..engine.config import ModelConfig
+    from ..engine.inference import InferenceEngine, SamplingParams
+    from ..models.dense import init_weights
+    from ..models.moe import MoeCausalLM
+    from ..parallel.context import single_process_context
+
+    dev = torch.device("cuda", 0)
+    single_process_context(dev)
+    cfg = ModelConfig(model_type="qwen3_moe", vocab_size=151936, hidden_size=2048, intermediate_size=6144,
+                      num_hidden_layers=layers, num_attention_heads=32, num_key_value_heads=4, head_dim=128, qkv_bias=False,
+                      qk_norm=True, tie_word_embeddings=False, rope_theta=1e6, num_experts=128, num_experts_per_tok=8,
+                      moe_intermediate_size=768, norm_topk_prob=True)
+    model = MoeCausalLM(cfg, device=dev)
+    init_weights(model, 0)
+    eng = InferenceEngine(model, cfg.vocab_size, dev, max_slots=batch, max_model_len=ctx + 512)
+    eng.begin(SamplingParams(temperature=1.0), (), 16)
+    with torch.no_grad():
+        eng.active[:batch] = 1
+        eng.seq_len[:batch] = ctx
+        eng.max_new[:batch] = 4096
+        eng.block_table.copy_(torch.arange(batch * eng.max_pages, dtype=torch.int32, device=dev).view(batch, eng.max_pages))
+    weights = sum(p.numel() * p.element_size() for n, p in model.named_parameters() if not n.startswith("embed"))
+
+    def run():
+        with torch.no_grad():
+            eng._decode(batch, eng._context_bucket(ctx + 1))
+
+    return run, 0.0, float(weights), f"B={batch} ctx={ctx}, {layers} MoE layers (128 experts local) + LM head, graph replay"
+
+
 def _lightning_inputs(seqs=16, length=1024, h=16, d=128):
     t = seqs * length
     wide = _bf16(t, 3 * h * d, scale=0.5)
@@ -399,7 +433,7 @@ def _tp_local_gemm(m, n, k):
 
 CASES = {
     "decode_step": case_decode_step,
-    "train_microbatch": case_train_microbatch,
+    "train_microbatch": case_train_microbatch, "decode_step_moe": case_decode_step_moe,
     "lm_head_lse": case_lm_head_lse, "lm_head_unfused": lambda: case_lm_head_lse(False),
     # per-rank GEMM shapes of a tensor-parallel decode step of the 7B model: tp 4 with 256 pooled rows, tp 8 with 512
     "tp4_gate_up": lambda: _tp_local_gemm(256, 9472, 3584), "tp4_down": lambda: _tp_local_gemm(256, 3584, 4736),

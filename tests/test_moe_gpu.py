@@ -52,7 +52,7 @@ def _plan_equal(a, b):
 
 
 @pytest.mark.parametrize("tokens,E,k,e_lo,e_count", [(1000, 128, 8, 0, 128), (1000, 128, 8, 32, 16), (5, 8, 2, 0, 8),
-                                                     (4096, 128, 8, 0, 128)])
+                                                     (4096, 128, 8, 0, 128), (64, 128, 8, 0, 128), (65, 128, 8, 112, 16)])
 def test_align_matches_reference(tokens, E, k, e_lo, e_count):
     torch.manual_seed(2)
     ids = torch.stack([torch.randperm(E)[:k] for _ in range(tokens)]).to(torch.int32).cuda()
@@ -173,3 +173,33 @@ def test_three_launch_align_matches_the_single_cta_kernel_with_capacity(routes, 
     for a, b in zip(*plans):
         assert torch.equal(a, b)
     assert (int(plans[0][5]) > 0) == drops                 # the small buffers really dropped routes, the last case none
+
+
+def test_inference_fast_paths_match_the_training_path():
+    """Without gradients the MoE layer copies and activates only the routed rows and takes its router logits from
+    the small fp32 kernel; the layer output must equal the grad-enabled path (which fills the padding rows)."""
+    from areno_b200.ops import activation
+
+    torch.manual_seed(9)
+    t, E, k, H, inter = 48, 32, 4, 512, 256
+    x = torch.randn(t, H, device="cuda").to(torch.bfloat16)
+    gate = torch.randn(E, H, device="cuda") * 0.1
+    w1 = (torch.randn(E, 2 * inter, H, device="cuda") * 0.03).to(torch.bfloat16)
+    w2 = (torch.randn(E, H, inter, device="cuda") * 0.03).to(torch.bfloat16)
+
+    def layer():
+        logits = moe_ops.router_logits(x, gate)
+        wts, ids = moe_ops.topk_softmax(logits, k, True)
+        plan = moe_ops.align(ids, 0, E)
+        xs = moe_ops.permute(x, plan)
+        a = activation.silu_and_mul(moe_ops.grouped_linear(xs, w1, plan), plan.row_route)
+        return logits, moe_ops.combine(moe_ops.grouped_linear(a, w2, plan), plan, wts)
+
+    with torch.enable_grad():
+        ref_logits, ref = layer()
+    with torch.no_grad():
+        logits, out = layer()
+    torch.cuda.synchronize()
+    assert torch.allclose(logits, ref_logits, atol=2e-4, rtol=1e-4)
+    assert torch.allclose(logits, x.float() @ gate.t(), atol=2e-4, rtol=1e-4)
+    assert torch.isfinite(out).all() and _rel(out, ref) < 1e-3
