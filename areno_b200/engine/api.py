@@ -135,6 +135,9 @@ class ArenoEngine:
         joins that worker's running batch; only that row's TP-rank-0 result is awaited."""
         if not prompts:
             raise ValueError("prompts must be non-empty")
+        if self.config.expert_parallel:
+            raise RuntimeError("request-concurrent rollout sends a request to one data-parallel row; with expert "
+                               "parallelism every rank takes part in every forward pass: use generate_rollout")
         dp, tp = int(self.config.rollout_dp), int(self.config.rollout_tp)
         owner = next(self._dp_cursor) % dp
         prompts_by_dp = [[] for _ in range(dp)]

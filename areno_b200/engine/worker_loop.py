@@ -73,8 +73,9 @@ def _local_rows(p: RolloutPayload, worker=None):
 
 def _rollout_blocking(worker, p: RolloutPayload) -> RolloutOutput:
     prompts, indices = _local_rows(p, worker)
-    if not prompts:
+    if not prompts and worker.rollout_ctx.ep_size == 1:
         return RolloutOutput(prompt_indices=[])
+    # expert parallel: a rank without prompts still joins every forward pass of the others (idle passes)
     out = worker.rollout(prompts, p.sampling_params, p.eos_token_ids, p.max_new_tokens, max_running=p.max_running_seqs,
                          progress_interval_s=p.decode_progress_interval_s)
     out.prompt_indices = list(indices)
@@ -101,7 +102,10 @@ class WorkerLoop:
                 self.put_result(WorkerResult(self.rank, cmd.request_id, True, None))
                 return
             try:
-                if cmd.op == Op.INFER_ROLLOUT and self.worker.rollout_ctx.tp_size == 1:
+                rctx = self.worker.rollout_ctx
+                # request-concurrent batching needs engines that may step on their own: not with tensor-parallel
+                # rollout nor with expert parallelism, whose ranks exchange tokens in every forward pass
+                if cmd.op == Op.INFER_ROLLOUT and rctx.tp_size == 1 and rctx.ep_size == 1:
                     self._continuous_rollout(cmd)
                 else:
                     self.put_result(WorkerResult(self.rank, cmd.request_id, True, execute(self.worker, cmd)))

@@ -150,12 +150,14 @@ class MoeCausalLM(DenseCausalLM):
         the exchange; attention and the dense parts have nothing to do.  One zero token with zero routing weights
         stands in for the batch."""
         cfg = self.cfg
-        dev = self.embed_tokens.weight.device
         k = cfg.num_experts_per_tok
-        x = torch.zeros((1, cfg.hidden_size), dtype=self.embed_tokens.weight.dtype, device=dev)
-        w = torch.zeros((1, k), dtype=torch.float32, device=dev)
-        ids = torch.arange(k, dtype=torch.int32, device=dev).unsqueeze(0)
+        x = w = ids = None
         for layer in self.layers:
             mlp = getattr(layer, "mlp", None)
             if isinstance(mlp, SparseMoeBlock) and mlp.experts.ep:
+                if x is None:
+                    ref = mlp.experts.gate_up
+                    x = torch.zeros((1, cfg.hidden_size), dtype=ref.dtype, device=ref.device)
+                    w = torch.zeros((1, k), dtype=torch.float32, device=ref.device)
+                    ids = torch.arange(k, dtype=torch.int32, device=ref.device).unsqueeze(0)
                 mlp.experts(x, w, ids)

@@ -88,8 +88,13 @@ def _rank_main(rank, world, port, ckpt_dir, ret):
         before = _named(worker)
         stats = worker.train(packs)
         after = _named(worker)
-        scored = worker.role_manager().score_logprobs("actor", [p + t for p, t in zip(mine, first.tokens)], 0, 1)
+        rm = worker.role_manager()
+        rm.score_token_budget = 40           # rank 0 scores in more micro-batches than rank 1: idle rounds on rank 1
+        scored = rm.score_logprobs("actor", [p + t for p, t in zip(mine, first.tokens)], 0, 1)
         second = worker.rollout(mine, params, (), 6)
+        # a rank without any prompt still takes part in the others' forward passes
+        lonely = worker.rollout(mine[:1] if rank == 0 else [], params, (), 4)
+        assert len(lonely.tokens) == (1 if rank == 0 else 0)
         worker.save_checkpoint(ckpt_dir)
         ret[rank] = dict(first=first.tokens, first_lp=first.logprobs, second=second.tokens, before=before, after=after,
                          loss=[s["loss"] for s in stats], scored=scored,

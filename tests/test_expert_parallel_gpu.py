@@ -70,6 +70,9 @@ def _rank_main(rank, world, port, impl, ret):
         rows = _rows(rank)
         scored = worker.role_manager().score_logprobs("actor", rows, 0, 1)
         out = worker.rollout([r[:20] for r in rows], SamplingParams(temperature=1.0, seed=9), (), 12)
+        # a rank without prompts joins the other rank's prefill with an idle pass and its decode steps with no slot active
+        lonely = worker.rollout([rows[0][:16]] if rank == 0 else [], SamplingParams(temperature=1.0, seed=3), (), 5)
+        assert [len(t) for t in lonely.tokens] == ([5] if rank == 0 else [])
         graphs = len(worker.infer._graphs)                  # building the trainer re-points the weights and drops them
         stats = worker.train(_packs(rank, world, rows))
         scored2 = worker.role_manager().score_logprobs("actor", rows, 0, 1)
