@@ -206,6 +206,9 @@ class RankWorker:
         if opt is not None and getattr(opt, "grad_comm", None) is not None:
             opt.grad_comm.close()
             opt.grad_comm = None
+        ctx = get_context()
+        if ctx.ep_runtime is not None:
+            ctx.ep_runtime.close()       # expert-parallel heaps (the peers have them mapped)
 
     def role_manager(self):
         if self.roles is None:
