@@ -236,8 +236,13 @@ class NativeBackend(Backend):
         out = self._require().generate_rollout(
             flat, max_new_tokens=sampling_params.max_new_tokens, max_running_prompts=opts["max_running_prompts"],
             max_prompt_len=opts["max_prompt_len"], eos_token_id=opts["eos_token_id"],
-            sampling_params=opts["sampling_params"], decode_progress_interval_s=opts["decode_progress_interval_s"])
+            sampling_params=opts["sampling_params"], decode_progress_interval_s=opts["decode_progress_interval_s"],
+            local=self._local_data(ctx))
         return self._to_results(out, len(prompt_tokens), n_samples)
+
+    @staticmethod
+    def _local_data(ctx) -> bool:
+        return bool(getattr(ctx.custom_config, "spmd_local_data", False))
 
     async def rollout_batch_async(self, ctx, prompt_tokens, n_samples, sampling_params) -> list[RolloutResult]:
         opts = rollout_options(ctx, sampling_params)
@@ -265,7 +270,8 @@ class NativeBackend(Backend):
                 counts.append(sft_target_token_count(chunk))
         if sft:
             annotate_sft_token_mean_packs(packs, counts, gradient_accumulation_steps=gradient_accumulation_steps)
-        stats = self._require().step(packs, gradient_accumulation_steps=gradient_accumulation_steps)
+        stats = self._require().step(packs, gradient_accumulation_steps=gradient_accumulation_steps,
+                                     local=self._local_data(ctx))
         return self._reduce_stats(stats, time.perf_counter() - t0)
 
     @staticmethod

@@ -30,6 +30,10 @@ class ArenoConfig:
     # how workers are launched: "spawn" (one process per GPU), "inprocess" (single GPU, no process hop),
     # "spmd" (this process is one of WORLD_SIZE ranks started by torch.distributed.run)
     launcher: str | None = None
+    # SPMD launches only (one driver process per rank): every rank hands the Trainer its OWN share of the prompts and
+    # training sequences and gets its own results and statistics back; nothing is exchanged between the ranks on
+    # the host.  All ranks must make the same calls with the same number of micro-batches.
+    spmd_local_data: bool = False
     model_config: Any = None  # explicit ModelConfig (synthetic models without a checkpoint directory)
     seed: int = 0
 

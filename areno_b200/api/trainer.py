@@ -67,15 +67,16 @@ class Trainer:
 
     @classmethod
     def from_worker(cls, worker, world_size: int = 1, tokenizer: Any = None, eos_ids: tuple[int, ...] = (),
-                    max_running_prompts: int | None = None) -> "Trainer":
-        """Wrap an already-built rank worker (in-process for one rank, SPMD under torchrun)."""
+                    max_running_prompts: int | None = None, local_data: bool = False) -> "Trainer":
+        """Wrap an already-built rank worker (in-process for one rank, SPMD under torchrun).  ``local_data``: see
+        ``ArenoConfig.spmd_local_data``."""
         from ..engine.api import ArenoEngine
         from .backend.native import NativeBackend
         from .config import ArenoConfig
 
         cfg = ArenoConfig(tp_size=worker.config.tp_size, dp_size=worker.config.dp_size,
                           max_running_prompts=max_running_prompts or worker.config.max_running_seqs * world_size,
-                          decode_progress_interval_s=0.0)
+                          decode_progress_interval_s=0.0, spmd_local_data=bool(local_data and world_size > 1))
         self = cls(world_size, "", custom_config=cfg)
         launcher = "spmd" if world_size > 1 else "inprocess"
         self._backend = NativeBackend(ArenoEngine(worker.config, launcher=launcher, worker=worker))

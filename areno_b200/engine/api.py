@@ -111,8 +111,15 @@ class ArenoEngine:
     def generate_rollout(self, prompts: list[list[int]], *, max_new_tokens: int, max_running_prompts: int,
                          max_prompt_len: int | None = None, eos_token_id=None,
                          sampling_params: SamplingParams | None = None, decode_progress_interval_s: float = 0.0,
-                         cancel_flags: torch.Tensor | None = None) -> RolloutOutput:
-        """One completion per prompt, merged over DP ranks in input order."""
+                         cancel_flags: torch.Tensor | None = None, local: bool = False) -> RolloutOutput:
+        """One completion per prompt, merged over DP ranks in input order.  ``local`` (SPMD launches): ``prompts``
+        are this rank's own share, generated by its own data-parallel row and returned to it alone."""
+        if local:
+            return self._generate_rollout_local(prompts, max_new_tokens=max_new_tokens,
+                                                max_running_prompts=max_running_prompts, eos_token_id=eos_token_id,
+                                                sampling_params=sampling_params,
+                                                decode_progress_interval_s=decode_progress_interval_s,
+                                                cancel_flags=cancel_flags)
         if not prompts:
             raise ValueError("prompts must be non-empty")
         if max_running_prompts < 1:
@@ -125,6 +132,25 @@ class ArenoEngine:
             cancel_flags=cancel_flags)
         results = self.cluster.call(Op.INFER_ROLLOUT, payload)
         return merge_rollouts_in_input_order(dp_rank0_results(results, self.config.rollout_tp, dp), len(prompts))
+
+    def _require_spmd(self):
+        if not getattr(self.cluster, "is_spmd", False):
+            raise RuntimeError("rank-local data needs the SPMD launcher (one driver process per rank, e.g. torchrun)")
+        return self.cluster.worker
+
+    def _generate_rollout_local(self, prompts, *, max_new_tokens, max_running_prompts, eos_token_id, sampling_params,
+                                decode_progress_interval_s, cancel_flags) -> RolloutOutput:
+        worker = self._require_spmd()
+        dp, mine = int(self.config.rollout_dp), int(worker.rollout_ctx.dp_rank)
+        prompts = list(prompts)
+        by_dp = [prompts if r == mine else [] for r in range(dp)]
+        idx_by_dp = [list(range(len(prompts))) if r == mine else [] for r in range(dp)]
+        payload = self._rollout_payload(prompts or [[0]], idx_by_dp, by_dp, max_new_tokens=max_new_tokens,
+                                        max_running_prompts=max_running_prompts, eos_token_id=eos_token_id,
+                                        sampling_params=sampling_params,
+                                        decode_progress_interval_s=decode_progress_interval_s, cancel_flags=cancel_flags)
+        results = self.cluster.call(Op.INFER_ROLLOUT, payload, gather=False)
+        return merge_rollouts_in_input_order(results, len(prompts))
 
     async def generate_rollout_async(self, prompts: list[list[int]], *, max_new_tokens: int, max_running_prompts: int,
                                      max_prompt_len: int | None = None, eos_token_id=None,
@@ -161,10 +187,22 @@ class ArenoEngine:
         return max(float(r or 0.0) for r in res) if res else 0.0
 
     # ------------------------------------------------------------------- train
-    def step(self, data_packs: list[dict[str, Any]], *, gradient_accumulation_steps: int | None = None) -> list[dict]:
+    def step(self, data_packs: list[dict[str, Any]], *, gradient_accumulation_steps: int | None = None,
+             local: bool = False) -> list[dict]:
+        """``local`` (SPMD launches): ``data_packs`` hold this rank's own sequences; every rank must pass the same
+        number of packs.  The returned statistics are this rank's own."""
         if not data_packs:
             return []
         dp = int(self.config.dp_size)
+        if local:
+            worker = self._require_spmd()
+            from ..parallel.context import get_context
+
+            mine = int(get_context().dp_rank)
+            del worker
+            packs_by_dp = [[p if r == mine else None for r in range(dp)] for p in data_packs]
+            results = self.cluster.call(Op.TRAIN, TrainPayload(packs_by_dp, gradient_accumulation_steps), gather=False)
+            return [merge_train_stats([st]) for st in results[0]]
         packs_by_dp = [split_data_pack_by_dp(p, dp) for p in data_packs]
         results = self.cluster.call(Op.TRAIN, TrainPayload(packs_by_dp, gradient_accumulation_steps))
         stats = []

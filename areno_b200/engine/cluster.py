@@ -392,13 +392,21 @@ class SPMDCluster(_ClusterBase):
     def worker(self):
         return self._worker
 
-    def call(self, op, payload=None, timeout=None, result_ranks=None):
+    is_spmd = True
+
+    def call(self, op, payload=None, timeout=None, result_ranks=None, gather: bool = True):
+        """``gather=False``: return this rank's result only (rank-local data mode: nothing is exchanged on the
+        host; a failing rank raises here and the others meet it at their next collective's timeout)."""
         from .worker_loop import execute
 
         try:
             mine = WorkerResult(self.rank, 0, True, execute(self._worker, Command(op, 0, payload)))
         except BaseException:  # noqa: BLE001
             mine = WorkerResult(self.rank, 0, False, None, traceback.format_exc())
+        if not gather:
+            if not mine.ok:
+                raise WorkerError(f"worker rank {mine.rank} failed in {op}:\n{mine.error}")
+            return [mine.payload]
         if self.world_size == 1:
             results = [mine]
         else:

@@ -402,7 +402,10 @@ def run_e2e(args, worker, mcfg, params, rank, world, device, n_prompts, pmin, pm
         from areno_b200.api.rewards import compute_group_advantages
     except Exception as exc:  # SDK layer not importable: report honestly
         return {"value": None, "unit": "tokens/s", "error": f"SDK unavailable: {exc}"}
-    trainer = Trainer.from_worker(worker, world_size=world)
+    # SPMD launch: every rank drives the SDK with its own share of the job (its prompts, its sequences); the ranks
+    # meet in the collectives of the engine, not in host-side object exchanges
+    local = world > 1
+    trainer = Trainer.from_worker(worker, world_size=world, local_data=local)
     api_params = ApiParams(temperature=1.0, top_p=1.0, top_k=-1, max_new_tokens=new_tokens, ignore_eos=True)
     loss_fn = partial(grpo_loss_fn, clip_eps=0.2)
     steps = max(1, min(args.steps, 2))
@@ -411,7 +414,7 @@ def run_e2e(args, worker, mcfg, params, rank, world, device, n_prompts, pmin, pm
 
     def step(i):
         prompts = []
-        for r in range(world):
+        for r in ([rank] if local else range(world)):
             prompts.extend(make_prompts(10_000 + i, r, mcfg.vocab_size, n_prompts, pmin, pmax))
         t_a = time.time()
         with trainer.rollout_session(sampling_params=api_params):
@@ -428,12 +431,12 @@ def run_e2e(args, worker, mcfg, params, rank, world, device, n_prompts, pmin, pm
                                            advantages=[0.0] * len(p) + [adv] * n_r, reward=rew, eos_token_id=0))
                 ntok += len(p) + n_r
         t_c = time.time()
-        stats = trainer.train(batch, loss_fn, mini_bs=3 * world)
+        stats = trainer.train(batch, loss_fn, mini_bs=3 if local else 3 * world)
         t_d = time.time()
         wall["rollout_call_s"] += t_b - t_a
         wall["build_batch_s"] += t_c - t_b
         wall["train_call_s"] += t_d - t_c
-        my_share = 1.0 / world
+        my_share = 1.0 if local else 1.0 / world
         # per rank: prompt ids (int64) for prefill; ids, positions (int64), 2 float32 signals, mask, seq ids for training
         counters["h2d"] += int(my_share * (sum(len(p) for p in prompts) * GROUP * 8 + ntok * (8 + 8 + 4 + 4 + 1 + 8)))
         counters["d2h"] += int(my_share * sum(len(s.resp_tokens) for r in results for s in r.sequences) * (4 + 4)) + 4 * 16
@@ -463,9 +466,15 @@ def run_e2e(args, worker, mcfg, params, rank, world, device, n_prompts, pmin, pm
         t = torch.tensor([dt], dtype=torch.float64, device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dt = float(t[0])
+        if local:       # every rank counted its own tokens
+            n_all = torch.tensor([float(tokens)], dtype=torch.float64, device=device)
+            dist.all_reduce(n_all, op=dist.ReduceOp.SUM)
+            tokens = float(n_all[0])
     return {"value": tokens / dt, "unit": "tokens/s", "steps": steps, "ms_per_step": dt / steps * 1e3,
             "h2d_bytes_per_step": counters["h2d"] // steps, "d2h_bytes_per_step": counters["d2h"] // steps,
-            "timing": "wall clock around Trainer.rollout_token_batch + Trainer.train, max over ranks",
+            "timing": "wall clock around Trainer.rollout_token_batch + Trainer.train, max over ranks"
+                      + ("; SPMD with rank-local batches (ArenoConfig.spmd_local_data): every rank drives the SDK "
+                         "with its own prompts and sequences" if local else ""),
             "step_rollout_time_s": stats.get("step_rollout_time_s"), "step_train_time_s": stats.get("step_train_time_s"),
             "wall_s_per_step_rank0": {k: round(v / steps, 3) for k, v in wall.items()}, "step_wall_s_rank0": per_step,
             "loss": stats.get("loss")}
