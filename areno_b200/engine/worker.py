@@ -261,7 +261,8 @@ class RankWorker:
         if ctx.rank == 0:
             with open(os.path.join(folder, "state.json"), "w") as f:
                 json.dump({"global_step": mgr.global_step, "optimizer_step": state["step"], "dp_size": state["dp_size"],
-                           "tp_size": ctx.tp_size, "world_size": ctx.world_size, "adam_8bit": bool(state["adam_8bit"]),
+                           "tp_size": ctx.tp_size, "ep_size": ctx.ep_size, "world_size": ctx.world_size,
+                           "adam_8bit": bool(state["adam_8bit"]),
                            "num_buckets": len(state["buckets"])}, f, indent=2)
 
     def load_training_state(self, path: str) -> bool:
@@ -280,7 +281,7 @@ class RankWorker:
         opt = mgr.optimizer
         shard = os.path.join(folder, f"optimizer-rank{ctx.rank:05d}-of-{ctx.world_size:05d}.safetensors")
         if (meta.get("world_size") != ctx.world_size or meta.get("tp_size") != ctx.tp_size
-                or meta.get("num_buckets") != len(opt.buckets) or bool(meta.get("adam_8bit")) != bool(opt.cfg.adam_8bit)
+                or int(meta.get("ep_size", 1)) != ctx.ep_size or meta.get("num_buckets") != len(opt.buckets) or bool(meta.get("adam_8bit")) != bool(opt.cfg.adam_8bit)
                 or not os.path.isfile(shard)):
             logger.warning("training state at %s does not match this layout; starting from fresh optimizer state", folder)
             return False

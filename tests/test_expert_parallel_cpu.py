@@ -96,6 +96,28 @@ def _rank_main(rank, world, port, ckpt_dir, ret):
         lonely = worker.rollout(mine[:1] if rank == 0 else [], params, (), 4)
         assert len(lonely.tokens) == (1 if rank == 0 else 0)
         worker.save_checkpoint(ckpt_dir)
+        # resume: a checkpoint with the optimizer side-car, one more step, against a fresh pair of workers that load it
+        os.environ["ARENO_SAVE_OPTIMIZER"] = "1"
+        resume_dir = os.path.join(ckpt_dir, "resume")
+        worker.save_checkpoint(resume_dir)
+        os.environ.pop("ARENO_SAVE_OPTIMIZER")
+        worker.train(packs)
+        continued = _named(worker)
+        from areno_b200.api import loss_fns
+        from areno_b200.engine.config import EngineConfig, OptimizerConfig, RuntimeConfig
+        from areno_b200.engine.worker import RankWorker
+
+        fresh = RankWorker(EngineConfig(model=_moe_config(), model_path=resume_dir, seed=99, tp_size=1, dp_size=2,
+                                        expert_parallel=True,
+                                        optimizer=OptimizerConfig(lr=1e-2, grad_clip_norm=1.0, weight_decay=0.0),
+                                        runtime=RuntimeConfig(eager_decode=True, max_model_len=128,
+                                                              activation_checkpointing=False), max_running_seqs=8), "cpu")
+        fresh.loss_fn = loss_fns.grpo_loss_fn
+        fresh.train(packs)
+        assert fresh.trainer.global_step == worker.trainer.global_step == 2
+        resumed = _named(fresh)
+        for n, t in continued.items():
+            assert (t - resumed[n]).abs().max() < 2e-6, (n, float((t - resumed[n]).abs().max()))
         ret[rank] = dict(first=first.tokens, first_lp=first.logprobs, second=second.tokens, before=before, after=after,
                          loss=[s["loss"] for s in stats], scored=scored,
                          local_buckets=sum(1 for b in worker.trainer.optimizer.buckets if b.local))
