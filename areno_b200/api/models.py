@@ -19,17 +19,17 @@ class SamplingParams(BaseModel):
     """Generation controls.  ``greedy`` forces temperature 0; ``top_k=-1`` disables top-k;
     ``max_context_len`` caps whole agentic trajectories (prompt plus every generated turn)."""
 
-    greedy: bool = Field(default=False)
-    top_p: float = Field(default=1.0)
-    top_k: int = Field(default=-1)
-    max_new_tokens: int = Field(default=16)
-    max_context_len: int | None = Field(default=None)
-    temperature: float = Field(default=1.0)
-    stop: list[str] | None = Field(default=None)
-    stop_token_ids: list[int] | None = Field(default=None)
-    ignore_eos: bool = Field(default=False)
-    skip_special_tokens: bool = Field(default=True)
-    max_prompt_len: int | None = Field(default=None)
+    greedy: bool = False
+    top_p: float = 1.0
+    top_k: int = -1
+    max_new_tokens: int = 16
+    max_context_len: int | None = None
+    temperature: float = 1.0
+    stop: list[str] | None = None
+    stop_token_ids: list[int] | None = None
+    ignore_eos: bool = False
+    skip_special_tokens: bool = True
+    max_prompt_len: int | None = None
 
 
 class RolloutSequence(BaseModel):
@@ -54,5 +54,5 @@ class TrainSequence(BaseModel):
     returns: list[float] = Field(default_factory=list)
     values: list[float] = Field(default_factory=list)
     ref_logprobs: list[float] = Field(default_factory=list)
-    reward: float = Field(default=0.0)
-    eos_token_id: int = Field(default=0)
+    reward: float = 0.0
+    eos_token_id: int = 0
