@@ -177,3 +177,32 @@ def test_expert_parallel_matches_a_single_process_with_all_experts():
         loaded = RankWorker(EngineConfig(model=_moe_config(), model_path=ckpt, runtime=RuntimeConfig(eager_decode=True, max_model_len=128)), "cpu")
         for n, p in loaded.model.named_parameters():
             assert (p.detach().float() - ref_after[n]).abs().max() < 3e-5, n
+
+
+def test_runtime_picks_communicators_by_power_of_two_bucket_and_honours_a_pinned_size():
+    from types import SimpleNamespace
+
+    from areno_b200.parallel.ep import EpCommCollective, EpRuntime
+
+    ctx = SimpleNamespace(ep_group=None, ep_size=4, ep_rank=1, ep_ctl_group=None)
+    rt = EpRuntime(ctx, hidden=64, k=2, num_experts=8, device="cpu")
+    assert rt.impl == "collective"                        # no CUDA device: library collectives
+    assert [EpRuntime.bucket(n) for n in (0, 1, 64, 65, 4096, 4097)] == [64, 64, 64, 128, 4096, 8192]
+    a, b = rt.comm(10), rt.comm(60)
+    assert a is b and isinstance(a, EpCommCollective) and a.cap == 64 and (a.e_lo, a.e_local) == (2, 2)
+    assert rt.comm(100).cap == 128 and len(rt._comms) == 2
+    with rt.pinned(3000):                                 # the group-wide maximum decides, not the local size
+        big = rt.comm(5)
+        assert big.cap == 4096
+        with rt.pinned(70):
+            assert rt.comm(5).cap == 128
+        assert rt.comm(1) is big
+        try:
+            rt.comm(5000)
+        except ValueError as exc:
+            assert "exceed" in str(exc)
+        else:
+            raise AssertionError("a pass larger than its pinned bucket must be refused")
+    assert rt.comm(5).cap == 64 and rt.dropped() == 0
+    rt.close()
+    assert not rt._comms
