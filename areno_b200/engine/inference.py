@@ -161,6 +161,7 @@ class InferenceEngine:
         # expert-parallel models exchange tokens in every forward pass: see step()
         self._ep = ctx.ep_runtime if (ctx.ep_size > 1 and hasattr(model, "ep_idle_forward")) else None
         self._ep_busy = True
+        self._ep_expect_prefill = True
 
     # ------------------------------------------------------------------ state
     def _alloc_state(self):
@@ -244,6 +245,7 @@ class InferenceEngine:
         self._lockstep = get_context().tp_size > 1
         if self._ep is not None:
             self._ep_busy = True
+            self._ep_expect_prefill = True
             self._peer_waits = self._peer_waits or self.cuda
             with self._ep.pinned(self.max_slots):
                 self._ep.comm(1)     # the decode-sized communicator exists before a graph capture could need it
@@ -275,16 +277,21 @@ class InferenceEngine:
         step.  Returns the requests that completed since the last call.
 
         Expert parallelism: every forward pass is an exchange among all ranks, whose engines hold different
-        requests.  Before each of the two passes of an iteration the ranks agree (a host all-reduce of a few
-        integers) on whether anybody runs it and at which size; a rank without work of its own joins a prefill
-        with an idle pass and a decode step with all slots inactive, so that all ranks launch (and capture) the
-        same sequence of exchanges."""
+        requests.  Before a pass the ranks agree (a host all-reduce of a few integers) on whether anybody runs it
+        and at which size; a rank without work of its own joins a prefill with an idle pass and a decode step with
+        all slots inactive, so that all ranks launch (and capture) the same sequence of exchanges.  The decode
+        agreement also carries how much prefill work and how many uncollected requests any rank still has: while
+        nobody can prefill, the prefill agreement of the next iteration is skipped, and when nothing is left
+        anywhere the loop of run_until_done ends."""
         done = self._poll(block=False)
         entries = self.sched.plan_prefill()
         ep = self._ep
         if ep is not None:
-            g_pre, g_busy = ep.agree_max([sum(int(e[3]) for e in entries) if entries else 0, int(not self.idle)])
-            self._ep_busy = bool(g_busy)
+            g_pre = 0
+            if self._ep_expect_prefill:
+                g_pre = ep.agree_max([sum(int(e[3]) for e in entries) if entries else 0])[0]
+            elif entries:
+                raise RuntimeError("expert parallel: prefill work appeared although the last agreement saw none")
             if g_pre > 0:
                 with trace_range("rollout/prefill"), ep.pinned(g_pre):
                     if entries:
@@ -310,8 +317,14 @@ class InferenceEngine:
         ctx_cap = self._context_bucket(self.sched.max_seq_len + 1) if decoding else 0
         run_decode = decoding
         if ep is not None:
-            g_dec, bucket, ctx_cap = ep.agree_max([int(decoding), bucket, ctx_cap])
+            sched = self.sched
+            prefill_work = sched.num_waiting + max(sched.num_running - sched.num_decoding, 0)
+            pending = sched.num_waiting + sched.num_running
+            g_dec, bucket, ctx_cap, g_prefill, g_pending = ep.agree_max([int(decoding), bucket, ctx_cap, prefill_work,
+                                                                          pending])
             run_decode = bool(g_dec)
+            self._ep_expect_prefill = g_prefill > 0
+            self._ep_busy = g_pending > 0
         if run_decode:
             if updates:
                 self._push_block_updates(updates)
