@@ -14,6 +14,32 @@ from typing import Any, Literal
 import torch
 
 
+_DTYPE_NAMES: dict[str, torch.dtype] = {
+    "bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
+    "float16": torch.float16, "fp16": torch.float16, "half": torch.float16,
+    "float32": torch.float32, "fp32": torch.float32, "float": torch.float32,
+}
+
+
+def parse_dtype(value: Any, default: torch.dtype = torch.bfloat16) -> torch.dtype:
+    """Floating-point dtype named by a checkpoint's ``config.json`` (``torch_dtype`` / ``dtype``): the long names, the
+    usual short forms and a ``torch.`` prefix are accepted, ``None`` or an empty string gives ``default``, and a name
+    that is not a floating-point dtype this framework computes in is an error instead of a silent bf16
+    (``areno/engine/config.py:286``)."""
+    if value is None or value == "":
+        return default
+    if isinstance(value, torch.dtype):
+        if value not in _DTYPE_NAMES.values():
+            raise ValueError(f"unsupported model dtype {value}")
+        return value
+    key = str(value).strip().lower()
+    if key.startswith("torch."):
+        key = key[len("torch."):]
+    if key not in _DTYPE_NAMES:
+        raise ValueError(f"unsupported model dtype {value!r}; one of {sorted(_DTYPE_NAMES)}")
+    return _DTYPE_NAMES[key]
+
+
 @dataclass
 class OptimizerConfig:
     lr: float = 1e-4

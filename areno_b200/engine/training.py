@@ -84,18 +84,23 @@ def pack_train_data(data_pack: dict[str, Any]) -> dict[str, Any]:
     return packed
 
 
-def to_device(pack: dict[str, Any], device: torch.device) -> dict[str, Any]:
-    """Move tensor values to ``device`` (pinned staging + async copy on CUDA)."""
-    out = {}
-    cuda = torch.device(device).type == "cuda"
-    for k, v in pack.items():
-        if isinstance(v, torch.Tensor) and v.device != device:
-            if cuda and not v.is_pinned() and v.numel() > 0:
-                v = v.pin_memory()
-            out[k] = v.to(device, non_blocking=True)
-        else:
-            out[k] = v
-    return out
+def to_device(pack: Any, device: torch.device) -> Any:
+    """Move every tensor of a pack to ``device`` (pinned staging + async copy on CUDA).  Dicts, lists and tuples are
+    walked recursively and rebuilt; anything else is passed through unchanged (``areno/engine/data.py``)."""
+    device = torch.device(device)
+    if isinstance(pack, torch.Tensor):
+        if pack.device == device:
+            return pack
+        if device.type == "cuda" and pack.device.type == "cpu" and not pack.is_pinned() and pack.numel() > 0:
+            pack = pack.pin_memory()
+        return pack.to(device, non_blocking=True)
+    if isinstance(pack, dict):
+        return {k: to_device(v, device) for k, v in pack.items()}
+    if isinstance(pack, tuple) and hasattr(pack, "_fields"):          # named tuple: positional constructor
+        return type(pack)(*(to_device(v, device) for v in pack))
+    if isinstance(pack, (list, tuple)):
+        return type(pack)(to_device(v, device) for v in pack)
+    return pack
 
 
 def split_data_pack_by_dp(pack: dict[str, Any], dp_size: int) -> list[dict[str, Any]]:

@@ -16,10 +16,9 @@ from typing import Any
 
 import torch
 
-from ..engine.config import ModelConfig
+from ..engine.config import ModelConfig, parse_dtype
 from .bailing import BailingCausalLM, BailingLinearAttention, BailingMLAttention, BailingSparseMoeBlock
 from .base import ModelAdapter
-from .dense_adapters import _DTYPES
 
 
 def _bool(value: Any, default: bool) -> bool:
@@ -31,9 +30,7 @@ def _bool(value: Any, default: bool) -> bool:
 
 
 def _dtype(name: Any, default=torch.bfloat16):
-    aliases = {"fp32": torch.float32, "float": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16, "half": torch.float16}
-    key = str(name).replace("torch.", "") if name is not None else ""
-    return _DTYPES.get(key) or aliases.get(key, default)
+    return parse_dtype(name, default)
 
 
 def _tensor_plan(model: BailingCausalLM, cfg: ModelConfig):

@@ -9,14 +9,10 @@ from __future__ import annotations
 
 from typing import Any
 
-import torch
 
-from ..engine.config import ModelConfig
+from ..engine.config import ModelConfig, parse_dtype
 from .base import ModelAdapter
 from .dense import DenseCausalLM
-
-_DTYPES = {"bfloat16": torch.bfloat16, "float16": torch.float16, "float32": torch.float32}
-
 
 def _common(hf: dict[str, Any], **over) -> ModelConfig:
     heads = int(hf["num_attention_heads"])
@@ -35,7 +31,7 @@ def _common(hf: dict[str, Any], **over) -> ModelConfig:
         max_position_embeddings=int(hf.get("max_position_embeddings", 4096)),
         tie_word_embeddings=bool(hf.get("tie_word_embeddings", False)),
         hidden_act=hf.get("hidden_act", "silu"),
-        dtype=_DTYPES.get(str(hf.get("torch_dtype") or hf.get("dtype") or "bfloat16"), torch.bfloat16),
+        dtype=parse_dtype(hf.get("torch_dtype") or hf.get("dtype")),
     )
     cfg.update(over)
     return ModelConfig(**cfg)

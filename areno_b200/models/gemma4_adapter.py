@@ -11,9 +11,8 @@ from typing import Any
 
 import torch
 
-from ..engine.config import ModelConfig
+from ..engine.config import ModelConfig, parse_dtype
 from .base import ModelAdapter
-from .dense_adapters import _DTYPES
 from .gemma4 import Gemma4CausalLM
 
 _LAYER_NORMS = (("input_norm", "input_layernorm"), ("post_attn_norm", "post_attention_layernorm"),
@@ -168,8 +167,7 @@ class Gemma4Adapter(ModelAdapter):
             rope_theta=float(c.get("rope_theta", 10000.0)), max_position_embeddings=int(c.get("max_position_embeddings", 131072)),
             tie_word_embeddings=bool(c.get("tie_word_embeddings", True)), qkv_bias=bool(c.get("attention_bias", False)),
             qk_norm=True, v_norm=True,
-            dtype=_DTYPES.get(str(hf.get("torch_dtype") or c.get("torch_dtype") or hf.get("dtype") or c.get("dtype") or "bfloat16"),
-                              torch.bfloat16),
+            dtype=parse_dtype(hf.get("torch_dtype") or c.get("torch_dtype") or hf.get("dtype") or c.get("dtype")),
             hidden_act="gelu_tanh", layer_types=tuple(c.get("layer_types") or ("full_attention",) * n),
             sliding_window=c.get("sliding_window"), swa_head_dim=int(c.get("swa_head_dim") or base_d),
             swa_num_key_value_heads=int(c.get("swa_num_key_value_heads") or c.get("num_key_value_heads", heads)),

@@ -19,9 +19,8 @@ from typing import Any
 
 import torch
 
-from ..engine.config import ModelConfig
+from ..engine.config import ModelConfig, parse_dtype
 from .base import ModelAdapter
-from .dense_adapters import _DTYPES
 from .hybrid import GatedDeltaNet, HybridCausalLM
 
 
@@ -34,8 +33,7 @@ def _text_config(hf: dict[str, Any], name: str, prefix: str) -> ModelConfig:
     rope = text.get("rope_parameters") or text.get("rope_scaling") or {}
     n = int(text["num_hidden_layers"])
     heads = int(text["num_attention_heads"])
-    dtype = _DTYPES.get(str(text.get("torch_dtype") or text.get("dtype") or hf.get("torch_dtype") or hf.get("dtype")
-                            or "bfloat16"), torch.bfloat16)
+    dtype = parse_dtype(text.get("torch_dtype") or text.get("dtype") or hf.get("torch_dtype") or hf.get("dtype"))
     return ModelConfig(
         model_type=name, checkpoint_prefix=prefix, vocab_size=int(text["vocab_size"]), hidden_size=int(text["hidden_size"]),
         intermediate_size=int(text["intermediate_size"]), num_hidden_layers=n, num_attention_heads=heads,
