@@ -82,13 +82,14 @@ def messages_to_prompt_tokens(tokenizer: Any, messages: list[dict[str, Any]], *,
     if tools:
         attempts += [dict(base, tools=tools), dict(base, tools=_tools_for_template(tools))]
     attempts.append(base)
-    last_exc: Exception | None = None
-    for kwargs in attempts:
+    # a template may reject ``tools`` in its own way (a TypeError for the keyword, a template error while it walks the
+    # schema): every attempt but the last is allowed to fail, the plain rendering reports its own error
+    for kwargs in attempts[:-1]:
         try:
             return normalize_token_ids(apply_chat_template_with_options(tokenizer, messages, **kwargs))
-        except TypeError as exc:
-            last_exc = exc
-    raise last_exc  # type: ignore[misc]
+        except Exception:  # noqa: BLE001
+            continue
+    return normalize_token_ids(apply_chat_template_with_options(tokenizer, messages, **attempts[-1]))
 
 
 def _decode(tokenizer: Any, ids: list[int], *, skip_special_tokens: bool) -> str:
