@@ -32,7 +32,14 @@ def dp_rank0_results(results: list, tp_size: int, dp_size: int) -> list:
     return [results[d * tp_size] for d in range(dp_size)]
 
 
+# statistics of a rollout that describe the slowest rank rather than a total
+_STATS_MAX_OVER_RANKS = ("decode_steps", "wall_s")
+
+
 def merge_rollouts_in_input_order(outputs: list[RolloutOutput], total: int) -> RolloutOutput:
+    """One output for ``total`` prompts from the ranks' shares (each names the input positions of its rows).  Numeric
+    statistics are summed over the ranks, except the ones that every rank measures for the same loop (steps, wall
+    time), which take the largest value."""
     merged = RolloutOutput(tokens=[[] for _ in range(total)], logprobs=[[] for _ in range(total)],
                            finish_reasons=["" for _ in range(total)], prompt_indices=list(range(total)))
     for out in outputs:
@@ -42,6 +49,13 @@ def merge_rollouts_in_input_order(outputs: list[RolloutOutput], total: int) -> R
             merged.tokens[idx] = out.tokens[j]
             merged.logprobs[idx] = out.logprobs[j]
             merged.finish_reasons[idx] = out.finish_reasons[j]
+        for key, val in (out.stats or {}).items():
+            if not isinstance(val, (int, float)) or isinstance(val, bool):
+                merged.stats.setdefault(key, val)
+            elif key in _STATS_MAX_OVER_RANKS:
+                merged.stats[key] = max(merged.stats.get(key, val), val)
+            else:
+                merged.stats[key] = merged.stats.get(key, 0) + val
     return merged
 
 
