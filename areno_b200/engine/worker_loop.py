@@ -128,10 +128,10 @@ class WorkerLoop:
         def admit(cmd: Command) -> None:
             rows, indices = _local_rows(cmd.payload, self.worker)
             state = {"cmd": cmd, "indices": list(indices), "left": len(rows), "reqs": []}
-            pending[cmd.request_id] = state
-            if not rows:
+            if not rows:                     # nothing for this data-parallel row: acknowledge once, track nothing
                 self._finish(state)
                 return
+            pending[cmd.request_id] = state
             seeded = cmd.payload.sampling_params.seed is not None
             for r, idx in zip(rows, indices):
                 # a seeded request reproduces: its rows draw from streams numbered by their position
