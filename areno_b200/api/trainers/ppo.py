@@ -148,35 +148,41 @@ class PPOTrainer(PolicyOnlyTrainer):
             resp_idx = [i for i, r in enumerate(rmask) if r]
             if not resp_idx or not any(lmask[i] for i in resp_idx):
                 continue
-            p0, n_r = resp_idx[0], len(resp_idx)
-            act_old = _floats(old_lp[p0:p0 + n_r])
-            if len(act_old) != n_r:
+            # A multi-turn agentic row has several assistant spans with tool results between them, so the response
+            # positions need not be contiguous: every per-action signal is gathered by position (the reference
+            # slices ``[first, first + count)``, which is the same thing only for a single span).
+            n_r = len(resp_idx)
+            if len(old_lp) < len(tokens) or len(ref_lp) < len(tokens):
                 raise ValueError("actor returned misaligned old logprobs")
-            act_values = _floats(values[p0 - 1:p0 + n_r - 1])
-            if len(act_values) != n_r:
+            if len(values) < len(tokens) or resp_idx[0] < 1:
                 raise ValueError("critic returned misaligned token values")
+            old_lp, ref_lp, values = _floats(old_lp), _floats(ref_lp), _floats(values)
+            act_old = [old_lp[i] for i in resp_idx]
+            act_values = [values[i - 1] for i in resp_idx]          # the value before token i is generated
             token_rewards = [0.0] * n_r
             token_rewards[-1] = float(reward)
             adv, ret = compute_gae(token_rewards, act_values, gamma=self.config.gamma, lam=self.config.lam)
             adv, ret = _floats(adv), _floats(ret)
             full_adv, full_ret, full_val = [0.0] * len(tokens), [0.0] * len(tokens), [0.0] * len(tokens)
+            full_old = [0.0] * len(tokens)
             for rel, ti in enumerate(resp_idx):
                 if lmask[ti]:
                     full_adv[ti] = adv[rel]
                 full_ret[ti] = ret[rel]
                 full_val[ti] = act_values[rel]
-            roll_resp = roll[p0:p0 + n_r]
-            rollout_lp.extend(lp for lp, on in zip(roll_resp, lmask[p0:p0 + n_r]) if on)
+                full_old[ti] = act_old[rel]
+            roll_resp = [float(roll[i]) for i in resp_idx]
+            rollout_lp.extend(lp for lp, i in zip(roll_resp, resp_idx) if lmask[i])
             old_all.extend(act_old)
             diff_all.extend(o - r for o, r in zip(act_old, roll_resp))
-            ref_all.extend(_floats(ref_lp[p0:p0 + n_r]))
+            ref_all.extend(ref_lp[i] for i in resp_idx)
             val_all.extend(act_values)
             ret_all.extend(ret)
             adv_all.extend(adv)
             batch.append(TrainSequence(
                 prompt_mask=[not r for r in rmask], loss_mask=list(lmask) if explicit_loss_mask else [],
-                tokens=list(tokens), logprobs=[0.0] * p0 + act_old + [0.0] * (len(tokens) - p0 - n_r),
-                advantages=full_adv, returns=full_ret, values=full_val, ref_logprobs=_floats(ref_lp),
+                tokens=list(tokens), logprobs=full_old,
+                advantages=full_adv, returns=full_ret, values=full_val, ref_logprobs=ref_lp[:len(tokens)],
                 reward=float(reward), eos_token_id=eos))
         if batch:
             stats = self._timed("critic_train_time_s", "critic", "train", len(batch), lambda: self.areno.train_values(
