@@ -110,7 +110,10 @@ def build_chat_completion_response(*, tokenizer: Any, model: str, prompt_tokens:
                                    parsed_tool_calls: list[list[dict[str, Any]]] | None = None,
                                    response_logprobs: list[list[float]] | None = None,
                                    include_areno_metadata: bool = False, input_tokens: list[int] | None = None,
-                                   stop_strings: list[str] | None = None) -> dict[str, Any]:
+                                   stop_strings: list[str] | None = None,
+                                   include_logprobs: bool = False) -> dict[str, Any]:
+    """``include_logprobs`` adds OpenAI's ``choices[i].logprobs.content``: one entry per generated token with the
+    log-probability the sampler drew it at (no alternatives: ``top_logprobs`` stays empty)."""
     tools = list(tools or [])
     response_logprobs = response_logprobs or [[] for _ in response_ids]
     choices = []
@@ -127,7 +130,13 @@ def build_chat_completion_response(*, tokenizer: Any, model: str, prompt_tokens:
         if calls:
             message = {"role": "assistant", "content": None, "tool_calls": calls}
             finish = "tool_calls"
-        choices.append({"index": i, "message": message, "finish_reason": finish})
+        choice: dict[str, Any] = {"index": i, "message": message, "finish_reason": finish}
+        if include_logprobs:
+            lps = response_logprobs[i] if i < len(response_logprobs) else []
+            choice["logprobs"] = {"content": [
+                {"token": _decode(tokenizer, [t], skip_special_tokens=False), "logprob": float(lp), "bytes": None,
+                 "top_logprobs": []} for t, lp in zip(ids, lps)]}
+        choices.append(choice)
     resp: dict[str, Any] = {
         "id": f"chatcmpl-{uuid.uuid4().hex}", "object": "chat.completion", "created": int(time.time()), "model": model,
         "choices": choices,

@@ -50,12 +50,14 @@ class ChatCompletionRequest(BaseModel):
     stream: bool = False
     stop: str | list[str] | None = None
     seed: int | None = None
+    logprobs: bool = False            # return the sampled tokens' log-probabilities (no top-k alternatives)
 
 
 class ChatCompletionChoice(BaseModel):
     index: int
     message: dict[str, Any]
     finish_reason: str
+    logprobs: dict[str, Any] | None = None
 
 
 class ChatCompletionUsage(BaseModel):
@@ -192,14 +194,16 @@ def normalize_stop(stop: str | list[str] | None) -> list[str]:
 
 # ------------------------------------------------------------------- response building
 def build_response(state: ServeState, request: ChatCompletionRequest, prompt: list[int],
-                   response_ids: list[list[int]], finish_reasons: list[str]) -> ChatCompletionResponse:
+                   response_ids: list[list[int]], finish_reasons: list[str],
+                   response_logprobs: list[list[float]] | None = None) -> ChatCompletionResponse:
     from ..api.openai_chat import build_chat_completion_response
 
     data = build_chat_completion_response(
         tokenizer=state.tokenizer, model=request.model or state.model_path,
         prompt_tokens=len(prompt) * len(response_ids), response_ids=response_ids, finish_reasons=finish_reasons,
         tools=request.tools, tool_choice=request.tool_choice, tool_call_parser=state.tool_call_parser,
-        stop_strings=normalize_stop(request.stop))
+        stop_strings=normalize_stop(request.stop), response_logprobs=response_logprobs,
+        include_logprobs=bool(request.logprobs))
     return ChatCompletionResponse(**data)
 
 
@@ -226,7 +230,8 @@ async def run_request_rollout(state: ServeState, item: PendingRequest) -> ChatCo
         decode_progress_interval_s=state.decode_progress_interval_s)
     if item.future.done():
         return None
-    return build_response(state, item.request, item.prompt, rollout.response_ids, rollout.finish_reason)
+    return build_response(state, item.request, item.prompt, rollout.response_ids, rollout.finish_reason,
+                          rollout.response_logprobs)
 
 
 async def run_request_task(state: ServeState, item: PendingRequest) -> None:

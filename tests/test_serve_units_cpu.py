@@ -178,3 +178,19 @@ def test_choices_of_one_request_share_the_prompt_and_count_it_once_each():
     prompts, kw = eng.calls[0]
     assert prompts[0] == prompts[1] == prompts[2] and kw["max_running_prompts"] == 3     # never below the request's n
     assert kw["sampling_params"].top_k == 5 and kw["max_prompt_len"] == 256 - 4
+
+
+def test_log_probabilities_of_the_sampled_tokens_on_request():
+    tok = FakeTokenizer()
+    ids = tok.encode("a b")
+    eng = ScriptedEngine(ids)
+    app = serve.create_app(model_path="fake", engine=eng, tokenizer=tok)
+    with TestClient(app) as client:
+        plain = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "x"}]}).json()
+        assert plain["choices"][0]["logprobs"] is None
+        body = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "x"}], "logprobs": True,
+                                                         "n": 2}).json()
+    for choice in body["choices"]:
+        content = choice["logprobs"]["content"]
+        assert [c["token"] for c in content] == ["a", "b"] and [c["logprob"] for c in content] == [0.0, 0.0]
+        assert all(c["top_logprobs"] == [] and c["bytes"] is None for c in content)
