@@ -53,7 +53,9 @@ def rollout_options(ctx: Context, sampling_params: SamplingParams) -> dict:
         "decode_progress_interval_s": cfg.decode_progress_interval_s,
         "sampling_params": EngineSamplingParams(
             temperature=0.0 if sampling_params.greedy else sampling_params.temperature, top_p=sampling_params.top_p,
-            top_k=max(0, sampling_params.top_k), stop_token_ids=stop, suppress_token_ids=suppress_ids),
+            top_k=max(0, sampling_params.top_k), stop_token_ids=stop, suppress_token_ids=suppress_ids,
+            min_new_tokens=max(0, int(getattr(sampling_params, "min_new_tokens", 0) or 0)),
+            seed=getattr(sampling_params, "seed", None)),
     }
 
 

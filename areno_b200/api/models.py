@@ -30,6 +30,11 @@ class SamplingParams(BaseModel):
     ignore_eos: bool = False
     skip_special_tokens: bool = True
     max_prompt_len: int | None = None
+    # additions to the reference's fields: EOS / stop ids are masked out for the first ``min_new_tokens`` tokens;
+    # with a ``seed`` every sample draws from a random stream numbered by its position in the request, so a rollout
+    # is reproducible whatever else shares the running batch
+    min_new_tokens: int = 0
+    seed: int | None = None
 
 
 class RolloutSequence(BaseModel):

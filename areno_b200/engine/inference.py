@@ -371,11 +371,15 @@ class InferenceEngine:
             klib.check_status(self.device)   # bounded waits that ran out during this rollout surface here
 
     def generate(self, prompts: list[list[int]], params: SamplingParams, eos_token_ids=(), max_new_tokens: int = 16,
-                 progress_interval_s: float = 0.0) -> RolloutOutput:
-        """Blocking helper: generate one completion per prompt, results in prompt order."""
+                 progress_interval_s: float = 0.0, stream_ids: list[int] | None = None) -> RolloutOutput:
+        """Blocking helper: generate one completion per prompt, results in prompt order.  With a seed the rows draw
+        from random streams numbered by ``stream_ids`` (default: their position in ``prompts``)."""
         self.begin(params, eos_token_ids, max_new_tokens)
         seeded = params.seed is not None
-        rids = [self.add_request(p, stream=i if seeded else None) for i, p in enumerate(prompts)]
+        if stream_ids is not None and len(stream_ids) != len(prompts):
+            raise ValueError("stream_ids must name one random stream per prompt")
+        streams = list(range(len(prompts))) if stream_ids is None else [int(i) for i in stream_ids]
+        rids = [self.add_request(p, stream=streams[i] if seeded else None) for i, p in enumerate(prompts)]
         t0 = time.time()
         self.run_until_done(progress_interval_s)
         reqs = [self._requests[r] for r in rids]

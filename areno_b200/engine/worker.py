@@ -126,10 +126,13 @@ class RankWorker:
     @torch.no_grad()
     def rollout(self, prompts: list[list[int]], params: SamplingParams, eos_token_ids=(), max_new_tokens: int = 16,
                 max_running: int | None = None, progress_interval_s: float | None = None,
-                gather_tp: bool = False) -> RolloutOutput:
+                gather_tp: bool = False, stream_ids: list[int] | None = None) -> RolloutOutput:
         """Generate one completion per prompt.  Every rank of a rollout TP group must pass the same
         prompts; with ``gather_tp`` each rank passes only its own prompts, the group's prompts are
-        concatenated in rank order, and each rank gets back the results of its own rows."""
+        concatenated in rank order, and each rank gets back the results of its own rows.  ``stream_ids`` number the
+        random streams of a seeded request (one per prompt; default: the position in ``prompts``): a request that is
+        dealt out over data-parallel rows passes each row its prompts' positions in the whole request, so that no
+        two of its samples share a stream."""
         self.prepare_for_rollout()
         rctx = self.rollout_ctx
         lo, hi = 0, len(prompts)
@@ -137,10 +140,11 @@ class RankWorker:
             import torch.distributed as dist
 
             parts: list = [None] * rctx.tp_size
-            dist.all_gather_object(parts, prompts, group=rctx.tp_group)
-            lo = sum(len(x) for x in parts[:rctx.tp_rank])
+            dist.all_gather_object(parts, (prompts, stream_ids), group=rctx.tp_group)
+            lo = sum(len(x[0]) for x in parts[:rctx.tp_rank])
             hi = lo + len(prompts)
-            prompts = [row for part in parts for row in part]
+            prompts = [row for part in parts for row in part[0]]
+            stream_ids = [i for part in parts for i in part[1]] if all(part[1] is not None for part in parts) else None
             max_running = (max_running or self.config.max_running_seqs) * rctx.tp_size
         longest = max((len(p) for p in prompts), default=1) + max_new_tokens
         need_len = (longest + 63) // 64 * 64
@@ -152,7 +156,8 @@ class RankWorker:
         with use_context(rctx):
             eng = self.inference_engine(slots, need_len)
             with trace_range("rollout"):
-                out = eng.generate(prompts, params, eos_token_ids, max_new_tokens, progress_interval_s=interval)
+                out = eng.generate(prompts, params, eos_token_ids, max_new_tokens, progress_interval_s=interval,
+                                   stream_ids=stream_ids)
         if (lo, hi) != (0, len(prompts)):
             out = RolloutOutput(tokens=out.tokens[lo:hi], logprobs=out.logprobs[lo:hi],
                                 finish_reasons=out.finish_reasons[lo:hi], stats=out.stats)

@@ -77,7 +77,7 @@ def _rollout_blocking(worker, p: RolloutPayload) -> RolloutOutput:
         return RolloutOutput(prompt_indices=[])
     # expert parallel: a rank without prompts still joins every forward pass of the others (idle passes)
     out = worker.rollout(prompts, p.sampling_params, p.eos_token_ids, p.max_new_tokens, max_running=p.max_running_seqs,
-                         progress_interval_s=p.decode_progress_interval_s)
+                         progress_interval_s=p.decode_progress_interval_s, stream_ids=list(indices))
     out.prompt_indices = list(indices)
     return out
 

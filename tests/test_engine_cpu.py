@@ -178,3 +178,23 @@ def test_check_token_ids_guard_reports_out_of_range_samples(monkeypatch):
     eng.vocab = 1
     with pytest.raises(RuntimeError, match="out of vocab range"):
         eng.generate([[5, 6, 7]], SamplingParams(temperature=0.0), (), 4)
+
+
+def test_seeded_request_dealt_over_data_parallel_rows_draws_each_sample_from_its_own_stream():
+    """Two engines stand for two data-parallel rows that share a seeded request of four samples of one prompt: with
+    the samples' positions in the request as stream ids, the rows reproduce what one engine generates for all four,
+    and no two samples coincide; numbering the streams per row would make the rows repeat each other."""
+    single_process_context()
+    model = DenseCausalLM(tiny_config())
+    init_weights(model, 3)
+    prompt = list(range(3, 30))
+    params = SamplingParams(temperature=1.0, seed=11)
+    whole = _engine(model).generate([prompt] * 4, params, (), 6)
+    row0 = _engine(model).generate([prompt] * 2, params, (), 6, stream_ids=[0, 2])
+    row1 = _engine(model).generate([prompt] * 2, params, (), 6, stream_ids=[1, 3])
+    assert [row0.tokens[0], row1.tokens[0], row0.tokens[1], row1.tokens[1]] == whole.tokens
+    assert len({tuple(t) for t in whole.tokens}) == 4
+    local = _engine(model).generate([prompt] * 2, params, (), 6)            # default numbering: 0, 1
+    assert local.tokens == whole.tokens[:2]
+    with pytest.raises(ValueError, match="one random stream per prompt"):
+        _engine(model).generate([prompt] * 2, params, (), 6, stream_ids=[0])

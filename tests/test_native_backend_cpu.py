@@ -117,6 +117,9 @@ def test_rollout_options_from_tokenizer_and_sampling_parameters():
     assert opts["eos_token_id"] == (2,) and opts["max_prompt_len"] == 99
     assert (sp.temperature, sp.top_p, sp.top_k, sp.stop_token_ids) == (0.7, 0.9, 0, (40,))
     assert sp.suppress_token_ids == (0, 1)                   # pad and bos may never be sampled; EOS may
+    assert sp.seed is None and sp.min_new_tokens == 0
+    seeded = rollout_options(ctx, SamplingParams(seed=17, min_new_tokens=3))["sampling_params"]
+    assert seeded.seed == 17 and seeded.min_new_tokens == 3
     greedy = rollout_options(ctx, SamplingParams(greedy=True, temperature=0.9, ignore_eos=True))
     assert greedy["sampling_params"].temperature == 0.0 and greedy["eos_token_id"] == ()
     assert greedy["sampling_params"].suppress_token_ids == (0, 1)

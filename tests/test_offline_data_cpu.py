@@ -312,7 +312,7 @@ def test_sampling_defaults_do_not_assume_a_backend():
     p = SamplingParams()
     assert (p.greedy, p.top_p, p.top_k, p.max_new_tokens, p.temperature) == (False, 1.0, -1, 16, 1.0)
     assert p.stop is None and p.stop_token_ids is None and p.max_context_len is None and p.max_prompt_len is None
-    assert p.ignore_eos is False and p.skip_special_tokens is True
+    assert p.ignore_eos is False and p.skip_special_tokens is True and p.min_new_tokens == 0 and p.seed is None
     q = p.model_copy()
     q.max_new_tokens = 4
     assert p.max_new_tokens == 16

@@ -79,8 +79,9 @@ class ScriptedWorker:
         self.log.append(("engine", slots, need_len))
         return self.engine
 
-    def rollout(self, prompts, params, eos, max_new, max_running=None, progress_interval_s=None):
+    def rollout(self, prompts, params, eos, max_new, max_running=None, progress_interval_s=None, stream_ids=None):
         self.log.append(("rollout", len(prompts), max_running))
+        self.stream_ids = stream_ids
         return RolloutOutput(tokens=[[9] for _ in prompts], logprobs=[[0.0] for _ in prompts],
                              finish_reasons=["stop"] * len(prompts))
 
@@ -187,6 +188,7 @@ def test_blocking_rollout_answers_for_this_rows_prompts_only():
     payload = RolloutPayload([[[1]], [[2], [3]]], [[0], [1, 2]], max_new_tokens=4, max_running_seqs=2)
     out = execute(w, Command(Op.INFER_ROLLOUT, 0, payload))
     assert out.prompt_indices == [1, 2] and out.tokens == [[9], [9]] and w.log == [("rollout", 2, 2)]
+    assert w.stream_ids == [1, 2]            # seeded samples are numbered by their position in the whole request
     empty = RolloutPayload([[[1]], []], [[0], []], max_new_tokens=4)
     out = execute(w, Command(Op.INFER_ROLLOUT, 0, empty))
     assert out.prompt_indices == [] and out.tokens == [] and len(w.log) == 1           # no rollout was started
