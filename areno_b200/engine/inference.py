@@ -126,7 +126,7 @@ class InferenceEngine:
     def __init__(self, model, vocab_size: int, device, *, max_slots: int = 64, max_model_len: int = 4096,
                  max_prefill_tokens: int = 16384, kv_fp8: bool = False, num_pages: int | None = None,
                  graph_buckets: list[int] | None = None, eager: bool = False, seed: int = 0,
-                 max_new_cap: int = 4096):
+                 max_new_cap: int = 4096, stream_salt: int = 0):
         self.model = model
         self.vocab = vocab_size
         self.device = torch.device(device)
@@ -139,6 +139,10 @@ class InferenceEngine:
         # the checked mode validates indices on the host before every launch, which a captured graph cannot do
         self.eager = eager or not self.cuda or klib.BOUNDS_CHECK
         self.seed = seed
+        # Engines of different data-parallel rows share the seed (the ranks of one tensor-parallel group must draw
+        # identical noise) and number their requests alike, so unseeded calls mix the row's number into their random
+        # streams: without it two samples of one prompt that land on different rows would come out identical.
+        self.stream_salt = int(stream_salt)
         self.calls = 0
         self.max_out = max_new_cap
         buckets = sorted(set(graph_buckets or [1, 2, 4, 8, 16, 32, 64, 128, 256, 512]))
@@ -230,7 +234,8 @@ class InferenceEngine:
         self.calls += 1
         # The per-call seed travels in the high word of each row's random-stream id (device memory), not
         # as a kernel argument: captured decode graphs stay valid from one call to the next.
-        self.call_seed = (params.seed if params.seed is not None else (self.seed * 1000003 + self.calls)) & 0x7FFFFFFF
+        self.call_seed = (params.seed if params.seed is not None else
+                          (self.seed * 1000003 + self.calls + 0x9E3779B1 * self.stream_salt)) & 0x7FFFFFFF
         self._graph_key = (params.temperature, params.top_k, params.top_p, params.min_new_tokens)
         self.step_count = 0
         self.decode_tokens = 0

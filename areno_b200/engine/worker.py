@@ -100,7 +100,7 @@ class RankWorker:
                 self.rollout_model, self.config.model.vocab_size, self.device, max_slots=slots, max_model_len=mlen,
                 max_prefill_tokens=rt.max_prefill_tokens, kv_fp8=rt.kv_dtype == "fp8",
                 graph_buckets=rt.decode_graph_buckets, eager=rt.eager_decode, seed=self.config.seed,
-                max_new_cap=mlen)
+                max_new_cap=mlen, stream_salt=int(self.rollout_ctx.dp_rank))
         return self.infer
 
     # ---------------------------------------------------------------- rollout

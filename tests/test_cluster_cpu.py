@@ -65,7 +65,7 @@ def test_rollout_and_step_over_two_dp_ranks_then_failures():
         again = eng.generate_rollout(list(reversed(prompts)), max_new_tokens=5, max_running_prompts=8,
                                      sampling_params=SamplingParams(temperature=0.0))
         assert list(reversed(again.tokens)) == out.tokens
-        packs = [_pack(p, t, l) for p, t, l in zip(prompts[:4], out.tokens, out.logprobs)]
+        packs =[_pack(p, t, l) for p, t, l in zip(prompts[:4], out.tokens, out.logprobs)]
         for pk in packs:
             pk["_loss_fn"] = _loss
         stats = eng.step([{k: (torch.cat([a[k], b[k]], 0) if k != "_loss_fn" and a[k].shape[1:] == b[k].shape[1:] else a[k])
@@ -88,6 +88,23 @@ def test_rollout_and_step_over_two_dp_ranks_then_failures():
         with pytest.raises(WorkerError, match="exited without reporting"):
             eng.cluster.call(Op.MODEL_INFO, None, timeout=60)
         assert time.time() - t0 < 30
+    finally:
+        eng.close()
+
+
+@pytest.mark.timeout(300)
+def test_samples_of_one_prompt_differ_across_data_parallel_ranks():
+    """The samples of a prompt are dealt over both ranks, which share a seed and number their requests alike: sampled
+    (not greedy) completions must still all differ instead of coming out in identical pairs."""
+    eng = _engine()
+    try:
+        prompt = torch.randint(3, 512, (12,), generator=torch.Generator().manual_seed(0)).tolist()
+        group = eng.generate_rollout([prompt] * 4, max_new_tokens=8, max_running_prompts=8,
+                                     sampling_params=SamplingParams(temperature=1.0))
+        assert len({tuple(t) for t in group.tokens}) == 4
+        seeded = [eng.generate_rollout([prompt] * 4, max_new_tokens=8, max_running_prompts=8,
+                                       sampling_params=SamplingParams(temperature=1.0, seed=21)).tokens for _ in range(2)]
+        assert seeded[0] == seeded[1] and len({tuple(t) for t in seeded[0]}) == 4
     finally:
         eng.close()
 

@@ -198,3 +198,20 @@ def test_seeded_request_dealt_over_data_parallel_rows_draws_each_sample_from_its
     assert local.tokens == whole.tokens[:2]
     with pytest.raises(ValueError, match="one random stream per prompt"):
         _engine(model).generate([prompt] * 2, params, (), 6, stream_ids=[0])
+
+
+def test_unseeded_engines_of_different_data_parallel_rows_draw_different_noise():
+    """Rows share the engine seed and number their requests alike; the row's number keeps their samples apart, while a
+    seeded request reproduces on whichever row serves it."""
+    single_process_context()
+    model = DenseCausalLM(tiny_config())
+    init_weights(model, 3)
+    prompt = list(range(3, 30))
+    free = SamplingParams(temperature=1.0)
+    row0 = _engine(model, seed=5, stream_salt=0).generate([prompt] * 2, free, (), 8)
+    row1 = _engine(model, seed=5, stream_salt=1).generate([prompt] * 2, free, (), 8)
+    again = _engine(model, seed=5, stream_salt=0).generate([prompt] * 2, free, (), 8)
+    assert row0.tokens == again.tokens and row0.tokens[0] != row1.tokens[0] and row0.tokens[1] != row1.tokens[1]
+    seeded = SamplingParams(temperature=1.0, seed=9)
+    assert _engine(model, seed=5, stream_salt=0).generate([prompt], seeded, (), 8).tokens == \
+        _engine(model, seed=5, stream_salt=3).generate([prompt], seeded, (), 8).tokens
