@@ -30,7 +30,7 @@ import torch
 
 from ..utils.log import get_logger
 from .config import EngineConfig
-from .protocol import Command, Op, WorkerResult
+from .protocol import Command, Op, WorkerResult, narrow_for_rank
 
 logger = get_logger()
 
@@ -297,9 +297,10 @@ class SpawnCluster(_ClusterBase):
         entry = {"kind": kind, "ranks": ranks, "results": {}, "op": op, **extra}
         with self._lock:
             self._pending[rid] = entry
-        cmd = Command(op, rid, payload, ranks)
-        for q in self._cmd_qs:
-            q.put(cmd)
+        tp, rollout_tp = int(self.config.tp_size), int(self.config.rollout_tp)
+        for rank, q in enumerate(self._cmd_qs):
+            mine = narrow_for_rank(payload, train_dp_rank=rank // tp, rollout_dp_rank=rank // rollout_tp)
+            q.put(Command(op, rid, mine, ranks))
         return rid
 
     @staticmethod

@@ -10,7 +10,7 @@ Role of ``areno/engine/protocol.py:31-151`` in the reference.
 from __future__ import annotations
 
 import enum
-from dataclasses import dataclass, field
+from dataclasses import dataclass, field, replace
 from typing import Any
 
 from .inference import SamplingParams
@@ -109,3 +109,23 @@ class CachePayload:
 @dataclass
 class SavePayload:
     path: str
+
+
+def narrow_for_rank(payload: Any, *, train_dp_rank: int, rollout_dp_rank: int) -> Any:
+    """The part of a payload that one rank reads.  Payloads carry one entry per data-parallel row (prompts, score
+    rows, training shards) and a worker only ever looks at its own row's, so a driver that ships commands to worker
+    processes blanks the others instead of serialising the whole job's data once per rank.  The shape stays the
+    same (a list with one slot per row), so workers index it as before."""
+    def only(rows, keep, empty):
+        return [row if i == keep else empty() for i, row in enumerate(rows)]
+
+    if isinstance(payload, RolloutPayload):
+        return replace(payload, prompts_by_dp=only(payload.prompts_by_dp, rollout_dp_rank, list),
+                       prompt_indices_by_dp=only(payload.prompt_indices_by_dp, rollout_dp_rank, list))
+    if isinstance(payload, ScorePayload):
+        return replace(payload, rows_by_dp=only(payload.rows_by_dp, train_dp_rank, list))
+    if isinstance(payload, (TrainPayload, TrainValuesPayload)):
+        packs = [only(shards, train_dp_rank, lambda: None) if isinstance(shards, (list, tuple)) else shards
+                 for shards in payload.packs]
+        return replace(payload, packs=packs)
+    return payload

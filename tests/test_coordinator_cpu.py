@@ -278,3 +278,21 @@ def test_from_pretrained_needs_a_model_or_a_config(monkeypatch):
     monkeypatch.setattr(engine_api, "make_cluster", lambda c, launcher, worker: ScriptedCluster(c, lambda *a: None))
     eng = ArenoEngine.from_pretrained(None, model_config=tiny_config(), tp_size=2, dp_size=2, max_running_seqs=7, seed=5)
     assert eng.config.dummy_load and eng.config.world_size == 4 and eng.config.max_running_seqs == 7 and eng.config.seed == 5
+
+
+def test_payloads_are_narrowed_to_what_a_rank_reads():
+    from areno_b200.engine.protocol import (CachePayload, ScorePayload, TrainPayload, TrainValuesPayload, narrow_for_rank)
+
+    roll = RolloutPayload([[[1], [2]], [[3]], [[4]]], [[0, 3], [1], [2]], max_new_tokens=4, max_cache_len=9)
+    mine = narrow_for_rank(roll, train_dp_rank=0, rollout_dp_rank=1)
+    assert mine.prompts_by_dp == [[], [[3]], []] and mine.prompt_indices_by_dp == [[], [1], []]
+    assert mine.max_cache_len == 9 and roll.prompts_by_dp[0] == [[1], [2]]          # the original is untouched
+    score = narrow_for_rank(ScorePayload("ref", [[[1]], [[2]]], 7, 4), train_dp_rank=1, rollout_dp_rank=0)
+    assert score.rows_by_dp == [[], [[2]]] and (score.role, score.pad_token_id, score.microbatch_size) == ("ref", 7, 4)
+    a, b, whole = {"x": 1}, {"x": 2}, {"x": 3}
+    train = narrow_for_rank(TrainPayload([[a, b], whole], 2), train_dp_rank=1, rollout_dp_rank=0)
+    assert train.packs == [[None, b], whole] and train.gradient_accumulation_steps == 2
+    critic = narrow_for_rank(TrainValuesPayload("critic", [[a, b]], None, 0.3, 0.7), train_dp_rank=0, rollout_dp_rank=0)
+    assert critic.packs == [[a, None]] and critic.cliprange_value == 0.3
+    cache = CachePayload(4, 128)
+    assert narrow_for_rank(cache, train_dp_rank=0, rollout_dp_rank=0) is cache and narrow_for_rank(None, train_dp_rank=0, rollout_dp_rank=0) is None
