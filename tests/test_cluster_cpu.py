@@ -105,6 +105,20 @@ def test_samples_of_one_prompt_differ_across_data_parallel_ranks():
         seeded = [eng.generate_rollout([prompt] * 4, max_new_tokens=8, max_running_prompts=8,
                                        sampling_params=SamplingParams(temperature=1.0, seed=21)).tokens for _ in range(2)]
         assert seeded[0] == seeded[1] and len({tuple(t) for t in seeded[0]}) == 4
+        # role scoring: rows are dealt over the ranks by stride and come back in row order; a frozen reference built
+        # from the actor's weights scores exactly like the actor
+        from areno_b200.api.roles import ModelRole
+
+        g = torch.Generator().manual_seed(1)
+        rows = [torch.randint(3, 512, (n,), generator=g).tolist() for n in (9, 4, 12, 7, 5)]
+        eng.ensure_roles({"ref": ModelRole("ref", "", trainable=False), "critic": ModelRole("critic", "", trainable=True)})
+        ref, actor = eng.score_logprobs("ref", rows), eng.score_logprobs("actor", rows)
+        assert [len(r) for r in ref] == [len(r) for r in rows] and all(r[0] == 0.0 and max(r[1:]) < 0 for r in ref)
+        for a, b in zip(ref, actor):
+            assert a == pytest.approx(b, abs=1e-6)
+        assert eng.score_logprobs("ref", list(reversed(rows)))[0] == pytest.approx(ref[-1], abs=1e-6)
+        values = eng.score_values("critic", rows)
+        assert [len(v) for v in values] == [len(r) for r in rows] and all(x == 0.0 for v in values for x in v)   # zero head
     finally:
         eng.close()
 
