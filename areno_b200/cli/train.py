@@ -93,6 +93,58 @@ OPTIONS = [
 ]
 GROUP_ORDER = ["Basic", "Rollout", "Train", "Checkpoint", "Observability"]
 
+# Help text of the options that do not carry one above (kept apart so that the table stays one line per flag).
+_HELP = {
+    "--epochs": "Passes over the dataset.",
+    "--mem-frac": "Fraction of GPU memory --tune-params may plan for.",
+    "--tune-max-samples": "Largest n_samples * batch the tuner tries.",
+    "--tp-size": "Tensor-parallel width (training and rollout).",
+    "--world-size": "Number of GPUs; data-parallel width is world / tp.",
+    "--max-prompt-tokens": "Prompts longer than this are skipped (and counted in the log).",
+    "--max-new-tokens": "Completion budget per sample.",
+    "--max-context-len": "Cap on a whole trajectory (agentic: prompt plus every turn); default: the model's limit.",
+    "--temperature": "Sampling temperature.",
+    "--top-k": "Keep the k most likely tokens (-1: off).",
+    "--top-p": "Nucleus sampling mass (1.0: off).",
+    "--greedy": "Arg-max decoding (temperature 0).",
+    "--attn-backend": "Accepted for compatibility; both values select this package's kernels.",
+    "--kv-dtype": "KV page storage: bf16, or fp8 (e4m3 with one scale per token and KV head).",
+    "--disable-thinking": "Render chat templates with enable_thinking=False where the template takes it.",
+    "--agent-timeout-s": "Time limit of one proxied chat completion.",
+    "--score-micro-bs": "Sequences per scoring micro-batch of the reference / critic / reward roles.",
+    "--lr": "Peak learning rate.",
+    "--min-lr": "Floor of the decay schedule.",
+    "--lr-decay-steps": "Optimizer steps over which the rate decays to --min-lr.",
+    "--lr-decay-style": "Shape of the decay.",
+    "--adam-beta1": "AdamW beta1.",
+    "--adam-beta2": "AdamW beta2.",
+    "--adam-8bit": "Block-scaled 8-bit AdamW moments (fp32 master weights stay).",
+    "--weight-decay": "Decoupled weight decay.",
+    "--grad-clip-norm": "Global gradient-norm clip.",
+    "--activation-checkpointing/--no-activation-checkpointing":
+        "Recompute layer activations in backward when memory is short (decided from free memory per micro-batch).",
+    "--train-tool-results": "Agentic: also train on tool-result tokens (default: context only).",
+    "--gspo-clip-eps": "GSPO sequence-ratio clip.",
+    "--grpo-clip-eps": "GRPO token-ratio clip.",
+    "--dpo-beta": "DPO temperature.",
+    "--critic-warmup-steps": "PPO: steps that train only the critic.",
+    "--critic-lr": "PPO critic learning rate.",
+    "--use-kl-loss/--no-use-kl-loss": "PPO: add a KL-to-reference penalty to the actor loss.",
+    "--kl-loss-coef": "PPO: weight of that penalty.",
+    "--kl-loss-type": "PPO: KL estimator.",
+    "--clip-eps": "PPO ratio clip.",
+    "--clip-ratio-c": "PPO dual-clip bound for negative advantages.",
+    "--value-clip-eps": "PPO value clip.",
+    "--value-loss-coef": "PPO value-loss weight.",
+    "--gamma": "PPO discount.",
+    "--lam": "PPO GAE lambda.",
+    "--save-interval": "Save every this many steps.",
+    "--metrics-log-dir": "TensorBoard event files (metrics.jsonl without a TensorBoard package).",
+}
+for _flag, _kw, _group in OPTIONS:
+    _kw.setdefault("help", _HELP.get(_flag))
+
+
 
 def option_name(flag: str) -> str:
     return flag.split("/")[0].lstrip("-").replace("-", "_")

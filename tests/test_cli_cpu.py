@@ -284,3 +284,12 @@ def test_train_smoke_script_runs_the_cli_path_end_to_end(algo):
     assert proc.returncode == 0, proc.stderr[-2000:]
     out = json.loads(proc.stdout.strip().splitlines()[-1])
     assert out["steps_done"] == 2 and out["checkpoints"] and out["metric_files"]
+
+
+def test_every_option_has_help_and_a_row_in_the_reference_page():
+    from pathlib import Path
+
+    page = (Path(__file__).resolve().parents[1] / "docs" / "cli_train.md").read_text()
+    for flag, kw, _group in cli_train.OPTIONS:
+        assert kw.get("help"), flag
+        assert f"| `{flag}` |" in page and kw["help"] in page, flag
