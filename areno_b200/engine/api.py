@@ -157,6 +157,11 @@ class ArenoEngine:
         worker = self._require_spmd()
         dp, mine = int(self.config.rollout_dp), int(worker.rollout_ctx.dp_rank)
         prompts = list(prompts)
+        if sampling_params is not None and sampling_params.seed is not None:
+            # every row numbers its own prompts from zero: keep the rows' seeded streams apart
+            from dataclasses import replace
+
+            sampling_params = replace(sampling_params, seed=(int(sampling_params.seed) + 0x9E3779B1 * mine) & 0x7FFFFFFF)
         by_dp = [prompts if r == mine else [] for r in range(dp)]
         idx_by_dp = [list(range(len(prompts))) if r == mine else [] for r in range(dp)]
         payload = self._rollout_payload(prompts or [[0]], idx_by_dp, by_dp, max_new_tokens=max_new_tokens,
