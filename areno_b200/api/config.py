@@ -13,20 +13,20 @@ class ArenoConfig:
     """Layout and tuning of the native backend.  ``optimizer`` / ``runtime`` are passed verbatim to the
     engine's ``OptimizerConfig`` / ``RuntimeConfig``."""
 
-    model_path: str | None = None
-    tp_size: int = 1
-    dp_size: int | None = None
+    model_path: str | None = None       # overrides the Trainer's model path (rarely needed)
+    tp_size: int = 1                    # tensor-parallel width of training (and of rollout unless set below)
+    dp_size: int | None = None          # None: world_size // tp_size
     # decode tensor-parallel over this many GPUs while training stays data parallel (needs tp_size == 1)
     rollout_tp_size: int | None = None
     # mixture-of-experts models: deal the experts out over the data-parallel ranks and exchange tokens with their
     # owners in every MoE layer, in rollout and training (needs tp_size == 1 and num_experts divisible by the ranks)
     expert_parallel: bool = False
-    devices: list[int] | None = None
-    dummy_load: bool = False
+    devices: list[int] | None = None    # GPU ordinals, one per rank; None: 0 .. world_size - 1
+    dummy_load: bool = False            # seeded random weights instead of reading the checkpoint
     optimizer: dict[str, Any] = field(default_factory=dict)
     runtime: dict[str, Any] = field(default_factory=dict)
-    max_running_prompts: int = 64
-    decode_progress_interval_s: float = 10.0
+    max_running_prompts: int = 64       # sequences decoded concurrently over the whole job
+    decode_progress_interval_s: float = 10.0      # period of the rollout progress log line (0: off)
     # how workers are launched: "spawn" (one process per GPU), "inprocess" (single GPU, no process hop),
     # "spmd" (this process is one of WORLD_SIZE ranks started by torch.distributed.run)
     launcher: str | None = None
@@ -35,7 +35,7 @@ class ArenoConfig:
     # the host.  All ranks must make the same calls with the same number of micro-batches.
     spmd_local_data: bool = False
     model_config: Any = None  # explicit ModelConfig (synthetic models without a checkpoint directory)
-    seed: int = 0
+    seed: int = 0                       # weight initialisation (dummy_load) and the samplers' base seed
 
 
 BackendConfig = ArenoConfig
