@@ -366,8 +366,11 @@ class InferenceEngine:
             if progress_interval_s > 0 and time.time() - t_last >= progress_interval_s:
                 now = time.time()
                 rate = (self.decode_tokens - tok_last) / max(now - t_last, 1e-9)
-                logger.info("decode progress running=%d waiting=%d steps=%d decode_tok_s=%.1f cuda_graph=%s",
-                            self.sched.num_running, self.sched.num_waiting, self.step_count, rate, not self.eager)
+                ctx = get_context()
+                if ctx.tp_rank == 0:      # one line per data-parallel row: the ranks of a TP group decode the same batch
+                    logger.info("decode progress row=%d/%d running=%d waiting=%d steps=%d decode_tok_s=%.1f cuda_graph=%s",
+                                ctx.dp_rank, ctx.dp_size, self.sched.num_running, self.sched.num_waiting, self.step_count,
+                                rate, not self.eager)
                 t_last, tok_last = now, self.decode_tokens
         for req in self._poll(block=True, drain=True):
             if on_finished is not None:

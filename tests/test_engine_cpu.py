@@ -215,3 +215,16 @@ def test_unseeded_engines_of_different_data_parallel_rows_draw_different_noise()
     seeded = SamplingParams(temperature=1.0, seed=9)
     assert _engine(model, seed=5, stream_salt=0).generate([prompt], seeded, (), 8).tokens == \
         _engine(model, seed=5, stream_salt=3).generate([prompt], seeded, (), 8).tokens
+
+
+def test_progress_line_names_the_data_parallel_row(caplog):
+    import logging
+
+    single_process_context()
+    model = DenseCausalLM(tiny_config())
+    init_weights(model, 3)
+    eng = _engine(model)
+    with caplog.at_level(logging.INFO, logger="areno"):
+        eng.generate([list(range(3, 20))] * 2, SamplingParams(temperature=0.0), (), 6, progress_interval_s=1e-9)
+    lines = [r.getMessage() for r in caplog.records if "decode progress" in r.getMessage()]
+    assert lines and all("row=0/1" in ln and "decode_tok_s=" in ln and "running=" in ln for ln in lines)
