@@ -1,0 +1,122 @@
+"""Property tests (hypothesis) of the pure host-side helpers: dealing sequences to ranks and micro-batches, padding and
+packing index arithmetic, prefix and merge helpers, and tool-call parsers that must never raise on arbitrary text."""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+from hypothesis import given, settings
+from hypothesis import strategies as st
+
+from areno_b200.api.agentic import common_prefix_len
+from areno_b200.api.backend.native import pad_rows
+from areno_b200.api.rewards import compute_group_advantages
+from areno_b200.api.tool_call_parser import get_tool_call_parser
+from areno_b200.engine._runtime import pack_indices
+from areno_b200.engine.api import merge_rollouts_in_input_order, split_list_by_dp
+from areno_b200.engine.inference import RolloutOutput
+from areno_b200.engine.training import balanced_partition, pack_into_bins, split_data_pack_by_dp
+
+lengths_st = st.lists(st.integers(min_value=1, max_value=2000), min_size=0, max_size=60)
+
+
+@given(lengths_st, st.integers(min_value=1, max_value=9))
+@settings(max_examples=200, deadline=None)
+def test_balanced_partition_deals_every_sequence_once_with_even_counts(lengths, parts):
+    plan = balanced_partition(lengths, parts)
+    assert len(plan) == parts and sorted(i for part in plan for i in part) == list(range(len(lengths)))
+    counts = [len(p) for p in plan]
+    assert max(counts) - min(counts) <= 1
+    if lengths and len(lengths) >= parts:
+        loads = [sum(lengths[i] for i in p) for p in plan]
+        assert max(loads) - min(loads) <= max(lengths)           # never worse than one sequence apart
+    assert plan == balanced_partition(list(lengths), parts)      # deterministic: every rank computes the same plan
+
+
+@given(lengths_st, st.integers(min_value=1, max_value=4096))
+@settings(max_examples=200, deadline=None)
+def test_bins_hold_every_sequence_once_and_respect_the_token_cap(lengths, cap):
+    bins = pack_into_bins(lengths, cap)
+    assert sorted(i for b in bins for i in b) == list(range(len(lengths))) and all(b for b in bins)
+    for b in bins:
+        assert sum(lengths[i] for i in b) <= cap or len(b) == 1  # only a single over-long sequence may exceed it
+
+
+@given(lengths_st, st.integers(min_value=64, max_value=4096), st.integers(min_value=1, max_value=12))
+@settings(max_examples=200, deadline=None)
+def test_fixed_bin_count_never_exceeds_the_request(lengths, cap, n_bins):
+    bins = pack_into_bins(lengths, cap, n_bins=n_bins)
+    assert len(bins) <= n_bins and sorted(i for b in bins for i in b) == list(range(len(lengths)))
+    if sum(lengths) <= cap:                                       # everything fits one bin: spread, not stacked
+        assert len(bins) == min(n_bins, len(lengths))
+
+
+@given(st.lists(st.lists(st.integers(min_value=-5, max_value=5), max_size=12), max_size=10),
+       st.one_of(st.none(), st.integers(min_value=0, max_value=15)))
+@settings(max_examples=200, deadline=None)
+def test_pad_rows_matches_a_plain_loop(rows, width):
+    out = pad_rows(rows, dtype=torch.long, fill_value=7, width=width)
+    w = (max((len(r) for r in rows), default=0) if width is None else width)
+    assert tuple(out.shape) == (len(rows), w)
+    for r, got in zip(rows, out.tolist()):
+        assert got == (list(r) + [7] * w)[:w]
+
+
+@given(st.lists(st.integers(min_value=0, max_value=20), min_size=1, max_size=12), st.integers(min_value=1, max_value=16))
+@settings(max_examples=200, deadline=None)
+def test_pack_indices_enumerate_tokens_and_actions_of_padded_rows(lengths, width):
+    lens = np.clip(np.asarray(lengths, dtype=np.int64), 1, width)
+    rows, cols, aidx, arows = pack_indices(np.asarray(lengths, dtype=np.int64), width)
+    want_rows = [r for r, n in enumerate(lens) for _ in range(n)]
+    want_cols = [c for n in lens for c in range(n)]
+    assert rows.tolist() == want_rows and cols.tolist() == want_cols
+    # an action is every token that has a successor in its row
+    starts = np.concatenate([[0], np.cumsum(lens)[:-1]])
+    want_actions = [int(s + c) for s, n in zip(starts, lens) for c in range(n - 1)]
+    assert aidx.tolist() == want_actions and arows.tolist() == [r for r, n in enumerate(lens) for _ in range(n - 1)]
+
+
+@given(st.lists(st.integers(0, 3), max_size=12), st.lists(st.integers(0, 3), max_size=12))
+def test_common_prefix_is_the_longest_agreeing_run(a, b):
+    n = common_prefix_len(a, b)
+    assert a[:n] == b[:n] and (n == min(len(a), len(b)) or a[n] != b[n])
+
+
+@given(st.lists(st.floats(min_value=-100, max_value=100, allow_nan=False), max_size=16))
+def test_group_advantages_are_centred_and_finite(rewards):
+    adv = compute_group_advantages(rewards)
+    assert len(adv) == len(rewards) and all(np.isfinite(adv))
+    if rewards:
+        assert abs(sum(adv)) < 1e-3 * max(1, len(adv))
+        order = np.argsort(rewards, kind="stable")
+        assert all(adv[order[i]] <= adv[order[i + 1]] + 1e-9 for i in range(len(order) - 1))      # order preserved
+
+
+@given(st.integers(1, 9), st.lists(st.integers(0, 50), max_size=40))
+def test_round_robin_dealing_and_merging_are_inverse(dp, items):
+    parts = split_list_by_dp(items, dp)
+    idx = split_list_by_dp(list(range(len(items))), dp)
+    outs = [RolloutOutput(tokens=[[v] for v in part], logprobs=[[0.0] for _ in part], finish_reasons=["stop"] * len(part),
+                          prompt_indices=ix) for part, ix in zip(parts, idx)]
+    merged = merge_rollouts_in_input_order(outs, len(items))
+    assert [t[0] for t in merged.tokens] == items
+
+
+@given(st.integers(1, 6), st.integers(0, 20))
+def test_pack_split_keeps_every_row_or_replicates_small_batches(dp, batch):
+    pack = {"input_ids": torch.arange(batch * 2).view(batch, 2), "tag": "x"}
+    shards = split_data_pack_by_dp(pack, dp)
+    assert len(shards) == dp
+    if batch >= dp and dp > 1:
+        assert sorted(int(v) for s in shards for v in s["input_ids"][:, 0]) == [2 * i for i in range(batch)]
+    else:
+        assert all(s is pack for s in shards)
+
+
+@given(st.text(max_size=300), st.sampled_from(["json", "qwen", "gemma4", "minicpm"]))
+@settings(max_examples=300, deadline=None)
+def test_tool_call_parsers_never_raise_and_only_name_declared_tools(text, name):
+    tools = [{"type": "function", "function": {"name": "lookup", "parameters": {"type": "object", "properties": {"q": {"type": "string"}}}}}]
+    result = get_tool_call_parser(name).parse(text, tools, None)
+    for call in result.tool_calls:
+        assert call["function"]["name"] == "lookup" and isinstance(call["function"]["arguments"], str)
