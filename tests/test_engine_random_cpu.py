@@ -1,0 +1,95 @@
+"""Randomised schedules through the inference engine on the CPU: requests of random lengths and budgets arrive at random
+steps, slots, prefill budget and page pool are small enough to force queueing, chunked prefill and evictions.  Greedy
+tokens must equal what the model generates for each prompt on its own with a full forward pass every step, whatever
+the schedule was; stop tokens end a sequence exactly where the stand-alone generation meets one."""
+
+from __future__ import annotations
+
+import random
+
+import pytest
+import torch
+
+from areno_b200.engine.inference import InferenceEngine, SamplingParams
+from areno_b200.models.dense import DenseCausalLM, TrainMeta, init_weights
+from areno_b200.ops.attention import build_varlen_meta
+from areno_b200.parallel.context import single_process_context
+from tests.helpers import tiny_config
+
+
+@pytest.fixture(scope="module")
+def model():
+    single_process_context()
+    m = DenseCausalLM(tiny_config())
+    init_weights(m, 7)
+    return m
+
+
+def _alone(model, prompt, max_new, stop):
+    """Greedy continuation by full forward passes; the stop token is kept, as the engine keeps it."""
+    toks = []
+    with torch.no_grad():
+        for _ in range(max_new):
+            toks.append(int(_logits(model, prompt + toks)[-1].argmax(-1)))
+            if toks[-1] in stop:
+                return toks, "stop"
+    return toks, "length"
+
+
+def _logits(model, tokens):
+    ids = torch.tensor(tokens)
+    with torch.no_grad():
+        h = model(ids, torch.arange(len(ids)), TrainMeta(build_varlen_meta([len(ids)]), False)).hidden_states
+        return model.compute_logits(h).float()
+
+
+# The engine reads keys and values back from 16-bit pages, the stand-alone pass keeps them in fp32: a token whose
+# logit is within this margin of the best one counts as the greedy choice (random-init logits have many near-ties).
+NEAR_TIE = 2e-2
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_any_schedule_gives_the_stand_alone_greedy_tokens(model, seed):
+    single_process_context()
+    rng = random.Random(seed)
+    slots = rng.choice([2, 3, 4])
+    budget = rng.choice([16, 32, 64])
+    n_req = rng.randint(4, 8)
+    reqs = [([rng.randrange(3, 512) for _ in range(rng.randint(2, 90))], rng.randint(1, 14)) for _ in range(n_req)]
+    longest = max(len(p) + n for p, n in reqs)
+    per_seq = (longest + 63) // 64
+    num_pages = rng.choice([per_seq + 1, per_seq * 2, per_seq * slots])          # tight pools force evictions
+    eng = InferenceEngine(model, 512, "cpu", max_slots=slots, max_model_len=per_seq * 64, max_prefill_tokens=budget,
+                          num_pages=num_pages)
+    # a stop token that some stand-alone generation actually produces, so that both finish reasons occur
+    probe, _ = _alone(model, reqs[0][0], reqs[0][1], ())
+    stop = (probe[len(probe) // 2],) if rng.random() < 0.7 else ()
+    eng.begin(SamplingParams(temperature=0.0), stop, 16)
+    arrivals = sorted((rng.randint(0, 25), i) for i in range(n_req))
+    rid_of, finished, step = {}, {}, 0
+    while len(finished) < n_req:
+        while arrivals and arrivals[0][0] <= step:
+            _, i = arrivals.pop(0)
+            rid_of[eng.add_request(reqs[i][0], reqs[i][1])] = i
+        for req in eng.step():
+            finished[rid_of[req.rid]] = req
+        step += 1
+        assert step < 3000, "the engine stopped making progress"
+    exact = 0
+    for i, (prompt, max_new) in enumerate(reqs):
+        got = finished[i]
+        want, reason = _alone(model, prompt, max_new, stop)
+        exact += got.tokens == want
+        # every token is the greedy choice given the tokens before it, up to near-ties
+        logits = _logits(model, prompt + got.tokens)[len(prompt) - 1:-1]
+        chosen = logits.gather(-1, torch.tensor(got.tokens)[:, None]).squeeze(-1)
+        assert bool((chosen >= logits.max(-1).values - NEAR_TIE).all()), (seed, i, len(prompt), max_new)
+        # and it ended where it had to: at its first stop token, or at its budget without having met one
+        if got.reason == "stop":
+            assert got.tokens[-1] in stop and not set(got.tokens[:-1]) & set(stop) and len(got.tokens) <= max_new
+        else:
+            assert got.reason == "length" and len(got.tokens) == max_new and not set(got.tokens) & set(stop)
+        ref_lp = torch.log_softmax(logits, -1).gather(-1, torch.tensor(got.tokens)[:, None]).squeeze(-1)
+        assert torch.allclose(ref_lp, torch.tensor(got.logprobs), atol=3e-2)
+    assert exact >= n_req - 2                  # near-ties are rare: most requests match token for token
+    assert eng.idle and eng.sched.num_free_pages == num_pages
