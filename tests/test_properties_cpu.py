@@ -120,3 +120,41 @@ def test_tool_call_parsers_never_raise_and_only_name_declared_tools(text, name):
     result = get_tool_call_parser(name).parse(text, tools, None)
     for call in result.tool_calls:
         assert call["function"]["name"] == "lookup" and isinstance(call["function"]["arguments"], str)
+
+
+@given(st.lists(st.tuples(st.lists(st.integers(0, 30), min_size=1, max_size=6),          # response words of a turn
+                          st.lists(st.integers(31, 60), min_size=0, max_size=4)),        # tool-result words after it
+                min_size=1, max_size=6),
+       st.lists(st.integers(61, 90), min_size=1, max_size=5))                            # the user's prompt
+@settings(max_examples=150, deadline=None)
+def test_merged_agentic_rows_carry_exactly_the_generated_tokens_as_response(turn_specs, prompt_words):
+    """Whatever the number of turns and tool results: the merged row's response positions are the turns' generated
+    tokens in order, with their log-probs, and everything else (prompt, tool results) is untrained context."""
+    from areno_b200.api.agentic import AgentItem, AgentTrajectoryTurn, LossMaskPolicy, SampleAccumulator
+    from tests.test_agentic_units_cpu import WordTokenizer
+
+    tok = WordTokenizer()
+    prompt = " ".join(f"w{w}" for w in prompt_words)
+    item = AgentItem(record={}, prompt=prompt, input_tokens=tok.encode(prompt), prompt_index=0, sample_index=0)
+    acc = SampleAccumulator(tok, LossMaskPolicy())
+    messages = [{"role": "user", "content": prompt}]
+    all_resp, all_lp, sample = [], [], None
+    for t, (resp_words, tool_words) in enumerate(turn_specs):
+        text = " ".join(f"w{w}" for w in resp_words)
+        ids = tok.encode(text)
+        lps = [-(t + 1) - 0.01 * k for k in range(len(ids))]
+        response = {"choices": [{"message": {"role": "assistant", "content": text}}],
+                    "areno": {"response_tokens": ids, "response_logprobs": lps}}
+        sample = acc.add_turn(AgentTrajectoryTurn(item=item, messages=list(messages), response=response))
+        all_resp += ids
+        all_lp += lps
+        messages = messages + [{"role": "assistant", "content": text}]
+        if tool_words:
+            messages = messages + [{"role": "tool", "name": "t", "content": " ".join(f"w{w}" for w in tool_words)}]
+    row, mask = sample.token_row, sample.response_mask_row
+    assert len(row) == len(mask) == len(sample.loss_mask_row) == len(sample.rollout_logprobs_row)
+    assert [t for t, m in zip(row, mask) if m] == all_resp
+    assert [lp for lp, m in zip(sample.rollout_logprobs_row, mask) if m] == all_lp
+    assert all(lp == 0.0 for lp, m in zip(sample.rollout_logprobs_row, mask) if not m)
+    assert sample.loss_mask_row == mask and sample.response_tokens == all_resp and len(acc.samples) == 1
+    assert row[:len(item.input_tokens)] == item.input_tokens and not any(mask[:len(item.input_tokens)])
