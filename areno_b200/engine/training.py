@@ -208,6 +208,14 @@ class TrainingManager:
     def train(self, packs: list, gradient_accumulation_steps: int | None = None) -> list[dict]:
         """``packs``: list of micro-batches, each a list of per-DP-rank shards (or a single pack)."""
         n = len(packs)
+        ctx = get_context()
+        if ctx.ep_size > 1 and ctx.ep_runtime is not None:
+            # every micro-batch is a group-wide token exchange: a rank with fewer of them would leave the others
+            # waiting inside one.  All ranks learn the spread here and fail together instead.
+            most, neg_least = ctx.ep_runtime.agree_max([n, -n])
+            if most != -neg_least:
+                raise ValueError(f"expert parallelism needs the same number of micro-batches on every rank; this call "
+                                 f"has between {-neg_least} and {most} (this rank: {n})")
         accum = n if not gradient_accumulation_steps else max(1, min(gradient_accumulation_steps, n))
         results = []
         for i, shards in enumerate(packs):

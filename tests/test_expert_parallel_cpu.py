@@ -118,6 +118,14 @@ def _rank_main(rank, world, port, ckpt_dir, ret):
         resumed = _named(fresh)
         for n, t in continued.items():
             assert (t - resumed[n]).abs().max() < 2e-6, (n, float((t - resumed[n]).abs().max()))
+        # ranks that bring different numbers of micro-batches fail together with a message, instead of one of them
+        # waiting for ever inside a token exchange
+        try:
+            worker.train(packs[: (2 if rank == 0 else 3)])
+            uneven = "no error"
+        except ValueError as exc:
+            uneven = str(exc)
+        assert "same number of micro-batches" in uneven and "between 2 and 3" in uneven, uneven
         ret[rank] = dict(first=first.tokens, first_lp=first.logprobs, second=second.tokens, before=before, after=after,
                          loss=[s["loss"] for s in stats], scored=scored,
                          local_buckets=sum(1 for b in worker.trainer.optimizer.buckets if b.local))
