@@ -25,7 +25,7 @@ from ..models.dense import TrainMeta
 from ..ops.attention import build_varlen_meta
 from ..parallel.context import get_context
 from ..utils.log import get_logger
-from .config import EngineConfig, OptimizerConfig
+from .config import OptimizerConfig
 from .logprobs import lm_head_logprobs
 from .optim import ShardedAdamW
 from .training import to_device

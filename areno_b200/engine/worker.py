@@ -14,7 +14,6 @@ from __future__ import annotations
 import json
 import os
 import time
-from typing import Any
 
 import torch
 

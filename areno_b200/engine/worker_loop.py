@@ -16,10 +16,9 @@ import queue
 import traceback
 from typing import Any, Callable
 
-from ..parallel.context import get_context, use_context
+from ..parallel.context import get_context
 from .inference import RolloutOutput
-from .protocol import (CachePayload, Command, Op, RolesPayload, RolloutPayload, SavePayload, ScorePayload, TrainPayload,
-                       TrainValuesPayload, WorkerResult)
+from .protocol import Command, Op, RolloutPayload, WorkerResult
 
 
 def execute(worker, cmd: Command) -> Any:

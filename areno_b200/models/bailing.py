@@ -29,7 +29,7 @@ from ..ops import attention as attn_ops
 from ..ops import gemm, linear_attn as la, moe as moe_ops, paged_attention as pa, rope as rope_ops
 from ..parallel import collectives as coll
 from ..parallel.context import get_context
-from .dense import Attention, DecoderLayer, DenseCausalLM, InferMeta, TrainMeta, _gather_history
+from .dense import Attention, DecoderLayer, DenseCausalLM, TrainMeta, _gather_history
 from .layers import ColumnParallelLinear, GatedMLP, MergedColumnParallelLinear, RMSNorm, RowParallelLinear, _param
 from .moe import Experts
 

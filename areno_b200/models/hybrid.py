@@ -24,7 +24,7 @@ from ..engine.config import ModelConfig
 from ..ops import gemm, linear_attn as la
 from ..parallel import collectives as coll
 from ..parallel.context import get_context
-from .dense import Attention, DecoderLayer, DenseCausalLM, InferMeta, TrainMeta
+from .dense import Attention, DecoderLayer, DenseCausalLM, TrainMeta
 from .layers import ColumnParallelLinear, RowParallelLinear, _param
 
 

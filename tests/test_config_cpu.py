@@ -10,7 +10,7 @@ import pytest
 import torch
 
 from areno_b200.api.trainer_config import TrainerConfig
-from areno_b200.engine.config import EngineConfig, ModelConfig, OptimizerConfig, RuntimeConfig, parse_dtype
+from areno_b200.engine.config import EngineConfig, OptimizerConfig, RuntimeConfig, parse_dtype
 from areno_b200.engine.training import to_device
 from areno_b200.models.registry import get_adapter
 from tests.helpers import tiny_config

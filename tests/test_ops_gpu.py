@@ -1,7 +1,5 @@
 """GPU numerics of the sm_100a kernels against plain PyTorch fp32 references."""
 
-import math
-
 import pytest
 import torch
 
