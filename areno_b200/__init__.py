@@ -27,3 +27,22 @@ def configure_allocator() -> None:
             torch.cuda.memory._set_allocator_settings("expandable_segments:True")
         except Exception:  # pragma: no cover - older torch without the setting
             pass
+
+
+# The names the reference's top-level package offers (``areno/__init__.py:46-66``), resolved on first use so that
+# ``import areno_b200`` stays free of torch-heavy imports.
+_LAZY_EXPORTS = {
+    "ArenoEngine": "areno_b200.engine.api", "EngineConfig": "areno_b200.engine.config",
+    "ModelConfig": "areno_b200.engine.config", "OptimizerConfig": "areno_b200.engine.config",
+    "RuntimeConfig": "areno_b200.engine.config", "RolloutOutput": "areno_b200.engine.inference",
+    "SamplingParams": "areno_b200.engine.inference", "TrainStats": "areno_b200.engine.training",
+    "Trainer": "areno_b200.api.trainer",
+}
+
+
+def __getattr__(name: str):
+    if name in _LAZY_EXPORTS:
+        import importlib
+
+        return getattr(importlib.import_module(_LAZY_EXPORTS[name]), name)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

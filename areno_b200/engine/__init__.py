@@ -10,6 +10,7 @@ _LAZY = {
     "RuntimeConfig": ("areno_b200.engine.config", "RuntimeConfig"),
     "SamplingParams": ("areno_b200.engine.inference", "SamplingParams"),
     "RolloutOutput": ("areno_b200.engine.inference", "RolloutOutput"),
+    "TrainStats": ("areno_b200.engine.training", "TrainStats"),
 }
 
 

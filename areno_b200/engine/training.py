@@ -173,12 +173,24 @@ def pack_into_bins(lengths: list[int], token_cap: int, n_bins: int | None = None
     return [sorted(b) for b in bins if b]
 
 
+class TrainStats(dict):
+    """Statistics of one training micro-step (``loss``, ``stepped``, ``global_step``, ``metrics``, ``num_tokens``): a
+    dict whose entries also read as attributes, the form of the reference's dataclass
+    (``areno/engine/data/batch.py:19-24``), so ``stats.loss`` and ``stats["loss"]`` both work."""
+
+    def __getattr__(self, name: str):
+        try:
+            return self[name]
+        except KeyError:
+            raise AttributeError(name) from None
+
+
 def merge_train_stats(stats: list[dict]) -> dict:
     """Mean over DP ranks of scalar stats (``areno/engine/runtime/common.py:112-132``)."""
     stats = [s for s in stats if s]
     if not stats:
-        return {}
-    out = dict(stats[0])
+        return TrainStats()
+    out = TrainStats(stats[0])
     out["loss"] = sum(s["loss"] for s in stats) / len(stats)
     metrics: dict[str, float] = {}
     for key in stats[0].get("metrics", {}):

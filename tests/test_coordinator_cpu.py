@@ -296,3 +296,25 @@ def test_payloads_are_narrowed_to_what_a_rank_reads():
     assert critic.packs == [[a, None]] and critic.cliprange_value == 0.3
     cache = CachePayload(4, 128)
     assert narrow_for_rank(cache, train_dp_rank=0, rollout_dp_rank=0) is cache and narrow_for_rank(None, train_dp_rank=0, rollout_dp_rank=0) is None
+
+
+def test_top_level_names_and_attribute_style_statistics():
+    import copy
+    import pickle
+
+    import areno_b200
+    from areno_b200.api import Trainer
+    from areno_b200.engine.training import TrainStats
+
+    assert areno_b200.Trainer is Trainer and areno_b200.ArenoEngine is ArenoEngine and areno_b200.EngineConfig is EngineConfig
+    assert areno_b200.SamplingParams is SamplingParams and areno_b200.RolloutOutput is RolloutOutput
+    assert areno_b200.TrainStats is TrainStats and areno_b200.ModelConfig is type(tiny_config())
+    with pytest.raises(AttributeError):
+        areno_b200.NoSuchName
+    merged = merge_train_stats([{"loss": 1.0, "stepped": True, "metrics": {"kl": 0.5}}, {"loss": 2.0, "metrics": {"kl": 1.5}}])
+    assert isinstance(merged, TrainStats) and merged.loss == merged["loss"] == 1.5 and merged.metrics == {"kl": 1.0}
+    assert merged.stepped is True and merged == {"loss": 1.5, "stepped": True, "metrics": {"kl": 1.0}}
+    with pytest.raises(AttributeError):
+        merged.absent
+    assert pickle.loads(pickle.dumps(merged)) == merged and copy.deepcopy(merged).loss == 1.5
+    assert merge_train_stats([]) == {}
