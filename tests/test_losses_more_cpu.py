@@ -232,3 +232,11 @@ def test_gae_terminal_reward_and_length_check():
     assert compute_gae([], [], gamma=0.9, lam=0.9) == ([], [])
     with pytest.raises(ValueError, match="one value per reward"):
         _compute_gae_python([1.0], [0.1, 0.2], gamma=0.9, lam=0.9)
+
+
+def test_losses_are_importable_from_the_reference_module_paths():
+    import importlib
+
+    for name in ("grpo", "gspo", "ppo", "dpo", "sft"):
+        mod = importlib.import_module(f"areno_b200.api.loss_fns.{name}")
+        assert getattr(mod, f"{name}_loss_fn") is getattr(loss_fns, f"{name}_loss_fn")
