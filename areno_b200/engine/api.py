@@ -252,9 +252,10 @@ class ArenoEngine:
     def score_rewards(self, role, token_rows, *, pad_token_id: int = 0):
         return self._score(Op.SCORE_REWARDS, role, token_rows, pad_token_id)
 
-    def train_values(self, role, packs, *, gradient_accumulation_steps=None, cliprange_value=0.5, value_loss_coef=0.5):
+    def train_values(self, role, data_packs, *, gradient_accumulation_steps=None, cliprange_value=0.5,
+                     value_loss_coef=0.5):
         dp = int(self.config.dp_size)
-        packs_by_dp = [split_data_pack_by_dp(p, dp) for p in packs]
+        packs_by_dp = [split_data_pack_by_dp(p, dp) for p in data_packs]
         results = self.cluster.call(Op.TRAIN_VALUES, TrainValuesPayload(role, packs_by_dp, gradient_accumulation_steps,
                                                                        cliprange_value, value_loss_coef))
         # every rank answers with one flat dict of critic statistics for the whole call: mean over the DP replicas
