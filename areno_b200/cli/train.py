@@ -460,7 +460,7 @@ def _build_command() -> click.Command:
     fn = _train_callback
     for flag, kw, _group in reversed(OPTIONS):
         fn = click.option(flag, **kw)(fn)
-    return click.command(name="train", cls=GroupedCommand, context_settings={"max_content_width": 120},
+    return click.command(name="train", cls=GroupedCommand, context_settings={"max_content_width": 120, "help_option_names": ["-h", "--help"]},
                          help="Train a model with SFT, DPO, GSPO, GRPO, PPO or a registered algorithm.")(fn)
 
 
