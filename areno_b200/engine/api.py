@@ -62,8 +62,15 @@ def merge_rollouts_in_input_order(outputs: list[RolloutOutput], total: int) -> R
 class ArenoEngine:
     def __init__(self, config: EngineConfig, loss_fn: Callable | None = None, launcher: str | None = None,
                  worker=None):
+        self.loss_fn = loss_fn if loss_fn is not None else config.train_loss_fn
+        if config.train_loss_fn is not None:
+            # the loss travels with the packs; the copy of the configuration that goes to the workers carries none
+            # (it is pickled for spawned workers, which a closure would not survive)
+            import copy
+
+            config = copy.copy(config)
+            config.train_loss_fn = None
         self.config = config
-        self.loss_fn = loss_fn
         self.cluster = make_cluster(config, launcher, worker)
         self._dp_cursor = itertools.count()
 
@@ -212,6 +219,10 @@ class ArenoEngine:
         number of packs.  The returned statistics are this rank's own."""
         if not data_packs:
             return []
+        if self.loss_fn is not None:
+            for p in data_packs:          # packs may bring their own loss; the engine's is the default
+                if isinstance(p, dict):
+                    p.setdefault("_loss_fn", self.loss_fn)
         dp = int(self.config.dp_size)
         if local:
             worker = self._require_spmd()

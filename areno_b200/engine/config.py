@@ -154,6 +154,13 @@ class ModelConfig:
     embed_scale: float = 1.0
     rope_interleaved: bool = False
     norm_weight_offset: float = 0.0   # Gemma-style (1 + w) norms use 1.0
+    # Fields of the reference's ``ModelConfig`` that select among its back ends or describe layers this framework
+    # does not execute (multi-token-prediction heads): accepted so that configs written for it construct, not read.
+    num_nextn_predict_layers: int = 0
+    mtp_loss_scaling_factor: float = 0.0
+    linear_backend: str | None = None
+    moe_backend: str | None = None
+    attn_backend: str | None = None
     extra: dict[str, Any] = field(default_factory=dict)
 
     @property
@@ -212,6 +219,9 @@ class EngineConfig:
     decode_progress_interval_s: float = 10.0
     seed: int = 0
     backend: Literal["nccl", "gloo"] | None = None
+    # ``loss_fn(data_pack, logprobs) -> loss | (loss, metrics)`` for packs that do not carry their own ``_loss_fn``
+    # (the reference's way of handing the loss to the engine; ``ArenoEngine(config, loss_fn=...)`` is the other)
+    train_loss_fn: Any = None
 
     def __post_init__(self) -> None:
         if isinstance(self.optimizer, dict):

@@ -69,6 +69,9 @@ class SamplingParams:
     seed: int | None = None
     stop_token_ids: tuple[int, ...] = ()
     suppress_token_ids: tuple[int, ...] = ()
+    # accepted for configurations written for the reference, where it asks the engine to look the special ids up; here
+    # the caller names the ids to suppress (the SDK backend derives them from the tokenizer)
+    suppress_special_tokens: bool = True
 
 
 @dataclass
@@ -91,6 +94,10 @@ class RolloutOutput:
     @property
     def finish_reason(self) -> list[str]:
         return self.finish_reasons
+
+    @property
+    def metrics(self) -> dict:
+        return self.stats
 
 
 @dataclass

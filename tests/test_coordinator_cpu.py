@@ -318,3 +318,35 @@ def test_top_level_names_and_attribute_style_statistics():
         merged.absent
     assert pickle.loads(pickle.dumps(merged)) == merged and copy.deepcopy(merged).loss == 1.5
     assert merge_train_stats([]) == {}
+
+
+def test_the_engines_loss_function_is_the_default_for_packs_without_one(monkeypatch):
+    seen = []
+
+    def handler(op, payload, rank, dp_rank, tp_rank):
+        seen.append([shards[dp_rank].get("_loss_fn") for shards in payload.packs])
+        return [{"loss": 0.0, "metrics": {}} for _ in payload.packs]
+
+    def engine_loss(pack, lp):
+        return lp.sum()
+
+    def pack_loss(pack, lp):
+        return lp.mean()
+
+    monkeypatch.setattr(engine_api, "make_cluster", lambda c, launcher, worker: ScriptedCluster(c, handler))
+    cfg = EngineConfig(model=tiny_config(), train_loss_fn=engine_loss)
+    eng = ArenoEngine(cfg)
+    assert eng.loss_fn is engine_loss and eng.config.train_loss_fn is None and cfg.train_loss_fn is engine_loss
+    eng.step([{"input_ids": torch.zeros(1, 2)}, {"input_ids": torch.zeros(1, 2), "_loss_fn": pack_loss}])
+    assert seen[-1] == [engine_loss, pack_loss]
+    explicit = ArenoEngine(cfg, loss_fn=pack_loss)
+    assert explicit.loss_fn is pack_loss
+    bare = ArenoEngine(EngineConfig(model=tiny_config()))
+    bare.step([{"input_ids": torch.zeros(1, 2)}])
+    assert seen[-1] == [None]                          # nothing stamped: the worker reports the missing loss
+
+
+def test_model_configs_written_for_the_reference_construct():
+    cfg = tiny_config(num_nextn_predict_layers=1, mtp_loss_scaling_factor=0.1, linear_backend="cublas", moe_backend="triton",
+                      attn_backend="flash")
+    assert cfg.num_nextn_predict_layers == 1 and cfg.attn_backend == "flash"
