@@ -74,3 +74,34 @@ def config_from_pretrained(model_path: str):
     hf = read_hf_config(model_path)
     adapter = find_adapter(hf)
     return adapter, adapter.config_from_hf(hf)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Dispatch helpers under the names of the reference's registry (``areno/models/registry.py:50-116``).
+
+def load_model_plugins() -> None:
+    """Register the bundled families (idempotent, thread-safe)."""
+    _ensure_bundled()
+
+
+def adapter_from_hf(model_path: str) -> ModelAdapter:
+    return find_adapter(read_hf_config(str(model_path)))
+
+
+def config_from_hf(model_path: str):
+    return config_from_pretrained(str(model_path))[1]
+
+
+def build_model(config, device="cpu"):
+    return get_adapter(config.model_type).build(config, device=device)
+
+
+def load_model_weights(model, config, model_path: str) -> None:
+    get_adapter(config.model_type).load_weights(model, str(model_path), config)
+
+
+def save_model_weights(model, config, output_path: str, source_path: str | None = None):
+    """Save through the family's adapter.  Wrappers that keep the module under ``_orig_mod`` are peeled off first."""
+    while getattr(model, "_orig_mod", None) is not None:
+        model = model._orig_mod
+    return get_adapter(config.model_type).save_weights(model, str(output_path), config, source_path)

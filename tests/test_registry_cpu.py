@@ -80,3 +80,30 @@ def test_registration_replaces_by_name_and_survives_threads(tmp_path):
     assert not errors
     names = registry.list_adapters()
     assert all(names.count(f"toy_{i}") == 1 for i in range(8)) and BUNDLED <= set(names)
+
+
+def test_dispatch_helpers_build_load_and_save_through_the_family_adapter(tmp_path):
+    import torch
+
+    from areno_b200.parallel.context import single_process_context
+    from tests.helpers import write_tiny_checkpoint
+
+    single_process_context()
+    src = str(tmp_path / "src")
+    write_tiny_checkpoint(src, seed=4)
+    registry.load_model_plugins()
+    assert registry.adapter_from_hf(src).name == "qwen2"
+    cfg = registry.config_from_hf(src)
+    model = registry.build_model(cfg)
+    registry.load_model_weights(model, cfg, src)
+
+    class Wrapped:                                   # what a compiling wrapper looks like from outside
+        def __init__(self, inner):
+            self._orig_mod = inner
+
+    out = str(tmp_path / "out")
+    registry.save_model_weights(Wrapped(Wrapped(model)), cfg, out, src)
+    again = registry.build_model(registry.config_from_hf(out))
+    registry.load_model_weights(again, cfg, out)
+    for (n, a), (_, b) in zip(model.named_parameters(), again.named_parameters()):
+        assert torch.equal(a, b), n
