@@ -25,13 +25,24 @@ def resolve_model_path(ref: str | None) -> str | None:
     return snapshot_download(repo_id=str(ref))
 
 
+def resolve_model_ref(model_ref: str, cache: dict[str, str] | None = None) -> str:
+    """``resolve_model_path`` with a cache keyed by the reference: several roles that name the same repo id are
+    resolved (and, the first time, downloaded) once (``areno/cli/model_refs.py:11-26``)."""
+    if cache is not None and model_ref in cache:
+        return cache[model_ref]
+    resolved = resolve_model_path(model_ref)
+    if cache is not None:
+        cache[model_ref] = resolved
+    return resolved
+
+
 def resolve_model_refs_for_config(config: Any) -> Any:
     """Return a copy of a trainer config with every checkpoint reference resolved to a directory."""
     if not is_dataclass(config):
         return config
     names = {f.name for f in fields(config)}
-    updates = {}
+    updates, cache = {}, {}
     for name in MODEL_REF_FIELDS:
         if name in names and getattr(config, name):
-            updates[name] = resolve_model_path(getattr(config, name))
+            updates[name] = resolve_model_ref(getattr(config, name), cache)
     return replace(config, **updates) if updates else config

@@ -97,6 +97,31 @@ def test_model_refs(tmp_path):
     cfg = PPOTrainerConfig(algo="ppo", ckpt=str(d), dataset_path="x", ref_ckpt=str(d), reward_ckpt=None)
     out = resolve_model_refs_for_config(cfg)
     assert out.ckpt == str(d) and out.ref_ckpt == str(d) and out.reward_ckpt is None and out is not cfg
+    # a repo id shared by several roles is fetched once
+    import sys
+    import types
+
+    from areno_b200.cli.model_refs import resolve_model_ref
+
+    calls = []
+    fake = types.ModuleType("huggingface_hub")
+    fake.snapshot_download = lambda repo_id: calls.append(repo_id) or f"/cache/{repo_id}"
+    old = sys.modules.get("huggingface_hub")
+    sys.modules["huggingface_hub"] = fake
+    try:
+        cfg = PPOTrainerConfig(algo="ppo", ckpt="org/model", dataset_path="x", ref_ckpt="org/model", critic_ckpt="org/model",
+                               reward_ckpt="org/reward")
+        out = resolve_model_refs_for_config(cfg)
+        assert (out.ckpt, out.ref_ckpt, out.critic_ckpt, out.reward_ckpt) == ("/cache/org/model",) * 3 + ("/cache/org/reward",)
+        assert calls == ["org/model", "org/reward"]
+        cache = {}
+        assert resolve_model_ref("org/other", cache) == resolve_model_ref("org/other", cache) and calls.count("org/other") == 1
+        assert resolve_model_ref("org/other") == "/cache/org/other" and calls.count("org/other") == 2      # no cache, no reuse
+    finally:
+        if old is None:
+            sys.modules.pop("huggingface_hub", None)
+        else:
+            sys.modules["huggingface_hub"] = old
 
 
 # ------------------------------------------------------------------- sampling reference
