@@ -204,9 +204,17 @@ def _spawn_entry(rank: int, config: EngineConfig, port: int, cmd_q, result_q) ->
 
 
 class SpawnCluster(_ClusterBase):
-    def __init__(self, config: EngineConfig, start: bool = True):
+    """One worker process per rank, fed through queues.  ``op_deadline_s`` (or ``ARENO_OP_DEADLINE_S``) is a watchdog: a
+    call that has not been answered by every awaited rank within that many seconds stops the worker PROCESSES
+    (shutdown request, then SIGTERM, then SIGKILL; devices are never reset) and raises, naming the ranks that were
+    silent.  Without it a call waits for as long as the workers live."""
+
+    def __init__(self, config: EngineConfig, start: bool = True, op_deadline_s: float | None = None):
         super().__init__(config)
         import torch.multiprocessing as mp
+
+        env = os.environ.get("ARENO_OP_DEADLINE_S")
+        self.op_deadline_s = float(op_deadline_s) if op_deadline_s is not None else (float(env) if env else None)
 
         self._mp = mp.get_context("spawn")
         self._procs: list = []
@@ -313,21 +321,48 @@ class SpawnCluster(_ClusterBase):
         return [entry["results"][r].payload if r in entry["results"] else None
                 for r in range(max(entry["ranks"]) + 1)]
 
+    def _abandon(self, rid: int, op) -> None:
+        """The watchdog's verdict on a call that ran past the deadline: stop the workers and say who was silent."""
+        with self._lock:
+            entry = self._pending.pop(rid, None)
+        silent = sorted(set(entry["ranks"]) - set(entry["results"])) if entry else []
+        self.close()
+        raise WorkerError(f"{op} was not answered within the {self.op_deadline_s:g} s deadline by rank(s) {silent}; "
+                          "the worker processes have been stopped")
+
     def call(self, op, payload=None, timeout=None, result_ranks=None):
         box: queue.Queue = queue.Queue()
-        self._submit(op, payload, result_ranks, "sync", {"box": box})
+        rid = self._submit(op, payload, result_ranks, "sync", {"box": box})
+        watchdog = timeout is None and self.op_deadline_s is not None
         try:
-            entry = box.get(timeout=timeout)
+            entry = box.get(timeout=self.op_deadline_s if watchdog else timeout)
         except queue.Empty:
+            if watchdog:
+                self._abandon(rid, op)
+            with self._lock:
+                self._pending.pop(rid, None)
             raise TimeoutError(f"{op} timed out after {timeout}s") from None
         return self._unpack(entry, op)
 
     async def call_async(self, op, payload=None, result_ranks=None):
         loop = asyncio.get_running_loop()
         fut = loop.create_future()
-        self._submit(op, payload, result_ranks, "async", {"future": (loop, fut)})
-        entry = await fut
+        rid = self._submit(op, payload, result_ranks, "async", {"future": (loop, fut)})
+        if self.op_deadline_s is None:
+            entry = await fut
+        else:
+            try:
+                entry = await asyncio.wait_for(asyncio.shield(fut), self.op_deadline_s)
+            except asyncio.TimeoutError:
+                await loop.run_in_executor(None, self._abandon_quietly, rid)
+                raise WorkerError(f"{op} was not answered within the {self.op_deadline_s:g} s deadline; the worker "
+                                  "processes have been stopped") from None
         return self._unpack(entry, op)
+
+    def _abandon_quietly(self, rid: int) -> None:
+        with self._lock:
+            self._pending.pop(rid, None)
+        self.close()
 
     def close(self) -> None:
         if self._closed:

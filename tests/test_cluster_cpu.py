@@ -123,6 +123,35 @@ def test_samples_of_one_prompt_differ_across_data_parallel_ranks():
         eng.close()
 
 
+def _sleepy_loss(pack, logprobs):
+    time.sleep(300)
+    return logprobs.sum()
+
+
+@pytest.mark.timeout(180)
+def test_watchdog_stops_the_workers_of_a_call_that_runs_past_its_deadline(monkeypatch):
+    monkeypatch.setenv("ARENO_OP_DEADLINE_S", "600")               # read at construction; tightened below
+    eng = _engine(dp=1)
+    try:
+        assert eng.cluster.op_deadline_s == 600.0
+        prompt = list(range(3, 12))
+        out = eng.generate_rollout([prompt], max_new_tokens=3, max_running_prompts=2,
+                                   sampling_params=SamplingParams(temperature=0.0))
+        pack = _pack(prompt, out.tokens[0], out.logprobs[0])
+        pack["_loss_fn"] = _sleepy_loss
+        procs = list(eng.cluster._procs)
+        eng.cluster.op_deadline_s = 2.0
+        t0 = time.time()
+        with pytest.raises(WorkerError, match=r"not answered within the 2 s deadline by rank\(s\) \[0\]"):
+            eng.step([pack])
+        assert time.time() - t0 < 60
+        assert all(not p.is_alive() for p in procs)                # processes stopped; nothing else was touched
+        with pytest.raises(WorkerError, match="closed"):
+            eng.cluster.call(Op.MODEL_INFO)
+    finally:
+        eng.close()
+
+
 @pytest.mark.timeout(120)
 def test_start_up_failure_is_reported():
     cfg = tiny_config(num_attention_heads=4, num_key_value_heads=2)
