@@ -68,7 +68,7 @@ class RuntimeConfig:
         default_factory=lambda: [1, 2, 4, 8, 12, 16, 24, 32, 40, 48, 56, 64, 96, 128, 192, 256, 384, 512]
     )
     max_prefill_tokens: int = 16384
-    kv_cache_fraction: float = 0.9
+    kv_cache_fraction: float = 0.9        # accepted for compatibility: the KV pool is running sequences x longest sequence
     max_model_len: int | None = None
     logprob_chunk: int = 4096             # rows per lm_head + log-prob chunk
     # training at tp_size > 1: shard the activations between the TP seams by tokens (all-gather + reduce-scatter in
