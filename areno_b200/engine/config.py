@@ -58,7 +58,7 @@ class OptimizerConfig:
 
 @dataclass
 class RuntimeConfig:
-    kv_block_size: int = 64               # tokens per KV page (fixed by the decode kernel)
+    kv_block_size: int = 64               # accepted for compatibility (checked, not read): pages hold 64 tokens
     kv_dtype: Literal["bf16", "fp8"] = "bf16"
     attn_backend: str = "flash"           # accepted for compatibility; one kernel family exists here
     activation_checkpointing: bool = True
@@ -74,7 +74,7 @@ class RuntimeConfig:
     # training at tp_size > 1: shard the activations between the TP seams by tokens (all-gather + reduce-scatter in
     # place of the all-reduces); ARENO_SEQUENCE_PARALLEL=1 switches it on as well
     sequence_parallel: bool = False
-    deterministic: bool = False
+    deterministic: bool = False           # accepted for compatibility: the kernels' reductions run in a fixed order anyway
 
     def __post_init__(self) -> None:
         if self.attn_backend not in {"flash", "native"}:
