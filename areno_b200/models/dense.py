@@ -344,23 +344,6 @@ class DenseCausalLM(nn.Module):
     def reset_kv_caches(self) -> None:
         """Nothing to zero: pages are only read below ``seq_lens``."""
 
-    def offload_kv_caches(self) -> None:
-        self._kv_host = [tuple(None if t is None else t.to("cpu") for t in c) for c in self.kv_caches()]
-        self.clear_kv_caches()
-
-    def onload_kv_caches(self) -> None:
-        dev = self.embed.weight.device
-        host = getattr(self, "_kv_host", None)
-        if host is not None:
-            self.set_kv_caches([tuple(None if t is None else t.to(dev) for t in c) for c in host])
-            self._kv_host = None
-
-    def prepare_infer_weights(self) -> None:
-        """Dense layers use the training weights directly for inference."""
-
-    def clear_infer_weights(self) -> None:
-        pass
-
     def offload_train_weights(self) -> None:
         for p in self.parameters():
             p.data = p.data.to("cpu", non_blocking=True)

@@ -206,31 +206,3 @@ def all_gather_last_dim(x):
     parts = [torch.empty_like(x) for _ in range(size)]
     dist.all_gather(parts, x, group=group)
     return torch.cat(parts, dim=-1)
-
-
-def all_gather_first_dim(x):
-    group, size, _ = _tp()
-    if size == 1:
-        return x.unsqueeze(0)
-    x = x.contiguous()
-    out = torch.empty((size, *x.shape), dtype=x.dtype, device=x.device)
-    dist.all_gather_into_tensor(out.view(-1, *x.shape[1:]) if x.dim() > 0 else out, x, group=group)
-    return out
-
-
-def broadcast_tensor(x, src_tp_rank: int = 0):
-    ctx = get_context()
-    if ctx.tp_size == 1:
-        return x
-    src = ctx.dp_rank * ctx.tp_size + src_tp_rank
-    dist.broadcast(x, src=src, group=ctx.tp_group)
-    return x
-
-
-def broadcast_object(obj, src_tp_rank: int = 0):
-    ctx = get_context()
-    if ctx.tp_size == 1:
-        return obj
-    box = [obj]
-    dist.broadcast_object_list(box, src=ctx.dp_rank * ctx.tp_size + src_tp_rank, group=ctx.tp_group)
-    return box[0]

@@ -12,7 +12,6 @@ from __future__ import annotations
 
 import contextlib
 import datetime
-import os
 from dataclasses import dataclass
 from typing import Any
 
@@ -41,10 +40,6 @@ class ParallelContext:
     ep_group: Any = None
     ep_ctl_group: Any = None
     ep_runtime: Any = None
-
-    @property
-    def is_tp_first(self) -> bool:
-        return self.tp_rank == 0
 
     @property
     def rollout_layout(self) -> "ParallelContext":
@@ -142,7 +137,3 @@ def destroy_parallel() -> None:
         except Exception:
             pass
     set_context(ParallelContext())
-
-
-def env_rank_world() -> tuple[int, int, int]:
-    return int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))

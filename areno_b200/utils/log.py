@@ -8,7 +8,6 @@ import os
 
 _LOGGER_NAME = "areno"
 _configured = False
-_once_keys: set[str] = set()
 
 
 def get_logger(name: str | None = None) -> logging.Logger:
@@ -24,11 +23,3 @@ def get_logger(name: str | None = None) -> logging.Logger:
         root.propagate = False
         _configured = True
     return root if not name else root.getChild(name)
-
-
-def log_once(key: str, message: str, level: int = logging.INFO) -> None:
-    """Emit ``message`` the first time ``key`` is seen in this process."""
-    if key in _once_keys:
-        return
-    _once_keys.add(key)
-    get_logger().log(level, message)
