@@ -373,14 +373,16 @@ class SpawnCluster(_ClusterBase):
                 q.put(Command(Op.SHUTDOWN, 0, None))
             except Exception:
                 pass
+        deadline = time.time() + 5.0                 # one grace period for all workers, not one each
         for p in self._procs:
-            p.join(timeout=5)
+            p.join(timeout=max(0.0, deadline - time.time()))
         for p in self._procs:
             if p.is_alive():
                 p.terminate()
+        deadline = time.time() + 2.0
         for p in self._procs:
             if p.is_alive():
-                p.join(timeout=2)
+                p.join(timeout=max(0.0, deadline - time.time()))
                 if p.is_alive():
                     p.kill()
         self._stop_pump.set()
