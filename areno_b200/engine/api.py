@@ -285,3 +285,9 @@ class ArenoEngine:
 
     def close(self) -> None:
         self.cluster.close()
+
+    def __enter__(self) -> "ArenoEngine":
+        return self
+
+    def __exit__(self, *_exc) -> None:
+        self.close()

@@ -350,3 +350,16 @@ def test_model_configs_written_for_the_reference_construct():
     cfg = tiny_config(num_nextn_predict_layers=1, mtp_loss_scaling_factor=0.1, linear_backend="cublas", moe_backend="triton",
                       attn_backend="flash")
     assert cfg.num_nextn_predict_layers == 1 and cfg.attn_backend == "flash"
+
+
+def test_the_engine_is_a_context_manager_that_closes_its_cluster(monkeypatch):
+    closed = []
+    eng, cluster = _engine(lambda *a: None, monkeypatch)
+    cluster.close = lambda: closed.append(True)
+    with eng as e:
+        assert e is eng
+    assert closed == [True]
+    with pytest.raises(KeyError):
+        with eng:
+            raise KeyError("boom")
+    assert closed == [True, True]
