@@ -109,7 +109,10 @@ def build_kernels(force: bool = False, verbose: bool = False) -> Path:
     if not force and out.exists() and stamp.exists() and stamp.read_text() == digest:
         return out
     if not os.path.exists(NVCC):
-        raise RuntimeError(f"nvcc not found at {NVCC}; cannot build {out}")
+        raise RuntimeError(
+            f"nvcc not found at {NVCC}: cannot build {out.name}.  Install the CUDA toolkit (12.8 or newer: the kernels "
+            "are compiled for sm_100a) or point CUDA_HOME at it; no GPU is needed to compile.  `areno check` lists what "
+            "else the machine is missing.")
     with _build_lock():
         if not force and out.exists() and stamp.exists() and stamp.read_text() == digest:
             return out   # another process built it while we waited

@@ -428,3 +428,13 @@ def test_importing_the_sdk_and_cli_entry_points_stays_light():
             "'areno_b200.models') if m in sys.modules])")
     out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd=str(ROOT), timeout=120)
     assert out.returncode == 0 and out.stdout.strip() == "[]", out.stdout + out.stderr
+
+
+def test_a_missing_compiler_is_reported_with_the_next_step(monkeypatch):
+    from areno_b200 import build
+
+    monkeypatch.setattr(build, "NVCC", "/nonexistent/cuda/bin/nvcc")
+    with pytest.raises(RuntimeError, match="CUDA_HOME") as err:
+        build.build_kernels(force=True)
+    assert "12.8" in str(err.value) and "areno check" in str(err.value) and "no GPU is needed" in str(err.value)
+    build.ensure_built()                       # an up-to-date library needs no compiler at all
