@@ -77,12 +77,14 @@ def test_pack_indices_enumerate_tokens_and_actions_of_padded_rows(lengths, width
 
 
 @given(st.lists(st.integers(0, 3), max_size=12), st.lists(st.integers(0, 3), max_size=12))
+@settings(deadline=None)
 def test_common_prefix_is_the_longest_agreeing_run(a, b):
     n = common_prefix_len(a, b)
     assert a[:n] == b[:n] and (n == min(len(a), len(b)) or a[n] != b[n])
 
 
 @given(st.lists(st.floats(min_value=-100, max_value=100, allow_nan=False), max_size=16))
+@settings(deadline=None)
 def test_group_advantages_are_centred_and_finite(rewards):
     adv = compute_group_advantages(rewards)
     assert len(adv) == len(rewards) and all(np.isfinite(adv))
@@ -93,6 +95,7 @@ def test_group_advantages_are_centred_and_finite(rewards):
 
 
 @given(st.integers(1, 9), st.lists(st.integers(0, 50), max_size=40))
+@settings(deadline=None)
 def test_round_robin_dealing_and_merging_are_inverse(dp, items):
     parts = split_list_by_dp(items, dp)
     idx = split_list_by_dp(list(range(len(items))), dp)
@@ -103,6 +106,7 @@ def test_round_robin_dealing_and_merging_are_inverse(dp, items):
 
 
 @given(st.integers(1, 6), st.integers(0, 20))
+@settings(deadline=None)
 def test_pack_split_keeps_every_row_or_replicates_small_batches(dp, batch):
     pack = {"input_ids": torch.arange(batch * 2).view(batch, 2), "tag": "x"}
     shards = split_data_pack_by_dp(pack, dp)
