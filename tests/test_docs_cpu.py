@@ -7,7 +7,7 @@ import re
 from pathlib import Path
 
 ROOT = Path(__file__).resolve().parents[1]
-GUIDES = sorted((ROOT / "docs").glob("*.md")) + [ROOT / "README.md", ROOT / "DESIGN.md"]
+GUIDES = sorted((ROOT / "docs").glob("*.md")) + [ROOT / "README.md"]
 
 
 def _text(paths) -> str:
