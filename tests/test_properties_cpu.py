@@ -17,6 +17,10 @@ from areno_b200.engine.api import merge_rollouts_in_input_order, split_list_by_d
 from areno_b200.engine.inference import RolloutOutput
 from areno_b200.engine.training import balanced_partition, pack_into_bins, split_data_pack_by_dp
 
+# the same examples on every run: a property test must not be the one test that fails by chance somewhere else
+settings.register_profile("fixed", derandomize=True, deadline=None, database=None)
+settings.load_profile("fixed")
+
 lengths_st = st.lists(st.integers(min_value=1, max_value=2000), min_size=0, max_size=60)
 
 
@@ -89,8 +93,12 @@ def test_group_advantages_are_centred_and_finite(rewards):
     adv = compute_group_advantages(rewards)
     assert len(adv) == len(rewards) and all(np.isfinite(adv))
     if rewards:
-        assert abs(sum(adv)) < 1e-3 * max(1, len(adv))
-        order = np.argsort(rewards, kind="stable")
+        # computed in float32: the centred values carry rounding of the size of the rewards, which the division by a
+        # small spread magnifies; the sum is zero up to that
+        spread = float(np.std(np.asarray(rewards, dtype=np.float32))) + 1e-8
+        slack = 4 * float(np.finfo(np.float32).eps) * max(abs(r) for r in rewards) * len(rewards) / spread
+        assert abs(sum(adv)) < 1e-3 * len(adv) + slack
+        order = np.argsort(np.asarray(rewards, dtype=np.float32), kind="stable")
         assert all(adv[order[i]] <= adv[order[i + 1]] + 1e-9 for i in range(len(order) - 1))      # order preserved
 
 
