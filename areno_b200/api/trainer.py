@@ -96,6 +96,15 @@ class Trainer:
             if self._metrics is not None:
                 self._metrics.close()
 
+    def __enter__(self) -> "Trainer":
+        """``with Trainer(...) as trainer:`` initialises on entry (unless ``init`` was called already) and closes on exit."""
+        if not self._initialized:
+            self.init()
+        return self
+
+    def __exit__(self, *_exc) -> None:
+        self.close()
+
     def _require(self) -> tuple[Backend, Context]:
         if self._backend is None or self._ctx is None:
             raise RuntimeError("Trainer is not initialized")

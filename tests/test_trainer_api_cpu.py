@@ -189,3 +189,14 @@ def test_phase_timers_show_up_in_the_train_result():
         tracing.configure(nvtx=False, timers=False)
     assert "device_ms/train/forward" in out
     assert not any(k.startswith("device_ms/") for k in t.train([_seq()], lambda pack, lp: lp.sum()))
+
+
+def test_trainer_as_a_context_manager_closes_the_backend():
+    t = _trainer()
+    backend = t._backend
+    with t as entered:
+        assert entered is t and t._initialized
+        t.train([_seq()], lambda pack, lp: lp.sum())
+    assert backend.calls[-1] == "close" and t._backend is None
+    with pytest.raises(RuntimeError):
+        t.train([_seq()], lambda pack, lp: lp.sum())
