@@ -17,12 +17,38 @@ from areno_b200.parallel.context import single_process_context
 from tests.helpers import tiny_config
 
 
-@pytest.fixture(scope="module")
-def model():
-    single_process_context()
+def _dense():
     m = DenseCausalLM(tiny_config())
     init_weights(m, 7)
     return m
+
+
+def _hybrid():
+    """Softmax attention interleaved with gated delta rule layers: convolution and recurrent state per engine slot,
+    which must be reset when a slot is reused and rebuilt when an evicted sequence is prefilled again."""
+    from areno_b200.models.hybrid import HybridCausalLM
+    from tests.test_hybrid_cpu import hybrid_config
+
+    m = HybridCausalLM(hybrid_config())
+    init_weights(m, 7)
+    with torch.no_grad():
+        for layer in m._linear_layers():
+            layer.attn.A_log.fill_(-1.0)
+            layer.attn.dt_bias.fill_(0.5)
+    return m
+
+
+def _bailing():
+    """Decayed linear attention (a running state per slot) next to softmax attention and a grouped sigmoid router."""
+    from tests.test_bailing_cpu import _model, bailing_config
+
+    return _model(bailing_config(), seed=7)
+
+
+@pytest.fixture(scope="module", params=["dense", "hybrid", "bailing"])
+def model(request):
+    single_process_context()
+    return {"dense": _dense, "hybrid": _hybrid, "bailing": _bailing}[request.param]()
 
 
 def _alone(model, prompt, max_new, stop):
@@ -48,24 +74,15 @@ def _logits(model, tokens):
 NEAR_TIE = 2e-2
 
 
-@pytest.mark.parametrize("seed", range(8))
-def test_any_schedule_gives_the_stand_alone_greedy_tokens(model, seed):
-    single_process_context()
-    rng = random.Random(seed)
-    slots = rng.choice([2, 3, 4])
-    budget = rng.choice([16, 32, 64])
-    n_req = rng.randint(4, 8)
-    reqs = [([rng.randrange(3, 512) for _ in range(rng.randint(2, 90))], rng.randint(1, 14)) for _ in range(n_req)]
+def _run_and_check(model, reqs, *, slots, budget, num_pages, stop, arrivals, tag):
+    """Drive the engine step by step with the given arrivals and check every finished request against the model run on
+    its own.  Returns how many sequences were evicted for lack of pages and resumed."""
+    n_req = len(reqs)
     longest = max(len(p) + n for p, n in reqs)
-    per_seq = (longest + 63) // 64
-    num_pages = rng.choice([per_seq + 1, per_seq * 2, per_seq * slots])          # tight pools force evictions
-    eng = InferenceEngine(model, 512, "cpu", max_slots=slots, max_model_len=per_seq * 64, max_prefill_tokens=budget,
-                          num_pages=num_pages)
-    # a stop token that some stand-alone generation actually produces, so that both finish reasons occur
-    probe, _ = _alone(model, reqs[0][0], reqs[0][1], ())
-    stop = (probe[len(probe) // 2],) if rng.random() < 0.7 else ()
+    eng = InferenceEngine(model, 512, "cpu", max_slots=slots, max_model_len=(longest + 63) // 64 * 64,
+                          max_prefill_tokens=budget, num_pages=num_pages)
     eng.begin(SamplingParams(temperature=0.0), stop, 16)
-    arrivals = sorted((rng.randint(0, 25), i) for i in range(n_req))
+    arrivals = sorted(arrivals)
     rid_of, finished, step = {}, {}, 0
     while len(finished) < n_req:
         while arrivals and arrivals[0][0] <= step:
@@ -78,12 +95,12 @@ def test_any_schedule_gives_the_stand_alone_greedy_tokens(model, seed):
     exact = 0
     for i, (prompt, max_new) in enumerate(reqs):
         got = finished[i]
-        want, reason = _alone(model, prompt, max_new, stop)
+        want, _reason = _alone(model, prompt, max_new, stop)
         exact += got.tokens == want
         # every token is the greedy choice given the tokens before it, up to near-ties
         logits = _logits(model, prompt + got.tokens)[len(prompt) - 1:-1]
         chosen = logits.gather(-1, torch.tensor(got.tokens)[:, None]).squeeze(-1)
-        assert bool((chosen >= logits.max(-1).values - NEAR_TIE).all()), (seed, i, len(prompt), max_new)
+        assert bool((chosen >= logits.max(-1).values - NEAR_TIE).all()), (tag, i, len(prompt), max_new)
         # and it ended where it had to: at its first stop token, or at its budget without having met one
         if got.reason == "stop":
             assert got.tokens[-1] in stop and not set(got.tokens[:-1]) & set(stop) and len(got.tokens) <= max_new
@@ -93,3 +110,34 @@ def test_any_schedule_gives_the_stand_alone_greedy_tokens(model, seed):
         assert torch.allclose(ref_lp, torch.tensor(got.logprobs), atol=3e-2)
     assert exact >= n_req // 2                 # near-ties are rare: most requests match token for token
     assert eng.idle and eng.sched.num_free_pages == num_pages
+    return sum(1 for r in eng._requests.values() if r.kept_tokens)
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_any_schedule_gives_the_stand_alone_greedy_tokens(model, seed):
+    single_process_context()
+    rng = random.Random(seed)
+    slots = rng.choice([2, 3, 4])
+    budget = rng.choice([16, 32, 64])
+    n_req = rng.randint(4, 8)
+    reqs = [([rng.randrange(3, 512) for _ in range(rng.randint(2, 90))], rng.randint(1, 14)) for _ in range(n_req)]
+    per_seq = (max(len(p) + n for p, n in reqs) + 63) // 64
+    num_pages = rng.choice([per_seq + 1, per_seq * 2, per_seq * slots])
+    # a stop token that some stand-alone generation actually produces, so that both finish reasons occur
+    probe, _ = _alone(model, reqs[0][0], reqs[0][1], ())
+    stop = (probe[len(probe) // 2],) if rng.random() < 0.7 else ()
+    arrivals = [(rng.randint(0, 25), i) for i in range(n_req)]
+    _run_and_check(model, reqs, slots=slots, budget=budget, num_pages=num_pages, stop=stop, arrivals=arrivals, tag=seed)
+
+
+@pytest.mark.parametrize("seed", range(3))
+def test_sequences_that_outgrow_a_tight_page_pool_are_evicted_and_resume(model, seed):
+    """Prompts that end just below a page boundary, three of them decoding at once over four pages: when they cross
+    the boundary together there is no page for everybody, some go back to the queue with what they have generated and
+    are prefilled again later (for the stateful families: with their recurrent state rebuilt from those tokens)."""
+    single_process_context()
+    rng = random.Random(100 + seed)
+    reqs = [([rng.randrange(3, 512) for _ in range(rng.randint(58, 62))], rng.randint(10, 14)) for _ in range(5)]
+    evicted = _run_and_check(model, reqs, slots=3, budget=64, num_pages=4, stop=(), arrivals=[(0, i) for i in range(5)],
+                             tag=("tight", seed))
+    assert evicted >= 1
