@@ -17,6 +17,18 @@ from areno_b200.parallel.context import single_process_context
 from tests.helpers import tiny_config
 
 
+@pytest.fixture(autouse=True)
+def _fp32_pages(monkeypatch):
+    """KV pages in fp32 instead of bf16: the comparison is about scheduling and state, not about page precision."""
+    from areno_b200.ops import paged_attention as pa
+
+    def fp32_pages(num_pages, kv_heads, head_dim, device, fp8=False):
+        shape = (num_pages, kv_heads, pa.PAGE, head_dim)
+        return torch.zeros(shape, device=device), torch.zeros(shape, device=device), None, None
+
+    monkeypatch.setattr(pa, "alloc_kv_cache", fp32_pages)
+
+
 def _dense():
     m = DenseCausalLM(tiny_config())
     init_weights(m, 7)
@@ -45,10 +57,28 @@ def _bailing():
     return _model(bailing_config(), seed=7)
 
 
-@pytest.fixture(scope="module", params=["dense", "hybrid", "bailing"])
+def _gemma4():
+    """Sliding-window and global layers with their own head geometry, tail layers that share the KV of earlier ones,
+    per-layer input embeddings, dense + MoE feed-forward, soft-capped logits."""
+    from tests.test_gemma4_cpu import _model, gemma_config
+
+    return _model(gemma_config(), seed=7)
+
+
+def _moe():
+    from areno_b200.models import registry
+    from tests.test_moe_cpu import moe_config
+
+    adapter = registry.get_adapter("qwen3_moe")
+    m = adapter.build(moe_config())
+    adapter.init_random(m, 7)
+    return m
+
+
+@pytest.fixture(scope="module", params=["dense", "hybrid", "bailing", "gemma4", "moe"])
 def model(request):
     single_process_context()
-    return {"dense": _dense, "hybrid": _hybrid, "bailing": _bailing}[request.param]()
+    return {"dense": _dense, "hybrid": _hybrid, "bailing": _bailing, "gemma4": _gemma4, "moe": _moe}[request.param]()
 
 
 def _alone(model, prompt, max_new, stop):
@@ -69,9 +99,9 @@ def _logits(model, tokens):
         return model.compute_logits(h).float()
 
 
-# The engine reads keys and values back from 16-bit pages, the stand-alone pass keeps them in fp32: a token whose
-# logit is within this margin of the best one counts as the greedy choice (random-init logits have many near-ties).
-NEAR_TIE = 2e-2
+# Cached and stand-alone passes add numbers in different orders: a token whose logit is within this margin of the best
+# one counts as the greedy choice (random-init logits have many near-ties).
+NEAR_TIE = 2e-3
 
 
 def _run_and_check(model, reqs, *, slots, budget, num_pages, stop, arrivals, tag):
@@ -107,7 +137,7 @@ def _run_and_check(model, reqs, *, slots, budget, num_pages, stop, arrivals, tag
         else:
             assert got.reason == "length" and len(got.tokens) == max_new and not set(got.tokens) & set(stop)
         ref_lp = torch.log_softmax(logits, -1).gather(-1, torch.tensor(got.tokens)[:, None]).squeeze(-1)
-        assert torch.allclose(ref_lp, torch.tensor(got.logprobs), atol=3e-2)
+        assert torch.allclose(ref_lp, torch.tensor(got.logprobs), atol=3e-3)
     assert exact >= n_req // 2                 # near-ties are rare: most requests match token for token
     assert eng.idle and eng.sched.num_free_pages == num_pages
     return sum(1 for r in eng._requests.values() if r.kept_tokens)
