@@ -171,3 +171,22 @@ def test_sequences_that_outgrow_a_tight_page_pool_are_evicted_and_resume(model, 
     evicted = _run_and_check(model, reqs, slots=3, budget=64, num_pages=4, stop=(), arrivals=[(0, i) for i in range(5)],
                              tag=("tight", seed))
     assert evicted >= 1
+
+
+def test_a_packed_training_batch_equals_every_sequence_on_its_own(model):
+    """Variable-length packing must not leak anything across sequence boundaries: not attention, not a sliding window,
+    and not the convolution or recurrent state of the linear-attention families."""
+    single_process_context()
+    g = torch.Generator().manual_seed(11)
+    lens = [9, 1, 23, 14]
+    rows = [torch.randint(3, 512, (n,), generator=g) for n in lens]
+    ids = torch.cat(rows)
+    pos = torch.cat([torch.arange(n) for n in lens])
+    with torch.no_grad():
+        packed = model(ids, pos, TrainMeta(build_varlen_meta(lens), False)).hidden_states
+        k = 0
+        for row in rows:
+            n = len(row)
+            alone = model(row, torch.arange(n), TrainMeta(build_varlen_meta([n]), False)).hidden_states
+            assert torch.allclose(packed[k:k + n], alone, atol=2e-5), (n, float((packed[k:k + n] - alone).abs().max()))
+            k += n
