@@ -190,3 +190,31 @@ def test_a_packed_training_batch_equals_every_sequence_on_its_own(model):
             alone = model(row, torch.arange(n), TrainMeta(build_varlen_meta([n]), False)).hidden_states
             assert torch.allclose(packed[k:k + n], alone, atol=2e-5), (n, float((packed[k:k + n] - alone).abs().max()))
             k += n
+
+
+def test_recompute_reproduces_the_gradients_of_every_family(model):
+    """Layers that are recomputed in backward must rebuild exactly what they produced in forward, including routing
+    decisions and the scans of the linear-attention layers."""
+    single_process_context()
+    g = torch.Generator().manual_seed(12)
+    lens = [10, 17]
+    ids = torch.randint(3, 512, (sum(lens),), generator=g)
+    pos = torch.cat([torch.arange(n) for n in lens])
+
+    def grads(ckpt):
+        for p in model.parameters():
+            p.grad = None
+        model.train()
+        out = model(ids, pos, TrainMeta(build_varlen_meta(lens), activation_checkpointing=ckpt))
+        loss = out.hidden_states.float().pow(2).mean()
+        loss.backward()
+        model.eval()
+        return float(loss.detach()), {n: p.grad.clone() for n, p in model.named_parameters() if p.grad is not None}
+
+    base_loss, base = grads(False)
+    loss, got = grads(True)
+    assert loss == pytest.approx(base_loss, rel=1e-6) and got.keys() == base.keys() and len(base) > 4
+    for name in base:
+        assert torch.allclose(got[name], base[name], atol=1e-6, rtol=1e-4), name
+    for p in model.parameters():
+        p.grad = None
