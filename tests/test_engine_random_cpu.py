@@ -1,7 +1,10 @@
 """Randomised schedules through the inference engine on the CPU: requests of random lengths and budgets arrive at random
 steps, slots, prefill budget and page pool are small enough to force queueing, chunked prefill and evictions.  Greedy
 tokens must equal what the model generates for each prompt on its own with a full forward pass every step, whatever
-the schedule was; stop tokens end a sequence exactly where the stand-alone generation meets one."""
+the schedule was; stop tokens end a sequence exactly where the stand-alone generation meets one.  Every model family
+takes the same walks (their per-slot state has to survive slot reuse and evictions), and two equivalences that the
+families' own state handling could break are checked for all of them: a packed training batch against its sequences
+one by one, and gradients with and without recomputed layers."""
 
 from __future__ import annotations
 
